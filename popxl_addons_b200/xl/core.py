@@ -1,0 +1,890 @@
+"""Graph substrate: Ir / Graph / Op / Tensor / TensorSpec / ReplicaGrouping and the build-time context stack.
+
+A model is described by running ordinary Python (`Module.build`, user functions) against symbolic `Tensor`s; every
+operator call appends an `Op` to the graph on top of the context stack. Nothing touches a device while building: shapes
+and dtypes are inferred by running each op's reference implementation on torch *meta* tensors. A `Session` later
+interprets the recorded graphs on real `torch.Tensor`s (CPU for tests and oracles, CUDA for production, one process
+per GPU).
+
+This file supplies the part of the `popxl` surface that popxl_addons relies on (module.py:8-12,
+variable_factory.py:9-14, transforms/*.py): `Ir`, `Graph`, `Tensor`, `TensorSpec`, `TensorByRef`, `variable`,
+`constant`, `graph_input`, `graph_output`, `name_scope`, `in_sequence`, `ipu`, `io_tiles`, `gcg/gir/gmg`,
+`ReplicaGrouping` and op-created hooks (transforms/pipelining.py:464-470).
+"""
+import contextlib
+import inspect
+import itertools
+import math
+from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Tuple, Union
+
+import numpy as np
+import torch
+
+from . import dtypes as _dt
+from .dtypes import dtype
+
+# ---------------------------------------------------------------------------------------------------------------
+# build-time context
+# ---------------------------------------------------------------------------------------------------------------
+
+
+class _BuildState:
+    def __init__(self):
+        self.graphs: List["Graph"] = []
+        self.scopes: List[str] = []
+        self.sequence: List[Any] = []
+        self.devices: List[int] = []
+        self.tile_sets: List[str] = []
+        self.merge_exchange: int = 0
+
+
+_STATE = _BuildState()
+
+
+def gcg() -> "Graph":
+    """Graph currently being built."""
+    if not _STATE.graphs:
+        raise RuntimeError("Trying to access a graph, but no graph has been selected. Hint - try performing the "
+                           "operations in a context of `with graph:`")
+    return _STATE.graphs[-1]
+
+
+def gir() -> "Ir":
+    return gcg().ir
+
+
+def gmg() -> "Graph":
+    return gir().main_graph
+
+
+def get_current_graph() -> "Graph":
+    return gcg()
+
+
+@contextlib.contextmanager
+def name_scope(name: str):
+    """Prefix names of tensors created inside with `name/`."""
+    _STATE.scopes.append(name)
+    try:
+        yield
+    finally:
+        _STATE.scopes.pop()
+
+
+def current_scope() -> str:
+    return "/".join(_STATE.scopes)
+
+
+@contextlib.contextmanager
+def in_sequence(enabled: Union[bool, str] = True):
+    """Ops are always executed in recorded order by the interpreter, so this only records the annotation."""
+    _STATE.sequence.append(enabled)
+    try:
+        yield
+    finally:
+        _STATE.sequence.pop()
+
+
+@contextlib.contextmanager
+def ipu(index: int):
+    """Place ops on device slot `index` (a pipeline stage's GPU). Kept under the reference's name for API parity."""
+    _STATE.devices.append(int(index))
+    try:
+        yield
+    finally:
+        _STATE.devices.pop()
+
+
+device = ipu
+
+
+def current_device() -> int:
+    return _STATE.devices[-1] if _STATE.devices else 0
+
+
+@contextlib.contextmanager
+def io_tiles():
+    """Ops inside run on the copy/IO stream instead of the compute stream (overlapped IO)."""
+    _STATE.tile_sets.append("io")
+    try:
+        yield
+    finally:
+        _STATE.tile_sets.pop()
+
+
+@contextlib.contextmanager
+def main_tiles():
+    _STATE.tile_sets.append("compute")
+    try:
+        yield
+    finally:
+        _STATE.tile_sets.pop()
+
+
+def current_tile_set() -> str:
+    return _STATE.tile_sets[-1] if _STATE.tile_sets else "compute"
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# ReplicaGrouping
+# ---------------------------------------------------------------------------------------------------------------
+
+
+class ReplicaGrouping:
+    """Partition of the `num_replicas` replicas (= ranks) into equally sized groups.
+
+    With `(stride s, group_size g)` replica `r` belongs to `{b*s*g + (r mod s) + j*s : j < g}`, `b = r div (s*g)`;
+    its position inside the group is `(r mod s*g) div s`. A grouping can also be given as an explicit assignment
+    (group index per replica), which is what `transpose()` produces when the complement is not expressible as
+    (stride, size). On one NVSwitch box every grouping costs the same, so a group is just a rank list.
+    """
+
+    def __init__(self, num_replicas: int, stride: int = 1, group_size: Optional[int] = None,
+                 assignment: Optional[Sequence[int]] = None):
+        self.num_replicas = int(num_replicas)
+        if assignment is not None:
+            self._assignment = [int(a) for a in assignment]
+            assert len(self._assignment) == self.num_replicas
+            self._stride, self._group_size = None, None
+            sizes = {}
+            for a in self._assignment:
+                sizes[a] = sizes.get(a, 0) + 1
+            if len(set(sizes.values())) != 1:
+                raise ValueError("All replica groups must have the same size")
+            self._group_size = next(iter(sizes.values()))
+            self._canonicalise()
+        else:
+            if group_size is None:
+                group_size = self.num_replicas // stride
+            stride, group_size = int(stride), int(group_size)
+            if group_size == 1:
+                stride = 1
+            if stride < 1 or group_size < 1 or self.num_replicas % (stride * group_size) != 0:
+                raise ValueError(
+                    f"Invalid replica grouping: stride={stride} group_size={group_size} "
+                    f"num_replicas={self.num_replicas}")
+            self._stride, self._group_size = stride, group_size
+            self._assignment = [self._group_of(r) for r in range(self.num_replicas)]
+
+    def _group_of(self, r: int) -> int:
+        s, g = self._stride, self._group_size
+        return (r // (s * g)) * s + (r % s)
+
+    def _canonicalise(self):
+        """If an explicit assignment equals some (stride, size) grouping, adopt that form (makes equality simple)."""
+        n, g = self.num_replicas, self._group_size
+        for s in range(1, n + 1):
+            if n % (s * g) != 0:
+                continue
+            if g == 1 and s != 1:
+                continue
+            cand = [(r // (s * g)) * s + (r % s) for r in range(n)]
+            if _same_partition(cand, self._assignment):
+                self._stride = s
+                self._assignment = cand
+                return
+
+    # -- properties -------------------------------------------------------------------------------------------
+    @property
+    def stride(self) -> int:
+        if self._stride is None:
+            raise ValueError("This replica grouping is defined by an explicit assignment and has no stride")
+        return self._stride
+
+    @property
+    def group_size(self) -> int:
+        return self._group_size
+
+    @property
+    def num_groups(self) -> int:
+        return self.num_replicas // self._group_size
+
+    @property
+    def assignment(self) -> List[int]:
+        return list(self._assignment)
+
+    @property
+    def is_const(self) -> bool:
+        return self._stride is None
+
+    @property
+    def const_rg(self):
+        return self
+
+    @property
+    def groups(self) -> List[List[int]]:
+        """Rank lists, ordered by group index; members in increasing replica order (= shard order)."""
+        out: Dict[int, List[int]] = {}
+        for r, a in enumerate(self._assignment):
+            out.setdefault(a, []).append(r)
+        return [out[k] for k in sorted(out)]
+
+    def group_of(self, replica: int) -> List[int]:
+        a = self._assignment[replica]
+        return [r for r, x in enumerate(self._assignment) if x == a]
+
+    def group_index(self, replica: int) -> int:
+        return self._assignment[replica]
+
+    def index_in_group(self, replica: int) -> int:
+        return self.group_of(replica).index(replica)
+
+    def transpose(self) -> "ReplicaGrouping":
+        """Complementary grouping: replicas at the same position of different groups form the new groups.
+        (TP grouping <-> DP grouping.)"""
+        assign = [self.index_in_group(r) for r in range(self.num_replicas)]
+        return ReplicaGrouping(self.num_replicas, assignment=assign)
+
+    def __eq__(self, other):
+        return (isinstance(other, ReplicaGrouping) and self.num_replicas == other.num_replicas
+                and _same_partition(self._assignment, other._assignment))
+
+    def __hash__(self):
+        return hash((self.num_replicas, tuple(tuple(g) for g in self.groups)))
+
+    def __repr__(self):
+        if self._stride is not None:
+            return (f"ReplicaGrouping(num_replicas={self.num_replicas}, stride={self._stride}, "
+                    f"group_size={self._group_size}, num_groups={self.num_groups})")
+        return f"ReplicaGrouping(num_replicas={self.num_replicas}, assignment={self._assignment})"
+
+
+def _same_partition(a: Sequence[int], b: Sequence[int]) -> bool:
+    fwd, bwd = {}, {}
+    for x, y in zip(a, b):
+        if fwd.setdefault(x, y) != y or bwd.setdefault(y, x) != x:
+            return False
+    return True
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Tensors
+# ---------------------------------------------------------------------------------------------------------------
+
+
+class TensorSpec:
+    """Shape + dtype (+ full `meta_shape` for a replica-sharded tensor): enough to create a graph input."""
+
+    def __init__(self, shape: Iterable[int], dtype: dtype, meta_shape: Optional[Iterable[int]] = None):
+        self.shape = tuple(int(s) for s in shape)
+        self.dtype = _dt.dtype.as_dtype(dtype)
+        self.meta_shape = tuple(int(s) for s in meta_shape) if meta_shape else ()
+
+    @property
+    def nelms(self) -> int:
+        return int(np.prod(self.shape)) if self.shape else 1
+
+    def __repr__(self):
+        ms = f", meta_shape={self.meta_shape}" if self.meta_shape else ""
+        return f"TensorSpec(shape={self.shape}, dtype={self.dtype}{ms})"
+
+    def __eq__(self, other):
+        return (isinstance(other, TensorSpec) and self.shape == other.shape and self.dtype == other.dtype
+                and self.meta_shape == other.meta_shape)
+
+    def __hash__(self):
+        return hash((self.shape, self.dtype, self.meta_shape))
+
+
+class Tensor:
+    """Symbolic value in a graph. Python operators record ops; identity (not value) defines equality/hashing."""
+
+    _counter = itertools.count()
+    kind = "act"
+
+    def __init__(self, graph: "Graph", shape, dtype_: dtype, name: Optional[str] = None, meta_shape=None,
+                 producer: Optional["Op"] = None):
+        self.graph = graph
+        self._shape = tuple(int(s) for s in shape)
+        self._dtype = _dt.dtype.as_dtype(dtype_)
+        self.meta_shape = tuple(int(s) for s in meta_shape) if meta_shape else ()
+        self.producer = producer
+        self.uid = next(Tensor._counter)
+        base = name if name else "t"
+        scope = current_scope()
+        full = f"{scope}/{base}" if scope else base
+        self.id = graph._unique_tensor_id(full)
+        self.device_index = current_device()
+        self.tile_set = current_tile_set()
+        graph._tensors.append(self)
+
+    # -- basic properties ---------------------------------------------------------------------------------------
+    @property
+    def name(self) -> str:
+        return self.id
+
+    @property
+    def shape(self) -> Tuple[int, ...]:
+        return self._shape
+
+    @property
+    def dtype(self) -> dtype:
+        return self._dtype
+
+    @property
+    def ir(self) -> "Ir":
+        return self.graph.ir
+
+    @property
+    def spec(self) -> TensorSpec:
+        return TensorSpec(self._shape, self._dtype, self.meta_shape)
+
+    @property
+    def nelms(self) -> int:
+        return int(np.prod(self._shape)) if self._shape else 1
+
+    @property
+    def rank(self) -> int:
+        return len(self._shape)
+
+    @property
+    def ipu(self) -> int:
+        return self.device_index
+
+    @property
+    def in_sync_with(self):
+        return self
+
+    def __repr__(self):
+        ms = f", meta_shape={self.meta_shape}" if self.meta_shape else ""
+        return f"Tensor[{self.id} {self._dtype} {self._shape}{ms}]"
+
+    def __hash__(self):
+        return self.uid
+
+    def __eq__(self, other):
+        return self is other
+
+    def __ne__(self, other):
+        return self is not other
+
+    def __len__(self):
+        if not self._shape:
+            raise TypeError("len() of a 0-d tensor")
+        return self._shape[0]
+
+    # -- operators (defer to the op library) --------------------------------------------------------------------
+    def _ops(self):
+        from . import ops
+
+        return ops
+
+    def _lift(self, other) -> "Tensor":
+        if isinstance(other, Tensor):
+            return other
+        dt = self._dtype
+        if isinstance(other, (bool, int, float)):
+            return constant(other, dt)
+        return constant(other, dt if np.asarray(other).dtype.kind == np.dtype(dt.as_numpy()).kind else None)
+
+    def __add__(self, o):
+        return self._ops().add(self, self._lift(o))
+
+    def __radd__(self, o):
+        return self._ops().add(self._lift(o), self)
+
+    def __sub__(self, o):
+        return self._ops().sub(self, self._lift(o))
+
+    def __rsub__(self, o):
+        return self._ops().sub(self._lift(o), self)
+
+    def __mul__(self, o):
+        return self._ops().mul(self, self._lift(o))
+
+    def __rmul__(self, o):
+        return self._ops().mul(self._lift(o), self)
+
+    def __truediv__(self, o):
+        return self._ops().div(self, self._lift(o))
+
+    def __rtruediv__(self, o):
+        return self._ops().div(self._lift(o), self)
+
+    def __mod__(self, o):
+        return self._ops().fmod(self, self._lift(o))
+
+    def __pow__(self, o):
+        return self._ops().pow(self, self._lift(o))
+
+    def __neg__(self):
+        return self._ops().negate(self)
+
+    def __matmul__(self, o):
+        return self._ops().matmul(self, o)
+
+    def __rmatmul__(self, o):
+        return self._ops().matmul(self._lift(o), self)
+
+    def __getitem__(self, key):
+        return self._ops().subscript(self, key)
+
+    def __iadd__(self, o):
+        return self._ops().add_(self, self._lift(o))
+
+    @property
+    def T(self) -> "Tensor":
+        return self._ops().transpose(self)
+
+    @property
+    def T_(self) -> "Tensor":
+        return self._ops().transpose(self)
+
+    def transpose(self, permutation: Optional[Iterable[int]] = None) -> "Tensor":
+        return self._ops().transpose(self, permutation)
+
+    transpose_ = transpose
+
+    def reshape(self, shape: Iterable[int]) -> "Tensor":
+        return self._ops().reshape(self, shape)
+
+    reshape_ = reshape
+
+    def flatten(self) -> "Tensor":
+        return self._ops().reshape(self, (-1,))
+
+    flatten_ = flatten
+
+    def detach(self) -> "Tensor":
+        return self._ops().detach(self)
+
+    detach_ = detach
+
+    def copy_to_ipu(self, destination: int, source: Optional[int] = None) -> "Tensor":
+        return self._ops().ipu_copy(self, destination, source)
+
+    def diag(self):
+        raise NotImplementedError
+
+
+class Variable(Tensor):
+    """Persistent tensor owned by the main graph. Replicas in the same group of `replica_grouping` hold identical
+    values; with `num_groups > 1` the host-side array has a leading `num_groups` axis."""
+
+    kind = "variable"
+
+    def __init__(self, graph, shape, dtype_, name=None, meta_shape=None, replica_grouping=None,
+                 remote_buffer=None, entry: Optional[int] = None, shard_group=None):
+        super().__init__(graph, shape, dtype_, name, meta_shape)
+        self.replica_grouping: ReplicaGrouping = replica_grouping or graph.ir.replica_grouping()
+        self.remote_buffer = remote_buffer
+        self.entry = entry
+        # group across which a replica-sharded variable is split (None: not sharded)
+        self.shard_group: Optional[ReplicaGrouping] = shard_group
+        self.retrieval_mode = "one_per_group"
+
+    @property
+    def shape_on_host(self) -> Tuple[int, ...]:
+        base = self.meta_shape if (self.meta_shape and self.shard_group is not None) else self._shape
+        if self.replica_grouping.num_groups > 1:
+            return (self.replica_grouping.num_groups, *base)
+        return tuple(base)
+
+    @property
+    def shape_on_replica(self) -> Tuple[int, ...]:
+        return self._shape
+
+    @property
+    def is_remote(self) -> bool:
+        return self.remote_buffer is not None
+
+
+class Constant(Tensor):
+    kind = "constant"
+
+    def __init__(self, graph, data: torch.Tensor, name=None):
+        super().__init__(graph, tuple(data.shape), _dt.dtype.as_dtype(data.dtype), name)
+        self.data = data
+
+
+class TensorByRef(Tensor):
+    """Annotation type: a `create_graph` parameter annotated with it becomes a by-reference graph input."""
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Ops and graphs
+# ---------------------------------------------------------------------------------------------------------------
+
+
+class Op:
+    """One recorded operation: `outputs = opdef(inputs, **attrs)`."""
+
+    __slots__ = ("opdef", "inputs", "outputs", "attrs", "graph", "name", "device_index", "tile_set", "stage",
+                 "debug", "uid", "__weakref__")
+    _counter = itertools.count()
+
+    def __init__(self, opdef, inputs, attrs, graph):
+        self.opdef = opdef
+        self.inputs: List[Tensor] = list(inputs)
+        self.outputs: List[Tensor] = []
+        self.attrs: Dict[str, Any] = attrs
+        self.graph = graph
+        self.name = opdef.name
+        self.device_index = current_device()
+        self.tile_set = current_tile_set()
+        self.stage = None
+        self.debug = None
+        self.uid = next(Op._counter)
+
+    @property
+    def op_type(self) -> str:
+        return self.opdef.name
+
+    def opid(self):
+        return self.opdef.name
+
+    def __repr__(self):
+        ins = ", ".join(t.id for t in self.inputs)
+        outs = ", ".join(t.id for t in self.outputs)
+        return f"{outs} = {self.opdef.name}({ins})"
+
+
+class Graph:
+    def __init__(self, ir: "Ir", name: str):
+        self.ir = ir
+        self.name = name
+        self.id = name
+        self._inputs: List[Tensor] = []
+        self._outputs: List[Tensor] = []
+        self._by_ref: set = set()
+        self.ops: List[Op] = []
+        self._tensors: List[Tensor] = []
+        self._ids: Dict[str, int] = {}
+        self._hooks: Dict[int, Callable] = {}
+        self._hook_ids = itertools.count()
+        self.can_autodiff = True
+        self.hints: Dict[str, Any] = {}
+
+    # -- context ------------------------------------------------------------------------------------------------
+    def __enter__(self):
+        _STATE.graphs.append(self)
+        return self
+
+    def __exit__(self, *exc):
+        _STATE.graphs.pop()
+        return False
+
+    def _unique_tensor_id(self, name: str) -> str:
+        n = self._ids.get(name, 0)
+        self._ids[name] = n + 1
+        return name if n == 0 else f"{name}__{n}"
+
+    # -- structure ----------------------------------------------------------------------------------------------
+    @property
+    def inputs(self) -> Tuple[Tensor, ...]:
+        return tuple(self._inputs)
+
+    @property
+    def outputs(self) -> Tuple[Tensor, ...]:
+        return tuple(self._outputs)
+
+    @property
+    def tensors(self) -> Tuple[Tensor, ...]:
+        return tuple(self._tensors)
+
+    @property
+    def variables(self) -> Tuple[Variable, ...]:
+        return tuple(t for t in self._tensors if isinstance(t, Variable))
+
+    @property
+    def constants(self) -> Tuple[Constant, ...]:
+        return tuple(t for t in self._tensors if isinstance(t, Constant))
+
+    @property
+    def inputs_by_name(self) -> Dict[str, Tensor]:
+        return {t.name: t for t in self._inputs}
+
+    @property
+    def main_graph(self) -> "Graph":
+        return self.ir.main_graph
+
+    def is_by_ref(self, t: Tensor) -> bool:
+        return t in self._by_ref
+
+    def get_input_tensors(self):
+        return self.inputs
+
+    def get_output_tensors(self):
+        return self.outputs
+
+    def called_graphs(self) -> List["Graph"]:
+        seen, out = set(), []
+        for op in self.ops:
+            for key in ("graph", "body"):
+                g = op.attrs.get(key)
+                if isinstance(g, Graph) and id(g) not in seen:
+                    seen.add(id(g))
+                    out.append(g)
+        return out
+
+    def __contains__(self, t) -> bool:
+        return isinstance(t, Tensor) and t.graph is self
+
+    # -- op hooks (used by the pipelining transform to see every op as it is created) ---------------------------
+    def register_op_created_hook(self, fn: Callable[[Op], None]) -> int:
+        h = next(self._hook_ids)
+        self._hooks[h] = fn
+        return h
+
+    def remove_op_created_hook(self, handle: int):
+        self._hooks.pop(handle, None)
+
+    def _op_created(self, op: Op):
+        for fn in list(self._hooks.values()):
+            fn(op)
+
+    def __repr__(self):
+        return f"Graph[{self.name}]"
+
+    def __hash__(self):
+        return id(self)
+
+    def __eq__(self, other):
+        return self is other
+
+    def print_ops(self) -> str:
+        return "\n".join(repr(o) for o in self.ops)
+
+
+class _PbIrShim:
+    """Minimal stand-in for the handful of low-level IR queries that user scripts written for the reference make."""
+
+    def __init__(self, ir):
+        self._ir = ir
+        self._options = type("SessionOptions", (), {})()
+
+    def getAllGraphs(self):
+        return list(self._ir.graphs)
+
+    def getSessionOptions(self):
+        return self._options
+
+    def logIr(self):
+        for g in self._ir.graphs:
+            print(f"--- {g.name}\n{g.print_ops()}")
+
+
+class Ir:
+    """Container of all graphs of one program plus the replication setup.
+
+    `replication="popdist"` (or "distributed") takes the replica count from `torch.distributed` / the launcher
+    environment: one replica per process, one process per GPU.
+    """
+
+    def __init__(self, replication: Union[int, str] = 1):
+        self.graphs: List[Graph] = []
+        self._graph_counter = itertools.count()
+        self.main_graph = Graph(self, "main")
+        self.graphs.append(self.main_graph)
+        self.distributed = False
+        if isinstance(replication, str):
+            import os
+
+            self.distributed = True
+            self._replication_factor = int(os.environ.get("WORLD_SIZE", "1"))
+        else:
+            self._replication_factor = int(replication)
+        self.num_host_transfers = 1
+        self.num_device_transfers = 1
+        self._pb_ir = _PbIrShim(self)
+        self.initial_values: Dict[Variable, Any] = {}
+        self.remote_buffers: List[Any] = []
+        self.streams: List[Any] = []
+        self.options: Dict[str, Any] = {}
+
+    # -- replication ----------------------------------------------------------------------------------------------
+    @property
+    def replication_factor(self) -> int:
+        return self._replication_factor
+
+    @replication_factor.setter
+    def replication_factor(self, n: int):
+        self._replication_factor = int(n)
+
+    @property
+    def instance_replication_factor(self) -> int:
+        """Replicas hosted by this process: all of them in single-process simulation, one when launched one process
+        per GPU."""
+        return 1 if self.distributed else self._replication_factor
+
+    def replica_grouping(self, stride: int = 1, group_size: Optional[int] = None) -> ReplicaGrouping:
+        return ReplicaGrouping(self._replication_factor, stride, group_size)
+
+    def replica_grouping_from_assignments(self, assignment: Sequence[int]) -> ReplicaGrouping:
+        return ReplicaGrouping(self._replication_factor, assignment=assignment)
+
+    # -- graph creation -------------------------------------------------------------------------------------------
+    def _new_graph_name(self, base: str) -> str:
+        return f"{base}_subgraph({next(self._graph_counter)})"
+
+    def create_empty_graph(self, name: Optional[str] = None) -> Graph:
+        g = Graph(self, self._new_graph_name(name or "graph"))
+        self.graphs.append(g)
+        return g
+
+    def create_graph(self, fn: Callable, *args, **kwargs) -> Graph:
+        """Trace `fn` into a new graph. Tensor / TensorSpec arguments (also inside lists) become graph inputs of the
+        same spec; anything else is passed through unchanged. The returned tensors become the graph outputs."""
+        if hasattr(fn, "build") and not inspect.isfunction(fn) and not inspect.ismethod(fn):
+            base = type(fn).__name__
+            sig_target = fn.build
+        else:
+            base = getattr(fn, "__name__", type(fn).__name__)
+            sig_target = fn
+        try:
+            sig = inspect.signature(sig_target)
+            bound = sig.bind(*args, **kwargs)
+        except TypeError as e:
+            raise ValueError(
+                f"The arguments, {args} and {kwargs}, do not match the signature of the function {base}: {e}"
+            ) from None
+        g = self.create_empty_graph(base)
+        new_args: List[Any] = []
+        new_kwargs: Dict[str, Any] = {}
+
+        def convert(value, pname, by_ref):
+            if isinstance(value, (Tensor, TensorSpec)):
+                ref = by_ref or (isinstance(value, Tensor) and value.graph.is_by_ref(value) and False)
+                return graph_input(value.shape, value.dtype, pname, by_ref=ref, meta_shape=value.meta_shape)
+            if isinstance(value, (list, tuple)) and value and all(isinstance(v, (Tensor, TensorSpec)) for v in value):
+                return type(value)(convert(v, f"{pname}_{i}", by_ref) for i, v in enumerate(value))
+            return value
+
+        with g:
+            for pname, value in bound.arguments.items():
+                param = sig.parameters[pname]
+                ann = param.annotation
+                by_ref = ann is TensorByRef or (isinstance(ann, str) and "TensorByRef" in ann)
+                if param.kind == inspect.Parameter.VAR_POSITIONAL:
+                    new_args.extend(convert(v, f"{pname}_{i}", by_ref) for i, v in enumerate(value))
+                elif param.kind == inspect.Parameter.VAR_KEYWORD:
+                    for k, v in value.items():
+                        new_kwargs[k] = convert(v, k, by_ref)
+                elif param.kind == inspect.Parameter.KEYWORD_ONLY:
+                    new_kwargs[pname] = convert(value, pname, by_ref)
+                else:
+                    new_args.append(convert(value, pname, by_ref))
+            result = fn(*new_args, **new_kwargs)
+            if result is None:
+                result = ()
+            elif isinstance(result, Tensor):
+                result = (result,)
+            for out in result:
+                if not isinstance(out, Tensor):
+                    raise ValueError(f"Graph outputs must be tensors, got {type(out)} from {base}")
+                graph_output(out)
+        return g
+
+    def __repr__(self):
+        return f"Ir(graphs={len(self.graphs)}, replication_factor={self._replication_factor})"
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# tensor factories
+# ---------------------------------------------------------------------------------------------------------------
+
+
+def graph_input(shape: Iterable[int], dtype: dtype, name: Optional[str] = None, by_ref: bool = False,
+                meta_shape: Optional[Iterable[int]] = None) -> Tensor:
+    g = gcg()
+    t = Tensor(g, shape, dtype, name or "input", meta_shape)
+    t.kind = "input"
+    g._inputs.append(t)
+    if by_ref:
+        g._by_ref.add(t)
+    return t
+
+
+def graph_output(t: Tensor) -> None:
+    g = gcg()
+    if t.graph is not g:
+        raise ValueError(f"{t} is not in the current graph {g.name}")
+    g._outputs.append(t)
+
+
+def _host_array(data, dt: Optional[dtype]):
+    if isinstance(data, torch.Tensor):
+        t = data.detach().cpu()
+    else:
+        arr = np.asarray(data)
+        if dt is None and arr.dtype == np.float64:
+            arr = arr.astype(np.float32)
+        if dt is None and arr.dtype == np.int64:
+            arr = arr.astype(np.int32)
+        t = _dt.to_torch(arr)
+    if dt is not None and t.dtype != dt.as_torch():
+        t = t.to(dt.as_torch())
+    return t
+
+
+def variable(data, dtype: Optional[dtype] = None, name: Optional[str] = None, downcast: bool = True,
+             replica_grouping: Optional[ReplicaGrouping] = None, retrieval_mode=None, log2_scale=None,
+             nan_on_overflow=None) -> Variable:
+    """Create a variable in the main graph initialised with `data` (host shape: `(num_groups, *shape)` when the
+    replica grouping has more than one group)."""
+    g = gcg()
+    if g is not g.ir.main_graph:
+        raise ValueError("Variables can only be created in the main graph")
+    dt = _dt.dtype.as_dtype(dtype) if dtype is not None else None
+    host = data if isinstance(data, np.memmap) else _host_array(data, dt)
+    if isinstance(host, np.memmap):
+        dt = dt or _dt.dtype.as_dtype(host.dtype)
+        full_shape = tuple(host.shape)
+    else:
+        dt = _dt.dtype.as_dtype(host.dtype)
+        full_shape = tuple(host.shape)
+    rg = replica_grouping or g.ir.replica_grouping()
+    if rg.num_groups > 1:
+        if not full_shape or full_shape[0] != rg.num_groups:
+            raise ValueError(
+                f"Variable data for a replica grouping with {rg.num_groups} groups must have a leading axis of that "
+                f"size. Got shape {full_shape}")
+        shape = full_shape[1:]
+    else:
+        shape = full_shape
+    v = Variable(g, shape, dt, name or "variable", replica_grouping=rg)
+    g.ir.initial_values[v] = host
+    return v
+
+
+def constant(data, dtype: Optional[dtype] = None, name: Optional[str] = None, downcast: bool = True) -> Constant:
+    g = gcg()
+    dt = _dt.dtype.as_dtype(dtype) if dtype is not None else None
+    return Constant(g, _host_array(data, dt), name or "const")
+
+
+def replica_sharded_variable(data, dtype: Optional[dtype] = None, name: Optional[str] = None,
+                             replica_grouping: Optional[ReplicaGrouping] = None,
+                             shard_over: Optional[int] = None, shard_grouping=None):
+    """Variable stored as flat `1/shard_over` shards. Returns `(variable, shard_tensor)`; here the variable *is* the
+    per-replica shard, so both entries are the same tensor."""
+    g = gcg()
+    dt = _dt.dtype.as_dtype(dtype) if dtype is not None else None
+    host = _host_array(data, dt)
+    rg = replica_grouping or g.ir.replica_grouping()
+    full_shape = tuple(host.shape[1:]) if rg.num_groups > 1 else tuple(host.shape)
+    if shard_grouping is None:
+        shard_over = shard_over or rg.group_size
+        shard_grouping = _shard_grouping_within(rg, shard_over)
+    nelms = int(np.prod(full_shape)) if full_shape else 1
+    n = shard_grouping.group_size
+    if nelms % n != 0:
+        raise ValueError(f"Cannot shard {nelms} elements over {n} replicas")
+    v = Variable(g, (nelms // n,), _dt.dtype.as_dtype(host.dtype), name or "variable", meta_shape=full_shape,
+                 replica_grouping=rg, shard_group=shard_grouping)
+    g.ir.initial_values[v] = host
+    return v, v
+
+
+def _shard_grouping_within(rg: ReplicaGrouping, shard_over: int) -> ReplicaGrouping:
+    """Sub-grouping of `rg` with `shard_over` members per group (the first `shard_over` positions, then the next...)."""
+    if shard_over == rg.group_size:
+        return rg
+    if rg.group_size % shard_over != 0:
+        raise ValueError(f"shard_over={shard_over} must divide the group size {rg.group_size}")
+    assign = [0] * rg.num_replicas
+    per = rg.group_size // shard_over
+    for gi, members in enumerate(rg.groups):
+        for pos, r in enumerate(members):
+            assign[r] = gi * per + pos // shard_over
+    return ReplicaGrouping(rg.num_replicas, assignment=assign)

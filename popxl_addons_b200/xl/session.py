@@ -1,0 +1,381 @@
+"""Session: owns device state (variables, remote-buffer slabs, constants) and interprets the recorded graphs.
+
+Execution model. Each op of a graph is run in recorded order for every *local* replica: all replicas when the whole
+replica set is simulated in one process (CPU backend, used by tests and as oracle), exactly one when the program is
+launched with one process per GPU. An op runs its native sm_100a kernel when one is registered for the device and
+accepts the operands, else its torch reference implementation. Tensors are released as soon as their last consumer
+in the graph has run. Host streams are staged through pinned memory.
+
+Parity: the `popxl.Session` surface used by popxl_addons/task_session.py:52-53,89-98,320-329 and every test
+(`run`, `get_tensor(s)_data`, `write_variable(s)_data`, context manager, `ir`, `is_attached`).
+"""
+import os
+from typing import Any, Dict, Iterable, List, Mapping, Optional
+
+import numpy as np
+import torch
+
+from . import dtypes as _dt
+from .buffers import DeviceToHostStream, HostToDeviceStream, RemoteBuffer
+from .comm import DistComm, SimComm
+from .core import Constant, Graph, Ir, Tensor, Variable
+
+
+def _resolve_device(device_desc: str) -> torch.device:
+    d = (device_desc or "auto").lower()
+    if d in ("cpu", "ipu_model"):
+        return torch.device("cpu")
+    if d.startswith("cuda"):
+        if ":" in d:
+            return torch.device(d)
+        return torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    # "ipu_hw" / "auto": the accelerator when there is one
+    if torch.cuda.is_available():
+        return torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    return torch.device("cpu")
+
+
+class Session:
+    def __init__(self, ir: Ir, device_desc: str = "auto", use_native: Optional[bool] = None):
+        self.ir = ir
+        self.device = _resolve_device(device_desc)
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        self.distributed = bool(ir.distributed) and int(os.environ.get("WORLD_SIZE", "1")) > 1
+        self.num_replicas = ir.replication_factor
+        if self.distributed:
+            self.comm = DistComm(self.num_replicas, self.device)
+            self.num_local = 1
+            self.replica_offset = self.comm.rank
+        else:
+            self.comm = SimComm(self.num_replicas)
+            self.num_local = self.num_replicas
+            self.replica_offset = 0
+        if use_native is None:
+            use_native = os.environ.get("XL_NATIVE", "1") != "0"
+        self.use_native = use_native and self.device.type == "cuda"
+        if self.use_native:
+            from ...ops import native as _native  # noqa: F401  (registers the CUDA kernels; raises if not built)
+
+        self._vars: Dict[Variable, List[torch.Tensor]] = {}
+        self._buffers: Dict[RemoteBuffer, List[torch.Tensor]] = {}
+        self._consts: Dict[Constant, torch.Tensor] = {}
+        self._liveness: Dict[Graph, Dict[int, List[Tensor]]] = {}
+        self._inputs: Dict[HostToDeviceStream, List[List[torch.Tensor]]] = {}
+        self._cursor: Dict[HostToDeviceStream, int] = {}
+        self._outputs: Dict[DeviceToHostStream, List[List[torch.Tensor]]] = {}
+        self.is_attached = False
+        self.profile: Optional[Dict[str, List[float]]] = None
+        self._init_state()
+
+    # ------------------------------------------------------------------------------------------------------
+    # replica helpers
+    # ------------------------------------------------------------------------------------------------------
+    def global_replica(self, local_index: int) -> int:
+        return self.replica_offset + local_index
+
+    # ------------------------------------------------------------------------------------------------------
+    # state
+    # ------------------------------------------------------------------------------------------------------
+    def _alloc_buffer(self, rb: RemoteBuffer) -> List[torch.Tensor]:
+        if rb not in self._buffers:
+            dt = rb.tensor_dtype.as_torch()
+            if rb.location == "host":
+                slabs = [torch.zeros((rb.entries, *rb.tensor_shape), dtype=dt,
+                                     pin_memory=self.device.type == "cuda") for _ in range(self.num_local)]
+            else:
+                slabs = [torch.zeros((rb.entries, *rb.tensor_shape), dtype=dt, device=self.device)
+                         for _ in range(self.num_local)]
+            self._buffers[rb] = slabs
+        return self._buffers[rb]
+
+    def _replica_slice_of_host(self, var: Variable, host, replica: int) -> torch.Tensor:
+        """Host array (full `shape_on_host`) -> the value replica `replica` holds."""
+        rg = var.replica_grouping
+        data = host
+        if rg.num_groups > 1:
+            data = data[rg.group_index(replica)]
+        if isinstance(data, np.ndarray):
+            data = _dt.to_torch(np.asarray(data))
+        if var.shard_group is not None:
+            n = var.nelms
+            i = var.shard_group.index_in_group(replica)
+            data = data.reshape(-1)[i * n:(i + 1) * n]
+        return data.reshape(var.shape).to(var.dtype.as_torch())
+
+    def _write_var(self, var: Variable, host):
+        vals = []
+        for r in range(self.num_local):
+            vals.append(self._replica_slice_of_host(var, host, self.global_replica(r)))
+        if var.remote_buffer is not None:
+            slabs = self._alloc_buffer(var.remote_buffer)
+            for r, v in enumerate(vals):
+                slabs[r][var.entry].copy_(v.reshape(var.remote_buffer.tensor_shape))
+        else:
+            if var in self._vars:
+                for r, v in enumerate(vals):
+                    self._vars[var][r].copy_(v)
+            else:
+                self._vars[var] = [v.to(self.device, copy=True) for v in vals]
+
+    def _init_state(self):
+        for rb in self.ir.remote_buffers:
+            self._alloc_buffer(rb)
+        for var, host in self.ir.initial_values.items():
+            self._write_var(var, host)
+
+    def _read_var_local(self, var: Variable) -> List[torch.Tensor]:
+        if var.remote_buffer is not None:
+            return [s[var.entry] for s in self._alloc_buffer(var.remote_buffer)]
+        return self._vars[var]
+
+    def get_tensor_data(self, tensor: Variable) -> np.ndarray:
+        return self.get_tensors_data([tensor])[tensor]
+
+    def get_tensors_data(self, tensors: Iterable[Variable]) -> Dict[Variable, np.ndarray]:
+        """Host copies of variables in their `shape_on_host`: one entry per replica group; replica-sharded variables
+        are re-assembled to their full `meta_shape`. Collective when distributed (every rank must call)."""
+        out = {}
+        for var in tensors:
+            if isinstance(var, Constant):
+                out[var] = _dt.to_numpy(var.data)
+                continue
+            if not isinstance(var, Variable):
+                raise TypeError(f"{var} is not a variable")
+            per_replica = self.comm.gather_to_host(self._read_var_local(var))
+            rg = var.replica_grouping
+            per_group = []
+            for members in rg.groups:
+                if var.shard_group is not None:
+                    # the replicas of this group that are in one shard group, in shard order
+                    shard_members = [r for r in var.shard_group.group_of(members[0])]
+                    full = torch.cat([per_replica[r].reshape(-1) for r in shard_members])
+                    per_group.append(full.reshape(var.meta_shape))
+                else:
+                    per_group.append(per_replica[members[0]].reshape(var.shape))
+            res = torch.stack(per_group) if rg.num_groups > 1 else per_group[0]
+            out[var] = _dt.to_numpy(res)
+        return out
+
+    def write_variable_data(self, tensor: Variable, data) -> None:
+        self.write_variables_data({tensor: data})
+
+    def write_variables_data(self, tensors: Mapping[Variable, Any]) -> None:
+        for var, data in tensors.items():
+            if not isinstance(var, Variable):
+                raise TypeError(f"{var} is not a variable")
+            host = _dt.to_torch(np.asarray(data)) if not isinstance(data, torch.Tensor) else data.detach().cpu()
+            if tuple(host.shape) != tuple(var.shape_on_host):
+                if host.numel() == int(np.prod(var.shape_on_host)):
+                    host = host.reshape(var.shape_on_host)
+                else:
+                    raise ValueError(f"Data shape {tuple(host.shape)} does not match the variable's host shape "
+                                     f"{var.shape_on_host} ({var})")
+            self._write_var(var, host)
+
+    # popxl names
+    def weights_to_host(self):
+        pass
+
+    def weights_from_host(self):
+        pass
+
+    def __enter__(self):
+        self.is_attached = True
+        return self
+
+    def __exit__(self, *exc):
+        self.is_attached = False
+        return False
+
+    # ------------------------------------------------------------------------------------------------------
+    # host IO
+    # ------------------------------------------------------------------------------------------------------
+    def _stage_inputs(self, inputs: Mapping[HostToDeviceStream, Any]):
+        T = int(self.ir.num_host_transfers)
+        R = self.num_replicas
+        self._inputs, self._cursor = {}, {}
+        for stream, arr in (inputs or {}).items():
+            if not isinstance(stream, HostToDeviceStream):
+                raise TypeError(f"{stream} is not a host-to-device stream")
+            host = arr if isinstance(arr, torch.Tensor) else _dt.to_torch(np.asarray(arr))
+            if host.dtype != stream.dtype.as_torch():
+                host = host.to(stream.dtype.as_torch())
+            n_local = self.num_local
+            full = (T, R, *stream.shape)
+            local = (T, n_local, *stream.shape)
+            numel = host.numel()
+            if numel == int(np.prod(full)) and (not self.distributed or R == 1):
+                host = host.reshape(full)
+            elif self.distributed and numel == int(np.prod(full)):
+                host = host.reshape(full)[:, self.replica_offset:self.replica_offset + 1]
+            elif numel == int(np.prod(local)):
+                host = host.reshape(local)
+            else:
+                raise ValueError(
+                    f"Input for stream {stream.name} has shape {tuple(host.shape)}; expected "
+                    f"(num_host_transfers={T}, replication_factor={R}, *{stream.shape}) with unit axes optional")
+            if self.device.type == "cuda":
+                if not host.is_pinned():
+                    host = host.contiguous().pin_memory()
+                dev = host.to(self.device, non_blocking=True)
+            else:
+                dev = host
+            self._inputs[stream] = dev
+            self._cursor[stream] = 0
+
+    def host_load(self, stream: HostToDeviceStream) -> List[torch.Tensor]:
+        if stream not in self._inputs:
+            raise KeyError(f"No input was provided for host stream {stream.name}")
+        i = self._cursor[stream]
+        data = self._inputs[stream]
+        if i >= data.shape[0]:
+            raise RuntimeError(
+                f"Stream {stream.name} was read more than num_host_transfers={data.shape[0]} times in one run")
+        self._cursor[stream] = i + 1
+        return [data[i, r] for r in range(self.num_local)]
+
+    def host_store(self, stream: DeviceToHostStream, vals: List[torch.Tensor]):
+        self._outputs.setdefault(stream, []).append([v.detach().clone() for v in vals])
+
+    def _collect_outputs(self) -> Dict[DeviceToHostStream, np.ndarray]:
+        T = int(self.ir.num_host_transfers)
+        res = {}
+        for stream, items in self._outputs.items():
+            stacked = torch.stack([torch.stack(per_replica) for per_replica in items])  # (t, R_local, *shape)
+            arr = _dt.to_numpy(stacked)
+            if arr.shape[1] == 1:
+                arr = arr[:, 0]
+            if arr.shape[0] == 1 and T == 1:
+                arr = arr[0]
+            res[stream] = arr
+        return res
+
+    # ------------------------------------------------------------------------------------------------------
+    # remote buffers / device copies
+    # ------------------------------------------------------------------------------------------------------
+    @staticmethod
+    def _index(idx: torch.Tensor) -> int:
+        return int(idx.reshape(-1)[0].item())
+
+    def remote_load(self, rb: RemoteBuffer, index: List[torch.Tensor]) -> List[torch.Tensor]:
+        slabs = self._alloc_buffer(rb)
+        out = []
+        for r in range(self.num_local):
+            i = self._index(index[r])
+            if not 0 <= i < rb.entries:
+                raise IndexError(f"remote_load index {i} out of range for {rb}")
+            out.append(slabs[r][i].to(self.device, non_blocking=True).clone() if rb.location == "host"
+                       else slabs[r][i].clone())
+        return out
+
+    def remote_store(self, rb: RemoteBuffer, index: List[torch.Tensor], vals: List[torch.Tensor]):
+        slabs = self._alloc_buffer(rb)
+        for r in range(self.num_local):
+            i = self._index(index[r])
+            if not 0 <= i < rb.entries:
+                raise IndexError(f"remote_store index {i} out of range for {rb}")
+            slabs[r][i].copy_(vals[r].reshape(rb.tensor_shape), non_blocking=True)
+
+    def device_copy(self, vals, op):
+        return vals
+
+    # ------------------------------------------------------------------------------------------------------
+    # interpreter
+    # ------------------------------------------------------------------------------------------------------
+    def _const(self, c: Constant) -> torch.Tensor:
+        v = self._consts.get(c)
+        if v is None:
+            v = c.data.to(self.device)
+            self._consts[c] = v
+        return v
+
+    def _last_uses(self, graph: Graph) -> Dict[int, List[Tensor]]:
+        lv = self._liveness.get(graph)
+        if lv is None or lv[-1] != (len(graph.ops), len(graph._outputs)):
+            last: Dict[Tensor, int] = {}
+            for i, op in enumerate(graph.ops):
+                for t in op.inputs:
+                    last[t] = i
+                for t in op.outputs:
+                    last.setdefault(t, i)
+            keep = set(graph._outputs) | set(graph._inputs)
+            table: Dict[int, List[Tensor]] = {}
+            for t, i in last.items():
+                if t in keep or isinstance(t, (Variable, Constant)):
+                    continue
+                table.setdefault(i, []).append(t)
+            table[-1] = (len(graph.ops), len(graph._outputs))
+            self._liveness[graph] = lv = table
+        return lv
+
+    def _value(self, t: Tensor, env) -> List[torch.Tensor]:
+        v = env.get(t)
+        if v is not None:
+            return v
+        if isinstance(t, Constant):
+            c = self._const(t)
+            v = [c] * self.num_local
+            env[t] = v
+            return v
+        if isinstance(t, Variable):
+            if t.remote_buffer is not None:
+                raise RuntimeError(f"{t} is a remote variable: read it with ops.remote_load")
+            return self._vars[t]
+        raise KeyError(f"Tensor {t} has no value: it was used before being produced, or belongs to another graph")
+
+    def _exec_ops(self, graph: Graph, env: Dict[Tensor, List[torch.Tensor]]):
+        frees = self._last_uses(graph)
+        native_dev = self.device.type if self.use_native else None
+        for i, op in enumerate(graph.ops):
+            od = op.opdef
+            if od.special is not None:
+                for t in op.inputs:
+                    if t not in env:
+                        env[t] = self._value(t, env)
+                od.special(self, op, env)
+            else:
+                ins = [self._value(t, env) for t in op.inputs]
+                fn = od.native.get(native_dev) if native_dev else None
+                outs_per_replica = []
+                for r in range(self.num_local):
+                    args = [v[r] for v in ins]
+                    res = NotImplemented
+                    if fn is not None:
+                        res = fn(*args, **op.attrs)
+                    if res is NotImplemented:
+                        res = od.impl(*args, **op.attrs)
+                    outs_per_replica.append((res,) if isinstance(res, torch.Tensor) else tuple(res or ()))
+                for j, t in enumerate(op.outputs):
+                    env[t] = [outs_per_replica[r][j] for r in range(self.num_local)]
+            dead = frees.get(i)
+            if dead:
+                for t in dead:
+                    env.pop(t, None)
+
+    def run_graph(self, graph: Graph, inputs: List[List[torch.Tensor]]) -> List[List[torch.Tensor]]:
+        env = dict(zip(graph._inputs, inputs))
+        self._exec_ops(graph, env)
+        return [self._value(t, env) for t in graph._outputs]
+
+    def run_repeat(self, op, graph: Graph, vals: List[List[torch.Tensor]], env):
+        n_out = len(graph._outputs)
+        outs = vals[:n_out]
+        for _ in range(op.attrs["count"]):
+            outs = self.run_graph(graph, vals)
+            vals = list(outs) + list(vals[n_out:])
+        for t, v in zip(op.outputs, outs):
+            env[t] = v
+
+    def run(self, inputs: Optional[Mapping[HostToDeviceStream, Any]] = None,
+            downcast_inputs: bool = True) -> Dict[DeviceToHostStream, np.ndarray]:
+        """Execute the main graph once. `inputs[stream]` has shape
+        `(num_host_transfers, replication_factor, *stream.shape)` (unit axes may be omitted; under one process per
+        GPU the replica axis may hold only this rank's slice)."""
+        self._outputs = {}
+        self._stage_inputs(inputs or {})
+        main = self.ir.main_graph
+        env: Dict[Tensor, List[torch.Tensor]] = {}
+        with torch.no_grad():
+            self._exec_ops(main, env)
+        return self._collect_outputs()
