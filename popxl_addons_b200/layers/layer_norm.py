@@ -1,0 +1,32 @@
+"""LayerNorm over the last axis of a 2-D `(N, C)` tensor.
+Parity: popxl_addons/layers/layer_norm.py:14-54."""
+from functools import partial
+from typing import Dict
+
+import numpy as np
+
+from .. import xl
+from ..module import Module
+from ..named_tensors import NamedTensors
+from ..xl import ops
+
+__all__ = ["LayerNorm"]
+
+
+class LayerNorm(Module):
+    def __init__(self, eps: float = 1e-5, cache: bool = False):
+        super().__init__(cache=cache)
+        self.eps = eps
+
+    def build(self, x: xl.Tensor) -> xl.Tensor:
+        if x.rank != 2:
+            raise ValueError(f"LayerNorm expects a 2-D (N, C) input; got shape {x.shape}. Flatten leading axes first.")
+        np_dt = x.dtype.as_numpy() if x.dtype._numpy is not None else np.float32
+        w = self.add_variable_input("weight", partial(np.ones, x.shape[-1], np_dt), x.dtype)
+        b = self.add_variable_input("bias", partial(np.zeros, x.shape[-1], np_dt), x.dtype)
+        return ops.layer_norm(x, w, b, eps=self.eps)
+
+    @staticmethod
+    def torch_mapping(variables: NamedTensors, nn_layer) -> Dict[xl.Tensor, np.ndarray]:
+        return {variables.weight: nn_layer.weight.data.detach().cpu().numpy().reshape(-1).copy(),
+                variables.bias: nn_layer.bias.data.detach().cpu().numpy().reshape(-1).copy()}

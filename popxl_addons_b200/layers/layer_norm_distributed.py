@@ -1,0 +1,28 @@
+"""LayerNorm whose hidden axis is sharded across `replica_grouping`; each replica holds its slice of gamma/beta.
+Parity: popxl_addons/layers/layer_norm_distributed.py:13-35."""
+from functools import partial
+
+import numpy as np
+
+from .. import xl
+from ..module import Module
+from ..ops.layer_norm_distributed import layer_norm_distributed
+
+__all__ = ["LayerNormDistributed"]
+
+
+class LayerNormDistributed(Module):
+    def __init__(self, replica_grouping: xl.ReplicaGrouping, eps: float = 1e-5):
+        super().__init__()
+        self.replica_grouping = replica_grouping
+        self.eps = eps
+
+    def build(self, x: xl.Tensor) -> xl.Tensor:
+        np_dt = x.dtype.as_numpy() if x.dtype._numpy is not None else np.float32
+        # parameters differ between the replicas of the group, i.e. they are identical across its transpose
+        param_rg = self.replica_grouping.transpose()
+        w = self.add_variable_input("weight", partial(np.ones, x.shape[-1], np_dt), x.dtype,
+                                    replica_grouping=param_rg)
+        b = self.add_variable_input("bias", partial(np.zeros, x.shape[-1], np_dt), x.dtype,
+                                    replica_grouping=param_rg)
+        return layer_norm_distributed(x, w, b, self.eps, self.replica_grouping)

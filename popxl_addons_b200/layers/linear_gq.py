@@ -1,0 +1,89 @@
+"""Inference-only Linear with 4-bit group-quantised weights; the dequantisation is fused into the GEMM on CUDA.
+
+`dim` selects the axis the quantisation groups run along: `-1`/`1` the output features, `0` the input features
+(the usual "groups of 64 along the input dimension"). Variables: `weight_compressed` uint16 `(U, C/gs, gs/4)`,
+`weight_decompression_scale` / `_bias` `(U, C/gs, 1)`, where `C` is the grouped axis and `U` the other one.
+Parity: popxl_addons/layers/linear_gq.py:19-136.
+"""
+from functools import partial
+from typing import Dict, Optional
+
+import numpy as np
+
+from .. import xl
+from ..module import Module
+from ..named_tensors import NamedTensors
+from ..ops.group_quantize_decompress import group_quantize_compress_numpy
+from ..xl.opdef import OpDef, emit1
+
+__all__ = ["LinearGQ"]
+
+import torch  # noqa: E402
+
+from ..ops.group_quantize_decompress import _decompress_ref  # noqa: E402
+
+
+def _linear_gq_ref(x, packed, scale, bias, *b, dim):
+    if x.device.type == "meta":
+        u, g, w = packed.shape
+        n = g * w * 4 if dim in (-1, 1) else u
+        return torch.empty((*x.shape[:-1], n), dtype=x.dtype, device="meta")
+    w = _decompress_ref(packed, scale, bias)
+    if dim not in (-1, 1):
+        w = w.t()
+    y = torch.matmul(x, w.to(x.dtype))
+    if b:
+        y = y + b[0].to(y.dtype)
+    return y
+
+
+OpDef("linear_gq", impl=_linear_gq_ref,
+      flops=lambda op: 2 * op.inputs[0].shape[-1] * op.outputs[0].nelms)
+
+
+class LinearGQ(Module):
+    def __init__(self, out_features: int, bias: bool = True, replica_grouping: Optional[xl.ReplicaGrouping] = None,
+                 group_size: int = 64, dim: int = -1):
+        super().__init__()
+        if group_size % 4:
+            raise ValueError("group_size must be a multiple of 4")
+        self.out_features = out_features
+        self.bias = bias
+        self.replica_grouping = replica_grouping
+        self.group_size = group_size
+        self.dim = dim
+
+    def build(self, x: xl.Tensor) -> xl.Tensor:
+        in_features = x.shape[-1]
+        if self.dim in (-1, 1):
+            u, c = in_features, self.out_features
+        else:
+            u, c = self.out_features, in_features
+        if c % self.group_size:
+            raise ValueError(f"The grouped axis ({c}) must be divisible by group_size ({self.group_size})")
+        n_groups, words = c // self.group_size, self.group_size // 4
+        np_dt = x.dtype.as_numpy() if x.dtype._numpy is not None else np.float32
+        rg = self.replica_grouping
+        packed = self.add_variable_input("weight_compressed", partial(np.zeros, (u, n_groups, words), np.uint16),
+                                         xl.uint16, replica_grouping=rg)
+        scale = self.add_variable_input("weight_decompression_scale", partial(np.ones, (u, n_groups, 1), np_dt),
+                                        x.dtype, replica_grouping=rg)
+        zero = self.add_variable_input("weight_decompression_bias", partial(np.zeros, (u, n_groups, 1), np_dt),
+                                       x.dtype, replica_grouping=rg)
+        ins = [x, packed, scale, zero]
+        if self.bias:
+            ins.append(self.add_variable_input("bias", partial(np.zeros, (self.out_features,), np_dt), x.dtype,
+                                               replica_grouping=rg))
+        return emit1("linear_gq", ins, {"dim": self.dim})
+
+    @staticmethod
+    def torch_mapping(variables: NamedTensors, nn_layer, group_size: int = 64, dim: int = -1,
+                      dtype=np.float16) -> Dict[xl.Tensor, np.ndarray]:
+        """Compress a `torch.nn.Linear` weight (stored `(out, in)`) into the layer's variables."""
+        w = nn_layer.weight.data.detach().cpu().float().numpy().T.astype(dtype)  # (in, out)
+        packed, scale, bias = group_quantize_compress_numpy(w, group_size, dim)
+        out = {variables.weight_compressed: packed, variables.weight_decompression_scale: scale.astype(dtype),
+               variables.weight_decompression_bias: bias.astype(dtype)}
+        if nn_layer.bias is not None and "bias" in variables:
+            out[variables.bias] = nn_layer.bias.data.detach().cpu().numpy().astype(dtype)
+        return out

@@ -1,0 +1,47 @@
+"""Dense x constant-sparse (CSR) matmul for inference.
+
+The sparsity pattern and the non-zero values are constants of the graph. On CUDA the product runs as a row-gather
+SpMM kernel; the CPU backend uses torch sparse.
+Parity: popxl_addons/ops/static_sparse_ops/dense_sparse_matmul.py:23-85.
+"""
+import numpy as np
+import torch
+
+from .. import xl
+from ..xl.opdef import OpDef, emit1
+
+__all__ = ["random_sparse", "dense_const_sparse_matmul"]
+
+
+def random_sparse(dense: np.ndarray, density: float = 0.5):
+    """Zero out a random `1 - density` fraction of `dense`; returns `(masked dense, scipy csr_matrix)`."""
+    from scipy.sparse import csr_matrix
+
+    mask = np.random.rand(*dense.shape) < density
+    masked = (dense * mask).astype(dense.dtype)
+    return masked, csr_matrix(masked)
+
+
+def _impl(lhs, indptr, indices, values, n_rows, n_cols):
+    if lhs.device.type == "meta":
+        return torch.empty((*lhs.shape[:-1], n_cols), dtype=lhs.dtype, device="meta")
+    csr = torch.sparse_csr_tensor(indptr.long(), indices.long(), values.float(), size=(n_rows, n_cols))
+    dense_rhs = csr.to_dense()
+    return torch.matmul(lhs.float(), dense_rhs).to(lhs.dtype)
+
+
+OpDef("dense_csr_matmul", impl=_impl)
+
+
+def dense_const_sparse_matmul(lhs: xl.Tensor, rhs, output_cols: int = None) -> xl.Tensor:
+    """`lhs (.., M, K) @ rhs (K, N)` with `rhs` a scipy CSR matrix baked into the graph."""
+    rhs = rhs.tocsr()
+    k, n = rhs.shape
+    if lhs.shape[-1] != k:
+        raise ValueError(f"Inner dimensions do not match: {lhs.shape} x {rhs.shape}")
+    if output_cols is not None and output_cols != n:
+        raise ValueError(f"output_cols={output_cols} does not match the sparse matrix ({n} columns)")
+    indptr = xl.constant(rhs.indptr.astype(np.int32), xl.int32, "csr_indptr")
+    indices = xl.constant(rhs.indices.astype(np.int32), xl.int32, "csr_indices")
+    values = xl.constant(rhs.data.astype(np.float32), xl.float32, "csr_values")
+    return emit1("dense_csr_matmul", [lhs, indptr, indices, values], {"n_rows": k, "n_cols": n})

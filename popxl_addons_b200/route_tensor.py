@@ -1,0 +1,96 @@
+"""Make a tensor of a parent graph available inside a (possibly deeply nested) called sub-graph.
+
+Sub-graphs only see their own inputs. `route_tensor_into_graph` adds a graph input to the target graph and to every
+graph on every call path between the tensor's graph and the target, and wires all call / repeat sites along those
+paths, so the tensor arrives wherever the target is executed.
+
+Parity: popxl_addons/route_tensor.py:11-221.
+"""
+from typing import Dict, Iterable, List, Optional, Set, Tuple
+
+from . import xl
+
+__all__ = ["route_tensor_into_graph", "is_subgraph"]
+
+
+def _called(op) -> Optional[xl.Graph]:
+    g = op.attrs.get("graph")
+    return g if isinstance(g, xl.Graph) and op.opdef.name in ("call", "repeat") else None
+
+
+def is_subgraph(parent: xl.Graph, subgraph: xl.Graph) -> bool:
+    """Is `subgraph` (transitively) called from `parent`?"""
+    seen: Set[int] = set()
+    stack = [parent]
+    while stack:
+        g = stack.pop()
+        for op in g.ops:
+            c = _called(op)
+            if c is None or id(c) in seen:
+                continue
+            if c is subgraph:
+                return True
+            seen.add(id(c))
+            stack.append(c)
+    return False
+
+
+def called_graph_paths(parent: xl.Graph, subgraph: xl.Graph) -> Set[Tuple[xl.Graph, ...]]:
+    """All chains of graphs `(g1, ..., subgraph)` such that `parent` calls g1, g1 calls g2, ..."""
+    paths: Set[Tuple[xl.Graph, ...]] = set()
+
+    def walk(g: xl.Graph, prefix: Tuple[xl.Graph, ...]):
+        for c in {id(_called(op)): _called(op) for op in g.ops if _called(op) is not None}.values():
+            chain = prefix + (c,)
+            if c is subgraph:
+                paths.add(chain)
+            elif c not in prefix:
+                walk(c, chain)
+
+    walk(parent, ())
+    return paths
+
+
+def _add_call_input(op, tensor: xl.Tensor, modified: bool):
+    op.inputs.append(tensor)
+    if modified:
+        op.attrs.setdefault("modified", set()).add(tensor)
+
+
+def route_tensor_into_graph(t: xl.Tensor, graph: Optional[xl.Graph] = None, modified: bool = False) -> xl.Tensor:
+    """Tensor inside `graph` (default: the current graph) that carries the value of `t`, which lives in a graph
+    that (transitively) calls `graph`. `modified=True` marks it as written by the sub-graph (by-reference)."""
+    graph = graph or xl.gcg()
+    if not isinstance(t, xl.Tensor):
+        raise TypeError(f"Not a tensor: {t}")
+    if t.graph is graph:
+        return t
+    src = t.graph
+    if t not in src._tensors:
+        raise ValueError(f"{t} is not in the graph {src.name}")
+    paths = called_graph_paths(src, graph)
+    if not paths:
+        raise ValueError(f"{t} is not in a known parent graph of {graph.name}: "
+                         f"{src.name} does not (transitively) call it")
+    routed: Dict[xl.Graph, xl.Tensor] = {src: t}
+
+    def input_of(g: xl.Graph) -> xl.Tensor:
+        if g not in routed:
+            with g:
+                routed[g] = xl.graph_input(t.shape, t.dtype, t.name.split("/")[-1], by_ref=modified,
+                                           meta_shape=t.meta_shape)
+        return routed[g]
+
+    wired: Set[int] = set()
+    for chain in paths:
+        caller = src
+        for callee in chain:
+            new_in = input_of(callee)
+            for op in caller.ops:
+                if _called(op) is callee and op.uid not in wired:
+                    # inputs are positional: the new graph input was appended last, so append the caller's tensor
+                    if len(op.inputs) < len(callee._inputs):
+                        _add_call_input(op, routed[caller], modified)
+                    wired.add(op.uid)
+            caller = callee
+    return routed[graph]

@@ -510,7 +510,7 @@ class Op:
     """One recorded operation: `outputs = opdef(inputs, **attrs)`."""
 
     __slots__ = ("opdef", "inputs", "outputs", "attrs", "graph", "name", "device_index", "tile_set", "stage",
-                 "debug", "uid", "__weakref__")
+                 "debug", "uid", "attrs_hint", "__weakref__")
     _counter = itertools.count()
 
     def __init__(self, opdef, inputs, attrs, graph):
@@ -524,6 +524,7 @@ class Op:
         self.tile_set = current_tile_set()
         self.stage = None
         self.debug = None
+        self.attrs_hint = None
         self.uid = next(Op._counter)
 
     @property
@@ -754,7 +755,7 @@ class Ir:
             for pname, value in bound.arguments.items():
                 param = sig.parameters[pname]
                 ann = param.annotation
-                by_ref = ann is TensorByRef or (isinstance(ann, str) and "TensorByRef" in ann)
+                by_ref = ann is TensorByRef or "TensorByRef" in str(ann)
                 if param.kind == inspect.Parameter.VAR_POSITIONAL:
                     new_args.extend(convert(v, f"{pname}_{i}", by_ref) for i, v in enumerate(value))
                 elif param.kind == inspect.Parameter.VAR_KEYWORD:

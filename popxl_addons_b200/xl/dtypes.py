@@ -111,7 +111,7 @@ def to_torch(data, dt: "dtype" = None) -> torch.Tensor:
         elif arr.dtype == np.uint64:
             t = torch.from_numpy(arr.view(np.int64).copy()).view(torch.uint64)
         else:
-            t = torch.from_numpy(np.ascontiguousarray(arr).copy())
+            t = torch.from_numpy(np.array(arr, order="C", copy=True))
     if dt is not None and t.dtype != dt.as_torch():
         t = t.to(dt.as_torch())
     return t

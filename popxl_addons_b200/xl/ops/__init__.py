@@ -92,7 +92,14 @@ def _vjp_div(ctx, op, gs):
 register("add", vjp=_vjp_add, keeps_meta=True)(lambda a, b: torch.add(a, b))
 register("sub", vjp=_vjp_sub, keeps_meta=True)(lambda a, b: torch.sub(a, b))
 register("mul", vjp=_vjp_mul, keeps_meta=True)(lambda a, b: torch.mul(a, b))
-register("div", vjp=_vjp_div, keeps_meta=True)(lambda a, b: torch.div(a, b))
+def _div_ref(a, b):
+    # integer operands divide like C (truncation), floats divide exactly
+    if not a.dtype.is_floating_point and not b.dtype.is_floating_point:
+        return torch.div(a, b, rounding_mode="trunc")
+    return torch.div(a, b)
+
+
+register("div", vjp=_vjp_div, keeps_meta=True)(_div_ref)
 register("fmod", keeps_meta=True)(lambda a, b: torch.fmod(a, b))
 register("remainder", keeps_meta=True)(lambda a, b: torch.remainder(a, b))
 
@@ -964,12 +971,14 @@ dynamic_update = dynamic_update_
 def _incmod_ref(t, increment, modulus):
     if t.device.type == "meta":
         return t
-    t.add_(increment).remainder_(modulus)
+    v = t.view(torch.int32) if t.dtype == torch.uint32 else t
+    v.add_(int(increment) if not t.dtype.is_floating_point else increment)
+    v.remainder_(int(modulus) if not t.dtype.is_floating_point else modulus)
     return t
 
 
 OpDef("increment_mod_", impl=_incmod_ref, inplace=True)
-OpDef("increment_mod", impl=lambda t, increment, modulus: torch.remainder(t + increment, modulus))
+OpDef("increment_mod", impl=lambda t, increment, modulus: _incmod_ref(t.clone(), increment, modulus))
 
 
 def increment_mod_(t: Tensor, increment: float, modulus: float) -> Tensor:

@@ -183,3 +183,15 @@ def replica_sharded_slice(t: Tensor, group: Optional[ReplicaGrouping] = None) ->
 
 
 replicated_slice = replica_sharded_slice
+
+
+# ---- forward-identity half of the tensor-parallel all-reduce (result of the OpToIdentity rewrite) -------------
+
+
+def _vjp_tp_identity(ctx, op, gs):
+    return [emit1("all_reduce", [gs[0]], dict(group=op.attrs["group"], op=op.attrs["op"], inplace=False,
+                                              identical_inputs=False, identical_grad_inputs=True))]
+
+
+OpDef("tp_identity", impl=lambda a, **kw: a, vjp=_vjp_tp_identity, keeps_meta=True,
+      infer=lambda op: [(op.inputs[0].shape, op.inputs[0].dtype, op.inputs[0].meta_shape)])

@@ -280,6 +280,15 @@ class Session:
     def device_copy(self, vals, op):
         return vals
 
+    def native_collective(self, name: str):
+        """Fused compute+collective kernel registered under `name` for this session's transport, or None (then the
+        op runs its reference composition over `self.comm`)."""
+        if not self.use_native or not self.distributed:
+            return None
+        from ...parallel import fused
+
+        return fused.lookup(name, self)
+
     # ------------------------------------------------------------------------------------------------------
     # interpreter
     # ------------------------------------------------------------------------------------------------------
