@@ -49,13 +49,12 @@ def autodiff_with_accumulation(graph: GraphWithNamedArgs, tensors_to_accumulate_
     g = grad.graph
     name_of = {t: k for k, t in graph.args.to_dict().items()}
     rgs = replica_groupings.to_dict() if replica_groupings is not None else {}
-    factories = NamedVariableFactories()
-    named = NamedTensors()
+    factories, named = {}, {}
     with g:
         counter, counter_f = add_variable_input("mean_accum_counter", lambda: np.zeros((), np.float32), xl.float32,
                                                 by_ref=True)
-        factories.insert("mean_accum_counter", counter_f)
-        named.insert("mean_accum_counter", counter)
+        factories["mean_accum_counter"] = counter_f
+        named["mean_accum_counter"] = counter
         drop = []
         for idx, ec in enumerate(info._expected_outputs):
             t = ec.fwd_tensor
@@ -69,8 +68,8 @@ def autodiff_with_accumulation(graph: GraphWithNamedArgs, tensors_to_accumulate_
                                                 by_ref=True, replica_grouping=rgs.get(key))
             if t.meta_shape:
                 accum.meta_shape = tuple(t.meta_shape)
-            factories.insert(f"accum.{key}", accum_f)
-            named.insert(f"accum.{key}", accum)
+            factories[f"accum.{key}"] = accum_f
+            named[f"accum.{key}"] = accum
             ops.var_updates.accumulate_mean_(accum, grad_t, counter)
             if t not in required:
                 drop.append(idx)
@@ -78,8 +77,8 @@ def autodiff_with_accumulation(graph: GraphWithNamedArgs, tensors_to_accumulate_
         for idx in sorted(drop, reverse=True):
             del g._outputs[idx]
             del info._expected_outputs[idx]
-    grad.args = named
-    return factories, grad
+    grad.args = NamedTensors.from_dict(named)
+    return NamedVariableFactories.from_dict(factories), grad
 
 
 def remap_grad_info(grad_info: GradGraphInfo, forward_graph: xl.Graph, backward_graph: xl.Graph) -> GradGraphInfo:
