@@ -1,0 +1,502 @@
+// bf16 / fp16 GEMM on the 5th-generation tensor cores (tcgen05) for sm_100a.
+//
+//   C[b] (M x N) = epilogue( A[b] (M x K) * B[b] (K x N) )
+//
+// Structure: persistent kernel, one CTA per SM, 192 threads:
+//   warp 0      TMA producer   : cp.async.bulk.tensor loads of A / B tiles into a 4-stage shared-memory ring
+//   warp 1      MMA issuer     : one elected thread issues tcgen05.mma (128 x BLOCK_N x 16), accumulators live in TMEM,
+//                                two accumulator buffers so the epilogue of tile i overlaps the main loop of tile i+1
+//   warps 2..5  epilogue       : tcgen05.ld TMEM -> registers, bias / activation / accumulate, 16-byte global stores
+// Either operand may be K-major (reduction dimension contiguous) or MN-major, so `x @ w`, `g @ w^T` and `x^T @ g`
+// (forward, data gradient, weight gradient) all run without materialising a transpose. Shared-memory tiles use the
+// 128-byte swizzle that both TMA and the UMMA shared-memory descriptors understand.
+//
+// Every wait on an mbarrier is bounded: when a wait gives up the kernel records a code in `*err`, raises a CTA-wide
+// abort flag, all roles leave their loops, TMEM is released and the kernel returns normally.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <stdio.h>
+
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 64;  // 64 x 2 bytes = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+enum { ERR_FULL_WAIT = 1, ERR_EMPTY_WAIT = 2, ERR_TMEM_FULL_WAIT = 3, ERR_TMEM_EMPTY_WAIT = 4 };
+
+struct GemmParams {
+  int M, N, K, batch;
+  int a_mn, b_mn;  // 0: K-major operand, 1: MN-major operand
+  void* C;
+  long long ldc, batch_stride_c;
+  int c_dtype;
+  const void* bias;  // length N, may be null
+  int bias_dtype;
+  int act;         // 0 none, 1 gelu(erf), 2 gelu(tanh), 3 relu
+  int accumulate;  // 0 overwrite, 1 C += alpha*acc, 2 running mean: C = C*t/(t+1) + acc/(t+1), t = *step
+  const float* step;
+  float alpha;
+  int is_fp16;
+  int* err;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false (and raises the abort flag) if the barrier did not flip in time or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  if (err) atomicCAS(err, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// Shared-memory matrix descriptor for a 128-byte-swizzled tile (version 1 = Blackwell, layout type 2 = SWIZZLE_128B).
+//   K-major : rows of 128 bytes, groups of 8 rows every 1024 bytes           -> SBO = 1024, LBO unused (1)
+//   MN-major: 64-element (128 B) column blocks of `lbo_bytes`, K groups of 8 -> SBO = 1024, LBO = lbo_bytes
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)(1024u >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+__device__ __forceinline__ float apply_act(float v, int act) {
+  if (act == 1) return 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+  if (act == 2) return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+  if (act == 3) return fmaxf(v, 0.f);
+  return v;
+}
+
+template <int BLOCK_N>
+struct SmemLayout {
+  static constexpr int A_BYTES = BLOCK_M * BLOCK_K * 2;
+  static constexpr int B_BYTES = BLOCK_N * BLOCK_K * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int TOTAL = TILE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+// tile index -> (batch, m block, n block). Tiles that run at the same time share A / B panels in L2: m-blocks are
+// walked in groups of 8 inside each n-column.
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& b, int& mb, int& nb) {
+  const int per_batch = tiles_m * tiles_n;
+  b = tile / per_batch;
+  int t = tile - b * per_batch;
+  constexpr int GROUP = 8;
+  const int group_size = GROUP * tiles_n;
+  const int g = t / group_size;
+  const int first_m = g * GROUP;
+  const int rows = min(GROUP, tiles_m - first_m);
+  const int in_group = t - g * group_size;
+  mb = first_m + in_group % rows;
+  nb = in_group / rows;
+}
+
+template <int BLOCK_N>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        const GemmParams p) {
+  using L = SmemLayout<BLOCK_N>;
+  constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // two accumulator buffers (power of two: 256 or 512)
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + L::TILE_BYTES);
+  uint64_t* full_bar = bars;                     // [STAGES]
+  uint64_t* empty_bar = bars + STAGES;           // [STAGES]
+  uint64_t* tmem_full_bar = bars + 2 * STAGES;   // [2]
+  uint64_t* tmem_empty_bar = bars + 2 * STAGES + 2;  // [2]
+  uint32_t* tmem_base_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = (volatile int*)(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_m = (p.M + BLOCK_M - 1) / BLOCK_M;
+  const int tiles_n = (p.N + BLOCK_N - 1) / BLOCK_N;
+  const int num_tiles = tiles_m * tiles_n * p.batch;
+  const int k_blocks = (p.K + BLOCK_K - 1) / BLOCK_K;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full_bar[a], 1);
+      mbar_init(&tmem_empty_bar[a], 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer ------------------------------------------------
+    if (elect_one()) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int b, mb, nb;
+        tile_coords(tile, tiles_m, tiles_n, b, mb, nb);
+        const int m0 = mb * BLOCK_M, n0 = nb * BLOCK_N;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, ERR_EMPTY_WAIT);
+          if (!ok) break;
+          uint8_t* sa = smem + stage * L::STAGE_BYTES;
+          uint8_t* sb = sa + L::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+          const int k0 = kb * BLOCK_K;
+          if (!p.a_mn) {
+            tma_load_3d(sa, &map_a, &full_bar[stage], k0, m0, b);  // box {64 k, 128 m}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_M / 64; ++j)                  // boxes {64 m, 64 k}
+              tma_load_3d(sa + j * (BLOCK_K * 128), &map_a, &full_bar[stage], m0 + j * 64, k0, b);
+          }
+          if (!p.b_mn) {
+            tma_load_3d(sb, &map_b, &full_bar[stage], k0, n0, b);  // box {64 k, BLOCK_N n}
+          } else {
+#pragma unroll
+            for (int j = 0; j < BLOCK_N / 64; ++j)                  // boxes {64 n, 64 k}
+              tma_load_3d(sb + j * (BLOCK_K * 128), &map_b, &full_bar[stage], n0 + j * 64, k0, b);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer --------------------------------------------------
+    if (elect_one()) {
+      const uint32_t fmt = p.is_fp16 ? 0u : 1u;
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.a_mn != 0) << 15) |
+                             ((uint32_t)(p.b_mn != 0) << 16) | ((uint32_t)(BLOCK_N >> 3) << 17) |
+                             ((uint32_t)(BLOCK_M >> 4) << 24);
+      const uint32_t a_lbo = p.a_mn ? BLOCK_K * 128 : 16;
+      const uint32_t b_lbo = p.b_mn ? BLOCK_K * 128 : 16;
+      const uint32_t a_kstep = p.a_mn ? UMMA_K * 128 : UMMA_K * 2;  // bytes to advance per UMMA_K
+      const uint32_t b_kstep = p.b_mn ? UMMA_K * 128 : UMMA_K * 2;
+      uint32_t stage = 0, phase = 0;
+      uint32_t acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.err, ERR_TMEM_EMPTY_WAIT);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.err, ERR_FULL_WAIT);
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::STAGE_BYTES);
+          const uint32_t sb = sa + L::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+            const uint64_t da = make_smem_desc(sa + k * a_kstep, a_lbo);
+            const uint64_t db = make_smem_desc(sb + k * b_kstep, b_lbo);
+            tcgen05_mma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tcgen05_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tcgen05_commit(&tmem_full_bar[acc]);  // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------ epilogue ----------------------------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    uint32_t acc = 0, acc_phase = 0;
+    bool ok = true;
+    float mean_a = 0.f, mean_b = 1.f;
+    if (p.accumulate == 2) {
+      const float t = *p.step;
+      mean_a = t / (t + 1.f);
+      mean_b = 1.f / (t + 1.f);
+    }
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int b, mb, nb;
+      tile_coords(tile, tiles_m, tiles_n, b, mb, nb);
+      ok = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, p.err, ERR_TMEM_FULL_WAIT);
+      if (!ok) break;
+      tcgen05_fence_after();
+      const int row = mb * BLOCK_M + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BLOCK_N;
+      uint8_t* crow = (uint8_t*)p.C + ((long long)b * p.batch_stride_c + (long long)row * p.ldc) *
+                                          (p.c_dtype == XL_F32 ? 4 : 2);
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(taddr + c, r);
+        tmem_ld_wait();
+        const int col0 = nb * BLOCK_N + c;
+        if (!row_ok || col0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (col0 + j < p.N) {
+              float bv;
+              if (p.bias_dtype == XL_F32) bv = ((const float*)p.bias)[col0 + j];
+              else if (p.bias_dtype == XL_BF16) bv = __bfloat162float(((const __nv_bfloat16*)p.bias)[col0 + j]);
+              else bv = __half2float(((const __half*)p.bias)[col0 + j]);
+              v[j] += bv;
+            }
+          }
+        }
+        if (p.act) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], p.act);
+        }
+        const bool full = (col0 + 32 <= p.N);
+        if (p.c_dtype == XL_F32) {
+          float* dst = (float*)crow + col0;
+          if (full && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              if (p.accumulate) {
+                const float4 old = *(const float4*)(dst + j);
+                if (p.accumulate == 1) { o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+                else { o.x = old.x * mean_a + o.x * mean_b; o.y = old.y * mean_a + o.y * mean_b;
+                       o.z = old.z * mean_a + o.z * mean_b; o.w = old.w * mean_a + o.w * mean_b; }
+              }
+              *(float4*)(dst + j) = o;
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+              float o = v[j];
+              if (p.accumulate == 1) o += dst[j];
+              else if (p.accumulate == 2) o = dst[j] * mean_a + o * mean_b;
+              dst[j] = o;
+            }
+          }
+        } else {
+          uint16_t* dst = (uint16_t*)crow + col0;
+          const bool bf = p.c_dtype == XL_BF16;
+          if (full && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 old;
+              if (p.accumulate) old = *(const uint4*)(dst + j);
+              uint4 o;
+              uint16_t* oe = (uint16_t*)&o;
+              const uint16_t* ol = (const uint16_t*)&old;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                float val = v[j + e];
+                if (p.accumulate) {
+                  const float prev = bf ? __bfloat162float(__ushort_as_bfloat16(ol[e])) : __half2float(__ushort_as_half(ol[e]));
+                  val = p.accumulate == 1 ? prev + val : prev * mean_a + val * mean_b;
+                }
+                oe[e] = bf ? __bfloat16_as_ushort(__float2bfloat16_rn(val)) : __half_as_ushort(__float2half_rn(val));
+              }
+              *(uint4*)(dst + j) = o;
+            }
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
+              float val = v[j];
+              if (p.accumulate) {
+                const float prev = bf ? __bfloat162float(__ushort_as_bfloat16(dst[j])) : __half2float(__ushort_as_half(dst[j]));
+                val = p.accumulate == 1 ? prev + val : prev * mean_a + val * mean_b;
+              }
+              dst[j] = bf ? __bfloat16_as_ushort(__float2bfloat16_rn(val)) : __half_as_ushort(__float2half_rn(val));
+            }
+          }
+        }
+      }
+      // all TMEM reads of this warp are complete (wait::ld above): hand the accumulator back to the MMA warp
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // ---- teardown: every role arrives here, also after an abort --------------------------------------------------------
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = (EncodeTiledFn)ptr;
+  return fn;
+}
+
+// 3-D map over a row-major matrix with `rows` rows of `cols` contiguous elements (leading dimension `ld`), `batch`
+// matrices `batch_stride` elements apart; boxes of {box_cols, box_rows, 1} with 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* ptr, int is_fp16, long long rows, long long cols, long long ld,
+             long long batch, long long batch_stride, int box_cols, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -2;
+  cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(batch > 1 ? batch_stride : rows * ld) * 2};
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, is_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void*)ptr, dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+template <int BLOCK_N>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int sm_count, cudaStream_t s) {
+  using L = SmemLayout<BLOCK_N>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int tiles = ((p.M + BLOCK_M - 1) / BLOCK_M) * ((p.N + BLOCK_N - 1) / BLOCK_N) * p.batch;
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  gemm_tcgen05_kernel<BLOCK_N><<<grid, NUM_THREADS, L::TOTAL, s>>>(ma, mb, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// C = epilogue(A * B), 16-bit operands, fp32 accumulation.
+//   a: if a_mn == 0 stored (M x K) row-major with leading dimension lda; if a_mn == 1 stored (K x M) row-major.
+//   b: if b_mn == 0 stored (N x K) row-major with leading dimension ldb; if b_mn == 1 stored (K x N) row-major.
+//   Leading dimensions and batch strides are in elements; pointers and leading dimensions must be 16-byte aligned.
+//   err: device int that receives a non-zero code if a bounded wait inside the kernel gave up (may be null).
+// Returns 0, a CUDA error code, or a negative value when the arguments are not supported by this kernel.
+XL_API int xl_gemm_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, int batch, int a_mn, int b_mn,
+                           long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
+                           long long stride_c, int ab_is_fp16, int c_dtype, const void* bias, int bias_dtype, int act,
+                           int accumulate, const float* step, float alpha, int* err, int sm_count, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -1;
+  if ((((uintptr_t)a) & 15) || (((uintptr_t)b) & 15) || (lda % 8) || (ldb % 8)) return -1;
+  if (batch > 1 && ((stride_a % 8) || (stride_b % 8))) return -1;
+  const int block_n = (N <= 128) ? 128 : 256;
+  CUtensorMap ma, mb;
+  int r;
+  if (!a_mn) r = make_map(&ma, a, ab_is_fp16, M, K, lda, batch, stride_a, BLOCK_K, BLOCK_M);
+  else r = make_map(&ma, a, ab_is_fp16, K, M, lda, batch, stride_a, 64, BLOCK_K);
+  if (r) return r;
+  if (!b_mn) r = make_map(&mb, b, ab_is_fp16, N, K, ldb, batch, stride_b, BLOCK_K, block_n);
+  else r = make_map(&mb, b, ab_is_fp16, K, N, ldb, batch, stride_b, 64, BLOCK_K);
+  if (r) return r;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = batch;
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  p.C = c; p.ldc = ldc; p.batch_stride_c = stride_c; p.c_dtype = c_dtype;
+  p.bias = bias; p.bias_dtype = bias_dtype; p.act = act; p.accumulate = accumulate; p.step = step;
+  p.alpha = alpha; p.is_fp16 = ab_is_fp16; p.err = err;
+  if (sm_count <= 0) sm_count = 148;
+  if (block_n == 128) return launch<128>(ma, mb, p, sm_count, s);
+  return launch<256>(ma, mb, p, sm_count, s);
+}

@@ -22,6 +22,5 @@ def cross_entropy_with_grad(x: xl.Tensor, labels: xl.Tensor, loss_scaling: Union
     """Loss and d(loss * loss_scaling)/dx in one pass (no separate backward graph needed for the loss)."""
     if not isinstance(loss_scaling, xl.Tensor):
         loss_scaling = xl.constant(loss_scaling, xl.float32, "loss_scaling")
-    probs = ops.softmax(x, axis=-1)
-    return ops.nll_loss_with_softmax_grad(probs, labels, loss_grad=loss_scaling, reduction=reduction,
-                                          ignore_index=ignore_index)
+    return ops.cross_entropy_with_grad(x, labels, loss_grad=loss_scaling, reduction=reduction,
+                                       ignore_index=ignore_index)

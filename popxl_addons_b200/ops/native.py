@@ -1,0 +1,708 @@
+"""Bridge between the op registry and the hand-written sm_100a kernels in `lib/libxlb200.so`.
+
+Importing this module loads the library (building it first if the sources are newer and nvcc is available) and
+attaches a CUDA implementation to every op that has one. A CUDA implementation returns `NotImplemented` for operands it
+does not cover (odd alignment, unsupported dtype); the session then runs the op's torch reference. If the library is
+missing on a machine with a GPU the import fails loudly rather than silently running the reference everywhere.
+"""
+import ctypes
+import os
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..xl import dtypes as _dt
+from ..xl.opdef import OPS, native
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libxlb200.so")
+
+F32, F16, BF16 = 0, 1, 2
+_CODE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+LAUNCHES = {"count": 0, "by_kernel": {}}
+
+
+def _load():
+    if not os.path.exists(_LIB_PATH):
+        try:
+            from .. import build as _build
+
+            _build.build()
+        except Exception as e:  # pragma: no cover
+            raise ImportError(f"Native library {_LIB_PATH} is missing and could not be built: {e}") from e
+    return ctypes.CDLL(_LIB_PATH)
+
+
+LIB = _load()
+_c_int, _c_ll, _c_f, _c_p = ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_void_p
+
+
+def _sig(name, *argtypes, restype=_c_int):
+    fn = getattr(LIB, name)
+    fn.argtypes = list(argtypes)
+    fn.restype = restype
+    return fn
+
+
+_gelu_fwd = _sig("xl_gelu_fwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p)
+_gelu_bwd = _sig("xl_gelu_bwd", _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p)
+_silu_fwd = _sig("xl_silu_fwd", _c_p, _c_p, _c_ll, _c_int, _c_p)
+_silu_bwd = _sig("xl_silu_bwd", _c_p, _c_p, _c_p, _c_ll, _c_int, _c_p)
+_swiglu_fwd = _sig("xl_swiglu_fwd", _c_p, _c_p, _c_p, _c_ll, _c_int, _c_p)
+_swiglu_bwd = _sig("xl_swiglu_bwd", _c_p, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_p)
+_ln_fwd = _sig("xl_layer_norm_fwd", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_f, _c_int, _c_p)
+_ln_bwd = _sig("xl_layer_norm_bwd", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p)
+_rms_fwd = _sig("xl_rms_norm_fwd", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_f, _c_int, _c_p)
+_rms_bwd = _sig("xl_rms_norm_bwd", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p)
+_norm_parts = _sig("xl_norm_bwd_parts", _c_ll)
+_adam = _sig("xl_adam_step", _c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_p, _c_f, _c_f, _c_f, _c_f, _c_f,
+             _c_f, _c_int, _c_ll, _c_p)
+_sgd = _sig("xl_sgd_step", _c_p, _c_int, _c_p, _c_int, _c_p, _c_f, _c_f, _c_f, _c_f, _c_ll, _c_p)
+_acc_mean = _sig("xl_accumulate_mean", _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_p)
+_sumsq_parts = _sig("xl_sumsq_parts", _c_ll)
+_sumsq = _sig("xl_grad_sumsq", _c_p, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_p)
+_rotary = _sig("xl_rotary", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll,
+               _c_ll, _c_ll, _c_ll, _c_ll, _c_ll, _c_p)
+_gq = _sig("xl_gq_decompress", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p)
+_sm_fwd = _sig("xl_attn_softmax_fwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p)
+_sm_bwd = _sig("xl_attn_softmax_bwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p)
+_ce = _sig("xl_ce_fwd_bwd", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p, _c_f, _c_int, _c_p)
+_gemm = _sig("xl_gemm_tcgen05", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll,
+             _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_p)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _count(name: str):
+    LAUNCHES["count"] += 1
+    LAUNCHES["by_kernel"][name] = LAUNCHES["by_kernel"].get(name, 0) + 1
+
+
+def _check(rc: int, name: str):
+    if rc != 0:
+        raise RuntimeError(f"CUDA kernel launcher {name} failed with code {rc} "
+                           f"({torch.cuda.get_device_name() if torch.cuda.is_available() else 'no device'})")
+
+
+def _ok(*ts) -> bool:
+    """Operands the vectorised kernels accept: CUDA, contiguous, 16-byte aligned, fp32 / fp16 / bf16."""
+    for t in ts:
+        if t is None:
+            continue
+        if not (t.is_cuda and t.is_contiguous() and t.dtype in _CODE and t.data_ptr() % 16 == 0):
+            return False
+    return True
+
+
+# ---- scratch memory ------------------------------------------------------------------------------------------------
+_WORKSPACE: Dict[Tuple[int, str], torch.Tensor] = {}
+_ERR: Dict[int, torch.Tensor] = {}
+
+
+def workspace(nbytes: int, device: torch.device, tag: str = "default") -> torch.Tensor:
+    """Per-device scratch buffer (fp32 view), grown on demand and reused by later launches on the same stream."""
+    key = (device.index or 0, tag)
+    buf = _WORKSPACE.get(key)
+    n = (nbytes + 3) // 4
+    if buf is None or buf.numel() < n:
+        buf = torch.empty(max(n, 1 << 18), dtype=torch.float32, device=device)
+        _WORKSPACE[key] = buf
+    return buf
+
+
+def gemm_error_flag(device: torch.device) -> torch.Tensor:
+    """Device int that the GEMM kernels set when one of their bounded waits gave up."""
+    idx = device.index or 0
+    if idx not in _ERR:
+        _ERR[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _ERR[idx]
+
+
+def check_gemm_errors():
+    """Raise if any GEMM launched so far reported a wait that ran out (synchronises the device)."""
+    for idx, flag in _ERR.items():
+        code = int(flag.item())
+        if code != 0:
+            flag.zero_()
+            names = {1: "operand tiles never arrived (TMA)", 2: "shared-memory stage was never released",
+                     3: "accumulator never completed", 4: "accumulator buffer was never drained"}
+            raise RuntimeError(f"tcgen05 GEMM on cuda:{idx} gave up waiting: {names.get(code, code)}")
+
+
+# ---- elementwise ---------------------------------------------------------------------------------------------------
+@native("gelu")
+def gelu_cuda(x, approximate="none"):
+    if not _ok(x):
+        return NotImplemented
+    y = torch.empty_like(x)
+    _check(_gelu_fwd(x.data_ptr(), y.data_ptr(), x.numel(), _CODE[x.dtype], int(approximate == "tanh"), _stream()),
+           "gelu_fwd")
+    _count("gelu_fwd")
+    return y
+
+
+@native("gelu_grad")
+def gelu_grad_cuda(x, g, approximate="none"):
+    if not _ok(x, g) or x.dtype != g.dtype:
+        return NotImplemented
+    dx = torch.empty_like(x)
+    _check(_gelu_bwd(x.data_ptr(), g.data_ptr(), dx.data_ptr(), x.numel(), _CODE[x.dtype],
+                     int(approximate == "tanh"), _stream()), "gelu_bwd")
+    _count("gelu_bwd")
+    return dx
+
+
+@native("swish")
+def swish_cuda(x):
+    if not _ok(x):
+        return NotImplemented
+    y = torch.empty_like(x)
+    _check(_silu_fwd(x.data_ptr(), y.data_ptr(), x.numel(), _CODE[x.dtype], _stream()), "silu_fwd")
+    _count("silu_fwd")
+    return y
+
+
+@native("swish_grad")
+def swish_grad_cuda(x, g):
+    if not _ok(x, g) or x.dtype != g.dtype:
+        return NotImplemented
+    dx = torch.empty_like(x)
+    _check(_silu_bwd(x.data_ptr(), g.data_ptr(), dx.data_ptr(), x.numel(), _CODE[x.dtype], _stream()), "silu_bwd")
+    _count("silu_bwd")
+    return dx
+
+
+@native("swiglu")
+def swiglu_cuda(gate, up):
+    if not _ok(gate, up) or gate.dtype != up.dtype or gate.shape != up.shape:
+        return NotImplemented
+    y = torch.empty_like(gate)
+    _check(_swiglu_fwd(gate.data_ptr(), up.data_ptr(), y.data_ptr(), gate.numel(), _CODE[gate.dtype], _stream()),
+           "swiglu_fwd")
+    _count("swiglu_fwd")
+    return y
+
+
+@native("swiglu_grad")
+def swiglu_grad_cuda(gate, up, g):
+    if not _ok(gate, up, g) or not (gate.dtype == up.dtype == g.dtype):
+        return NotImplemented
+    dg, du = torch.empty_like(gate), torch.empty_like(up)
+    _check(_swiglu_bwd(gate.data_ptr(), up.data_ptr(), g.data_ptr(), dg.data_ptr(), du.data_ptr(), gate.numel(),
+                       _CODE[gate.dtype], _stream()), "swiglu_bwd")
+    _count("swiglu_bwd")
+    return dg, du
+
+
+# ---- normalisation -------------------------------------------------------------------------------------------------
+@native("layer_norm")
+def layer_norm_cuda(x, w, b, eps):
+    if not _ok(x, w, b) or not (x.dtype == w.dtype == b.dtype):
+        return NotImplemented
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    y = torch.empty_like(x)
+    mean = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    rstd = torch.empty_like(mean)
+    rc = _ln_fwd(x.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rows, cols,
+                 float(eps), _CODE[x.dtype], _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "layer_norm_fwd")
+    _count("layer_norm_fwd")
+    return y, mean, rstd
+
+
+@native("layer_norm_grad")
+def layer_norm_grad_cuda(x, w, mean, rstd, g):
+    if not _ok(x, w, g, mean, rstd) or not (x.dtype == w.dtype == g.dtype):
+        return NotImplemented
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    dx, dw, db = torch.empty_like(x), torch.empty_like(w), torch.empty_like(w)
+    ws = workspace(_norm_parts(rows) * 2 * cols * 4, x.device, "norm")
+    rc = _ln_bwd(x.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(), g.data_ptr(), dx.data_ptr(),
+                 dw.data_ptr(), db.data_ptr(), ws.data_ptr(), rows, cols, _CODE[x.dtype], _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "layer_norm_bwd")
+    _count("layer_norm_bwd")
+    return dx, dw, db
+
+
+@native("rms_norm")
+def rms_norm_cuda(x, w, eps):
+    if not _ok(x, w) or x.dtype != w.dtype:
+        return NotImplemented
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    y = torch.empty_like(x)
+    rstd = torch.empty(x.shape[:-1], dtype=torch.float32, device=x.device)
+    rc = _rms_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), rows, cols, float(eps), _CODE[x.dtype],
+                  _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "rms_norm_fwd")
+    _count("rms_norm_fwd")
+    return y, rstd
+
+
+@native("rms_norm_grad")
+def rms_norm_grad_cuda(x, w, rstd, g):
+    if not _ok(x, w, g, rstd) or not (x.dtype == w.dtype == g.dtype):
+        return NotImplemented
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    dx, dw = torch.empty_like(x), torch.empty_like(w)
+    ws = workspace(_norm_parts(rows) * 2 * cols * 4, x.device, "norm")
+    rc = _rms_bwd(x.data_ptr(), w.data_ptr(), rstd.data_ptr(), g.data_ptr(), dx.data_ptr(), dw.data_ptr(),
+                  ws.data_ptr(), rows, cols, _CODE[x.dtype], _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "rms_norm_bwd")
+    _count("rms_norm_bwd")
+    return dx, dw
+
+
+# ---- optimizer -----------------------------------------------------------------------------------------------------
+def _scalars(extra, attrs):
+    """Resolve op scalars to floats; tensor-valued scalars make the native path decline (they stay on device)."""
+    vals = dict(attrs)
+    if vals.pop("_tensor_scalars"):
+        return None
+    return vals
+
+
+@native("adam_fused_")
+def adam_cuda(w, g, m, v, *rest, has_step, has_master, bias_correction, **attrs):
+    rest = list(rest)
+    step = rest.pop(0) if has_step else None
+    master = rest.pop(0) if has_master else None
+    s = _scalars(rest, attrs)
+    if s is None or not _ok(w, g, m, v, master) or v.dtype != torch.float32:
+        return NotImplemented
+    if g.dtype != w.dtype and g.dtype != torch.float32:
+        return NotImplemented
+    if step is not None and step.dtype != torch.float32:
+        return NotImplemented
+    rc = _adam(w.data_ptr(), _CODE[w.dtype], g.data_ptr(), _CODE[g.dtype], m.data_ptr(), _CODE[m.dtype], v.data_ptr(),
+               master.data_ptr() if master is not None else None, step.data_ptr() if step is not None else None,
+               float(s["lr"]), float(s["beta1"]), float(s["beta2"]), float(s["epsilon"]), float(s["weight_decay"]),
+               float(s["grad_scale"]), int(bool(bias_correction)), w.numel(), _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "adam_step")
+    _count("adam_step")
+    return w
+
+
+@native("sgd_fused_")
+def sgd_cuda(w, g, *rest, has_momentum, **attrs):
+    rest = list(rest)
+    buf = rest.pop(0) if has_momentum else None
+    s = _scalars(rest, attrs)
+    if s is None or not _ok(w, g, buf) or (buf is not None and buf.dtype != torch.float32):
+        return NotImplemented
+    rc = _sgd(w.data_ptr(), _CODE[w.dtype], g.data_ptr(), _CODE[g.dtype], buf.data_ptr() if buf is not None else None,
+              float(s["lr"]), float(s["momentum"]), float(s["weight_decay"]), float(s["grad_scale"]), w.numel(),
+              _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "sgd_step")
+    _count("sgd_step")
+    return w
+
+
+@native("accumulate_mean_")
+def accumulate_mean_cuda(acc, x, *extra, **attrs):
+    if attrs.get("_tensor_scalars") != ("step",) or not _ok(acc, x) or extra[0].dtype != torch.float32:
+        return NotImplemented
+    _check(_acc_mean(acc.data_ptr(), _CODE[acc.dtype], x.data_ptr(), _CODE[x.dtype], extra[0].data_ptr(), acc.numel(),
+                     _stream()), "accumulate_mean")
+    _count("accumulate_mean")
+    return acc
+
+
+def grad_sumsq_cuda(t, scale):
+    if not _ok(t) or not (scale.is_cuda and scale.dtype == torch.float32):
+        return NotImplemented
+    out = torch.empty((), dtype=torch.float32, device=t.device)
+    ws = workspace(_sumsq_parts(t.numel()) * 4, t.device, "sumsq")
+    _check(_sumsq(t.data_ptr(), _CODE[t.dtype], scale.data_ptr(), out.data_ptr(), ws.data_ptr(), t.numel(), _stream()),
+           "grad_sumsq")
+    _count("grad_sumsq")
+    return out
+
+
+# ---- rotary / int4 -------------------------------------------------------------------------------------------------
+def rotary_launch(x, sin, cos, y, rotary_dim, inverse):
+    """Rotate `x (B,H,S,D)` into `y` (may alias `x`); both may be strided views whose last axis is contiguous."""
+    B, H, S, D = x.shape
+    _check(_rotary(x.data_ptr(), sin.data_ptr(), cos.data_ptr(), y.data_ptr(), B, H, S, D, rotary_dim, sin.shape[0],
+                   int(bool(inverse)), _CODE[x.dtype], x.stride(0), x.stride(1), x.stride(2), y.stride(0), y.stride(1),
+                   y.stride(2), _stream()), "rotary")
+    _count("rotary")
+
+
+@native("rotary_pos_embed")
+def rotary_cuda(x, sin, cos, rotary_dim, inverse):
+    if not (x.is_cuda and x.dtype in _CODE and x.dim() == 4 and x.stride(-1) == 1) or not _ok(sin, cos):
+        return NotImplemented
+    if not (x.dtype == sin.dtype == cos.dtype) or x.shape[-1] % 2 or rotary_dim % 2:
+        return NotImplemented
+    y = torch.empty_like(x)  # keeps the strides of a dense permuted view
+    if y.stride(-1) != 1:
+        y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    rotary_launch(x, sin, cos, y, rotary_dim, inverse)
+    return y
+
+
+def gq_decompress_cuda(packed, scale, bias):
+    if not (packed.is_cuda and packed.is_contiguous() and packed.dtype == torch.uint16) or not _ok(scale, bias):
+        return NotImplemented
+    if scale.dtype != bias.dtype:
+        return NotImplemented
+    r, g, w = packed.shape
+    out = torch.empty((r, g * w * 4), dtype=scale.dtype, device=packed.device)
+    rc = _gq(packed.data_ptr(), scale.data_ptr(), bias.data_ptr(), out.data_ptr(), packed.numel(), w, _CODE[scale.dtype],
+             _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "gq_decompress")
+    _count("gq_decompress")
+    return out
+
+
+# ---- GEMM ----------------------------------------------------------------------------------------------------------
+_SM_COUNT: Dict[int, int] = {}
+
+
+def _sms(device) -> int:
+    idx = device.index or 0
+    if idx not in _SM_COUNT:
+        _SM_COUNT[idx] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNT[idx]
+
+
+def _major(t: torch.Tensor, contraction_last: bool):
+    """(is_mn_major, leading dimension) of a 2-D (or batched 3-D) operand view, or None if neither axis is dense.
+    `contraction_last`: the reduction dimension is the last axis (A operand) rather than the second-to-last (B)."""
+    s_row, s_col = t.stride(-2), t.stride(-1)
+    rows, cols = t.shape[-2], t.shape[-1]
+    if s_col == 1 and (s_row >= cols):
+        # last axis contiguous
+        return (0 if contraction_last else 1), s_row
+    if s_row == 1 and (s_col >= rows):
+        return (1 if contraction_last else 0), s_col
+    if cols == 1 and s_row == 1:
+        return (1 if contraction_last else 0), max(s_col, rows)
+    return None
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = None, act: int = 0,
+         out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, accumulate: int = 0,
+         step: Optional[torch.Tensor] = None, alpha: float = 1.0):
+    """`out = act(alpha * a @ b + bias)` on the tcgen05 kernel. `a`: (M,K) or (B,M,K); `b`: (K,N) or (B,K,N); either may
+    be a transposed view. With `accumulate=1` the result is added to `out`, with `accumulate=2` it is folded into `out`
+    as a running mean with count `step`. Returns NotImplemented for operands the kernel cannot take."""
+    if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16) or not (a.is_cuda and b.is_cuda):
+        return NotImplemented
+    batched = a.dim() == 3
+    if a.dim() not in (2, 3) or b.dim() != a.dim():
+        return NotImplemented
+    ma, mb = _major(a, True), _major(b, False)
+    if ma is None or mb is None:
+        return NotImplemented
+    (a_mn, lda), (b_mn, ldb) = ma, mb
+    M, K = a.shape[-2], a.shape[-1]
+    N = b.shape[-1]
+    if b.shape[-2] != K:
+        raise ValueError(f"gemm shape mismatch {tuple(a.shape)} x {tuple(b.shape)}")
+    batch = a.shape[0] if batched else 1
+    sa = a.stride(0) if batched else 0
+    sb = b.stride(0) if batched else 0
+    if batched and b.shape[0] != batch:
+        return NotImplemented
+    if lda % 8 or ldb % 8 or a.data_ptr() % 16 or b.data_ptr() % 16 or (batched and (sa % 8 or sb % 8)):
+        return NotImplemented
+    if out is None:
+        out_dtype = out_dtype or a.dtype
+        out = torch.empty((batch, M, N) if batched else (M, N), dtype=out_dtype, device=a.device)
+    if out.dtype not in _CODE or out.stride(-1) != 1 or out.dim() != a.dim():
+        return NotImplemented
+    ldc = out.stride(-2)
+    stride_c = out.stride(0) if batched else 0
+    esz = out.element_size()
+    if (ldc * esz) % 16 or out.data_ptr() % 16 or (batched and (stride_c * esz) % 16):
+        return NotImplemented
+    if bias is not None and not (bias.is_cuda and bias.is_contiguous() and bias.dtype in _CODE and bias.numel() == N):
+        return NotImplemented
+    err = gemm_error_flag(a.device)
+    rc = _gemm(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, batch, a_mn, b_mn, lda, ldb, ldc, sa, sb, stride_c,
+               int(a.dtype == torch.float16), _CODE[out.dtype], bias.data_ptr() if bias is not None else None,
+               _CODE[bias.dtype] if bias is not None else 0, act, accumulate,
+               step.data_ptr() if step is not None else None, float(alpha), err.data_ptr(), _sms(a.device), _stream())
+    if rc < 0:
+        return NotImplemented
+    _check(rc, "gemm_tcgen05")
+    _count("gemm_tcgen05")
+    return out
+
+
+def _flatten_batch(t: torch.Tensor) -> Optional[torch.Tensor]:
+    """View an N-D operand as 3-D (batch, rows, cols) without copying, if its batch axes are jointly dense."""
+    if t.dim() == 3:
+        return t
+    if t.is_contiguous():
+        return t.view(-1, t.shape[-2], t.shape[-1])
+    # batch axes must collapse to one stride
+    stride = t.stride(-3)
+    expected = stride
+    for d in range(t.dim() - 3, -1, -1):
+        if t.shape[d] != 1 and t.stride(d) != expected:
+            return None
+        expected = t.stride(d) * t.shape[d] if t.shape[d] != 1 else expected
+        if d > 0:
+            expected = t.stride(d) * t.shape[d]
+    n = 1
+    for sdim in t.shape[:-2]:
+        n *= sdim
+    return torch.as_strided(t, (n, t.shape[-2], t.shape[-1]), (stride, t.stride(-2), t.stride(-1)), t.storage_offset())
+
+
+@native("matmul")
+def matmul_cuda(a, b):
+    if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16):
+        return NotImplemented
+    if b.dim() == 2 and a.dim() >= 2:
+        a2 = a.reshape(-1, a.shape[-1]) if a.dim() > 2 else a
+        res = gemm(a2, b)
+        if res is NotImplemented:
+            return res
+        return res.view(*a.shape[:-1], b.shape[-1])
+    if a.dim() == b.dim() and a.dim() >= 3 and a.shape[:-2] == b.shape[:-2]:
+        a3, b3 = _flatten_batch(a), _flatten_batch(b)
+        if a3 is None or b3 is None:
+            return NotImplemented
+        res = gemm(a3, b3)
+        if res is NotImplemented:
+            return res
+        return res.view(*a.shape[:-2], a.shape[-2], b.shape[-1])
+    return NotImplemented
+
+
+_ACT = {"none": 0, "gelu": 1, "gelu_tanh": 2, "relu": 3}
+
+
+@native("linear_bias_act")
+def linear_bias_act_cuda(x, w, *b, act):
+    if x.dtype != w.dtype or x.dtype not in (torch.bfloat16, torch.float16) or not x.is_contiguous():
+        return NotImplemented
+    res = gemm(x.reshape(-1, x.shape[-1]), w, bias=b[0] if b else None, act=_ACT[act])
+    if res is NotImplemented:
+        return res
+    return res.view(*x.shape[:-1], w.shape[-1])
+
+
+# ---- attention: two batched tcgen05 GEMMs around a fused scale + causal-mask + softmax kernel ---------------------------
+@native("attention")
+def attention_cuda(q, k, v, causal, scale):
+    if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.bfloat16, torch.float16) or q.dim() != 4:
+        return NotImplemented
+    B, H, Sq, D = q.shape
+    Sk = k.shape[-2]
+    q3, k3, v3 = (_flatten_batch(t) for t in (q, k, v))
+    if q3 is None or k3 is None or v3 is None:
+        return NotImplemented
+    scores = gemm(q3, k3.transpose(-1, -2))
+    if scores is NotImplemented:
+        return NotImplemented
+    lse = torch.empty((B * H, Sq), dtype=torch.float32, device=q.device)
+    rc = _sm_fwd(scores.data_ptr(), lse.data_ptr(), B * H * Sq, Sq, Sk, float(scale), int(bool(causal)),
+                 _CODE[scores.dtype], _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "attn_softmax_fwd")
+    _count("attn_softmax_fwd")
+    o = gemm(scores, v3)
+    if o is NotImplemented:
+        return NotImplemented
+    return o.view(B, H, Sq, D), lse.view(B, H, Sq)
+
+
+@native("attention_grad")
+def attention_grad_cuda(q, k, v, o, lse, do, causal, scale):
+    if not (q.dtype == k.dtype == v.dtype == do.dtype) or q.dtype not in (torch.bfloat16, torch.float16):
+        return NotImplemented
+    B, H, Sq, D = q.shape
+    Sk = k.shape[-2]
+    q3, k3, v3, do3 = (_flatten_batch(t) for t in (q, k, v, do))
+    if any(t is None for t in (q3, k3, v3, do3)):
+        return NotImplemented
+    # probabilities are recomputed from q, k (they are not kept between forward and backward)
+    p = gemm(q3, k3.transpose(-1, -2))
+    if p is NotImplemented:
+        return NotImplemented
+    tmp_lse = torch.empty((B * H, Sq), dtype=torch.float32, device=q.device)
+    rc = _sm_fwd(p.data_ptr(), tmp_lse.data_ptr(), B * H * Sq, Sq, Sk, float(scale), int(bool(causal)),
+                 _CODE[p.dtype], _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "attn_softmax_fwd")
+    _count("attn_softmax_fwd")
+    dv = gemm(p.transpose(-1, -2), do3)
+    dp = gemm(do3, v3.transpose(-1, -2))
+    if dv is NotImplemented or dp is NotImplemented:
+        return NotImplemented
+    rc = _sm_bwd(p.data_ptr(), dp.data_ptr(), B * H * Sq, Sq, Sk, float(scale), int(bool(causal)), _CODE[p.dtype],
+                 _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "attn_softmax_bwd")
+    _count("attn_softmax_bwd")
+    dq = gemm(dp, k3)
+    dk = gemm(dp.transpose(-1, -2), q3)
+    if dq is NotImplemented or dk is NotImplemented:
+        return NotImplemented
+    return dq.view_as(q), dk.view_as(k), dv.view_as(v)
+
+
+def _heads_view(mat, col0, B, S, H, D):
+    """(B, H, S, D) strided view of columns [col0, col0 + H*D) of a (B*S, ld) row-major matrix."""
+    ld = mat.stride(0)
+    return torch.as_strided(mat, (B, H, S, D), (S * ld, D, ld, 1), mat.storage_offset() + col0)
+
+
+@native("attention_qkv")
+def attention_qkv_cuda(qkv, sin, cos, seq_len, n_heads, head_dim, rotary_dim, causal, scale, inplace):
+    if qkv.dtype not in (torch.bfloat16, torch.float16) or not (qkv.is_cuda and qkv.is_contiguous()):
+        return NotImplemented
+    T = qkv.shape[0]
+    B, S, H, D = T // seq_len, seq_len, n_heads, head_dim
+    hd = H * D
+    rot = qkv if inplace else qkv.clone()
+    q, k, v = (_heads_view(rot, i * hd, B, S, H, D) for i in range(3))
+    if rotary_dim:
+        if sin.dtype != qkv.dtype or not _ok(sin, cos):
+            return NotImplemented
+        rotary_launch(q, sin, cos, q, rotary_dim, False)
+        rotary_launch(k, sin, cos, k, rotary_dim, False)
+    out = torch.empty((T, hd), dtype=qkv.dtype, device=qkv.device)
+    o = _heads_view(out, 0, B, S, H, D)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=qkv.device)
+    for b in range(B):
+        scores = gemm(q[b], k[b].transpose(-1, -2))
+        if scores is NotImplemented:
+            return NotImplemented
+        rc = _sm_fwd(scores.data_ptr(), lse[b].data_ptr(), H * S, S, S, float(scale), int(bool(causal)),
+                     _CODE[scores.dtype], _stream())
+        if rc == -1:
+            return NotImplemented
+        _check(rc, "attn_softmax_fwd")
+        _count("attn_softmax_fwd")
+        if gemm(scores, v[b], out=o[b]) is NotImplemented:
+            return NotImplemented
+    return out, rot, lse
+
+
+@native("attention_qkv_grad")
+def attention_qkv_grad_cuda(qkv_rot, lse, dout, sin, cos, seq_len, n_heads, head_dim, rotary_dim, causal, scale):
+    if qkv_rot.dtype not in (torch.bfloat16, torch.float16) or not (qkv_rot.is_contiguous() and dout.is_contiguous()):
+        return NotImplemented
+    if dout.dtype != qkv_rot.dtype:
+        return NotImplemented
+    T = qkv_rot.shape[0]
+    B, S, H, D = T // seq_len, seq_len, n_heads, head_dim
+    hd = H * D
+    q, k, v = (_heads_view(qkv_rot, i * hd, B, S, H, D) for i in range(3))
+    do = _heads_view(dout, 0, B, S, H, D)
+    dqkv = torch.empty_like(qkv_rot)
+    dq, dk, dv = (_heads_view(dqkv, i * hd, B, S, H, D) for i in range(3))
+    tmp_lse = torch.empty((H, S), dtype=torch.float32, device=qkv_rot.device)
+    for b in range(B):
+        p = gemm(q[b], k[b].transpose(-1, -2))
+        if p is NotImplemented:
+            return NotImplemented
+        rc = _sm_fwd(p.data_ptr(), tmp_lse.data_ptr(), H * S, S, S, float(scale), int(bool(causal)), _CODE[p.dtype],
+                     _stream())
+        if rc == -1:
+            return NotImplemented
+        _check(rc, "attn_softmax_fwd")
+        _count("attn_softmax_fwd")
+        if gemm(p.transpose(-1, -2), do[b], out=dv[b]) is NotImplemented:
+            return NotImplemented
+        dp = gemm(do[b], v[b].transpose(-1, -2))
+        if dp is NotImplemented:
+            return NotImplemented
+        _check(_sm_bwd(p.data_ptr(), dp.data_ptr(), H * S, S, S, float(scale), int(bool(causal)), _CODE[p.dtype],
+                       _stream()), "attn_softmax_bwd")
+        _count("attn_softmax_bwd")
+        if gemm(dp, k[b], out=dq[b]) is NotImplemented or gemm(dp.transpose(-1, -2), q[b], out=dk[b]) is NotImplemented:
+            return NotImplemented
+    if rotary_dim:
+        rotary_launch(dq, sin, cos, dq, rotary_dim, True)
+        rotary_launch(dk, sin, cos, dk, rotary_dim, True)
+    return dqkv
+
+
+# ---- fused cross-entropy -------------------------------------------------------------------------------------------------
+@native("ce_with_grad")
+def ce_with_grad_cuda(logits, labels, loss_grad, ignore_index, reduction):
+    if not _ok(logits) or not labels.is_cuda:
+        return NotImplemented
+    V = logits.shape[-1]
+    rows = logits.numel() // V
+    lab = labels.reshape(-1)
+    if lab.dtype != torch.int32:
+        lab = lab.to(torch.int32)
+    ii = -100 if ignore_index is None else int(ignore_index)
+    loss_row = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    dlogits = torch.empty_like(logits)
+    lg = loss_grad.float().reshape(())
+    if reduction == "mean":
+        count = (lab != ii).sum().clamp(min=1).float()
+        scale_t = (lg / count).reshape(1)
+    else:
+        count = None
+        scale_t = lg.reshape(1)
+    rc = _ce(logits.data_ptr(), lab.data_ptr(), loss_row.data_ptr(), dlogits.data_ptr(), rows, V, ii,
+             scale_t.data_ptr(), 1.0, _CODE[logits.dtype], _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "ce_fwd_bwd")
+    _count("ce_fwd_bwd")
+    if reduction == "mean":
+        loss = loss_row.sum() / count
+    elif reduction == "sum":
+        loss = loss_row.sum()
+    else:
+        loss = loss_row.reshape(labels.shape)
+    return loss.to(logits.dtype), dlogits
+
+
+# ---- registration of ops defined outside xl.ops ------------------------------------------------------------------------
+def _register_late():
+    from . import grad_reduce_square_add as _g, group_quantize_decompress as _q  # noqa: F401  (define the OpDefs)
+
+    OPS["grad_reduce_square_add"].native["cuda"] = grad_sumsq_cuda
+    OPS["group_quantize_decompress"].native["cuda"] = gq_decompress_cuda
+
+    from ..layers import linear_gq as _lgq  # noqa: F401
+
+    def linear_gq_cuda(x, packed, scale, zero, *b, dim):
+        w = gq_decompress_cuda(packed, scale, zero)
+        if w is NotImplemented or x.dtype not in (torch.bfloat16, torch.float16) or w.dtype != x.dtype:
+            return NotImplemented
+        wt = w if dim in (-1, 1) else w.t()
+        res = gemm(x.reshape(-1, x.shape[-1]), wt, bias=b[0] if b else None)
+        if res is NotImplemented:
+            return res
+        return res.view(*x.shape[:-1], wt.shape[-1])
+
+    OPS["linear_gq"].native["cuda"] = linear_gq_cuda
+
+
+_register_late()

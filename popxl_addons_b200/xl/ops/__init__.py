@@ -1317,5 +1317,30 @@ from .control import (CallSiteInfo, RepeatSiteInfo, call, call_with_info, repeat
                       conditional)
 from .io import (host_load, host_store, remote_load, remote_load_, remote_store, ipu_copy)  # noqa: E402
 from . import var_updates, collectives  # noqa: E402
-from .fused import (attention, attention_decode, rotary_pos_embed, linear_bias_act)  # noqa: E402
+from .fused import (attention, attention_decode, attention_qkv, rotary_pos_embed, linear_bias_act)  # noqa: E402
 from .fused import kv_cache_update_  # noqa: E402
+
+
+# ---- fused cross-entropy (loss + d loss / d logits in one op) --------------------------------------------------
+
+
+def _ce_with_grad_ref(logits, labels, loss_grad, ignore_index, reduction):
+    probs = torch.softmax(logits.float(), dim=-1).to(logits.dtype) if logits.device.type != "meta" else logits
+    if logits.device.type == "meta":
+        shape = () if reduction != "none" else labels.shape
+        return torch.empty(shape, dtype=logits.dtype, device="meta"), torch.empty_like(logits)
+    return _nll_softmax_grad_ref(probs, labels, loss_grad, ignore_index, reduction)
+
+
+OpDef("ce_with_grad", impl=_ce_with_grad_ref)
+
+
+def cross_entropy_with_grad(logits: Tensor, labels: Tensor, loss_grad=1.0, reduction: str = "mean",
+                            ignore_index: Optional[int] = None) -> Tuple[Tensor, Tensor]:
+    """Softmax cross-entropy of `logits (.., classes)` against integer `labels`, and its gradient with respect to
+    the logits multiplied by `loss_grad`, from one fused pass."""
+    if not isinstance(loss_grad, Tensor):
+        loss_grad = constant(loss_grad, _dt.float32)
+    loss, dlogits = emit("ce_with_grad", [logits, labels, loss_grad],
+                         {"ignore_index": ignore_index, "reduction": reduction})
+    return loss, dlogits

@@ -194,3 +194,77 @@ def linear_bias_act(x: Tensor, w: Tensor, b: Optional[Tensor] = None, act: str =
     """`act(x @ w + b)` as one GEMM with a fused epilogue."""
     ins = [x, w] + ([b] if b is not None else [])
     return emit1("linear_bias_act", ins, {"act": act})
+
+
+# ---- attention on a packed qkv matrix (the transformer hot path) ----------------------------------------------
+
+
+def _split_heads(qkv, seq_len, n_heads, head_dim):
+    T = qkv.shape[0]
+    B = T // seq_len
+    hd = n_heads * head_dim
+    parts = [qkv[:, i * hd:(i + 1) * hd].reshape(B, seq_len, n_heads, head_dim).permute(0, 2, 1, 3) for i in range(3)]
+    return parts, B
+
+
+def _attn_qkv_fwd_ref(qkv, sin, cos, seq_len, n_heads, head_dim, rotary_dim, causal, scale, inplace):
+    if qkv.device.type == "meta":
+        T = qkv.shape[0]
+        return (torch.empty((T, n_heads * head_dim), dtype=qkv.dtype, device="meta"), torch.empty_like(qkv),
+                torch.empty((T // seq_len, n_heads, seq_len), dtype=torch.float32, device="meta"))
+    (q, k, v), B = _split_heads(qkv, seq_len, n_heads, head_dim)
+    if rotary_dim:
+        q = _rotary_ref(q, sin, cos, rotary_dim, False)
+        k = _rotary_ref(k, sin, cos, rotary_dim, False)
+    o, lse = _attn_fwd_ref(q, k, v, causal, scale)
+    T = qkv.shape[0]
+    rot = torch.cat([t.permute(0, 2, 1, 3).reshape(T, n_heads * head_dim) for t in (q, k, v)], dim=-1).to(qkv.dtype)
+    return o.permute(0, 2, 1, 3).reshape(T, n_heads * head_dim), rot, lse
+
+
+def _attn_qkv_bwd_ref(qkv_rot, lse, dout, sin, cos, seq_len, n_heads, head_dim, rotary_dim, causal, scale):
+    if qkv_rot.device.type == "meta":
+        return torch.empty_like(qkv_rot)
+    (q, k, v), B = _split_heads(qkv_rot, seq_len, n_heads, head_dim)
+    T = qkv_rot.shape[0]
+    do = dout.reshape(B, seq_len, n_heads, head_dim).permute(0, 2, 1, 3)
+    o, _ = _attn_fwd_ref(q, k, v, causal, scale)
+    dq, dk, dv = _attn_bwd_ref(q, k, v, o, lse, do, causal, scale)
+    if rotary_dim:
+        dq = _rotary_ref(dq, sin, cos, rotary_dim, True)
+        dk = _rotary_ref(dk, sin, cos, rotary_dim, True)
+    return torch.cat([t.permute(0, 2, 1, 3).reshape(T, n_heads * head_dim) for t in (dq, dk, dv)],
+                     dim=-1).to(qkv_rot.dtype)
+
+
+def _vjp_attn_qkv(ctx, op, gs):
+    qkv, sin, cos = op.inputs
+    out, rot, lse = op.outputs
+    a = {k: v for k, v in op.attrs.items() if k != "inplace"}
+    return [emit1("attention_qkv_grad", [ctx.fwd(rot), ctx.fwd(lse), gs[0], ctx.fwd(sin), ctx.fwd(cos)], a), None, None]
+
+
+def _attn_qkv_flops(op):
+    a = op.attrs
+    T = op.inputs[0].shape[0]
+    f = 4 * T * a["seq_len"] * a["n_heads"] * a["head_dim"]
+    return f // 2 if a["causal"] else f
+
+
+OpDef("attention_qkv", impl=_attn_qkv_fwd_ref, vjp=_vjp_attn_qkv, flops=_attn_qkv_flops)
+OpDef("attention_qkv_grad", impl=_attn_qkv_bwd_ref, flops=lambda op: int(2.5 * _attn_qkv_flops(op)))
+
+
+def attention_qkv(qkv: Tensor, sin: Tensor, cos: Tensor, seq_len: int, n_heads: int, head_dim: int,
+                  rotary_dim: int = 0, causal: bool = True, scale: Optional[float] = None,
+                  inplace: bool = False) -> Tensor:
+    """Self-attention on a packed projection `qkv (batch*seq, 3*heads*head_dim)` = `[q | k | v]`: rotary embedding of
+    q and k (first `rotary_dim` features of every head, interleaved pairs; 0 disables), causal softmax attention,
+    output `(batch*seq, heads*head_dim)` ready for the output projection. Heads are addressed as strided views of the
+    packed matrix, so no transposes are materialised. `inplace=True` lets the kernel rotate q and k inside `qkv`."""
+    if qkv.rank != 2 or qkv.shape[1] != 3 * n_heads * head_dim or qkv.shape[0] % seq_len:
+        raise ValueError(f"qkv must be (batch*seq, 3*heads*head_dim); got {qkv.shape}")
+    scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+    return emit("attention_qkv", [qkv, sin, cos],
+                dict(seq_len=int(seq_len), n_heads=int(n_heads), head_dim=int(head_dim), rotary_dim=int(rotary_dim),
+                     causal=bool(causal), scale=scale, inplace=bool(inplace)))[0]

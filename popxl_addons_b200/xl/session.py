@@ -387,4 +387,9 @@ class Session:
         env: Dict[Tensor, List[torch.Tensor]] = {}
         with torch.no_grad():
             self._exec_ops(main, env)
-        return self._collect_outputs()
+        out = self._collect_outputs()
+        if self.use_native:
+            from ...ops import native as _native
+
+            _native.check_gemm_errors()
+        return out

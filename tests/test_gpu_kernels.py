@@ -1,0 +1,272 @@
+"""Every CUDA kernel against the plain-PyTorch fp32 reference of the same op (the op's own reference implementation,
+evaluated in fp32 on the same inputs)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def nat():
+    from popxl_addons_b200.ops import native
+
+    return native
+
+
+def _tol(dtype):
+    return dict(rtol=2e-2, atol=2e-2) if dtype != torch.float32 else dict(rtol=1e-4, atol=1e-5)
+
+
+def _ref(name):
+    from popxl_addons_b200.xl.opdef import OPS
+    import popxl_addons_b200.xl.ops  # noqa: F401
+
+    return OPS[name].impl
+
+
+DTYPES = [torch.float32, torch.bfloat16, torch.float16]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("approx", ["none", "tanh"])
+def test_gelu(nat, dtype, approx):
+    torch.manual_seed(0)
+    x = torch.randn(1000, 517, device="cuda", dtype=dtype)
+    g = torch.randn_like(x)
+    y = nat.gelu_cuda(x, approximate=approx)
+    dx = nat.gelu_grad_cuda(x, g, approximate=approx)
+    torch.testing.assert_close(y.float(), _ref("gelu")(x.float(), approx), **_tol(dtype))
+    torch.testing.assert_close(dx.float(), _ref("gelu_grad")(x.float(), g.float(), approx), **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu_and_silu(nat, dtype):
+    torch.manual_seed(1)
+    a = torch.randn(64, 1024, device="cuda", dtype=dtype)
+    b = torch.randn_like(a)
+    g = torch.randn_like(a)
+    torch.testing.assert_close(nat.swiglu_cuda(a, b).float(), _ref("swiglu")(a.float(), b.float()), **_tol(dtype))
+    da, db = nat.swiglu_grad_cuda(a, b, g)
+    ra, rb = _ref("swiglu_grad")(a.float(), b.float(), g.float())
+    torch.testing.assert_close(da.float(), ra, **_tol(dtype))
+    torch.testing.assert_close(db.float(), rb, **_tol(dtype))
+    torch.testing.assert_close(nat.swish_cuda(a).float(), _ref("swish")(a.float()), **_tol(dtype))
+    torch.testing.assert_close(nat.swish_grad_cuda(a, g).float(), _ref("swish_grad")(a.float(), g.float()), **_tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("cols", [768, 4096])
+def test_layer_norm_fwd_bwd(nat, dtype, cols):
+    torch.manual_seed(2)
+    x = torch.randn(300, cols, device="cuda", dtype=dtype) * 2 + 0.5
+    w = torch.randn(cols, device="cuda", dtype=dtype)
+    b = torch.randn(cols, device="cuda", dtype=dtype)
+    g = torch.randn_like(x)
+    y, mean, rstd = nat.layer_norm_cuda(x, w, b, 1e-5)
+    ry, rmean, rrstd = _ref("layer_norm")(x.float(), w.float(), b.float(), 1e-5)
+    torch.testing.assert_close(y.float(), ry, **_tol(dtype))
+    torch.testing.assert_close(mean, rmean, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(rstd, rrstd, rtol=1e-4, atol=1e-4)
+    dx, dw, db = nat.layer_norm_grad_cuda(x, w, mean, rstd, g)
+    rdx, rdw, rdb = _ref("layer_norm_grad")(x.float(), w.float(), rmean, rrstd, g.float())
+    torch.testing.assert_close(dx.float(), rdx, **_tol(dtype))
+    big = dict(rtol=3e-2, atol=0.3) if dtype != torch.float32 else dict(rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(dw.float(), rdw, **big)
+    torch.testing.assert_close(db.float(), rdb, **big)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rms_norm_fwd_bwd(nat, dtype):
+    torch.manual_seed(3)
+    x = torch.randn(257, 4096, device="cuda", dtype=dtype)
+    w = torch.randn(4096, device="cuda", dtype=dtype)
+    g = torch.randn_like(x)
+    y, rstd = nat.rms_norm_cuda(x, w, 1e-5)
+    ry, rr = _ref("rms_norm")(x.float(), w.float(), 1e-5)
+    torch.testing.assert_close(y.float(), ry, **_tol(dtype))
+    dx, dw = nat.rms_norm_grad_cuda(x, w, rstd, g)
+    rdx, rdw = _ref("rms_norm_grad")(x.float(), w.float(), rr, g.float())
+    torch.testing.assert_close(dx.float(), rdx, **_tol(dtype))
+    big = dict(rtol=3e-2, atol=0.3) if dtype != torch.float32 else dict(rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(dw.float(), rdw, **big)
+
+
+@pytest.mark.parametrize("wdtype,mdtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32),
+                                           (torch.bfloat16, torch.float16), (torch.float16, torch.bfloat16)])
+def test_adam_matches_torch_adamw(nat, wdtype, mdtype):
+    torch.manual_seed(4)
+    n = 100003
+    w0 = torch.randn(n, device="cuda")
+    master = w0.clone() if wdtype != torch.float32 else None
+    w = w0.to(wdtype)
+    m = torch.zeros(n, device="cuda", dtype=mdtype)
+    v = torch.zeros(n, device="cuda")
+    step = torch.zeros((), device="cuda")
+    ref_w = w0.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([ref_w], lr=1e-2, betas=(0.9, 0.95), eps=1e-6, weight_decay=0.1)
+    for i in range(3):
+        g = torch.randn(n, device="cuda")
+        args = [w, g.to(wdtype) if i % 2 else g, m, v, step] + ([master] if master is not None else [])
+        out = nat.adam_cuda(*args, has_step=True, has_master=master is not None, bias_correction=True, lr=1e-2,
+                            beta1=0.9, beta2=0.95, epsilon=1e-6, weight_decay=0.1, grad_scale=1.0, _tensor_scalars=())
+        assert out is w
+        ref_w.grad = (g.to(wdtype).float() if i % 2 else g)
+        opt.step()
+    assert float(step) == 3.0
+    got = master if master is not None else w
+    tol = dict(rtol=1e-4, atol=1e-5) if mdtype == torch.float32 else dict(rtol=2e-2, atol=2e-3)
+    torch.testing.assert_close(got.float(), ref_w.detach(), **tol)
+
+
+def test_sgd_and_accumulate_mean_and_sumsq(nat):
+    torch.manual_seed(5)
+    n = 4099
+    w = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    buf = torch.zeros(n, device="cuda")
+    ref = _ref("sgd_fused_")(w.clone(), g, buf.clone(), has_momentum=True, lr=0.1, momentum=0.9, weight_decay=0.01,
+                             grad_scale=0.5, _tensor_scalars=())
+    nat.sgd_cuda(w, g, buf, has_momentum=True, lr=0.1, momentum=0.9, weight_decay=0.01, grad_scale=0.5,
+                 _tensor_scalars=())
+    torch.testing.assert_close(w, ref, rtol=1e-5, atol=1e-6)
+    acc = torch.zeros(n, device="cuda")
+    step = torch.zeros((), device="cuda")
+    xs = [torch.randn(n, device="cuda", dtype=torch.bfloat16) for _ in range(4)]
+    for x in xs:
+        nat.accumulate_mean_cuda(acc, x, step, step=None, _tensor_scalars=("step",))
+        step += 1
+    torch.testing.assert_close(acc, torch.stack([x.float() for x in xs]).mean(0), rtol=1e-5, atol=1e-6)
+    t = torch.randn(1 << 20, device="cuda", dtype=torch.bfloat16)
+    s = nat.grad_sumsq_cuda(t, torch.tensor(0.25, device="cuda"))
+    torch.testing.assert_close(s, (t.float() ** 2).sum() * 0.25, rtol=1e-4, atol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_rotary(nat, dtype):
+    from popxl_addons_b200.ops.rotary_pos_embed import trig_tables
+
+    torch.manual_seed(6)
+    x = torch.randn(2, 4, 128, 256, device="cuda", dtype=dtype)
+    sin, cos = trig_tables(128, 64)
+    sin = torch.tensor(sin[None], device="cuda", dtype=dtype)
+    cos = torch.tensor(cos[None], device="cuda", dtype=dtype)
+    for inverse in (False, True):
+        y = nat.rotary_cuda(x, sin, cos, 64, inverse)
+        ref = _ref("rotary_pos_embed")(x.float(), sin.float(), cos.float(), 64, inverse)
+        torch.testing.assert_close(y.float(), ref, **_tol(dtype))
+
+
+def test_group_quantize_decompress(nat):
+    from popxl_addons_b200.ops.group_quantize_decompress import (group_quantize_compress_numpy,
+                                                                group_quantize_decompress_numpy)
+
+    rng = np.random.RandomState(7)
+    w = rng.randn(512, 1024).astype(np.float16)
+    packed, scale, bias = group_quantize_compress_numpy(w, 64, -1)
+    ref = group_quantize_decompress_numpy(packed, scale, bias)
+    from popxl_addons_b200.xl.dtypes import to_torch
+
+    out = nat.gq_decompress_cuda(to_torch(packed).cuda(), torch.tensor(scale).cuda(), torch.tensor(bias).cuda())
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref.astype(np.float32), atol=1e-2)
+    assert np.abs(ref.astype(np.float32) - w.astype(np.float32)).max() < 0.5
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_cross_entropy_fused(nat, dtype):
+    torch.manual_seed(8)
+    logits = torch.randn(64, 50400, device="cuda", dtype=dtype) * 3
+    labels = torch.randint(0, 50400, (64,), device="cuda", dtype=torch.int32)
+    labels[5] = -100
+    loss, dl = nat.ce_with_grad_cuda(logits, labels, torch.tensor(2.0, device="cuda"), -100, "mean")
+    ref_logits = logits.float().clone().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(ref_logits, labels.long(), ignore_index=-100)
+    (ref * 2.0).backward()
+    torch.testing.assert_close(loss.float(), ref.detach(), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(dl.float(), ref_logits.grad, rtol=2e-2, atol=1e-4)
+
+
+# ---- tcgen05 GEMM -------------------------------------------------------------------------------------------------------
+
+
+def _gemm_check(nat, a, b, **kw):
+    out = nat.gemm(a, b, **kw)
+    assert out is not NotImplemented
+    torch.cuda.synchronize()
+    nat.check_gemm_errors()
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 128), (2048, 4096, 1024), (200, 328, 136),
+                                   (16, 4096, 4096), (1000, 50400, 512)])
+def test_gemm_k_major_a_mn_major_b(nat, dtype, M, N, K):
+    """Forward layout: x (M,K) row-major @ w (K,N) row-major."""
+    torch.manual_seed(10)
+    a = torch.randn(M, K, device="cuda", dtype=dtype)
+    b = torch.randn(K, N, device="cuda", dtype=dtype)
+    out = _gemm_check(nat, a, b)
+    ref = a.float() @ b.float()
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 256), (2048, 1024, 4096), (136, 200, 328)])
+def test_gemm_all_operand_layouts(nat, M, N, K):
+    torch.manual_seed(11)
+    dtype = torch.bfloat16
+    a_km = torch.randn(M, K, device="cuda", dtype=dtype)          # K-major A
+    a_mn = torch.randn(K, M, device="cuda", dtype=dtype).t()       # MN-major A (view)
+    b_mn = torch.randn(K, N, device="cuda", dtype=dtype)          # MN-major B
+    b_km = torch.randn(N, K, device="cuda", dtype=dtype).t()       # K-major B (view)
+    for a in (a_km, a_mn):
+        for b in (b_mn, b_km):
+            out = _gemm_check(nat, a, b)
+            ref = a.float() @ b.float()
+            torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+
+
+def test_gemm_batched_and_epilogues(nat):
+    torch.manual_seed(12)
+    dtype = torch.bfloat16
+    q = torch.randn(6, 256, 128, device="cuda", dtype=dtype)
+    k = torch.randn(6, 384, 128, device="cuda", dtype=dtype)
+    s = _gemm_check(nat, q, k.transpose(-1, -2))
+    torch.testing.assert_close(s.float(), q.float() @ k.float().transpose(-1, -2), rtol=2e-2, atol=0.3)
+    a = torch.randn(512, 256, device="cuda", dtype=dtype)
+    b = torch.randn(256, 384, device="cuda", dtype=dtype)
+    bias = torch.randn(384, device="cuda", dtype=dtype)
+    out = _gemm_check(nat, a, b, bias=bias, act=1)
+    ref = torch.nn.functional.gelu(a.float() @ b.float() + bias.float())
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=0.3)
+    # fp32 output, accumulate and running mean
+    acc = torch.ones(512, 384, device="cuda")
+    _gemm_check(nat, a, b, out=acc, accumulate=1)
+    torch.testing.assert_close(acc, 1.0 + a.float() @ b.float(), rtol=1e-3, atol=1e-2)
+    mean = torch.zeros(512, 384, device="cuda")
+    step = torch.zeros((), device="cuda")
+    parts = []
+    for i in range(3):
+        ai = torch.randn(512, 256, device="cuda", dtype=dtype)
+        parts.append(ai.float() @ b.float())
+        _gemm_check(nat, ai, b, out=mean, accumulate=2, step=step)
+        step += 1
+    torch.testing.assert_close(mean, torch.stack(parts).mean(0), rtol=1e-3, atol=1e-2)
+
+
+def test_attention_forward_backward(nat):
+    torch.manual_seed(13)
+    B, H, S, D = 2, 4, 512, 128
+    q, k, v = (torch.randn(B, H, S, D, device="cuda", dtype=torch.bfloat16) * 0.5 for _ in range(3))
+    do = torch.randn(B, H, S, D, device="cuda", dtype=torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    o, lse = nat.attention_cuda(q, k, v, True, scale)
+    ro, rlse = _ref("attention")(q.float(), k.float(), v.float(), True, scale)
+    torch.testing.assert_close(o.float(), ro, rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(lse, rlse, rtol=1e-2, atol=2e-2)
+    dq, dk, dv = nat.attention_grad_cuda(q, k, v, o, lse, do, True, scale)
+    rdq, rdk, rdv = _ref("attention_grad")(q.float(), k.float(), v.float(), ro, rlse, do.float(), True, scale)
+    for got, ref in ((dq, rdq), (dk, rdk), (dv, rdv)):
+        torch.testing.assert_close(got.float(), ref, rtol=5e-2, atol=5e-2)
+    nat.check_gemm_errors()
