@@ -17,7 +17,7 @@ from .. import xl
 from ..xl import ops
 from ..xl.opdef import OpDef, emit
 
-__all__ = ["cross_entropy_sharded_loss", "cross_entropy_sharded_wr_loss"]
+__all__ = ["cross_entropy_sharded_loss", "cross_entropy_sharded_wr_loss", "cross_entropy_sharded_with_grad"]
 
 
 def _local_stats(logits: torch.Tensor):
@@ -102,6 +102,35 @@ def cross_entropy_sharded_loss(logits: xl.Tensor, indices: xl.Tensor, ignore_ind
     loss, _ = emit("ce_sharded", [logits, indices], {"group": group, "root_only": False},
                    ["cross_entropy_sharded_out", "cross_entropy_sharded_soft_max_out"])
     return _reduce_loss(loss, indices, ignore_index, reduction)
+
+
+def cross_entropy_sharded_with_grad(logits: xl.Tensor, indices: xl.Tensor, loss_scaling=1.0, ignore_index=None,
+                                    replica_grouping: Optional[xl.ReplicaGrouping] = None, reduction: str = "mean"):
+    """Vocabulary-sharded counterpart of `cross_entropy_with_grad`: returns `(loss, d(loss*loss_scaling)/dlogits)`
+    where the gradient is this replica's slice. No separate backward graph is needed for the loss."""
+    group = replica_grouping if replica_grouping is not None else xl.gcg().ir.replica_grouping()
+    rows, _nls = emit("ce_sharded", [logits, indices], {"group": group, "root_only": False},
+                      ["cross_entropy_sharded_out", "cross_entropy_sharded_soft_max_out"])
+    n = logits.shape[0]
+    scale = loss_scaling if isinstance(loss_scaling, xl.Tensor) else xl.constant(float(loss_scaling), xl.float32)
+    if ignore_index is not None:
+        ii = ignore_index if isinstance(ignore_index, xl.Tensor) else xl.constant(ignore_index, indices.dtype)
+        mask = ops.cast(ops.logical_not(ops.equal(indices, ii)), xl.float32)
+    else:
+        mask = None
+    if reduction == "mean":
+        denom = ops.sum(mask) if mask is not None else xl.constant(float(n), xl.float32)
+        per_row = ops.div(scale, denom)
+    elif reduction in ("sum", "none"):
+        per_row = scale
+    else:
+        raise ValueError(f"`reduction` should be one of `mean`, `sum` and `none`. Passed: {reduction}")
+    dl = ops.expand(ops.reshape(per_row, (1,)), (n,)) if per_row.shape == () else per_row
+    if mask is not None:
+        dl = dl * mask
+    dl = ops.cast(dl, logits.dtype)
+    (dlogits,) = emit("ce_sharded_grad", [_nls, indices, dl])
+    return _reduce_loss(rows, indices, ignore_index, reduction), dlogits
 
 
 # ---- variant: all shards are tensors of one replica -----------------------------------------------------------

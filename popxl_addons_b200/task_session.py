@@ -203,9 +203,9 @@ class TaskSession(xl.Session):
         self.write_variables_data({named[k]: np.asarray(v) for k, v in loaded.items() if k in named})
 
     # -- running ----------------------------------------------------------------------------------------------
-    def run(self, inputs: Optional[Mapping] = None, downcast_inputs: bool = True):
+    def run(self, inputs: Optional[Mapping] = None, downcast_inputs: bool = True, fetch: bool = True):
         self.session_state["steps"] += 1
-        return super().run(inputs or {}, downcast_inputs)
+        return super().run(inputs or {}, downcast_inputs, fetch)
 
 
 def initialise_memmap_dir_from_checkpoint(checkpoint_dir: str, memmap_dir: str):

@@ -35,10 +35,13 @@ def autodiff_with_accumulation(graph: GraphWithNamedArgs, tensors_to_accumulate_
                                grads_required: Optional[Iterable[xl.Tensor]] = None,
                                grads_provided: Optional[Iterable[xl.Tensor]] = None,
                                called_graphs_grad_info: Optional[Mapping[xl.Graph, GradGraphInfo]] = None,
-                               replica_groupings=None) -> Tuple[NamedVariableFactories, GraphWithNamedArgs]:
+                               replica_groupings=None,
+                               accum_dtype: Optional[xl.dtype] = None
+                               ) -> Tuple[NamedVariableFactories, GraphWithNamedArgs]:
     """Gradient graph that, instead of returning the gradients of `tensors_to_accumulate_grads`, folds them into
     by-reference accumulators `accum.<name>` as a *running mean* over calls, counted by the scalar
     `mean_accum_counter` (zero it to start a new mean). Other `grads_required` remain graph outputs.
+    Accumulators have the dtype of their tensor unless `accum_dtype` is given (e.g. fp32 sums for bf16 weights).
 
     Returns the factories for the accumulators/counter and the gradient graph (its `args` name them)."""
     accumulate = list(tensors_to_accumulate_grads)
@@ -62,9 +65,10 @@ def autodiff_with_accumulation(graph: GraphWithNamedArgs, tensors_to_accumulate_
                 continue
             key = name_of.get(t, t.name.replace("/", "_").replace(".", "_"))
             grad_t = g._outputs[idx]
-            np_dtype = t.dtype.as_numpy() if t.dtype._numpy is not None else np.float32
+            a_dt = accum_dtype or t.dtype
+            np_dtype = a_dt.as_numpy() if a_dt._numpy is not None else np.float32
             shape = tuple(t.shape)
-            accum, accum_f = add_variable_input(f"accum.{key}", lambda s=shape, d=np_dtype: np.zeros(s, d), t.dtype,
+            accum, accum_f = add_variable_input(f"accum.{key}", lambda s=shape, d=np_dtype: np.zeros(s, d), a_dt,
                                                 by_ref=True, replica_grouping=rgs.get(key))
             if t.meta_shape:
                 accum.meta_shape = tuple(t.meta_shape)

@@ -74,7 +74,7 @@ class VariableFactory:
         invoked once immediately (to fail early and to learn the shape)."""
         if callable(data_iter):
             first = data_iter()
-            if not isinstance(first, (np.ndarray, np.generic)) and not hasattr(first, "shape"):
+            if not isinstance(first, (np.ndarray, np.generic, xl.LazyInit)) and not hasattr(first, "shape"):
                 raise ValueError("`data_iter` must return an array. "
                                  f"Got {type(first)} from {getattr(data_iter, '__name__', data_iter)}")
             source = itertools.chain([first], _repeat_call(data_iter))
@@ -88,7 +88,9 @@ class VariableFactory:
         self.by_ref = by_ref
         ir = xl.gcg().ir
         self.replica_grouping = replica_grouping or ir.replica_grouping()
-        example = np.asarray(self.data_iter.peek())
+        example = self.data_iter.peek()
+        if not isinstance(example, xl.LazyInit):
+            example = np.asarray(example)
         self.dtype = xl.dtype.as_dtype(dtype) if dtype is not None else xl.dtype.as_dtype(
             np.float32 if example.dtype == np.float64 else example.dtype)
         full_shape = tuple(example.shape)
@@ -115,9 +117,12 @@ class VariableFactory:
     # -- variable side ------------------------------------------------------------------------------------------
     def next_data(self) -> np.ndarray:
         n = self.replica_grouping.num_groups
+        first = next(self.data_iter)
+        if isinstance(first, xl.LazyInit):
+            return first.with_groups(n) if n > 1 else first
         if n > 1:
-            return np.stack([np.asarray(next(self.data_iter)) for _ in range(n)])
-        return np.asarray(next(self.data_iter))
+            return np.stack([np.asarray(first)] + [np.asarray(next(self.data_iter)) for _ in range(n - 1)])
+        return np.asarray(first)
 
     def next_memmap(self, path: str, empty: bool = False, read_only_if_exists: bool = False) -> np.memmap:
         """Backing `.npy` file for the variable: opened if it exists, else created (by process 0) and filled."""

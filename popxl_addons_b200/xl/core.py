@@ -781,6 +781,48 @@ class Ir:
 
 
 # ---------------------------------------------------------------------------------------------------------------
+# lazily materialised initial values
+# ---------------------------------------------------------------------------------------------------------------
+
+
+class LazyInit:
+    """Initial value of a variable described by a recipe instead of a host array. It is materialised directly on the
+    session's device (per replica group, seeded by `seed + group index`), so a multi-billion-parameter model neither
+    needs host memory for its initial weights nor a host-to-device copy of them.
+    `kind`: "normal" (mean 0, `std`), "zeros", "ones", or "copy" (value of variable `source`, cast)."""
+
+    def __init__(self, shape, dtype=np.float32, kind: str = "normal", std: float = 0.02, seed: int = 0, source=None,
+                 groups: int = 0):
+        self.shape = tuple(int(s) for s in shape)
+        self.dtype = np.dtype(dtype) if not isinstance(dtype, _dt.dtype) else dtype
+        self.kind, self.std, self.seed, self.source, self.groups = kind, std, seed, source, groups
+        self.ndim = len(self.shape)
+
+    def with_groups(self, n: int) -> "LazyInit":
+        """Same recipe for `n` replica groups (host shape gains a leading axis of `n`)."""
+        out = LazyInit((n, *self.shape), self.dtype, self.kind, self.std, self.seed, self.source, groups=n)
+        return out
+
+    def astype(self, dtype):
+        return LazyInit(self.shape, dtype, self.kind, self.std, self.seed, self.source, self.groups)
+
+    def materialize(self, device, torch_dtype, group: int = 0) -> torch.Tensor:
+        shape = self.shape[1:] if self.groups else self.shape
+        if self.kind == "zeros":
+            return torch.zeros(shape, dtype=torch_dtype, device=device)
+        if self.kind == "ones":
+            return torch.ones(shape, dtype=torch_dtype, device=device)
+        if self.kind == "normal":
+            gen = torch.Generator(device=device)
+            gen.manual_seed((self.seed + 7919 * group) & 0x7FFFFFFF)
+            # always drawn in fp32 so that a 16-bit weight and its fp32 master copy (same recipe) agree exactly
+            t = torch.empty(shape, dtype=torch.float32, device=device)
+            t.normal_(0.0, self.std, generator=gen)
+            return t.to(torch_dtype)
+        raise ValueError(f"LazyInit kind {self.kind!r} cannot be materialised on its own")
+
+
+# ---------------------------------------------------------------------------------------------------------------
 # tensor factories
 # ---------------------------------------------------------------------------------------------------------------
 
@@ -804,6 +846,8 @@ def graph_output(t: Tensor) -> None:
 
 
 def _host_array(data, dt: Optional[dtype]):
+    if isinstance(data, LazyInit):
+        return data
     if isinstance(data, torch.Tensor):
         t = data.detach().cpu()
     else:
@@ -828,7 +872,7 @@ def variable(data, dtype: Optional[dtype] = None, name: Optional[str] = None, do
         raise ValueError("Variables can only be created in the main graph")
     dt = _dt.dtype.as_dtype(dtype) if dtype is not None else None
     host = data if isinstance(data, np.memmap) else _host_array(data, dt)
-    if isinstance(host, np.memmap):
+    if isinstance(host, (np.memmap, LazyInit)):
         dt = dt or _dt.dtype.as_dtype(host.dtype)
         full_shape = tuple(host.shape)
     else:
@@ -871,7 +915,7 @@ def replica_sharded_variable(data, dtype: Optional[dtype] = None, name: Optional
     n = shard_grouping.group_size
     if nelms % n != 0:
         raise ValueError(f"Cannot shard {nelms} elements over {n} replicas")
-    v = Variable(g, (nelms // n,), _dt.dtype.as_dtype(host.dtype), name or "variable", meta_shape=full_shape,
+    v = Variable(g, (nelms // n,), dt or _dt.dtype.as_dtype(host.dtype), name or "variable", meta_shape=full_shape,
                  replica_grouping=rg, shard_group=shard_grouping)
     g.ir.initial_values[v] = host
     return v, v

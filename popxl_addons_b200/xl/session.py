@@ -18,7 +18,7 @@ import torch
 from . import dtypes as _dt
 from .buffers import DeviceToHostStream, HostToDeviceStream, RemoteBuffer
 from .comm import DistComm, SimComm
-from .core import Constant, Graph, Ir, Tensor, Variable
+from .core import Constant, Graph, Ir, LazyInit, Tensor, Variable
 
 
 def _resolve_device(device_desc: str) -> torch.device:
@@ -65,6 +65,8 @@ class Session:
         self._cursor: Dict[HostToDeviceStream, int] = {}
         self._outputs: Dict[DeviceToHostStream, List[List[torch.Tensor]]] = {}
         self.is_attached = False
+        self.h2d_bytes = 0  # host->device / device->host traffic of `run` so far (bytes of the tensors copied)
+        self.d2h_bytes = 0
         self.profile: Optional[Dict[str, List[float]]] = None
         self._init_state()
 
@@ -93,7 +95,17 @@ class Session:
         """Host array (full `shape_on_host`) -> the value replica `replica` holds."""
         rg = var.replica_grouping
         data = host
-        if rg.num_groups > 1:
+        if isinstance(data, LazyInit):
+            if data.kind == "copy":
+                src = data.source
+                local = replica - self.replica_offset
+                full = self._vars[src][local]
+                if src.shard_group is not None:
+                    raise ValueError("LazyInit copy of a sharded variable is not supported")
+                data = full.detach()
+            else:
+                data = data.materialize(self.device, var.dtype.as_torch(), rg.group_index(replica))
+        elif rg.num_groups > 1:
             data = data[rg.group_index(replica)]
         if isinstance(data, np.ndarray):
             data = _dt.to_torch(np.asarray(data))
@@ -121,7 +133,13 @@ class Session:
     def _init_state(self):
         for rb in self.ir.remote_buffers:
             self._alloc_buffer(rb)
+        deferred = []
         for var, host in self.ir.initial_values.items():
+            if isinstance(host, LazyInit) and host.kind == "copy":
+                deferred.append((var, host))  # copies are made once their source exists
+            else:
+                self._write_var(var, host)
+        for var, host in deferred:
             self._write_var(var, host)
 
     def _read_var_local(self, var: Variable) -> List[torch.Tensor]:
@@ -199,6 +217,7 @@ class Session:
             if not isinstance(stream, HostToDeviceStream):
                 raise TypeError(f"{stream} is not a host-to-device stream")
             host = arr if isinstance(arr, torch.Tensor) else _dt.to_torch(np.asarray(arr))
+            self.h2d_bytes += host.numel() * host.element_size() if host.device.type == "cpu" else 0
             if host.dtype != stream.dtype.as_torch():
                 host = host.to(stream.dtype.as_torch())
             n_local = self.num_local
@@ -215,12 +234,12 @@ class Session:
                 raise ValueError(
                     f"Input for stream {stream.name} has shape {tuple(host.shape)}; expected "
                     f"(num_host_transfers={T}, replication_factor={R}, *{stream.shape}) with unit axes optional")
-            if self.device.type == "cuda":
+            if self.device.type == "cuda" and host.device.type == "cpu":
                 if not host.is_pinned():
                     host = host.contiguous().pin_memory()
                 dev = host.to(self.device, non_blocking=True)
             else:
-                dev = host
+                dev = host  # already resident on the session's device
             self._inputs[stream] = dev
             self._cursor[stream] = 0
 
@@ -238,11 +257,15 @@ class Session:
     def host_store(self, stream: DeviceToHostStream, vals: List[torch.Tensor]):
         self._outputs.setdefault(stream, []).append([v.detach().clone() for v in vals])
 
-    def _collect_outputs(self) -> Dict[DeviceToHostStream, np.ndarray]:
+    def _collect_outputs(self, fetch: bool = True) -> Dict[DeviceToHostStream, np.ndarray]:
         T = int(self.ir.num_host_transfers)
         res = {}
         for stream, items in self._outputs.items():
             stacked = torch.stack([torch.stack(per_replica) for per_replica in items])  # (t, R_local, *shape)
+            if not fetch:
+                res[stream] = stacked
+                continue
+            self.d2h_bytes += stacked.numel() * stacked.element_size() if stacked.device.type != "cpu" else 0
             arr = _dt.to_numpy(stacked)
             if arr.shape[1] == 1:
                 arr = arr[:, 0]
@@ -377,18 +400,20 @@ class Session:
             env[t] = v
 
     def run(self, inputs: Optional[Mapping[HostToDeviceStream, Any]] = None,
-            downcast_inputs: bool = True) -> Dict[DeviceToHostStream, np.ndarray]:
+            downcast_inputs: bool = True, fetch: bool = True) -> Dict[DeviceToHostStream, np.ndarray]:
         """Execute the main graph once. `inputs[stream]` has shape
         `(num_host_transfers, replication_factor, *stream.shape)` (unit axes may be omitted; under one process per
-        GPU the replica axis may hold only this rank's slice)."""
+        GPU the replica axis may hold only this rank's slice). Host inputs are staged through pinned memory; tensors
+        already on the session's device are used as they are. With `fetch=False` the outputs stay on the device
+        (stacked torch tensors) and the call does not synchronise."""
         self._outputs = {}
         self._stage_inputs(inputs or {})
         main = self.ir.main_graph
         env: Dict[Tensor, List[torch.Tensor]] = {}
         with torch.no_grad():
             self._exec_ops(main, env)
-        out = self._collect_outputs()
-        if self.use_native:
+        out = self._collect_outputs(fetch)
+        if self.use_native and fetch:
             from ...ops import native as _native
 
             _native.check_gemm_errors()
