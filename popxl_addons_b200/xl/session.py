@@ -55,7 +55,7 @@ class Session:
             use_native = os.environ.get("XL_NATIVE", "1") != "0"
         self.use_native = use_native and self.device.type == "cuda"
         if self.use_native:
-            from ...ops import native as _native  # noqa: F401  (registers the CUDA kernels; raises if not built)
+            from ..ops import native as _native  # noqa: F401  (registers the CUDA kernels; raises if not built)
 
         self._vars: Dict[Variable, List[torch.Tensor]] = {}
         self._buffers: Dict[RemoteBuffer, List[torch.Tensor]] = {}
@@ -308,7 +308,7 @@ class Session:
         op runs its reference composition over `self.comm`)."""
         if not self.use_native or not self.distributed:
             return None
-        from ...parallel import fused
+        from ..parallel import fused
 
         return fused.lookup(name, self)
 
@@ -414,7 +414,7 @@ class Session:
             self._exec_ops(main, env)
         out = self._collect_outputs(fetch)
         if self.use_native and fetch:
-            from ...ops import native as _native
+            from ..ops import native as _native
 
             _native.check_gemm_errors()
         return out
