@@ -8,19 +8,34 @@
 // ------------------------------------------------------------------------------------------------------------------
 // generic 1-/2-/3-operand elementwise driver
 // ------------------------------------------------------------------------------------------------------------------
+constexpr int EW_UNROLL = 4;  // 16-byte vectors per thread and iteration: keeps ~64 B per thread in flight
+
 template <typename T, typename F>
 __global__ void __launch_bounds__(256) ew_unary_kernel(const T* __restrict__ x, T* __restrict__ y, long long n, F f) {
   constexpr int N = XlVec<T>::N;
   const long long nvec = n / N;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (; i + (EW_UNROLL - 1) * stride < nvec; i += EW_UNROLL * stride) {
+    float a[EW_UNROLL][N];
+#pragma unroll
+    for (int u = 0; u < EW_UNROLL; ++u) xl_load16(x + (i + u * stride) * N, a[u]);
+#pragma unroll
+    for (int u = 0; u < EW_UNROLL; ++u) {
+#pragma unroll
+      for (int k = 0; k < N; ++k) a[u][k] = f(a[u][k]);
+      xl_store16(y + (i + u * stride) * N, a[u]);
+    }
+  }
+  for (; i < nvec; i += stride) {
     float a[N];
     xl_load16(x + i * N, a);
 #pragma unroll
     for (int k = 0; k < N; ++k) a[k] = f(a[k]);
     xl_store16(y + i * N, a);
   }
-  for (long long i = nvec * N + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-    y[i] = xl_from_float<T>(f(xl_to_float(x[i])));
+  for (long long j = nvec * N + blockIdx.x * (long long)blockDim.x + threadIdx.x; j < n; j += stride)
+    y[j] = xl_from_float<T>(f(xl_to_float(x[j])));
 }
 
 template <typename T, typename F>
@@ -28,7 +43,23 @@ __global__ void __launch_bounds__(256)
     ew_binary_kernel(const T* __restrict__ x, const T* __restrict__ g, T* __restrict__ y, long long n, F f) {
   constexpr int N = XlVec<T>::N;
   const long long nvec = n / N;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (; i + (EW_UNROLL - 1) * stride < nvec; i += EW_UNROLL * stride) {
+    float a[EW_UNROLL][N], b[EW_UNROLL][N];
+#pragma unroll
+    for (int u = 0; u < EW_UNROLL; ++u) {
+      xl_load16(x + (i + u * stride) * N, a[u]);
+      xl_load16(g + (i + u * stride) * N, b[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < EW_UNROLL; ++u) {
+#pragma unroll
+      for (int k = 0; k < N; ++k) a[u][k] = f(a[u][k], b[u][k]);
+      xl_store16(y + (i + u * stride) * N, a[u]);
+    }
+  }
+  for (; i < nvec; i += stride) {
     float a[N], b[N];
     xl_load16(x + i * N, a);
     xl_load16(g + i * N, b);
@@ -36,8 +67,8 @@ __global__ void __launch_bounds__(256)
     for (int k = 0; k < N; ++k) a[k] = f(a[k], b[k]);
     xl_store16(y + i * N, a);
   }
-  for (long long i = nvec * N + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-    y[i] = xl_from_float<T>(f(xl_to_float(x[i]), xl_to_float(g[i])));
+  for (long long j = nvec * N + blockIdx.x * (long long)blockDim.x + threadIdx.x; j < n; j += stride)
+    y[j] = xl_from_float<T>(f(xl_to_float(x[j]), xl_to_float(g[j])));
 }
 
 // ---- GELU ---------------------------------------------------------------------------------------------------------

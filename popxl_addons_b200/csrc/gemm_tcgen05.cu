@@ -2,11 +2,11 @@
 //
 //   C[b] (M x N) = epilogue( A[b] (M x K) * B[b] (K x N) )
 //
-// Structure: persistent kernel, one CTA per SM, 192 threads:
+// Structure: persistent kernel, one CTA per SM, 320 threads:
 //   warp 0      TMA producer   : cp.async.bulk.tensor loads of A / B tiles into a 4-stage shared-memory ring
 //   warp 1      MMA issuer     : one elected thread issues tcgen05.mma (128 x BLOCK_N x 16), accumulators live in TMEM,
 //                                two accumulator buffers so the epilogue of tile i overlaps the main loop of tile i+1
-//   warps 2..5  epilogue       : tcgen05.ld TMEM -> registers, bias / activation / accumulate, 16-byte global stores
+//   warps 2..9  epilogue       : tcgen05.ld TMEM -> registers, bias / activation / accumulate, 16-byte global stores
 // Either operand may be K-major (reduction dimension contiguous) or MN-major, so `x @ w`, `g @ w^T` and `x^T @ g`
 // (forward, data gradient, weight gradient) all run without materialising a transpose. Shared-memory tiles use the
 // 128-byte swizzle that both TMA and the UMMA shared-memory descriptors understand.
@@ -24,7 +24,8 @@ constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 64;  // 64 x 2 bytes = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 4;
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_EPI_WARPS = 8;  // two warps per TMEM lane quarter, each draining half of the accumulator columns
+constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 enum { ERR_FULL_WAIT = 1, ERR_EMPTY_WAIT = 2, ERR_TMEM_FULL_WAIT = 3, ERR_TMEM_EMPTY_WAIT = 4 };
@@ -209,7 +210,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full_bar[a], 1);
-      mbar_init(&tmem_empty_bar[a], 4);  // one arrival per epilogue warp
+      mbar_init(&tmem_empty_bar[a], NUM_EPI_WARPS);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -298,7 +299,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     }
   } else {
     // ------------------------------------------------ epilogue ----------------------------------------------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    const int q = warp & 3;                     // TMEM lane quarter this warp may access
+    const int col_half = (warp - 2) >> 2;       // which half of the accumulator columns this warp drains
+    constexpr int COLS_PER_WARP = BLOCK_N / (NUM_EPI_WARPS / 4);
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     float mean_a = 0.f, mean_b = 1.f;
@@ -319,7 +322,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       uint8_t* crow = (uint8_t*)p.C + ((long long)b * p.batch_stride_c + (long long)row * p.ldc) *
                                           (p.c_dtype == XL_F32 ? 4 : 2);
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N; c += 32) {
+      for (int c = col_half * COLS_PER_WARP; c < (col_half + 1) * COLS_PER_WARP; c += 32) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c, r);
         tmem_ld_wait();

@@ -156,9 +156,7 @@ class DecoderBlock(Module):
         if par.tp > 1:
             h = replicated_all_reduce_identical_inputs(h, group=par.tp_group)
         wqkv, bqkv = self._linear("attention.qkv", h, 3 * hd, bias, par)
-        qkv = h @ wqkv
-        if bqkv is not None:
-            qkv = qkv + bqkv
+        qkv = ops.linear_bias_act(h, wqkv, bqkv) if bqkv is not None else h @ wqkv
         a = ops.attention_qkv(qkv, sin, cos, cfg.seq_len, heads, cfg.head_dim, cfg.rotary_dim, causal=True,
                               inplace=True)
         wo = self.add_variable_input("attention.out.weight",
@@ -184,18 +182,22 @@ class DecoderBlock(Module):
             z = ops.swiglu(h @ wg, h @ wu)
         else:
             w1, b1 = self._linear("mlp.fc_in", h, f, True, par)
-            z = ops.gelu((h @ w1) + b1, approximate="tanh" if cfg.family == "gpt2" else "none")
+            # the bias is added in the GEMM epilogue; the activation stays a separate op because its input is needed
+            # again by the backward pass
+            z = ops.gelu(ops.linear_bias_act(h, w1, b1), approximate="tanh" if cfg.family == "gpt2" else "none")
         w2 = self.add_variable_input("mlp.fc_out.weight",
                                      _normal((f, cfg.hidden), cfg.init_std / math.sqrt(2 * cfg.layers), cfg.np_dtype),
                                      cfg.xl_dtype, replica_grouping=par.sharded_rg, overwrite=True)
-        y = z @ w2
-        if par.tp > 1:
-            y = replicated_all_reduce_identical_grad_inputs(y, group=par.tp_group)
+        b2 = None
         if cfg.family != "llama":
             b2 = self.add_variable_input("mlp.fc_out.bias", _const_init("zeros", (cfg.hidden,), cfg.np_dtype),
                                          cfg.xl_dtype, overwrite=True)
-            y = y + b2
-        return y
+        if par.tp == 1 and b2 is not None:
+            return ops.linear_bias_act(z, w2, b2)
+        y = z @ w2
+        if par.tp > 1:
+            y = replicated_all_reduce_identical_grad_inputs(y, group=par.tp_group)
+        return y + b2 if b2 is not None else y
 
     def build(self, x: xl.Tensor, sin: xl.Tensor, cos: xl.Tensor) -> xl.Tensor:
         cfg = self.cfg
@@ -257,12 +259,11 @@ class DecoderHead(Module):
         shard = Embedding.get_vocab_shard_size(cfg.vocab_size, par.tp)
         wl = self.add_variable_input("lm_head.weight", _normal((cfg.hidden, shard), cfg.init_std, cfg.np_dtype),
                                      cfg.xl_dtype, replica_grouping=par.sharded_rg, overwrite=True)
-        logits = h @ wl
         if cfg.family == "gptj":
             bl = self.add_variable_input("lm_head.bias", _const_init("zeros", (shard,), cfg.np_dtype), cfg.xl_dtype,
                                          replica_grouping=par.sharded_rg, overwrite=True)
-            logits = logits + bl
-        return logits
+            return ops.linear_bias_act(h, wl, bl)
+        return h @ wl
 
 
 def rotary_tables(cfg: DecoderConfig):

@@ -326,6 +326,14 @@ def accumulate_mean_cuda(acc, x, *extra, **attrs):
     return acc
 
 
+@native("matmul_accumulate_mean_")
+def matmul_accumulate_mean_cuda(acc, a, b, step):
+    if step.dtype != torch.float32 or not acc.is_contiguous():
+        return NotImplemented
+    res = gemm(a, b, out=acc, accumulate=2, step=step)
+    return res
+
+
 def grad_sumsq_cuda(t, scale):
     if not _ok(t) or not (scale.is_cuda and scale.dtype == torch.float32):
         return NotImplemented

@@ -36,12 +36,14 @@ def autodiff_with_accumulation(graph: GraphWithNamedArgs, tensors_to_accumulate_
                                grads_provided: Optional[Iterable[xl.Tensor]] = None,
                                called_graphs_grad_info: Optional[Mapping[xl.Graph, GradGraphInfo]] = None,
                                replica_groupings=None,
-                               accum_dtype: Optional[xl.dtype] = None
+                               accum_dtype: Optional[xl.dtype] = None, fuse_matmul: bool = True
                                ) -> Tuple[NamedVariableFactories, GraphWithNamedArgs]:
     """Gradient graph that, instead of returning the gradients of `tensors_to_accumulate_grads`, folds them into
     by-reference accumulators `accum.<name>` as a *running mean* over calls, counted by the scalar
     `mean_accum_counter` (zero it to start a new mean). Other `grads_required` remain graph outputs.
     Accumulators have the dtype of their tensor unless `accum_dtype` is given (e.g. fp32 sums for bf16 weights).
+    With `fuse_matmul`, a gradient that is the direct result of a matmul and is used for nothing else is never written
+    out: the matmul and the accumulation become one `matmul_accumulate_mean_` op (GEMM with accumulating epilogue).
 
     Returns the factories for the accumulators/counter and the gradient graph (its `args` name them)."""
     accumulate = list(tensors_to_accumulate_grads)
@@ -74,15 +76,33 @@ def autodiff_with_accumulation(graph: GraphWithNamedArgs, tensors_to_accumulate_
                 accum.meta_shape = tuple(t.meta_shape)
             factories[f"accum.{key}"] = accum_f
             named[f"accum.{key}"] = accum
-            ops.var_updates.accumulate_mean_(accum, grad_t, counter)
             if t not in required:
                 drop.append(idx)
+            if fuse_matmul and t not in required and _fuse_matmul_into_accumulator(g, grad_t, accum, counter):
+                continue
+            ops.var_updates.accumulate_mean_(accum, grad_t, counter)
         ops.add_(counter, xl.constant(1.0, xl.float32))
         for idx in sorted(drop, reverse=True):
             del g._outputs[idx]
             del info._expected_outputs[idx]
     grad.args = NamedTensors.from_dict(named)
     return NamedVariableFactories.from_dict(factories), grad
+
+
+def _fuse_matmul_into_accumulator(g: xl.Graph, grad_t: xl.Tensor, accum: xl.Tensor, counter: xl.Tensor) -> bool:
+    """If `grad_t` comes straight out of a 2-D matmul and has no other consumer, replace that matmul by a
+    `matmul_accumulate_mean_` emitted now (current graph must be `g`). Returns whether the rewrite happened."""
+    op = grad_t.producer
+    if op is None or op.opdef.name != "matmul" or op.graph is not g:
+        return False
+    a, b = op.inputs
+    if a.rank != 2 or b.rank != 2 or tuple(grad_t.shape) != tuple(accum.shape):
+        return False
+    if any(grad_t in other.inputs for other in g.ops) or g._outputs.count(grad_t) > 1:
+        return False
+    g.ops.remove(op)
+    ops.var_updates.matmul_accumulate_mean_(accum, a, b, counter)
+    return True
 
 
 def remap_grad_info(grad_info: GradGraphInfo, forward_graph: xl.Graph, backward_graph: xl.Graph) -> GradGraphInfo:

@@ -1,0 +1,124 @@
+"""Per-kernel timing against the roofline: `python -m popxl_addons_b200.utils.kernel_bench [--peaks MEASURED_PEAKS.json]`.
+
+Times every hot kernel on shapes of the GPT-J-6B configuration with CUDA events (3 warm-up + 10 timed launches, an L2
+flush between launches) and reports achieved TFLOP/s or GB/s as a fraction of the measured peaks, next to the library
+kernel (cuBLAS / torch) on the same shape for reference.
+"""
+import argparse
+import json
+import os
+
+import torch
+
+
+def _flush():
+    if not hasattr(_flush, "buf"):
+        _flush.buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    _flush.buf.zero_()
+
+
+def time_ms(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    times = []
+    for _ in range(iters):
+        _flush()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--peaks", default=os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json"))
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args()
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    src = "fallback"
+    if os.path.exists(args.peaks):
+        peaks.update(json.load(open(args.peaks)))
+        src = "measured"
+    from popxl_addons_b200.ops import native as nat
+
+    rows = []
+    bf = torch.bfloat16
+
+    def gemm_row(name, M, N, K, a_t=False, b_t=False, batch=1):
+        a = torch.randn((batch, K, M) if a_t else (batch, M, K), device="cuda", dtype=bf)
+        b = torch.randn((batch, N, K) if b_t else (batch, K, N), device="cuda", dtype=bf)
+        av = a.transpose(-1, -2) if a_t else a
+        bv = b.transpose(-1, -2) if b_t else b
+        if batch == 1:
+            av, bv = av[0], bv[0]
+        ours = time_ms(lambda: nat.gemm(av, bv))
+        lib = time_ms(lambda: torch.matmul(av, bv))
+        fl = 2.0 * M * N * K * batch
+        rows.append(dict(kernel=name, shape=f"{batch}x{M}x{N}x{K}", ms=ours, tflops=fl / ours / 1e9,
+                         frac_of_peak=fl / ours / 1e9 / peaks["bf16_tflops"], lib_ms=lib, lib_tflops=fl / lib / 1e9,
+                         vs_lib=lib / ours))
+
+    gemm_row("gemm fwd qkv", 2048, 12288, 4096)
+    gemm_row("gemm fwd fc_in", 2048, 16384, 4096)
+    gemm_row("gemm fwd fc_out", 2048, 4096, 16384)
+    gemm_row("gemm dgrad fc_in (B K-major)", 2048, 4096, 16384, b_t=True)
+    gemm_row("gemm wgrad fc_in (A,B MN-major)", 4096, 16384, 2048, a_t=True)
+    gemm_row("gemm lm_head", 2048, 50400, 4096)
+    gemm_row("gemm attn scores", 2048, 2048, 256, b_t=True, batch=16)
+    gemm_row("gemm attn pv", 2048, 256, 2048, batch=16)
+    gemm_row("gemm square 8192", 8192, 8192, 8192)
+
+    def mem_row(name, fn, nbytes):
+        ms = time_ms(fn)
+        rows.append(dict(kernel=name, ms=ms, gbs=nbytes / ms / 1e6, frac_of_peak=nbytes / ms / 1e6 / peaks["hbm_gbs"]))
+
+    x = torch.randn(2048, 16384, device="cuda", dtype=bf)
+    g = torch.randn_like(x)
+    mem_row("gelu fwd 2048x16384", lambda: nat.gelu_cuda(x), 2 * x.numel() * 2)
+    mem_row("gelu bwd 2048x16384", lambda: nat.gelu_grad_cuda(x, g), 3 * x.numel() * 2)
+    h = torch.randn(8192, 4096, device="cuda", dtype=bf)
+    w = torch.randn(4096, device="cuda", dtype=bf)
+    b = torch.randn(4096, device="cuda", dtype=bf)
+    gh = torch.randn_like(h)
+    y, mean, rstd = nat.layer_norm_cuda(h, w, b, 1e-5)
+    mem_row("layer_norm fwd 8192x4096", lambda: nat.layer_norm_cuda(h, w, b, 1e-5), 2 * h.numel() * 2)
+    mem_row("layer_norm bwd 8192x4096", lambda: nat.layer_norm_grad_cuda(h, w, mean, rstd, gh), 3 * h.numel() * 2)
+    n = 1 << 27
+    pw = torch.randn(n, device="cuda", dtype=bf)
+    pg = torch.randn(n, device="cuda")
+    pm, pv, pmaster = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda"), pw.float()
+    step = torch.zeros((), device="cuda")
+    mem_row("adam 128M params (bf16 w, fp32 g/m/v/master)",
+            lambda: nat.adam_cuda(pw, pg, pm, pv, step, pmaster, has_step=True, has_master=True, bias_correction=True,
+                                  lr=1e-4, beta1=0.9, beta2=0.95, epsilon=1e-5, weight_decay=0.01, grad_scale=1.0,
+                                  _tensor_scalars=()), n * (2 + 4 + 4 * 2 + 4 * 2 + 4 * 2 + 2))
+    sc = torch.randn(16 * 2048, 2048, device="cuda", dtype=bf)
+    lse = torch.empty(16 * 2048, device="cuda")
+    mem_row("attn softmax fwd 16x2048x2048",
+            lambda: nat._check(nat._sm_fwd(sc.data_ptr(), lse.data_ptr(), 16 * 2048, 2048, 2048, 0.0625, 1, 2,
+                                           nat._stream()), "sm"), 2 * sc.numel() * 2)
+    lg = torch.randn(2048, 50400, device="cuda", dtype=bf)
+    lab = torch.randint(0, 50400, (2048,), device="cuda", dtype=torch.int32)
+    one = torch.ones((), device="cuda")
+    mem_row("cross-entropy fwd+bwd 2048x50400", lambda: nat.ce_with_grad_cuda(lg, lab, one, None, "mean"),
+            2 * lg.numel() * 2)
+    nat.check_gemm_errors()
+    print(f"peaks ({src}): hbm {peaks['hbm_gbs']} GB/s, bf16 {peaks['bf16_tflops']} TFLOP/s")
+    for r in rows:
+        if "tflops" in r:
+            print(f"{r['kernel']:38s} {r['shape']:>22s} {r['ms']:8.3f} ms {r['tflops']:8.1f} TF "
+                  f"({r['frac_of_peak']*100:5.1f}% of {src}) | cuBLAS {r['lib_ms']:8.3f} ms {r['lib_tflops']:8.1f} TF "
+                  f"| ours/cuBLAS speed {r['vs_lib']:.2f}x")
+        else:
+            print(f"{r['kernel']:62s} {r['ms']:8.3f} ms {r['gbs']:8.1f} GB/s ({r['frac_of_peak']*100:5.1f}% of {src})")
+    if args.out:
+        json.dump(rows, open(args.out, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()

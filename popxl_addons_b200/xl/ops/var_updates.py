@@ -254,3 +254,24 @@ def sgd_fused_(var: Tensor, grad: Tensor, momentum_buffer: Optional[Tensor] = No
     ins, attrs = _pack(ins, lr=lr, momentum=momentum, weight_decay=weight_decay, grad_scale=grad_scale)
     attrs.update(has_momentum=momentum_buffer is not None)
     return emit1("sgd_fused_", ins, attrs)
+
+
+# ---- weight-gradient GEMM fused with the running-mean accumulation ---------------------------------------------
+
+
+def _mm_acc_mean_ref(acc, a, b, step):
+    if acc.device.type == "meta":
+        return acc
+    t = step.float().reshape(())
+    prod = torch.matmul(a.float(), b.float())
+    return acc.copy_((acc.float() * (t / (t + 1.0)) + prod * (1.0 / (t + 1.0))).to(acc.dtype))
+
+
+OpDef("matmul_accumulate_mean_", impl=_mm_acc_mean_ref, inplace=True, keeps_meta=True,
+      flops=lambda op: 2 * op.inputs[1].shape[-1] * op.inputs[0].nelms)
+
+
+def matmul_accumulate_mean_(acc: Tensor, lhs: Tensor, rhs: Tensor, step: Tensor) -> Tensor:
+    """`acc = acc * step/(step+1) + (lhs @ rhs)/(step+1)`: the product never exists in memory, the GEMM epilogue
+    folds each output tile into the accumulator (weight gradients under gradient accumulation)."""
+    return emit1("matmul_accumulate_mean_", [acc, lhs, rhs, step])
