@@ -1,0 +1,151 @@
+// Collective kernels over symmetric memory (peer loads / stores over NVLink, bounded waits):
+//   xl_symm_barrier          cross-rank barrier on a signal pad (stream-ordered fence between phases of a step)
+//   xl_symm_all_reduce       one-shot all-reduce of a small fp32 vector (statistics of sharded cross-entropy / LayerNorm)
+//   xl_rts_adam              replicated-tensor-sharding optimizer step in ONE kernel:
+//                            gradient reduce-scatter (each rank reads its shard of every peer's accumulator), mean,
+//                            AdamW on the local fp32 master / moment shards, and all-gather of the updated 16-bit
+//                            weights (each rank stores its shard into every peer's weight buffer)
+#include "comm.cuh"
+
+unsigned int xl_host_comm_spin_limit = XL_COMM_SPIN_DEFAULT;
+
+// Set the poll budget of all later waits on peers (0 restores the default).
+XL_API int xl_set_comm_spin_limit(unsigned int polls) {
+  xl_host_comm_spin_limit = polls ? polls : XL_COMM_SPIN_DEFAULT;
+  return 0;
+}
+
+__global__ void symm_barrier_kernel(unsigned int* const* pads, int rank, int world, int channel, int* err,
+                                    unsigned int limit) {
+  xl_group_barrier(pads, rank, world, channel, err, limit);
+}
+
+XL_API int xl_symm_barrier(const void* pads_dev, int rank, int world, int channel, int* err, cudaStream_t s) {
+  if (world > 32) return -1;
+  symm_barrier_kernel<<<1, 32, 0, s>>>((unsigned int* const*)pads_dev, rank, world, channel, err,
+                                       xl_host_comm_spin_limit);
+  return (int)cudaGetLastError();
+}
+
+// Every rank has written its `n` floats at `offset` of its own symmetric buffer before the launch (stream order).
+// op: 0 add, 1 max. One CTA: the message is a few thousand elements at most (latency-bound by design).
+__global__ void __launch_bounds__(1024)
+    symm_all_reduce_kernel(float* const* bufs, unsigned int* const* pads, long long offset, float* out, int n, int op,
+                           int rank, int world, int channel, int* err, unsigned int limit) {
+  __shared__ int ok_s;
+  if (threadIdx.x < 32) {
+    const bool ok = xl_group_barrier(pads, rank, world, channel, err, limit);
+    if (threadIdx.x == 0) ok_s = ok;
+  }
+  __syncthreads();
+  if (ok_s) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float acc = op == 0 ? 0.f : -INFINITY;
+      for (int p = 0; p < world; ++p) {
+        const float v = bufs[p][offset + i];
+        acc = op == 0 ? acc + v : fmaxf(acc, v);
+      }
+      out[i] = acc;
+    }
+  }
+  __syncthreads();
+  // peers may overwrite their buffers only after everyone has read them
+  if (threadIdx.x < 32) xl_group_barrier(pads, rank, world, channel + 1, err, limit);
+}
+
+XL_API int xl_symm_all_reduce(const void* bufs_dev, const void* pads_dev, long long offset_elems, float* out, int n,
+                              int op, int rank, int world, int channel, int* err, cudaStream_t s) {
+  if (world > 32 || n <= 0) return -1;
+  symm_all_reduce_kernel<<<1, 1024, 0, s>>>((float* const*)bufs_dev, (unsigned int* const*)pads_dev, offset_elems, out,
+                                             n, op, rank, world, channel, err, xl_host_comm_spin_limit);
+  return (int)cudaGetLastError();
+}
+
+struct RtsAdamArgs {
+  float lr, beta1, beta2, eps, weight_decay, grad_scale;
+  int bias_correction;
+};
+
+constexpr int RTS_MAX_WORLD = 8;
+struct RtsPtrs {
+  const float* grads[RTS_MAX_WORLD];  // every rank's full gradient accumulator (fp32)
+  void* weights[RTS_MAX_WORLD];       // every rank's full 16-bit weight tensor
+};
+
+// shard = elements [shard_off, shard_off + shard_n) of the flattened tensor; shard_off and shard_n are multiples of 4.
+template <typename TW, typename TM>
+__global__ void __launch_bounds__(256)
+    rts_adam_kernel(RtsPtrs ptrs, float* __restrict__ master, TM* __restrict__ m, float* __restrict__ v,
+                    const float* __restrict__ step, long long shard_off, long long shard_n, int world, RtsAdamArgs a) {
+  float c1 = 1.f, c2 = 1.f;
+  if (step != nullptr && a.bias_correction) {
+    const float t = *step;
+    c1 = 1.f / (1.f - powf(a.beta1, t));
+    c2 = 1.f / (1.f - powf(a.beta2, t));
+  }
+  const float inv_world = 1.f / world;
+  const long long nvec = shard_n / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    const long long e = i * 4;
+    float4 g = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < world; ++p) {  // reduce-scatter: my shard of every peer's gradient
+      const float4 t = *reinterpret_cast<const float4*>(ptrs.grads[p] + shard_off + e);
+      g.x += t.x; g.y += t.y; g.z += t.z; g.w += t.w;
+    }
+    float gv[4] = {g.x, g.y, g.z, g.w};
+    const float4 w4 = *reinterpret_cast<const float4*>(master + e);
+    const float4 v4 = *reinterpret_cast<const float4*>(v + e);
+    float wv[4] = {w4.x, w4.y, w4.z, w4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+    TW wq[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float gf = gv[k] * inv_world * a.grad_scale;
+      const float mf = xl_to_float(m[e + k]) * a.beta1 + gf * (1.f - a.beta1);
+      vv[k] = vv[k] * a.beta2 + gf * gf * (1.f - a.beta2);
+      const TM mq = xl_from_float<TM>(mf);
+      m[e + k] = mq;
+      const float upd = (xl_to_float(mq) * c1) / (sqrtf(vv[k] * c2) + a.eps) + wv[k] * a.weight_decay;
+      wv[k] -= a.lr * upd;
+      wq[k] = xl_from_float<TW>(wv[k]);
+    }
+    *reinterpret_cast<float4*>(master + e) = make_float4(wv[0], wv[1], wv[2], wv[3]);
+    *reinterpret_cast<float4*>(v + e) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    const uint2 packed = *reinterpret_cast<const uint2*>(wq);
+    for (int p = 0; p < world; ++p)  // all-gather: my shard into every peer's weights
+      *reinterpret_cast<uint2*>((TW*)ptrs.weights[p] + shard_off + e) = packed;
+  }
+}
+
+__global__ void rts_step_increment_kernel(float* step) { *step += 1.f; }
+
+// grads / weights: host arrays of `world` device pointers (this rank's own pointer included at index `rank`).
+// Call between two xl_symm_barrier launches: the first guarantees that every rank's accumulators are final, the second
+// that every rank's weight shards have arrived before the weights are used.
+XL_API int xl_rts_adam(const void* const* grads, void* const* weights, int w_dtype, float* master, void* m, int m_dtype,
+                       float* v, float* step, long long shard_off, long long shard_n, int world, float lr, float beta1,
+                       float beta2, float eps, float weight_decay, float grad_scale, int bias_correction,
+                       cudaStream_t s) {
+  if (world > RTS_MAX_WORLD || (shard_off & 3) || (shard_n & 3)) return -1;
+  if (w_dtype != XL_BF16 && w_dtype != XL_F16) return -1;
+  RtsPtrs ptrs;
+  for (int p = 0; p < world; ++p) {
+    ptrs.grads[p] = (const float*)grads[p];
+    ptrs.weights[p] = weights[p];
+  }
+  RtsAdamArgs a{lr, beta1, beta2, eps, weight_decay, grad_scale, bias_correction};
+  if (step) rts_step_increment_kernel<<<1, 1, 0, s>>>(step);
+  const int grid = xl_grid_for(shard_n / 4, 256, 148 * 8);
+#define XL_RTS_LAUNCH(TW, TM) \
+  rts_adam_kernel<TW, TM><<<grid, 256, 0, s>>>(ptrs, master, (TM*)m, v, step, shard_off, shard_n, world, a)
+  if (w_dtype == XL_BF16) {
+    if (m_dtype == XL_F32) XL_RTS_LAUNCH(__nv_bfloat16, float);
+    else if (m_dtype == XL_BF16) XL_RTS_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else XL_RTS_LAUNCH(__nv_bfloat16, __half);
+  } else {
+    if (m_dtype == XL_F32) XL_RTS_LAUNCH(__half, float);
+    else if (m_dtype == XL_BF16) XL_RTS_LAUNCH(__half, __nv_bfloat16);
+    else XL_RTS_LAUNCH(__half, __half);
+  }
+#undef XL_RTS_LAUNCH
+  return (int)cudaGetLastError();
+}

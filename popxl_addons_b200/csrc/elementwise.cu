@@ -72,8 +72,27 @@ __global__ void __launch_bounds__(256)
 }
 
 // ---- GELU ---------------------------------------------------------------------------------------------------------
+// erf by the Abramowitz-Stegun 7.1.26 rational approximation (|error| < 1.5e-7): ~10 instructions instead of ~30 for
+// erff, which otherwise makes the 16-bit GELU kernels compute-bound instead of bandwidth-bound.
+__device__ __forceinline__ float xl_fast_erf(float x) {
+  const float ax = fabsf(x);
+  const float t = __fdividef(1.f, fmaf(0.3275911f, ax, 1.f));
+  const float poly = t * fmaf(t, fmaf(t, fmaf(t, fmaf(t, 1.061405429f, -1.453152027f), 1.421413741f), -0.284496736f), 0.254829592f);
+  const float r = 1.f - poly * __expf(-ax * ax);
+  return copysignf(r, x);
+}
 struct GeluErf {
   __device__ __forceinline__ float operator()(float x) const { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+};
+struct GeluErfFast {
+  __device__ __forceinline__ float operator()(float x) const { return 0.5f * x * (1.f + xl_fast_erf(x * 0.70710678118654752f)); }
+};
+struct GeluErfGradFast {
+  __device__ __forceinline__ float operator()(float x, float g) const {
+    const float cdf = 0.5f * (1.f + xl_fast_erf(x * 0.70710678118654752f));
+    const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
+    return g * (cdf + x * pdf);
+  }
 };
 struct GeluTanh {
   __device__ __forceinline__ float operator()(float x) const {
@@ -112,6 +131,7 @@ XL_API int xl_gelu_fwd(const void* x, void* y, long long n, int dtype, int tanh_
   const int grid = xl_grid_for(n, 256 * 8);
   XL_DISPATCH_DTYPE(dtype, T, {
     if (tanh_approx) ew_unary_kernel<T><<<grid, 256, 0, s>>>((const T*)x, (T*)y, n, GeluTanh());
+    else if (sizeof(T) == 2) ew_unary_kernel<T><<<grid, 256, 0, s>>>((const T*)x, (T*)y, n, GeluErfFast());
     else ew_unary_kernel<T><<<grid, 256, 0, s>>>((const T*)x, (T*)y, n, GeluErf());
   });
   return (int)cudaGetLastError();
@@ -120,6 +140,7 @@ XL_API int xl_gelu_bwd(const void* x, const void* g, void* dx, long long n, int 
   const int grid = xl_grid_for(n, 256 * 8);
   XL_DISPATCH_DTYPE(dtype, T, {
     if (tanh_approx) ew_binary_kernel<T><<<grid, 256, 0, s>>>((const T*)x, (const T*)g, (T*)dx, n, GeluTanhGrad());
+    else if (sizeof(T) == 2) ew_binary_kernel<T><<<grid, 256, 0, s>>>((const T*)x, (const T*)g, (T*)dx, n, GeluErfGradFast());
     else ew_binary_kernel<T><<<grid, 256, 0, s>>>((const T*)x, (const T*)g, (T*)dx, n, GeluErfGrad());
   });
   return (int)cudaGetLastError();
@@ -534,7 +555,8 @@ __global__ void __launch_bounds__(256)
     rotary_kernel(const T* __restrict__ x, const T* __restrict__ sin_t, const T* __restrict__ cos_t, T* __restrict__ y,
                   long long total_pairs, int H, int S, int D, int R, int sin_batch, float sign, long long xb,
                   long long xh, long long xs, long long yb, long long yh, long long ys) {
-  const int pairs_per_row = D / 2;
+  // in place only the rotated pairs are touched; out of place the pass-through features are copied as well
+  const int pairs_per_row = (x == y) ? R / 2 : D / 2;
   for (long long p = blockIdx.x * (long long)blockDim.x + threadIdx.x; p < total_pairs; p += (long long)gridDim.x * blockDim.x) {
     const int j = (int)(p % pairs_per_row);
     long long row = p / pairs_per_row;  // (b*H + h)*S + s
@@ -561,7 +583,8 @@ __global__ void __launch_bounds__(256)
 XL_API int xl_rotary(const void* x, const void* sin_t, const void* cos_t, void* y, long long B, int H, int S, int D,
                      int R, int sin_batch, int inverse, int dtype, long long xb, long long xh, long long xs,
                      long long yb, long long yh, long long ys, cudaStream_t s) {
-  const long long pairs = B * H * S * (long long)(D / 2);
+  const long long pairs = B * H * S * (long long)((x == y ? R : D) / 2);
+  if (pairs == 0) return 0;
   const int grid = xl_grid_for(pairs, 256 * 4);
   XL_DISPATCH_DTYPE(dtype, T, {
     rotary_kernel<T><<<grid, 256, 0, s>>>((const T*)x, (const T*)sin_t, (const T*)cos_t, (T*)y, pairs, H, S, D, R,

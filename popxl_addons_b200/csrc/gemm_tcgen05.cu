@@ -13,7 +13,7 @@
 //
 // Every wait on an mbarrier is bounded: when a wait gives up the kernel records a code in `*err`, raises a CTA-wide
 // abort flag, all roles leave their loops, TMEM is released and the kernel returns normally.
-#include "common.cuh"
+#include "comm.cuh"
 
 #include <cuda.h>
 #include <stdio.h>
@@ -39,11 +39,19 @@ struct GemmParams {
   const void* bias;  // length N, may be null
   int bias_dtype;
   int act;         // 0 none, 1 gelu(erf), 2 gelu(tanh), 3 relu
-  int accumulate;  // 0 overwrite, 1 C += alpha*acc, 2 running mean: C = C*t/(t+1) + acc/(t+1), t = *step
+  int accumulate;  // 0 overwrite, 1 C += alpha*acc, 2 running mean: C = C*t/(t+1) + acc/(t+1), t = *step,
+                   // 3 all-reduce: C is a multicast (NVLS) address, every tile is pushed with multimem.red.add into
+                   //   the output buffer of every rank of the group (buffers zeroed before the launch)
   const float* step;
   float alpha;
   int is_fp16;
   int* err;
+  // all-reduce mode only
+  unsigned int* const* pads;  // signal pad of every rank
+  int comm_rank, comm_world;
+  unsigned int* local_sync;   // [0] "peers are ready" epoch flag, [1] count of epilogue warps that finished
+  unsigned int epoch;
+  unsigned int comm_spin_limit;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------------------
@@ -310,6 +318,24 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       mean_a = t / (t + 1.f);
       mean_b = 1.f / (t + 1.f);
     }
+    if (p.accumulate == 3) {
+      // Nobody may push into a peer's output before that peer has zeroed it, i.e. before it has entered this kernel:
+      // the first epilogue warp of CTA 0 runs the cross-rank barrier and publishes the epoch to the other CTAs.
+      if (blockIdx.x == 0 && warp == 2) {
+        const bool peers_ok = xl_group_barrier(p.pads, p.comm_rank, p.comm_world, 0, p.err, p.comm_spin_limit);
+        if (lane == 0 && peers_ok) xl_st_release_gpu(p.local_sync, p.epoch);
+      }
+      bool ready = false;
+      for (unsigned int i = 0; i < p.comm_spin_limit && !ready; ++i) {
+        ready = xl_ld_acquire_gpu(p.local_sync) == p.epoch;
+        if (!ready && (i & 1023u) == 1023u && *abort_flag) break;
+      }
+      if (!ready) {
+        ok = false;
+        *abort_flag = 1;
+        if (p.err) atomicCAS(p.err, 0, (int)XL_COMM_TIMEOUT_FLAG);
+      }
+    }
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       int b, mb, nb;
       tile_coords(tile, tiles_m, tiles_n, b, mb, nb);
@@ -373,7 +399,20 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         } else {
           uint16_t* dst = (uint16_t*)crow + col0;
           const bool bf = p.c_dtype == XL_BF16;
-          if (full && (((uintptr_t)dst) & 15) == 0) {
+          if (p.accumulate == 3) {
+            // host guarantees N % 8 == 0 and 16-byte aligned rows in this mode
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (col0 + j >= p.N) break;
+              uint4 o;
+              uint16_t* oe = (uint16_t*)&o;
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                oe[e] = bf ? __bfloat16_as_ushort(__float2bfloat16_rn(v[j + e])) : __half_as_ushort(__float2half_rn(v[j + e]));
+              if (bf) xl_multimem_red_add_bf16x8(dst + j, o);
+              else xl_multimem_red_add_f16x8(dst + j, o);
+            }
+          } else if (full && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               uint4 old;
@@ -409,6 +448,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (p.accumulate == 3) {
+      // The kernel may only finish once every rank's pushes have landed here: the last epilogue warp of this rank
+      // to finish runs the closing cross-rank barrier (each warp fences its own pushes first).
+      __threadfence_system();
+      unsigned int prev = 0;
+      if (lane == 0) prev = atomicAdd(p.local_sync + 1, 1u);
+      prev = __shfl_sync(0xffffffffu, prev, 0);
+      if (prev == gridDim.x * NUM_EPI_WARPS - 1) {
+        if (lane == 0) p.local_sync[1] = 0;
+        xl_group_barrier(p.pads, p.comm_rank, p.comm_world, 1, p.err, p.comm_spin_limit);
+      }
     }
   }
 
@@ -476,11 +527,17 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
 //   b: if b_mn == 0 stored (N x K) row-major with leading dimension ldb; if b_mn == 1 stored (K x N) row-major.
 //   Leading dimensions and batch strides are in elements; pointers and leading dimensions must be 16-byte aligned.
 //   err: device int that receives a non-zero code if a bounded wait inside the kernel gave up (may be null).
+//   accumulate == 3 (GEMM fused with an all-reduce over NVSwitch): `c` is the multicast address of an output buffer
+//   that every rank of the group zeroed in stream order before this launch; comm_pads = device array with the signal
+//   pad of every rank, comm_local_sync = two zero-initialised device words of this rank, comm_epoch = a value that
+//   differs from the previous call's. All ranks must launch the same GEMM shape.
 // Returns 0, a CUDA error code, or a negative value when the arguments are not supported by this kernel.
 XL_API int xl_gemm_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, int batch, int a_mn, int b_mn,
                            long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
                            long long stride_c, int ab_is_fp16, int c_dtype, const void* bias, int bias_dtype, int act,
-                           int accumulate, const float* step, float alpha, int* err, int sm_count, cudaStream_t s) {
+                           int accumulate, const float* step, float alpha, int* err, int sm_count,
+                           const void* comm_pads, int comm_rank, int comm_world, unsigned int* comm_local_sync,
+                           unsigned int comm_epoch, cudaStream_t s) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -1;
   if ((((uintptr_t)a) & 15) || (((uintptr_t)b) & 15) || (lda % 8) || (ldb % 8)) return -1;
   if (batch > 1 && ((stride_a % 8) || (stride_b % 8))) return -1;
@@ -499,6 +556,11 @@ XL_API int xl_gemm_tcgen05(const void* a, const void* b, void* c, int M, int N, 
   p.C = c; p.ldc = ldc; p.batch_stride_c = stride_c; p.c_dtype = c_dtype;
   p.bias = bias; p.bias_dtype = bias_dtype; p.act = act; p.accumulate = accumulate; p.step = step;
   p.alpha = alpha; p.is_fp16 = ab_is_fp16; p.err = err;
+  p.pads = (unsigned int* const*)comm_pads; p.comm_rank = comm_rank; p.comm_world = comm_world;
+  p.local_sync = comm_local_sync; p.epoch = comm_epoch; p.comm_spin_limit = xl_host_comm_spin_limit;
+  if (accumulate == 3 && (comm_pads == nullptr || comm_local_sync == nullptr || (N % 8) || c_dtype == XL_F32 ||
+                          (ldc % 8) || comm_world > 32))
+    return -1;
   if (sm_count <= 0) sm_count = 148;
   if (block_n == 128) return launch<128>(ma, mb, p, sm_count, s);
   return launch<256>(ma, mb, p, sm_count, s);

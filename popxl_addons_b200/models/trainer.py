@@ -41,7 +41,7 @@ class DecoderTrainer:
     def __init__(self, cfg: DecoderConfig, micro_batches: int = 16, micro_batch_size: int = 1, device: str = "auto",
                  seed: int = 0, lr: float = 1e-4, weight_decay: float = 0.01, beta1: float = 0.9, beta2: float = 0.95,
                  eps: float = 1e-5, recompute: bool = True, optimizer_state_dtype: xl.dtype = xl.float32,
-                 shard_optimizer: bool = True, use_native: Optional[bool] = None):
+                 shard_optimizer: bool = True, use_native: Optional[bool] = None, fused_collectives: bool = True):
         self.cfg = cfg
         self.micro_batches = micro_batches
         self.micro_batch_size = micro_batch_size
@@ -55,9 +55,15 @@ class DecoderTrainer:
         self.recompute = recompute
         self.state_dtype = optimizer_state_dtype
         self.shard_optimizer = shard_optimizer and cfg.dp > 1
+        self.fused_collectives = fused_collectives
         t0 = time.perf_counter()
         self._build()
         apply_pre_alias_patterns(self.ir)
+        self.fused_gemm_collectives = 0
+        if fused_collectives and cfg.tp > 1:
+            from ..parallel import fuse_gemm_collectives
+
+            self.fused_gemm_collectives = fuse_gemm_collectives(self.ir)
         self.build_seconds = time.perf_counter() - t0
         self.session = TaskSession(self.inputs, self.outputs, self.state, 1, self.ir, device, use_native=use_native)
         self.tokens_per_step = micro_batches * micro_batch_size * cfg.seq_len * cfg.dp
@@ -151,6 +157,9 @@ class DecoderTrainer:
             self.master: Dict[str, xl.Variable] = {}
             opt_state = {}
             opt_graphs: Dict[tuple, tuple] = {}
+            from ..optimizers.rts_adam import RTSAdamStep
+
+            fused_jobs = []  # (weight, accumulator, master shard, decay, name): emitted together below
             for group_name, wtree, atree in ([("embedding", emb_vars, emb_acc), ("head", head_vars, head_acc)] +
                                              [(f"layer{i}", blk_vars[i], blk_acc[i]) for i in range(cfg.layers)]):
                 wd, ad = wtree.to_dict(), atree.accum.to_dict()
@@ -166,6 +175,16 @@ class DecoderTrainer:
                                   else torch.tensor(np.asarray(host)).float()).numpy()
                     rg = w.replica_grouping
                     shardable = self.shard_optimizer and w.nelms % cfg.dp == 0
+                    fusable = (shardable and self.fused_collectives and w.dtype in (xl.bfloat16, xl.float16)
+                               and (w.nelms // cfg.dp) % 4 == 0)
+                    if fusable:
+                        master, _ = xl.replica_sharded_variable(host32, xl.float32, f"master.{full}",
+                                                                replica_grouping=rg, shard_grouping=par.dp_group)
+                        self.master[full] = master
+                        w.symmetric_group = par.dp_group
+                        g.symmetric_group = par.dp_group
+                        fused_jobs.append((w, g, master, decay, full, rg))
+                        continue
                     if shardable:
                         g = reduce_replica_sharded_tensor(g, "mean", par.dp_group, par.dp_group)
                         master, _ = xl.replica_sharded_variable(host32, xl.float32, f"master.{full}",
@@ -191,6 +210,20 @@ class DecoderTrainer:
                     if shardable:
                         new_w = ops.collectives.replicated_all_gather(new_w, par.dp_group, output_shape=w.shape)
                     ops.var_updates.copy_var_update_(w, new_w)
+            # one fused kernel per parameter: reduce-scatter + AdamW + all-gather; only the first call waits for all
+            # replicas' accumulators and only the last one for all replicas' weight shards
+            for j, (w, g, master, decay, full, rg) in enumerate(fused_jobs):
+                first, last = j == 0, j == len(fused_jobs) - 1
+                key = ("fused", tuple(w.shape), decay, first, last)
+                if key not in opt_graphs:
+                    opt_graphs[key] = RTSAdamStep().create_graph(
+                        w, g, master, par.dp_group, rg, lr=self.hp["lr"], beta1=self.hp["beta1"],
+                        beta2=self.hp["beta2"], eps=self.hp["eps"], weight_decay=decay,
+                        first_order_dtype=self.state_dtype, sync_before=first, sync_after=last)
+                ofacts, ograph = opt_graphs[key]
+                ostate = ofacts.init(f"adam.{full}")
+                ograph.bind(ostate).call(w, g, master)
+                opt_state[full] = ostate
             for atree in [emb_acc, head_acc] + blk_acc:
                 ops.var_updates.accumulator_zero_(atree.mean_accum_counter)
 

@@ -69,7 +69,13 @@ _sm_fwd = _sig("xl_attn_softmax_fwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _
 _sm_bwd = _sig("xl_attn_softmax_bwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p)
 _ce = _sig("xl_ce_fwd_bwd", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p, _c_f, _c_int, _c_p)
 _gemm = _sig("xl_gemm_tcgen05", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll,
-             _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_p)
+             _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_p, _c_int,
+             _c_int, _c_p, ctypes.c_uint, _c_p)
+_symm_barrier = _sig("xl_symm_barrier", _c_p, _c_int, _c_int, _c_int, _c_p, _c_p)
+_symm_all_reduce = _sig("xl_symm_all_reduce", _c_p, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p,
+                        _c_p)
+_rts_adam = _sig("xl_rts_adam", _c_p, _c_p, _c_int, _c_p, _c_p, _c_int, _c_p, _c_p, _c_ll, _c_ll, _c_int, _c_f, _c_f,
+                 _c_f, _c_f, _c_f, _c_f, _c_int, _c_p)
 
 
 def _stream() -> int:
@@ -412,10 +418,12 @@ def _major(t: torch.Tensor, contraction_last: bool):
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = None, act: int = 0,
          out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, accumulate: int = 0,
-         step: Optional[torch.Tensor] = None, alpha: float = 1.0):
+         step: Optional[torch.Tensor] = None, alpha: float = 1.0, comm=None):
     """`out = act(alpha * a @ b + bias)` on the tcgen05 kernel. `a`: (M,K) or (B,M,K); `b`: (K,N) or (B,K,N); either may
     be a transposed view. With `accumulate=1` the result is added to `out`, with `accumulate=2` it is folded into `out`
-    as a running mean with count `step`. Returns NotImplemented for operands the kernel cannot take."""
+    as a running mean with count `step`. `accumulate=3` with `comm` (a group context owning `out` in symmetric memory)
+    all-reduces the product over the group inside the kernel: `out` must have been zeroed on this stream.
+    Returns NotImplemented for operands the kernel cannot take."""
     if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16) or not (a.is_cuda and b.is_cuda):
         return NotImplemented
     batched = a.dim() == 3
@@ -449,10 +457,21 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
     if bias is not None and not (bias.is_cuda and bias.is_contiguous() and bias.dtype in _CODE and bias.numel() == N):
         return NotImplemented
     err = gemm_error_flag(a.device)
-    rc = _gemm(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, batch, a_mn, b_mn, lda, ldb, ldc, sa, sb, stride_c,
+    out_ptr, pads, crank, cworld, lsync, epoch = out.data_ptr(), None, 0, 1, None, 0
+    if accumulate == 3:
+        if comm is None or batched:
+            return NotImplemented
+        out_ptr = comm.arena.multicast_ptr(out)
+        if not out_ptr:
+            return NotImplemented
+        pads, crank, cworld = comm.arena.pads_dev.data_ptr(), comm.rank, comm.world
+        lsync, epoch = comm.arena.local_sync.data_ptr(), comm.arena.next_epoch()
+        err = comm.err
+    rc = _gemm(a.data_ptr(), b.data_ptr(), out_ptr, M, N, K, batch, a_mn, b_mn, lda, ldb, ldc, sa, sb, stride_c,
                int(a.dtype == torch.float16), _CODE[out.dtype], bias.data_ptr() if bias is not None else None,
                _CODE[bias.dtype] if bias is not None else 0, act, accumulate,
-               step.data_ptr() if step is not None else None, float(alpha), err.data_ptr(), _sms(a.device), _stream())
+               step.data_ptr() if step is not None else None, float(alpha), err.data_ptr(), _sms(a.device), pads, crank,
+               cworld, lsync, epoch, _stream())
     if rc < 0:
         return NotImplemented
     _check(rc, "gemm_tcgen05")

@@ -1,0 +1,5 @@
+"""Multi-GPU runtime: symmetric-memory arenas over NVLink / NVSwitch, the fused compute + collective kernels that use
+them, and the graph pass that rewrites GEMM -> all-reduce pairs into one fused op."""
+from .passes import fuse_gemm_collectives
+
+__all__ = ["fuse_gemm_collectives"]

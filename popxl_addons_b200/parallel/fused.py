@@ -1,0 +1,183 @@
+"""Fused compute + collective kernels on one process per GPU, and the session-side plumbing they need (arenas per
+replica group, placement of variables in symmetric memory, a communicator that serves small reductions from a one-shot
+NVLink kernel and everything else from NCCL)."""
+import ctypes
+import os
+from typing import Dict, List, Optional
+
+import torch
+
+from ..xl.comm import DistComm
+from ..xl.core import ReplicaGrouping
+from .symm import LOCAL_SYNC_OFFSET, SymmArena
+
+_SMALL_ALL_REDUCE_ELEMS = 16384  # fp32 elements served by the one-shot kernel (64 KiB)
+
+
+class GroupContext:
+    """Everything the fused kernels need for one replica group of this rank."""
+
+    def __init__(self, session, grouping: ReplicaGrouping, nbytes: int):
+        pg, members = session.comm.group_for(grouping)
+        self.pg, self.members = pg, members
+        self.arena = SymmArena(nbytes, pg, session.device)
+        self.rank, self.world = self.arena.rank, self.arena.world
+        self.stage = self.arena.alloc((_SMALL_ALL_REDUCE_ELEMS,), torch.float32)  # staging for small all-reduces
+        self.err = torch.zeros(1, dtype=torch.int32, device=session.device)
+
+    def check(self):
+        code = int(self.err.item())
+        if code:
+            self.err.zero_()
+            names = {101: "a peer never consumed this rank's previous signal", 102: "a peer's signal never arrived",
+                     103: "the start-of-kernel handshake with the peers did not complete"}
+            raise CollectiveTimeout(f"collective on group {self.members} gave up waiting: {names.get(code, code)}")
+
+
+class CollectiveTimeout(RuntimeError):
+    """A bounded device-side wait on a peer ran out; the CUDA context is still usable."""
+
+
+def _key(grouping: ReplicaGrouping):
+    return tuple(tuple(g) for g in grouping.groups)
+
+
+class FusedRuntime:
+    def __init__(self, session):
+        self.session = session
+        self.groups: Dict[tuple, GroupContext] = {}
+        self.budget: Dict[tuple, int] = {}
+
+    def reserve(self, grouping: ReplicaGrouping, nbytes: int):
+        k = _key(grouping)
+        self.budget[k] = self.budget.get(k, 0) + int(nbytes) + 512
+
+    def context(self, grouping: ReplicaGrouping) -> GroupContext:
+        k = _key(grouping)
+        if k not in self.groups:
+            base = 256 << 20  # room for fused-GEMM output rings and staging
+            self.groups[k] = GroupContext(self.session, grouping, self.budget.get(k, 0) + base)
+        return self.groups[k]
+
+    def check(self):
+        for ctx in self.groups.values():
+            ctx.check()
+
+
+def runtime(session) -> FusedRuntime:
+    rt = getattr(session, "_fused_runtime", None)
+    if rt is None:
+        rt = FusedRuntime(session)
+        session._fused_runtime = rt
+    return rt
+
+
+# ---- native collectives looked up by the ops -------------------------------------------------------------------------
+
+
+def _lib():
+    from ..ops import native
+
+    return native
+
+
+def matmul_all_reduce(ex, op, a_vals, w_vals):
+    nat = _lib()
+    a, w = a_vals[0], w_vals[0]
+    ctx = runtime(ex).context(op.attrs["group"])
+    if ctx.world == 1:
+        return NotImplemented
+    if not ctx.arena.mc_base or a.dtype not in (torch.bfloat16, torch.float16) or w.shape[-1] % 8:
+        return NotImplemented
+    M, N = a.shape[0], w.shape[-1]
+    out = ctx.arena.ring((M, N), a.dtype)
+    out.zero_()
+    res = nat.gemm(a, w, out=out, accumulate=3, comm=ctx)
+    if res is NotImplemented:
+        return NotImplemented
+    return [out.clone()]
+
+
+def small_all_reduce(ctx: GroupContext, t: torch.Tensor, op: str) -> Optional[torch.Tensor]:
+    """fp32 add / max all-reduce of at most 64 KiB through peer loads (one kernel, two signal rounds)."""
+    nat = _lib()
+    n = t.numel()
+    if t.dtype != torch.float32 or n > _SMALL_ALL_REDUCE_ELEMS or op not in ("add", "max") or ctx.world == 1:
+        return None
+    ctx.stage[:n].copy_(t.reshape(-1))
+    out = torch.empty_like(t)
+    off = ctx.arena.offset_of(ctx.stage) // 4
+    rc = nat._symm_all_reduce(ctx.arena.bases_dev.data_ptr(), ctx.arena.pads_dev.data_ptr(), off, out.data_ptr(), n,
+                              0 if op == "add" else 1, ctx.rank, ctx.world, 2, ctx.err.data_ptr(), nat._stream())
+    nat._check(rc, "symm_all_reduce")
+    nat._count("symm_all_reduce")
+    return out
+
+
+class FusedComm(DistComm):
+    """NCCL transport with small fp32 reductions served by the one-shot NVLink kernel."""
+
+    def __init__(self, num_replicas: int, device: torch.device, session):
+        super().__init__(num_replicas, device)
+        self._session = session
+
+    def all_reduce(self, vals, grouping, op, inplace=False):
+        t = vals[0]
+        if t.dtype == torch.float32 and t.numel() <= _SMALL_ALL_REDUCE_ELEMS and op in ("add", "max") \
+                and grouping.group_size > 1 and t.is_contiguous():
+            ctx = runtime(self._session).context(grouping)
+            out = small_all_reduce(ctx, t, op)
+            if out is not None:
+                if inplace:
+                    t.copy_(out)
+                    return [t]
+                return [out]
+        return super().all_reduce(vals, grouping, op, inplace)
+
+
+def group_barrier(ctx: GroupContext, channel: int = 4):
+    nat = _lib()
+    nat._check(nat._symm_barrier(ctx.arena.pads_dev.data_ptr(), ctx.rank, ctx.world, channel, ctx.err.data_ptr(),
+                                 nat._stream()), "symm_barrier")
+    nat._count("symm_barrier")
+
+
+def rts_adam(ex, op, w_vals, acc_vals, master_vals, m_vals, v_vals, step_vals):
+    """One kernel: reduce-scatter of the gradient accumulators + AdamW on the local shard + all-gather of the new
+    16-bit weights, over peer pointers. Needs the weight and the accumulator in this group's symmetric arena."""
+    nat = _lib()
+    a = op.attrs
+    ctx = runtime(ex).context(a["group"])
+    w, acc, master, m, v, step = w_vals[0], acc_vals[0], master_vals[0], m_vals[0], v_vals[0], step_vals[0]
+    if ctx.world == 1 or ctx.world > 8:
+        return NotImplemented
+    if not (ctx.arena.contains(w) and ctx.arena.contains(acc)):
+        return NotImplemented
+    if w.dtype not in (torch.bfloat16, torch.float16) or acc.dtype != torch.float32 or v.dtype != torch.float32 \
+            or master.dtype != torch.float32 or step.dtype != torch.float32:
+        return NotImplemented
+    shard_n = master.numel()
+    if shard_n % 4 or shard_n * ctx.world != w.numel():
+        return NotImplemented
+    grads = (ctypes.c_void_p * ctx.world)(*ctx.arena.peer_ptrs(acc))
+    weights = (ctypes.c_void_p * ctx.world)(*ctx.arena.peer_ptrs(w))
+    if a["sync_before"]:
+        group_barrier(ctx, 4)
+    rc = nat._rts_adam(grads, weights, nat._CODE[w.dtype], master.data_ptr(), m.data_ptr(), nat._CODE[m.dtype],
+                       v.data_ptr(), step.data_ptr(), ctx.rank * shard_n, shard_n, ctx.world, a["lr"], a["beta1"],
+                       a["beta2"], a["eps"], a["weight_decay"], a["grad_scale"], int(a["bias_correction"]),
+                       nat._stream())
+    if rc == -1:
+        return NotImplemented
+    nat._check(rc, "rts_adam")
+    nat._count("rts_adam")
+    if a["sync_after"]:
+        group_barrier(ctx, 5)
+    return True
+
+
+_TABLE = {"matmul_all_reduce": matmul_all_reduce, "rts_adam": rts_adam}
+
+
+def lookup(name: str, session):
+    return _TABLE.get(name)

@@ -1,0 +1,82 @@
+"""Graph pass: GEMM followed by a tensor-parallel all-reduce becomes one op.
+
+`y = all_reduce(a @ w)` (row-parallel Linear forward, and the data-gradient GEMM of a column-parallel Linear in the
+backward pass) is rewritten to `matmul_all_reduce(a, w)`. On one process per GPU that op runs as a single tcgen05 GEMM
+kernel whose epilogue pushes every finished tile into all ranks' output buffers with `multimem.red.add` through
+NVSwitch, so the reduction overlaps the remaining tiles; elsewhere it runs as matmul + all-reduce.
+"""
+import torch
+
+from .. import xl
+from ..xl.opdef import OPS, OpDef
+
+
+def _special_matmul_all_reduce(ex, op, env):
+    a, w = env[op.inputs[0]], env[op.inputs[1]]
+    native = ex.native_collective("matmul_all_reduce")
+    if native is not None:
+        res = native(ex, op, a, w)
+        if res is not NotImplemented:
+            env[op.outputs[0]] = res
+            return
+    mm = OPS["matmul"]
+    fn = mm.native.get(ex.device.type) if ex.use_native else None
+    outs = []
+    for r in range(ex.num_local):
+        y = fn(a[r], w[r]) if fn is not None else NotImplemented
+        if y is NotImplemented:
+            y = mm.impl(a[r], w[r])
+        outs.append(y)
+    env[op.outputs[0]] = ex.comm.all_reduce(outs, op.attrs["group"], "add", inplace=True)
+
+
+def _vjp_matmul_all_reduce(ctx, op, gs):
+    # forward all-reduce / backward identity, then the ordinary matmul rule
+    from ..xl.ops import matmul, reshape, transpose
+
+    (g,) = gs
+    a, w = op.inputs
+    fa, fw = ctx.fwd(a), ctx.fwd(w)
+    ga = matmul(g, transpose(fw))
+    gw = matmul(transpose(reshape(fa, (-1, a.shape[-1]))), reshape(g, (-1, g.shape[-1])))
+    return [ga, gw]
+
+
+OpDef("matmul_all_reduce", special=_special_matmul_all_reduce, vjp=_vjp_matmul_all_reduce, collective=True,
+      infer=lambda op: [((*op.inputs[0].shape[:-1], op.inputs[1].shape[-1]), op.inputs[0].dtype, ())],
+      flops=lambda op: 2 * op.inputs[0].shape[-1] * op.outputs[0].nelms)
+
+
+def fuse_gemm_collectives(ir: xl.Ir) -> int:
+    """Rewrite `matmul -> all_reduce(add)` pairs (matmul result used by nothing else, 2-D weight) in every graph of
+    `ir`. Returns the number of fused pairs. Run after autodiff and `apply_pre_alias_patterns`."""
+    fused = 0
+    for g in ir.graphs:
+        consumers = {}
+        for op in g.ops:
+            for t in op.inputs:
+                consumers.setdefault(t, []).append(op)
+        new_ops = []
+        skip = set()
+        for op in g.ops:
+            if op.uid in skip:
+                continue
+            if op.opdef.name == "matmul" and op.inputs[1].rank == 2 and op.inputs[0].rank == 2:
+                y = op.outputs[0]
+                users = consumers.get(y, [])
+                if (len(users) == 1 and users[0].opdef.name == "all_reduce" and users[0].attrs["op"] == "add"
+                        and not users[0].attrs.get("identical_inputs") and y not in g._outputs
+                        and users[0].attrs["group"].group_size > 1):
+                    ar = users[0]
+                    op.opdef = OPS["matmul_all_reduce"]
+                    op.name = "matmul_all_reduce"
+                    op.attrs = {"group": ar.attrs["group"]}
+                    # the fused op produces the all-reduce's output tensor
+                    out = ar.outputs[0]
+                    out.producer = op
+                    op.outputs = [out]
+                    skip.add(ar.uid)
+                    fused += 1
+            new_ops.append(op)
+        g.ops = [o for o in new_ops if o.uid not in skip]
+    return fused

@@ -472,6 +472,9 @@ class Variable(Tensor):
         # group across which a replica-sharded variable is split (None: not sharded)
         self.shard_group: Optional[ReplicaGrouping] = shard_group
         self.retrieval_mode = "one_per_group"
+        # replica group whose members may access this variable's storage directly over NVLink (the session then
+        # places it in that group's symmetric-memory arena when it runs one process per GPU)
+        self.symmetric_group: Optional[ReplicaGrouping] = None
 
     @property
     def shape_on_host(self) -> Tuple[int, ...]:

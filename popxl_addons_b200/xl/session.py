@@ -43,16 +43,21 @@ class Session:
             torch.cuda.set_device(self.device)
         self.distributed = bool(ir.distributed) and int(os.environ.get("WORLD_SIZE", "1")) > 1
         self.num_replicas = ir.replication_factor
+        if use_native is None:
+            use_native = os.environ.get("XL_NATIVE", "1") != "0"
         if self.distributed:
-            self.comm = DistComm(self.num_replicas, self.device)
+            if use_native and self.device.type == "cuda":
+                from ..parallel.fused import FusedComm
+
+                self.comm = FusedComm(self.num_replicas, self.device, self)
+            else:
+                self.comm = DistComm(self.num_replicas, self.device)
             self.num_local = 1
             self.replica_offset = self.comm.rank
         else:
             self.comm = SimComm(self.num_replicas)
             self.num_local = self.num_replicas
             self.replica_offset = 0
-        if use_native is None:
-            use_native = os.environ.get("XL_NATIVE", "1") != "0"
         self.use_native = use_native and self.device.type == "cuda"
         if self.use_native:
             from ..ops import native as _native  # noqa: F401  (registers the CUDA kernels; raises if not built)
@@ -127,6 +132,12 @@ class Session:
             if var in self._vars:
                 for r, v in enumerate(vals):
                     self._vars[var][r].copy_(v)
+            elif var.symmetric_group is not None and self.distributed and self.use_native:
+                from ..parallel.fused import runtime
+
+                store = runtime(self).context(var.symmetric_group).arena.alloc(var.shape, var.dtype.as_torch())
+                store.copy_(vals[0])
+                self._vars[var] = [store]
             else:
                 self._vars[var] = [v.to(self.device, copy=True) for v in vals]
 
@@ -134,6 +145,12 @@ class Session:
         for rb in self.ir.remote_buffers:
             self._alloc_buffer(rb)
         deferred = []
+        if self.distributed and self.use_native:
+            from ..parallel.fused import runtime
+
+            for var in self.ir.initial_values:
+                if var.symmetric_group is not None and var.remote_buffer is None:
+                    runtime(self).reserve(var.symmetric_group, var.nelms * var.dtype.itemsize)
         for var, host in self.ir.initial_values.items():
             if isinstance(host, LazyInit) and host.kind == "copy":
                 deferred.append((var, host))  # copies are made once their source exists
@@ -417,4 +434,6 @@ class Session:
             from ..ops import native as _native
 
             _native.check_gemm_errors()
+            if getattr(self, "_fused_runtime", None) is not None:
+                self._fused_runtime.check()
         return out
