@@ -49,8 +49,8 @@ struct GemmParams {
   // all-reduce mode only
   unsigned int* const* pads;  // signal pad of every rank
   int comm_rank, comm_world;
-  unsigned int* local_sync;   // [0] "peers are ready" epoch flag, [1] count of epilogue warps that finished
-  unsigned int epoch;
+  unsigned int* local_sync;   // [0] "peers are ready" flag (set by CTA 0, cleared by the last warp to finish),
+                              // [1] count of epilogue warps that finished
   unsigned int comm_spin_limit;
 };
 
@@ -323,11 +323,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       // the first epilogue warp of CTA 0 runs the cross-rank barrier and publishes the epoch to the other CTAs.
       if (blockIdx.x == 0 && warp == 2) {
         const bool peers_ok = xl_group_barrier(p.pads, p.comm_rank, p.comm_world, 0, p.err, p.comm_spin_limit);
-        if (lane == 0 && peers_ok) xl_st_release_gpu(p.local_sync, p.epoch);
+        if (lane == 0 && peers_ok) xl_st_release_gpu(p.local_sync, 1u);
       }
       bool ready = false;
       for (unsigned int i = 0; i < p.comm_spin_limit && !ready; ++i) {
-        ready = xl_ld_acquire_gpu(p.local_sync) == p.epoch;
+        ready = xl_ld_acquire_gpu(p.local_sync) == 1u;
         if (!ready && (i & 1023u) == 1023u && *abort_flag) break;
       }
       if (!ready) {
@@ -457,7 +457,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       if (lane == 0) prev = atomicAdd(p.local_sync + 1, 1u);
       prev = __shfl_sync(0xffffffffu, prev, 0);
       if (prev == gridDim.x * NUM_EPI_WARPS - 1) {
-        if (lane == 0) p.local_sync[1] = 0;
+        // every epilogue warp of this rank has passed the ready check by now: re-arm both words for the next launch
+        if (lane == 0) { p.local_sync[1] = 0; xl_st_release_gpu(p.local_sync, 0u); }
         xl_group_barrier(p.pads, p.comm_rank, p.comm_world, 1, p.err, p.comm_spin_limit);
       }
     }
@@ -529,15 +530,16 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
 //   err: device int that receives a non-zero code if a bounded wait inside the kernel gave up (may be null).
 //   accumulate == 3 (GEMM fused with an all-reduce over NVSwitch): `c` is the multicast address of an output buffer
 //   that every rank of the group zeroed in stream order before this launch; comm_pads = device array with the signal
-//   pad of every rank, comm_local_sync = two zero-initialised device words of this rank, comm_epoch = a value that
-//   differs from the previous call's. All ranks must launch the same GEMM shape.
+//   pad of every rank, comm_local_sync = two zero-initialised device words of this rank (the kernel leaves them zero).
+//   All ranks must launch the same GEMM shape. No launch argument changes between calls, so the launch can be
+//   captured in a CUDA graph and replayed.
 // Returns 0, a CUDA error code, or a negative value when the arguments are not supported by this kernel.
 XL_API int xl_gemm_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, int batch, int a_mn, int b_mn,
                            long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
                            long long stride_c, int ab_is_fp16, int c_dtype, const void* bias, int bias_dtype, int act,
                            int accumulate, const float* step, float alpha, int* err, int sm_count,
                            const void* comm_pads, int comm_rank, int comm_world, unsigned int* comm_local_sync,
-                           unsigned int comm_epoch, cudaStream_t s) {
+                           cudaStream_t s) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -1;
   if ((((uintptr_t)a) & 15) || (((uintptr_t)b) & 15) || (lda % 8) || (ldb % 8)) return -1;
   if (batch > 1 && ((stride_a % 8) || (stride_b % 8))) return -1;
@@ -557,7 +559,7 @@ XL_API int xl_gemm_tcgen05(const void* a, const void* b, void* c, int M, int N, 
   p.bias = bias; p.bias_dtype = bias_dtype; p.act = act; p.accumulate = accumulate; p.step = step;
   p.alpha = alpha; p.is_fp16 = ab_is_fp16; p.err = err;
   p.pads = (unsigned int* const*)comm_pads; p.comm_rank = comm_rank; p.comm_world = comm_world;
-  p.local_sync = comm_local_sync; p.epoch = comm_epoch; p.comm_spin_limit = xl_host_comm_spin_limit;
+  p.local_sync = comm_local_sync; p.comm_spin_limit = xl_host_comm_spin_limit;
   if (accumulate == 3 && (comm_pads == nullptr || comm_local_sync == nullptr || (N % 8) || c_dtype == XL_F32 ||
                           (ldc % 8) || comm_world > 32))
     return -1;

@@ -41,7 +41,7 @@ class DecoderTrainer:
     def __init__(self, cfg: DecoderConfig, micro_batches: int = 16, micro_batch_size: int = 1, device: str = "auto",
                  seed: int = 0, lr: float = 1e-4, weight_decay: float = 0.01, beta1: float = 0.9, beta2: float = 0.95,
                  eps: float = 1e-5, recompute: bool = True, optimizer_state_dtype: xl.dtype = xl.float32,
-                 shard_optimizer: bool = True, use_native: Optional[bool] = None, fused_collectives: bool = True):
+                 shard_optimizer: bool = True, use_native: Optional[bool] = None, fused_collectives: bool = True, cuda_graphs: bool = True):
         self.cfg = cfg
         self.micro_batches = micro_batches
         self.micro_batch_size = micro_batch_size
@@ -56,6 +56,7 @@ class DecoderTrainer:
         self.state_dtype = optimizer_state_dtype
         self.shard_optimizer = shard_optimizer and cfg.dp > 1
         self.fused_collectives = fused_collectives
+        self.cuda_graphs = cuda_graphs
         t0 = time.perf_counter()
         self._build()
         apply_pre_alias_patterns(self.ir)
@@ -151,7 +152,7 @@ class DecoderTrainer:
             mb_inputs[sin_i], mb_inputs[cos_i] = sin, cos
             if off_i is not None:
                 mb_inputs[off_i] = offset_var
-            ops.repeat(mb, self.micro_batches, inputs_dict=mb_inputs)
+            ops.repeat(mb, self.micro_batches, inputs_dict=mb_inputs, cuda_graph=self.cuda_graphs)
 
             # ---- optimizer -------------------------------------------------------------------------------------
             self.master: Dict[str, xl.Variable] = {}

@@ -70,7 +70,7 @@ _sm_bwd = _sig("xl_attn_softmax_bwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _
 _ce = _sig("xl_ce_fwd_bwd", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p, _c_f, _c_int, _c_p)
 _gemm = _sig("xl_gemm_tcgen05", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll,
              _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_p, _c_int,
-             _c_int, _c_p, ctypes.c_uint, _c_p)
+             _c_int, _c_p, _c_p)
 _symm_barrier = _sig("xl_symm_barrier", _c_p, _c_int, _c_int, _c_int, _c_p, _c_p)
 _symm_all_reduce = _sig("xl_symm_all_reduce", _c_p, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p,
                         _c_p)
@@ -82,9 +82,22 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_RECORDING = []  # stack of lists: kernels launched while a CUDA graph is being captured
+
+
 def _count(name: str):
     LAUNCHES["count"] += 1
     LAUNCHES["by_kernel"][name] = LAUNCHES["by_kernel"].get(name, 0) + 1
+    if _RECORDING:
+        _RECORDING[-1].append(name)
+
+
+def count_replay(names):
+    """Account for the kernels of a captured graph each time it is replayed."""
+    LAUNCHES["count"] += len(names)
+    by = LAUNCHES["by_kernel"]
+    for n in names:
+        by[n] = by.get(n, 0) + 1
 
 
 def _check(rc: int, name: str):
@@ -457,7 +470,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
     if bias is not None and not (bias.is_cuda and bias.is_contiguous() and bias.dtype in _CODE and bias.numel() == N):
         return NotImplemented
     err = gemm_error_flag(a.device)
-    out_ptr, pads, crank, cworld, lsync, epoch = out.data_ptr(), None, 0, 1, None, 0
+    out_ptr, pads, crank, cworld, lsync = out.data_ptr(), None, 0, 1, None
     if accumulate == 3:
         if comm is None or batched:
             return NotImplemented
@@ -465,13 +478,13 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
         if not out_ptr:
             return NotImplemented
         pads, crank, cworld = comm.arena.pads_dev.data_ptr(), comm.rank, comm.world
-        lsync, epoch = comm.arena.local_sync.data_ptr(), comm.arena.next_epoch()
+        lsync = comm.arena.local_sync.data_ptr()
         err = comm.err
     rc = _gemm(a.data_ptr(), b.data_ptr(), out_ptr, M, N, K, batch, a_mn, b_mn, lda, ldb, ldc, sa, sb, stride_c,
                int(a.dtype == torch.float16), _CODE[out.dtype], bias.data_ptr() if bias is not None else None,
                _CODE[bias.dtype] if bias is not None else 0, act, accumulate,
                step.data_ptr() if step is not None else None, float(alpha), err.data_ptr(), _sms(a.device), pads, crank,
-               cworld, lsync, epoch, _stream())
+               cworld, lsync, _stream())
     if rc < 0:
         return NotImplemented
     _check(rc, "gemm_tcgen05")

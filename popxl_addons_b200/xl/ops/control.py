@@ -175,22 +175,24 @@ OpDef("repeat", infer=_infer_call, special=_special_repeat)
 
 def repeat_with_info(graph: Graph, repeat_count: int, *inputs,
                      inputs_dict: Optional[Mapping[Tensor, Tensor]] = None,
-                     check_inputs: bool = True) -> CallSiteInfo:
+                     check_inputs: bool = True, cuda_graph: bool = False) -> CallSiteInfo:
     """Run `graph` `repeat_count` times. Output `i` of one iteration feeds input `i` of the next (loop-carried);
-    the remaining inputs keep their value. Returns the outputs of the last iteration."""
+    the remaining inputs keep their value. Returns the outputs of the last iteration.
+    `cuda_graph=True` (body without outputs, state kept in by-reference inputs, no data-dependent host decisions)
+    lets a CUDA session capture one iteration as a CUDA graph and replay it, removing per-kernel launch overhead."""
     if repeat_count < 0:
         raise ValueError("repeat_count must be >= 0")
     resolved = _resolve_inputs(graph, inputs, inputs_dict)
     if len(graph._outputs) > len(graph._inputs):
         raise ValueError("A repeated graph cannot have more outputs than inputs")
-    outs = emit("repeat", resolved, {"graph": graph, "count": int(repeat_count)},
+    outs = emit("repeat", resolved, {"graph": graph, "count": int(repeat_count), "cuda_graph": bool(cuda_graph)},
                 [t.id.split("/")[-1] for t in graph._outputs])
     return CallSiteInfo(outs[0].producer if outs else gcg().ops[-1])
 
 
-def repeat(graph: Graph, repeat_count: int, *inputs,
-           inputs_dict: Optional[Mapping[Tensor, Tensor]] = None, check_inputs: bool = True) -> Tuple[Tensor, ...]:
-    return repeat_with_info(graph, repeat_count, *inputs, inputs_dict=inputs_dict).outputs
+def repeat(graph: Graph, repeat_count: int, *inputs, inputs_dict: Optional[Mapping[Tensor, Tensor]] = None,
+           check_inputs: bool = True, cuda_graph: bool = False) -> Tuple[Tensor, ...]:
+    return repeat_with_info(graph, repeat_count, *inputs, inputs_dict=inputs_dict, cuda_graph=cuda_graph).outputs
 
 
 # ---- conditional ---------------------------------------------------------------------------------------------

@@ -70,6 +70,9 @@ class Session:
         self._cursor: Dict[HostToDeviceStream, int] = {}
         self._outputs: Dict[DeviceToHostStream, List[List[torch.Tensor]]] = {}
         self.is_attached = False
+        self._captured: Dict[int, dict] = {}
+        self._capture_inputs = None
+        self._capture_outputs = None
         self.h2d_bytes = 0  # host->device / device->host traffic of `run` so far (bytes of the tensors copied)
         self.d2h_bytes = 0
         self.profile: Optional[Dict[str, List[float]]] = None
@@ -261,6 +264,8 @@ class Session:
             self._cursor[stream] = 0
 
     def host_load(self, stream: HostToDeviceStream) -> List[torch.Tensor]:
+        if getattr(self, "_capture_inputs", None) is not None:
+            return [self._capture_inputs[stream]]
         if stream not in self._inputs:
             raise KeyError(f"No input was provided for host stream {stream.name}")
         i = self._cursor[stream]
@@ -272,6 +277,9 @@ class Session:
         return [data[i, r] for r in range(self.num_local)]
 
     def host_store(self, stream: DeviceToHostStream, vals: List[torch.Tensor]):
+        if getattr(self, "_capture_outputs", None) is not None:
+            self._capture_outputs.append((stream, [v.detach().clone() for v in vals]))
+            return
         self._outputs.setdefault(stream, []).append([v.detach().clone() for v in vals])
 
     def _collect_outputs(self, fetch: bool = True) -> Dict[DeviceToHostStream, np.ndarray]:
@@ -409,12 +417,86 @@ class Session:
 
     def run_repeat(self, op, graph: Graph, vals: List[List[torch.Tensor]], env):
         n_out = len(graph._outputs)
+        count = op.attrs["count"]
+        if (op.attrs.get("cuda_graph") and self.device.type == "cuda" and n_out == 0 and self.num_local == 1
+                and os.environ.get("XL_CUDA_GRAPHS", "1") != "0"):
+            self._run_repeat_captured(op, graph, vals, count)
+            return
         outs = vals[:n_out]
-        for _ in range(op.attrs["count"]):
+        for _ in range(count):
             outs = self.run_graph(graph, vals)
             vals = list(outs) + list(vals[n_out:])
         for t, v in zip(op.outputs, outs):
             env[t] = v
+
+    # -- CUDA-graph replay of a loop body -----------------------------------------------------------------------
+    def _run_repeat_captured(self, op, graph: Graph, vals, count: int):
+        """Loop body without loop-carried values, host syncs or shape changes: the first iteration ever runs eagerly
+        (lazy initialisation: arenas, workspaces, library handles), the second is captured into a CUDA graph, all
+        later ones (in this and every following `run`) replay it. Host-stream reads inside the body go through a
+        static staging tensor that is refreshed before each replay; host-stream writes are copied out after it."""
+        state = self._captured.get(op.uid)
+        it = 0
+        if state is None:
+            self.run_graph(graph, vals)  # eager warm-up iteration
+            it = 1
+            if count == 1:
+                return
+            state = self._capture(op, graph, vals)
+            self._captured[op.uid] = state
+            self._after_replay(state)
+            it = 2
+        ptrs = tuple(v[0].data_ptr() for v in vals)
+        if ptrs != state["ptrs"]:
+            raise RuntimeError("inputs of a CUDA-graph-captured loop changed address between runs")
+        from ..ops import native as _native
+
+        for _ in range(it, count):
+            for stream, static in state["static_in"].items():
+                static.copy_(self._next_host_item(stream), non_blocking=True)
+            state["graph"].replay()
+            _native.count_replay(state["kernels"])
+            self._after_replay(state)
+
+    def _next_host_item(self, stream):
+        i = self._cursor[stream]
+        data = self._inputs[stream]
+        if i >= data.shape[0]:
+            raise RuntimeError(f"Stream {stream.name} was read more than num_host_transfers={data.shape[0]} times")
+        self._cursor[stream] = i + 1
+        return data[i, 0]
+
+    def _capture(self, op, graph: Graph, vals):
+        from ..ops import native as _native
+
+        static_in = {}
+        for o in graph.ops:
+            if o.opdef.name == "host_load":
+                st = o.attrs["stream"]
+                static_in[st] = torch.empty_like(self._inputs[st][0, 0])
+        for stream, static in static_in.items():
+            static.copy_(self._next_host_item(stream), non_blocking=True)
+        self._capture_inputs = static_in
+        self._capture_outputs = []
+        kernels: List[str] = []
+        _native._RECORDING.append(kernels)
+        g = torch.cuda.CUDAGraph()
+        torch.cuda.synchronize(self.device)
+        try:
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                self.run_graph(graph, vals)
+        finally:
+            _native._RECORDING.pop()
+            outs = self._capture_outputs
+            self._capture_inputs, self._capture_outputs = None, None
+        g.replay()  # capture records but does not execute
+        _native.count_replay(kernels)
+        return {"graph": g, "static_in": static_in, "outputs": outs, "kernels": kernels,
+                "ptrs": tuple(v[0].data_ptr() for v in vals)}
+
+    def _after_replay(self, state):
+        for stream, tensors in state["outputs"]:
+            self._outputs.setdefault(stream, []).append([t.clone() for t in tensors])
 
     def run(self, inputs: Optional[Mapping[HostToDeviceStream, Any]] = None,
             downcast_inputs: bool = True, fetch: bool = True) -> Dict[DeviceToHostStream, np.ndarray]:
