@@ -94,7 +94,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
     ap.add_argument("--model", default="gptj_6b")
     ap.add_argument("--micro-batches", type=int, default=16)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (diagnostics only; such a run is "
@@ -122,10 +122,47 @@ def main():
     W = max(args.warmup, 3)
     K = args.steps
     t0 = time.perf_counter()
-    trainer = DecoderTrainer(cfg, micro_batches=args.micro_batches, micro_batch_size=1, device="cuda", seed=0,
-                             lr=1e-4)
+    if args.impl == "torch":
+        # PyTorch + cuBLAS + flash SDPA + NCCL implementation of the same step (the number to beat on this machine)
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+        from torch_decoder import TorchTrainer
+
+        class _NoNative:
+            LAUNCHES = {"count": 0, "by_kernel": {}}
+
+            @staticmethod
+            def check_gemm_errors():
+                pass
+
+        native = _NoNative
+        tt = TorchTrainer(cfg, micro_batches=args.micro_batches)
+
+        class _Adapter:
+            tokens_per_step = tt.tokens_per_step
+
+            class session:
+                h2d_bytes = 0
+                d2h_bytes = 0
+
+            def synthetic_tokens(self, seed=0):
+                g = torch.Generator().manual_seed(seed + rank // max(tp, 1))
+                return torch.randint(0, cfg.vocab_size, (args.micro_batches, 1, 1, cfg.seq_len + 1), generator=g,
+                                     dtype=torch.int32).pin_memory()
+
+            def step(self, t):
+                _Adapter.session.h2d_bytes += t.numel() * 4
+                _Adapter.session.d2h_bytes += 4
+                return tt.step(t)
+
+            def step_device(self, t):
+                return tt.step_device(t)
+
+        trainer = _Adapter()
+    else:
+        trainer = DecoderTrainer(cfg, micro_batches=args.micro_batches, micro_batch_size=1, device="cuda", seed=0,
+                                 lr=1e-4)
+        from popxl_addons_b200.ops import native
     setup_s = time.perf_counter() - t0
-    from popxl_addons_b200.ops import native
 
     dist = torch.distributed if world > 1 else None
 
@@ -176,7 +213,7 @@ def main():
     if rank == 0:
         flops_per_token = 6 * cfg.param_count() + 6 * cfg.layers * cfg.seq_len * cfg.heads * cfg.head_dim
         line = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
+            "impl": args.impl, "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
             "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)",
             "config": {"model": f"{args.model} ({cfg.layers} layers, hidden {cfg.hidden}, {cfg.heads} heads x "
