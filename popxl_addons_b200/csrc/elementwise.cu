@@ -837,3 +837,37 @@ XL_API int xl_amax(const void* x, int dtype, float* out_zeroed, long long n, cud
   XL_DISPATCH_DTYPE(dtype, T, { amax_kernel<T><<<grid, 256, 0, s>>>((const T*)x, (unsigned int*)out_zeroed, n); });
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------------------------
+// Allocation-free sum of squares (see xl_noalloc.h). Same two kernels as xl_grad_sumsq, but the per-block partial sums
+// live in a fixed array that is part of the library image instead of caller-provided scratch.
+// ------------------------------------------------------------------------------------------------------------------
+#include "xl_noalloc.h"
+
+static __device__ __align__(256) float xl_noalloc_partials[XL_NOALLOC_SUMSQ_PARTS];
+
+// Device address of the array above, per device. The array's name is only a stand-in in host code, so the address
+// is looked up once per device (with that device current) and cached.
+static float* xl_noalloc_partials_addr[XL_NOALLOC_MAX_DEVICES] = {nullptr};
+
+XL_API int xl_grad_sumsq_noalloc(const void* x, int dtype, const float* scale, float* out, long long n, cudaStream_t s) {
+  if (x == nullptr || out == nullptr || n <= 0) return XL_NOALLOC_BAD_ARGUMENT;
+  if (n > XL_NOALLOC_SUMSQ_MAX_ELEMS) return XL_NOALLOC_TOO_LARGE;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= XL_NOALLOC_MAX_DEVICES) return XL_NOALLOC_BAD_ARGUMENT;
+  if (xl_noalloc_partials_addr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, xl_noalloc_partials);
+    if (e != cudaSuccess) return (int)e;
+    xl_noalloc_partials_addr[dev] = p;
+  }
+  float* partials = xl_noalloc_partials_addr[dev];
+  const int parts = xl_grid_for(n, 256 * 16, XL_NOALLOC_SUMSQ_PARTS);
+  // every one of the `parts` slots is overwritten by its block before the finish kernel reads it: nothing left over
+  // from an earlier call is ever consumed, so the array needs no clearing
+  XL_DISPATCH_DTYPE(dtype, T, { sumsq_partial_kernel<T><<<parts, 256, 0, s>>>((const T*)x, partials, n); });
+  sumsq_finish_kernel<<<1, 256, 0, s>>>(partials, parts, scale, out);
+  return (int)cudaGetLastError();
+}
