@@ -89,6 +89,109 @@ def run_reference(args):
     return 0
 
 
+DECODE_METRIC = "int4 decode tokens/s GPT-J-6B shape, TP over all GPUs (batch 16, prompt 512, 128 new tokens, greedy)"
+
+
+def run_decode(args):
+    """Int4 group-quantised greedy generation: weights N(0, 0.02) quantised in groups of 64 along the input dimension
+    with fp16 scale and bias, bf16 activations and KV cache, tensor parallel over all GPUs. One step = one whole
+    `generate` call (prefill of the prompts + `new_tokens - 1` single-token steps)."""
+    import numpy as np
+    import torch
+
+    from popxl_addons_b200.models.decoder import DecoderConfig
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
+    torch.cuda.set_device(local_rank)
+    cfg = getattr(DecoderConfig, args.model)(tp=args.gpus, dp=1)
+    if args.layers:
+        cfg.layers = args.layers
+    W, K = max(args.warmup, 3), args.steps
+    B, P, N = args.batch, args.prompt_len, args.new_tokens
+    t0 = time.perf_counter()
+    if args.impl == "torch":
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+        from torch_generator import TorchGenerator
+
+        gen = TorchGenerator(cfg, B, P, N, group_size=64, cache_dense=args.torch_dense,
+                             cuda_graph=not args.no_cuda_graphs)
+        launches_of = lambda: 0  # noqa: E731
+        kernels_of = lambda: {}  # noqa: E731
+    else:
+        from popxl_addons_b200.models.generator import DecoderGenerator
+        from popxl_addons_b200.ops import native
+
+        gen = DecoderGenerator(cfg, B, P, N, group_size=64, device="cuda", seed=0, cuda_graphs=not args.no_cuda_graphs)
+        launches_of = lambda: native.LAUNCHES["count"]  # noqa: E731
+        kernels_of = lambda: native.LAUNCHES["by_kernel"]  # noqa: E731
+    setup_s = time.perf_counter() - t0
+    dist = torch.distributed if world > 1 else None
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    rs = np.random.RandomState(0)
+    prompts = [torch.from_numpy(rs.randint(0, cfg.vocab_size, (B, P)).astype(np.int32)).pin_memory() for _ in range(W + K)]
+    for i in range(W):
+        out = gen.generate(prompts[i])
+    launches0 = launches_of()
+    dev_ms = prefill_ms = decode_ms = 0.0
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        t1 = time.perf_counter()
+        for i in range(K):
+            out = gen.generate(prompts[W + i])  # pinned prompt -> device, program, tokens -> host
+            prefill_ms += gen.prefill_ms()
+            decode_ms += gen.decode_ms()
+        barrier()
+        e2e_s = time.perf_counter() - t1
+    dev_ms = prefill_ms + decode_ms  # CUDA events recorded by the program around its two phases
+    launches = launches_of() - launches0
+    times = torch.tensor([dev_ms, e2e_s * 1e3, prefill_ms, decode_ms], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms, prefill_ms, decode_ms = (float(t) for t in times)
+    if args.impl != "torch":
+        native.check_gemm_errors()
+    if rank == 0:
+        toks = B * N * K
+        line = {
+            "impl": args.impl, "metric": DECODE_METRIC, "value": toks / (dev_ms / 1e3), "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16 activations and KV cache, int4 weights (fp16 scales)",
+            "data": "synthetic (uniform random prompt ids, random-init N(0,0.02) weights quantised to int4)",
+            "config": {"model": f"{args.model} ({cfg.layers} layers, hidden {cfg.hidden}, {cfg.heads} heads x "
+                                f"{cfg.head_dim}, ffn {cfg.ffn}, vocab {cfg.vocab_size})",
+                       "global_batch": B, "seq_len": P + N, "prompt_len": P, "new_tokens": N,
+                       "parallelism": f"tp{args.gpus}", "group_size": 64,
+                       "cuda_graphs": not args.no_cuda_graphs,
+                       "torch_weights": ("bf16 copy cached" if args.torch_dense else "int4, de-quantised per call")
+                       if args.impl == "torch" else None,
+                       "l2": "every decoding step streams all int4 weights and the KV cache (several GB in total), "
+                             "beyond the 126 MB L2; no flush needed",
+                       "headline": not args.layers and args.model == "gptj_6b" and (B, P, N) == (16, 512, 128)},
+            "clocks": clocks.summary(),
+            "e2e": {"value": toks / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / K,
+                    "h2d_bytes_per_step": B * P * 4, "d2h_bytes_per_step": B * N * 4},
+            "gpu_launches": int(launches), "kernels": kernels_of(),
+            "prefill_ms": prefill_ms / K, "decode_ms": decode_ms / K,
+            "decode_only_tokens_per_s": B * (N - 1) * K / (decode_ms / 1e3),
+            "ms_per_decode_step": decode_ms / K / (N - 1),
+            "sample_tokens": [int(t) for t in np.asarray(out)[0, :8]], "setup_seconds": setup_s,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -99,9 +202,19 @@ def main():
     ap.add_argument("--micro-batches", type=int, default=16)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (diagnostics only; such a run is "
                                                          "labelled and is not the headline configuration)")
+    ap.add_argument("--mode", default="train", choices=["train", "decode"],
+                    help="train: the training step (default, headline); decode: int4 greedy generation, TP over all GPUs")
+    ap.add_argument("--batch", type=int, default=16, help="decode mode: sequences per batch")
+    ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--new-tokens", type=int, default=128)
+    ap.add_argument("--no-cuda-graphs", action="store_true")
+    ap.add_argument("--torch-dense", action="store_true",
+                    help="decode mode, --impl torch: keep a bf16 copy of every weight instead of de-quantising per call")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.mode == "decode":
+        return run_decode(args)
 
     import torch
 

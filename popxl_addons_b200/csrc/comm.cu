@@ -149,3 +149,42 @@ XL_API int xl_rts_adam(const void* const* grads, void* const* weights, int w_dty
 #undef XL_RTS_LAUNCH
   return (int)cudaGetLastError();
 }
+
+// One-shot all-reduce (add) of a 16-bit vector through the NVLS multicast address: every rank has written its data at
+// the same offset of the symmetric buffer; after a barrier each rank reads the whole vector with multimem.ld_reduce
+// (the switch adds the replicas, fp32 accumulation) into `out`. For the 128 KiB activations of token-by-token decoding:
+// latency-bound, one CTA.
+__global__ void __launch_bounds__(1024)
+    symm_all_reduce_mc_kernel(const void* mc_in, unsigned int* const* pads, uint4* __restrict__ out, int nvec, int bf16,
+                              int rank, int world, int channel, int* err, unsigned int limit) {
+  __shared__ int ok_s;
+  if (threadIdx.x < 32) {
+    const bool ok = xl_group_barrier(pads, rank, world, channel, err, limit);
+    if (threadIdx.x == 0) ok_s = ok;
+  }
+  __syncthreads();
+  if (ok_s) {
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      uint4 v;
+      const char* a = (const char*)mc_in + (size_t)i * 16;
+      if (bf16)
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(a) : "memory");
+      else
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(a) : "memory");
+      out[i] = v;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) xl_group_barrier(pads, rank, world, channel + 1, err, limit);
+}
+
+// nbytes must be a multiple of 16; mc_in = multicast address of the staged input.
+XL_API int xl_symm_all_reduce_mc(const void* mc_in, const void* pads_dev, void* out, long long nbytes, int dtype, int rank,
+                                 int world, int channel, int* err, cudaStream_t s) {
+  if (world > 32 || nbytes <= 0 || (nbytes & 15) || dtype == XL_F32) return -1;
+  symm_all_reduce_mc_kernel<<<1, 1024, 0, s>>>(mc_in, (unsigned int* const*)pads_dev, (uint4*)out, (int)(nbytes / 16),
+                                               dtype == XL_BF16, rank, world, channel, err, xl_host_comm_spin_limit);
+  return (int)cudaGetLastError();
+}

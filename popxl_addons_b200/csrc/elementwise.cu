@@ -597,9 +597,9 @@ XL_API int xl_rotary(const void* x, const void* sin_t, const void* cos_t, void* 
 // int4 group de-quantisation. packed: (rows, groups, gs/4) u16, first element in the top nibble. One thread -> two
 // words -> eight outputs (one 16-byte store for 16-bit outputs).
 // ------------------------------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, typename S>
 __global__ void __launch_bounds__(256)
-    gq_decompress_kernel(const uint16_t* __restrict__ packed, const T* __restrict__ scale, const T* __restrict__ bias,
+    gq_decompress_kernel(const uint16_t* __restrict__ packed, const S* __restrict__ scale, const S* __restrict__ bias,
                          T* __restrict__ out, long long n_pairs, int words_per_group) {
   for (long long p = blockIdx.x * (long long)blockDim.x + threadIdx.x; p < n_pairs; p += (long long)gridDim.x * blockDim.x) {
     const uint32_t two = *reinterpret_cast<const uint32_t*>(packed + 2 * p);
@@ -616,14 +616,18 @@ __global__ void __launch_bounds__(256)
     for (int k = 0; k < 8; ++k) out[8 * p + k] = o[k];
   }
 }
+// `dtype`: type of the output; `scale_dtype`: type of the per-group scale and bias (may differ, e.g. fp16 scales with a
+// bf16 model).
 XL_API int xl_gq_decompress(const void* packed, const void* scale, const void* bias, void* out, long long n_words,
-                            int words_per_group, int dtype, cudaStream_t s) {
+                            int words_per_group, int dtype, int scale_dtype, cudaStream_t s) {
   if ((n_words & 1) || (words_per_group & 1)) return -1;
   const long long pairs = n_words / 2;
   const int grid = xl_grid_for(pairs, 256 * 4);
   XL_DISPATCH_DTYPE(dtype, T, {
-    gq_decompress_kernel<T><<<grid, 256, 0, s>>>((const uint16_t*)packed, (const T*)scale, (const T*)bias, (T*)out, pairs,
-                                                words_per_group);
+    XL_DISPATCH_DTYPE(scale_dtype, S, {
+      gq_decompress_kernel<T, S><<<grid, 256, 0, s>>>((const uint16_t*)packed, (const S*)scale, (const S*)bias, (T*)out,
+                                                     pairs, words_per_group);
+    });
   });
   return (int)cudaGetLastError();
 }

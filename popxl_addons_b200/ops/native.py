@@ -64,13 +64,23 @@ _sumsq_parts = _sig("xl_sumsq_parts", _c_ll)
 _sumsq = _sig("xl_grad_sumsq", _c_p, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_p)
 _rotary = _sig("xl_rotary", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll,
                _c_ll, _c_ll, _c_ll, _c_ll, _c_ll, _c_p)
-_gq = _sig("xl_gq_decompress", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p)
+_gq = _sig("xl_gq_decompress", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p)
 _sm_fwd = _sig("xl_attn_softmax_fwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p)
 _sm_bwd = _sig("xl_attn_softmax_bwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p)
 _ce = _sig("xl_ce_fwd_bwd", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p, _c_f, _c_int, _c_p)
 _gemm = _sig("xl_gemm_tcgen05", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll,
              _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_p, _c_int,
              _c_int, _c_p, _c_p)
+_gq_small = _sig("xl_gq_gemm_small_m", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                 _c_p)
+_rot_append = _sig("xl_rotary_append", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                   _c_p)
+_attn_dec = _sig("xl_attn_decode", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int,
+                 _c_int, _c_p)
+_argmax = _sig("xl_argmax_rows", _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p)
+_advance = _sig("xl_advance_position", _c_p, _c_p)
+_store_row = _sig("xl_store_row", _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_p)
+_symm_all_reduce_mc = _sig("xl_symm_all_reduce_mc", _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p)
 _symm_barrier = _sig("xl_symm_barrier", _c_p, _c_int, _c_int, _c_int, _c_p, _c_p)
 _symm_all_reduce = _sig("xl_symm_all_reduce", _c_p, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p,
                         _c_p)
@@ -387,15 +397,15 @@ def rotary_cuda(x, sin, cos, rotary_dim, inverse):
     return y
 
 
-def gq_decompress_cuda(packed, scale, bias):
+def gq_decompress_cuda(packed, scale, bias, out_dtype=None):
     if not (packed.is_cuda and packed.is_contiguous() and packed.dtype == torch.uint16) or not _ok(scale, bias):
         return NotImplemented
     if scale.dtype != bias.dtype:
         return NotImplemented
     r, g, w = packed.shape
-    out = torch.empty((r, g * w * 4), dtype=scale.dtype, device=packed.device)
-    rc = _gq(packed.data_ptr(), scale.data_ptr(), bias.data_ptr(), out.data_ptr(), packed.numel(), w, _CODE[scale.dtype],
-             _stream())
+    out = torch.empty((r, g * w * 4), dtype=out_dtype or scale.dtype, device=packed.device)
+    rc = _gq(packed.data_ptr(), scale.data_ptr(), bias.data_ptr(), out.data_ptr(), packed.numel(), w, _CODE[out.dtype],
+             _CODE[scale.dtype], _stream())
     if rc == -1:
         return NotImplemented
     _check(rc, "gq_decompress")
@@ -723,6 +733,91 @@ def ce_with_grad_cuda(logits, labels, loss_grad, ignore_index, reduction):
     return loss.to(logits.dtype), dlogits
 
 
+# ---- decoding path -------------------------------------------------------------------------------------------------------
+@native("rotary_kv_append_")
+def rotary_kv_append_cuda(qkv, sin_tab, cos_tab, k_cache, v_cache, pos, n_heads, head_dim, rotary_dim):
+    if not _ok(qkv, k_cache, v_cache) or pos.dtype != torch.int32 or qkv.dtype != k_cache.dtype:
+        return NotImplemented
+    if rotary_dim and not (_ok(sin_tab, cos_tab) and sin_tab.dtype == qkv.dtype):
+        return NotImplemented
+    B = qkv.shape[0]
+    _check(_rot_append(qkv.data_ptr(), sin_tab.data_ptr(), cos_tab.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                       pos.data_ptr(), B, n_heads, head_dim, rotary_dim, k_cache.shape[2], _CODE[qkv.dtype], _stream()),
+           "rotary_append")
+    _count("rotary_append")
+    return qkv
+
+
+@native("attention_decode_packed")
+def attention_decode_packed_cuda(qkv, k_cache, v_cache, pos, n_heads, head_dim, scale):
+    if not _ok(qkv, k_cache, v_cache) or pos.dtype != torch.int32 or head_dim % 32 or head_dim > 256:
+        return NotImplemented
+    B, smax = qkv.shape[0], k_cache.shape[2]
+    splits = 4 if smax > 256 else 1
+    out = torch.empty((B, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    ws = workspace(B * n_heads * splits * (head_dim + 2) * 4, qkv.device, "attn_decode")
+    rc = _attn_dec(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), ws.data_ptr(),
+                   pos.data_ptr(), B, n_heads, head_dim, smax, float(scale), splits, _CODE[qkv.dtype], _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "attn_decode")
+    _count("attn_decode")
+    return out
+
+
+@native("argmax_rows")
+def argmax_rows_cuda(logits, valid, index_offset):
+    if not _ok(logits) or logits.dim() != 2:
+        return NotImplemented
+    rows, V = logits.shape
+    m = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    i = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _check(_argmax(logits.data_ptr(), m.data_ptr(), i.data_ptr(), rows, V, valid, index_offset, _CODE[logits.dtype],
+                   _stream()), "argmax_rows")
+    _count("argmax_rows")
+    return m, i
+
+
+@native("advance_position_")
+def advance_position_cuda(pos):
+    if pos.dtype != torch.int32:
+        return NotImplemented
+    _check(_advance(pos.data_ptr(), _stream()), "advance_position")
+    _count("advance_position")
+    return pos
+
+
+@native("store_row_")
+def store_row_cuda(buf, pos, vals, base):
+    if buf.dtype != torch.int32 or vals.dtype != torch.int32 or pos.dtype != torch.int32 or not buf.is_contiguous():
+        return NotImplemented
+    _check(_store_row(buf.data_ptr(), pos.data_ptr(), base, vals.data_ptr(), vals.numel(), buf.shape[0], _stream()),
+           "store_row")
+    _count("store_row")
+    return buf
+
+
+def gq_gemm_small_m(x, packed, scale, zero, bias):
+    """`x (M<=16, K) @ dequant(packed (N, K/gs, gs/4))^T + bias` with the de-quantisation fused into the GEMM."""
+    M, K = x.shape
+    N, groups, words = packed.shape
+    gs = words * 4
+    if M > 16 or not _ok(x, scale, zero, bias) or x.dtype not in (torch.bfloat16, torch.float16):
+        return NotImplemented
+    if scale.dtype != zero.dtype or scale.dtype not in (torch.bfloat16, torch.float16) or groups * gs != K \
+            or not packed.is_contiguous() or (bias is not None and bias.dtype != x.dtype):
+        return NotImplemented
+    y = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    rc = _gq_small(x.data_ptr(), packed.data_ptr(), scale.data_ptr(), zero.data_ptr(),
+                   bias.data_ptr() if bias is not None else None, y.data_ptr(), M, N, K, gs, _CODE[x.dtype],
+                   _CODE[scale.dtype], _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "gq_gemm_small_m")
+    _count("gq_gemm_small_m")
+    return y
+
+
 # ---- registration of ops defined outside xl.ops ------------------------------------------------------------------------
 def _register_late():
     from . import grad_reduce_square_add as _g, group_quantize_decompress as _q  # noqa: F401  (define the OpDefs)
@@ -733,8 +828,15 @@ def _register_late():
     from ..layers import linear_gq as _lgq  # noqa: F401
 
     def linear_gq_cuda(x, packed, scale, zero, *b, dim):
-        w = gq_decompress_cuda(packed, scale, zero)
-        if w is NotImplemented or x.dtype not in (torch.bfloat16, torch.float16) or w.dtype != x.dtype:
+        x2 = x.reshape(-1, x.shape[-1])
+        if dim == 0 and x2.shape[0] <= 16 and x2.is_contiguous():
+            y = gq_gemm_small_m(x2, packed, scale, zero, b[0] if b else None)
+            if y is not NotImplemented:
+                return y.view(*x.shape[:-1], packed.shape[0])
+        if x.dtype not in (torch.bfloat16, torch.float16):
+            return NotImplemented
+        w = gq_decompress_cuda(packed, scale, zero, out_dtype=x.dtype)
+        if w is NotImplemented:
             return NotImplemented
         wt = w if dim in (-1, 1) else w.t()
         res = gemm(x.reshape(-1, x.shape[-1]), wt, bias=b[0] if b else None)

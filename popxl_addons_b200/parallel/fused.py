@@ -12,6 +12,11 @@ from ..xl.core import ReplicaGrouping
 from .symm import LOCAL_SYNC_OFFSET, SymmArena
 
 _SMALL_ALL_REDUCE_ELEMS = 16384  # fp32 elements served by the one-shot kernel (64 KiB)
+_SMALL_ALL_REDUCE_16BIT_BYTES = 256 << 10  # 16-bit activations served by the one-shot multimem kernel
+
+
+# multimem needs NVLS; tests that lose a rank on purpose switch it off together with NCCL's
+_MC_ALL_REDUCE = os.environ.get("XL_MULTIMEM", "1") != "0"
 
 
 class GroupContext:
@@ -22,7 +27,7 @@ class GroupContext:
         self.pg, self.members = pg, members
         self.arena = SymmArena(nbytes, pg, session.device)
         self.rank, self.world = self.arena.rank, self.arena.world
-        self.stage = self.arena.alloc((_SMALL_ALL_REDUCE_ELEMS,), torch.float32)  # staging for small all-reduces
+        self.stage = self.arena.alloc((_SMALL_ALL_REDUCE_16BIT_BYTES // 4,), torch.float32)  # staging, small all-reduces
         self.err = torch.zeros(1, dtype=torch.int32, device=session.device)
 
     def check(self):
@@ -87,7 +92,7 @@ def matmul_all_reduce(ex, op, a_vals, w_vals):
     ctx = runtime(ex).context(op.attrs["group"])
     if ctx.world == 1:
         return NotImplemented
-    if not ctx.arena.mc_base or a.dtype not in (torch.bfloat16, torch.float16) or w.shape[-1] % 8:
+    if not _MC_ALL_REDUCE or not ctx.arena.mc_base or a.dtype not in (torch.bfloat16, torch.float16) or w.shape[-1] % 8:
         return NotImplemented
     M, N = a.shape[0], w.shape[-1]
     out = ctx.arena.ring((M, N), a.dtype)
@@ -114,8 +119,29 @@ def small_all_reduce(ctx: GroupContext, t: torch.Tensor, op: str) -> Optional[to
     return out
 
 
+def small_all_reduce_16bit(ctx: GroupContext, t: torch.Tensor) -> Optional[torch.Tensor]:
+    """Sum all-reduce of a small bf16/fp16 tensor (decode-step activations): every rank stages its input in symmetric
+    memory and reads the sum of all replicas with `multimem.ld_reduce` (fp32 accumulation inside NVSwitch). One kernel,
+    two signal rounds; no data crosses NVLink twice."""
+    nat = _lib()
+    nbytes = t.numel() * 2
+    if t.dtype not in (torch.bfloat16, torch.float16) or nbytes > _SMALL_ALL_REDUCE_16BIT_BYTES or nbytes % 16 \
+            or ctx.world == 1 or not ctx.arena.mc_base:
+        return None
+    stage = ctx.stage.view(t.dtype)[:t.numel()]
+    stage.copy_(t.reshape(-1))
+    out = torch.empty_like(t)
+    rc = nat._symm_all_reduce_mc(ctx.arena.multicast_ptr(stage), ctx.arena.pads_dev.data_ptr(), out.data_ptr(), nbytes,
+                                 nat._CODE[t.dtype], ctx.rank, ctx.world, 6, ctx.err.data_ptr(), nat._stream())
+    if rc == -1:
+        return None
+    nat._check(rc, "symm_all_reduce_mc")
+    nat._count("symm_all_reduce_mc")
+    return out
+
+
 class FusedComm(DistComm):
-    """NCCL transport with small fp32 reductions served by the one-shot NVLink kernel."""
+    """NCCL transport with small reductions served by the one-shot NVLink kernels."""
 
     def __init__(self, num_replicas: int, device: torch.device, session):
         super().__init__(num_replicas, device)
@@ -127,6 +153,15 @@ class FusedComm(DistComm):
                 and grouping.group_size > 1 and t.is_contiguous():
             ctx = runtime(self._session).context(grouping)
             out = small_all_reduce(ctx, t, op)
+            if out is not None:
+                if inplace:
+                    t.copy_(out)
+                    return [t]
+                return [out]
+        if t.dtype in (torch.bfloat16, torch.float16) and op == "add" and grouping.group_size > 1 \
+                and t.is_contiguous() and t.numel() * 2 <= _SMALL_ALL_REDUCE_16BIT_BYTES and _MC_ALL_REDUCE:
+            ctx = runtime(self._session).context(grouping)
+            out = small_all_reduce_16bit(ctx, t)
             if out is not None:
                 if inplace:
                     t.copy_(out)

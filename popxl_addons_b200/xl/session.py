@@ -70,6 +70,7 @@ class Session:
         self._cursor: Dict[HostToDeviceStream, int] = {}
         self._outputs: Dict[DeviceToHostStream, List[List[torch.Tensor]]] = {}
         self.is_attached = False
+        self.timestamps: Dict[str, Any] = {}
         self._captured: Dict[int, dict] = {}
         self._capture_inputs = None
         self._capture_outputs = None
@@ -327,6 +328,24 @@ class Session:
 
     def device_copy(self, vals, op):
         return vals
+
+    def record_timestamp(self, name: str):
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+        else:
+            import time
+
+            ev = time.perf_counter()
+        self.timestamps[name] = ev
+
+    def elapsed_ms(self, start: str, end: str) -> float:
+        """Device time between two `ops.timestamp` marks of the last run (synchronises)."""
+        a, b = self.timestamps[start], self.timestamps[end]
+        if self.device.type == "cuda":
+            b.synchronize()
+            return a.elapsed_time(b)
+        return (b - a) * 1e3
 
     def native_collective(self, name: str):
         """Fused compute+collective kernel registered under `name` for this session's transport, or None (then the

@@ -1,0 +1,128 @@
+"""Decode-path CUDA kernels against the fp32 PyTorch reference of the same op, and the generation program on the GPU
+(CUDA-graph replay of the decode step) against the same program on the CPU backend."""
+import dataclasses
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def nat():
+    from popxl_addons_b200.ops import native
+
+    return native
+
+
+def _ref(name):
+    from popxl_addons_b200.xl.opdef import OPS
+    import popxl_addons_b200.xl.ops  # noqa: F401
+
+    return OPS[name].impl
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K,gs", [(16, 512, 4096, 64), (1, 1536, 512, 64), (7, 200, 256, 32), (16, 6304, 4096, 64),
+                                      (16, 4096, 2048, 128)])
+def test_gq_gemm_small_m(nat, dtype, M, N, K, gs):
+    from popxl_addons_b200.models.generator import quantize_rows
+
+    torch.manual_seed(0)
+    w = torch.randn(N, K, device="cuda") * 0.05
+    packed, scale, zero = quantize_rows(w, gs)
+    scale, zero = scale.to(dtype), zero.to(dtype)
+    x = (torch.randn(M, K, device="cuda") * 0.5).to(dtype)
+    bias = torch.randn(N, device="cuda").to(dtype)
+    y = nat.gq_gemm_small_m(x, packed, scale, zero, bias)
+    assert y is not NotImplemented
+    p = packed.to(torch.int32) & 0xFFFF
+    codes = torch.stack([(p >> 12) & 15, (p >> 8) & 15, (p >> 4) & 15, p & 15], dim=-1).float().reshape(N, K // gs, gs)
+    deq = (codes * scale.float() + zero.float()).to(dtype).float().reshape(N, K)  # kernel rounds weights to 16 bits
+    want = x.float() @ deq.t() + bias.float()
+    torch.testing.assert_close(y.float(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K / 256))
+    y2 = nat.gq_gemm_small_m(x, packed, scale, zero, None)
+    torch.testing.assert_close(y2.float(), want - bias.float(), rtol=2e-2, atol=2e-2 * math.sqrt(K / 256))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,D,R,S,pos", [(16, 2, 256, 64, 640, 512), (3, 4, 64, 32, 128, 0), (2, 16, 128, 0, 300, 299)])
+def test_rotary_append_and_attention_decode(nat, dtype, B, H, D, R, S, pos):
+    from popxl_addons_b200.ops.rotary_pos_embed import trig_tables
+
+    torch.manual_seed(1)
+    qkv = torch.randn(B, 3 * H * D, device="cuda").to(dtype)
+    k = torch.randn(B, H, S, D, device="cuda").to(dtype)
+    v = torch.randn(B, H, S, D, device="cuda").to(dtype)
+    sin, cos = (torch.tensor(t, device="cuda").to(dtype) for t in trig_tables(S, R or 2))
+    p = torch.tensor(pos, dtype=torch.int32, device="cuda")
+    qkv_r, k_r, v_r = qkv.float(), k.float(), v.float()
+    _ref("rotary_kv_append_")(qkv_r, sin.float(), cos.float(), k_r, v_r, p, H, D, R)
+    out = nat.rotary_kv_append_cuda(qkv, sin, cos, k, v, p, H, D, R)
+    assert out is not NotImplemented
+    tol = dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(qkv.float(), qkv_r, **tol)
+    torch.testing.assert_close(k.float(), k_r, **tol)
+    torch.testing.assert_close(v.float(), v_r, **tol)
+    scale = 1.0 / math.sqrt(D)
+    a = nat.attention_decode_packed_cuda(qkv, k, v, p, H, D, scale)
+    assert a is not NotImplemented
+    want = _ref("attention_decode_packed")(qkv.float(), k.float(), v.float(), p, H, D, scale)
+    torch.testing.assert_close(a.float(), want, **tol)
+
+
+def test_argmax_store_row_advance(nat):
+    torch.manual_seed(2)
+    logits = torch.randn(16, 6300, device="cuda").bfloat16()
+    m, i = nat.argmax_rows_cuda(logits, 6000, 100)
+    rm, ri = logits[:, :6000].float().max(dim=-1)
+    torch.testing.assert_close(m, rm)
+    # ties between equal bf16 values may resolve to different columns: compare the values at the chosen columns
+    torch.testing.assert_close(logits.float().gather(1, (i - 100).long()[:, None])[:, 0], rm)
+    pos = torch.tensor(5, dtype=torch.int32, device="cuda")
+    buf = torch.zeros(4, 16, dtype=torch.int32, device="cuda")
+    nat.advance_position_cuda(pos)
+    assert int(pos) == 6
+    nat.store_row_cuda(buf, pos, i, 4)
+    assert torch.equal(buf[2], i) and int(buf[0].abs().sum()) == 0
+    nat.store_row_cuda(buf, pos, i, 7)  # row -1: ignored
+    nat.store_row_cuda(buf, pos, i, 0)  # row 6: ignored
+    assert int((buf != 0).any(dim=1).sum()) == 1
+
+
+@pytest.mark.parametrize("cuda_graphs", [False, True])
+def test_generation_on_gpu_matches_cpu_backend(cuda_graphs):
+    from popxl_addons_b200.models.decoder import DecoderConfig
+    from popxl_addons_b200.models.generator import DecoderGenerator
+    from popxl_addons_b200.ops import native
+
+    cfg = dataclasses.replace(DecoderConfig.tiny(tp=1, dp=1), dtype="bfloat16", hidden=256, heads=4, head_dim=64,
+                              rotary_dim=32, ffn=512, vocab_size=1000)
+    B, P, N, gs = 4, 16, 8, 64
+    rs = np.random.RandomState(0)
+    hd = cfg.heads * cfg.head_dim
+    w = {"wte": rs.normal(0, 1.0, (cfg.vocab_size, cfg.hidden)), "lm_head": rs.normal(0, 0.5, (cfg.vocab_size, cfg.hidden))}
+    for l in range(cfg.layers):
+        w[f"layer{l}.qkv"] = rs.normal(0, 0.1, (3 * hd, cfg.hidden))
+        w[f"layer{l}.out"] = rs.normal(0, 0.1, (cfg.hidden, hd))
+        w[f"layer{l}.fc_in"] = rs.normal(0, 0.1, (cfg.ffn, cfg.hidden))
+        w[f"layer{l}.fc_out"] = rs.normal(0, 0.1, (cfg.hidden, cfg.ffn))
+    prompt = rs.randint(0, cfg.vocab_size, (B, P)).astype(np.int32)
+    cpu = DecoderGenerator(cfg, B, P, N, gs, device="cpu", cuda_graphs=False)
+    cpu.load_dense(w)
+    want = cpu.generate(prompt)
+    before = dict(native.LAUNCHES)
+    gpu = DecoderGenerator(cfg, B, P, N, gs, device="cuda", cuda_graphs=cuda_graphs)
+    gpu.load_dense(w)
+    got = gpu.generate(prompt)
+    got2 = gpu.generate(prompt)
+    np.testing.assert_array_equal(got, got2)
+    # bf16 accumulation order differs between the backends; greedy paths may part after a near-tie. Require that the
+    # first tokens agree everywhere and that most sequences agree completely.
+    np.testing.assert_array_equal(got[:, 0], want[:, 0])
+    assert (got == want).all(axis=1).mean() >= 0.5
+    for k in ("gq_gemm_small_m", "attn_decode", "rotary_append", "argmax_rows"):
+        assert native.LAUNCHES.get(k, 0) > before.get(k, 0), f"{k} kernel did not run"
+    assert gpu.decode_ms() > 0
