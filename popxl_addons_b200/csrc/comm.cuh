@@ -86,6 +86,17 @@ __device__ __forceinline__ void xl_multimem_red_add_f16x8(void* mc_addr, uint4 v
                "r"(v.z), "r"(v.w)
                : "memory");
 }
+// vector reduction into one (possibly remote) address: used when each row has a single owner (reduce-scatter)
+__device__ __forceinline__ void xl_red_add_bf16x8(void* addr, uint4 v) {
+  asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void xl_red_add_f16x8(void* addr, uint4 v) {
+  asm volatile("red.relaxed.sys.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
 __device__ __forceinline__ void xl_multimem_red_add_f32x4(void* mc_addr, float4 v) {
   asm volatile("multimem.red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "f"(v.x), "f"(v.y),
                "f"(v.z), "f"(v.w)

@@ -49,56 +49,70 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
 // packed: (N, K/gs, gs/4) u16, first element of a word in its top nibble; scale / zero: (N, K/gs).
 // Any assignment of actual k indices to the 16 k-slots of an MMA is valid as long as A and B agree, so each lane
 // keeps the 32 consecutive k values of its 16-byte weight load and feeds them to 8 MMAs, 4 values at a time.
+//
+// Grid (ceil(N / 32), ksplit). The warps of a CTA split the CTA's K range in chunks of 128 and reduce through shared
+// memory. With ksplit > 1 the CTAs of one column tile add their partial sums into an fp32 workspace tile; the last one
+// to arrive (a counter per tile) applies the epilogue, writes y and leaves workspace and counter zeroed for the next
+// launch. Epilogue: + bias, GELU on the columns >= act_from_col. x and y are windows of wider matrices (ldx, ldy).
 template <typename T, typename S>
-__global__ void __launch_bounds__(GQ_WARPS * 32)
+__global__ void __launch_bounds__(GQ_WARPS * 32, 3)
     gq_gemm_small_m_kernel(const T* __restrict__ x, const uint16_t* __restrict__ packed, const S* __restrict__ scale,
                            const S* __restrict__ zero, const T* __restrict__ bias, T* __restrict__ y, int M, int N, int K,
-                           int group_size) {
+                           int group_size, long long ldx, long long ldy, int act_from_col, float* __restrict__ ws,
+                           unsigned int* __restrict__ counters) {
   __shared__ float red[GQ_WARPS][16][8 * GQ_NT + 1];
+  __shared__ unsigned int is_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int quad = lane >> 2, j = lane & 3;  // quad: row of A / column of B inside a tile; j: k sub-slot
   const int n_base = blockIdx.x * (8 * GQ_NT);
   const int groups = K / group_size;
+  const int ksplit = gridDim.y;
   constexpr bool BF = std::is_same<T, __nv_bfloat16>::value;
   float c[GQ_NT][4];
 #pragma unroll
   for (int t = 0; t < GQ_NT; ++t)
 #pragma unroll
     for (int e = 0; e < 4; ++e) c[t][e] = 0.f;
-  const int k_per_warp = (K / GQ_KCHUNK + GQ_WARPS - 1) / GQ_WARPS * GQ_KCHUNK;
-  const int k_begin = warp * k_per_warp;
-  const int k_end = min(K, k_begin + k_per_warp);
+  const int chunks = K / GQ_KCHUNK;
+  const int chunk_begin = (int)((long long)chunks * blockIdx.y / ksplit);
+  const int chunk_end = (int)((long long)chunks * (blockIdx.y + 1) / ksplit);
   const bool row_lo = quad < M, row_hi = quad + 8 < M;
-  for (int k0 = k_begin; k0 < k_end; k0 += GQ_KCHUNK) {
-    const int k_lane = k0 + j * 32;  // this lane's 32 consecutive k values
-    // activations: rows quad and quad+8, 32 values each
-    uint4 xa[4], xb[4];
-    const uint4 zero4 = make_uint4(0, 0, 0, 0);
-#pragma unroll
-    for (int v = 0; v < 4; ++v) {
-      xa[v] = row_lo ? *reinterpret_cast<const uint4*>(x + (long long)quad * K + k_lane + v * 8) : zero4;
-      xb[v] = row_hi ? *reinterpret_cast<const uint4*>(x + (long long)(quad + 8) * K + k_lane + v * 8) : zero4;
-    }
-    const uint32_t* xa32 = reinterpret_cast<const uint32_t*>(xa);
-    const uint32_t* xb32 = reinterpret_cast<const uint32_t*>(xb);
+  for (int ch = chunk_begin + warp; ch < chunk_end; ch += GQ_WARPS) {
+    const int k_lane = ch * GQ_KCHUNK + j * 32;  // this lane's 32 consecutive k values
+    // weights first (the long-latency loads), then the activations: rows quad and quad+8, 32 values each
+    uint4 wq[GQ_NT];
+    float sc[GQ_NT], zp[GQ_NT];
     const int g = k_lane / group_size;
 #pragma unroll
     for (int t = 0; t < GQ_NT; ++t) {
       const int n = n_base + t * 8 + quad;
-      uint4 wq = make_uint4(0, 0, 0, 0);
-      float sc = 0.f, zp = 0.f;
+      wq[t] = make_uint4(0, 0, 0, 0);
+      sc[t] = 0.f;
+      zp[t] = 0.f;
       if (n < N) {
-        wq = *reinterpret_cast<const uint4*>(packed + (long long)n * (K / 4) + k_lane / 4);
-        sc = xl_to_float(scale[(long long)n * groups + g]);
-        zp = xl_to_float(zero[(long long)n * groups + g]);
+        wq[t] = *reinterpret_cast<const uint4*>(packed + (long long)n * (K / 4) + k_lane / 4);
+        sc[t] = xl_to_float(scale[(long long)n * groups + g]);
+        zp[t] = xl_to_float(zero[(long long)n * groups + g]);
       }
-      const uint16_t* w16 = reinterpret_cast<const uint16_t*>(&wq);
+    }
+    uint4 xa[4], xb[4];
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      xa[v] = row_lo ? *reinterpret_cast<const uint4*>(x + (long long)quad * ldx + k_lane + v * 8) : zero4;
+      xb[v] = row_hi ? *reinterpret_cast<const uint4*>(x + (long long)(quad + 8) * ldx + k_lane + v * 8) : zero4;
+    }
+    const uint32_t* xa32 = reinterpret_cast<const uint32_t*>(xa);
+    const uint32_t* xb32 = reinterpret_cast<const uint32_t*>(xb);
+#pragma unroll
+    for (int t = 0; t < GQ_NT; ++t) {
+      const uint16_t* w16 = reinterpret_cast<const uint16_t*>(&wq[t]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         // word i holds k_lane + 4i .. 4i+3
         const uint32_t w = w16[i];
-        const float v0 = (float)((w >> 12) & 0xF) * sc + zp, v1 = (float)((w >> 8) & 0xF) * sc + zp;
-        const float v2 = (float)((w >> 4) & 0xF) * sc + zp, v3 = (float)(w & 0xF) * sc + zp;
+        const float v0 = (float)((w >> 12) & 0xF) * sc[t] + zp[t], v1 = (float)((w >> 8) & 0xF) * sc[t] + zp[t];
+        const float v2 = (float)((w >> 4) & 0xF) * sc[t] + zp[t], v3 = (float)(w & 0xF) * sc[t] + zp[t];
         const uint32_t b[2] = {pack2<T>(v0, v1), pack2<T>(v2, v3)};
         const uint32_t a[4] = {xa32[2 * i], xb32[2 * i], xa32[2 * i + 1], xb32[2 * i + 1]};
         mma_m16n8k16(c[t], a, b, BF);
@@ -114,217 +128,372 @@ __global__ void __launch_bounds__(GQ_WARPS * 32)
     red[warp][quad + 8][t * 8 + 2 * j + 1] = c[t][3];
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < 16 * 8 * GQ_NT; idx += blockDim.x) {
+  constexpr int TILE = 16 * 8 * GQ_NT;
+  float* wtile = ws + (long long)blockIdx.x * TILE;
+  if (ksplit > 1) {
+    for (int idx = threadIdx.x; idx < TILE; idx += blockDim.x) {
+      const int r = idx / (8 * GQ_NT), col = idx % (8 * GQ_NT);
+      if (r < M && n_base + col < N) {
+        float acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < GQ_WARPS; ++w) acc += red[w][r][col];
+        atomicAdd(wtile + idx, acc);
+      }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(counters + blockIdx.x, 1u) == (unsigned int)ksplit - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+  }
+  for (int idx = threadIdx.x; idx < TILE; idx += blockDim.x) {
     const int r = idx / (8 * GQ_NT), col = idx % (8 * GQ_NT);
     const int n = n_base + col;
     if (r < M && n < N) {
       float acc = 0.f;
+      if (ksplit > 1) {
+        acc = __ldcg(wtile + idx);
+        wtile[idx] = 0.f;
+      } else {
 #pragma unroll
-      for (int w = 0; w < GQ_WARPS; ++w) acc += red[w][r][col];
+        for (int w = 0; w < GQ_WARPS; ++w) acc += red[w][r][col];
+      }
       if (bias) acc += xl_to_float(bias[n]);
-      y[(long long)r * N + n] = xl_from_float<T>(acc);
+      if (n >= act_from_col) acc = 0.5f * acc * (1.f + erff(acc * 0.70710678118654752f));
+      y[(long long)r * ldy + n] = xl_from_float<T>(acc);
     }
   }
+  if (ksplit > 1 && threadIdx.x == 0) counters[blockIdx.x] = 0;
 }
 
-// Requirements: M <= 16, K % 128 == 0, group_size % 32 == 0, 16-byte aligned pointers. Returns -1 otherwise.
+// Requirements: M <= 16, K % 128 == 0, group_size % 32 == 0, 16-byte aligned x rows and weight rows. `ws` / `counters`:
+// zero-initialised scratch of at least ceil(N/32)*512 floats / ceil(N/32) words, needed when ksplit > 1 (the kernel
+// leaves them zeroed). act_from_col: first column that gets GELU (>= N: none). Returns -1 for unsupported arguments.
 template <typename T>
 static void gq_small_launch(const void* x, const void* packed, const void* scale, const void* zero, const void* bias, void* y,
-                            int M, int N, int K, int group_size, int scale_dtype, int grid, cudaStream_t s) {
+                            int M, int N, int K, int group_size, long long ldx, long long ldy, int act_from_col,
+                            float* ws, unsigned int* counters, int scale_dtype, dim3 grid, cudaStream_t s) {
   if (scale_dtype == XL_F16)
-    gq_gemm_small_m_kernel<T, __half><<<grid, GQ_WARPS * 32, 0, s>>>((const T*)x, (const uint16_t*)packed,
-                                                                     (const __half*)scale, (const __half*)zero,
-                                                                     (const T*)bias, (T*)y, M, N, K, group_size);
+    gq_gemm_small_m_kernel<T, __half><<<grid, GQ_WARPS * 32, 0, s>>>(
+        (const T*)x, (const uint16_t*)packed, (const __half*)scale, (const __half*)zero, (const T*)bias, (T*)y, M, N, K,
+        group_size, ldx, ldy, act_from_col, ws, counters);
   else
     gq_gemm_small_m_kernel<T, __nv_bfloat16><<<grid, GQ_WARPS * 32, 0, s>>>(
         (const T*)x, (const uint16_t*)packed, (const __nv_bfloat16*)scale, (const __nv_bfloat16*)zero, (const T*)bias,
-        (T*)y, M, N, K, group_size);
+        (T*)y, M, N, K, group_size, ldx, ldy, act_from_col, ws, counters);
 }
 // `dtype`: type of x, bias and y (fp16 or bf16); `scale_dtype`: type of the per-group scale and zero point (fp16 / bf16).
 XL_API int xl_gq_gemm_small_m(const void* x, const void* packed, const void* scale, const void* zero, const void* bias,
-                              void* y, int M, int N, int K, int group_size, int dtype, int scale_dtype, cudaStream_t s) {
+                              void* y, int M, int N, int K, int group_size, long long ldx, long long ldy, int act_from_col,
+                              int ksplit, float* ws, unsigned int* counters, int dtype, int scale_dtype, cudaStream_t s) {
   if (M < 1 || M > 16 || K % GQ_KCHUNK || group_size % 32 || K % group_size || dtype == XL_F32 || scale_dtype == XL_F32)
     return -1;
-  const int grid = (N + 8 * GQ_NT - 1) / (8 * GQ_NT);
+  if ((ldx % 8) || ksplit < 1 || ksplit > K / GQ_KCHUNK || (ksplit > 1 && (ws == nullptr || counters == nullptr))) return -1;
+  const dim3 grid((N + 8 * GQ_NT - 1) / (8 * GQ_NT), ksplit);
   if (dtype == XL_BF16)
-    gq_small_launch<__nv_bfloat16>(x, packed, scale, zero, bias, y, M, N, K, group_size, scale_dtype, grid, s);
+    gq_small_launch<__nv_bfloat16>(x, packed, scale, zero, bias, y, M, N, K, group_size, ldx, ldy, act_from_col, ws,
+                                   counters, scale_dtype, grid, s);
   else
-    gq_small_launch<__half>(x, packed, scale, zero, bias, y, M, N, K, group_size, scale_dtype, grid, s);
+    gq_small_launch<__half>(x, packed, scale, zero, bias, y, M, N, K, group_size, ldx, ldy, act_from_col, ws, counters,
+                            scale_dtype, grid, s);
   return (int)cudaGetLastError();
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// Rotary at a device-side position + KV-cache append.
-// qkv: (B, 3*H*D) new-token projections [q | k | v]; rotates q and k in place (first R features of each head) for
-// position pos = *pos_ptr and copies k, v into the caches (B, H, Smax, D) at that position.
-// sin / cos tables: (Smax, R/2).
+// Rotary at a device-side position + KV-cache append, one launch.
+// qkv: rows of `ld` elements whose first 3*H*D hold the new-token projections [q | k | v]; rotates q and k in place
+// (first R features of each head, interleaved pairs) for position pos = *pos_ptr and writes k, v into the caches
+// (B, H, Smax, D) at that position. sin / cos tables: (Smax, R/2). One thread per (b, h, feature pair).
 // ------------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256)
-    rotary_append_kernel(T* __restrict__ qkv, const T* __restrict__ sin_t, const T* __restrict__ cos_t,
+    rotary_append_kernel(T* __restrict__ qkv, long long ld, const T* __restrict__ sin_t, const T* __restrict__ cos_t,
                          T* __restrict__ k_cache, T* __restrict__ v_cache, const int* __restrict__ pos_ptr, int B, int H,
                          int D, int R, int Smax) {
   const int pos = *pos_ptr;
-  const int hd = H * D;
-  const long long total = (long long)B * hd;  // one thread per (b, h, d) feature of k / v, pairs handled by even d
+  if (pos < 0 || pos >= Smax) return;
+  const int hd = H * D, half = D / 2;
+  const long long total = (long long)B * H * half;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int d = (int)(i % D);
-    const int h = (int)((i / D) % H);
-    const int b = (int)(i / hd);
-    T* q = qkv + (long long)b * 3 * hd + h * D;
+    const int d = 2 * (int)(i % half);
+    const int h = (int)((i / half) % H);
+    const int b = (int)(i / ((long long)half * H));
+    T* q = qkv + (long long)b * ld + h * D + d;
     T* k = q + hd;
     const T* v = q + 2 * hd;
-    if (d < R && (d & 1) == 0) {
+    float k0 = xl_to_float(k[0]), k1 = xl_to_float(k[1]);
+    if (d < R) {
       const float sn = xl_to_float(sin_t[(long long)pos * (R / 2) + d / 2]);
       const float cs = xl_to_float(cos_t[(long long)pos * (R / 2) + d / 2]);
-      const float q0 = xl_to_float(q[d]), q1 = xl_to_float(q[d + 1]);
-      q[d] = xl_from_float<T>(q0 * cs - q1 * sn);
-      q[d + 1] = xl_from_float<T>(q1 * cs + q0 * sn);
-      const float k0 = xl_to_float(k[d]), k1 = xl_to_float(k[d + 1]);
-      const T r0 = xl_from_float<T>(k0 * cs - k1 * sn), r1 = xl_from_float<T>(k1 * cs + k0 * sn);
-      k[d] = r0;
-      k[d + 1] = r1;
+      const float q0 = xl_to_float(q[0]), q1 = xl_to_float(q[1]);
+      q[0] = xl_from_float<T>(q0 * cs - q1 * sn);
+      q[1] = xl_from_float<T>(q1 * cs + q0 * sn);
+      const float r0 = k0 * cs - k1 * sn, r1 = k1 * cs + k0 * sn;
+      k0 = r0;
+      k1 = r1;
+      k[0] = xl_from_float<T>(k0);
+      k[1] = xl_from_float<T>(k1);
     }
-  }
-  // second pass (after the rotation of this thread's own pairs is visible to itself only): copy is done by a separate
-  // kernel launch below to avoid intra-kernel ordering between threads
-}
-
-template <typename T>
-__global__ void __launch_bounds__(256)
-    kv_append_kernel(const T* __restrict__ qkv, T* __restrict__ k_cache, T* __restrict__ v_cache,
-                     const int* __restrict__ pos_ptr, int B, int H, int D, int Smax) {
-  const int pos = *pos_ptr;
-  const int hd = H * D;
-  const long long total = (long long)B * hd;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    const int d = (int)(i % D);
-    const int h = (int)((i / D) % H);
-    const int b = (int)(i / hd);
-    const long long src = (long long)b * 3 * hd + h * D + d;
     const long long dst = (((long long)b * H + h) * Smax + pos) * D + d;
-    k_cache[dst] = qkv[src + hd];
-    v_cache[dst] = qkv[src + 2 * hd];
+    k_cache[dst] = xl_from_float<T>(k0);
+    k_cache[dst + 1] = xl_from_float<T>(k1);
+    v_cache[dst] = v[0];
+    v_cache[dst + 1] = v[1];
   }
 }
 
-XL_API int xl_rotary_append(void* qkv, const void* sin_t, const void* cos_t, void* k_cache, void* v_cache,
+XL_API int xl_rotary_append(void* qkv, long long ld, const void* sin_t, const void* cos_t, void* k_cache, void* v_cache,
                             const int* pos_ptr, int B, int H, int D, int R, int Smax, int dtype, cudaStream_t s) {
-  const long long total = (long long)B * H * D;
+  if ((D & 1) || (R & 1) || R > D) return -1;
+  const long long total = (long long)B * H * (D / 2);
   const int grid = xl_grid_for(total, 256);
   XL_DISPATCH_DTYPE(dtype, T, {
-    if (R > 0)
-      rotary_append_kernel<T><<<grid, 256, 0, s>>>((T*)qkv, (const T*)sin_t, (const T*)cos_t, (T*)k_cache, (T*)v_cache,
-                                                   pos_ptr, B, H, D, R, Smax);
-    kv_append_kernel<T><<<grid, 256, 0, s>>>((const T*)qkv, (T*)k_cache, (T*)v_cache, pos_ptr, B, H, D, Smax);
+    rotary_append_kernel<T><<<grid, 256, 0, s>>>((T*)qkv, ld, (const T*)sin_t, (const T*)cos_t, (T*)k_cache, (T*)v_cache,
+                                                 pos_ptr, B, H, D, R, Smax);
   });
   return (int)cudaGetLastError();
 }
 
 // ------------------------------------------------------------------------------------------------------------------
-// Decode attention: one query per (b, h) against cache positions [0, len), len = *pos_ptr + 1.
-// Grid (B*H, splits): each CTA covers a slice of the positions with an online softmax (one warp per position at a
-// time, lanes over the head dimension) and writes (max, sum, unnormalised output); the combine kernel merges the splits.
+// Decode attention: one query per (b, h) against cache positions [0, len), len = *pos_ptr + 1, one launch.
+// Grid (B*H, splits): each CTA covers a slice of the positions with an online softmax. A warp takes four positions per
+// iteration (lanes over the head dimension, one vector load of D/32 values per lane, position and tensor), so eight
+// independent loads are in flight per lane. Each CTA writes (max, sum, unnormalised output) of its slice; the last CTA
+// of a (b, h) to finish (a counter per (b, h), left at zero again) merges the slices and writes the output row.
 // ------------------------------------------------------------------------------------------------------------------
 constexpr int AD_WARPS = 4;
 constexpr int AD_MAX_D = 256;  // head_dim <= 256 (8 values per lane)
+constexpr int AD_UNROLL = 4;
 
-template <typename T>
+template <typename T, int VPL>
+struct alignas(VPL * 2 >= 16 ? 16 : (VPL == 4 ? 8 : (VPL == 2 ? 4 : 2))) AdVec {
+  T v[VPL];
+};
+
+template <typename T, int VPL>
 __global__ void __launch_bounds__(AD_WARPS * 32)
-    attn_decode_split_kernel(const T* __restrict__ qkv, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
-                             float* __restrict__ part, const int* __restrict__ pos_ptr, int H, int D, int Smax,
-                             float scale, int splits) {
-  const int bh = blockIdx.x, split = blockIdx.y;
+    attn_decode_kernel(const T* __restrict__ qkv, long long ldq, const T* __restrict__ k_cache,
+                       const T* __restrict__ v_cache, T* __restrict__ out, long long ldo, float* __restrict__ part,
+                       unsigned int* __restrict__ counters, const int* __restrict__ pos_ptr, int H, int Smax, float scale) {
+  constexpr int D = VPL * 32;
+  using Vec = AdVec<T, VPL>;
+  const int bh = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
   const int b = bh / H, h = bh % H;
-  const int len = *pos_ptr + 1;
+  const int len = min(*pos_ptr + 1, Smax);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int per = (len + splits - 1) / splits;
   const int s_begin = split * per, s_end = min(len, s_begin + per);
-  const int VPL = D / 32;  // values per lane (D multiple of 32, <= 8)
-  float q[8], o[8];
-  const T* qp = qkv + (long long)b * 3 * H * D + h * D;
+  float q[VPL], o[VPL];
+  {
+    const Vec qv = *reinterpret_cast<const Vec*>(qkv + (long long)b * ldq + h * D + lane * VPL);
 #pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    q[e] = (e < VPL) ? xl_to_float(qp[lane * VPL + e]) * scale : 0.f;
-    o[e] = 0.f;
+    for (int e = 0; e < VPL; ++e) {
+      q[e] = xl_to_float(qv.v[e]) * scale;
+      o[e] = 0.f;
+    }
   }
   float m = -INFINITY, l = 0.f;
-  const T* kb = k_cache + ((long long)bh * Smax) * D;
-  const T* vb = v_cache + ((long long)bh * Smax) * D;
-  for (int sidx = s_begin + warp; sidx < s_end; sidx += AD_WARPS) {
-    float dot = 0.f;
+  const T* kb = k_cache + ((long long)bh * Smax) * D + lane * VPL;
+  const T* vb = v_cache + ((long long)bh * Smax) * D + lane * VPL;
+  for (int s0 = s_begin + warp * AD_UNROLL; s0 < s_end; s0 += AD_WARPS * AD_UNROLL) {
+    Vec kk[AD_UNROLL], vv[AD_UNROLL];
 #pragma unroll
-    for (int e = 0; e < 8; ++e)
-      if (e < VPL) dot += q[e] * xl_to_float(kb[(long long)sidx * D + lane * VPL + e]);
-    dot = xl_warp_sum(dot);
-    const float m_new = fmaxf(m, dot);
-    const float corr = __expf(m - m_new), p = __expf(dot - m_new);
-    l = l * corr + p;
+    for (int u = 0; u < AD_UNROLL; ++u) {
+      const int sidx = min(s0 + u, s_end - 1);  // clamped: the duplicates are masked out below
+      kk[u] = *reinterpret_cast<const Vec*>(kb + (long long)sidx * D);
+      vv[u] = *reinterpret_cast<const Vec*>(vb + (long long)sidx * D);
+    }
+    float dot[AD_UNROLL];
 #pragma unroll
-    for (int e = 0; e < 8; ++e)
-      if (e < VPL) o[e] = o[e] * corr + p * xl_to_float(vb[(long long)sidx * D + lane * VPL + e]);
+    for (int u = 0; u < AD_UNROLL; ++u) {
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < VPL; ++e) d += q[e] * xl_to_float(kk[u].v[e]);
+      dot[u] = d;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+      for (int u = 0; u < AD_UNROLL; ++u) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], off);
+    }
+    float m_new = m;
+#pragma unroll
+    for (int u = 0; u < AD_UNROLL; ++u) {
+      if (s0 + u >= s_end) dot[u] = -INFINITY;
+      m_new = fmaxf(m_new, dot[u]);
+    }
+    const float corr = __expf(m - m_new);  // m_new is finite here: position s0 is valid
+    l *= corr;
+#pragma unroll
+    for (int e = 0; e < VPL; ++e) o[e] *= corr;
+#pragma unroll
+    for (int u = 0; u < AD_UNROLL; ++u) {
+      const float p = __expf(dot[u] - m_new);  // exp(-inf) = 0 for the masked duplicates
+      l += p;
+#pragma unroll
+      for (int e = 0; e < VPL; ++e) o[e] += p * xl_to_float(vv[u].v[e]);
+    }
     m = m_new;
   }
   // merge the warps of this CTA
   __shared__ float sm[AD_WARPS], sl[AD_WARPS], so[AD_WARPS][AD_MAX_D];
+  __shared__ unsigned int is_last;
   if (lane == 0) { sm[warp] = m; sl[warp] = l; }
 #pragma unroll
-  for (int e = 0; e < 8; ++e)
-    if (e < VPL) so[warp][lane * VPL + e] = o[e];
+  for (int e = 0; e < VPL; ++e) so[warp][lane * VPL + e] = o[e];
   __syncthreads();
+  float* mine = part + ((long long)bh * splits + split) * (D + 2);
   if (warp == 0) {
     float mm = -INFINITY;
     for (int w = 0; w < AD_WARPS; ++w) mm = fmaxf(mm, sm[w]);
     float ll = 0.f;
-    float acc[8];
+    float acc[VPL];
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int e = 0; e < VPL; ++e) acc[e] = 0.f;
     for (int w = 0; w < AD_WARPS; ++w) {
       const float f = (sm[w] == -INFINITY) ? 0.f : __expf(sm[w] - mm);
       ll += sl[w] * f;
 #pragma unroll
-      for (int e = 0; e < 8; ++e)
-        if (e < VPL) acc[e] += so[w][lane * VPL + e] * f;
+      for (int e = 0; e < VPL; ++e) acc[e] += so[w][lane * VPL + e] * f;
     }
-    float* dst = part + ((long long)bh * splits + split) * (D + 2);
-    if (lane == 0) { dst[0] = mm; dst[1] = ll; }
+    if (splits == 1) {
+      const float inv = 1.f / ll;
+      Vec r;
 #pragma unroll
-    for (int e = 0; e < 8; ++e)
-      if (e < VPL) dst[2 + lane * VPL + e] = acc[e];
+      for (int e = 0; e < VPL; ++e) r.v[e] = xl_from_float<T>(acc[e] * inv);
+      *reinterpret_cast<Vec*>(out + (long long)b * ldo + h * D + lane * VPL) = r;
+    } else {
+      if (lane == 0) { mine[0] = mm; mine[1] = ll; }
+#pragma unroll
+      for (int e = 0; e < VPL; ++e) mine[2 + lane * VPL + e] = acc[e];
+    }
   }
-}
-
-template <typename T>
-__global__ void attn_decode_combine_kernel(const float* __restrict__ part, T* __restrict__ out, int D, int splits) {
-  const int bh = blockIdx.x;
+  if (splits == 1) return;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicAdd(counters + bh, 1u) == (unsigned int)splits - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
   const float* p = part + (long long)bh * splits * (D + 2);
   float mm = -INFINITY;
-  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, p[s * (D + 2)]);
+  for (int sp = 0; sp < splits; ++sp) mm = fmaxf(mm, __ldcg(p + sp * (D + 2)));
   float ll = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = p[s * (D + 2)];
-    ll += (ms == -INFINITY) ? 0.f : p[s * (D + 2) + 1] * __expf(ms - mm);
+  for (int sp = 0; sp < splits; ++sp) {
+    const float ms = __ldcg(p + sp * (D + 2));
+    ll += (ms == -INFINITY) ? 0.f : __ldcg(p + sp * (D + 2) + 1) * __expf(ms - mm);
   }
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float acc = 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = p[s * (D + 2)];
-      if (ms != -INFINITY) acc += p[s * (D + 2) + 2 + d] * __expf(ms - mm);
+    for (int sp = 0; sp < splits; ++sp) {
+      const float ms = __ldcg(p + sp * (D + 2));
+      if (ms != -INFINITY) acc += __ldcg(p + sp * (D + 2) + 2 + d) * __expf(ms - mm);
     }
-    out[(long long)bh * D + d] = xl_from_float<T>(acc / ll);
+    out[(long long)b * ldo + h * D + d] = xl_from_float<T>(acc / ll);
+  }
+  if (threadIdx.x == 0) counters[bh] = 0;
+}
+
+// q: rows of ldq elements (the first H*D are used); out: rows of ldo elements (H*D written). scratch: at least
+// B*H*splits*(D+2) floats; counters: B*H zero-initialised words (left zeroed). D in {64, 128, 256}; ldq, ldo and the
+// window offsets must keep every head 16-byte aligned.
+XL_API int xl_attn_decode(const void* qkv, long long ldq, const void* k_cache, const void* v_cache, void* out, long long ldo,
+                          float* scratch, unsigned int* counters, const int* pos_ptr, int B, int H, int D, int Smax,
+                          float scale, int splits, int dtype, cudaStream_t s) {
+  if ((D != 64 && D != 128 && D != 256) || splits < 1 || dtype == XL_F32 || (ldq % 8) || (ldo % 8)) return -1;
+  if (splits > 1 && (scratch == nullptr || counters == nullptr)) return -1;
+  dim3 grid(B * H, splits);
+#define XL_AD_LAUNCH(T, VPL)                                                                                          \
+  attn_decode_kernel<T, VPL><<<grid, AD_WARPS * 32, 0, s>>>((const T*)qkv, ldq, (const T*)k_cache, (const T*)v_cache, \
+                                                            (T*)out, ldo, scratch, counters, pos_ptr, H, Smax, scale)
+  if (dtype == XL_BF16) {
+    if (D == 256) XL_AD_LAUNCH(__nv_bfloat16, 8);
+    else if (D == 128) XL_AD_LAUNCH(__nv_bfloat16, 4);
+    else XL_AD_LAUNCH(__nv_bfloat16, 2);
+  } else {
+    if (D == 256) XL_AD_LAUNCH(__half, 8);
+    else if (D == 128) XL_AD_LAUNCH(__half, 4);
+    else XL_AD_LAUNCH(__half, 2);
+  }
+#undef XL_AD_LAUNCH
+  return (int)cudaGetLastError();
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Residual update + LayerNorm for a few rows: x += delta (+ bias); h = LayerNorm(x) * w + b. One CTA per row.
+// ------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+    add_layer_norm_kernel(T* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ bias,
+                          const T* __restrict__ w, const T* __restrict__ b, T* __restrict__ h, int cols, float eps) {
+  constexpr int MAX_PER = 32;  // cols <= 256 * 32
+  const int row = blockIdx.x;
+  T* xr = x + (long long)row * cols;
+  float v[MAX_PER];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAX_PER; ++i) {
+    const int c = threadIdx.x + i * 256;
+    v[i] = 0.f;
+    if (c < cols) {
+      float t = xl_to_float(xr[c]);
+      if (delta) t += xl_to_float(delta[(long long)row * cols + c]);
+      if (bias) t += xl_to_float(bias[c]);
+      const T rounded = xl_from_float<T>(t);
+      if (delta || bias) xr[c] = rounded;
+      v[i] = xl_to_float(rounded);
+      sum += v[i];
+    }
+  }
+  __shared__ float red[8];
+  __shared__ float stat[2];
+  sum = xl_warp_sum(sum);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += red[i];
+    stat[0] = t / cols;
+  }
+  __syncthreads();
+  const float mean = stat[0];
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAX_PER; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < cols) sq += (v[i] - mean) * (v[i] - mean);
+  }
+  sq = xl_warp_sum(sq);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += red[i];
+    stat[1] = rsqrtf(t / cols + eps);
+  }
+  __syncthreads();
+  const float rstd = stat[1];
+#pragma unroll
+  for (int i = 0; i < MAX_PER; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < cols) {
+      float t = (v[i] - mean) * rstd;
+      if (w) t *= xl_to_float(w[c]);
+      if (b) t += xl_to_float(b[c]);
+      h[(long long)row * cols + c] = xl_from_float<T>(t);
+    }
   }
 }
 
-// out: (B, H*D). scratch: B*H*splits*(D+2) floats.
-XL_API int xl_attn_decode(const void* qkv, const void* k_cache, const void* v_cache, void* out, float* scratch,
-                          const int* pos_ptr, int B, int H, int D, int Smax, float scale, int splits, int dtype,
-                          cudaStream_t s) {
-  if (D % 32 || D > AD_MAX_D || splits < 1) return -1;
-  dim3 grid(B * H, splits);
+// x (rows, cols) is updated in place when delta or bias is given; h (rows, cols) receives the normalised rows.
+XL_API int xl_add_layer_norm(void* x, const void* delta, const void* bias, const void* w, const void* b, void* h,
+                             int rows, int cols, float eps, int dtype, cudaStream_t s) {
+  if (cols > 256 * 32 || rows < 1) return -1;
   XL_DISPATCH_DTYPE(dtype, T, {
-    attn_decode_split_kernel<T><<<grid, AD_WARPS * 32, 0, s>>>((const T*)qkv, (const T*)k_cache, (const T*)v_cache,
-                                                               scratch, pos_ptr, H, D, Smax, scale, splits);
-    attn_decode_combine_kernel<T><<<B * H, 128, 0, s>>>(scratch, (T*)out, D, splits);
+    add_layer_norm_kernel<T><<<rows, 256, 0, s>>>((T*)x, (const T*)delta, (const T*)bias, (const T*)w, (const T*)b, (T*)h,
+                                                 cols, eps);
   });
   return (int)cudaGetLastError();
 }

@@ -52,6 +52,18 @@ struct GemmParams {
   unsigned int* local_sync;   // [0] "peers are ready" flag (set by CTA 0, cleared by the last warp to finish),
                               // [1] count of epilogue warps that finished
   unsigned int comm_spin_limit;
+  // reduce-scatter mode (accumulate == 4): row r belongs to rank r / rs_rows and is added into that rank's shard buffer
+  void* const* rs_dst;  // device array [world]: output shard (rs_rows x ldc) of every rank, as mapped by this rank
+  int rs_rows;
+  // all-gather prologue: one operand is a row-sharded matrix whose remote row blocks are pulled from the peers by the
+  // first `n_copy` CTAs of this launch while the other CTAs already multiply the local rows.
+  int gather_mode;                  // 0 none, 1: A (M x K, K-major) sharded over M, 2: B (K x N, N contiguous) sharded over K
+  int n_copy;                       // copy CTAs
+  int gather_bps;                   // row blocks per shard (a row block = BLOCK_M rows of A or BLOCK_K rows of B)
+  long long gather_block_bytes;     // bytes of one row block (rows are contiguous: leading dimension == row length)
+  const uint8_t* const* gather_src; // device array [world]: the full matrix in every rank's memory
+  uint8_t* gather_dst;              // the full matrix in this rank's memory (own shard already in place)
+  unsigned int* gather_flags;       // one word per row block of the full matrix, zeroed before the launch; 1 = landed
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------------------
@@ -94,6 +106,24 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
+
+// plain (untiled) bulk copies, used by the copy CTAs of the all-gather prologue; never multicast
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N> __device__ __forceinline__ void bulk_wait_all() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols)
@@ -174,11 +204,10 @@ struct SmemLayout {
 
 // tile index -> (batch, m block, n block). Tiles that run at the same time share A / B panels in L2: m-blocks are
 // walked in groups of 8 inside each n-column.
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& b, int& mb, int& nb) {
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& b, int& mb, int& nb, int GROUP = 8) {
   const int per_batch = tiles_m * tiles_n;
   b = tile / per_batch;
   int t = tile - b * per_batch;
-  constexpr int GROUP = 8;
   const int group_size = GROUP * tiles_n;
   const int g = t / group_size;
   const int first_m = g * GROUP;
@@ -206,19 +235,29 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // the first n_copy CTAs of a launch with an all-gather prologue only move data; the others are the GEMM's CTAs
+  const int n_copy = p.gather_mode ? p.n_copy : 0;
+  const bool is_copy = (int)blockIdx.x < n_copy;
+  const int cta = (int)blockIdx.x - n_copy, ncta = (int)gridDim.x - n_copy;
+  const int raster_group = p.gather_mode == 1 ? min(8, p.gather_bps) : 8;
+  const int gather_rot = p.gather_mode ? p.comm_rank * p.gather_bps : 0;  // own shard's row blocks come first
   const int tiles_m = (p.M + BLOCK_M - 1) / BLOCK_M;
   const int tiles_n = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int num_tiles = tiles_m * tiles_n * p.batch;
   const int k_blocks = (p.K + BLOCK_K - 1) / BLOCK_K;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
-    }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(&tmem_full_bar[a], 1);
-      mbar_init(&tmem_empty_bar[a], NUM_EPI_WARPS);  // one arrival per epilogue warp
+    if (is_copy) {
+      for (int s = 0; s < 2 * STAGES + 4; ++s) mbar_init(&bars[s], 1);  // one barrier per slot of the copy ring
+    } else {
+      for (int s = 0; s < STAGES; ++s) {
+        mbar_init(&full_bar[s], 1);
+        mbar_init(&empty_bar[s], 1);
+      }
+      for (int a = 0; a < 2; ++a) {
+        mbar_init(&tmem_full_bar[a], 1);
+        mbar_init(&tmem_empty_bar[a], NUM_EPI_WARPS);  // one arrival per epilogue warp
+      }
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -232,16 +271,140 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
-  if (warp == 0) {
+  if (is_copy) {
+    // ------------------------------------------------ all-gather copy CTA -----------------------------------------
+    // Lane 0 of warp 0 streams this CTA's share of the remote row blocks peer -> shared-memory ring -> local matrix
+    // with bulk async copies and raises the block's flag once its bytes have landed. Remote blocks are visited in
+    // order of distance (rank+1 first), the order in which the GEMM CTAs will ask for them.
+    if (warp == 0) {
+      constexpr int PIECE = 16384;
+      constexpr int SLOTS = (L::TILE_BYTES / PIECE) < (2 * STAGES + 4) ? (L::TILE_BYTES / PIECE) : (2 * STAGES + 4);
+      constexpr int STORE_LAG = SLOTS / 2;  // loads in flight ahead of the stores
+      constexpr int FLAG_LAG = 2;           // a block is flagged once its last store is FLAG_LAG groups behind
+      bool ok = true;
+      // peers are ready (their shards are final) once the group barrier has completed; CTA 0 runs it for all copy CTAs
+      if (blockIdx.x == 0) {
+        const bool peers_ok = xl_group_barrier(p.pads, p.comm_rank, p.comm_world, 8, p.err, p.comm_spin_limit);
+        if (lane == 0 && peers_ok) xl_st_release_gpu(p.local_sync + 2, 1u);
+      }
+      if (lane == 0) {
+        bool ready = false;
+        for (unsigned int i = 0; i < p.comm_spin_limit && !ready; ++i) ready = xl_ld_acquire_gpu(p.local_sync + 2) == 1u;
+        if (!ready) {
+          ok = false;
+          if (p.err) atomicCAS(p.err, 0, (int)XL_COMM_TIMEOUT_FLAG);
+        }
+        fence_proxy_async_global();  // the peers' shards were written through the generic proxy
+        const int remote_blocks = (p.comm_world - 1) * p.gather_bps;
+        const int my_chunks = ok ? (remote_blocks - (int)blockIdx.x + n_copy - 1) / n_copy : 0;
+        const int ppc = (int)((p.gather_block_bytes + PIECE - 1) / PIECE);  // pieces per row block
+        const int total = my_chunks * ppc;
+        int flagged = 0;  // chunks of this CTA already flagged
+        auto block_of = [&](int chunk_i) {  // chunk_i-th chunk of this CTA -> row block of the full matrix
+          const int c = (int)blockIdx.x + chunk_i * n_copy;
+          const int peer = (p.comm_rank + 1 + c / p.gather_bps) % p.comm_world;
+          return peer * p.gather_bps + c % p.gather_bps;
+        };
+        auto piece_span = [&](int t, int& peer, long long& off, uint32_t& bytes) {
+          const int blk = block_of(t / ppc);
+          peer = blk / p.gather_bps;
+          const long long in_blk = (long long)(t % ppc) * PIECE;
+          off = (long long)blk * p.gather_block_bytes + in_blk;
+          const long long left = p.gather_block_bytes - in_blk;
+          bytes = (uint32_t)(left < PIECE ? left : PIECE);
+        };
+        auto flag_done = [&](int upto_piece) {  // every store up to piece `upto_piece` has completed
+          while (flagged < my_chunks && (flagged + 1) * ppc - 1 <= upto_piece) {
+            fence_proxy_async_global();
+            __threadfence();
+            xl_st_release_gpu(p.gather_flags + block_of(flagged), 1u);
+            ++flagged;
+          }
+        };
+        int loads_issued = 0, stores_issued = 0;
+        for (int it = 0; it < total + STORE_LAG && ok; ++it) {
+          if (it < total) {
+            const int slot = it % SLOTS;
+            if (it >= SLOTS) bulk_wait_read<SLOTS - STORE_LAG - 1>();  // the store that last used this slot has read it
+            int peer; long long off; uint32_t bytes;
+            piece_span(it, peer, off, bytes);
+            mbar_expect_tx(&bars[slot], bytes);
+            bulk_load(smem + slot * PIECE, p.gather_src[peer] + off, bytes, &bars[slot]);
+            ++loads_issued;
+          }
+          const int j = it - STORE_LAG;
+          if (j >= 0) {
+            const int slot = j % SLOTS;
+            ok = mbar_wait(&bars[slot], (uint32_t)(j / SLOTS) & 1u, abort_flag, p.err, ERR_FULL_WAIT);
+            if (!ok) break;
+            int peer; long long off; uint32_t bytes;
+            piece_span(j, peer, off, bytes);
+            bulk_store(p.gather_dst + off, smem + slot * PIECE, bytes);
+            bulk_commit();
+            ++stores_issued;
+            bulk_wait_all<FLAG_LAG>();
+            flag_done(j - FLAG_LAG);
+          }
+        }
+        bulk_wait_all<0>();
+        if (ok) flag_done(total - 1);
+        // after an abort: loads still in flight target this CTA's shared memory; give them a bounded time to land
+        for (int t = stores_issued; t < loads_issued; ++t) {
+          for (uint32_t i = 0; i < SPIN_LIMIT; ++i)
+            if (mbar_try_wait(&bars[t % SLOTS], (uint32_t)(t / SLOTS) & 1u)) break;
+        }
+      }
+      __syncwarp();
+      // the peers may not change their shards before every rank has finished reading: the last copy CTA of this rank
+      // to finish runs the closing barrier and re-arms the two control words for the next launch
+      __threadfence_system();
+      unsigned int prev = 0;
+      if (lane == 0) prev = atomicAdd(p.local_sync + 3, 1u);
+      prev = __shfl_sync(0xffffffffu, prev, 0);
+      if (prev == (unsigned int)n_copy - 1) {
+        if (lane == 0) { p.local_sync[3] = 0; xl_st_release_gpu(p.local_sync + 2, 0u); }
+        xl_group_barrier(p.pads, p.comm_rank, p.comm_world, 9, p.err, p.comm_spin_limit);
+      }
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------ TMA producer ------------------------------------------------
     if (elect_one()) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      uint32_t seen[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // remote row blocks already known to have landed
+      auto wait_block = [&](int blk) -> bool {
+        if (blk / p.gather_bps == p.comm_rank) return true;  // own shard
+        if (blk < 256 && (seen[blk >> 5] >> (blk & 31) & 1u)) return true;
+        bool ready = false;
+        for (unsigned int i = 0; i < p.comm_spin_limit && !ready; ++i) {
+          ready = xl_ld_acquire_gpu(p.gather_flags + blk) == 1u;
+          if (!ready && (i & 1023u) == 1023u && *abort_flag) break;
+        }
+        if (!ready) {
+          *abort_flag = 1;
+          if (p.err) atomicCAS(p.err, 0, (int)XL_COMM_TIMEOUT_FLAG);
+          return false;
+        }
+        fence_proxy_async_global();  // the block was written through the async proxy of another SM
+        if (blk < 256) seen[blk >> 5] |= 1u << (blk & 31);
+        return true;
+      };
+      for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
         int b, mb, nb;
-        tile_coords(tile, tiles_m, tiles_n, b, mb, nb);
+        tile_coords(tile, tiles_m, tiles_n, b, mb, nb, raster_group);
+        if (p.gather_mode == 1) {
+          mb = (mb + gather_rot) % tiles_m;
+          ok = wait_block(mb);
+          if (!ok) break;
+        }
         const int m0 = mb * BLOCK_M, n0 = nb * BLOCK_N;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb_i = 0; kb_i < k_blocks; ++kb_i) {
+          int kb = kb_i;
+          if (p.gather_mode == 2) {
+            kb = (kb_i + gather_rot) % k_blocks;
+            ok = wait_block(kb);
+            if (!ok) break;
+          }
           ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.err, ERR_EMPTY_WAIT);
           if (!ok) break;
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
@@ -266,6 +429,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
       }
     }
+  } else if (is_copy) {
+    // the other warps of a copy CTA have nothing to do
   } else if (warp == 1) {
     // ------------------------------------------------ MMA issuer --------------------------------------------------
     if (elect_one()) {
@@ -280,7 +445,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       uint32_t stage = 0, phase = 0;
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
         ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.err, ERR_TMEM_EMPTY_WAIT);
         if (!ok) break;
         tcgen05_fence_after();
@@ -318,10 +483,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       mean_a = t / (t + 1.f);
       mean_b = 1.f / (t + 1.f);
     }
-    if (p.accumulate == 3) {
+    if (p.accumulate >= 3) {
       // Nobody may push into a peer's output before that peer has zeroed it, i.e. before it has entered this kernel:
-      // the first epilogue warp of CTA 0 runs the cross-rank barrier and publishes the epoch to the other CTAs.
-      if (blockIdx.x == 0 && warp == 2) {
+      // the first epilogue warp of the first GEMM CTA runs the cross-rank barrier and publishes it to the other CTAs.
+      if (cta == 0 && warp == 2) {
         const bool peers_ok = xl_group_barrier(p.pads, p.comm_rank, p.comm_world, 0, p.err, p.comm_spin_limit);
         if (lane == 0 && peers_ok) xl_st_release_gpu(p.local_sync, 1u);
       }
@@ -336,17 +501,24 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (p.err) atomicCAS(p.err, 0, (int)XL_COMM_TIMEOUT_FLAG);
       }
     }
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
       int b, mb, nb;
-      tile_coords(tile, tiles_m, tiles_n, b, mb, nb);
+      tile_coords(tile, tiles_m, tiles_n, b, mb, nb, raster_group);
+      if (p.gather_mode == 1) mb = (mb + gather_rot) % tiles_m;
       ok = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, p.err, ERR_TMEM_FULL_WAIT);
       if (!ok) break;
       tcgen05_fence_after();
       const int row = mb * BLOCK_M + q * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BLOCK_N;
-      uint8_t* crow = (uint8_t*)p.C + ((long long)b * p.batch_stride_c + (long long)row * p.ldc) *
-                                          (p.c_dtype == XL_F32 ? 4 : 2);
+      uint8_t* crow;
+      if (p.accumulate == 4) {
+        // reduce-scatter: the row lives in the output shard of its owner rank
+        const int owner = row_ok ? row / p.rs_rows : 0;
+        crow = (uint8_t*)p.rs_dst[owner] + (long long)(row - owner * p.rs_rows) * p.ldc * 2;
+      } else {
+        crow = (uint8_t*)p.C + ((long long)b * p.batch_stride_c + (long long)row * p.ldc) * (p.c_dtype == XL_F32 ? 4 : 2);
+      }
 #pragma unroll 1
       for (int c = col_half * COLS_PER_WARP; c < (col_half + 1) * COLS_PER_WARP; c += 32) {
         uint32_t r[32];
@@ -399,8 +571,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         } else {
           uint16_t* dst = (uint16_t*)crow + col0;
           const bool bf = p.c_dtype == XL_BF16;
-          if (p.accumulate == 3) {
-            // host guarantees N % 8 == 0 and 16-byte aligned rows in this mode
+          if (p.accumulate >= 3) {
+            // host guarantees N % 8 == 0 and 16-byte aligned rows in these modes
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               if (col0 + j >= p.N) break;
@@ -409,8 +581,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
               for (int e = 0; e < 8; ++e)
                 oe[e] = bf ? __bfloat16_as_ushort(__float2bfloat16_rn(v[j + e])) : __half_as_ushort(__float2half_rn(v[j + e]));
-              if (bf) xl_multimem_red_add_bf16x8(dst + j, o);
-              else xl_multimem_red_add_f16x8(dst + j, o);
+              if (p.accumulate == 3) {
+                if (bf) xl_multimem_red_add_bf16x8(dst + j, o);
+                else xl_multimem_red_add_f16x8(dst + j, o);
+              } else {
+                if (bf) xl_red_add_bf16x8(dst + j, o);
+                else xl_red_add_f16x8(dst + j, o);
+              }
             }
           } else if (full && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
@@ -449,14 +626,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
-    if (p.accumulate == 3) {
+    if (p.accumulate >= 3) {
       // The kernel may only finish once every rank's pushes have landed here: the last epilogue warp of this rank
       // to finish runs the closing cross-rank barrier (each warp fences its own pushes first).
       __threadfence_system();
       unsigned int prev = 0;
       if (lane == 0) prev = atomicAdd(p.local_sync + 1, 1u);
       prev = __shfl_sync(0xffffffffu, prev, 0);
-      if (prev == gridDim.x * NUM_EPI_WARPS - 1) {
+      if (prev == (unsigned int)ncta * NUM_EPI_WARPS - 1) {
         // every epilogue warp of this rank has passed the ready check by now: re-arm both words for the next launch
         if (lane == 0) { p.local_sync[1] = 0; xl_st_release_gpu(p.local_sync, 0u); }
         xl_group_barrier(p.pads, p.comm_rank, p.comm_world, 1, p.err, p.comm_spin_limit);
@@ -516,7 +693,9 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
     configured = true;
   }
   const int tiles = ((p.M + BLOCK_M - 1) / BLOCK_M) * ((p.N + BLOCK_N - 1) / BLOCK_N) * p.batch;
-  const int grid = tiles < sm_count ? tiles : sm_count;
+  const int n_copy = p.gather_mode ? p.n_copy : 0;  // copy CTAs and GEMM CTAs wait on one another: all must be resident
+  const int gemm_ctas = tiles < sm_count - n_copy ? tiles : sm_count - n_copy;
+  const int grid = gemm_ctas + n_copy;
   gemm_tcgen05_kernel<BLOCK_N><<<grid, NUM_THREADS, L::TOTAL, s>>>(ma, mb, p);
   return (int)cudaGetLastError();
 }
@@ -534,12 +713,25 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
 //   All ranks must launch the same GEMM shape. No launch argument changes between calls, so the launch can be
 //   captured in a CUDA graph and replayed.
 // Returns 0, a CUDA error code, or a negative value when the arguments are not supported by this kernel.
-XL_API int xl_gemm_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, int batch, int a_mn, int b_mn,
-                           long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
-                           long long stride_c, int ab_is_fp16, int c_dtype, const void* bias, int bias_dtype, int act,
-                           int accumulate, const float* step, float alpha, int* err, int sm_count,
-                           const void* comm_pads, int comm_rank, int comm_world, unsigned int* comm_local_sync,
-                           cudaStream_t s) {
+// Full entry point. On top of xl_gemm_tcgen05:
+//   accumulate == 4 (GEMM fused with a reduce-scatter over NVLink): row r of the product is added (`red.add`, 16-byte
+//   vectors) into the output shard of rank r / rs_rows; rs_dst = device array with every rank's shard buffer
+//   (rs_rows x ldc, zeroed in stream order before the launch), M == rs_rows * comm_world. `c` is unused.
+//   gather_mode != 0 (all-gather fused into the GEMM): the sharded operand (1: A sharded over M, 2: B stored (K x N)
+//   and sharded over K) lives in a full-size matrix of which only this rank's row range is valid at launch;
+//   gather_src = device array with that matrix in every rank's memory, gather_dst = this rank's copy (the pointer
+//   also given as `a` / `b`), gather_flags = one zeroed word per row block (128 rows of A / 64 rows of B),
+//   gather_bps = row blocks per shard, n_copy = number of CTAs that pull the remote row blocks (bulk async copies
+//   through shared memory) while the remaining CTAs start on the local rows. The gathered matrix stays valid after
+//   the kernel. Uses comm_local_sync[2..3] and signal channels 8 and 9.
+XL_API int xl_gemm_tcgen05_fused(const void* a, const void* b, void* c, int M, int N, int K, int batch, int a_mn, int b_mn,
+                                 long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
+                                 long long stride_c, int ab_is_fp16, int c_dtype, const void* bias, int bias_dtype,
+                                 int act, int accumulate, const float* step, float alpha, int* err, int sm_count,
+                                 const void* comm_pads, int comm_rank, int comm_world, unsigned int* comm_local_sync,
+                                 const void* rs_dst, int rs_rows, int gather_mode, const void* gather_src,
+                                 void* gather_dst, unsigned int* gather_flags, int gather_bps, int n_copy,
+                                 cudaStream_t s) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -1;
   if ((((uintptr_t)a) & 15) || (((uintptr_t)b) & 15) || (lda % 8) || (ldb % 8)) return -1;
   if (batch > 1 && ((stride_a % 8) || (stride_b % 8))) return -1;
@@ -560,10 +752,44 @@ XL_API int xl_gemm_tcgen05(const void* a, const void* b, void* c, int M, int N, 
   p.alpha = alpha; p.is_fp16 = ab_is_fp16; p.err = err;
   p.pads = (unsigned int* const*)comm_pads; p.comm_rank = comm_rank; p.comm_world = comm_world;
   p.local_sync = comm_local_sync; p.comm_spin_limit = xl_host_comm_spin_limit;
-  if (accumulate == 3 && (comm_pads == nullptr || comm_local_sync == nullptr || (N % 8) || c_dtype == XL_F32 ||
-                          (ldc % 8) || comm_world > 32))
-    return -1;
+  p.rs_dst = (void* const*)rs_dst; p.rs_rows = rs_rows;
+  p.gather_mode = gather_mode; p.n_copy = n_copy; p.gather_bps = gather_bps;
+  p.gather_src = (const uint8_t* const*)gather_src; p.gather_dst = (uint8_t*)gather_dst; p.gather_flags = gather_flags;
+  p.gather_block_bytes = 0;
   if (sm_count <= 0) sm_count = 148;
+  if (accumulate >= 3 && (comm_pads == nullptr || comm_local_sync == nullptr || (N % 8) || c_dtype == XL_F32 ||
+                          (ldc % 8) || comm_world > 32 || batch != 1))
+    return -1;
+  if (accumulate == 4 && (rs_dst == nullptr || rs_rows <= 0 || (long long)rs_rows * comm_world != M)) return -1;
+  if (accumulate > 4 || accumulate < 0) return -1;
+  if (gather_mode) {
+    if (gather_mode != 1 && gather_mode != 2) return -1;
+    if (comm_pads == nullptr || comm_local_sync == nullptr || gather_src == nullptr || gather_dst == nullptr ||
+        gather_flags == nullptr || comm_world < 2 || comm_world > 32 || batch != 1 || n_copy < 1 ||
+        n_copy > sm_count / 2 || gather_bps < 1)
+      return -1;
+    if (gather_mode == 1) {  // A: (M x K) K-major, contiguous rows, M = world * bps * BLOCK_M
+      if (a_mn || lda != K || (long long)gather_bps * comm_world * BLOCK_M != M || gather_dst != a) return -1;
+      p.gather_block_bytes = (long long)BLOCK_M * K * 2;
+    } else {                 // B: (K x N) with N contiguous, K = world * bps * BLOCK_K
+      if (!b_mn || ldb != N || (long long)gather_bps * comm_world * BLOCK_K != K || gather_dst != b) return -1;
+      p.gather_block_bytes = (long long)BLOCK_K * N * 2;
+    }
+  }
   if (block_n == 128) return launch<128>(ma, mb, p, sm_count, s);
   return launch<256>(ma, mb, p, sm_count, s);
+}
+
+// C = epilogue(A * B), 16-bit operands, fp32 accumulation (no reduce-scatter, no all-gather prologue).
+XL_API int xl_gemm_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, int batch, int a_mn, int b_mn,
+                           long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
+                           long long stride_c, int ab_is_fp16, int c_dtype, const void* bias, int bias_dtype, int act,
+                           int accumulate, const float* step, float alpha, int* err, int sm_count,
+                           const void* comm_pads, int comm_rank, int comm_world, unsigned int* comm_local_sync,
+                           cudaStream_t s) {
+  if (accumulate > 3) return -1;
+  return xl_gemm_tcgen05_fused(a, b, c, M, N, K, batch, a_mn, b_mn, lda, ldb, ldc, stride_a, stride_b, stride_c,
+                               ab_is_fp16, c_dtype, bias, bias_dtype, act, accumulate, step, alpha, err, sm_count,
+                               comm_pads, comm_rank, comm_world, comm_local_sync, nullptr, 0, 0, nullptr, nullptr,
+                               nullptr, 0, 0, s);
 }

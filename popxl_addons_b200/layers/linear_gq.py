@@ -16,7 +16,7 @@ from ..named_tensors import NamedTensors
 from ..ops.group_quantize_decompress import group_quantize_compress_numpy
 from ..xl.opdef import OpDef, emit1
 
-__all__ = ["LinearGQ"]
+__all__ = ["LinearGQ", "linear_gq_window"]
 
 import torch  # noqa: E402
 
@@ -39,6 +39,35 @@ def _linear_gq_ref(x, packed, scale, bias, *b, dim):
 
 OpDef("linear_gq", impl=_linear_gq_ref,
       flops=lambda op: 2 * op.inputs[0].shape[-1] * op.outputs[0].nelms)
+
+
+def _linear_gq_window_ref(x, packed, scale, bias, *b, x_col, k, act_from_col):
+    if x.device.type == "meta":
+        return torch.empty((x.shape[0], packed.shape[0]), dtype=x.dtype, device="meta")
+    w = _decompress_ref(packed, scale, bias)  # (out, k)
+    y = torch.matmul(x[:, x_col:x_col + k], w.t().to(x.dtype))
+    if b:
+        y = y + b[0].to(y.dtype)
+    if act_from_col is not None and act_from_col < y.shape[1]:
+        y = torch.cat([y[:, :act_from_col], torch.nn.functional.gelu(y[:, act_from_col:].float()).to(y.dtype)], dim=1)
+    return y
+
+
+OpDef("linear_gq_window", impl=_linear_gq_window_ref,
+      flops=lambda op: 2 * op.attrs["k"] * op.outputs[0].nelms)
+
+
+def linear_gq_window(x: xl.Tensor, packed: xl.Tensor, scale: xl.Tensor, zero: xl.Tensor, bias: Optional[xl.Tensor] = None,
+                     x_col: int = 0, k: Optional[int] = None, act_from_col: Optional[int] = None) -> xl.Tensor:
+    """`act(x[:, x_col : x_col + k] @ dequant(packed)^T + bias)` for weights quantised along the input dimension
+    (`packed (out, k/gs, gs/4)`); GELU on the output columns `>= act_from_col`. Reading a column window lets one buffer
+    hold the inputs of several fused layers side by side."""
+    from ..xl.opdef import emit1
+
+    k = int(k) if k is not None else x.shape[1] - x_col
+    ins = [x, packed, scale, zero] + ([bias] if bias is not None else [])
+    return emit1("linear_gq_window", ins, dict(x_col=int(x_col), k=k,
+                                               act_from_col=None if act_from_col is None else int(act_from_col)))
 
 
 class LinearGQ(Module):

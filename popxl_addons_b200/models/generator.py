@@ -21,6 +21,7 @@ import torch
 
 from .. import xl
 from ..layers.embedding import Embedding
+from ..layers.linear_gq import linear_gq_window
 from ..named_tensors import NamedTensors
 from ..ops.group_quantize_decompress import group_quantize_compress_numpy
 from ..ops.rotary_pos_embed import trig_tables
@@ -144,11 +145,12 @@ class DecoderGenerator:
             for i in range(cfg.layers):
                 L = {"ln_w": xl.variable(np.ones(cfg.hidden, np.float32), dt, f"layer{i}.ln_1.weight"),
                      "ln_b": xl.variable(np.zeros(cfg.hidden, np.float32), dt, f"layer{i}.ln_1.bias"),
-                     "qkv": _GQ(f"layer{i}.attention.qkv", 3 * hd, cfg.hidden, self.gs, dt, rg, scale_dtype=sdt),
-                     "out": _GQ(f"layer{i}.attention.out", cfg.hidden, hd, self.gs, dt, rg, scale_dtype=sdt),
-                     "fc_in": _GQ(f"layer{i}.mlp.fc_in", F, cfg.hidden, self.gs, dt, rg, bias=True, scale_dtype=sdt),
-                     "fc_out": _GQ(f"layer{i}.mlp.fc_out", cfg.hidden, F, self.gs, dt, rg, bias=True, bias_rg=None,
-                                   scale_dtype=sdt),
+                     # both layers that read the normalised input share one weight: rows [q | k | v | fc_in]
+                     "w1": _GQ(f"layer{i}.qkv_fc_in", 3 * hd + F, cfg.hidden, self.gs, dt, rg, bias=True,
+                               scale_dtype=sdt),
+                     # both layers whose outputs are summed share one weight: input columns [attention | fc_in output]
+                     "w2": _GQ(f"layer{i}.out_fc_out", cfg.hidden, hd + F, self.gs, dt, rg, bias=True, bias_rg=None,
+                               scale_dtype=sdt),
                      "k": xl.variable(np.zeros((B, H, S, D), np.float32), dt, f"layer{i}.k_cache"),
                      "v": xl.variable(np.zeros((B, H, S, D), np.float32), dt, f"layer{i}.v_cache")}
                 self.layers.append(L)
@@ -163,9 +165,8 @@ class DecoderGenerator:
                 idx = tokens - off if cfg.tp > 1 else tokens
                 return all_reduce(ops.gather(wte, idx, axis=0, zero_OOR=cfg.tp > 1))
 
-            def select_token(h, lnw, lnb, head, off):
-                """Final norm, vocabulary-sharded logits, greedy choice agreed between the shards."""
-                hn = ops.layer_norm(h, lnw, lnb, eps=cfg.eps)
+            def select_token(hn, head, off):
+                """Vocabulary-sharded logits of the normalised hidden state, greedy choice agreed between the shards."""
                 logits = _linear_gq(hn, head)
                 valid = vshard  # padded rows of the last shard are excluded below via the index check
                 m, idx = ops.argmax_rows(logits, valid, 0)
@@ -182,23 +183,35 @@ class DecoderGenerator:
                 win = ops.negate(ops.collectives.replicated_all_reduce(ops.negate(cand), "max", tp_group))
                 return ops.cast(win, xl.int32)
 
-            def block(x, L, decode: bool, pos=None):
+            def rows(w: Dict[str, xl.Tensor], lo: int, hi: int) -> Dict[str, xl.Tensor]:
+                """Output rows [lo, hi) of a quantised weight (a contiguous slice of every one of its tensors)."""
+                return {k: v[lo:hi] for k, v in w.items()}
+
+            def prefill_block(x, L):
+                """Whole prompt: de-quantise + tcgen05 GEMMs, causal attention on the packed projections."""
                 h = ops.layer_norm(x, L["ln_w"], L["ln_b"], eps=cfg.eps)
-                qkv = _linear_gq(h, L["qkv"])
-                if decode:
-                    qkv = ops.rotary_kv_append_(qkv, sin_tab_i, cos_tab_i, L["k"], L["v"], pos, H, D, cfg.rotary_dim)
-                    a = ops.attention_decode_packed(qkv, L["k"], L["v"], pos, H, D)
-                else:
-                    out, rot, _ = emit("attention_qkv", [qkv, sin_p_i, cos_p_i],
-                                                 dict(seq_len=P, n_heads=H, head_dim=D, rotary_dim=cfg.rotary_dim,
-                                                      causal=True, scale=1.0 / float(np.sqrt(D)), inplace=True))
-                    ops.kv_cache_fill_(rot, L["k"], L["v"], P, H, D)
-                    a = out
-                o = _linear_gq(a, L["out"])
-                z = ops.gelu(_linear_gq(h, L["fc_in"]))
-                y = _linear_gq(z, L["fc_out"], use_bias=False)
-                y = all_reduce(o + y)
-                return x + y + L["fc_out"]["bias"]
+                qkv = _linear_gq(h, rows(L["w1"], 0, 3 * hd), use_bias=False)
+                out, rot, _ = emit("attention_qkv", [qkv, sin_p_i, cos_p_i],
+                                   dict(seq_len=P, n_heads=H, head_dim=D, rotary_dim=cfg.rotary_dim, causal=True,
+                                        scale=1.0 / float(np.sqrt(D)), inplace=True))
+                ops.kv_cache_fill_(rot, L["k"], L["v"], P, H, D)
+                z = ops.gelu(_linear_gq(h, rows(L["w1"], 3 * hd, 3 * hd + F)))
+                y = _linear_gq(ops.concat([out, z], axis=1), L["w2"], use_bias=False)
+                return x + all_reduce(y) + L["w2"]["bias"]
+
+            def decode_block(x, delta, delta_bias, L, pos):
+                """One token per sequence, five kernels: residual + LayerNorm; [qkv | gelu(fc_in)] in one de-quantising
+                GEMM; rotary + cache append; attention, written next to the fc_in output; [out | fc_out] in one GEMM."""
+                h = ops.add_layer_norm_(x, delta, delta_bias, L["ln_w"], L["ln_b"], eps=cfg.eps)
+                w1 = L["w1"]
+                buf = linear_gq_window(h, w1["weight_compressed"], w1["weight_decompression_scale"],
+                                       w1["weight_decompression_bias"], w1["bias"], act_from_col=3 * hd)
+                buf = ops.rotary_kv_append_(buf, sin_tab_i, cos_tab_i, L["k"], L["v"], pos, H, D, cfg.rotary_dim)
+                buf = ops.attention_decode_into_(buf, L["k"], L["v"], pos, H, D, out_col=2 * hd)
+                w2 = L["w2"]
+                y = linear_gq_window(buf, w2["weight_compressed"], w2["weight_decompression_scale"],
+                                     w2["weight_decompression_bias"], None, x_col=2 * hd, k=hd + F)
+                return all_reduce(y)
 
             # graphs take every variable as an input; collect them in a fixed order
             flat: Dict[str, xl.Tensor] = {"wte": self.wte, "ln_f_w": self.ln_f[0], "ln_f_b": self.ln_f[1],
@@ -210,7 +223,7 @@ class DecoderGenerator:
             for i, L in enumerate(self.layers):
                 for key in ("ln_w", "ln_b", "k", "v"):
                     flat[f"l{i}.{key}"] = L[key]
-                for key in ("qkv", "out", "fc_in", "fc_out"):
+                for key in ("w1", "w2"):
                     for k, v in L[key].tensors().items():
                         flat[f"l{i}.{key}.{k}"] = v
             by_ref = {"pos", "cur", "out_buf"} | {f"l{i}.{k}" for i in range(cfg.layers) for k in ("k", "v")}
@@ -227,7 +240,7 @@ class DecoderGenerator:
                 layers = []
                 for i in range(cfg.layers):
                     L = {key: ins[f"l{i}.{key}"] for key in ("ln_w", "ln_b", "k", "v")}
-                    for key in ("qkv", "out", "fc_in", "fc_out"):
+                    for key in ("w1", "w2"):
                         L[key] = {k[len(f"l{i}.{key}."):]: t for k, t in ins.items() if k.startswith(f"l{i}.{key}.")}
                     layers.append(L)
                 head = {k[len("head."):]: t for k, t in ins.items() if k.startswith("head.")}
@@ -242,9 +255,10 @@ class DecoderGenerator:
                 prompt = ops.host_load(self.inputs.prompt)
                 x = embed(ops.reshape(prompt, (B * P,)), ins["wte"], ins["off"])
                 for L in layers:
-                    x = block(x, L, decode=False)
+                    x = prefill_block(x, L)
                 last = ops.reshape(x, (B, P, cfg.hidden))[:, P - 1]
-                tok = select_token(last, ins["ln_f_w"], ins["ln_f_b"], head, ins["off"])
+                hn = ops.layer_norm(last, ins["ln_f_w"], ins["ln_f_b"], eps=cfg.eps)
+                tok = select_token(hn, head, ins["off"])
                 ops.var_updates.copy_var_update_(ins["cur"], tok)
                 ops.store_row_(ins["out_buf"], ins["pos"], tok, base=P)
 
@@ -253,9 +267,12 @@ class DecoderGenerator:
                 sin_tab_i, cos_tab_i = ins["sin_tab"], ins["cos_tab"]
                 layers, head = unpack(ins)
                 x = embed(ins["cur"], ins["wte"], ins["off"])
+                delta = delta_bias = None
                 for L in layers:
-                    x = block(x, L, decode=True, pos=ins["pos"])
-                tok = select_token(x, ins["ln_f_w"], ins["ln_f_b"], head, ins["off"])
+                    delta = decode_block(x, delta, delta_bias, L, ins["pos"])
+                    delta_bias = L["w2"]["bias"]
+                hn = ops.add_layer_norm_(x, delta, delta_bias, ins["ln_f_w"], ins["ln_f_b"], eps=cfg.eps)
+                tok = select_token(hn, head, ins["off"])
                 ops.advance_position_(ins["pos"])
                 ops.var_updates.copy_var_update_(ins["cur"], tok)
                 ops.store_row_(ins["out_buf"], ins["pos"], tok, base=P)
@@ -280,7 +297,7 @@ class DecoderGenerator:
     def _gq_sets(self):
         out = [("lm_head", self.head, 0)]
         for i, L in enumerate(self.layers):
-            for key in ("qkv", "out", "fc_in", "fc_out"):
+            for key in ("w1", "w2"):
                 out.append((f"layer{i}.{key}", L[key], i + 1))
         return out
 
@@ -310,36 +327,46 @@ class DecoderGenerator:
         `layer{i}.ln_1.weight/bias`. qkv rows are ordered `[q | k | v]`, each head-major."""
         cfg, tp = self.cfg, self.cfg.tp
         s = self.session
-        hd_full = cfg.heads * cfg.head_dim
 
-        def shard_out(w, r, parts=1):
+        def f32(name):
+            v = weights.get(name)
+            return None if v is None else np.asarray(v, np.float32)
+
+        def shard_rows(w, r, parts=1):
             # split the output rows into `parts` equal sections (q, k, v) and take rank r's slice of each
             secs = np.split(w, parts, axis=0)
             return np.concatenate([np.split(sec, tp, axis=0)[r] for sec in secs], axis=0)
 
-        for name, q, _ in self._gq_sets():
-            w = np.asarray(weights[name], np.float32)
-            b = weights.get(f"{name}.bias")
-            for r in range(s.num_local):
-                tr = s.global_replica(r) % tp
-                col_parallel = name.endswith(("qkv", "fc_in")) or name == "lm_head"
-                if name == "lm_head":
-                    pad = q.out_f * tp - w.shape[0]
-                    wl = np.split(np.pad(w, ((0, pad), (0, 0))), tp, axis=0)[tr]
-                    bl = None if b is None else np.split(np.pad(np.asarray(b, np.float32), (0, pad)), tp)[tr]
-                elif col_parallel:
-                    parts = 3 if name.endswith("qkv") else 1
-                    wl = shard_out(w, tr, parts)
-                    bl = None if b is None else shard_out(np.asarray(b, np.float32)[:, None], tr, parts)[:, 0]
-                else:
-                    wl = np.split(w, tp, axis=1)[tr]
-                    bl = None if b is None else np.asarray(b, np.float32)
-                packed, scale, zero = quantize_rows(torch.tensor(wl), self.gs)
-                s._vars[q.packed][r].view(torch.int16).copy_(packed)
-                s._vars[q.scale][r].copy_(scale.to(s._vars[q.scale][r].dtype))
-                s._vars[q.zero][r].copy_(zero.to(s._vars[q.zero][r].dtype))
-                if bl is not None and q.bias is not None:
-                    s._vars[q.bias][r].copy_(torch.tensor(bl).to(s._vars[q.bias][r].dtype))
+        def store(q, r, wl, bl):
+            packed, scale, zero = quantize_rows(torch.tensor(wl), self.gs)
+            s._vars[q.packed][r].view(torch.int16).copy_(packed)
+            s._vars[q.scale][r].copy_(scale.to(s._vars[q.scale][r].dtype))
+            s._vars[q.zero][r].copy_(zero.to(s._vars[q.zero][r].dtype))
+            if bl is not None and q.bias is not None:
+                s._vars[q.bias][r].copy_(torch.tensor(bl).to(s._vars[q.bias][r].dtype))
+
+        for r in range(s.num_local):
+            tr = s.global_replica(r) % tp
+            w, b = f32("lm_head"), f32("lm_head.bias")
+            pad = self.head.out_f * tp - w.shape[0]
+            store(self.head, r, np.split(np.pad(w, ((0, pad), (0, 0))), tp, axis=0)[tr],
+                  None if b is None else np.split(np.pad(b, (0, pad)), tp)[tr])
+            for i, L in enumerate(self.layers):
+                qkv, fc_in = f32(f"layer{i}.qkv"), f32(f"layer{i}.fc_in")
+                qkv_l, fc_in_l = shard_rows(qkv, tr, 3), shard_rows(fc_in, tr)
+                b_qkv, b_fc = f32(f"layer{i}.qkv.bias"), f32(f"layer{i}.fc_in.bias")
+                b1 = np.concatenate([
+                    np.zeros(qkv_l.shape[0], np.float32) if b_qkv is None else shard_rows(b_qkv[:, None], tr, 3)[:, 0],
+                    np.zeros(fc_in_l.shape[0], np.float32) if b_fc is None else shard_rows(b_fc[:, None], tr)[:, 0]])
+                store(L["w1"], r, np.concatenate([qkv_l, fc_in_l], axis=0), b1)
+                out_l = np.split(f32(f"layer{i}.out"), tp, axis=1)[tr]
+                fc_out_l = np.split(f32(f"layer{i}.fc_out"), tp, axis=1)[tr]
+                b_out, b_fco = f32(f"layer{i}.out.bias"), f32(f"layer{i}.fc_out.bias")
+                b2 = np.zeros(cfg.hidden, np.float32)
+                for bb in (b_out, b_fco):
+                    if bb is not None:
+                        b2 = b2 + bb
+                store(L["w2"], r, np.concatenate([out_l, fc_out_l], axis=1), b2)
         vshard = self.wte.shape[0]
         wte = np.asarray(weights["wte"], np.float32)
         wte = np.pad(wte, ((0, vshard * tp - wte.shape[0]), (0, 0)))

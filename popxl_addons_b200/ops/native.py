@@ -71,12 +71,16 @@ _ce = _sig("xl_ce_fwd_bwd", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p,
 _gemm = _sig("xl_gemm_tcgen05", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll,
              _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_p, _c_int,
              _c_int, _c_p, _c_p)
-_gq_small = _sig("xl_gq_gemm_small_m", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                 _c_p)
-_rot_append = _sig("xl_rotary_append", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                   _c_p)
-_attn_dec = _sig("xl_attn_decode", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int,
-                 _c_int, _c_p)
+_gemm_fused = _sig("xl_gemm_tcgen05_fused", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
+                   _c_ll, _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_p,
+                   _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p)
+_gq_small = _sig("xl_gq_gemm_small_m", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
+                 _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_p)
+_rot_append = _sig("xl_rotary_append", _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                   _c_int, _c_p)
+_attn_dec = _sig("xl_attn_decode", _c_p, _c_ll, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
+                 _c_f, _c_int, _c_int, _c_p)
+_add_ln = _sig("xl_add_layer_norm", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_f, _c_int, _c_p)
 _argmax = _sig("xl_argmax_rows", _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p)
 _advance = _sig("xl_advance_position", _c_p, _c_p)
 _store_row = _sig("xl_store_row", _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_p)
@@ -441,12 +445,16 @@ def _major(t: torch.Tensor, contraction_last: bool):
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = None, act: int = 0,
          out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, accumulate: int = 0,
-         step: Optional[torch.Tensor] = None, alpha: float = 1.0, comm=None):
+         step: Optional[torch.Tensor] = None, alpha: float = 1.0, comm=None, rs_dst: Optional[torch.Tensor] = None,
+         gather: Optional[tuple] = None):
     """`out = act(alpha * a @ b + bias)` on the tcgen05 kernel. `a`: (M,K) or (B,M,K); `b`: (K,N) or (B,K,N); either may
     be a transposed view. With `accumulate=1` the result is added to `out`, with `accumulate=2` it is folded into `out`
     as a running mean with count `step`. `accumulate=3` with `comm` (a group context owning `out` in symmetric memory)
     all-reduces the product over the group inside the kernel: `out` must have been zeroed on this stream.
-    Returns NotImplemented for operands the kernel cannot take."""
+    `accumulate=4` with `comm` and `rs_dst` (int64 device tensor: every rank's zeroed output shard, `out` being this
+    rank's) reduce-scatters the product over the rows instead. `gather=(mode, src_ptrs, flags, blocks_per_shard,
+    n_copy)` pulls the remote row blocks of the sharded operand (mode 1: `a`, mode 2: `b`) from the peers inside the
+    kernel. Returns NotImplemented for operands the kernel cannot take."""
     if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16) or not (a.is_cuda and b.is_cuda):
         return NotImplemented
     batched = a.dim() == 3
@@ -472,6 +480,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
         out = torch.empty((batch, M, N) if batched else (M, N), dtype=out_dtype, device=a.device)
     if out.dtype not in _CODE or out.stride(-1) != 1 or out.dim() != a.dim():
         return NotImplemented
+    if accumulate == 4 and (rs_dst is None or comm is None or out.shape[-2] * comm.world != M):
+        return NotImplemented
     ldc = out.stride(-2)
     stride_c = out.stride(0) if batched else 0
     esz = out.element_size()
@@ -490,11 +500,25 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
         pads, crank, cworld = comm.arena.pads_dev.data_ptr(), comm.rank, comm.world
         lsync = comm.arena.local_sync.data_ptr()
         err = comm.err
-    rc = _gemm(a.data_ptr(), b.data_ptr(), out_ptr, M, N, K, batch, a_mn, b_mn, lda, ldb, ldc, sa, sb, stride_c,
-               int(a.dtype == torch.float16), _CODE[out.dtype], bias.data_ptr() if bias is not None else None,
-               _CODE[bias.dtype] if bias is not None else 0, act, accumulate,
-               step.data_ptr() if step is not None else None, float(alpha), err.data_ptr(), _sms(a.device), pads, crank,
-               cworld, lsync, _stream())
+    rs_ptr, rs_rows = None, 0
+    g_mode, g_src, g_dst, g_flags, g_bps, g_copy = 0, None, None, None, 0, 0
+    if accumulate == 4 or gather is not None:
+        if comm is None or batched:
+            return NotImplemented
+        pads, crank, cworld = comm.arena.pads_dev.data_ptr(), comm.rank, comm.world
+        lsync = comm.arena.local_sync.data_ptr()
+        err = comm.err
+        if accumulate == 4:
+            rs_ptr, rs_rows = rs_dst.data_ptr(), out.shape[-2]
+        if gather is not None:
+            g_mode, src_ptrs, flags, g_bps, g_copy = gather
+            g_src, g_flags = src_ptrs.data_ptr(), flags.data_ptr()
+            g_dst = a.data_ptr() if g_mode == 1 else b.data_ptr()
+    rc = _gemm_fused(a.data_ptr(), b.data_ptr(), out_ptr, M, N, K, batch, a_mn, b_mn, lda, ldb, ldc, sa, sb, stride_c,
+                     int(a.dtype == torch.float16), _CODE[out.dtype], bias.data_ptr() if bias is not None else None,
+                     _CODE[bias.dtype] if bias is not None else 0, act, accumulate,
+                     step.data_ptr() if step is not None else None, float(alpha), err.data_ptr(), _sms(a.device), pads,
+                     crank, cworld, lsync, rs_ptr, rs_rows, g_mode, g_src, g_dst, g_flags, g_bps, g_copy, _stream())
     if rc < 0:
         return NotImplemented
     _check(rc, "gemm_tcgen05")
@@ -734,35 +758,88 @@ def ce_with_grad_cuda(logits, labels, loss_grad, ignore_index, reduction):
 
 
 # ---- decoding path -------------------------------------------------------------------------------------------------------
+def _row_window_ok(t) -> bool:
+    """2-D, CUDA, unit column stride, 16-byte aligned rows (a column window of a wider row-major matrix is fine)."""
+    return (t.is_cuda and t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
+            and t.dtype in (torch.bfloat16, torch.float16))
+
+
 @native("rotary_kv_append_")
 def rotary_kv_append_cuda(qkv, sin_tab, cos_tab, k_cache, v_cache, pos, n_heads, head_dim, rotary_dim):
-    if not _ok(qkv, k_cache, v_cache) or pos.dtype != torch.int32 or qkv.dtype != k_cache.dtype:
+    if not _row_window_ok(qkv) or not _ok(k_cache, v_cache) or pos.dtype != torch.int32 or qkv.dtype != k_cache.dtype:
         return NotImplemented
     if rotary_dim and not (_ok(sin_tab, cos_tab) and sin_tab.dtype == qkv.dtype):
         return NotImplemented
     B = qkv.shape[0]
-    _check(_rot_append(qkv.data_ptr(), sin_tab.data_ptr(), cos_tab.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
-                       pos.data_ptr(), B, n_heads, head_dim, rotary_dim, k_cache.shape[2], _CODE[qkv.dtype], _stream()),
-           "rotary_append")
+    rc = _rot_append(qkv.data_ptr(), qkv.stride(0), sin_tab.data_ptr(), cos_tab.data_ptr(), k_cache.data_ptr(),
+                     v_cache.data_ptr(), pos.data_ptr(), B, n_heads, head_dim, rotary_dim, k_cache.shape[2],
+                     _CODE[qkv.dtype], _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "rotary_append")
     _count("rotary_append")
     return qkv
 
 
-@native("attention_decode_packed")
-def attention_decode_packed_cuda(qkv, k_cache, v_cache, pos, n_heads, head_dim, scale):
-    if not _ok(qkv, k_cache, v_cache) or pos.dtype != torch.int32 or head_dim % 32 or head_dim > 256:
+_AD_SCRATCH: Dict[int, torch.Tensor] = {}
+
+
+def _attn_decode_launch(qkv, k_cache, v_cache, pos, n_heads, head_dim, scale, out):
+    if not (_row_window_ok(qkv) and _row_window_ok(out)) or not _ok(k_cache, v_cache) or pos.dtype != torch.int32:
+        return NotImplemented
+    if head_dim not in (64, 128, 256) or k_cache.dtype != qkv.dtype or out.dtype != qkv.dtype:
         return NotImplemented
     B, smax = qkv.shape[0], k_cache.shape[2]
-    splits = 4 if smax > 256 else 1
-    out = torch.empty((B, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
-    ws = workspace(B * n_heads * splits * (head_dim + 2) * 4, qkv.device, "attn_decode")
-    rc = _attn_dec(qkv.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), ws.data_ptr(),
-                   pos.data_ptr(), B, n_heads, head_dim, smax, float(scale), splits, _CODE[qkv.dtype], _stream())
+    bh = B * n_heads
+    # enough CTAs to fill the machine, at least 32 cache positions per CTA
+    splits = max(1, min((4 * _sms(qkv.device) + bh - 1) // bh, (smax + 31) // 32, 64))
+    ws = workspace(bh * splits * (head_dim + 2) * 4, qkv.device, "attn_decode")
+    idx = qkv.device.index or 0
+    counters = _AD_SCRATCH.get(idx)
+    if counters is None or counters.numel() < bh:
+        counters = _AD_SCRATCH[idx] = torch.zeros(max(bh, 4096), dtype=torch.int32, device=qkv.device)
+    rc = _attn_dec(qkv.data_ptr(), qkv.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), out.stride(0),
+                   ws.data_ptr(), counters.data_ptr(), pos.data_ptr(), B, n_heads, head_dim, smax, float(scale), splits,
+                   _CODE[qkv.dtype], _stream())
     if rc == -1:
         return NotImplemented
     _check(rc, "attn_decode")
     _count("attn_decode")
     return out
+
+
+@native("attention_decode_packed")
+def attention_decode_packed_cuda(qkv, k_cache, v_cache, pos, n_heads, head_dim, scale):
+    out = torch.empty((qkv.shape[0], n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+    return _attn_decode_launch(qkv, k_cache, v_cache, pos, n_heads, head_dim, scale, out)
+
+
+@native("attention_decode_into_")
+def attention_decode_into_cuda(buf, k_cache, v_cache, pos, n_heads, head_dim, out_col, scale):
+    hd = n_heads * head_dim
+    res = _attn_decode_launch(buf, k_cache, v_cache, pos, n_heads, head_dim, scale, buf[:, out_col:out_col + hd])
+    return buf if res is not NotImplemented else NotImplemented
+
+
+@native("add_layer_norm_")
+def add_layer_norm_cuda(x, *rest, has_delta, has_bias, eps):
+    rest = list(rest)
+    delta = rest.pop(0) if has_delta else None
+    bias = rest.pop(0) if has_bias else None
+    w, b = rest
+    if not _ok(x, delta, bias, w, b) or x.dim() != 2 or x.shape[1] > 8192:
+        return NotImplemented
+    if any(t is not None and t.dtype != x.dtype for t in (delta, bias, w, b)):
+        return NotImplemented
+    h = torch.empty_like(x)
+    rc = _add_ln(x.data_ptr(), delta.data_ptr() if delta is not None else None,
+                 bias.data_ptr() if bias is not None else None, w.data_ptr(), b.data_ptr(), h.data_ptr(), x.shape[0],
+                 x.shape[1], float(eps), _CODE[x.dtype], _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "add_layer_norm")
+    _count("add_layer_norm")
+    return h
 
 
 @native("argmax_rows")
@@ -797,20 +874,45 @@ def store_row_cuda(buf, pos, vals, base):
     return buf
 
 
-def gq_gemm_small_m(x, packed, scale, zero, bias):
-    """`x (M<=16, K) @ dequant(packed (N, K/gs, gs/4))^T + bias` with the de-quantisation fused into the GEMM."""
+_GQ_SCRATCH: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def _gq_scratch(device, n_tiles: int):
+    """Zero-initialised split-K scratch of the small-M GEMM (the kernel hands it back zeroed after every launch)."""
+    idx = device.index or 0
+    cur = _GQ_SCRATCH.get(idx)
+    if cur is None or cur[1].numel() < n_tiles:
+        n = max(n_tiles, 2048)
+        cur = (torch.zeros(n * 512, dtype=torch.float32, device=device), torch.zeros(n, dtype=torch.int32, device=device))
+        _GQ_SCRATCH[idx] = cur
+    return cur
+
+
+def gq_gemm_small_m(x, packed, scale, zero, bias, out=None, act_from_col=None, ksplit=None):
+    """`x (M<=16, K) @ dequant(packed (N, K/gs, gs/4))^T + bias` with the de-quantisation fused into the GEMM; GELU on
+    the output columns `>= act_from_col` if given. `x` and `out` may be column windows of wider row-major matrices."""
     M, K = x.shape
     N, groups, words = packed.shape
     gs = words * 4
-    if M > 16 or not _ok(x, scale, zero, bias) or x.dtype not in (torch.bfloat16, torch.float16):
+    if M > 16 or not x.is_cuda or x.dtype not in (torch.bfloat16, torch.float16) or x.stride(1) != 1:
+        return NotImplemented
+    if x.stride(0) % 8 or x.data_ptr() % 16 or not _ok(scale, zero, bias):
         return NotImplemented
     if scale.dtype != zero.dtype or scale.dtype not in (torch.bfloat16, torch.float16) or groups * gs != K \
             or not packed.is_contiguous() or (bias is not None and bias.dtype != x.dtype):
         return NotImplemented
-    y = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    y = out if out is not None else torch.empty((M, N), dtype=x.dtype, device=x.device)
+    if y.shape != (M, N) or y.dtype != x.dtype or y.stride(1) != 1:
+        return NotImplemented
+    n_tiles = (N + 31) // 32
+    if ksplit is None:
+        ksplit = max(1, min((3 * _sms(x.device)) // n_tiles, K // 1024))
+    ws, counters = _gq_scratch(x.device, n_tiles) if ksplit > 1 else (None, None)
     rc = _gq_small(x.data_ptr(), packed.data_ptr(), scale.data_ptr(), zero.data_ptr(),
-                   bias.data_ptr() if bias is not None else None, y.data_ptr(), M, N, K, gs, _CODE[x.dtype],
-                   _CODE[scale.dtype], _stream())
+                   bias.data_ptr() if bias is not None else None, y.data_ptr(), M, N, K, gs, x.stride(0), y.stride(0),
+                   N if act_from_col is None else int(act_from_col), ksplit,
+                   ws.data_ptr() if ws is not None else None, counters.data_ptr() if counters is not None else None,
+                   _CODE[x.dtype], _CODE[scale.dtype], _stream())
     if rc == -1:
         return NotImplemented
     _check(rc, "gq_gemm_small_m")
@@ -845,6 +947,14 @@ def _register_late():
         return res.view(*x.shape[:-1], wt.shape[-1])
 
     OPS["linear_gq"].native["cuda"] = linear_gq_cuda
+
+    def linear_gq_window_cuda(x, packed, scale, zero, *b, x_col, k, act_from_col):
+        xw = x[:, x_col:x_col + k]
+        if xw.shape[0] > 16:
+            return NotImplemented
+        return gq_gemm_small_m(xw, packed, scale, zero, b[0] if b else None, act_from_col=act_from_col)
+
+    OPS["linear_gq_window"].native["cuda"] = linear_gq_window_cuda
 
 
 _register_late()

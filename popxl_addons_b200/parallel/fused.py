@@ -103,6 +103,73 @@ def matmul_all_reduce(ex, op, a_vals, w_vals):
     return [out.clone()]
 
 
+def _peer_ptr_tensor(ctx: GroupContext, t: torch.Tensor) -> torch.Tensor:
+    """int64 device tensor with the address of arena tensor `t` in every rank's memory (cached per buffer)."""
+    cache = ctx.__dict__.setdefault("_peer_ptr_cache", {})
+    key = t.data_ptr()
+    if key not in cache:
+        cache[key] = torch.tensor(ctx.arena.peer_ptrs(t), dtype=torch.int64, device=t.device)
+    return cache[key]
+
+
+def gemm_reduce_scatter(ctx: GroupContext, a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+                        zero: bool = True):
+    """Rows `[rank*M/world, (rank+1)*M/world)` of `sum over ranks (a @ w)`, one kernel: every finished tile is added
+    (`red.add` over NVLink) into the output shard of the rank that owns its rows. `out` (default: a ring buffer of the
+    group's arena) must live in the arena; with `zero=False` the caller has zeroed it (or wants to add to it: several
+    GEMMs may reduce into the same shard). Returns the shard (valid once the kernel has finished) or NotImplemented."""
+    nat = _lib()
+    M, N = a.shape[0], w.shape[-1]
+    if ctx.world == 1 or M % ctx.world or N % 8 or a.dtype not in (torch.bfloat16, torch.float16):
+        return NotImplemented
+    if out is None:
+        out = ctx.arena.ring((M // ctx.world, N), a.dtype)
+    if zero:
+        out.zero_()
+    res = nat.gemm(a, w, out=out, accumulate=4, comm=ctx, rs_dst=_peer_ptr_tensor(ctx, out))
+    return out if res is not NotImplemented else NotImplemented
+
+
+def gathered_operand(ctx: GroupContext, rows: int, cols: int, dtype, block_rows: int, name: str = ""):
+    """Arena matrix `(rows, cols)` for an operand that is row-sharded over the group: returns `(full, own)` where
+    `own` is the view of this rank's row range. `rows / world` must be a multiple of `block_rows` (128 for the left
+    operand, 64 for the right operand of the GEMM that gathers it)."""
+    if rows % (ctx.world * block_rows):
+        raise ValueError(f"{rows} rows cannot be split into {ctx.world} shards of whole {block_rows}-row blocks")
+    cache = ctx.__dict__.setdefault("_gathered", {})
+    key = (rows, cols, dtype, name)
+    if key not in cache:
+        cache[key] = ctx.arena.alloc((rows, cols), dtype)
+    full = cache[key]
+    per = rows // ctx.world
+    return full, full[ctx.rank * per:(ctx.rank + 1) * per]
+
+
+def all_gather_gemm(ctx: GroupContext, a_full: torch.Tensor, b: torch.Tensor, sharded: str = "a", n_copy: int = 8,
+                    **gemm_kwargs):
+    """`a_full @ b` where one operand is row-sharded over the group and only this rank's rows are present at launch
+    (`sharded="a"`: `a_full (M, K)` split over M; `sharded="b"`: `b (K, N)` split over K, e.g. a weight whose shards
+    live on the ranks of a data-parallel group). The kernel's copy CTAs pull the remote row blocks over NVLink while its
+    GEMM CTAs work on the local rows first; afterwards the gathered operand is complete in this rank's memory."""
+    nat = _lib()
+    op = a_full if sharded == "a" else b
+    if ctx.world == 1 or not ctx.arena.contains(op) or not op.is_contiguous():
+        return NotImplemented
+    block_rows = 128 if sharded == "a" else 64
+    if op.shape[0] % (ctx.world * block_rows):
+        return NotImplemented
+    bps = op.shape[0] // ctx.world // block_rows
+    flags = ctx.__dict__.get("_gather_flags")
+    if flags is None:
+        flags = ctx._gather_flags = torch.zeros(4096, dtype=torch.int32, device=op.device)
+    if ctx.world * bps > flags.numel():
+        return NotImplemented
+    flags[:ctx.world * bps].zero_()
+    res = nat.gemm(a_full, b, comm=ctx, gather=(1 if sharded == "a" else 2, _peer_ptr_tensor(ctx, op), flags, bps, n_copy),
+                   **gemm_kwargs)
+    return res
+
+
 def small_all_reduce(ctx: GroupContext, t: torch.Tensor, op: str) -> Optional[torch.Tensor]:
     """fp32 add / max all-reduce of at most 64 KiB through peer loads (one kernel, two signal rounds)."""
     nat = _lib()

@@ -99,7 +99,13 @@ class DistComm:
 
         if not dist.is_initialized():
             backend = "nccl" if device.type == "cuda" else "gloo"
-            dist.init_process_group(backend=backend, device_id=device if device.type == "cuda" else None)
+            import datetime
+            import os
+
+            # a collective that waits longer than this ends with an error instead of blocking the job for good
+            timeout = datetime.timedelta(seconds=float(os.environ.get("XL_COLLECTIVE_TIMEOUT_S", "600")))
+            dist.init_process_group(backend=backend, device_id=device if device.type == "cuda" else None,
+                                    timeout=timeout)
         self.dist = dist
         self.rank = dist.get_rank()
         self.world_size = dist.get_world_size()

@@ -26,7 +26,7 @@ def _rotary_kv_append_ref(qkv, sin_tab, cos_tab, k_cache, v_cache, pos, n_heads,
     hd = n_heads * head_dim
     q = qkv[:, :hd].reshape(B, n_heads, 1, head_dim)
     k = qkv[:, hd:2 * hd].reshape(B, n_heads, 1, head_dim)
-    v = qkv[:, 2 * hd:].reshape(B, n_heads, 1, head_dim)
+    v = qkv[:, 2 * hd:3 * hd].reshape(B, n_heads, 1, head_dim)
     if rotary_dim:
         s, c = sin_tab[p:p + 1].unsqueeze(0), cos_tab[p:p + 1].unsqueeze(0)
         q = _rotary_ref(q, s, c, rotary_dim, False)
@@ -84,6 +84,33 @@ def _kv_fill_ref(rot, k_cache, v_cache, seq_len, n_heads, head_dim):
     return k_cache
 
 
+def _attn_decode_into_ref(buf, k_cache, v_cache, pos, n_heads, head_dim, out_col, scale):
+    if buf.device.type == "meta":
+        return buf
+    o = _attn_decode_packed_ref(buf, k_cache, v_cache, pos, n_heads, head_dim, scale)
+    buf[:, out_col:out_col + n_heads * head_dim].copy_(o)
+    return buf
+
+
+def _add_layer_norm_ref(x, *rest, has_delta, has_bias, eps):
+    if x.device.type == "meta":
+        return torch.empty_like(x)
+    rest = list(rest)
+    delta = rest.pop(0) if has_delta else None
+    bias = rest.pop(0) if has_bias else None
+    w, b = rest
+    if delta is not None or bias is not None:
+        t = x.float()
+        if delta is not None:
+            t = t + delta.float()
+        if bias is not None:
+            t = t + bias.float()
+        x.copy_(t.to(x.dtype))
+    return torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), w.float(), b.float(), eps).to(x.dtype)
+
+
+OpDef("attention_decode_into_", impl=_attn_decode_into_ref, inplace=True)
+OpDef("add_layer_norm_", impl=_add_layer_norm_ref)
 OpDef("rotary_kv_append_", impl=_rotary_kv_append_ref, inplace=True)
 OpDef("attention_decode_packed", impl=_attn_decode_packed_ref)
 OpDef("argmax_rows", impl=_argmax_rows_ref)
@@ -106,6 +133,24 @@ def attention_decode_packed(qkv: Tensor, k_cache: Tensor, v_cache: Tensor, pos: 
     scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
     return emit1("attention_decode_packed", [qkv, k_cache, v_cache, pos],
                  dict(n_heads=int(n_heads), head_dim=int(head_dim), scale=scale))
+
+
+def attention_decode_into_(buf: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, n_heads: int, head_dim: int,
+                           out_col: int, scale: Optional[float] = None) -> Tensor:
+    """Like `attention_decode_packed` with the query in the first `heads*head_dim` columns of `buf`, but the result is
+    written into `buf[:, out_col : out_col + heads*head_dim]` (so that it sits next to other inputs of the following
+    linear layer)."""
+    scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+    return emit1("attention_decode_into_", [buf, k_cache, v_cache, pos],
+                 dict(n_heads=int(n_heads), head_dim=int(head_dim), out_col=int(out_col), scale=scale))
+
+
+def add_layer_norm_(x: Tensor, delta: Optional[Tensor], bias: Optional[Tensor], weight: Tensor, ln_bias: Tensor,
+                    eps: float = 1e-5) -> Tensor:
+    """Residual update fused with the following LayerNorm: `x += delta (+ bias)` in place (skipped when both are None),
+    returns `layer_norm(x) * weight + ln_bias`."""
+    ins = [x] + ([delta] if delta is not None else []) + ([bias] if bias is not None else []) + [weight, ln_bias]
+    return emit1("add_layer_norm_", ins, dict(has_delta=delta is not None, has_bias=bias is not None, eps=float(eps)))
 
 
 def argmax_rows(logits: Tensor, valid: Optional[int] = None, index_offset: int = 0) -> Tuple[Tensor, Tensor]:

@@ -10,6 +10,7 @@ Parity: the `popxl.Session` surface used by popxl_addons/task_session.py:52-53,8
 (`run`, `get_tensor(s)_data`, `write_variable(s)_data`, context manager, `ir`, `is_attached`).
 """
 import os
+import sys
 from typing import Any, Dict, Iterable, List, Mapping, Optional
 
 import numpy as np
@@ -456,12 +457,21 @@ class Session:
         static staging tensor that is refreshed before each replay; host-stream writes are copied out after it."""
         state = self._captured.get(op.uid)
         it = 0
+        debug = os.environ.get("XL_DEBUG_CAPTURE") == "1"
+
+        def note(msg):
+            if debug:
+                torch.cuda.synchronize(self.device)
+                print(f"[capture rank {os.environ.get('RANK', '0')}] {graph.name}: {msg}", file=sys.stderr, flush=True)
+
         if state is None:
             self.run_graph(graph, vals)  # eager warm-up iteration
+            note("eager iteration done")
             it = 1
             if count == 1:
                 return
             state = self._capture(op, graph, vals)
+            note("captured and replayed once")
             self._captured[op.uid] = state
             self._after_replay(state)
             it = 2
@@ -508,6 +518,9 @@ class Session:
             _native._RECORDING.pop()
             outs = self._capture_outputs
             self._capture_inputs, self._capture_outputs = None, None
+        if os.environ.get("XL_DEBUG_CAPTURE") == "1":
+            print(f"[capture rank {os.environ.get('RANK', '0')}] {graph.name}: capture ended, {len(kernels)} own kernels",
+                  file=sys.stderr, flush=True)
         g.replay()  # capture records but does not execute
         _native.count_replay(kernels)
         return {"graph": g, "static_in": static_in, "outputs": outs, "kernels": kernels,

@@ -27,6 +27,10 @@ def main():
     ap.add_argument("--fused", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--big", type=int, default=0)
+    ap.add_argument("--m", type=int, default=2048)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--n-copy", type=int, default=8)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -89,6 +93,108 @@ def main():
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if rank == 0:
             print(json.dumps({"ok": bool(flag.item())}))
+    elif args.mode == "fusedgemm":
+        # GEMM + reduce-scatter and all-gather + GEMM kernels against NCCL + torch.matmul on the same data
+        from popxl_addons_b200 import xl as popxl
+        from popxl_addons_b200.ops import native
+        from popxl_addons_b200.parallel import fused
+
+        ir = popxl.Ir(replication="popdist")
+        with ir.main_graph:
+            pass
+        s = popxl.Session(ir, "cuda")
+        ctx = fused.runtime(s).context(ir.replica_grouping())
+        dev = s.device
+        M, N, K = args.m, args.n, args.k
+        result = {"world": world}
+
+        def timed(fn, iters=10):
+            for _ in range(3):
+                fn()
+            dist.barrier()
+            torch.cuda.synchronize()
+            st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            st.record()
+            for _ in range(iters):
+                fn()
+            en.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([st.elapsed_time(en) / iters], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t)
+
+        torch.manual_seed(100 + rank)
+        # --- reduce-scatter: every rank holds a K-slice of the contraction -------------------------------------------
+        a = (torch.randn(M, K, device=dev) * 0.1).bfloat16()
+        w = (torch.randn(K, N, device=dev) * 0.1).bfloat16()
+        full = a.float() @ w.float()
+        dist.all_reduce(full)
+        mine = fused.gemm_reduce_scatter(ctx, a, w)
+        assert mine is not NotImplemented
+        torch.cuda.synchronize()
+        want = full[rank * (M // world):(rank + 1) * (M // world)]
+        result["rs_err"] = float((mine.float() - want).abs().max() / want.abs().max())
+        result["rs_ms"] = timed(lambda: fused.gemm_reduce_scatter(ctx, a, w))
+
+        def nccl_rs():
+            y = a @ w
+            out = torch.empty(M // world, N, device=dev, dtype=y.dtype)
+            dist.reduce_scatter_tensor(out, y)
+            return out
+
+        result["rs_nccl_ms"] = timed(nccl_rs)
+        result["gemm_ms"] = timed(lambda: native.gemm(a, w))
+        # --- all-gather of the left operand (rows sharded) ---------------------------------------------------------------
+        a_full, a_own = fused.gathered_operand(ctx, M, K, torch.bfloat16, 128, "a")
+        a_own.copy_((torch.randn(M // world, K, device=dev) * 0.1).bfloat16())
+        gathered = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(gathered, a_own.contiguous())
+        # poison the remote rows so that stale data cannot pass
+        for r in range(world):
+            if r != rank:
+                a_full[r * (M // world):(r + 1) * (M // world)].fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()
+        y = fused.all_gather_gemm(ctx, a_full, w, sharded="a", n_copy=args.n_copy)
+        assert y is not NotImplemented
+        torch.cuda.synchronize()
+        want = gathered.float() @ w.float()
+        result["ag_a_err"] = float((y.float() - want).abs().max() / want.abs().max())
+        result["ag_a_gathered_ok"] = bool(torch.equal(a_full, gathered))
+        result["ag_a_ms"] = timed(lambda: fused.all_gather_gemm(ctx, a_full, w, sharded="a", n_copy=args.n_copy))
+
+        def nccl_ag():
+            g = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+            dist.all_gather_into_tensor(g, a_own)
+            return g @ w
+
+        result["ag_a_nccl_ms"] = timed(nccl_ag)
+        # --- all-gather of the right operand (a weight whose K rows are sharded) -------------------------------------------
+        w_full, w_own = fused.gathered_operand(ctx, K, N, torch.bfloat16, 64, "w")
+        w_own.copy_((torch.randn(K // world, N, device=dev) * 0.1).bfloat16())
+        wg = torch.empty(K, N, device=dev, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(wg, w_own.contiguous())
+        for r in range(world):
+            if r != rank:
+                w_full[r * (K // world):(r + 1) * (K // world)].fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()
+        y = fused.all_gather_gemm(ctx, a, w_full, sharded="b", n_copy=args.n_copy)
+        assert y is not NotImplemented
+        torch.cuda.synchronize()
+        want = a.float() @ wg.float()
+        result["ag_b_err"] = float((y.float() - want).abs().max() / want.abs().max())
+        result["ag_b_gathered_ok"] = bool(torch.equal(w_full, wg))
+        result["ag_b_ms"] = timed(lambda: fused.all_gather_gemm(ctx, a, w_full, sharded="b", n_copy=args.n_copy))
+        try:
+            ctx.check()
+            native.check_gemm_errors()
+            result["errors"] = None
+        except Exception as e:  # a bounded wait gave up
+            result["errors"] = str(e)
+        result["shape"] = [M, N, K]
+        if rank == 0:
+            print(json.dumps(result))
     elif args.mode == "fail":
         # rank 1 stops between steps; rank 0 notices on the host before launching anything that would wait for it
         from datetime import timedelta

@@ -47,6 +47,49 @@ def test_gq_gemm_small_m(nat, dtype, M, N, K, gs):
     torch.testing.assert_close(y2.float(), want - bias.float(), rtol=2e-2, atol=2e-2 * math.sqrt(K / 256))
 
 
+@pytest.mark.parametrize("ksplit", [1, 3, None])
+def test_gq_gemm_small_m_windows_split_k_and_gelu(nat, ksplit):
+    """Input and output as column windows of wider buffers, K split over several CTAs (twice in a row: the scratch must
+    come back zeroed), GELU on the upper output columns, fp16 scales with bf16 activations."""
+    from popxl_addons_b200.models.generator import quantize_rows
+
+    torch.manual_seed(3)
+    M, N, K, gs = 16, 1000, 3072, 64
+    w = torch.randn(N, K, device="cuda") * 0.05
+    packed, scale, zero = quantize_rows(w, gs)
+    scale, zero = scale.half(), zero.half()
+    xbuf = (torch.randn(M, K + 512, device="cuda") * 0.5).bfloat16()
+    ybuf = torch.zeros(M, N + 256, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(N, device="cuda").bfloat16()
+    p = packed.to(torch.int32) & 0xFFFF
+    codes = torch.stack([(p >> 12) & 15, (p >> 8) & 15, (p >> 4) & 15, p & 15], dim=-1).float().reshape(N, K // gs, gs)
+    deq = (codes * scale.float() + zero.float()).bfloat16().float().reshape(N, K)
+    want = xbuf[:, 256:256 + K].float() @ deq.t() + bias.float()
+    want[:, 600:] = torch.nn.functional.gelu(want[:, 600:])
+    for _ in range(2):
+        y = nat.gq_gemm_small_m(xbuf[:, 256:256 + K], packed, scale, zero, bias, out=ybuf[:, 128:128 + N],
+                                act_from_col=600, ksplit=ksplit)
+        assert y is not NotImplemented
+        torch.testing.assert_close(ybuf[:, 128:128 + N].float(), want, rtol=2e-2, atol=6e-2)
+    assert float(ybuf[:, :128].abs().sum()) == 0 and float(ybuf[:, 128 + N:].abs().sum()) == 0
+
+
+def test_add_layer_norm(nat):
+    torch.manual_seed(4)
+    x = torch.randn(16, 4096, device="cuda").bfloat16()
+    delta, bias = torch.randn_like(x), torch.randn(4096, device="cuda").bfloat16()
+    w, b = torch.randn(4096, device="cuda").bfloat16(), torch.randn(4096, device="cuda").bfloat16()
+    ref = _ref("add_layer_norm_")
+    for has_delta, has_bias in [(True, True), (True, False), (False, False)]:
+        x1, x2 = x.clone(), x.clone()
+        args = ([delta] if has_delta else []) + ([bias] if has_bias else []) + [w, b]
+        h = nat.add_layer_norm_cuda(x1, *args, has_delta=has_delta, has_bias=has_bias, eps=1e-5)
+        want = ref(x2, *args, has_delta=has_delta, has_bias=has_bias, eps=1e-5)
+        assert h is not NotImplemented
+        torch.testing.assert_close(x1.float(), x2.float(), rtol=1e-2, atol=1e-2)
+        torch.testing.assert_close(h.float(), want.float(), rtol=2e-2, atol=3e-2)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("B,H,D,R,S,pos", [(16, 2, 256, 64, 640, 512), (3, 4, 64, 32, 128, 0), (2, 16, 128, 0, 300, 299)])
 def test_rotary_append_and_attention_decode(nat, dtype, B, H, D, R, S, pos):
@@ -71,6 +114,14 @@ def test_rotary_append_and_attention_decode(nat, dtype, B, H, D, R, S, pos):
     assert a is not NotImplemented
     want = _ref("attention_decode_packed")(qkv.float(), k.float(), v.float(), p, H, D, scale)
     torch.testing.assert_close(a.float(), want, **tol)
+    # same, with query and result inside a wider buffer (twice: the split counters must come back zeroed)
+    buf = torch.zeros(B, 3 * H * D + 64, device="cuda", dtype=dtype)
+    buf[:, :3 * H * D] = qkv
+    for _ in range(2):
+        res = nat.attention_decode_into_cuda(buf, k, v, p, H, D, 2 * H * D, scale)
+        assert res is not NotImplemented
+        torch.testing.assert_close(buf[:, 2 * H * D:3 * H * D].float(), want, **tol)
+    torch.testing.assert_close(buf[:, :2 * H * D], qkv[:, :2 * H * D])
 
 
 def test_argmax_store_row_advance(nat):
@@ -113,7 +164,7 @@ def test_generation_on_gpu_matches_cpu_backend(cuda_graphs):
     cpu = DecoderGenerator(cfg, B, P, N, gs, device="cpu", cuda_graphs=False)
     cpu.load_dense(w)
     want = cpu.generate(prompt)
-    before = dict(native.LAUNCHES)
+    before = dict(native.LAUNCHES["by_kernel"])
     gpu = DecoderGenerator(cfg, B, P, N, gs, device="cuda", cuda_graphs=cuda_graphs)
     gpu.load_dense(w)
     got = gpu.generate(prompt)
@@ -123,6 +174,6 @@ def test_generation_on_gpu_matches_cpu_backend(cuda_graphs):
     # first tokens agree everywhere and that most sequences agree completely.
     np.testing.assert_array_equal(got[:, 0], want[:, 0])
     assert (got == want).all(axis=1).mean() >= 0.5
-    for k in ("gq_gemm_small_m", "attn_decode", "rotary_append", "argmax_rows"):
-        assert native.LAUNCHES.get(k, 0) > before.get(k, 0), f"{k} kernel did not run"
+    for k in ("gq_gemm_small_m", "attn_decode", "rotary_append", "argmax_rows", "add_layer_norm"):
+        assert native.LAUNCHES["by_kernel"].get(k, 0) > before.get(k, 0), f"{k} kernel did not run"
     assert gpu.decode_ms() > 0
