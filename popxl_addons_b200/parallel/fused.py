@@ -210,8 +210,8 @@ def small_all_reduce_16bit(ctx: GroupContext, t: torch.Tensor) -> Optional[torch
 class FusedComm(DistComm):
     """NCCL transport with small reductions served by the one-shot NVLink kernels."""
 
-    def __init__(self, num_replicas: int, device: torch.device, session):
-        super().__init__(num_replicas, device)
+    def __init__(self, num_replicas: int, device: torch.device, session, devices_per_replica: int = 1):
+        super().__init__(num_replicas, device, devices_per_replica)
         self._session = session
 
     def all_reduce(self, vals, grouping, op, inplace=False):

@@ -32,6 +32,21 @@ from ..xl.ops.control import CallSiteInfo
 __all__ = ["pipelined_execution", "Pipelining", "StageContext", "Stash", "Restore"]
 
 
+def _placeholder(orig: xl.Tensor) -> xl.Tensor:
+    """Zero tensor standing in for `orig` in cycles where its producer has not run yet (same device slot)."""
+    v = ops.init(orig.shape, orig.dtype, orig.name.split("/")[-1] + "_dummy", "zero")
+    v.device_index = orig.device_index
+    v.producer.device_index = orig.device_index
+    return v
+
+
+def _input_like(t: xl.Tensor, by_ref: bool = False) -> xl.Tensor:
+    """Graph input standing for `t`, on the same device slot."""
+    g_in = xl.graph_input(t.shape, t.dtype, t.name.split("/")[-1], by_ref=by_ref, meta_shape=t.meta_shape)
+    g_in.device_index = t.device_index
+    return g_in
+
+
 class _Part:
     """One piece of the pipeline (a stage's compute, or the copy graph) as a graph plus the original tensors its
     inputs and outputs stand for."""
@@ -50,7 +65,7 @@ class _Part:
                     v = orig
                 else:
                     # produced by a part that has not run yet in this ramp-up cycle: placeholder
-                    v = ops.init(orig.shape, orig.dtype, orig.name.split("/")[-1] + "_dummy", "zero")
+                    v = _placeholder(orig)
                     cur[orig] = v
             inputs[g_in] = v
         outs = ops.call(self.graph, inputs_dict=inputs)
@@ -84,8 +99,7 @@ class Pipelining:
                     continue
                 if t not in part.inputs:
                     with g:
-                        part.inputs[t] = xl.graph_input(t.shape, t.dtype, t.name.split("/")[-1], by_ref=True,
-                                                        meta_shape=t.meta_shape)
+                        part.inputs[t] = _input_like(t, by_ref=True)
                 op.inputs[i] = part.inputs[t]
             op.graph = g
             g.ops.append(op)
@@ -169,10 +183,9 @@ class Pipelining:
             with loop:
                 lcur: Dict[xl.Tensor, xl.Tensor] = {}
                 for t in cross:
-                    lcur[t] = xl.graph_input(t.shape, t.dtype, t.name.split("/")[-1], meta_shape=t.meta_shape)
+                    lcur[t] = _input_like(t)
                 for e in externals:
-                    lcur[e] = xl.graph_input(e.shape, e.dtype, e.name.split("/")[-1], by_ref=True,
-                                             meta_shape=e.meta_shape)
+                    lcur[e] = _input_like(e, by_ref=True)
                 self.cycle(0, S, lcur)
                 for t in cross:
                     v = lcur[t]
@@ -182,7 +195,7 @@ class Pipelining:
             carried = []
             for t in cross:
                 if t not in cur:
-                    cur[t] = ops.init(t.shape, t.dtype, t.name.split("/")[-1] + "_dummy", "zero")
+                    cur[t] = _placeholder(t)
                 carried.append(cur[t])
             outs = ops.repeat(loop, self.steps - (S - 1), *carried, *externals)
             for t, o in zip(cross, outs):

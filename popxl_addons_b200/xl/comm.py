@@ -94,7 +94,7 @@ class DistComm:
 
     _REDUCE = {"add": "SUM", "max": "MAX", "min": "MIN", "mul": "PRODUCT", "mean": "SUM"}
 
-    def __init__(self, num_replicas: int, device: torch.device):
+    def __init__(self, num_replicas: int, device: torch.device, devices_per_replica: int = 1):
         import torch.distributed as dist
 
         if not dist.is_initialized():
@@ -107,12 +107,16 @@ class DistComm:
             dist.init_process_group(backend=backend, device_id=device if device.type == "cuda" else None,
                                     timeout=timeout)
         self.dist = dist
-        self.rank = dist.get_rank()
+        self.world_rank = dist.get_rank()
         self.world_size = dist.get_world_size()
-        if num_replicas != self.world_size:
-            raise ValueError(f"replication_factor={num_replicas} must equal the number of processes "
-                             f"{self.world_size} (one replica per process)")
+        self.slots = int(devices_per_replica)  # processes per replica (pipeline device slots)
+        if num_replicas * self.slots != self.world_size:
+            raise ValueError(f"replication_factor={num_replicas} x devices_per_replica={self.slots} must equal the "
+                             f"number of processes {self.world_size}")
+        self.rank = self.world_rank // self.slots  # replica index of this process
+        self.slot = self.world_rank % self.slots
         self.num_replicas = num_replicas
+        self._p2p: list = []
         self.device = device
         self._groups: Dict[tuple, object] = {}
 
@@ -122,12 +126,14 @@ class DistComm:
         if key not in self._groups:
             mine = None
             for members in grouping.groups:
-                if len(members) == self.world_size:
-                    pg = self.dist.group.WORLD
-                else:
-                    pg = self.dist.new_group(ranks=list(members))
-                if self.rank in members:
-                    mine = (pg, list(members))
+                for slot in range(self.slots):  # the same slot of every member replica forms one process group
+                    ranks = [m * self.slots + slot for m in members]
+                    if len(ranks) == self.world_size:
+                        pg = self.dist.group.WORLD
+                    else:
+                        pg = self.dist.new_group(ranks=ranks)
+                    if self.rank in members and slot == self.slot:
+                        mine = (pg, list(members))
             self._groups[key] = mine
         return self._groups[key]
 
@@ -139,6 +145,23 @@ class DistComm:
             if op == "mean":
                 t.div_(len(members))
         return [t]
+
+    # -- point-to-point between the device slots of one replica (pipeline stage boundaries) ------------------------
+    def send_to_slot(self, t: torch.Tensor, slot: int):
+        self._p2p.append(self.dist.P2POp(self.dist.isend, t.contiguous(), self.rank * self.slots + slot))
+
+    def recv_from_slot(self, shape, dtype, slot: int) -> torch.Tensor:
+        t = torch.empty(tuple(shape), dtype=dtype, device=self.device)
+        self._p2p.append(self.dist.P2POp(self.dist.irecv, t, self.rank * self.slots + slot))
+        return t
+
+    def flush_p2p(self):
+        """Issue all queued sends and receives as one batch (concurrent, so their order between ranks cannot
+        deadlock) and order them before whatever this rank launches next."""
+        if self._p2p:
+            ops, self._p2p = self._p2p, []
+            for w in self.dist.batch_isend_irecv(ops):
+                w.wait()
 
     def reduce_scatter(self, vals, grouping, op):
         pg, members = self.group_for(grouping)

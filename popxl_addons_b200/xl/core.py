@@ -304,7 +304,8 @@ class Tensor:
         scope = current_scope()
         full = f"{scope}/{base}" if scope else base
         self.id = graph._unique_tensor_id(full)
-        self.device_index = current_device()
+        # an op's outputs live where the op runs; other tensors where the enclosing `ipu(...)` context says
+        self.device_index = producer.device_index if producer is not None else current_device()
         self.tile_set = current_tile_set()
         graph._tensors.append(self)
 
@@ -512,7 +513,7 @@ class TensorByRef(Tensor):
 class Op:
     """One recorded operation: `outputs = opdef(inputs, **attrs)`."""
 
-    __slots__ = ("opdef", "inputs", "outputs", "attrs", "graph", "name", "device_index", "tile_set", "stage",
+    __slots__ = ("opdef", "inputs", "outputs", "attrs", "graph", "name", "device_index", "device_explicit", "tile_set", "stage",
                  "debug", "uid", "attrs_hint", "__weakref__")
     _counter = itertools.count()
 
@@ -523,7 +524,14 @@ class Op:
         self.attrs: Dict[str, Any] = attrs
         self.graph = graph
         self.name = opdef.name
-        self.device_index = current_device()
+        # device slot: the enclosing `ipu(...)` context if there is one; otherwise the op follows its operands
+        # (ops that transforms create outside any context, e.g. stash updates or gradient accumulation)
+        self.device_explicit = bool(_STATE.devices)
+        if _STATE.devices:
+            self.device_index = _STATE.devices[-1]
+        else:
+            on = [t.device_index for t in self.inputs if not isinstance(t, Constant)]
+            self.device_index = max(on) if on else 0
         self.tile_set = current_tile_set()
         self.stage = None
         self.debug = None
@@ -675,7 +683,11 @@ class Ir:
     environment: one replica per process, one process per GPU.
     """
 
-    def __init__(self, replication: Union[int, str] = 1):
+    def __init__(self, replication: Union[int, str] = 1, devices_per_replica: int = 1):
+        """`devices_per_replica` > 1 with `replication="popdist"`: every replica spans that many processes / GPUs, one
+        per device slot (`ipu(i)`, a pipeline stage); process `rank` hosts slot `rank % devices_per_replica` of
+        replica `rank // devices_per_replica`."""
+        self.devices_per_replica = int(devices_per_replica)
         self.graphs: List[Graph] = []
         self._graph_counter = itertools.count()
         self.main_graph = Graph(self, "main")
@@ -685,7 +697,10 @@ class Ir:
             import os
 
             self.distributed = True
-            self._replication_factor = int(os.environ.get("WORLD_SIZE", "1"))
+            world = int(os.environ.get("WORLD_SIZE", "1"))
+            if world % self.devices_per_replica:
+                raise ValueError(f"WORLD_SIZE={world} is not a multiple of devices_per_replica={devices_per_replica}")
+            self._replication_factor = world // self.devices_per_replica
         else:
             self._replication_factor = int(replication)
         self.num_host_transfers = 1

@@ -148,11 +148,20 @@ def _vjp_call(ctx, op, gs):
 OpDef("call", infer=_infer_call, special=_special_call, vjp=_vjp_call)
 
 
+def _place_outputs(outs, graph: Graph):
+    """Device slot of a call's results: the slot the call was placed on explicitly (`with ipu(i)`), else wherever the
+    called graph produces them (a graph may span slots, e.g. the copy graph of a pipeline)."""
+    if outs and not outs[0].producer.device_explicit:
+        for o, go in zip(outs, graph._outputs):
+            o.device_index = go.device_index
+
+
 def call_with_info(graph: Graph, *inputs, inputs_dict: Optional[Mapping[Tensor, Tensor]] = None,
                    check_inputs: bool = True) -> CallSiteInfo:
     """Call `graph`. Positional inputs fill, in order, the graph inputs that `inputs_dict` does not cover."""
     resolved = _resolve_inputs(graph, inputs, inputs_dict)
     outs = emit("call", resolved, {"graph": graph}, [t.id.split("/")[-1] for t in graph._outputs])
+    _place_outputs(outs, graph)
     return CallSiteInfo(outs[0].producer if outs else gcg().ops[-1])
 
 
@@ -187,6 +196,7 @@ def repeat_with_info(graph: Graph, repeat_count: int, *inputs,
         raise ValueError("A repeated graph cannot have more outputs than inputs")
     outs = emit("repeat", resolved, {"graph": graph, "count": int(repeat_count), "cuda_graph": bool(cuda_graph)},
                 [t.id.split("/")[-1] for t in graph._outputs])
+    _place_outputs(outs, graph)
     return CallSiteInfo(outs[0].producer if outs else gcg().ops[-1])
 
 

@@ -46,15 +46,20 @@ class Session:
         self.num_replicas = ir.replication_factor
         if use_native is None:
             use_native = os.environ.get("XL_NATIVE", "1") != "0"
+        self.slots = int(getattr(ir, "devices_per_replica", 1)) if self.distributed else 1
+        self.slot: Optional[int] = None  # device slot (pipeline stage GPU) this process executes; None: all of them
+        self._frame_dev: List[Optional[int]] = []
         if self.distributed:
             if use_native and self.device.type == "cuda":
                 from ..parallel.fused import FusedComm
 
-                self.comm = FusedComm(self.num_replicas, self.device, self)
+                self.comm = FusedComm(self.num_replicas, self.device, self, devices_per_replica=self.slots)
             else:
-                self.comm = DistComm(self.num_replicas, self.device)
+                self.comm = DistComm(self.num_replicas, self.device, devices_per_replica=self.slots)
             self.num_local = 1
             self.replica_offset = self.comm.rank
+            if self.slots > 1:
+                self.slot = self.comm.slot
         else:
             self.comm = SimComm(self.num_replicas)
             self.num_local = self.num_replicas
@@ -146,10 +151,54 @@ class Session:
             else:
                 self._vars[var] = [v.to(self.device, copy=True) for v in vals]
 
+    def _variable_slots(self) -> Dict[Variable, set]:
+        """Device slots whose ops read or write each variable (following call sites into the called graphs)."""
+        owners: Dict[Variable, set] = {}
+
+        def walk(graph, binding, frame):
+            for op in graph.ops:
+                dev = self._effective_device(op, frame)
+                sub = op.attrs.get("graph") if op.opdef.name in ("call", "repeat") else None
+                if sub is not None:
+                    inner = {gi: binding.get(t, t) for gi, t in zip(sub._inputs, op.inputs)}
+                    walk(sub, inner, dev if op.device_explicit else frame)
+                    continue
+                if op.opdef.name == "conditional":
+                    for key in ("then_graph", "else_graph"):
+                        g2 = op.attrs[key]
+                        inner = {gi: binding.get(t, t) for gi, t in zip(g2._inputs, op.inputs[1:])}
+                        walk(g2, inner, dev if op.device_explicit else frame)
+                    continue
+                for t in op.inputs:
+                    root = binding.get(t, t)
+                    if isinstance(root, Variable):
+                        owners.setdefault(root, set()).add(dev)
+        walk(self.ir.main_graph, {}, None)
+        return owners
+
+    @staticmethod
+    def _effective_device(op, frame: Optional[int]) -> int:
+        """Ops placed explicitly (`with ipu(i)`) run there; other ops run where the enclosing explicitly placed call
+        runs, or, outside any such call, where their operands live."""
+        if op.device_explicit or frame is None:
+            return op.device_index
+        return frame
+
+    def owns(self, var: Variable) -> bool:
+        """Whether this process holds `var` (always true unless replicas span several processes)."""
+        return self.slot is None or var in self._vars or var.remote_buffer is not None
+
     def _init_state(self):
         for rb in self.ir.remote_buffers:
             self._alloc_buffer(rb)
         deferred = []
+        skip = set()
+        if self.slot is not None:
+            owners = self._variable_slots()
+            for var in self.ir.initial_values:
+                slots = owners.get(var) or {var.device_index}
+                if self.slot not in slots:
+                    skip.add(var)
         if self.distributed and self.use_native:
             from ..parallel.fused import runtime
 
@@ -157,6 +206,8 @@ class Session:
                 if var.symmetric_group is not None and var.remote_buffer is None:
                     runtime(self).reserve(var.symmetric_group, var.nelms * var.dtype.itemsize)
         for var, host in self.ir.initial_values.items():
+            if var in skip:
+                continue
             if isinstance(host, LazyInit) and host.kind == "copy":
                 deferred.append((var, host))  # copies are made once their source exists
             else:
@@ -328,7 +379,20 @@ class Session:
             slabs[r][i].copy_(vals[r].reshape(rb.tensor_shape), non_blocking=True)
 
     def device_copy(self, vals, op):
-        return vals
+        """Stage-boundary copy. One process per device slot: the source slot queues a send, the destination slot a
+        receive (issued together, see `DistComm.flush_p2p`); elsewhere all slots share this process's memory."""
+        if self.slot is None:
+            return vals
+        src, dst = op.attrs["source"], op.attrs["destination"]
+        if src == dst:
+            return vals
+        if self.slot == src:
+            self.comm.send_to_slot(vals[0], dst)
+            return None
+        if self.slot == dst:
+            out = op.outputs[0]
+            return [self.comm.recv_from_slot(out.shape, out.dtype.as_torch(), src)]
+        return None
 
     def record_timestamp(self, name: str):
         if self.device.type == "cuda":
@@ -398,14 +462,42 @@ class Session:
         if isinstance(t, Variable):
             if t.remote_buffer is not None:
                 raise RuntimeError(f"{t} is a remote variable: read it with ops.remote_load")
+            if self.slot is not None and t not in self._vars:
+                return None
             return self._vars[t]
+        if self.slot is not None:
+            return None  # lives on another device slot (another process)
         raise KeyError(f"Tensor {t} has no value: it was used before being produced, or belongs to another graph")
 
     def _exec_ops(self, graph: Graph, env: Dict[Tensor, List[torch.Tensor]]):
         frees = self._last_uses(graph)
         native_dev = self.device.type if self.use_native else None
+        staged = self.slot is not None
+        frame = self._frame_dev[-1] if self._frame_dev else None
         for i, op in enumerate(graph.ops):
             od = op.opdef
+            if staged:
+                name = od.name
+                if name in ("call", "repeat", "conditional"):
+                    # control flow runs everywhere; what it calls is filtered op by op
+                    self.comm.flush_p2p()
+                    for t in op.inputs:
+                        if t not in env:
+                            env[t] = self._value(t, env)
+                    self._frame_dev.append(self._effective_device(op, frame) if op.device_explicit else frame)
+                    try:
+                        od.special(self, op, env)
+                    finally:
+                        self._frame_dev.pop()
+                    self._free_dead(frees, i, env)
+                    continue
+                if name == "ipu_copy":
+                    env[op.outputs[0]] = self.device_copy(env.get(op.inputs[0]), op)
+                    self._free_dead(frees, i, env)
+                    continue
+                if self._effective_device(op, frame) != self.slot:
+                    continue
+                self.comm.flush_p2p()  # received tensors may be read from here on
             if od.special is not None:
                 for t in op.inputs:
                     if t not in env:
@@ -425,10 +517,16 @@ class Session:
                     outs_per_replica.append((res,) if isinstance(res, torch.Tensor) else tuple(res or ()))
                 for j, t in enumerate(op.outputs):
                     env[t] = [outs_per_replica[r][j] for r in range(self.num_local)]
-            dead = frees.get(i)
-            if dead:
-                for t in dead:
-                    env.pop(t, None)
+            self._free_dead(frees, i, env)
+        if staged:
+            self.comm.flush_p2p()
+
+    @staticmethod
+    def _free_dead(frees, i, env):
+        dead = frees.get(i)
+        if dead:
+            for t in dead:
+                env.pop(t, None)
 
     def run_graph(self, graph: Graph, inputs: List[List[torch.Tensor]]) -> List[List[torch.Tensor]]:
         env = dict(zip(graph._inputs, inputs))

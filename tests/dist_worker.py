@@ -31,6 +31,7 @@ def main():
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--n-copy", type=int, default=8)
+    ap.add_argument("--slots", type=int, default=2)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -195,6 +196,50 @@ def main():
         result["shape"] = [M, N, K]
         if rank == 0:
             print(json.dumps(result))
+    elif args.mode == "pipeline":
+        # a replica spans `--slots` processes: forward on slot 0, loss term on slot 1, backward on slot 0 again;
+        # stage boundaries are send/recv between the processes, replicas are data-parallel (gradient all-reduce)
+        from popxl_addons_b200 import xl as popxl
+        from popxl_addons_b200.xl import ops
+        import popxl_addons_b200 as addons
+        from popxl_addons_b200.layers import Linear
+
+        steps, slots = 6, args.slots
+        np.random.seed(42)
+        ir = popxl.Ir(replication="popdist", devices_per_replica=slots)
+        R = ir.replication_factor
+        data = np.random.normal(0, 1, (steps, R, 1, 4)).astype(np.float32)
+        with ir.main_graph:
+            with addons.pipelined_execution(steps) as p:
+                with p.stage(0), popxl.ipu(0):
+                    _, x_stream, x = addons.host_load(data[0, 0], popxl.float32, "x")
+                    fargs, lin = Linear(4).create_graph(x)
+                    dargs, dlin = addons.autodiff_with_accumulation(lin, [lin.args.weight])
+                    w, dw = fargs.init(), dargs.init()
+                    info = lin.bind(w).call_with_info(x)
+                    y, *_ = info.outputs
+                    y = y.copy_to_ipu(1)
+                with p.stage(1), popxl.ipu(1):
+                    scale = popxl.variable(np.full((4,), 2.0, np.float32), name="scale")
+                    y = y * scale + 1
+                    y = y.copy_to_ipu(0)
+                with p.stage(2), popxl.ipu(0):
+                    dlin.bind(dw).call(y, args=p.stash_and_restore_activations(info, dlin.grad_graph_info))
+            with popxl.ipu(0):
+                g = ops.collectives.replicated_all_reduce(dw.accum.weight, "mean", ir.replica_grouping())
+                out = addons.host_store(g)
+        ir.num_host_transfers = steps
+        s = popxl.Session(ir, args.device)
+        replica, slot = rank // slots, rank % slots
+        res = s.run({x_stream: data[:, replica]})
+        owned = {"w": s.owns(w.weight), "dw": s.owns(dw.accum.weight), "scale": s.owns(scale)}
+        payload = {"rank": rank, "slot": slot, "owned": owned}
+        if slot == 0:
+            payload["grad"] = np.asarray(res[out]).reshape(-1).tolist()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, payload)
+        if rank == 0:
+            print(json.dumps({"ranks": gathered, "data_seed": 42}))
     elif args.mode == "fail":
         # rank 1 stops between steps; rank 0 notices on the host before launching anything that would wait for it
         from datetime import timedelta

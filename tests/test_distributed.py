@@ -99,3 +99,41 @@ def test_gpu_gemm_reduce_scatter_and_all_gather_gemm():
     assert res["errors"] is None
     assert res["rs_err"] < 2e-2 and res["ag_a_err"] < 2e-2 and res["ag_b_err"] < 2e-2
     assert res["ag_a_gathered_ok"] and res["ag_b_gathered_ok"]
+
+
+@pytest.mark.parametrize("nproc", [2, 4])
+def test_pipeline_stages_on_separate_processes(nproc):
+    """A replica spanning two processes (one per device slot, stage boundaries as send/recv) must produce the gradients
+    of the same program run sequentially; with 4 processes two such replicas average their gradients."""
+    from popxl_addons_b200 import xl as popxl
+    import popxl_addons_b200 as addons
+    from popxl_addons_b200.layers import Linear
+
+    steps, R = 6, nproc // 2
+    np.random.seed(42)
+    data = np.random.normal(0, 1, (steps, R, 1, 4)).astype(np.float32)
+    grads = []
+    for r in range(R):
+        np.random.seed(42)
+        np.random.normal(0, 1, (steps, R, 1, 4))  # same generator position as in the workers
+        ir = popxl.Ir()
+        with ir.main_graph:
+            _, x_stream, x = addons.host_load(data[0, 0], popxl.float32, "x")
+            fargs, lin = Linear(4).create_graph(x)
+            dargs, dlin = addons.autodiff_with_accumulation(lin, [lin.args.weight])
+            w, dw = fargs.init(), dargs.init()
+            info = lin.bind(w).call_with_info(x)
+            y, *_ = info.outputs
+            y = y * 2.0 + 1
+            dlin.bind(dw).call(y, args=dlin.grad_graph_info.inputs_dict(info))
+        with popxl.Session(ir, "cpu") as s:
+            for n in range(steps):
+                s.run({x_stream: data[n, r]})
+        grads.append(s.get_tensor_data(dw.accum.weight).copy())
+    want = np.mean(grads, axis=0).reshape(-1)
+    res = launch(nproc, "--mode", "pipeline", "--slots", "2", timeout=240)
+    for info in res["ranks"]:
+        assert info["owned"] == ({"w": True, "dw": True, "scale": False} if info["slot"] == 0 else
+                                 {"w": False, "dw": False, "scale": True})
+        if info["slot"] == 0:
+            np.testing.assert_allclose(info["grad"], want, rtol=1e-5, atol=1e-6)
