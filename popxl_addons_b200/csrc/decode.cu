@@ -36,144 +36,194 @@ __device__ __forceinline__ void mma_m16n8k16(float (&c)[4], const uint32_t (&a)[
   }
 }
 
-template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
-template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
-}
-template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
-  __half2 v = __floats2half2_rn(lo, hi);
-  return *reinterpret_cast<uint32_t*>(&v);
+// ---- de-quantisation without integer->float conversions ------------------------------------------------------------
+// A nibble n placed in the mantissa of a 16-bit float with a suitable exponent IS the number base + n
+// (bf16: 0x4180 | n << 3 = 16 + n; fp16: 0x5400 | n << 4 = 64 + n). A packed subtraction of the base (exact) and one
+// packed FMA per two weights give n * s + z, rounded once like the reference. The byte shuffles below turn one 32-bit
+// load (two packed words = 8 nibbles, first element of a word in its top nibble) into four registers of two
+// consecutive weights each, low half first.
+template <typename T> struct GqFmt;
+template <> struct GqFmt<__nv_bfloat16> {
+  using T2 = __nv_bfloat162;
+  static constexpr uint32_t MASK = 0x78787878u, MAGIC = 0x41804180u;
+  static constexpr float BASE = 16.f;
+  static __device__ __forceinline__ uint32_t lo(uint32_t w) { return (w << 3) & MASK; }
+  static __device__ __forceinline__ uint32_t hi(uint32_t w) { return (w >> 1) & MASK; }
+  static __device__ __forceinline__ T2 pair(float a) { return __float2bfloat162_rn(a); }
+};
+template <> struct GqFmt<__half> {
+  using T2 = __half2;
+  static constexpr uint32_t MASK = 0xF0F0F0F0u, MAGIC = 0x54005400u;
+  static constexpr float BASE = 64.f;
+  static __device__ __forceinline__ uint32_t lo(uint32_t w) { return (w << 4) & MASK; }
+  static __device__ __forceinline__ uint32_t hi(uint32_t w) { return w & MASK; }
+  static __device__ __forceinline__ T2 pair(float a) { return __float2half2_rn(a); }
+};
+
+// w: two packed words (word 0 in the low half). out[0..1]: weights 0-1, 2-3 of word 0; out[2..3]: the same of word 1.
+template <typename T>
+__device__ __forceinline__ void gq_dequant8(uint32_t w, typename GqFmt<T>::T2 s2, typename GqFmt<T>::T2 z2, uint32_t (&out)[4]) {
+  using F = GqFmt<T>;
+  using T2 = typename F::T2;
+  const uint32_t lo = F::lo(w), hi = F::hi(w);  // low / high nibble of every byte, moved into the mantissa position
+  const uint32_t sel[4] = {0x0501u, 0x0400u, 0x0703u, 0x0602u};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t v = (__byte_perm(hi, lo, sel[i]) & 0x00FF00FFu) | F::MAGIC;
+    T2 r = __hfma2(__hsub2(*reinterpret_cast<T2*>(&v), F::pair(F::BASE)), s2, z2);
+    out[i] = *reinterpret_cast<uint32_t*>(&r);
+  }
 }
 
 // packed: (N, K/gs, gs/4) u16, first element of a word in its top nibble; scale / zero: (N, K/gs).
 // Any assignment of actual k indices to the 16 k-slots of an MMA is valid as long as A and B agree, so each lane
 // keeps the 32 consecutive k values of its 16-byte weight load and feeds them to 8 MMAs, 4 values at a time.
 //
-// Grid (ceil(N / 32), ksplit). The warps of a CTA split the CTA's K range in chunks of 128 and reduce through shared
-// memory. With ksplit > 1 the CTAs of one column tile add their partial sums into an fp32 workspace tile; the last one
-// to arrive (a counter per tile) applies the epilogue, writes y and leaves workspace and counter zeroed for the next
-// launch. Epilogue: + bias, GELU on the columns >= act_from_col. x and y are windows of wider matrices (ldx, ldy).
+// Work = (column tiles of 32) x (K chunks of 128), tile-major, cut into equal contiguous ranges, one per CTA
+// ("stream-K": the grid is sized to the machine, not to the problem, so there is no partial last wave). A CTA walks
+// its range tile by tile; its warps split the chunks of the current tile segment and reduce through shared memory.
+// A segment that covers a whole tile is finished by its CTA; otherwise the CTAs sharing the tile add their partial
+// sums into an fp32 workspace tile and the one that completes the tile's chunk count applies the epilogue and leaves
+// workspace and counter zeroed for the next launch. Epilogue: + bias, GELU on the columns >= act_from_col. x and y are
+// windows of wider matrices (ldx, ldy).
 template <typename T, typename S>
 __global__ void __launch_bounds__(GQ_WARPS * 32, 3)
     gq_gemm_small_m_kernel(const T* __restrict__ x, const uint16_t* __restrict__ packed, const S* __restrict__ scale,
                            const S* __restrict__ zero, const T* __restrict__ bias, T* __restrict__ y, int M, int N, int K,
                            int group_size, long long ldx, long long ldy, int act_from_col, float* __restrict__ ws,
                            unsigned int* __restrict__ counters) {
+  using F = GqFmt<T>;
+  using T2 = typename F::T2;
   __shared__ float red[GQ_WARPS][16][8 * GQ_NT + 1];
-  __shared__ unsigned int is_last;
+  __shared__ unsigned int finish;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int quad = lane >> 2, j = lane & 3;  // quad: row of A / column of B inside a tile; j: k sub-slot
-  const int n_base = blockIdx.x * (8 * GQ_NT);
   const int groups = K / group_size;
-  const int ksplit = gridDim.y;
   constexpr bool BF = std::is_same<T, __nv_bfloat16>::value;
-  float c[GQ_NT][4];
-#pragma unroll
-  for (int t = 0; t < GQ_NT; ++t)
-#pragma unroll
-    for (int e = 0; e < 4; ++e) c[t][e] = 0.f;
-  const int chunks = K / GQ_KCHUNK;
-  const int chunk_begin = (int)((long long)chunks * blockIdx.y / ksplit);
-  const int chunk_end = (int)((long long)chunks * (blockIdx.y + 1) / ksplit);
-  const bool row_lo = quad < M, row_hi = quad + 8 < M;
-  for (int ch = chunk_begin + warp; ch < chunk_end; ch += GQ_WARPS) {
-    const int k_lane = ch * GQ_KCHUNK + j * 32;  // this lane's 32 consecutive k values
-    // weights first (the long-latency loads), then the activations: rows quad and quad+8, 32 values each
-    uint4 wq[GQ_NT];
-    float sc[GQ_NT], zp[GQ_NT];
-    const int g = k_lane / group_size;
-#pragma unroll
-    for (int t = 0; t < GQ_NT; ++t) {
-      const int n = n_base + t * 8 + quad;
-      wq[t] = make_uint4(0, 0, 0, 0);
-      sc[t] = 0.f;
-      zp[t] = 0.f;
-      if (n < N) {
-        wq[t] = *reinterpret_cast<const uint4*>(packed + (long long)n * (K / 4) + k_lane / 4);
-        sc[t] = xl_to_float(scale[(long long)n * groups + g]);
-        zp[t] = xl_to_float(zero[(long long)n * groups + g]);
-      }
-    }
-    uint4 xa[4], xb[4];
-    const uint4 zero4 = make_uint4(0, 0, 0, 0);
-#pragma unroll
-    for (int v = 0; v < 4; ++v) {
-      xa[v] = row_lo ? *reinterpret_cast<const uint4*>(x + (long long)quad * ldx + k_lane + v * 8) : zero4;
-      xb[v] = row_hi ? *reinterpret_cast<const uint4*>(x + (long long)(quad + 8) * ldx + k_lane + v * 8) : zero4;
-    }
-    const uint32_t* xa32 = reinterpret_cast<const uint32_t*>(xa);
-    const uint32_t* xb32 = reinterpret_cast<const uint32_t*>(xb);
-#pragma unroll
-    for (int t = 0; t < GQ_NT; ++t) {
-      const uint16_t* w16 = reinterpret_cast<const uint16_t*>(&wq[t]);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        // word i holds k_lane + 4i .. 4i+3
-        const uint32_t w = w16[i];
-        const float v0 = (float)((w >> 12) & 0xF) * sc[t] + zp[t], v1 = (float)((w >> 8) & 0xF) * sc[t] + zp[t];
-        const float v2 = (float)((w >> 4) & 0xF) * sc[t] + zp[t], v3 = (float)(w & 0xF) * sc[t] + zp[t];
-        const uint32_t b[2] = {pack2<T>(v0, v1), pack2<T>(v2, v3)};
-        const uint32_t a[4] = {xa32[2 * i], xb32[2 * i], xa32[2 * i + 1], xb32[2 * i + 1]};
-        mma_m16n8k16(c[t], a, b, BF);
-      }
-    }
-  }
-  // reduce the K slices of the warps through shared memory
-#pragma unroll
-  for (int t = 0; t < GQ_NT; ++t) {
-    red[warp][quad][t * 8 + 2 * j] = c[t][0];
-    red[warp][quad][t * 8 + 2 * j + 1] = c[t][1];
-    red[warp][quad + 8][t * 8 + 2 * j] = c[t][2];
-    red[warp][quad + 8][t * 8 + 2 * j + 1] = c[t][3];
-  }
-  __syncthreads();
   constexpr int TILE = 16 * 8 * GQ_NT;
-  float* wtile = ws + (long long)blockIdx.x * TILE;
-  if (ksplit > 1) {
-    for (int idx = threadIdx.x; idx < TILE; idx += blockDim.x) {
-      const int r = idx / (8 * GQ_NT), col = idx % (8 * GQ_NT);
-      if (r < M && n_base + col < N) {
-        float acc = 0.f;
+  const int chunks = K / GQ_KCHUNK;
+  const int n_tiles = (N + 8 * GQ_NT - 1) / (8 * GQ_NT);
+  const long long total = (long long)n_tiles * chunks;
+  long long item = total * blockIdx.x / gridDim.x;
+  const long long item_end = total * (blockIdx.x + 1) / gridDim.x;
+  const bool row_lo = quad < M, row_hi = quad + 8 < M;
+  while (item < item_end) {
+    const int tile = (int)(item / chunks);
+    const int c0 = (int)(item - (long long)tile * chunks);
+    const int c1 = (int)min((long long)chunks, c0 + (item_end - item));
+    const int n_base = tile * (8 * GQ_NT);
+    float c[GQ_NT][4];
 #pragma unroll
-        for (int w = 0; w < GQ_WARPS; ++w) acc += red[w][r][col];
-        atomicAdd(wtile + idx, acc);
+    for (int t = 0; t < GQ_NT; ++t)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) c[t][e] = 0.f;
+    for (int ch = c0 + warp; ch < c1; ch += GQ_WARPS) {
+      const int k_lane = ch * GQ_KCHUNK + j * 32;  // this lane's 32 consecutive k values
+      // weights first (the long-latency loads), then the activations: rows quad and quad+8, 32 values each
+      uint4 wq[GQ_NT];
+      T2 s2[GQ_NT], z2[GQ_NT];
+      const int g = k_lane / group_size;
+#pragma unroll
+      for (int t = 0; t < GQ_NT; ++t) {
+        const int n = n_base + t * 8 + quad;
+        wq[t] = make_uint4(0, 0, 0, 0);
+        float sc = 0.f, zp = 0.f;
+        if (n < N) {
+          wq[t] = __ldcs(reinterpret_cast<const uint4*>(packed + (long long)n * (K / 4) + k_lane / 4));
+          sc = xl_to_float(scale[(long long)n * groups + g]);
+          zp = xl_to_float(zero[(long long)n * groups + g]);
+        }
+        s2[t] = F::pair(sc);
+        z2[t] = F::pair(zp);
+      }
+      uint4 xa[4], xb[4];
+      const uint4 zero4 = make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        xa[v] = row_lo ? *reinterpret_cast<const uint4*>(x + (long long)quad * ldx + k_lane + v * 8) : zero4;
+        xb[v] = row_hi ? *reinterpret_cast<const uint4*>(x + (long long)(quad + 8) * ldx + k_lane + v * 8) : zero4;
+      }
+      const uint32_t* xa32 = reinterpret_cast<const uint32_t*>(xa);
+      const uint32_t* xb32 = reinterpret_cast<const uint32_t*>(xb);
+#pragma unroll
+      for (int t = 0; t < GQ_NT; ++t) {
+        const uint32_t* w32 = reinterpret_cast<const uint32_t*>(&wq[t]);
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          // 32-bit word m holds packed words 2m and 2m+1, i.e. k_lane + 8m .. 8m+7
+          uint32_t b[4];
+          gq_dequant8<T>(w32[m], s2[t], z2[t], b);
+          const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
+          const uint32_t a0[4] = {xa32[4 * m], xb32[4 * m], xa32[4 * m + 1], xb32[4 * m + 1]};
+          const uint32_t a1[4] = {xa32[4 * m + 2], xb32[4 * m + 2], xa32[4 * m + 3], xb32[4 * m + 3]};
+          mma_m16n8k16(c[t], a0, b0, BF);
+          mma_m16n8k16(c[t], a1, b1, BF);
+        }
       }
     }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) is_last = atomicAdd(counters + blockIdx.x, 1u) == (unsigned int)ksplit - 1;
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-  }
-  for (int idx = threadIdx.x; idx < TILE; idx += blockDim.x) {
-    const int r = idx / (8 * GQ_NT), col = idx % (8 * GQ_NT);
-    const int n = n_base + col;
-    if (r < M && n < N) {
-      float acc = 0.f;
-      if (ksplit > 1) {
-        acc = __ldcg(wtile + idx);
-        wtile[idx] = 0.f;
-      } else {
+    // reduce the K slices of the warps through shared memory
+    __syncthreads();  // the previous segment's readers are done with `red`
 #pragma unroll
-        for (int w = 0; w < GQ_WARPS; ++w) acc += red[w][r][col];
-      }
-      if (bias) acc += xl_to_float(bias[n]);
-      if (n >= act_from_col) acc = 0.5f * acc * (1.f + erff(acc * 0.70710678118654752f));
-      y[(long long)r * ldy + n] = xl_from_float<T>(acc);
+    for (int t = 0; t < GQ_NT; ++t) {
+      red[warp][quad][t * 8 + 2 * j] = c[t][0];
+      red[warp][quad][t * 8 + 2 * j + 1] = c[t][1];
+      red[warp][quad + 8][t * 8 + 2 * j] = c[t][2];
+      red[warp][quad + 8][t * 8 + 2 * j + 1] = c[t][3];
     }
+    __syncthreads();
+    const bool whole = (c1 - c0) == chunks;
+    float* wtile = ws + (long long)tile * TILE;
+    bool finishing = whole;
+    if (!whole) {
+      for (int idx = threadIdx.x; idx < TILE; idx += blockDim.x) {
+        const int r = idx / (8 * GQ_NT), col = idx % (8 * GQ_NT);
+        if (r < M && n_base + col < N) {
+          float acc = 0.f;
+#pragma unroll
+          for (int w = 0; w < GQ_WARPS; ++w) acc += red[w][r][col];
+          atomicAdd(wtile + idx, acc);
+        }
+      }
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0)
+        finish = atomicAdd(counters + tile, (unsigned int)(c1 - c0)) + (unsigned int)(c1 - c0) == (unsigned int)chunks;
+      __syncthreads();
+      finishing = finish != 0;
+      if (finishing) __threadfence();
+    }
+    if (finishing) {
+      for (int idx = threadIdx.x; idx < TILE; idx += blockDim.x) {
+        const int r = idx / (8 * GQ_NT), col = idx % (8 * GQ_NT);
+        const int n = n_base + col;
+        if (r < M && n < N) {
+          float acc = 0.f;
+          if (!whole) {
+            acc = __ldcg(wtile + idx);
+            wtile[idx] = 0.f;
+          } else {
+#pragma unroll
+            for (int w = 0; w < GQ_WARPS; ++w) acc += red[w][r][col];
+          }
+          if (bias) acc += xl_to_float(bias[n]);
+          if (n >= act_from_col) acc = 0.5f * acc * (1.f + erff(acc * 0.70710678118654752f));
+          y[(long long)r * ldy + n] = xl_from_float<T>(acc);
+        }
+      }
+      if (!whole && threadIdx.x == 0) counters[tile] = 0;
+    }
+    item += c1 - c0;
   }
-  if (ksplit > 1 && threadIdx.x == 0) counters[blockIdx.x] = 0;
 }
 
 // Requirements: M <= 16, K % 128 == 0, group_size % 32 == 0, 16-byte aligned x rows and weight rows. `ws` / `counters`:
-// zero-initialised scratch of at least ceil(N/32)*512 floats / ceil(N/32) words, needed when ksplit > 1 (the kernel
-// leaves them zeroed). act_from_col: first column that gets GELU (>= N: none). Returns -1 for unsupported arguments.
+// zero-initialised scratch of ceil(N/32)*512 floats / ceil(N/32) words (the kernel leaves them zeroed). `ctas`: size of
+// the grid (0: three per SM of a 148-SM part). act_from_col: first column that gets GELU (>= N: none). Returns -1 for
+// unsupported arguments.
 template <typename T>
 static void gq_small_launch(const void* x, const void* packed, const void* scale, const void* zero, const void* bias, void* y,
                             int M, int N, int K, int group_size, long long ldx, long long ldy, int act_from_col,
-                            float* ws, unsigned int* counters, int scale_dtype, dim3 grid, cudaStream_t s) {
+                            float* ws, unsigned int* counters, int scale_dtype, int grid, cudaStream_t s) {
   if (scale_dtype == XL_F16)
     gq_gemm_small_m_kernel<T, __half><<<grid, GQ_WARPS * 32, 0, s>>>(
         (const T*)x, (const uint16_t*)packed, (const __half*)scale, (const __half*)zero, (const T*)bias, (T*)y, M, N, K,
@@ -186,17 +236,19 @@ static void gq_small_launch(const void* x, const void* packed, const void* scale
 // `dtype`: type of x, bias and y (fp16 or bf16); `scale_dtype`: type of the per-group scale and zero point (fp16 / bf16).
 XL_API int xl_gq_gemm_small_m(const void* x, const void* packed, const void* scale, const void* zero, const void* bias,
                               void* y, int M, int N, int K, int group_size, long long ldx, long long ldy, int act_from_col,
-                              int ksplit, float* ws, unsigned int* counters, int dtype, int scale_dtype, cudaStream_t s) {
+                              int ctas, float* ws, unsigned int* counters, int dtype, int scale_dtype, cudaStream_t s) {
   if (M < 1 || M > 16 || K % GQ_KCHUNK || group_size % 32 || K % group_size || dtype == XL_F32 || scale_dtype == XL_F32)
     return -1;
-  if ((ldx % 8) || ksplit < 1 || ksplit > K / GQ_KCHUNK || (ksplit > 1 && (ws == nullptr || counters == nullptr))) return -1;
-  const dim3 grid((N + 8 * GQ_NT - 1) / (8 * GQ_NT), ksplit);
+  if ((ldx % 8) || ws == nullptr || counters == nullptr) return -1;
+  const long long total = (long long)((N + 8 * GQ_NT - 1) / (8 * GQ_NT)) * (K / GQ_KCHUNK);
+  long long grid = ctas > 0 ? ctas : 3 * 148;
+  if (grid > total) grid = total;
   if (dtype == XL_BF16)
     gq_small_launch<__nv_bfloat16>(x, packed, scale, zero, bias, y, M, N, K, group_size, ldx, ldy, act_from_col, ws,
-                                   counters, scale_dtype, grid, s);
+                                   counters, scale_dtype, (int)grid, s);
   else
     gq_small_launch<__half>(x, packed, scale, zero, bias, y, M, N, K, group_size, ldx, ldy, act_from_col, ws, counters,
-                            scale_dtype, grid, s);
+                            scale_dtype, (int)grid, s);
   return (int)cudaGetLastError();
 }
 
@@ -420,6 +472,29 @@ XL_API int xl_attn_decode(const void* qkv, long long ldq, const void* k_cache, c
   return (int)cudaGetLastError();
 }
 
+// N consecutive elements (N * sizeof(T) a multiple of 16, p 16-byte aligned) through 128-bit accesses
+template <typename T, int N> __device__ __forceinline__ void xl_load_vec(const T* __restrict__ p, float (&out)[N]) {
+  constexpr int PER = 16 / sizeof(T);
+#pragma unroll
+  for (int q = 0; q < N / PER; ++q) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p + q * PER);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) out[q * PER + i] = xl_to_float(e[i]);
+  }
+}
+template <typename T, int N> __device__ __forceinline__ void xl_store_vec(T* __restrict__ p, const float (&in)[N]) {
+  constexpr int PER = 16 / sizeof(T);
+#pragma unroll
+  for (int q = 0; q < N / PER; ++q) {
+    uint4 raw;
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) e[i] = xl_from_float<T>(in[q * PER + i]);
+    *reinterpret_cast<uint4*>(p + q * PER) = raw;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------------------------
 // Residual update + LayerNorm for a few rows: x += delta (+ bias); h = LayerNorm(x) * w + b. One CTA per row.
 // ------------------------------------------------------------------------------------------------------------------
@@ -427,23 +502,35 @@ template <typename T>
 __global__ void __launch_bounds__(256)
     add_layer_norm_kernel(T* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ bias,
                           const T* __restrict__ w, const T* __restrict__ b, T* __restrict__ h, int cols, float eps) {
-  constexpr int MAX_PER = 32;  // cols <= 256 * 32
+  constexpr int MAX_VEC = 4;  // vectors of 8 elements per thread: cols <= 256 * 8 * 4
   const int row = blockIdx.x;
   T* xr = x + (long long)row * cols;
-  float v[MAX_PER];
+  float v[MAX_VEC][8];
   float sum = 0.f;
 #pragma unroll
-  for (int i = 0; i < MAX_PER; ++i) {
-    const int c = threadIdx.x + i * 256;
-    v[i] = 0.f;
+  for (int i = 0; i < MAX_VEC; ++i) {
+    const int c = (threadIdx.x + i * 256) * 8;
     if (c < cols) {
-      float t = xl_to_float(xr[c]);
-      if (delta) t += xl_to_float(delta[(long long)row * cols + c]);
-      if (bias) t += xl_to_float(bias[c]);
-      const T rounded = xl_from_float<T>(t);
-      if (delta || bias) xr[c] = rounded;
-      v[i] = xl_to_float(rounded);
-      sum += v[i];
+      xl_load_vec<T, 8>(xr + c, v[i]);
+      if (delta) {
+        float d[8];
+        xl_load_vec<T, 8>(delta + (long long)row * cols + c, d);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] += d[e];
+      }
+      if (bias) {
+        float d[8];
+        xl_load_vec<T, 8>(bias + c, d);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] += d[e];
+      }
+      if (delta || bias) {
+        xl_store_vec<T, 8>(xr + c, v[i]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[i][e] = xl_to_float(xl_from_float<T>(v[i][e]));  // what later readers of x see
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum += v[i][e];
     }
   }
   __shared__ float red[8];
@@ -460,9 +547,12 @@ __global__ void __launch_bounds__(256)
   const float mean = stat[0];
   float sq = 0.f;
 #pragma unroll
-  for (int i = 0; i < MAX_PER; ++i) {
-    const int c = threadIdx.x + i * 256;
-    if (c < cols) sq += (v[i] - mean) * (v[i] - mean);
+  for (int i = 0; i < MAX_VEC; ++i) {
+    const int c = (threadIdx.x + i * 256) * 8;
+    if (c < cols) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sq += (v[i][e] - mean) * (v[i][e] - mean);
+    }
   }
   sq = xl_warp_sum(sq);
   __syncthreads();
@@ -476,13 +566,15 @@ __global__ void __launch_bounds__(256)
   __syncthreads();
   const float rstd = stat[1];
 #pragma unroll
-  for (int i = 0; i < MAX_PER; ++i) {
-    const int c = threadIdx.x + i * 256;
+  for (int i = 0; i < MAX_VEC; ++i) {
+    const int c = (threadIdx.x + i * 256) * 8;
     if (c < cols) {
-      float t = (v[i] - mean) * rstd;
-      if (w) t *= xl_to_float(w[c]);
-      if (b) t += xl_to_float(b[c]);
-      h[(long long)row * cols + c] = xl_from_float<T>(t);
+      float wv[8], bv[8], o[8];
+      xl_load_vec<T, 8>(w + c, wv);
+      xl_load_vec<T, 8>(b + c, bv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = (v[i][e] - mean) * rstd * wv[e] + bv[e];
+      xl_store_vec<T, 8>(h + (long long)row * cols + c, o);
     }
   }
 }
@@ -490,7 +582,7 @@ __global__ void __launch_bounds__(256)
 // x (rows, cols) is updated in place when delta or bias is given; h (rows, cols) receives the normalised rows.
 XL_API int xl_add_layer_norm(void* x, const void* delta, const void* bias, const void* w, const void* b, void* h,
                              int rows, int cols, float eps, int dtype, cudaStream_t s) {
-  if (cols > 256 * 32 || rows < 1) return -1;
+  if (cols > 256 * 32 || (cols % 8) || rows < 1 || w == nullptr || b == nullptr) return -1;
   XL_DISPATCH_DTYPE(dtype, T, {
     add_layer_norm_kernel<T><<<rows, 256, 0, s>>>((T*)x, (const T*)delta, (const T*)bias, (const T*)w, (const T*)b, (T*)h,
                                                  cols, eps);

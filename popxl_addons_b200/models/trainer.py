@@ -37,6 +37,93 @@ from .decoder import DecoderBlock, DecoderConfig, DecoderEmbedding, DecoderHead,
 __all__ = ["DecoderTrainer"]
 
 
+def build_optimizer(ir, cfg, par, groups, hp, state_dtype, shard_optimizer, fused_collectives, slot_of=None):
+    """Emit the AdamW update of every parameter of `groups` (`(name, weights, accumulators)` triples) into the
+    current graph: fp32 master weights and moments, sharded over the data-parallel group when `shard_optimizer`
+    (as one fused reduce-scatter + AdamW + all-gather kernel per parameter when `fused_collectives`), otherwise a
+    gradient all-reduce followed by a replicated update. `slot_of(name)` places a group's update on a device slot
+    (pipeline parallel). Returns `(master weights by name, optimizer state by name)`."""
+    import contextlib
+
+    def placed(name):
+        return xl.ipu(slot_of(name)) if slot_of is not None else contextlib.nullcontext()
+
+    masters: Dict[str, xl.Variable] = {}
+    opt_state = {}
+    opt_graphs: Dict[tuple, tuple] = {}
+    from ..optimizers.rts_adam import RTSAdamStep
+
+    fused_jobs = []  # (weight, accumulator, master shard, decay, name): emitted together below
+    for group_name, wtree, atree in groups:
+        wd, ad = wtree.to_dict(), atree.accum.to_dict()
+        with placed(group_name):
+            for pname, w in wd.items():
+                g = ad[pname]
+                full = f"{group_name}.{pname}"
+                decay = hp["weight_decay"] if w.rank >= 2 else 0.0
+                host = ir.initial_values[w]
+                if isinstance(host, xl.LazyInit):
+                    host32 = host.astype(np.float32)  # same recipe and seed, drawn in fp32
+                else:
+                    host32 = (host.float() if isinstance(host, torch.Tensor)
+                              else torch.tensor(np.asarray(host)).float()).numpy()
+                rg = w.replica_grouping
+                shardable = shard_optimizer and w.nelms % cfg.dp == 0
+                fusable = (shardable and fused_collectives and w.dtype in (xl.bfloat16, xl.float16)
+                           and (w.nelms // cfg.dp) % 4 == 0)
+                if fusable:
+                    master, _ = xl.replica_sharded_variable(host32, xl.float32, f"master.{full}",
+                                                            replica_grouping=rg, shard_grouping=par.dp_group)
+                    masters[full] = master
+                    w.symmetric_group = par.dp_group
+                    g.symmetric_group = par.dp_group
+                    fused_jobs.append((w, g, master, decay, full, rg, group_name))
+                    continue
+                if shardable:
+                    g = reduce_replica_sharded_tensor(g, "mean", par.dp_group, par.dp_group)
+                    master, _ = xl.replica_sharded_variable(host32, xl.float32, f"master.{full}",
+                                                            replica_grouping=rg, shard_grouping=par.dp_group)
+                    key = ("sharded", master.shape, decay)
+                else:
+                    if cfg.dp > 1:
+                        g = ops.collectives.replicated_all_reduce(g, "mean", par.dp_group)
+                    master = xl.variable(host32, xl.float32, f"master.{full}", replica_grouping=rg)
+                    key = ("full", tuple(w.shape), decay)
+                masters[full] = master
+                if key not in opt_graphs:
+                    with xl.ipu(None):  # the graph is shared by parameters on different slots
+                        ofacts, ograph = AdamOptimizerStep().create_graph(
+                            master, g, rg, lr=hp["lr"], beta1=hp["beta1"], beta2=hp["beta2"], eps=hp["eps"],
+                            weight_decay=decay, first_order_dtype=state_dtype, bias_correction=True)
+                    opt_graphs[key] = (ofacts, ograph)
+                ofacts, ograph = opt_graphs[key]
+                ostate = ofacts.init(f"adam.{full}")
+                ograph.bind(ostate).call(master, g)
+                opt_state[full] = ostate
+                new_w = ops.cast(master, w.dtype)
+                if shardable:
+                    new_w = ops.collectives.replicated_all_gather(new_w, par.dp_group, output_shape=w.shape)
+                ops.var_updates.copy_var_update_(w, new_w)
+    # one fused kernel per parameter: reduce-scatter + AdamW + all-gather; only the first call waits for all
+    # replicas' accumulators and only the last one for all replicas' weight shards
+    for j, (w, g, master, decay, full, rg, group_name) in enumerate(fused_jobs):
+        # barriers are per process: the first / last fused update of every device slot carries them
+        same = [k for k, job in enumerate(fused_jobs) if slot_of is None or slot_of(job[6]) == slot_of(group_name)]
+        first, last = j == same[0], j == same[-1]
+        key = ("fused", tuple(w.shape), decay, first, last)
+        if key not in opt_graphs:
+            with xl.ipu(None):
+                opt_graphs[key] = RTSAdamStep().create_graph(
+                    w, g, master, par.dp_group, rg, lr=hp["lr"], beta1=hp["beta1"], beta2=hp["beta2"], eps=hp["eps"],
+                    weight_decay=decay, first_order_dtype=state_dtype, sync_before=first, sync_after=last)
+        ofacts, ograph = opt_graphs[key]
+        with placed(group_name):
+            ostate = ofacts.init(f"adam.{full}")
+            ograph.bind(ostate).call(w, g, master)
+        opt_state[full] = ostate
+    return masters, opt_state
+
+
 class DecoderTrainer:
     def __init__(self, cfg: DecoderConfig, micro_batches: int = 16, micro_batch_size: int = 1, device: str = "auto",
                  seed: int = 0, lr: float = 1e-4, weight_decay: float = 0.01, beta1: float = 0.9, beta2: float = 0.95,
@@ -155,76 +242,10 @@ class DecoderTrainer:
             ops.repeat(mb, self.micro_batches, inputs_dict=mb_inputs, cuda_graph=self.cuda_graphs)
 
             # ---- optimizer -------------------------------------------------------------------------------------
-            self.master: Dict[str, xl.Variable] = {}
-            opt_state = {}
-            opt_graphs: Dict[tuple, tuple] = {}
-            from ..optimizers.rts_adam import RTSAdamStep
-
-            fused_jobs = []  # (weight, accumulator, master shard, decay, name): emitted together below
-            for group_name, wtree, atree in ([("embedding", emb_vars, emb_acc), ("head", head_vars, head_acc)] +
-                                             [(f"layer{i}", blk_vars[i], blk_acc[i]) for i in range(cfg.layers)]):
-                wd, ad = wtree.to_dict(), atree.accum.to_dict()
-                for pname, w in wd.items():
-                    g = ad[pname]
-                    full = f"{group_name}.{pname}"
-                    decay = self.hp["weight_decay"] if w.rank >= 2 else 0.0
-                    host = ir.initial_values[w]
-                    if isinstance(host, xl.LazyInit):
-                        host32 = host.astype(np.float32)  # same recipe and seed, drawn in fp32
-                    else:
-                        host32 = (host.float() if isinstance(host, torch.Tensor)
-                                  else torch.tensor(np.asarray(host)).float()).numpy()
-                    rg = w.replica_grouping
-                    shardable = self.shard_optimizer and w.nelms % cfg.dp == 0
-                    fusable = (shardable and self.fused_collectives and w.dtype in (xl.bfloat16, xl.float16)
-                               and (w.nelms // cfg.dp) % 4 == 0)
-                    if fusable:
-                        master, _ = xl.replica_sharded_variable(host32, xl.float32, f"master.{full}",
-                                                                replica_grouping=rg, shard_grouping=par.dp_group)
-                        self.master[full] = master
-                        w.symmetric_group = par.dp_group
-                        g.symmetric_group = par.dp_group
-                        fused_jobs.append((w, g, master, decay, full, rg))
-                        continue
-                    if shardable:
-                        g = reduce_replica_sharded_tensor(g, "mean", par.dp_group, par.dp_group)
-                        master, _ = xl.replica_sharded_variable(host32, xl.float32, f"master.{full}",
-                                                                replica_grouping=rg, shard_grouping=par.dp_group)
-                        key = ("sharded", master.shape, decay)
-                    else:
-                        if cfg.dp > 1:
-                            g = ops.collectives.replicated_all_reduce(g, "mean", par.dp_group)
-                        master = xl.variable(host32, xl.float32, f"master.{full}", replica_grouping=rg)
-                        key = ("full", tuple(w.shape), decay)
-                    self.master[full] = master
-                    if key not in opt_graphs:
-                        ofacts, ograph = AdamOptimizerStep().create_graph(
-                            master, g, rg, lr=self.hp["lr"], beta1=self.hp["beta1"], beta2=self.hp["beta2"],
-                            eps=self.hp["eps"], weight_decay=decay, first_order_dtype=self.state_dtype,
-                            bias_correction=True)
-                        opt_graphs[key] = (ofacts, ograph)
-                    ofacts, ograph = opt_graphs[key]
-                    ostate = ofacts.init(f"adam.{full}")
-                    ograph.bind(ostate).call(master, g)
-                    opt_state[full] = ostate
-                    new_w = ops.cast(master, w.dtype)
-                    if shardable:
-                        new_w = ops.collectives.replicated_all_gather(new_w, par.dp_group, output_shape=w.shape)
-                    ops.var_updates.copy_var_update_(w, new_w)
-            # one fused kernel per parameter: reduce-scatter + AdamW + all-gather; only the first call waits for all
-            # replicas' accumulators and only the last one for all replicas' weight shards
-            for j, (w, g, master, decay, full, rg) in enumerate(fused_jobs):
-                first, last = j == 0, j == len(fused_jobs) - 1
-                key = ("fused", tuple(w.shape), decay, first, last)
-                if key not in opt_graphs:
-                    opt_graphs[key] = RTSAdamStep().create_graph(
-                        w, g, master, par.dp_group, rg, lr=self.hp["lr"], beta1=self.hp["beta1"],
-                        beta2=self.hp["beta2"], eps=self.hp["eps"], weight_decay=decay,
-                        first_order_dtype=self.state_dtype, sync_before=first, sync_after=last)
-                ofacts, ograph = opt_graphs[key]
-                ostate = ofacts.init(f"adam.{full}")
-                ograph.bind(ostate).call(w, g, master)
-                opt_state[full] = ostate
+            groups = ([("embedding", emb_vars, emb_acc), ("head", head_vars, head_acc)] +
+                      [(f"layer{i}", blk_vars[i], blk_acc[i]) for i in range(cfg.layers)])
+            self.master, opt_state = build_optimizer(ir, cfg, par, groups, self.hp, self.state_dtype,
+                                                     self.shard_optimizer, self.fused_collectives)
             for atree in [emb_acc, head_acc] + blk_acc:
                 ops.var_updates.accumulator_zero_(atree.mean_accum_counter)
 

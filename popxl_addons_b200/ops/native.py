@@ -888,7 +888,7 @@ def _gq_scratch(device, n_tiles: int):
     return cur
 
 
-def gq_gemm_small_m(x, packed, scale, zero, bias, out=None, act_from_col=None, ksplit=None):
+def gq_gemm_small_m(x, packed, scale, zero, bias, out=None, act_from_col=None, ctas=None):
     """`x (M<=16, K) @ dequant(packed (N, K/gs, gs/4))^T + bias` with the de-quantisation fused into the GEMM; GELU on
     the output columns `>= act_from_col` if given. `x` and `out` may be column windows of wider row-major matrices."""
     M, K = x.shape
@@ -905,14 +905,11 @@ def gq_gemm_small_m(x, packed, scale, zero, bias, out=None, act_from_col=None, k
     if y.shape != (M, N) or y.dtype != x.dtype or y.stride(1) != 1:
         return NotImplemented
     n_tiles = (N + 31) // 32
-    if ksplit is None:
-        ksplit = max(1, min((3 * _sms(x.device)) // n_tiles, K // 1024))
-    ws, counters = _gq_scratch(x.device, n_tiles) if ksplit > 1 else (None, None)
+    ws, counters = _gq_scratch(x.device, n_tiles)
     rc = _gq_small(x.data_ptr(), packed.data_ptr(), scale.data_ptr(), zero.data_ptr(),
                    bias.data_ptr() if bias is not None else None, y.data_ptr(), M, N, K, gs, x.stride(0), y.stride(0),
-                   N if act_from_col is None else int(act_from_col), ksplit,
-                   ws.data_ptr() if ws is not None else None, counters.data_ptr() if counters is not None else None,
-                   _CODE[x.dtype], _CODE[scale.dtype], _stream())
+                   N if act_from_col is None else int(act_from_col), int(ctas or 3 * _sms(x.device)),
+                   ws.data_ptr(), counters.data_ptr(), _CODE[x.dtype], _CODE[scale.dtype], _stream())
     if rc == -1:
         return NotImplemented
     _check(rc, "gq_gemm_small_m")

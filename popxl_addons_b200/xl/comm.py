@@ -186,9 +186,15 @@ class DistComm:
         return [out]
 
     def gather_to_host(self, vals):
+        """Values of all replicas (indexed by replica), on the host: gathered over the processes that hold the same
+        device slot of every replica."""
         t = vals[0].detach().contiguous()
-        out = [torch.empty_like(t) for _ in range(self.world_size)]
-        self.dist.all_gather(out, t)
+        pg, _ = self.group_for(ReplicaGrouping(self.num_replicas))
+        out = [torch.empty_like(t) for _ in range(self.num_replicas)]
+        if self.num_replicas > 1:
+            self.dist.all_gather(out, t, group=pg)
+        else:
+            out = [t]
         return [o.cpu() for o in out]
 
     def send(self, t: torch.Tensor, dst: int):

@@ -86,9 +86,11 @@ def in_sequence(enabled: Union[bool, str] = True):
 
 
 @contextlib.contextmanager
-def ipu(index: int):
-    """Place ops on device slot `index` (a pipeline stage's GPU). Kept under the reference's name for API parity."""
-    _STATE.devices.append(int(index))
+def ipu(index: Optional[int]):
+    """Place ops on device slot `index` (a pipeline stage's GPU). Kept under the reference's name for API parity.
+    `ipu(None)` suspends an enclosing placement: ops created inside follow their operands, or the call site when they
+    belong to a graph that is called from several slots."""
+    _STATE.devices.append(None if index is None else int(index))
     try:
         yield
     finally:
@@ -99,7 +101,7 @@ device = ipu
 
 
 def current_device() -> int:
-    return _STATE.devices[-1] if _STATE.devices else 0
+    return _STATE.devices[-1] if _STATE.devices and _STATE.devices[-1] is not None else 0
 
 
 @contextlib.contextmanager
@@ -526,8 +528,8 @@ class Op:
         self.name = opdef.name
         # device slot: the enclosing `ipu(...)` context if there is one; otherwise the op follows its operands
         # (ops that transforms create outside any context, e.g. stash updates or gradient accumulation)
-        self.device_explicit = bool(_STATE.devices)
-        if _STATE.devices:
+        self.device_explicit = bool(_STATE.devices) and _STATE.devices[-1] is not None
+        if self.device_explicit:
             self.device_index = _STATE.devices[-1]
         else:
             on = [t.device_index for t in self.inputs if not isinstance(t, Constant)]

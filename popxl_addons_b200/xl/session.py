@@ -233,6 +233,9 @@ class Session:
                 continue
             if not isinstance(var, Variable):
                 raise TypeError(f"{var} is not a variable")
+            if not self.owns(var):
+                raise KeyError(f"{var} lives on another device slot (this process holds slot {self.slot}); read it "
+                               f"from the process that owns it (`Session.owns`)")
             per_replica = self.comm.gather_to_host(self._read_var_local(var))
             rg = var.replica_grouping
             per_group = []

@@ -240,6 +240,28 @@ def main():
         dist.all_gather_object(gathered, payload)
         if rank == 0:
             print(json.dumps({"ranks": gathered, "data_seed": 42}))
+    elif args.mode == "pp_train":
+        # pipeline-parallel trainer: `--slots` processes per replica, world / slots data-parallel replicas
+        from popxl_addons_b200.models import decoder as dec
+        from popxl_addons_b200.models.decoder import DecoderConfig
+        from popxl_addons_b200.models.pipeline_trainer import PipelineTrainer
+
+        dp = world // args.slots
+        cfg = DecoderConfig.tiny("llama", layers=4, dtype=args.dtype, tp=1, dp=dp)
+        dec._SEED[0] = 0
+        tr = PipelineTrainer(cfg, stages=args.slots, micro_batches=6, device=args.device, lr=1e-2,
+                             fused_collectives=bool(args.fused))
+        replica = rank // args.slots
+        losses = []
+        for step in range(args.steps):
+            g = torch.Generator().manual_seed(step)
+            tok = torch.randint(0, cfg.vocab_size, (6, dp, 1, cfg.seq_len + 1), generator=g, dtype=torch.int32)
+            loss = tr.step(tok[:, replica:replica + 1])
+            losses.append(loss)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, {"rank": rank, "losses": losses})
+        if rank == 0:
+            print(json.dumps({"ranks": gathered}))
     elif args.mode == "fail":
         # rank 1 stops between steps; rank 0 notices on the host before launching anything that would wait for it
         from datetime import timedelta

@@ -137,3 +137,30 @@ def test_pipeline_stages_on_separate_processes(nproc):
                                  {"w": False, "dw": False, "scale": True})
         if info["slot"] == 0:
             np.testing.assert_allclose(info["grad"], want, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("nproc", [2, 4])
+def test_pipeline_trainer_on_separate_processes_matches_simulation(nproc):
+    """Llama-shaped model, 2 device slots per replica, 1 or 2 data-parallel replicas: the losses of three optimizer steps
+    must match the same trainer run in one process (all slots and replicas simulated in-process)."""
+    from popxl_addons_b200.models import decoder as dec
+    from popxl_addons_b200.models.decoder import DecoderConfig
+    from popxl_addons_b200.models.pipeline_trainer import PipelineTrainer
+
+    dp = nproc // 2
+    cfg = DecoderConfig.tiny("llama", layers=4, dtype="float32", tp=1, dp=dp)
+    dec._SEED[0] = 0
+    tr = PipelineTrainer(cfg, stages=2, micro_batches=6, device="cpu", lr=1e-2)
+    want = []
+    for step in range(3):
+        g = torch.Generator().manual_seed(step)
+        tok = torch.randint(0, cfg.vocab_size, (6, dp, 1, cfg.seq_len + 1), generator=g, dtype=torch.int32)
+        out = tr.session.run({tr.inputs.tokens: tok, tr.inputs.labels: tok})[tr.outputs.loss]
+        want.append(np.asarray(out).reshape(6, dp).mean(axis=0))  # per replica
+    res = launch(nproc, "--mode", "pp_train", "--slots", "2", "--dtype", "float32", timeout=400)
+    for info in res["ranks"]:
+        replica, slot = info["rank"] // 2, info["rank"] % 2
+        if slot == 1:
+            np.testing.assert_allclose(info["losses"], [w[replica] for w in want], rtol=1e-4)
+        else:
+            assert info["losses"] == [None] * 3

@@ -47,10 +47,10 @@ def test_gq_gemm_small_m(nat, dtype, M, N, K, gs):
     torch.testing.assert_close(y2.float(), want - bias.float(), rtol=2e-2, atol=2e-2 * math.sqrt(K / 256))
 
 
-@pytest.mark.parametrize("ksplit", [1, 3, None])
-def test_gq_gemm_small_m_windows_split_k_and_gelu(nat, ksplit):
-    """Input and output as column windows of wider buffers, K split over several CTAs (twice in a row: the scratch must
-    come back zeroed), GELU on the upper output columns, fp16 scales with bf16 activations."""
+@pytest.mark.parametrize("ctas", [1, 7, 100, None])
+def test_gq_gemm_small_m_windows_split_k_and_gelu(nat, ctas):
+    """Input and output as column windows of wider buffers, the work cut into different numbers of CTA ranges, so that
+    tiles are shared between CTAs in different ways (twice in a row: the scratch must come back zeroed), GELU on the upper output columns, fp16 scales with bf16 activations."""
     from popxl_addons_b200.models.generator import quantize_rows
 
     torch.manual_seed(3)
@@ -68,7 +68,7 @@ def test_gq_gemm_small_m_windows_split_k_and_gelu(nat, ksplit):
     want[:, 600:] = torch.nn.functional.gelu(want[:, 600:])
     for _ in range(2):
         y = nat.gq_gemm_small_m(xbuf[:, 256:256 + K], packed, scale, zero, bias, out=ybuf[:, 128:128 + N],
-                                act_from_col=600, ksplit=ksplit)
+                                act_from_col=600, ctas=ctas)
         assert y is not NotImplemented
         torch.testing.assert_close(ybuf[:, 128:128 + N].float(), want, rtol=2e-2, atol=6e-2)
     assert float(ybuf[:, :128].abs().sum()) == 0 and float(ybuf[:, 128 + N:].abs().sum()) == 0
