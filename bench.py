@@ -89,7 +89,19 @@ def run_reference(args):
     return 0
 
 
+PIPELINE_METRIC = "train tokens/s Llama-2-7B shape PPxDP (bf16, fp32 Adam, seq 2048, 32 micro-batches of 1)"
 DECODE_METRIC = "int4 decode tokens/s GPT-J-6B shape, TP over all GPUs (batch 16, prompt 512, 128 new tokens, greedy)"
+
+
+def _shutdown(dist):
+    """Leave without tearing the NCCL communicators down: destroying them while captured CUDA graphs that contain
+    their kernels are still alive has been seen to block for minutes."""
+    if dist is not None:
+        dist.barrier()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    if dist is not None:
+        os._exit(0)
 
 
 def run_decode(args):
@@ -186,9 +198,7 @@ def run_decode(args):
             "sample_tokens": [int(t) for t in np.asarray(out)[0, :8]], "setup_seconds": setup_s,
         }
         print(json.dumps(line))
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    _shutdown(dist)
     return 0
 
 
@@ -202,8 +212,11 @@ def main():
     ap.add_argument("--micro-batches", type=int, default=16)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (diagnostics only; such a run is "
                                                          "labelled and is not the headline configuration)")
-    ap.add_argument("--mode", default="train", choices=["train", "decode"],
-                    help="train: the training step (default, headline); decode: int4 greedy generation, TP over all GPUs")
+    ap.add_argument("--mode", default="train", choices=["train", "decode", "pipeline"],
+                    help="train: the training step (default, headline); decode: int4 greedy generation, TP over all GPUs; "
+                         "pipeline: pipeline x data parallel training (--stages device slots per replica)")
+    ap.add_argument("--tp", type=int, default=0, help="train mode: tensor-parallel width (default min(gpus, 4))")
+    ap.add_argument("--stages", type=int, default=4, help="pipeline mode: device slots (GPUs) per replica")
     ap.add_argument("--batch", type=int, default=16, help="decode mode: sequences per batch")
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--new-tokens", type=int, default=128)
@@ -229,6 +242,18 @@ def main():
             raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
     torch.cuda.set_device(local_rank)
     tp, dp = layout_for(args.gpus)
+    if args.tp:
+        tp, dp = args.tp, args.gpus // args.tp
+    pipeline = args.mode == "pipeline"
+    if pipeline:
+        if args.impl != "ours":
+            raise SystemExit("pipeline mode has no --impl torch arm")
+        stages = min(args.stages, args.gpus)
+        tp, dp = 1, args.gpus // stages
+        if args.model == "gptj_6b":
+            args.model = "llama2_7b"
+        if args.micro_batches == 16:
+            args.micro_batches = 32
     cfg = getattr(DecoderConfig, args.model)(tp=tp, dp=dp)
     if args.layers:
         cfg.layers = args.layers
@@ -271,6 +296,12 @@ def main():
                 return tt.step_device(t)
 
         trainer = _Adapter()
+    elif pipeline:
+        from popxl_addons_b200.models.pipeline_trainer import PipelineTrainer
+        from popxl_addons_b200.ops import native
+
+        trainer = PipelineTrainer(cfg, stages=stages, micro_batches=args.micro_batches, micro_batch_size=1, device="cuda",
+                                  seed=0, lr=1e-4)
     else:
         trainer = DecoderTrainer(cfg, micro_batches=args.micro_batches, micro_batch_size=1, device="cuda", seed=0,
                                  lr=1e-4)
@@ -289,6 +320,9 @@ def main():
     losses = []
     for i in range(W):
         losses.append(trainer.step(host_tokens[i]))
+    if pipeline:
+        # only the last slot of a replica sees the loss: share it for the report
+        losses = [l if l is not None else float("nan") for l in losses]
 
     # ---- device-timed region: K steps, inputs resident, CUDA events, max over ranks ----------------------------------
     launches0 = native.LAUNCHES["count"]
@@ -313,6 +347,10 @@ def main():
         losses.append(trainer.step(host_tokens[W + i]))
     barrier()
     e2e_s = time.perf_counter() - t1
+    if pipeline and dist is not None:
+        box = [losses]
+        dist.broadcast_object_list(box, src=stages - 1)  # the last slot of replica 0 computes the loss
+        losses = box[0]
     h2d = (trainer.session.h2d_bytes - h2d0) // K
     d2h = (trainer.session.d2h_bytes - d2h0) // K
 
@@ -326,30 +364,28 @@ def main():
     if rank == 0:
         flops_per_token = 6 * cfg.param_count() + 6 * cfg.layers * cfg.seq_len * cfg.heads * cfg.head_dim
         line = {
-            "impl": args.impl, "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
+            "impl": args.impl, "metric": PIPELINE_METRIC if pipeline else METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
             "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)",
             "config": {"model": f"{args.model} ({cfg.layers} layers, hidden {cfg.hidden}, {cfg.heads} heads x "
                                 f"{cfg.head_dim}, ffn {cfg.ffn}, vocab {cfg.vocab_size})",
                        "global_batch": args.micro_batches * dp, "seq_len": cfg.seq_len,
-                       "parallelism": f"tp{tp}xdp{dp}", "micro_batches": args.micro_batches, "micro_batch_size": 1,
+                       "parallelism": (f"pp{stages}xdp{dp}" if pipeline else f"tp{tp}xdp{dp}"), "micro_batches": args.micro_batches, "micro_batch_size": 1,
                        "optimizer": "AdamW, fp32 master weights + fp32 moments" +
                                     (", state sharded over dp (RTS)" if dp > 1 else ""),
                        "recompute": "per layer", "l2": "each step streams >100 GB of weights, optimizer state and "
                                                        "activations, far beyond the 126 MB L2; no flush needed",
-                       "headline": not args.layers and args.model == "gptj_6b"},
+                       "headline": not args.layers and args.model == "gptj_6b" and not pipeline and not args.tp},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches),
             "kernels": native.LAUNCHES["by_kernel"],
             "model_tflops_per_gpu": flops_per_token * value / args.gpus / 1e12,
-            "loss_first_last": [losses[0], losses[-1]], "setup_seconds": setup_s,
+            "loss_first_last": [losses[0], losses[-1]], "setup_seconds": setup_s, "mode": args.mode,
         }
         print(json.dumps(line))
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    _shutdown(dist)
     return 0
 
 

@@ -150,23 +150,40 @@ XL_API int xl_rts_adam(const void* const* grads, void* const* weights, int w_dty
   return (int)cudaGetLastError();
 }
 
-// One-shot all-reduce (add) of a 16-bit vector through the NVLS multicast address: every rank has written its data at
-// the same offset of the symmetric buffer; after a barrier each rank reads the whole vector with multimem.ld_reduce
-// (the switch adds the replicas, fp32 accumulation) into `out`. For the 128 KiB activations of token-by-token decoding:
-// latency-bound, one CTA.
-__global__ void __launch_bounds__(1024)
-    symm_all_reduce_mc_kernel(const void* mc_in, unsigned int* const* pads, uint4* __restrict__ out, int nvec, int bf16,
+// One-shot all-reduce (sum) of a small 16-bit tensor, latency-bound (the 128 KiB activations of token-by-token decoding).
+// Every rank copies its input into one half of a staging buffer in symmetric memory, the ranks meet at a barrier, and
+// every rank reads the sum of all replicas of that half through the multicast address (`multimem.ld_reduce`: NVSwitch
+// adds the replicas, fp32 accumulation). The work is split over up to MC_MAX_CTAS CTAs; CTA b handles slice b on every
+// rank and synchronises only with the peers' CTA b (signal channel `channel + b`), so no grid-wide step is needed.
+// The halves alternate from call to call (a counter in device memory, advanced by the last CTA to finish): a rank can
+// only reach the next use of a half after every peer has passed the barrier of the call in between, i.e. has finished
+// reading it, so no closing barrier is needed and the launch has no argument that changes between calls (it can be
+// replayed from a CUDA graph).
+constexpr int MC_MAX_CTAS = 16;
+constexpr int MC_THREADS = 512;
+
+__global__ void __launch_bounds__(MC_THREADS)
+    symm_all_reduce_mc_kernel(const uint4* __restrict__ in, uint4* stage_local, const char* stage_mc, long long half_bytes,
+                              unsigned int* state, unsigned int* const* pads, uint4* __restrict__ out, int nvec, int bf16,
                               int rank, int world, int channel, int* err, unsigned int limit) {
   __shared__ int ok_s;
+  const unsigned int parity = *((volatile unsigned int*)state) & 1u;
+  const int per = (nvec + gridDim.x - 1) / gridDim.x;
+  const int v0 = blockIdx.x * per, v1 = min(nvec, v0 + per);
+  uint4* mine = stage_local + parity * (half_bytes / 16);
+  for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) mine[i] = in[i];
+  __threadfence_system();
+  __syncthreads();
   if (threadIdx.x < 32) {
-    const bool ok = xl_group_barrier(pads, rank, world, channel, err, limit);
+    const bool ok = xl_group_barrier(pads, rank, world, channel + blockIdx.x, err, limit);
     if (threadIdx.x == 0) ok_s = ok;
   }
   __syncthreads();
   if (ok_s) {
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    const char* src = stage_mc + parity * half_bytes;
+    for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
       uint4 v;
-      const char* a = (const char*)mc_in + (size_t)i * 16;
+      const char* a = src + (size_t)i * 16;
       if (bf16)
         asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
                      : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(a) : "memory");
@@ -177,14 +194,29 @@ __global__ void __launch_bounds__(1024)
     }
   }
   __syncthreads();
-  if (threadIdx.x < 32) xl_group_barrier(pads, rank, world, channel + 1, err, limit);
+  if (threadIdx.x == 0) {
+    const unsigned int ticket = atomicAdd(state + 1, 1u);
+    if (ticket == gridDim.x - 1) {
+      state[1] = 0;
+      __threadfence();
+      *((volatile unsigned int*)state) = parity + 1u;  // the next call uses the other half
+    }
+  }
 }
 
-// nbytes must be a multiple of 16; mc_in = multicast address of the staged input.
-XL_API int xl_symm_all_reduce_mc(const void* mc_in, const void* pads_dev, void* out, long long nbytes, int dtype, int rank,
-                                 int world, int channel, int* err, cudaStream_t s) {
-  if (world > 32 || nbytes <= 0 || (nbytes & 15) || dtype == XL_F32) return -1;
-  symm_all_reduce_mc_kernel<<<1, 1024, 0, s>>>(mc_in, (unsigned int* const*)pads_dev, (uint4*)out, (int)(nbytes / 16),
-                                               dtype == XL_BF16, rank, world, channel, err, xl_host_comm_spin_limit);
+// in / out: this rank's input and result (nbytes, a multiple of 16, at most half_bytes); stage_local / stage_mc: local
+// and multicast address of a staging buffer of 2 * half_bytes in symmetric memory; state: two zero-initialised words of
+// this rank; uses signal channels channel .. channel + 15.
+XL_API int xl_symm_all_reduce_mc(const void* in, void* stage_local, const void* stage_mc, long long half_bytes,
+                                 unsigned int* state, const void* pads_dev, void* out, long long nbytes, int dtype,
+                                 int rank, int world, int channel, int* err, cudaStream_t s) {
+  if (world > 32 || nbytes <= 0 || (nbytes & 15) || nbytes > half_bytes || (half_bytes & 15) || dtype == XL_F32) return -1;
+  const int nvec = (int)(nbytes / 16);
+  int grid = (nvec + MC_THREADS - 1) / MC_THREADS;
+  if (grid > MC_MAX_CTAS) grid = MC_MAX_CTAS;
+  symm_all_reduce_mc_kernel<<<grid, MC_THREADS, 0, s>>>((const uint4*)in, (uint4*)stage_local, (const char*)stage_mc,
+                                                       half_bytes, state, (unsigned int* const*)pads_dev, (uint4*)out,
+                                                       nvec, dtype == XL_BF16, rank, world, channel, err,
+                                                       xl_host_comm_spin_limit);
   return (int)cudaGetLastError();
 }

@@ -20,7 +20,7 @@
 // ------------------------------------------------------------------------------------------------------------------
 // int4 group-quantised GEMM, M <= 16
 // ------------------------------------------------------------------------------------------------------------------
-constexpr int GQ_NT = 4;         // n-tiles of 8 columns per warp -> a CTA covers 32 output columns
+constexpr int GQ_NT = 8;         // n-tiles of 8 columns per warp -> a CTA covers 64 output columns
 constexpr int GQ_WARPS = 8;      // warps of a CTA split K between them
 constexpr int GQ_KCHUNK = 128;   // k values per warp iteration (32 per lane quad member)
 
@@ -79,7 +79,7 @@ __device__ __forceinline__ void gq_dequant8(uint32_t w, typename GqFmt<T>::T2 s2
 // Any assignment of actual k indices to the 16 k-slots of an MMA is valid as long as A and B agree, so each lane
 // keeps the 32 consecutive k values of its 16-byte weight load and feeds them to 8 MMAs, 4 values at a time.
 //
-// Work = (column tiles of 32) x (K chunks of 128), tile-major, cut into equal contiguous ranges, one per CTA
+// Work = (column tiles of 64) x (K chunks of 128), tile-major, cut into equal contiguous ranges, one per CTA
 // ("stream-K": the grid is sized to the machine, not to the problem, so there is no partial last wave). A CTA walks
 // its range tile by tile; its warps split the chunks of the current tile segment and reduce through shared memory.
 // A segment that covers a whole tile is finished by its CTA; otherwise the CTAs sharing the tile add their partial
@@ -87,11 +87,11 @@ __device__ __forceinline__ void gq_dequant8(uint32_t w, typename GqFmt<T>::T2 s2
 // workspace and counter zeroed for the next launch. Epilogue: + bias, GELU on the columns >= act_from_col. x and y are
 // windows of wider matrices (ldx, ldy).
 template <typename T, typename S>
-__global__ void __launch_bounds__(GQ_WARPS * 32, 3)
+__global__ void __launch_bounds__(GQ_WARPS * 32, 2)
     gq_gemm_small_m_kernel(const T* __restrict__ x, const uint16_t* __restrict__ packed, const S* __restrict__ scale,
                            const S* __restrict__ zero, const T* __restrict__ bias, T* __restrict__ y, int M, int N, int K,
                            int group_size, long long ldx, long long ldy, int act_from_col, float* __restrict__ ws,
-                           unsigned int* __restrict__ counters) {
+                           unsigned int* __restrict__ counters, int sz_transposed) {
   using F = GqFmt<T>;
   using T2 = typename F::T2;
   __shared__ float red[GQ_WARPS][16][8 * GQ_NT + 1];
@@ -121,43 +121,54 @@ __global__ void __launch_bounds__(GQ_WARPS * 32, 3)
       const int k_lane = ch * GQ_KCHUNK + j * 32;  // this lane's 32 consecutive k values
       // weights first (the long-latency loads), then the activations: rows quad and quad+8, 32 values each
       uint4 wq[GQ_NT];
-      T2 s2[GQ_NT], z2[GQ_NT];
+      uint32_t sz[GQ_NT];  // (scale, zero) of this lane's group, two S values
       const int g = k_lane / group_size;
 #pragma unroll
       for (int t = 0; t < GQ_NT; ++t) {
         const int n = n_base + t * 8 + quad;
         wq[t] = make_uint4(0, 0, 0, 0);
-        float sc = 0.f, zp = 0.f;
+        sz[t] = 0;
         if (n < N) {
           wq[t] = __ldcs(reinterpret_cast<const uint4*>(packed + (long long)n * (K / 4) + k_lane / 4));
-          sc = xl_to_float(scale[(long long)n * groups + g]);
-          zp = xl_to_float(zero[(long long)n * groups + g]);
+          if (sz_transposed) {
+            // scale holds (groups, N, 2): 8 consecutive columns of one group are one 32-byte segment
+            sz[t] = reinterpret_cast<const uint32_t*>(scale)[(long long)g * N + n];
+          } else {
+            const S sv = scale[(long long)n * groups + g], zv = zero[(long long)n * groups + g];
+            sz[t] = (uint32_t)(*reinterpret_cast<const uint16_t*>(&sv)) |
+                    ((uint32_t)(*reinterpret_cast<const uint16_t*>(&zv)) << 16);
+          }
         }
-        s2[t] = F::pair(sc);
-        z2[t] = F::pair(zp);
       }
-      uint4 xa[4], xb[4];
-      const uint4 zero4 = make_uint4(0, 0, 0, 0);
 #pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        xa[v] = row_lo ? *reinterpret_cast<const uint4*>(x + (long long)quad * ldx + k_lane + v * 8) : zero4;
-        xb[v] = row_hi ? *reinterpret_cast<const uint4*>(x + (long long)(quad + 8) * ldx + k_lane + v * 8) : zero4;
-      }
-      const uint32_t* xa32 = reinterpret_cast<const uint32_t*>(xa);
-      const uint32_t* xb32 = reinterpret_cast<const uint32_t*>(xb);
+      for (int half = 0; half < 2; ++half) {
+        uint4 xa[2], xb[2];
+        const uint4 zero4 = make_uint4(0, 0, 0, 0);
 #pragma unroll
-      for (int t = 0; t < GQ_NT; ++t) {
-        const uint32_t* w32 = reinterpret_cast<const uint32_t*>(&wq[t]);
+        for (int v = 0; v < 2; ++v) {
+          const long long off = k_lane + (2 * half + v) * 8;
+          xa[v] = row_lo ? *reinterpret_cast<const uint4*>(x + (long long)quad * ldx + off) : zero4;
+          xb[v] = row_hi ? *reinterpret_cast<const uint4*>(x + (long long)(quad + 8) * ldx + off) : zero4;
+        }
+        const uint32_t* xa32 = reinterpret_cast<const uint32_t*>(xa);
+        const uint32_t* xb32 = reinterpret_cast<const uint32_t*>(xb);
 #pragma unroll
-        for (int m = 0; m < 4; ++m) {
-          // 32-bit word m holds packed words 2m and 2m+1, i.e. k_lane + 8m .. 8m+7
-          uint32_t b[4];
-          gq_dequant8<T>(w32[m], s2[t], z2[t], b);
-          const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
-          const uint32_t a0[4] = {xa32[4 * m], xb32[4 * m], xa32[4 * m + 1], xb32[4 * m + 1]};
-          const uint32_t a1[4] = {xa32[4 * m + 2], xb32[4 * m + 2], xa32[4 * m + 3], xb32[4 * m + 3]};
-          mma_m16n8k16(c[t], a0, b0, BF);
-          mma_m16n8k16(c[t], a1, b1, BF);
+        for (int t = 0; t < GQ_NT; ++t) {
+          const uint32_t* w32 = reinterpret_cast<const uint32_t*>(&wq[t]);
+          const uint16_t s16 = (uint16_t)(sz[t] & 0xFFFFu), z16 = (uint16_t)(sz[t] >> 16);
+          const T2 s2 = F::pair(xl_to_float(*reinterpret_cast<const S*>(&s16)));
+          const T2 z2 = F::pair(xl_to_float(*reinterpret_cast<const S*>(&z16)));
+#pragma unroll
+          for (int mm = 0; mm < 2; ++mm) {
+            // 32-bit word m holds packed words 2m and 2m+1, i.e. k_lane + 8m .. 8m+7
+            uint32_t b[4];
+            gq_dequant8<T>(w32[2 * half + mm], s2, z2, b);
+            const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
+            const uint32_t a0[4] = {xa32[4 * mm], xb32[4 * mm], xa32[4 * mm + 1], xb32[4 * mm + 1]};
+            const uint32_t a1[4] = {xa32[4 * mm + 2], xb32[4 * mm + 2], xa32[4 * mm + 3], xb32[4 * mm + 3]};
+            mma_m16n8k16(c[t], a0, b0, BF);
+            mma_m16n8k16(c[t], a1, b1, BF);
+          }
         }
       }
     }
@@ -217,38 +228,41 @@ __global__ void __launch_bounds__(GQ_WARPS * 32, 3)
 }
 
 // Requirements: M <= 16, K % 128 == 0, group_size % 32 == 0, 16-byte aligned x rows and weight rows. `ws` / `counters`:
-// zero-initialised scratch of ceil(N/32)*512 floats / ceil(N/32) words (the kernel leaves them zeroed). `ctas`: size of
-// the grid (0: three per SM of a 148-SM part). act_from_col: first column that gets GELU (>= N: none). Returns -1 for
+// zero-initialised scratch of ceil(N/64)*1024 floats / ceil(N/64) words (the kernel leaves them zeroed). `ctas`: size of
+// the grid (0: two per SM of a 148-SM part). sz_transposed: `scale` holds (scale, zero) pairs laid out (K/gs, N, 2)
+// and `zero` is unused: the layout in which the eight columns of an MMA tile are one contiguous 32-byte read. act_from_col: first column that gets GELU (>= N: none). Returns -1 for
 // unsupported arguments.
 template <typename T>
 static void gq_small_launch(const void* x, const void* packed, const void* scale, const void* zero, const void* bias, void* y,
                             int M, int N, int K, int group_size, long long ldx, long long ldy, int act_from_col,
-                            float* ws, unsigned int* counters, int scale_dtype, int grid, cudaStream_t s) {
+                            float* ws, unsigned int* counters, int scale_dtype, int sz_transposed, int grid,
+                            cudaStream_t s) {
   if (scale_dtype == XL_F16)
     gq_gemm_small_m_kernel<T, __half><<<grid, GQ_WARPS * 32, 0, s>>>(
         (const T*)x, (const uint16_t*)packed, (const __half*)scale, (const __half*)zero, (const T*)bias, (T*)y, M, N, K,
-        group_size, ldx, ldy, act_from_col, ws, counters);
+        group_size, ldx, ldy, act_from_col, ws, counters, sz_transposed);
   else
     gq_gemm_small_m_kernel<T, __nv_bfloat16><<<grid, GQ_WARPS * 32, 0, s>>>(
         (const T*)x, (const uint16_t*)packed, (const __nv_bfloat16*)scale, (const __nv_bfloat16*)zero, (const T*)bias,
-        (T*)y, M, N, K, group_size, ldx, ldy, act_from_col, ws, counters);
+        (T*)y, M, N, K, group_size, ldx, ldy, act_from_col, ws, counters, sz_transposed);
 }
 // `dtype`: type of x, bias and y (fp16 or bf16); `scale_dtype`: type of the per-group scale and zero point (fp16 / bf16).
 XL_API int xl_gq_gemm_small_m(const void* x, const void* packed, const void* scale, const void* zero, const void* bias,
                               void* y, int M, int N, int K, int group_size, long long ldx, long long ldy, int act_from_col,
-                              int ctas, float* ws, unsigned int* counters, int dtype, int scale_dtype, cudaStream_t s) {
+                              int ctas, float* ws, unsigned int* counters, int dtype, int scale_dtype, int sz_transposed,
+                              cudaStream_t s) {
   if (M < 1 || M > 16 || K % GQ_KCHUNK || group_size % 32 || K % group_size || dtype == XL_F32 || scale_dtype == XL_F32)
     return -1;
   if ((ldx % 8) || ws == nullptr || counters == nullptr) return -1;
   const long long total = (long long)((N + 8 * GQ_NT - 1) / (8 * GQ_NT)) * (K / GQ_KCHUNK);
-  long long grid = ctas > 0 ? ctas : 3 * 148;
+  long long grid = ctas > 0 ? ctas : 2 * 148;
   if (grid > total) grid = total;
   if (dtype == XL_BF16)
     gq_small_launch<__nv_bfloat16>(x, packed, scale, zero, bias, y, M, N, K, group_size, ldx, ldy, act_from_col, ws,
-                                   counters, scale_dtype, (int)grid, s);
+                                   counters, scale_dtype, sz_transposed, (int)grid, s);
   else
     gq_small_launch<__half>(x, packed, scale, zero, bias, y, M, N, K, group_size, ldx, ldy, act_from_col, ws, counters,
-                            scale_dtype, (int)grid, s);
+                            scale_dtype, sz_transposed, (int)grid, s);
   return (int)cudaGetLastError();
 }
 

@@ -27,6 +27,7 @@ constexpr int STAGES = 4;
 constexpr int NUM_EPI_WARPS = 8;  // two warps per TMEM lane quarter, each draining half of the accumulator columns
 constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr int EPI_STAGE_BYTES = 4096;  // per epilogue warp, only in the modes that push tiles to peers
 
 enum { ERR_FULL_WAIT = 1, ERR_EMPTY_WAIT = 2, ERR_TMEM_FULL_WAIT = 3, ERR_TMEM_EMPTY_WAIT = 4 };
 
@@ -64,7 +65,25 @@ struct GemmParams {
   const uint8_t* const* gather_src; // device array [world]: the full matrix in every rank's memory
   uint8_t* gather_dst;              // the full matrix in this rank's memory (own shard already in place)
   unsigned int* gather_flags;       // one word per row block of the full matrix, zeroed before the launch; 1 = landed
+  // causal structure of square attention products (rows and columns / contraction index are token positions):
+  //   1: output tiles entirely above the diagonal are not computed (S = Q K^T, dP = dO V^T; the softmax kernels never
+  //      read them and overwrite them with zeros)
+  //   2: the left operand is zero right of the diagonal (O = P V, dQ = dS K): contraction stops at the tile's last row
+  //   3: the (transposed) left operand is zero before the diagonal (dV = P^T dO, dK = dS^T Q): contraction starts at
+  //      the tile's first row
+  int causal;
 };
+
+// k-block range of a tile under the causal modes; false: the tile is skipped altogether
+__device__ __forceinline__ bool tile_k_range(const GemmParams& p, int mb, int nb, int k_blocks, int block_n, int& kb0,
+                                             int& kb1) {
+  kb0 = 0;
+  kb1 = k_blocks;
+  if (p.causal == 1) return nb * block_n <= mb * BLOCK_M + BLOCK_M - 1;
+  if (p.causal == 2) kb1 = min(k_blocks, (mb * BLOCK_M + BLOCK_M + BLOCK_K - 1) / BLOCK_K);
+  if (p.causal == 3) kb0 = min(k_blocks - 1, (mb * BLOCK_M) / BLOCK_K);
+  return true;
+}
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -398,7 +417,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           if (!ok) break;
         }
         const int m0 = mb * BLOCK_M, n0 = nb * BLOCK_N;
-        for (int kb_i = 0; kb_i < k_blocks; ++kb_i) {
+        int kb0, kb1;
+        if (!tile_k_range(p, mb, nb, k_blocks, BLOCK_N, kb0, kb1)) continue;
+        for (int kb_i = kb0; kb_i < kb1; ++kb_i) {
           int kb = kb_i;
           if (p.gather_mode == 2) {
             kb = (kb_i + gather_rot) % k_blocks;
@@ -446,11 +467,17 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       uint32_t acc = 0, acc_phase = 0;
       bool ok = true;
       for (int tile = cta; tile < num_tiles && ok; tile += ncta) {
+        int kb0 = 0, kb1 = k_blocks;
+        if (p.causal) {
+          int b, mb, nb;
+          tile_coords(tile, tiles_m, tiles_n, b, mb, nb, raster_group);
+          if (!tile_k_range(p, mb, nb, k_blocks, BLOCK_N, kb0, kb1)) continue;
+        }
         ok = mbar_wait(&tmem_empty_bar[acc], acc_phase ^ 1, abort_flag, p.err, ERR_TMEM_EMPTY_WAIT);
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.err, ERR_FULL_WAIT);
           if (!ok) break;
           tcgen05_fence_after();
@@ -460,7 +487,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
             const uint64_t da = make_smem_desc(sa + k * a_kstep, a_lbo);
             const uint64_t db = make_smem_desc(sb + k * b_kstep, b_lbo);
-            tcgen05_mma_f16(tmem_d, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            tcgen05_mma_f16(tmem_d, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           tcgen05_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -505,6 +532,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       int b, mb, nb;
       tile_coords(tile, tiles_m, tiles_n, b, mb, nb, raster_group);
       if (p.gather_mode == 1) mb = (mb + gather_rot) % tiles_m;
+      if (p.causal == 1 && nb * BLOCK_N > mb * BLOCK_M + BLOCK_M - 1) continue;
       ok = mbar_wait(&tmem_full_bar[acc], acc_phase, abort_flag, p.err, ERR_TMEM_FULL_WAIT);
       if (!ok) break;
       tcgen05_fence_after();
@@ -518,6 +546,69 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         crow = (uint8_t*)p.rs_dst[owner] + (long long)(row - owner * p.rs_rows) * p.ldc * 2;
       } else {
         crow = (uint8_t*)p.C + ((long long)b * p.batch_stride_c + (long long)row * p.ldc) * (p.c_dtype == XL_F32 ? 4 : 2);
+      }
+      if (p.accumulate >= 3) {
+        // Pushes over NVLink should be whole 128-byte lines. TMEM hands every lane one row, so the tile goes through
+        // a per-warp staging area in shared memory (32 rows x 64 columns, 16-byte chunks swizzled by row): written by
+        // rows, read back with eight lanes covering 128 contiguous bytes of one row.
+        uint8_t* stage = smem + L::TILE_BYTES + 256 + (warp - 2) * EPI_STAGE_BYTES;
+        const bool bf = p.c_dtype == XL_BF16;
+#pragma unroll 1
+        for (int c = col_half * COLS_PER_WARP; c < (col_half + 1) * COLS_PER_WARP; c += 64) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr + c + h * 32, r);
+            tmem_ld_wait();
+            const int col0 = nb * BLOCK_N + c + h * 32;
+#pragma unroll
+            for (int jj = 0; jj < 4; ++jj) {
+              uint4 o;
+              uint16_t* oe = (uint16_t*)&o;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                float val = __uint_as_float(r[jj * 8 + e]) * p.alpha;
+                if (p.bias && col0 + jj * 8 + e < p.N) {
+                  const int bc = col0 + jj * 8 + e;
+                  val += p.bias_dtype == XL_F32 ? ((const float*)p.bias)[bc]
+                         : p.bias_dtype == XL_BF16 ? __bfloat162float(((const __nv_bfloat16*)p.bias)[bc])
+                                                   : __half2float(((const __half*)p.bias)[bc]);
+                }
+                if (p.act) val = apply_act(val, p.act);
+                oe[e] = bf ? __bfloat16_as_ushort(__float2bfloat16_rn(val)) : __half_as_ushort(__float2half_rn(val));
+              }
+              const int chunk = h * 4 + jj;
+              *(uint4*)(stage + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = o;
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int rr = it * 4 + (lane >> 3), cc = lane & 7;
+            const uint4 o = *(const uint4*)(stage + rr * 128 + ((cc ^ (rr & 7)) << 4));
+            const int grow = mb * BLOCK_M + q * 32 + rr;
+            const int gcol = nb * BLOCK_N + c + cc * 8;
+            if (grow < p.M && gcol < p.N) {
+              uint16_t* dst;
+              if (p.accumulate == 4) {
+                const int owner = grow / p.rs_rows;
+                dst = (uint16_t*)p.rs_dst[owner] + (long long)(grow - owner * p.rs_rows) * p.ldc + gcol;
+                if (bf) xl_red_add_bf16x8(dst, o);
+                else xl_red_add_f16x8(dst, o);
+              } else {
+                dst = (uint16_t*)p.C + (long long)grow * p.ldc + gcol;
+                if (bf) xl_multimem_red_add_bf16x8(dst, o);
+                else xl_multimem_red_add_f16x8(dst, o);
+              }
+            }
+          }
+          __syncwarp();
+        }
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        continue;
       }
 #pragma unroll 1
       for (int c = col_half * COLS_PER_WARP; c < (col_half + 1) * COLS_PER_WARP; c += 32) {
@@ -571,25 +662,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         } else {
           uint16_t* dst = (uint16_t*)crow + col0;
           const bool bf = p.c_dtype == XL_BF16;
-          if (p.accumulate >= 3) {
-            // host guarantees N % 8 == 0 and 16-byte aligned rows in these modes
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              if (col0 + j >= p.N) break;
-              uint4 o;
-              uint16_t* oe = (uint16_t*)&o;
-#pragma unroll
-              for (int e = 0; e < 8; ++e)
-                oe[e] = bf ? __bfloat16_as_ushort(__float2bfloat16_rn(v[j + e])) : __half_as_ushort(__float2half_rn(v[j + e]));
-              if (p.accumulate == 3) {
-                if (bf) xl_multimem_red_add_bf16x8(dst + j, o);
-                else xl_multimem_red_add_f16x8(dst + j, o);
-              } else {
-                if (bf) xl_red_add_bf16x8(dst + j, o);
-                else xl_red_add_f16x8(dst + j, o);
-              }
-            }
-          } else if (full && (((uintptr_t)dst) & 15) == 0) {
+          if (full && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               uint4 old;
@@ -687,16 +760,19 @@ template <int BLOCK_N>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int sm_count, cudaStream_t s) {
   using L = SmemLayout<BLOCK_N>;
   static bool configured = false;
+  constexpr int TOTAL_COMM = L::TOTAL + NUM_EPI_WARPS * EPI_STAGE_BYTES;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BLOCK_N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         TOTAL_COMM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
+  const int smem_bytes = p.accumulate >= 3 ? TOTAL_COMM : L::TOTAL;
   const int tiles = ((p.M + BLOCK_M - 1) / BLOCK_M) * ((p.N + BLOCK_N - 1) / BLOCK_N) * p.batch;
   const int n_copy = p.gather_mode ? p.n_copy : 0;  // copy CTAs and GEMM CTAs wait on one another: all must be resident
   const int gemm_ctas = tiles < sm_count - n_copy ? tiles : sm_count - n_copy;
   const int grid = gemm_ctas + n_copy;
-  gemm_tcgen05_kernel<BLOCK_N><<<grid, NUM_THREADS, L::TOTAL, s>>>(ma, mb, p);
+  gemm_tcgen05_kernel<BLOCK_N><<<grid, NUM_THREADS, smem_bytes, s>>>(ma, mb, p);
   return (int)cudaGetLastError();
 }
 
@@ -714,6 +790,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
 //   captured in a CUDA graph and replayed.
 // Returns 0, a CUDA error code, or a negative value when the arguments are not supported by this kernel.
 // Full entry point. On top of xl_gemm_tcgen05:
+//   causal = 1 / 2 / 3: square attention products whose masked half is not computed (see GemmParams::causal).
 //   accumulate == 4 (GEMM fused with a reduce-scatter over NVLink): row r of the product is added (`red.add`, 16-byte
 //   vectors) into the output shard of rank r / rs_rows; rs_dst = device array with every rank's shard buffer
 //   (rs_rows x ldc, zeroed in stream order before the launch), M == rs_rows * comm_world. `c` is unused.
@@ -730,7 +807,7 @@ XL_API int xl_gemm_tcgen05_fused(const void* a, const void* b, void* c, int M, i
                                  int act, int accumulate, const float* step, float alpha, int* err, int sm_count,
                                  const void* comm_pads, int comm_rank, int comm_world, unsigned int* comm_local_sync,
                                  const void* rs_dst, int rs_rows, int gather_mode, const void* gather_src,
-                                 void* gather_dst, unsigned int* gather_flags, int gather_bps, int n_copy,
+                                 void* gather_dst, unsigned int* gather_flags, int gather_bps, int n_copy, int causal,
                                  cudaStream_t s) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -1;
   if ((((uintptr_t)a) & 15) || (((uintptr_t)b) & 15) || (lda % 8) || (ldb % 8)) return -1;
@@ -756,6 +833,10 @@ XL_API int xl_gemm_tcgen05_fused(const void* a, const void* b, void* c, int M, i
   p.gather_mode = gather_mode; p.n_copy = n_copy; p.gather_bps = gather_bps;
   p.gather_src = (const uint8_t* const*)gather_src; p.gather_dst = (uint8_t*)gather_dst; p.gather_flags = gather_flags;
   p.gather_block_bytes = 0;
+  p.causal = causal;
+  if (causal < 0 || causal > 3 || (causal && (gather_mode || accumulate >= 3))) return -1;
+  if (causal && (M != N && causal == 1)) return -1;
+  if (causal >= 2 && M != K) return -1;
   if (sm_count <= 0) sm_count = 148;
   if (accumulate >= 3 && (comm_pads == nullptr || comm_local_sync == nullptr || (N % 8) || c_dtype == XL_F32 ||
                           (ldc % 8) || comm_world > 32 || batch != 1))
@@ -791,5 +872,5 @@ XL_API int xl_gemm_tcgen05(const void* a, const void* b, void* c, int M, int N, 
   return xl_gemm_tcgen05_fused(a, b, c, M, N, K, batch, a_mn, b_mn, lda, ldb, ldc, stride_a, stride_b, stride_c,
                                ab_is_fp16, c_dtype, bias, bias_dtype, act, accumulate, step, alpha, err, sm_count,
                                comm_pads, comm_rank, comm_world, comm_local_sync, nullptr, 0, 0, nullptr, nullptr,
-                               nullptr, 0, 0, s);
+                               nullptr, 0, 0, 0, s);
 }

@@ -16,7 +16,7 @@ from ..named_tensors import NamedTensors
 from ..ops.group_quantize_decompress import group_quantize_compress_numpy
 from ..xl.opdef import OpDef, emit1
 
-__all__ = ["LinearGQ", "linear_gq_window"]
+__all__ = ["LinearGQ", "linear_gq_window", "linear_gq_window_t", "interleave_scale_zero"]
 
 import torch  # noqa: E402
 
@@ -55,6 +55,35 @@ def _linear_gq_window_ref(x, packed, scale, bias, *b, x_col, k, act_from_col):
 
 OpDef("linear_gq_window", impl=_linear_gq_window_ref,
       flops=lambda op: 2 * op.attrs["k"] * op.outputs[0].nelms)
+
+
+def interleave_scale_zero(scale: torch.Tensor, zero: torch.Tensor) -> torch.Tensor:
+    """`(out, groups, 1)` scale and zero point -> one `(groups, out, 2)` tensor of (scale, zero) pairs: the layout in
+    which the fused small-batch kernel reads the eight output columns of an MMA tile as one 32-byte segment."""
+    return torch.stack([scale.reshape(scale.shape[0], -1).t(), zero.reshape(zero.shape[0], -1).t()], dim=-1).contiguous()
+
+
+def _linear_gq_window_t_ref(x, packed, sz, *b, x_col, k, act_from_col):
+    if x.device.type == "meta":
+        return torch.empty((x.shape[0], packed.shape[0]), dtype=x.dtype, device="meta")
+    scale = sz[..., 0].t().unsqueeze(-1)
+    zero = sz[..., 1].t().unsqueeze(-1)
+    return _linear_gq_window_ref(x, packed, scale, zero, *b, x_col=x_col, k=k, act_from_col=act_from_col)
+
+
+OpDef("linear_gq_window_t", impl=_linear_gq_window_t_ref,
+      flops=lambda op: 2 * op.attrs["k"] * op.outputs[0].nelms)
+
+
+def linear_gq_window_t(x: xl.Tensor, packed: xl.Tensor, scale_zero: xl.Tensor, bias: Optional[xl.Tensor] = None,
+                       x_col: int = 0, k: Optional[int] = None, act_from_col: Optional[int] = None) -> xl.Tensor:
+    """`linear_gq_window` with the scales and zero points given as `interleave_scale_zero(scale, zero)`."""
+    from ..xl.opdef import emit1
+
+    k = int(k) if k is not None else x.shape[1] - x_col
+    ins = [x, packed, scale_zero] + ([bias] if bias is not None else [])
+    return emit1("linear_gq_window_t", ins, dict(x_col=int(x_col), k=k,
+                                                 act_from_col=None if act_from_col is None else int(act_from_col)))
 
 
 def linear_gq_window(x: xl.Tensor, packed: xl.Tensor, scale: xl.Tensor, zero: xl.Tensor, bias: Optional[xl.Tensor] = None,

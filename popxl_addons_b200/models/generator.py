@@ -21,7 +21,7 @@ import torch
 
 from .. import xl
 from ..layers.embedding import Embedding
-from ..layers.linear_gq import linear_gq_window
+from ..layers.linear_gq import interleave_scale_zero, linear_gq_window_t
 from ..named_tensors import NamedTensors
 from ..ops.group_quantize_decompress import group_quantize_compress_numpy
 from ..ops.rotary_pos_embed import trig_tables
@@ -68,6 +68,9 @@ class _GQ:
         sdt = scale_dtype or dtype
         self.scale = xl.variable(rep(ones), sdt, f"{name}.weight_decompression_scale", replica_grouping=rg)
         self.zero = xl.variable(rep(0 * ones), sdt, f"{name}.weight_decompression_bias", replica_grouping=rg)
+        # the same scales and zero points as (scale, zero) pairs, group-major: the layout the decode kernel reads
+        self.sz = xl.variable(rep(np.zeros((in_f // gs, out_f, 2), np.float32)), sdt, f"{name}.weight_scale_zero_t",
+                              replica_grouping=rg)
         self.bias = None
         if bias:
             brg = rg if bias_rg == "same" else None
@@ -77,7 +80,7 @@ class _GQ:
 
     def tensors(self):
         d = {"weight_compressed": self.packed, "weight_decompression_scale": self.scale,
-             "weight_decompression_bias": self.zero}
+             "weight_decompression_bias": self.zero, "weight_scale_zero_t": self.sz}
         if self.bias is not None:
             d["bias"] = self.bias
         return d
@@ -167,7 +170,7 @@ class DecoderGenerator:
 
             def select_token(hn, head, off):
                 """Vocabulary-sharded logits of the normalised hidden state, greedy choice agreed between the shards."""
-                logits = _linear_gq(hn, head)
+                logits = linear_gq_window_t(hn, head["weight_compressed"], head["weight_scale_zero_t"], head["bias"])
                 valid = vshard  # padded rows of the last shard are excluded below via the index check
                 m, idx = ops.argmax_rows(logits, valid, 0)
                 idx = idx + off if cfg.tp > 1 else idx
@@ -204,13 +207,13 @@ class DecoderGenerator:
                 GEMM; rotary + cache append; attention, written next to the fc_in output; [out | fc_out] in one GEMM."""
                 h = ops.add_layer_norm_(x, delta, delta_bias, L["ln_w"], L["ln_b"], eps=cfg.eps)
                 w1 = L["w1"]
-                buf = linear_gq_window(h, w1["weight_compressed"], w1["weight_decompression_scale"],
-                                       w1["weight_decompression_bias"], w1["bias"], act_from_col=3 * hd)
+                buf = linear_gq_window_t(h, w1["weight_compressed"], w1["weight_scale_zero_t"], w1["bias"],
+                                         act_from_col=3 * hd)
                 buf = ops.rotary_kv_append_(buf, sin_tab_i, cos_tab_i, L["k"], L["v"], pos, H, D, cfg.rotary_dim)
                 buf = ops.attention_decode_into_(buf, L["k"], L["v"], pos, H, D, out_col=2 * hd)
                 w2 = L["w2"]
-                y = linear_gq_window(buf, w2["weight_compressed"], w2["weight_decompression_scale"],
-                                     w2["weight_decompression_bias"], None, x_col=2 * hd, k=hd + F)
+                y = linear_gq_window_t(buf, w2["weight_compressed"], w2["weight_scale_zero_t"], None, x_col=2 * hd,
+                                       k=hd + F)
                 return all_reduce(y)
 
             # graphs take every variable as an input; collect them in a fixed order
@@ -315,6 +318,7 @@ class DecoderGenerator:
                 s._vars[q.packed][r].view(torch.int16).copy_(packed)
                 s._vars[q.scale][r].copy_(scale.to(s._vars[q.scale][r].dtype))
                 s._vars[q.zero][r].copy_(zero.to(s._vars[q.zero][r].dtype))
+                s._vars[q.sz][r].copy_(interleave_scale_zero(s._vars[q.scale][r], s._vars[q.zero][r]))
         for r in range(s.num_local):
             grp = self.wte.replica_grouping.group_index(s.global_replica(r))
             gen = torch.Generator(device=dev).manual_seed(seed * 7919 + 17 + grp)
@@ -342,6 +346,7 @@ class DecoderGenerator:
             s._vars[q.packed][r].view(torch.int16).copy_(packed)
             s._vars[q.scale][r].copy_(scale.to(s._vars[q.scale][r].dtype))
             s._vars[q.zero][r].copy_(zero.to(s._vars[q.zero][r].dtype))
+            s._vars[q.sz][r].copy_(interleave_scale_zero(s._vars[q.scale][r], s._vars[q.zero][r]))
             if bl is not None and q.bias is not None:
                 s._vars[q.bias][r].copy_(torch.tensor(bl).to(s._vars[q.bias][r].dtype))
 

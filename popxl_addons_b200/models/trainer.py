@@ -148,7 +148,7 @@ class DecoderTrainer:
         self._build()
         apply_pre_alias_patterns(self.ir)
         self.fused_gemm_collectives = 0
-        if fused_collectives and cfg.tp > 1:
+        if fused_collectives and cfg.tp > 1 and os.environ.get("XL_FUSE_GEMM_AR", "1") != "0":
             from ..parallel import fuse_gemm_collectives
 
             self.fused_gemm_collectives = fuse_gemm_collectives(self.ir)

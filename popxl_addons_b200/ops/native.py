@@ -73,9 +73,9 @@ _gemm = _sig("xl_gemm_tcgen05", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int
              _c_int, _c_p, _c_p)
 _gemm_fused = _sig("xl_gemm_tcgen05_fused", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
                    _c_ll, _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_p,
-                   _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p)
+                   _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p)
 _gq_small = _sig("xl_gq_gemm_small_m", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
-                 _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_p)
+                 _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p)
 _rot_append = _sig("xl_rotary_append", _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                    _c_int, _c_p)
 _attn_dec = _sig("xl_attn_decode", _c_p, _c_ll, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
@@ -84,7 +84,8 @@ _add_ln = _sig("xl_add_layer_norm", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, 
 _argmax = _sig("xl_argmax_rows", _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p)
 _advance = _sig("xl_advance_position", _c_p, _c_p)
 _store_row = _sig("xl_store_row", _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_p)
-_symm_all_reduce_mc = _sig("xl_symm_all_reduce_mc", _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p)
+_symm_all_reduce_mc = _sig("xl_symm_all_reduce_mc", _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int,
+                           _c_int, _c_p, _c_p)
 _symm_barrier = _sig("xl_symm_barrier", _c_p, _c_int, _c_int, _c_int, _c_p, _c_p)
 _symm_all_reduce = _sig("xl_symm_all_reduce", _c_p, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p,
                         _c_p)
@@ -446,7 +447,7 @@ def _major(t: torch.Tensor, contraction_last: bool):
 def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = None, act: int = 0,
          out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, accumulate: int = 0,
          step: Optional[torch.Tensor] = None, alpha: float = 1.0, comm=None, rs_dst: Optional[torch.Tensor] = None,
-         gather: Optional[tuple] = None):
+         gather: Optional[tuple] = None, causal: int = 0):
     """`out = act(alpha * a @ b + bias)` on the tcgen05 kernel. `a`: (M,K) or (B,M,K); `b`: (K,N) or (B,K,N); either may
     be a transposed view. With `accumulate=1` the result is added to `out`, with `accumulate=2` it is folded into `out`
     as a running mean with count `step`. `accumulate=3` with `comm` (a group context owning `out` in symmetric memory)
@@ -454,7 +455,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
     `accumulate=4` with `comm` and `rs_dst` (int64 device tensor: every rank's zeroed output shard, `out` being this
     rank's) reduce-scatters the product over the rows instead. `gather=(mode, src_ptrs, flags, blocks_per_shard,
     n_copy)` pulls the remote row blocks of the sharded operand (mode 1: `a`, mode 2: `b`) from the peers inside the
-    kernel. Returns NotImplemented for operands the kernel cannot take."""
+    kernel. `causal` (1, 2, 3) skips the masked half of square attention products: 1 = output tiles above the diagonal
+    (Q K^T), 2 = contraction up to the row (P V), 3 = contraction from the row (P^T dO).
+    Returns NotImplemented for operands the kernel cannot take."""
     if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16) or not (a.is_cuda and b.is_cuda):
         return NotImplemented
     batched = a.dim() == 3
@@ -518,7 +521,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
                      int(a.dtype == torch.float16), _CODE[out.dtype], bias.data_ptr() if bias is not None else None,
                      _CODE[bias.dtype] if bias is not None else 0, act, accumulate,
                      step.data_ptr() if step is not None else None, float(alpha), err.data_ptr(), _sms(a.device), pads,
-                     crank, cworld, lsync, rs_ptr, rs_rows, g_mode, g_src, g_dst, g_flags, g_bps, g_copy, _stream())
+                     crank, cworld, lsync, rs_ptr, rs_rows, g_mode, g_src, g_dst, g_flags, g_bps, g_copy, int(causal),
+                     _stream())
     if rc < 0:
         return NotImplemented
     _check(rc, "gemm_tcgen05")
@@ -650,6 +654,10 @@ def _heads_view(mat, col0, B, S, H, D):
     return torch.as_strided(mat, (B, H, S, D), (S * ld, D, ld, 1), mat.storage_offset() + col0)
 
 
+# the masked half of causal attention products is not computed (XL_CAUSAL_SKIP=0 computes the full products)
+_CAUSAL_SKIP = os.environ.get("XL_CAUSAL_SKIP", "1") != "0"
+
+
 @native("attention_qkv")
 def attention_qkv_cuda(qkv, sin, cos, seq_len, n_heads, head_dim, rotary_dim, causal, scale, inplace):
     if qkv.dtype not in (torch.bfloat16, torch.float16) or not (qkv.is_cuda and qkv.is_contiguous()):
@@ -667,8 +675,9 @@ def attention_qkv_cuda(qkv, sin, cos, seq_len, n_heads, head_dim, rotary_dim, ca
     out = torch.empty((T, hd), dtype=qkv.dtype, device=qkv.device)
     o = _heads_view(out, 0, B, S, H, D)
     lse = torch.empty((B, H, S), dtype=torch.float32, device=qkv.device)
+    c1, c2, c3 = (1, 2, 3) if causal and _CAUSAL_SKIP else (0, 0, 0)
     for b in range(B):
-        scores = gemm(q[b], k[b].transpose(-1, -2))
+        scores = gemm(q[b], k[b].transpose(-1, -2), causal=c1)
         if scores is NotImplemented:
             return NotImplemented
         rc = _sm_fwd(scores.data_ptr(), lse[b].data_ptr(), H * S, S, S, float(scale), int(bool(causal)),
@@ -677,7 +686,7 @@ def attention_qkv_cuda(qkv, sin, cos, seq_len, n_heads, head_dim, rotary_dim, ca
             return NotImplemented
         _check(rc, "attn_softmax_fwd")
         _count("attn_softmax_fwd")
-        if gemm(scores, v[b], out=o[b]) is NotImplemented:
+        if gemm(scores, v[b], out=o[b], causal=c2) is NotImplemented:
             return NotImplemented
     return out, rot, lse
 
@@ -696,8 +705,9 @@ def attention_qkv_grad_cuda(qkv_rot, lse, dout, sin, cos, seq_len, n_heads, head
     dqkv = torch.empty_like(qkv_rot)
     dq, dk, dv = (_heads_view(dqkv, i * hd, B, S, H, D) for i in range(3))
     tmp_lse = torch.empty((H, S), dtype=torch.float32, device=qkv_rot.device)
+    c1, c2, c3 = (1, 2, 3) if causal and _CAUSAL_SKIP else (0, 0, 0)
     for b in range(B):
-        p = gemm(q[b], k[b].transpose(-1, -2))
+        p = gemm(q[b], k[b].transpose(-1, -2), causal=c1)
         if p is NotImplemented:
             return NotImplemented
         rc = _sm_fwd(p.data_ptr(), tmp_lse.data_ptr(), H * S, S, S, float(scale), int(bool(causal)), _CODE[p.dtype],
@@ -706,15 +716,16 @@ def attention_qkv_grad_cuda(qkv_rot, lse, dout, sin, cos, seq_len, n_heads, head
             return NotImplemented
         _check(rc, "attn_softmax_fwd")
         _count("attn_softmax_fwd")
-        if gemm(p.transpose(-1, -2), do[b], out=dv[b]) is NotImplemented:
+        if gemm(p.transpose(-1, -2), do[b], out=dv[b], causal=c3) is NotImplemented:
             return NotImplemented
-        dp = gemm(do[b], v[b].transpose(-1, -2))
+        dp = gemm(do[b], v[b].transpose(-1, -2), causal=c1)
         if dp is NotImplemented:
             return NotImplemented
         _check(_sm_bwd(p.data_ptr(), dp.data_ptr(), H * S, S, S, float(scale), int(bool(causal)), _CODE[p.dtype],
                        _stream()), "attn_softmax_bwd")
         _count("attn_softmax_bwd")
-        if gemm(dp, k[b], out=dq[b]) is NotImplemented or gemm(dp.transpose(-1, -2), q[b], out=dk[b]) is NotImplemented:
+        if gemm(dp, k[b], out=dq[b], causal=c2) is NotImplemented \
+                or gemm(dp.transpose(-1, -2), q[b], out=dk[b], causal=c3) is NotImplemented:
             return NotImplemented
     if rotary_dim:
         rotary_launch(dq, sin, cos, dq, rotary_dim, True)
@@ -890,10 +901,16 @@ def _gq_scratch(device, n_tiles: int):
 
 def gq_gemm_small_m(x, packed, scale, zero, bias, out=None, act_from_col=None, ctas=None):
     """`x (M<=16, K) @ dequant(packed (N, K/gs, gs/4))^T + bias` with the de-quantisation fused into the GEMM; GELU on
-    the output columns `>= act_from_col` if given. `x` and `out` may be column windows of wider row-major matrices."""
+    the output columns `>= act_from_col` if given. `x` and `out` may be column windows of wider row-major matrices.
+    With `zero=None`, `scale` holds (scale, zero) pairs laid out `(K/gs, N, 2)` (see `interleave_scale_zero`)."""
     M, K = x.shape
     N, groups, words = packed.shape
     gs = words * 4
+    transposed = zero is None
+    if transposed:
+        if scale.shape != (groups, N, 2) or not scale.is_contiguous():
+            return NotImplemented
+        zero = scale
     if M > 16 or not x.is_cuda or x.dtype not in (torch.bfloat16, torch.float16) or x.stride(1) != 1:
         return NotImplemented
     if x.stride(0) % 8 or x.data_ptr() % 16 or not _ok(scale, zero, bias):
@@ -908,8 +925,8 @@ def gq_gemm_small_m(x, packed, scale, zero, bias, out=None, act_from_col=None, c
     ws, counters = _gq_scratch(x.device, n_tiles)
     rc = _gq_small(x.data_ptr(), packed.data_ptr(), scale.data_ptr(), zero.data_ptr(),
                    bias.data_ptr() if bias is not None else None, y.data_ptr(), M, N, K, gs, x.stride(0), y.stride(0),
-                   N if act_from_col is None else int(act_from_col), int(ctas or 3 * _sms(x.device)),
-                   ws.data_ptr(), counters.data_ptr(), _CODE[x.dtype], _CODE[scale.dtype], _stream())
+                   N if act_from_col is None else int(act_from_col), int(ctas or 2 * _sms(x.device)),
+                   ws.data_ptr(), counters.data_ptr(), _CODE[x.dtype], _CODE[scale.dtype], int(transposed), _stream())
     if rc == -1:
         return NotImplemented
     _check(rc, "gq_gemm_small_m")
@@ -952,6 +969,14 @@ def _register_late():
         return gq_gemm_small_m(xw, packed, scale, zero, b[0] if b else None, act_from_col=act_from_col)
 
     OPS["linear_gq_window"].native["cuda"] = linear_gq_window_cuda
+
+    def linear_gq_window_t_cuda(x, packed, sz, *b, x_col, k, act_from_col):
+        xw = x[:, x_col:x_col + k]
+        if xw.shape[0] > 16:
+            return NotImplemented
+        return gq_gemm_small_m(xw, packed, sz, None, b[0] if b else None, act_from_col=act_from_col)
+
+    OPS["linear_gq_window_t"].native["cuda"] = linear_gq_window_t_cuda
 
 
 _register_late()

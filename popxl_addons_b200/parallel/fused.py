@@ -12,7 +12,7 @@ from ..xl.core import ReplicaGrouping
 from .symm import LOCAL_SYNC_OFFSET, SymmArena
 
 _SMALL_ALL_REDUCE_ELEMS = 16384  # fp32 elements served by the one-shot kernel (64 KiB)
-_SMALL_ALL_REDUCE_16BIT_BYTES = 256 << 10  # 16-bit activations served by the one-shot multimem kernel
+_SMALL_ALL_REDUCE_16BIT_BYTES = 128 << 10  # 16-bit activations served by the one-shot multimem kernel
 
 
 # multimem needs NVLS; tests that lose a rank on purpose switch it off together with NCCL's
@@ -27,7 +27,9 @@ class GroupContext:
         self.pg, self.members = pg, members
         self.arena = SymmArena(nbytes, pg, session.device)
         self.rank, self.world = self.arena.rank, self.arena.world
-        self.stage = self.arena.alloc((_SMALL_ALL_REDUCE_16BIT_BYTES // 4,), torch.float32)  # staging, small all-reduces
+        self.stage = self.arena.alloc((_SMALL_ALL_REDUCE_ELEMS,), torch.float32)  # staging of the small fp32 all-reduce
+        # two alternating halves for the one-shot 16-bit all-reduce
+        self.stage16 = self.arena.alloc((2 * _SMALL_ALL_REDUCE_16BIT_BYTES,), torch.uint8)
         self.err = torch.zeros(1, dtype=torch.int32, device=session.device)
 
     def check(self):
@@ -145,7 +147,7 @@ def gathered_operand(ctx: GroupContext, rows: int, cols: int, dtype, block_rows:
     return full, full[ctx.rank * per:(ctx.rank + 1) * per]
 
 
-def all_gather_gemm(ctx: GroupContext, a_full: torch.Tensor, b: torch.Tensor, sharded: str = "a", n_copy: int = 8,
+def all_gather_gemm(ctx: GroupContext, a_full: torch.Tensor, b: torch.Tensor, sharded: str = "a", n_copy: int = 16,
                     **gemm_kwargs):
     """`a_full @ b` where one operand is row-sharded over the group and only this rank's rows are present at launch
     (`sharded="a"`: `a_full (M, K)` split over M; `sharded="b"`: `b (K, N)` split over K, e.g. a weight whose shards
@@ -188,18 +190,19 @@ def small_all_reduce(ctx: GroupContext, t: torch.Tensor, op: str) -> Optional[to
 
 def small_all_reduce_16bit(ctx: GroupContext, t: torch.Tensor) -> Optional[torch.Tensor]:
     """Sum all-reduce of a small bf16/fp16 tensor (decode-step activations): every rank stages its input in symmetric
-    memory and reads the sum of all replicas with `multimem.ld_reduce` (fp32 accumulation inside NVSwitch). One kernel,
-    two signal rounds; no data crosses NVLink twice."""
+    memory and reads the sum of all replicas with `multimem.ld_reduce` (fp32 accumulation inside NVSwitch). One kernel
+    (staging copy included), one signal round."""
     nat = _lib()
     nbytes = t.numel() * 2
     if t.dtype not in (torch.bfloat16, torch.float16) or nbytes > _SMALL_ALL_REDUCE_16BIT_BYTES or nbytes % 16 \
-            or ctx.world == 1 or not ctx.arena.mc_base:
+            or ctx.world == 1 or not ctx.arena.mc_base or t.data_ptr() % 16:
         return None
-    stage = ctx.stage.view(t.dtype)[:t.numel()]
-    stage.copy_(t.reshape(-1))
     out = torch.empty_like(t)
-    rc = nat._symm_all_reduce_mc(ctx.arena.multicast_ptr(stage), ctx.arena.pads_dev.data_ptr(), out.data_ptr(), nbytes,
-                                 nat._CODE[t.dtype], ctx.rank, ctx.world, 6, ctx.err.data_ptr(), nat._stream())
+    state = ctx.arena.local_sync[4:6]
+    rc = nat._symm_all_reduce_mc(t.data_ptr(), ctx.stage16.data_ptr(), ctx.arena.multicast_ptr(ctx.stage16),
+                                 _SMALL_ALL_REDUCE_16BIT_BYTES, state.data_ptr(), ctx.arena.pads_dev.data_ptr(),
+                                 out.data_ptr(), nbytes, nat._CODE[t.dtype], ctx.rank, ctx.world, 16, ctx.err.data_ptr(),
+                                 nat._stream())
     if rc == -1:
         return None
     nat._check(rc, "symm_all_reduce_mc")

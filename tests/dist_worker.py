@@ -27,9 +27,9 @@ def main():
     ap.add_argument("--fused", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--big", type=int, default=0)
-    ap.add_argument("--m", type=int, default=2048)
-    ap.add_argument("--n", type=int, default=4096)
-    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--gemm-m", dest="m", type=int, default=2048)
+    ap.add_argument("--gemm-n", dest="n", type=int, default=4096)
+    ap.add_argument("--gemm-k", dest="k", type=int, default=4096)
     ap.add_argument("--n-copy", type=int, default=8)
     ap.add_argument("--slots", type=int, default=2)
     args = ap.parse_args()
@@ -145,6 +145,31 @@ def main():
 
         result["rs_nccl_ms"] = timed(nccl_rs)
         result["gemm_ms"] = timed(lambda: native.gemm(a, w))
+
+        # GEMM + all-reduce: multimem.red epilogue (zero + kernel + copy out, as the graph op does) vs GEMM + NCCL
+        def fused_ar():
+            out = ctx.arena.ring((M, N), a.dtype)
+            out.zero_()
+            native.gemm(a, w, out=out, accumulate=3, comm=ctx)
+            return out.clone()
+
+        def nccl_ar():
+            y = native.gemm(a, w)
+            dist.all_reduce(y)
+            return y
+
+        got = fused_ar()
+        torch.cuda.synchronize()
+        result["ar_err"] = float((got.float() - full).abs().max() / full.abs().max())
+        result["ar_fused_ms"] = timed(fused_ar)
+        result["ar_nccl_ms"] = timed(nccl_ar)
+        ybuf = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        result["nccl_all_reduce_only_ms"] = timed(lambda: dist.all_reduce(ybuf))
+        small = torch.randn(2048, device=dev)
+        result["small_all_reduce_ms"] = timed(lambda: s.comm.all_reduce([small], ir.replica_grouping(), "add"))
+        act = torch.randn(16, 4096, device=dev).bfloat16()
+        result["mc_all_reduce_16x4096_ms"] = timed(lambda: s.comm.all_reduce([act], ir.replica_grouping(), "add"))
+        result["nccl_all_reduce_16x4096_ms"] = timed(lambda: dist.all_reduce(act))
         # --- all-gather of the left operand (rows sharded) ---------------------------------------------------------------
         a_full, a_own = fused.gathered_operand(ctx, M, K, torch.bfloat16, 128, "a")
         a_own.copy_((torch.randn(M // world, K, device=dev) * 0.1).bfloat16())
@@ -289,6 +314,10 @@ def main():
         os._exit(0)
     if dist.is_initialized():
         dist.barrier()
+        if args.device == "cuda":
+            # leave without tearing NCCL down: with captured CUDA graphs alive that has been seen to block for minutes
+            sys.stdout.flush()
+            os._exit(0)
         dist.destroy_process_group()
 
 

@@ -94,10 +94,10 @@ def test_gpu_rank_collectives():
 def test_gpu_gemm_reduce_scatter_and_all_gather_gemm():
     """The tcgen05 GEMM with the reduce-scatter epilogue (`red.add` into the owner's shard) and with the all-gather
     prologue (copy CTAs pulling peer row blocks) against NCCL + fp32 matmul on the same data."""
-    res = launch(2, "--mode", "fusedgemm", "--m", "1024", "--n", "1024", "--k", "1024", timeout=300,
+    res = launch(2, "--mode", "fusedgemm", "--gemm-m", "1024", "--gemm-n", "1024", "--gemm-k", "1024", timeout=300,
                  env={"XL_COLLECTIVE_TIMEOUT_S": "120"})
     assert res["errors"] is None
-    assert res["rs_err"] < 2e-2 and res["ag_a_err"] < 2e-2 and res["ag_b_err"] < 2e-2
+    assert res["rs_err"] < 2e-2 and res["ag_a_err"] < 2e-2 and res["ag_b_err"] < 2e-2 and res["ar_err"] < 2e-2
     assert res["ag_a_gathered_ok"] and res["ag_b_gathered_ok"]
 
 

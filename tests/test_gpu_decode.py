@@ -72,6 +72,14 @@ def test_gq_gemm_small_m_windows_split_k_and_gelu(nat, ctas):
         assert y is not NotImplemented
         torch.testing.assert_close(ybuf[:, 128:128 + N].float(), want, rtol=2e-2, atol=6e-2)
     assert float(ybuf[:, :128].abs().sum()) == 0 and float(ybuf[:, 128 + N:].abs().sum()) == 0
+    # the same with the scales and zero points as group-major (scale, zero) pairs
+    from popxl_addons_b200.layers.linear_gq import interleave_scale_zero
+
+    ybuf.zero_()
+    y = nat.gq_gemm_small_m(xbuf[:, 256:256 + K], packed, interleave_scale_zero(scale, zero), None, bias,
+                            out=ybuf[:, 128:128 + N], act_from_col=600, ctas=ctas)
+    assert y is not NotImplemented
+    torch.testing.assert_close(ybuf[:, 128:128 + N].float(), want, rtol=2e-2, atol=6e-2)
 
 
 def test_add_layer_norm(nat):
