@@ -26,11 +26,11 @@ constexpr int GQ_KCHUNK = 128;   // k values per warp iteration (32 per lane qua
 
 __device__ __forceinline__ void mma_m16n8k16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2], bool bf16) {
   if (bf16) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
   } else {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
   }
@@ -140,6 +140,13 @@ __global__ void __launch_bounds__(GQ_WARPS * 32, 2)
           }
         }
       }
+      T2 s2[GQ_NT], z2[GQ_NT];
+#pragma unroll
+      for (int t = 0; t < GQ_NT; ++t) {
+        const uint16_t s16 = (uint16_t)(sz[t] & 0xFFFFu), z16 = (uint16_t)(sz[t] >> 16);
+        s2[t] = F::pair(xl_to_float(*reinterpret_cast<const S*>(&s16)));
+        z2[t] = F::pair(xl_to_float(*reinterpret_cast<const S*>(&z16)));
+      }
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         uint4 xa[2], xb[2];
@@ -152,20 +159,18 @@ __global__ void __launch_bounds__(GQ_WARPS * 32, 2)
         }
         const uint32_t* xa32 = reinterpret_cast<const uint32_t*>(xa);
         const uint32_t* xb32 = reinterpret_cast<const uint32_t*>(xb);
+        // k-step outermost: consecutive MMAs go to different accumulators, so none waits for its predecessor
 #pragma unroll
-        for (int t = 0; t < GQ_NT; ++t) {
-          const uint32_t* w32 = reinterpret_cast<const uint32_t*>(&wq[t]);
-          const uint16_t s16 = (uint16_t)(sz[t] & 0xFFFFu), z16 = (uint16_t)(sz[t] >> 16);
-          const T2 s2 = F::pair(xl_to_float(*reinterpret_cast<const S*>(&s16)));
-          const T2 z2 = F::pair(xl_to_float(*reinterpret_cast<const S*>(&z16)));
+        for (int mm = 0; mm < 2; ++mm) {
+          const uint32_t a0[4] = {xa32[4 * mm], xb32[4 * mm], xa32[4 * mm + 1], xb32[4 * mm + 1]};
+          const uint32_t a1[4] = {xa32[4 * mm + 2], xb32[4 * mm + 2], xa32[4 * mm + 3], xb32[4 * mm + 3]};
 #pragma unroll
-          for (int mm = 0; mm < 2; ++mm) {
-            // 32-bit word m holds packed words 2m and 2m+1, i.e. k_lane + 8m .. 8m+7
+          for (int t = 0; t < GQ_NT; ++t) {
+            // 32-bit word m of a lane's 16 bytes holds packed words 2m and 2m+1, i.e. k_lane + 8m .. 8m+7
+            const uint32_t w = reinterpret_cast<const uint32_t*>(&wq[t])[2 * half + mm];
             uint32_t b[4];
-            gq_dequant8<T>(w32[2 * half + mm], s2, z2, b);
+            gq_dequant8<T>(w, s2[t], z2[t], b);
             const uint32_t b0[2] = {b[0], b[1]}, b1[2] = {b[2], b[3]};
-            const uint32_t a0[4] = {xa32[4 * mm], xb32[4 * mm], xa32[4 * mm + 1], xb32[4 * mm + 1]};
-            const uint32_t a1[4] = {xa32[4 * mm + 2], xb32[4 * mm + 2], xa32[4 * mm + 3], xb32[4 * mm + 3]};
             mma_m16n8k16(c[t], a0, b0, BF);
             mma_m16n8k16(c[t], a1, b1, BF);
           }

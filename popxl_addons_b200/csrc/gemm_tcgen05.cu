@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     if (warp == 0) {
       constexpr int PIECE = 16384;
       constexpr int SLOTS = (L::TILE_BYTES / PIECE) < (2 * STAGES + 4) ? (L::TILE_BYTES / PIECE) : (2 * STAGES + 4);
-      constexpr int STORE_LAG = SLOTS / 2;  // loads in flight ahead of the stores
+      constexpr int STORE_LAG = SLOTS - 2;  // loads in flight ahead of the stores (remote latency dominates)
       constexpr int FLAG_LAG = 2;           // a block is flagged once its last store is FLAG_LAG groups behind
       bool ok = true;
       // peers are ready (their shards are final) once the group barrier has completed; CTA 0 runs it for all copy CTAs

@@ -148,12 +148,14 @@ class DecoderBlock(Module):
                                     overwrite=True)
         return ops.layer_norm(x, w, b, eps=cfg.eps)
 
-    def _attention(self, h, sin, cos, par):
+    def _attention(self, h, sin, cos, par, collectives: bool = True):
+        """`collectives=False`: the caller has marked `h` as identical over the TP group and reduces the result itself
+        (blocks whose attention and feed-forward share input and output need one all-reduce, not two)."""
         cfg = self.cfg
         heads = cfg.heads // par.tp
         hd = heads * cfg.head_dim
         bias = cfg.family == "gpt2"
-        if par.tp > 1:
+        if par.tp > 1 and collectives:
             h = replicated_all_reduce_identical_inputs(h, group=par.tp_group)
         wqkv, bqkv = self._linear("attention.qkv", h, 3 * hd, bias, par)
         qkv = ops.linear_bias_act(h, wqkv, bqkv) if bqkv is not None else h @ wqkv
@@ -163,7 +165,7 @@ class DecoderBlock(Module):
                                      _normal((hd, cfg.hidden), cfg.init_std / math.sqrt(2 * cfg.layers), cfg.np_dtype),
                                      cfg.xl_dtype, replica_grouping=par.sharded_rg, overwrite=True)
         o = a @ wo
-        if par.tp > 1:
+        if par.tp > 1 and collectives:
             o = replicated_all_reduce_identical_grad_inputs(o, group=par.tp_group)
         if bias:
             bo = self.add_variable_input("attention.out.bias", _const_init("zeros", (cfg.hidden,), cfg.np_dtype),
@@ -171,10 +173,11 @@ class DecoderBlock(Module):
             o = o + bo
         return o
 
-    def _mlp(self, h, par):
+    def _mlp(self, h, par, collectives: bool = True):
+        """With `collectives=False` returns `(partial result, output bias)`: the caller reduces and adds the bias."""
         cfg = self.cfg
         f = cfg.ffn // par.tp
-        if par.tp > 1:
+        if par.tp > 1 and collectives:
             h = replicated_all_reduce_identical_inputs(h, group=par.tp_group)
         if cfg.family == "llama":
             wg, _ = self._linear("mlp.gate", h, f, False, par)
@@ -192,6 +195,8 @@ class DecoderBlock(Module):
         if cfg.family != "llama":
             b2 = self.add_variable_input("mlp.fc_out.bias", _const_init("zeros", (cfg.hidden,), cfg.np_dtype),
                                          cfg.xl_dtype, overwrite=True)
+        if not collectives:
+            return z @ w2, b2
         if par.tp == 1 and b2 is not None:
             return ops.linear_bias_act(z, w2, b2)
         y = z @ w2
@@ -205,7 +210,15 @@ class DecoderBlock(Module):
         if cfg.family == "gptj":
             # parallel residual: attention and feed-forward read the same normalised input
             h = self._norm("ln_1", x)
-            return x + self._attention(h, sin, cos, par) + self._mlp(h, par)
+            if par.tp == 1:
+                return x + self._attention(h, sin, cos, par) + self._mlp(h, par)
+            # one identity / all-reduce pair around both branches: a single all-reduce per layer in the forward pass
+            # (of the summed partial results) and a single one in the backward pass (of the summed input gradients)
+            h = replicated_all_reduce_identical_inputs(h, group=par.tp_group)
+            o = self._attention(h, sin, cos, par, collectives=False)
+            y, b2 = self._mlp(h, par, collectives=False)
+            s = replicated_all_reduce_identical_grad_inputs(o + y, group=par.tp_group)
+            return x + s + b2
         x = x + self._attention(self._norm("ln_1", x), sin, cos, par)
         return x + self._mlp(self._norm("ln_2", x), par)
 

@@ -803,7 +803,7 @@ def _attn_decode_launch(qkv, k_cache, v_cache, pos, n_heads, head_dim, scale, ou
     B, smax = qkv.shape[0], k_cache.shape[2]
     bh = B * n_heads
     # enough CTAs to fill the machine, at least 32 cache positions per CTA
-    splits = max(1, min((4 * _sms(qkv.device) + bh - 1) // bh, (smax + 31) // 32, 64))
+    splits = max(1, min((8 * _sms(qkv.device) + bh - 1) // bh, (smax + 31) // 32, 64))
     ws = workspace(bh * splits * (head_dim + 2) * 4, qkv.device, "attn_decode")
     idx = qkv.device.index or 0
     counters = _AD_SCRATCH.get(idx)

@@ -105,6 +105,25 @@ def matmul_all_reduce(ex, op, a_vals, w_vals):
     return [out.clone()]
 
 
+def matmul2_all_reduce(ex, op, a1_vals, w1_vals, a2_vals, w2_vals):
+    """`all_reduce(a1 @ w1 + a2 @ w2)`: both GEMMs push their tiles (`multimem.red`) into the same zeroed output."""
+    nat = _lib()
+    a1, w1, a2, w2 = a1_vals[0], w1_vals[0], a2_vals[0], w2_vals[0]
+    ctx = runtime(ex).context(op.attrs["group"])
+    if ctx.world == 1 or not _MC_ALL_REDUCE or not ctx.arena.mc_base or w1.shape[-1] % 8:
+        return NotImplemented
+    if a1.dtype not in (torch.bfloat16, torch.float16) or a2.dtype != a1.dtype:
+        return NotImplemented
+    M, N = a1.shape[0], w1.shape[-1]
+    out = ctx.arena.ring((M, N), a1.dtype)
+    out.zero_()
+    if nat.gemm(a1, w1, out=out, accumulate=3, comm=ctx) is NotImplemented:
+        return NotImplemented
+    if nat.gemm(a2, w2, out=out, accumulate=3, comm=ctx) is NotImplemented:
+        raise RuntimeError("second GEMM of a fused pair was rejected after the first one ran")
+    return [out.clone()]
+
+
 def _peer_ptr_tensor(ctx: GroupContext, t: torch.Tensor) -> torch.Tensor:
     """int64 device tensor with the address of arena tensor `t` in every rank's memory (cached per buffer)."""
     cache = ctx.__dict__.setdefault("_peer_ptr_cache", {})
@@ -281,7 +300,7 @@ def rts_adam(ex, op, w_vals, acc_vals, master_vals, m_vals, v_vals, step_vals):
     return True
 
 
-_TABLE = {"matmul_all_reduce": matmul_all_reduce, "rts_adam": rts_adam}
+_TABLE = {"matmul_all_reduce": matmul_all_reduce, "matmul2_all_reduce": matmul2_all_reduce, "rts_adam": rts_adam}
 
 
 def lookup(name: str, session):

@@ -47,10 +47,86 @@ OpDef("matmul_all_reduce", special=_special_matmul_all_reduce, vjp=_vjp_matmul_a
       flops=lambda op: 2 * op.inputs[0].shape[-1] * op.outputs[0].nelms)
 
 
+def _special_matmul2_all_reduce(ex, op, env):
+    a1, w1, a2, w2 = (env[t] for t in op.inputs)
+    native = ex.native_collective("matmul2_all_reduce")
+    if native is not None:
+        res = native(ex, op, a1, w1, a2, w2)
+        if res is not NotImplemented:
+            env[op.outputs[0]] = res
+            return
+    mm = OPS["matmul"]
+    fn = mm.native.get(ex.device.type) if ex.use_native else None
+
+    def product(a, w):
+        y = fn(a, w) if fn is not None else NotImplemented
+        return mm.impl(a, w) if y is NotImplemented else y
+
+    outs = []
+    for r in range(ex.num_local):
+        y = product(a1[r], w1[r])
+        y += product(a2[r], w2[r])
+        outs.append(y)
+    env[op.outputs[0]] = ex.comm.all_reduce(outs, op.attrs["group"], "add", inplace=True)
+
+
+def _vjp_matmul2_all_reduce(ctx, op, gs):
+    from ..xl.ops import matmul, reshape, transpose
+
+    (g,) = gs
+    grads = []
+    g2 = reshape(g, (-1, g.shape[-1]))
+    for a, w in ((op.inputs[0], op.inputs[1]), (op.inputs[2], op.inputs[3])):
+        fa, fw = ctx.fwd(a), ctx.fwd(w)
+        grads += [matmul(g, transpose(fw)), matmul(transpose(reshape(fa, (-1, a.shape[-1]))), g2)]
+    return grads
+
+
+OpDef("matmul2_all_reduce", special=_special_matmul2_all_reduce, vjp=_vjp_matmul2_all_reduce, collective=True,
+      infer=lambda op: [((*op.inputs[0].shape[:-1], op.inputs[1].shape[-1]), op.inputs[0].dtype, ())],
+      flops=lambda op: 2 * (op.inputs[0].shape[-1] + op.inputs[2].shape[-1]) * op.outputs[0].nelms)
+
+
+def _fuse_pairs(g) -> int:
+    """`all_reduce(matmul(a1, w1) + matmul(a2, w2))` -> one op: both GEMMs push their tiles into the same output."""
+    consumers = {}
+    for op in g.ops:
+        for t in op.inputs:
+            consumers.setdefault(t, []).append(op)
+    fused, skip = 0, set()
+    for ar in g.ops:
+        if ar.opdef.name != "all_reduce" or ar.attrs["op"] != "add" or ar.attrs.get("identical_inputs") \
+                or ar.attrs["group"].group_size <= 1:
+            continue
+        add = ar.inputs[0].producer
+        if add is None or add.opdef.name != "add" or add.graph is not g or len(consumers.get(add.outputs[0], [])) != 1 \
+                or add.outputs[0] in g._outputs:
+            continue
+        mms = [t.producer for t in add.inputs]
+        if any(m is None or m.opdef.name != "matmul" or m.graph is not g or len(consumers.get(m.outputs[0], [])) != 1
+               or m.outputs[0] in g._outputs or m.inputs[0].rank != 2 or m.inputs[1].rank != 2 for m in mms):
+            continue
+        if mms[0] is mms[1] or mms[0].outputs[0].shape != mms[1].outputs[0].shape:
+            continue
+        # the fused op takes the place of the all-reduce (all four operands exist by then)
+        ar.opdef = OPS["matmul2_all_reduce"]
+        ar.name = "matmul2_all_reduce"
+        ar.inputs = [mms[0].inputs[0], mms[0].inputs[1], mms[1].inputs[0], mms[1].inputs[1]]
+        ar.attrs = {"group": ar.attrs["group"]}
+        skip.update({add.uid, mms[0].uid, mms[1].uid})
+        fused += 1
+    if fused:
+        g.ops = [o for o in g.ops if o.uid not in skip]
+    return fused
+
+
 def fuse_gemm_collectives(ir: xl.Ir) -> int:
-    """Rewrite `matmul -> all_reduce(add)` pairs (matmul result used by nothing else, 2-D weight) in every graph of
-    `ir`. Returns the number of fused pairs. Run after autodiff and `apply_pre_alias_patterns`."""
+    """Rewrite `matmul -> all_reduce(add)` pairs (matmul result used by nothing else, 2-D weight) and
+    `all_reduce(matmul + matmul)` triples in every graph of `ir`. Returns the number of fused collectives. Run after
+    autodiff and `apply_pre_alias_patterns`."""
     fused = 0
+    for g in ir.graphs:
+        fused += _fuse_pairs(g)
     for g in ir.graphs:
         consumers = {}
         for op in g.ops:

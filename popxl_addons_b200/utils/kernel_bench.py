@@ -38,7 +38,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--peaks", default=os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json"))
     ap.add_argument("--out", default=None)
+    ap.add_argument("--only", default=None, help="run only the rows whose name contains this text (profiler captures)")
+    ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
+    want = (lambda name: args.only is None or args.only in name)
     peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
     src = "fallback"
     if os.path.exists(args.peaks):
@@ -50,14 +53,16 @@ def main():
     bf = torch.bfloat16
 
     def gemm_row(name, M, N, K, a_t=False, b_t=False, batch=1):
+        if not want(name):
+            return
         a = torch.randn((batch, K, M) if a_t else (batch, M, K), device="cuda", dtype=bf)
         b = torch.randn((batch, N, K) if b_t else (batch, K, N), device="cuda", dtype=bf)
         av = a.transpose(-1, -2) if a_t else a
         bv = b.transpose(-1, -2) if b_t else b
         if batch == 1:
             av, bv = av[0], bv[0]
-        ours = time_ms(lambda: nat.gemm(av, bv))
-        lib = time_ms(lambda: torch.matmul(av, bv))
+        ours = time_ms(lambda: nat.gemm(av, bv), iters=args.iters)
+        lib = time_ms(lambda: torch.matmul(av, bv), iters=args.iters) if args.only is None else ours
         fl = 2.0 * M * N * K * batch
         rows.append(dict(kernel=name, shape=f"{batch}x{M}x{N}x{K}", ms=ours, tflops=fl / ours / 1e9,
                          frac_of_peak=fl / ours / 1e9 / peaks["bf16_tflops"], lib_ms=lib, lib_tflops=fl / lib / 1e9,
@@ -74,7 +79,9 @@ def main():
     gemm_row("gemm square 8192", 8192, 8192, 8192)
 
     def mem_row(name, fn, nbytes):
-        ms = time_ms(fn)
+        if not want(name):
+            return
+        ms = time_ms(fn, iters=args.iters)
         rows.append(dict(kernel=name, ms=ms, gbs=nbytes / ms / 1e6, frac_of_peak=nbytes / ms / 1e6 / peaks["hbm_gbs"]))
 
     x = torch.randn(2048, 16384, device="cuda", dtype=bf)
@@ -107,6 +114,39 @@ def main():
     one = torch.ones((), device="cuda")
     mem_row("cross-entropy fwd+bwd 2048x50400", lambda: nat.ce_with_grad_cuda(lg, lab, one, None, "mean"),
             2 * lg.numel() * 2)
+    # ---- token-by-token decoding kernels (batch 16; GPT-J-6B shape at TP1 and at TP8) ----------------------------------
+    from popxl_addons_b200.layers.linear_gq import interleave_scale_zero
+    from popxl_addons_b200.models.generator import quantize_rows
+
+    def gq_row(name, N, K, act_from=None):
+        if not want(name):
+            return
+        wq = torch.randn(N, K, device="cuda") * 0.02
+        packed, scale, zero = quantize_rows(wq, 64)
+        sz = interleave_scale_zero(scale.half(), zero.half())
+        packed = packed.view(torch.uint16)
+        xin = torch.randn(16, K, device="cuda", dtype=bf)
+        nbytes = N * K // 2 + sz.numel() * 2 + xin.numel() * 2 + 16 * N * 2
+        mem_row(name, lambda: nat.gq_gemm_small_m(xin, packed, sz, None, None, act_from_col=act_from), nbytes)
+
+    gq_row("gq gemm M=16 [qkv|fc_in] tp1 28672x4096", 28672, 4096, 12288)
+    gq_row("gq gemm M=16 [out|fc_out] tp1 4096x20480", 4096, 20480)
+    gq_row("gq gemm M=16 [qkv|fc_in] tp8 3584x4096", 3584, 4096, 1536)
+    gq_row("gq gemm M=16 [out|fc_out] tp8 4096x2560", 4096, 2560)
+    for heads, tag in ((16, "tp1"), (2, "tp8")):
+        name = f"attn decode B=16 H={heads} D=256 len=576 {tag}"
+        if want(name):
+            qkv = torch.randn(16, 3 * heads * 256, device="cuda", dtype=bf)
+            kc = torch.randn(16, heads, 640, 256, device="cuda", dtype=bf)
+            vc = torch.randn_like(kc)
+            pos = torch.tensor(575, dtype=torch.int32, device="cuda")
+            mem_row(name, lambda: nat.attention_decode_packed_cuda(qkv, kc, vc, pos, heads, 256, 0.0625),
+                    2 * 16 * heads * 576 * 256 * 2)
+    if want("add_layer_norm 16x4096"):
+        xr = torch.randn(16, 4096, device="cuda", dtype=bf)
+        dl = torch.randn_like(xr)
+        mem_row("add_layer_norm 16x4096",
+                lambda: nat.add_layer_norm_cuda(xr, dl, w, b, has_delta=True, has_bias=False, eps=1e-5), 4 * xr.numel() * 2)
     nat.check_gemm_errors()
     print(f"peaks ({src}): hbm {peaks['hbm_gbs']} GB/s, bf16 {peaks['bf16_tflops']} TFLOP/s")
     for r in rows:

@@ -30,7 +30,7 @@ def main():
     ap.add_argument("--gemm-m", dest="m", type=int, default=2048)
     ap.add_argument("--gemm-n", dest="n", type=int, default=4096)
     ap.add_argument("--gemm-k", dest="k", type=int, default=4096)
-    ap.add_argument("--n-copy", type=int, default=8)
+    ap.add_argument("--n-copy", type=int, default=16)
     ap.add_argument("--slots", type=int, default=2)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
