@@ -93,6 +93,13 @@ PIPELINE_METRIC = "train tokens/s Llama-2-7B shape PPxDP (bf16, fp32 Adam, seq 2
 DECODE_METRIC = "int4 decode tokens/s GPT-J-6B shape, TP over all GPUs (batch 16, prompt 512, 128 new tokens, greedy)"
 
 
+def _shrink(cfg, k: int):
+    """One rank's share of a k-way tensor-parallel layout as a stand-alone model (diagnostics only)."""
+    cfg.heads //= k
+    cfg.ffn //= k
+    cfg.vocab_size = (cfg.vocab_size + k - 1) // k
+
+
 def _shutdown(dist):
     """Leave without tearing the NCCL communicators down: destroying them while captured CUDA graphs that contain
     their kernels are still alive has been seen to block for minutes."""
@@ -122,6 +129,8 @@ def run_decode(args):
     cfg = getattr(DecoderConfig, args.model)(tp=args.gpus, dp=1)
     if args.layers:
         cfg.layers = args.layers
+    if args.emulate_tp:
+        _shrink(cfg, args.emulate_tp)
     W, K = max(args.warmup, 3), args.steps
     B, P, N = args.batch, args.prompt_len, args.new_tokens
     t0 = time.perf_counter()
@@ -187,7 +196,9 @@ def run_decode(args):
                        if args.impl == "torch" else None,
                        "l2": "every decoding step streams all int4 weights and the KV cache (several GB in total), "
                              "beyond the 126 MB L2; no flush needed",
-                       "headline": not args.layers and args.model == "gptj_6b" and (B, P, N) == (16, 512, 128)},
+                       "headline": (not args.layers and not args.emulate_tp and args.model == "gptj_6b"
+                                    and (B, P, N) == (16, 512, 128)),
+                       "emulate_tp": args.emulate_tp or None},
             "clocks": clocks.summary(),
             "e2e": {"value": toks / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / K,
                     "h2d_bytes_per_step": B * P * 4, "d2h_bytes_per_step": B * N * 4},
@@ -222,6 +233,9 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--new-tokens", type=int, default=128)
     ap.add_argument("--no-cuda-graphs", action="store_true")
+    ap.add_argument("--emulate-tp", type=int, default=0,
+                    help="diagnostics: run ONE rank's shard shapes of a K-way tensor-parallel layout (heads, ffn and "
+                         "vocabulary divided by K, no collectives) to separate kernel time from communication")
     ap.add_argument("--torch-dense", action="store_true",
                     help="decode mode, --impl torch: keep a bf16 copy of every weight instead of de-quantising per call")
     args = ap.parse_args()
@@ -258,6 +272,8 @@ def main():
     cfg = getattr(DecoderConfig, args.model)(tp=tp, dp=dp)
     if args.layers:
         cfg.layers = args.layers
+    if args.emulate_tp:
+        _shrink(cfg, args.emulate_tp)
     W = max(args.warmup, 3)
     K = args.steps
     t0 = time.perf_counter()
@@ -376,7 +392,9 @@ def main():
                                     (", state sharded over dp (RTS)" if dp > 1 else ""),
                        "recompute": "per layer", "l2": "each step streams >100 GB of weights, optimizer state and "
                                                        "activations, far beyond the 126 MB L2; no flush needed",
-                       "headline": (not args.layers and args.model == "gptj_6b" and not pipeline and not args.tp
+                       "emulate_tp": args.emulate_tp or None,
+                       "headline": (not args.layers and not args.emulate_tp and args.model == "gptj_6b" and not pipeline
+                                    and not args.tp
                                     and args.micro_batch_size == 1 and args.micro_batches == 16)},
             "clocks": clocks.summary(),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": int(h2d),

@@ -220,3 +220,147 @@ XL_API int xl_symm_all_reduce_mc(const void* in, void* stage_local, const void* 
                                                        xl_host_comm_spin_limit);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Decode step: all-reduce of the layer output fused with the residual update and the next LayerNorm.
+//   x += sum over ranks(delta_partial) (+ bias);  h = LayerNorm(x) * w + b          rows <= 16, one CTA per row
+// Same protocol as the one-shot all-reduce above (and the same staging halves, counter and signal channels, so the two
+// kernels can be mixed in one program): CTA r copies row r of this rank's partial result into the current half, meets
+// the peers' CTA r at a barrier, reads the sum of all replicas of the row through the multicast address and normalises
+// it. One launch replaces staging copy + all-reduce + residual add + LayerNorm.
+// ---------------------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+    ar_add_layer_norm_kernel(T* __restrict__ x, const T* __restrict__ delta_partial, const T* __restrict__ bias,
+                             const T* __restrict__ w, const T* __restrict__ b, T* __restrict__ h, int cols, float eps,
+                             uint4* stage_local, const char* stage_mc, long long half_bytes, unsigned int* state,
+                             unsigned int* const* pads, int rank, int world, int channel, int* err, unsigned int limit) {
+  constexpr int MAX_VEC = 4;  // vectors of 8 elements per thread: cols <= 256 * 8 * 4
+  __shared__ int ok_s;
+  __shared__ float red[8];
+  __shared__ float stat[2];
+  const int row = blockIdx.x;
+  const int nvec = cols / 8;
+  const unsigned int parity = *((volatile unsigned int*)state) & 1u;
+  uint4* mine = stage_local + parity * (half_bytes / 16) + (long long)row * nvec;
+  const uint4* src = reinterpret_cast<const uint4*>(delta_partial + (long long)row * cols);
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) mine[i] = src[i];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const bool ok = xl_group_barrier(pads, rank, world, channel + row, err, limit);
+    if (threadIdx.x == 0) ok_s = ok;
+  }
+  __syncthreads();
+  const bool ok = ok_s != 0;
+  const char* red_src = stage_mc + parity * half_bytes + (long long)row * nvec * 16;
+  T* xr = x + (long long)row * cols;
+  float v[MAX_VEC][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAX_VEC; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      if (ok) {
+        const char* a = red_src + (size_t)vi * 16;
+        if (std::is_same<T, __nv_bfloat16>::value)
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "l"(a) : "memory");
+        else
+          asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w) : "l"(a) : "memory");
+      }
+      const T* de = reinterpret_cast<const T*>(&raw);
+      const uint4 xraw = *reinterpret_cast<const uint4*>(xr + vi * 8);
+      const T* xe = reinterpret_cast<const T*>(&xraw);
+      uint4 braw = make_uint4(0, 0, 0, 0);
+      if (bias) braw = *reinterpret_cast<const uint4*>(bias + vi * 8);
+      const T* be = reinterpret_cast<const T*>(&braw);
+      uint4 oraw;
+      T* oe = reinterpret_cast<T*>(&oraw);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float t = xl_to_float(xe[e]) + xl_to_float(de[e]);
+        if (bias) t += xl_to_float(be[e]);
+        oe[e] = xl_from_float<T>(t);
+        v[i][e] = xl_to_float(oe[e]);
+        sum += v[i][e];
+      }
+      *reinterpret_cast<uint4*>(xr + vi * 8) = oraw;
+    }
+  }
+  sum = xl_warp_sum(sum);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += red[i];
+    stat[0] = t / cols;
+  }
+  __syncthreads();
+  const float mean = stat[0];
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAX_VEC; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sq += (v[i][e] - mean) * (v[i][e] - mean);
+    }
+  }
+  sq = xl_warp_sum(sq);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < 8; ++i) t += red[i];
+    stat[1] = rsqrtf(t / cols + eps);
+  }
+  __syncthreads();
+  const float rstd = stat[1];
+#pragma unroll
+  for (int i = 0; i < MAX_VEC; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+      const uint4 wraw = *reinterpret_cast<const uint4*>(w + vi * 8), bbraw = *reinterpret_cast<const uint4*>(b + vi * 8);
+      const T* we = reinterpret_cast<const T*>(&wraw);
+      const T* bbe = reinterpret_cast<const T*>(&bbraw);
+      uint4 oraw;
+      T* oe = reinterpret_cast<T*>(&oraw);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) oe[e] = xl_from_float<T>((v[i][e] - mean) * rstd * xl_to_float(we[e]) + xl_to_float(bbe[e]));
+      *reinterpret_cast<uint4*>(h + (long long)row * cols + vi * 8) = oraw;
+    }
+  }
+  if (threadIdx.x == 0) {
+    const unsigned int ticket = atomicAdd(state + 1, 1u);
+    if (ticket == gridDim.x - 1) {
+      state[1] = 0;
+      __threadfence();
+      *((volatile unsigned int*)state) = parity + 1u;
+    }
+  }
+}
+
+// rows <= 16, cols % 8 == 0, cols <= 8192, rows * cols * 2 <= half_bytes, 16-bit dtype. Returns -1 otherwise.
+XL_API int xl_ar_add_layer_norm(void* x, const void* delta_partial, const void* bias, const void* w, const void* b, void* h,
+                                int rows, int cols, float eps, int dtype, void* stage_local, const void* stage_mc,
+                                long long half_bytes, unsigned int* state, const void* pads_dev, int rank, int world,
+                                int channel, int* err, cudaStream_t s) {
+  if (rows < 1 || rows > 16 || (cols % 8) || cols > 8192 || dtype == XL_F32 || world > 32 ||
+      (long long)rows * cols * 2 > half_bytes || w == nullptr || b == nullptr)
+    return -1;
+  if (dtype == XL_BF16)
+    ar_add_layer_norm_kernel<__nv_bfloat16><<<rows, 256, 0, s>>>(
+        (__nv_bfloat16*)x, (const __nv_bfloat16*)delta_partial, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)w,
+        (const __nv_bfloat16*)b, (__nv_bfloat16*)h, cols, eps, (uint4*)stage_local, (const char*)stage_mc, half_bytes, state,
+        (unsigned int* const*)pads_dev, rank, world, channel, err, xl_host_comm_spin_limit);
+  else
+    ar_add_layer_norm_kernel<__half><<<rows, 256, 0, s>>>(
+        (__half*)x, (const __half*)delta_partial, (const __half*)bias, (const __half*)w, (const __half*)b, (__half*)h, cols,
+        eps, (uint4*)stage_local, (const char*)stage_mc, half_bytes, state, (unsigned int* const*)pads_dev, rank, world,
+        channel, err, xl_host_comm_spin_limit);
+  return (int)cudaGetLastError();
+}

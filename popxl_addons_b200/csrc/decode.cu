@@ -107,6 +107,29 @@ __global__ void __launch_bounds__(GQ_WARPS * 32, 2)
   long long item = total * blockIdx.x / gridDim.x;
   const long long item_end = total * (blockIdx.x + 1) / gridDim.x;
   const bool row_lo = quad < M, row_hi = quad + 8 < M;
+  // Weights reach the MMAs through a per-warp double buffer in shared memory filled with cp.async: while a warp works on
+  // one chunk (8 tiles x 512 B) the next one, possibly of the next tile segment, is already in flight, so DRAM latency
+  // is hidden without spending registers. Every lane reads back exactly the 16-byte pieces it copied itself.
+  extern __shared__ uint4 wbuf_all[];
+  uint4* wbuf = wbuf_all + warp * (2 * GQ_NT * 32);
+  auto prefetch = [&](int tile_, int ch_, int buf_) {
+    const int k_lane_ = ch_ * GQ_KCHUNK + j * 32;
+#pragma unroll
+    for (int t = 0; t < GQ_NT; ++t) {
+      const int n = tile_ * (8 * GQ_NT) + t * 8 + quad;
+      uint4* dst = wbuf + (buf_ * GQ_NT + t) * 32 + lane;
+      if (n < N) {
+        const uint16_t* src = packed + (long long)n * (K / 4) + k_lane_ / 4;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+                     : "memory");
+      } else {
+        *dst = make_uint4(0, 0, 0, 0);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  int buf = 0;
+  bool have = false;  // wbuf[buf] already holds (or is receiving) this warp's first chunk of the current segment
   while (item < item_end) {
     const int tile = (int)(item / chunks);
     const int c0 = (int)(item - (long long)tile * chunks);
@@ -117,19 +140,34 @@ __global__ void __launch_bounds__(GQ_WARPS * 32, 2)
     for (int t = 0; t < GQ_NT; ++t)
 #pragma unroll
       for (int e = 0; e < 4; ++e) c[t][e] = 0.f;
+    if (!have && c0 + warp < c1) prefetch(tile, c0 + warp, buf);
+    have = false;
     for (int ch = c0 + warp; ch < c1; ch += GQ_WARPS) {
+      // start the copy of the chunk after this one: the next of this segment, or this warp's first of the next segment
+      bool next_issued = false;
+      if (ch + GQ_WARPS < c1) {
+        prefetch(tile, ch + GQ_WARPS, buf ^ 1);
+        next_issued = true;
+      } else {
+        const long long nit = item + (c1 - c0);
+        if (nit < item_end) {
+          const int ntile = (int)(nit / chunks);
+          const int nc0 = (int)(nit - (long long)ntile * chunks);
+          const int nc1 = (int)min((long long)chunks, nc0 + (item_end - nit));
+          if (nc0 + warp < nc1) {
+            prefetch(ntile, nc0 + warp, buf ^ 1);
+            next_issued = have = true;
+          }
+        }
+      }
       const int k_lane = ch * GQ_KCHUNK + j * 32;  // this lane's 32 consecutive k values
-      // weights first (the long-latency loads), then the activations: rows quad and quad+8, 32 values each
-      uint4 wq[GQ_NT];
       uint32_t sz[GQ_NT];  // (scale, zero) of this lane's group, two S values
       const int g = k_lane / group_size;
 #pragma unroll
       for (int t = 0; t < GQ_NT; ++t) {
         const int n = n_base + t * 8 + quad;
-        wq[t] = make_uint4(0, 0, 0, 0);
         sz[t] = 0;
         if (n < N) {
-          wq[t] = __ldcs(reinterpret_cast<const uint4*>(packed + (long long)n * (K / 4) + k_lane / 4));
           if (sz_transposed) {
             // scale holds (groups, N, 2): 8 consecutive columns of one group are one 32-byte segment
             sz[t] = reinterpret_cast<const uint32_t*>(scale)[(long long)g * N + n];
@@ -140,6 +178,12 @@ __global__ void __launch_bounds__(GQ_WARPS * 32, 2)
           }
         }
       }
+      if (next_issued) asm volatile("cp.async.wait_group 1;" ::: "memory");
+      else asm volatile("cp.async.wait_group 0;" ::: "memory");
+      uint4 wq[GQ_NT];
+#pragma unroll
+      for (int t = 0; t < GQ_NT; ++t) wq[t] = wbuf[(buf * GQ_NT + t) * 32 + lane];
+      buf ^= 1;
       T2 s2[GQ_NT], z2[GQ_NT];
 #pragma unroll
       for (int t = 0; t < GQ_NT; ++t) {
@@ -242,12 +286,19 @@ static void gq_small_launch(const void* x, const void* packed, const void* scale
                             int M, int N, int K, int group_size, long long ldx, long long ldy, int act_from_col,
                             float* ws, unsigned int* counters, int scale_dtype, int sz_transposed, int grid,
                             cudaStream_t s) {
+  constexpr int WBUF_BYTES = GQ_WARPS * 2 * GQ_NT * 32 * 16;  // per-warp double buffer of weight chunks
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(gq_gemm_small_m_kernel<T, __half>, cudaFuncAttributeMaxDynamicSharedMemorySize, WBUF_BYTES);
+    cudaFuncSetAttribute(gq_gemm_small_m_kernel<T, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, WBUF_BYTES);
+    configured = true;
+  }
   if (scale_dtype == XL_F16)
-    gq_gemm_small_m_kernel<T, __half><<<grid, GQ_WARPS * 32, 0, s>>>(
+    gq_gemm_small_m_kernel<T, __half><<<grid, GQ_WARPS * 32, WBUF_BYTES, s>>>(
         (const T*)x, (const uint16_t*)packed, (const __half*)scale, (const __half*)zero, (const T*)bias, (T*)y, M, N, K,
         group_size, ldx, ldy, act_from_col, ws, counters, sz_transposed);
   else
-    gq_gemm_small_m_kernel<T, __nv_bfloat16><<<grid, GQ_WARPS * 32, 0, s>>>(
+    gq_gemm_small_m_kernel<T, __nv_bfloat16><<<grid, GQ_WARPS * 32, WBUF_BYTES, s>>>(
         (const T*)x, (const uint16_t*)packed, (const __nv_bfloat16*)scale, (const __nv_bfloat16*)zero, (const T*)bias,
         (T*)y, M, N, K, group_size, ldx, ldy, act_from_col, ws, counters, sz_transposed);
 }

@@ -202,19 +202,25 @@ class DecoderGenerator:
                 y = _linear_gq(ops.concat([out, z], axis=1), L["w2"], use_bias=False)
                 return x + all_reduce(y) + L["w2"]["bias"]
 
+            def residual_norm(x, delta, delta_bias, lnw, lnb):
+                """`x += all_reduce(delta) + bias; LayerNorm(x)`: one kernel, the all-reduce over the TP group included."""
+                if delta is not None and cfg.tp > 1:
+                    return ops.all_reduce_add_layer_norm_(x, delta, delta_bias, lnw, lnb, tp_group, eps=cfg.eps)
+                return ops.add_layer_norm_(x, delta, delta_bias, lnw, lnb, eps=cfg.eps)
+
             def decode_block(x, delta, delta_bias, L, pos):
-                """One token per sequence, five kernels: residual + LayerNorm; [qkv | gelu(fc_in)] in one de-quantising
-                GEMM; rotary + cache append; attention, written next to the fc_in output; [out | fc_out] in one GEMM."""
-                h = ops.add_layer_norm_(x, delta, delta_bias, L["ln_w"], L["ln_b"], eps=cfg.eps)
+                """One token per sequence, five kernels: (all-reduce +) residual + LayerNorm; [qkv | gelu(fc_in)] in one
+                de-quantising GEMM; rotary + cache append; attention, written next to the fc_in output; [out | fc_out] in
+                one GEMM. Returns this rank's partial layer output; the next layer's first kernel reduces it."""
+                h = residual_norm(x, delta, delta_bias, L["ln_w"], L["ln_b"])
                 w1 = L["w1"]
                 buf = linear_gq_window_t(h, w1["weight_compressed"], w1["weight_scale_zero_t"], w1["bias"],
                                          act_from_col=3 * hd)
                 buf = ops.rotary_kv_append_(buf, sin_tab_i, cos_tab_i, L["k"], L["v"], pos, H, D, cfg.rotary_dim)
                 buf = ops.attention_decode_into_(buf, L["k"], L["v"], pos, H, D, out_col=2 * hd)
                 w2 = L["w2"]
-                y = linear_gq_window_t(buf, w2["weight_compressed"], w2["weight_scale_zero_t"], None, x_col=2 * hd,
-                                       k=hd + F)
-                return all_reduce(y)
+                return linear_gq_window_t(buf, w2["weight_compressed"], w2["weight_scale_zero_t"], None, x_col=2 * hd,
+                                          k=hd + F)
 
             # graphs take every variable as an input; collect them in a fixed order
             flat: Dict[str, xl.Tensor] = {"wte": self.wte, "ln_f_w": self.ln_f[0], "ln_f_b": self.ln_f[1],
@@ -274,7 +280,7 @@ class DecoderGenerator:
                 for L in layers:
                     delta = decode_block(x, delta, delta_bias, L, ins["pos"])
                     delta_bias = L["w2"]["bias"]
-                hn = ops.add_layer_norm_(x, delta, delta_bias, ins["ln_f_w"], ins["ln_f_b"], eps=cfg.eps)
+                hn = residual_norm(x, delta, delta_bias, ins["ln_f_w"], ins["ln_f_b"])
                 tok = select_token(hn, head, ins["off"])
                 ops.advance_position_(ins["pos"])
                 ops.var_updates.copy_var_update_(ins["cur"], tok)

@@ -80,6 +80,8 @@ _rot_append = _sig("xl_rotary_append", _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p
                    _c_int, _c_p)
 _attn_dec = _sig("xl_attn_decode", _c_p, _c_ll, _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
                  _c_f, _c_int, _c_int, _c_p)
+_ar_add_ln = _sig("xl_ar_add_layer_norm", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_f, _c_int, _c_p, _c_p, _c_ll,
+                  _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p)
 _add_ln = _sig("xl_add_layer_norm", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_f, _c_int, _c_p)
 _argmax = _sig("xl_argmax_rows", _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p)
 _advance = _sig("xl_advance_position", _c_p, _c_p)

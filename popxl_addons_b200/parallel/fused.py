@@ -89,39 +89,55 @@ def _lib():
 
 
 def matmul_all_reduce(ex, op, a_vals, w_vals):
-    nat = _lib()
-    a, w = a_vals[0], w_vals[0]
     ctx = runtime(ex).context(op.attrs["group"])
-    if ctx.world == 1:
-        return NotImplemented
-    if not _MC_ALL_REDUCE or not ctx.arena.mc_base or a.dtype not in (torch.bfloat16, torch.float16) or w.shape[-1] % 8:
-        return NotImplemented
-    M, N = a.shape[0], w.shape[-1]
-    out = ctx.arena.ring((M, N), a.dtype)
+    out = _gemms_all_reduce(ctx, [(a_vals[0], w_vals[0])])
+    return NotImplemented if out is None else [out]
+
+
+# From this group size on, an all-reduce is done as reduce-scatter epilogue + all-gather: pushing every tile to all ranks
+# (`multimem.red`) makes each GPU receive world x the output, the reduce-scatter form (world - 1) / world of it.
+_RS_AG_FROM_WORLD = int(os.environ.get("XL_RS_AG_FROM_WORLD", "4"))
+
+
+def _gemms_all_reduce(ctx: GroupContext, pairs):
+    """`all_reduce(sum of a @ w over pairs)` with the reduction fused into the GEMM epilogues; None if unsupported."""
+    nat = _lib()
+    a0, w0 = pairs[0]
+    M, N = a0.shape[0], w0.shape[-1]
+    if ctx.world == 1 or N % 8 or a0.dtype not in (torch.bfloat16, torch.float16):
+        return None
+    if any(a.dtype != a0.dtype or a.shape[0] != M or w.shape[-1] != N for a, w in pairs):
+        return None
+    if ctx.world >= _RS_AG_FROM_WORLD and M % ctx.world == 0:
+        # every tile is added into the shard of the rank that owns its rows, then the shards are gathered
+        shard = ctx.arena.ring((M // ctx.world, N), a0.dtype)
+        shard.zero_()
+        dst = _peer_ptr_tensor(ctx, shard)
+        for i, (a, w) in enumerate(pairs):
+            if nat.gemm(a, w, out=shard, accumulate=4, comm=ctx, rs_dst=dst) is NotImplemented:
+                if i:
+                    raise RuntimeError("a GEMM of a fused group was rejected after an earlier one ran")
+                return None
+        out = torch.empty((M, N), dtype=a0.dtype, device=a0.device)
+        torch.distributed.all_gather_into_tensor(out, shard, group=ctx.pg)
+        return out
+    if not _MC_ALL_REDUCE or not ctx.arena.mc_base:
+        return None
+    out = ctx.arena.ring((M, N), a0.dtype)
     out.zero_()
-    res = nat.gemm(a, w, out=out, accumulate=3, comm=ctx)
-    if res is NotImplemented:
-        return NotImplemented
-    return [out.clone()]
+    for i, (a, w) in enumerate(pairs):
+        if nat.gemm(a, w, out=out, accumulate=3, comm=ctx) is NotImplemented:
+            if i:
+                raise RuntimeError("a GEMM of a fused group was rejected after an earlier one ran")
+            return None
+    return out.clone()
 
 
 def matmul2_all_reduce(ex, op, a1_vals, w1_vals, a2_vals, w2_vals):
-    """`all_reduce(a1 @ w1 + a2 @ w2)`: both GEMMs push their tiles (`multimem.red`) into the same zeroed output."""
-    nat = _lib()
-    a1, w1, a2, w2 = a1_vals[0], w1_vals[0], a2_vals[0], w2_vals[0]
+    """`all_reduce(a1 @ w1 + a2 @ w2)`: both GEMMs reduce into the same zeroed output from their epilogues."""
     ctx = runtime(ex).context(op.attrs["group"])
-    if ctx.world == 1 or not _MC_ALL_REDUCE or not ctx.arena.mc_base or w1.shape[-1] % 8:
-        return NotImplemented
-    if a1.dtype not in (torch.bfloat16, torch.float16) or a2.dtype != a1.dtype:
-        return NotImplemented
-    M, N = a1.shape[0], w1.shape[-1]
-    out = ctx.arena.ring((M, N), a1.dtype)
-    out.zero_()
-    if nat.gemm(a1, w1, out=out, accumulate=3, comm=ctx) is NotImplemented:
-        return NotImplemented
-    if nat.gemm(a2, w2, out=out, accumulate=3, comm=ctx) is NotImplemented:
-        raise RuntimeError("second GEMM of a fused pair was rejected after the first one ran")
-    return [out.clone()]
+    out = _gemms_all_reduce(ctx, [(a1_vals[0], w1_vals[0]), (a2_vals[0], w2_vals[0])])
+    return NotImplemented if out is None else [out]
 
 
 def _peer_ptr_tensor(ctx: GroupContext, t: torch.Tensor) -> torch.Tensor:
@@ -300,7 +316,36 @@ def rts_adam(ex, op, w_vals, acc_vals, master_vals, m_vals, v_vals, step_vals):
     return True
 
 
-_TABLE = {"matmul_all_reduce": matmul_all_reduce, "matmul2_all_reduce": matmul2_all_reduce, "rts_adam": rts_adam}
+def ar_add_layer_norm(ex, op, x_vals, delta_vals, *rest):
+    """All-reduce of the partial layer output + residual update + LayerNorm in one kernel (token-by-token decoding)."""
+    nat = _lib()
+    a = op.attrs
+    ctx = runtime(ex).context(a["group"])
+    x, delta = x_vals[0], delta_vals[0]
+    rest = [r[0] for r in rest]
+    bias = rest.pop(0) if a["has_bias"] else None
+    w, b = rest
+    if ctx.world == 1 or not _MC_ALL_REDUCE or not ctx.arena.mc_base or x.dim() != 2:
+        return NotImplemented
+    if x.dtype not in (torch.bfloat16, torch.float16) or not nat._ok(x, delta, bias, w, b):
+        return NotImplemented
+    if any(t is not None and t.dtype != x.dtype for t in (delta, bias, w, b)) or delta.shape != x.shape:
+        return NotImplemented
+    h = torch.empty_like(x)
+    state = ctx.arena.local_sync[4:6]
+    rc = nat._ar_add_ln(x.data_ptr(), delta.data_ptr(), bias.data_ptr() if bias is not None else None, w.data_ptr(),
+                        b.data_ptr(), h.data_ptr(), x.shape[0], x.shape[1], float(a["eps"]), nat._CODE[x.dtype],
+                        ctx.stage16.data_ptr(), ctx.arena.multicast_ptr(ctx.stage16), _SMALL_ALL_REDUCE_16BIT_BYTES,
+                        state.data_ptr(), ctx.arena.pads_dev.data_ptr(), ctx.rank, ctx.world, 16, ctx.err.data_ptr(),
+                        nat._stream())
+    if rc == -1:
+        return NotImplemented
+    nat._check(rc, "ar_add_layer_norm")
+    nat._count("ar_add_layer_norm")
+    return [h]
+
+
+_TABLE = {"matmul_all_reduce": matmul_all_reduce, "ar_add_layer_norm": ar_add_layer_norm, "matmul2_all_reduce": matmul2_all_reduce, "rts_adam": rts_adam}
 
 
 def lookup(name: str, session):

@@ -1345,4 +1345,5 @@ def cross_entropy_with_grad(logits: Tensor, labels: Tensor, loss_grad=1.0, reduc
                          {"ignore_index": ignore_index, "reduction": reduction})
     return loss, dlogits
 from .decode import (rotary_kv_append_, attention_decode_packed, argmax_rows, advance_position_, store_row_,  # noqa: E402
-                     kv_cache_fill_, timestamp, attention_decode_into_, add_layer_norm_)
+                     kv_cache_fill_, timestamp, attention_decode_into_, add_layer_norm_,
+                     all_reduce_add_layer_norm_)

@@ -10,7 +10,7 @@ from typing import Optional, Tuple
 import torch
 
 from ..core import Tensor
-from ..opdef import OpDef, emit, emit1
+from ..opdef import OPS, OpDef, emit, emit1
 from .fused import _rotary_ref
 
 
@@ -151,6 +151,42 @@ def add_layer_norm_(x: Tensor, delta: Optional[Tensor], bias: Optional[Tensor], 
     returns `layer_norm(x) * weight + ln_bias`."""
     ins = [x] + ([delta] if delta is not None else []) + ([bias] if bias is not None else []) + [weight, ln_bias]
     return emit1("add_layer_norm_", ins, dict(has_delta=delta is not None, has_bias=bias is not None, eps=float(eps)))
+
+
+def _special_ar_add_layer_norm(ex, op, env):
+    a = op.attrs
+    vals = [env[t] for t in op.inputs]
+    native = ex.native_collective("ar_add_layer_norm")
+    if native is not None:
+        res = native(ex, op, *vals)
+        if res is not NotImplemented:
+            env[op.outputs[0]] = res
+            return
+    # composition: all-reduce of the partial update, then the residual + LayerNorm op
+    vals[1] = ex.comm.all_reduce(vals[1], a["group"], "add")
+    od = OPS["add_layer_norm_"]
+    fn = od.native.get(ex.device.type) if ex.use_native else None
+    kw = dict(has_delta=True, has_bias=a["has_bias"], eps=a["eps"])
+    outs = []
+    for r in range(ex.num_local):
+        args = [v[r] for v in vals]
+        res = fn(*args, **kw) if fn is not None else NotImplemented
+        if res is NotImplemented:
+            res = od.impl(*args, **kw)
+        outs.append(res)
+    env[op.outputs[0]] = outs
+
+
+OpDef("all_reduce_add_layer_norm_", special=_special_ar_add_layer_norm, collective=True,
+      infer=lambda op: [(op.inputs[0].shape, op.inputs[0].dtype, ())])
+
+
+def all_reduce_add_layer_norm_(x: Tensor, delta_partial: Tensor, bias: Optional[Tensor], weight: Tensor, ln_bias: Tensor,
+                               group, eps: float = 1e-5) -> Tensor:
+    """`add_layer_norm_(x, all_reduce(delta_partial, group), bias, ...)` as one op: on one process per GPU the sum over
+    the group, the residual update and the LayerNorm run in a single kernel."""
+    ins = [x, delta_partial] + ([bias] if bias is not None else []) + [weight, ln_bias]
+    return emit1("all_reduce_add_layer_norm_", ins, dict(group=group, has_bias=bias is not None, eps=float(eps)))
 
 
 def argmax_rows(logits: Tensor, valid: Optional[int] = None, index_offset: int = 0) -> Tuple[Tensor, Tensor]:

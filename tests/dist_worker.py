@@ -104,6 +104,7 @@ def main():
         with ir.main_graph:
             pass
         s = popxl.Session(ir, "cuda")
+        fused.runtime(s).reserve(ir.replica_grouping(), 640 << 20)  # operands of the micro-benchmarks below
         ctx = fused.runtime(s).context(ir.replica_grouping())
         dev = s.device
         M, N, K = args.m, args.n, args.k
@@ -212,6 +213,72 @@ def main():
         result["ag_b_err"] = float((y.float() - want).abs().max() / want.abs().max())
         result["ag_b_gathered_ok"] = bool(torch.equal(w_full, wg))
         result["ag_b_ms"] = timed(lambda: fused.all_gather_gemm(ctx, a, w_full, sharded="b", n_copy=args.n_copy))
+        # --- decode step: all-reduce + residual + LayerNorm in one kernel vs NCCL + the local kernel -----------------------------
+        from types import SimpleNamespace
+
+        xr = torch.randn(16, 4096, device=dev).bfloat16()
+        dl = (torch.randn(16, 4096, device=dev) * 0.5).bfloat16()
+        bs = torch.randn(4096, device=dev).bfloat16()
+        lw, lb = torch.randn(4096, device=dev).bfloat16(), torch.randn(4096, device=dev).bfloat16()
+        dist.broadcast(xr, 0)  # the residual stream is identical on the ranks of a TP group
+        for t_ in (bs, lw, lb):
+            dist.broadcast(t_, 0)
+        fake_op = SimpleNamespace(attrs=dict(group=ir.replica_grouping(), has_bias=True, eps=1e-5))
+        for trial in range(3):  # several calls: the staging halves alternate
+            x1, x2 = xr.clone(), xr.clone()
+            (h1,) = fused.ar_add_layer_norm(s, fake_op, [x1], [dl], [bs], [lw], [lb])
+            dsum = dl.float().clone()
+            dist.all_reduce(dsum)
+            h2 = native.add_layer_norm_cuda(x2, dsum.bfloat16(), bs, lw, lb, has_delta=True, has_bias=True, eps=1e-5)
+            torch.cuda.synchronize()
+            result["ar_ln_err"] = max(result.get("ar_ln_err", 0.0), float((h1.float() - h2.float()).abs().max()),
+                                      float((x1.float() - x2.float()).abs().max()))
+        x1 = xr.clone()
+        result["ar_ln_fused_ms"] = timed(lambda: fused.ar_add_layer_norm(s, fake_op, [x1], [dl], [bs], [lw], [lb]))
+
+        def nccl_ar_ln():
+            d = dl.clone()
+            dist.all_reduce(d)
+            return native.add_layer_norm_cuda(x1, d, bs, lw, lb, has_delta=True, has_bias=True, eps=1e-5)
+
+        result["ar_ln_nccl_ms"] = timed(nccl_ar_ln)
+        # --- fused reduce-scatter + AdamW + all-gather over peer pointers (one kernel) vs NCCL + the local Adam kernel --------
+        import ctypes
+
+        n_par = 1 << 26  # 64 Mi parameters
+        shard = n_par // world
+        wt = ctx.arena.alloc((n_par,), torch.bfloat16)
+        acc = ctx.arena.alloc((n_par,), torch.float32)
+        wt.normal_(0, 0.02)
+        acc.normal_(0, 1e-3)
+        master = wt[rank * shard:(rank + 1) * shard].float()
+        m1, v1 = torch.zeros_like(master), torch.zeros_like(master)
+        step_t = torch.zeros((), device=dev)
+        grads = (ctypes.c_void_p * world)(*ctx.arena.peer_ptrs(acc))
+        weights = (ctypes.c_void_p * world)(*ctx.arena.peer_ptrs(wt))
+        torch.cuda.synchronize()
+        dist.barrier()
+
+        def fused_adam():
+            fused.group_barrier(ctx, 4)
+            native._check(native._rts_adam(grads, weights, native._CODE[wt.dtype], master.data_ptr(), m1.data_ptr(),
+                                           native._CODE[m1.dtype], v1.data_ptr(), step_t.data_ptr(), rank * shard, shard,
+                                           world, 1e-4, 0.9, 0.95, 1e-5, 0.01, 1.0, 1, native._stream()), "rts_adam")
+            fused.group_barrier(ctx, 5)
+
+        g_shard = torch.empty(shard, device=dev)
+        w_full = torch.empty(n_par, device=dev, dtype=torch.bfloat16)
+
+        def nccl_adam():
+            dist.reduce_scatter_tensor(g_shard, acc, op=dist.ReduceOp.AVG)
+            native.adam_cuda(w_full[rank * shard:(rank + 1) * shard], g_shard, m1, v1, step_t, master, has_step=True,
+                             has_master=True, bias_correction=True, lr=1e-4, beta1=0.9, beta2=0.95, epsilon=1e-5,
+                             weight_decay=0.01, grad_scale=1.0, _tensor_scalars=())
+            dist.all_gather_into_tensor(w_full, w_full[rank * shard:(rank + 1) * shard].clone())
+
+        result["rts_adam_fused_ms"] = timed(fused_adam, iters=5)
+        result["rts_adam_nccl_ms"] = timed(nccl_adam, iters=5)
+        result["rts_adam_params"] = n_par
         try:
             ctx.check()
             native.check_gemm_errors()

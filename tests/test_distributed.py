@@ -99,6 +99,7 @@ def test_gpu_gemm_reduce_scatter_and_all_gather_gemm():
     assert res["errors"] is None
     assert res["rs_err"] < 2e-2 and res["ag_a_err"] < 2e-2 and res["ag_b_err"] < 2e-2 and res["ar_err"] < 2e-2
     assert res["ag_a_gathered_ok"] and res["ag_b_gathered_ok"]
+    assert res["ar_ln_err"] < 0.1  # bf16 rounding of the summed update (magnitudes ~ 4)
 
 
 @pytest.mark.parametrize("nproc", [2, 4])
