@@ -88,6 +88,7 @@ _advance = _sig("xl_advance_position", _c_p, _c_p)
 _store_row = _sig("xl_store_row", _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_p)
 _symm_all_reduce_mc = _sig("xl_symm_all_reduce_mc", _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int,
                            _c_int, _c_p, _c_p)
+_set_spin = _sig("xl_set_comm_spin_limit", ctypes.c_uint)
 _symm_barrier = _sig("xl_symm_barrier", _c_p, _c_int, _c_int, _c_int, _c_p, _c_p)
 _symm_all_reduce = _sig("xl_symm_all_reduce", _c_p, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p,
                         _c_p)
@@ -771,6 +772,11 @@ def ce_with_grad_cuda(logits, labels, loss_grad, ignore_index, reduction):
 
 
 # ---- decoding path -------------------------------------------------------------------------------------------------------
+def set_comm_spin_limit(polls: int) -> None:
+    """Poll budget of every bounded wait on a peer in kernels launched from now on (0 restores the default)."""
+    _set_spin(int(polls))
+
+
 def _row_window_ok(t) -> bool:
     """2-D, CUDA, unit column stride, 16-byte aligned rows (a column window of a wider row-major matrix is fine)."""
     return (t.is_cuda and t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0

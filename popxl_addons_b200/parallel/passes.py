@@ -87,6 +87,67 @@ OpDef("matmul2_all_reduce", special=_special_matmul2_all_reduce, vjp=_vjp_matmul
       flops=lambda op: 2 * (op.inputs[0].shape[-1] + op.inputs[2].shape[-1]) * op.outputs[0].nelms)
 
 
+def _matmul_add_ref(c, a, w):
+    if c.device.type == "meta":
+        return torch.empty_like(c)
+    return c + torch.matmul(a, w).to(c.dtype)
+
+
+def _matmul_add_cuda(c, a, w):
+    from ..ops import native
+
+    if c.dim() != 2 or a.dim() != 2 or w.dim() != 2 or not c.is_contiguous():
+        return NotImplemented
+    res = native.gemm(a, w, out=c, accumulate=1)  # c += a @ w in the GEMM epilogue (c is dead after this op)
+    return res
+
+
+def _vjp_matmul_add(ctx, op, gs):
+    from ..xl.ops import matmul, transpose
+
+    (g,) = gs
+    c, a, w = op.inputs
+    return [g, matmul(g, transpose(ctx.fwd(w))), matmul(transpose(ctx.fwd(a)), g)]
+
+
+OpDef("matmul_add", impl=_matmul_add_ref, vjp=_vjp_matmul_add,
+      flops=lambda op: 2 * op.inputs[1].shape[-1] * op.outputs[0].nelms)
+OPS["matmul_add"].native["cuda"] = _matmul_add_cuda
+
+
+def fuse_matmul_sums(ir: xl.Ir) -> int:
+    """`matmul(a1, w1) + matmul(a2, w2)` (both products used by nothing else) -> the second GEMM accumulates into the
+    first one's result in its epilogue: one elementwise pass less. Returns the number of rewrites."""
+    n = 0
+    for g in ir.graphs:
+        consumers = {}
+        for op in g.ops:
+            for t in op.inputs:
+                consumers.setdefault(t, []).append(op)
+        drop = set()
+        for add in g.ops:
+            if add.opdef.name != "add" or len(add.inputs) != 2:
+                continue
+            m1, m2 = add.inputs[0].producer, add.inputs[1].producer
+            if any(m is None or m.opdef.name != "matmul" or m.graph is not g or m.uid in drop
+                   or len(consumers.get(m.outputs[0], [])) != 1 or m.outputs[0] in g._outputs
+                   or m.inputs[0].rank != 2 or m.inputs[1].rank != 2 for m in (m1, m2)):
+                continue
+            if m1 is m2 or m1.outputs[0].shape != m2.outputs[0].shape or m1.outputs[0].dtype != m2.outputs[0].dtype:
+                continue
+            # the add becomes `matmul_add(first product, a2, w2)`; the second matmul disappears. Operands of the second
+            # product exist before the add, so the op order stays valid.
+            add.opdef = OPS["matmul_add"]
+            add.name = "matmul_add"
+            add.inputs = [m1.outputs[0], m2.inputs[0], m2.inputs[1]]
+            add.attrs = {}
+            drop.add(m2.uid)
+            n += 1
+        if drop:
+            g.ops = [o for o in g.ops if o.uid not in drop]
+    return n
+
+
 def _fuse_pairs(g) -> int:
     """`all_reduce(matmul(a1, w1) + matmul(a2, w2))` -> one op: both GEMMs push their tiles into the same output."""
     consumers = {}

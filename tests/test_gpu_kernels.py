@@ -270,3 +270,42 @@ def test_attention_forward_backward(nat):
     for got, ref in ((dq, rdq), (dk, rdk), (dv, rdv)):
         torch.testing.assert_close(got.float(), ref, rtol=5e-2, atol=5e-2)
     nat.check_gemm_errors()
+
+
+def test_bounded_wait_on_a_peer_gives_up_and_reports(nat):
+    """Failure detection on the device without a fault: a barrier whose peer never signals (a flag nothing sets) must
+    run out of its poll budget, record the reason in the status word and return; the context stays usable."""
+    pad_a = torch.zeros(256, dtype=torch.int32, device="cuda")  # this rank's signal pad
+    pad_b = torch.zeros(256, dtype=torch.int32, device="cuda")  # stands for the silent peer's pad
+    pads = torch.tensor([pad_a.data_ptr(), pad_b.data_ptr()], dtype=torch.int64, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    nat.set_comm_spin_limit(1 << 12)
+    try:
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        nat._check(nat._symm_barrier(pads.data_ptr(), 0, 2, 4, err.data_ptr(), nat._stream()), "symm_barrier")
+        end.record()
+        torch.cuda.synchronize()
+    finally:
+        nat.set_comm_spin_limit(0)
+    assert int(err.item()) == 102  # "a peer's signal never arrived"
+    assert start.elapsed_time(end) < 1000.0
+    # the signal this rank sent did arrive at the (silent) peer's pad: slot (channel 4, sender 0)
+    assert int(pad_b[4 * 2 + 0].item()) == 1
+    # and the context is intact: ordinary work still runs
+    x = torch.randn(1024, 512, device="cuda").bfloat16()
+    torch.testing.assert_close(nat.gelu_cuda(x, approximate="none").float(), torch.nn.functional.gelu(x.float()),
+                               rtol=2e-2, atol=2e-2)
+
+
+def test_matmul_add_accumulates_in_the_epilogue(nat):
+    from popxl_addons_b200.parallel.passes import _matmul_add_cuda
+
+    torch.manual_seed(7)
+    a1, w1 = (torch.randn(512, 384, device="cuda") * 0.1).bfloat16(), (torch.randn(384, 640, device="cuda") * 0.1).bfloat16()
+    a2, w2 = (torch.randn(512, 256, device="cuda") * 0.1).bfloat16(), (torch.randn(256, 640, device="cuda") * 0.1).bfloat16()
+    c = nat.gemm(a1, w1)
+    want = c.float() + a2.float() @ w2.float()
+    got = _matmul_add_cuda(c, a2, w2)
+    assert got is not NotImplemented and got.data_ptr() == c.data_ptr()
+    torch.testing.assert_close(got.float(), want, rtol=2e-2, atol=2e-2)
