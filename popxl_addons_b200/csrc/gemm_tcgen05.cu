@@ -72,6 +72,10 @@ struct GemmParams {
   //   3: the (transposed) left operand is zero before the diagonal (dV = P^T dO, dK = dS^T Q): contraction starts at
   //      the tile's first row
   int causal;
+  // 8-bit float operands (tcgen05 kind::f8f6f4; both operands K-major): -1 = 16-bit operands, else the format of A / B
+  // (0 = e4m3, 1 = e5m2). A k-block is then 128 elements, still one 128-byte swizzle row.
+  int fp8_a, fp8_b;
+  const float* alpha_log2;  // optional device scalar: the result is also multiplied by 2^(*alpha_log2)
 };
 
 // k-block range of a tile under the causal modes; false: the tile is skipped altogether
@@ -165,6 +169,15 @@ __device__ __forceinline__ void tcgen05_mma_f16(uint32_t tmem_d, uint64_t desc_a
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
@@ -263,7 +276,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   const int tiles_m = (p.M + BLOCK_M - 1) / BLOCK_M;
   const int tiles_n = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int num_tiles = tiles_m * tiles_n * p.batch;
-  const int k_blocks = (p.K + BLOCK_K - 1) / BLOCK_K;
+  const bool fp8 = p.fp8_a >= 0;
+  const int k_elems = fp8 ? 2 * BLOCK_K : BLOCK_K;  // elements per k-block: always 128 bytes
+  const int k_blocks = (p.K + k_elems - 1) / k_elems;
 
   if (threadIdx.x == 0) {
     if (is_copy) {
@@ -431,7 +446,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           uint8_t* sa = smem + stage * L::STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
           mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
-          const int k0 = kb * BLOCK_K;
+          const int k0 = kb * k_elems;
           if (!p.a_mn) {
             tma_load_3d(sa, &map_a, &full_bar[stage], k0, m0, b);  // box {64 k, 128 m}
           } else {
@@ -456,7 +471,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     // ------------------------------------------------ MMA issuer --------------------------------------------------
     if (elect_one()) {
       const uint32_t fmt = p.is_fp16 ? 0u : 1u;
-      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(p.a_mn != 0) << 15) |
+      const uint32_t fmt_a = fp8 ? (uint32_t)p.fp8_a : fmt, fmt_b = fp8 ? (uint32_t)p.fp8_b : fmt;
+      const uint32_t idesc = (1u << 4) | (fmt_a << 7) | (fmt_b << 10) | ((uint32_t)(p.a_mn != 0) << 15) |
                              ((uint32_t)(p.b_mn != 0) << 16) | ((uint32_t)(BLOCK_N >> 3) << 17) |
                              ((uint32_t)(BLOCK_M >> 4) << 24);
       const uint32_t a_lbo = p.a_mn ? BLOCK_K * 128 : 16;
@@ -487,7 +503,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
             const uint64_t da = make_smem_desc(sa + k * a_kstep, a_lbo);
             const uint64_t db = make_smem_desc(sb + k * b_kstep, b_lbo);
-            tcgen05_mma_f16(tmem_d, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+            if (fp8) tcgen05_mma_f8(tmem_d, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+            else tcgen05_mma_f16(tmem_d, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           tcgen05_commit(&empty_bar[stage]);  // frees the stage once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -505,6 +522,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     float mean_a = 0.f, mean_b = 1.f;
+    const float alpha_eff = p.alpha_log2 ? p.alpha * exp2f(*p.alpha_log2) : p.alpha;
     if (p.accumulate == 2) {
       const float t = *p.step;
       mean_a = t / (t + 1.f);
@@ -567,7 +585,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
               uint16_t* oe = (uint16_t*)&o;
 #pragma unroll
               for (int e = 0; e < 8; ++e) {
-                float val = __uint_as_float(r[jj * 8 + e]) * p.alpha;
+                float val = __uint_as_float(r[jj * 8 + e]) * alpha_eff;
                 if (p.bias && col0 + jj * 8 + e < p.N) {
                   const int bc = col0 + jj * 8 + e;
                   val += p.bias_dtype == XL_F32 ? ((const float*)p.bias)[bc]
@@ -619,7 +637,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (!row_ok || col0 >= p.N) continue;
         float v[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha_eff;
         if (p.bias) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -747,10 +765,13 @@ int make_map(CUtensorMap* map, const void* ptr, int is_fp16, long long rows, lon
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return -2;
   cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch};
-  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(batch > 1 ? batch_stride : rows * ld) * 2};
+  const cuuint64_t esz = is_fp16 == 2 ? 1 : 2;  // is_fp16: 0 bf16, 1 fp16, 2 one-byte elements (fp8)
+  cuuint64_t strides[2] = {(cuuint64_t)ld * esz, (cuuint64_t)(batch > 1 ? batch_stride : rows * ld) * esz};
   cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, is_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void*)ptr, dims,
+  const CUtensorMapDataType dt = is_fp16 == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : is_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUresult r = fn(map, dt, 3, (void*)ptr, dims,
                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -3;
@@ -833,6 +854,8 @@ XL_API int xl_gemm_tcgen05_fused(const void* a, const void* b, void* c, int M, i
   p.gather_mode = gather_mode; p.n_copy = n_copy; p.gather_bps = gather_bps;
   p.gather_src = (const uint8_t* const*)gather_src; p.gather_dst = (uint8_t*)gather_dst; p.gather_flags = gather_flags;
   p.gather_block_bytes = 0;
+  p.fp8_a = p.fp8_b = -1;
+  p.alpha_log2 = nullptr;
   p.causal = causal;
   if (causal < 0 || causal > 3 || (causal && (gather_mode || accumulate >= 3))) return -1;
   if (causal && (M != N && causal == 1)) return -1;
@@ -857,6 +880,37 @@ XL_API int xl_gemm_tcgen05_fused(const void* a, const void* b, void* c, int M, i
       p.gather_block_bytes = (long long)BLOCK_K * N * 2;
     }
   }
+  if (block_n == 128) return launch<128>(ma, mb, p, sm_count, s);
+  return launch<256>(ma, mb, p, sm_count, s);
+}
+
+// C = 2^(*alpha_log2) * alpha * (A * B^T) for 8-bit float operands (tcgen05 kind::f8f6f4), fp32 accumulation.
+//   a: (M x K) row-major, b: (N x K) row-major (both K-major), one byte per element, formats fmt_a / fmt_b
+//   (0 = e4m3, 1 = e5m2); lda, ldb multiples of 16; c: (M x N) fp32 / fp16 / bf16; alpha_log2 may be null.
+XL_API int xl_gemm_tcgen05_fp8(const void* a, const void* b, void* c, int M, int N, int K, long long lda, long long ldb,
+                               long long ldc, int fmt_a, int fmt_b, int c_dtype, const void* bias, int bias_dtype,
+                               float alpha, const float* alpha_log2, int* err, int sm_count, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0 || fmt_a < 0 || fmt_a > 1 || fmt_b < 0 || fmt_b > 1) return -1;
+  if ((((uintptr_t)a) & 15) || (((uintptr_t)b) & 15) || (lda % 16) || (ldb % 16)) return -1;
+  const int block_n = (N <= 128) ? 128 : 256;
+  CUtensorMap ma, mb;
+  int r = make_map(&ma, a, 2, M, K, lda, 1, 0, 2 * BLOCK_K, BLOCK_M);
+  if (r) return r;
+  r = make_map(&mb, b, 2, N, K, ldb, 1, 0, 2 * BLOCK_K, block_n);
+  if (r) return r;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = 1;
+  p.a_mn = 0; p.b_mn = 0;
+  p.C = c; p.ldc = ldc; p.batch_stride_c = 0; p.c_dtype = c_dtype;
+  p.bias = bias; p.bias_dtype = bias_dtype; p.act = 0; p.accumulate = 0; p.step = nullptr;
+  p.alpha = alpha; p.is_fp16 = 0; p.err = err;
+  p.pads = nullptr; p.comm_rank = 0; p.comm_world = 1; p.local_sync = nullptr; p.comm_spin_limit = 0;
+  p.rs_dst = nullptr; p.rs_rows = 0;
+  p.gather_mode = 0; p.n_copy = 0; p.gather_bps = 0; p.gather_src = nullptr; p.gather_dst = nullptr;
+  p.gather_flags = nullptr; p.gather_block_bytes = 0;
+  p.causal = 0;
+  p.fp8_a = fmt_a; p.fp8_b = fmt_b; p.alpha_log2 = alpha_log2;
+  if (sm_count <= 0) sm_count = 148;
   if (block_n == 128) return launch<128>(ma, mb, p, sm_count, s);
   return launch<256>(ma, mb, p, sm_count, s);
 }

@@ -88,6 +88,19 @@ _advance = _sig("xl_advance_position", _c_p, _c_p)
 _store_row = _sig("xl_store_row", _c_p, _c_p, _c_int, _c_p, _c_int, _c_int, _c_p)
 _symm_all_reduce_mc = _sig("xl_symm_all_reduce_mc", _c_p, _c_p, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int,
                            _c_int, _c_p, _c_p)
+_gemm_fp8 = _sig("xl_gemm_tcgen05_fp8", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_int,
+                 _c_p, _c_int, _c_f, _c_p, _c_p, _c_int, _c_p)
+_to_fp8 = _sig("xl_pow2_cast_to_fp8", _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_p)
+_from_fp8 = _sig("xl_pow2_cast_from_fp8", _c_p, _c_p, _c_int, _c_p, _c_int, _c_ll, _c_int, _c_p)
+_mse_scale = _sig("xl_fp8_mse_scale", _c_p, _c_int, _c_ll, _c_p, _c_int, _c_int, ctypes.c_double, _c_p, _c_p)
+_csr_mm = _sig("xl_dense_csr_matmul", _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p)
+_gather_rows = _sig("xl_gather_rows", _c_p, _c_int, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p)
+_scatter_rows = _sig("xl_scatter_add_rows", _c_p, _c_int, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p)
+_row_sum_sumsq = _sig("xl_row_sum_sumsq", _c_p, _c_int, _c_p, _c_int, _c_int, _c_p)
+_ln_apply_stats = _sig("xl_ln_apply_stats", _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_f, _c_f, _c_p)
+_row_max = _sig("xl_row_max", _c_p, _c_int, _c_p, _c_int, _c_int, _c_p)
+_ce_shard_sumexp = _sig("xl_ce_shard_sumexp", _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p)
+_ce_shard_grad = _sig("xl_ce_shard_grad", _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p)
 _set_spin = _sig("xl_set_comm_spin_limit", ctypes.c_uint)
 _symm_barrier = _sig("xl_symm_barrier", _c_p, _c_int, _c_int, _c_int, _c_p, _c_p)
 _symm_all_reduce = _sig("xl_symm_all_reduce", _c_p, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p,
@@ -942,12 +955,209 @@ def gq_gemm_small_m(x, packed, scale, zero, bias, out=None, act_from_col=None, c
     return y
 
 
+# ---- FP8 ---------------------------------------------------------------------------------------------------------------------
+_FP8_TORCH = {"float8_143": torch.float8_e4m3fn, "float8_152": torch.float8_e5m2}
+_FP8_E5M2 = {torch.float8_e4m3fn: 0, torch.float8_e5m2: 1}
+
+
+def _log2_arg(log2_scale):
+    """(pointer, is_int) of a device scalar holding a power-of-two exponent."""
+    if log2_scale.dtype == torch.int32:
+        return log2_scale, 1
+    if log2_scale.dtype == torch.float32:
+        return log2_scale, 0
+    return log2_scale.float(), 0
+
+
+@native("pow2scale_cast_to_fp8")
+def pow2scale_cast_to_fp8_cuda(x, log2_scale, dt):
+    if not _ok(x) or not log2_scale.is_cuda or log2_scale.numel() != 1 or dt.name not in _FP8_TORCH:
+        return NotImplemented
+    tdt = _FP8_TORCH[dt.name]
+    y = torch.empty(x.shape, dtype=tdt, device=x.device)
+    ls, is_int = _log2_arg(log2_scale)
+    _check(_to_fp8(x.data_ptr(), _CODE[x.dtype], ls.data_ptr(), is_int, y.data_ptr(), x.numel(), _FP8_E5M2[tdt], _stream()),
+           "pow2_cast_to_fp8")
+    _count("pow2_cast_to_fp8")
+    return y
+
+
+@native("pow2scale_cast_from_fp8")
+def pow2scale_cast_from_fp8_cuda(x, log2_scale, dt):
+    if x.dtype not in _FP8_E5M2 or not (x.is_cuda and x.is_contiguous()) or log2_scale.numel() != 1:
+        return NotImplemented
+    out_dt = dt.as_torch()
+    if out_dt not in _CODE:
+        return NotImplemented
+    y = torch.empty(x.shape, dtype=out_dt, device=x.device)
+    ls, is_int = _log2_arg(log2_scale)
+    _check(_from_fp8(x.data_ptr(), ls.data_ptr(), is_int, y.data_ptr(), _CODE[out_dt], x.numel(), _FP8_E5M2[x.dtype],
+                     _stream()), "pow2_cast_from_fp8")
+    _count("pow2_cast_from_fp8")
+    return y
+
+
+def gemm_fp8(a, b_t, out_dtype=torch.bfloat16, alpha: float = 1.0, log2_scale=None, bias=None):
+    """`2^log2_scale * alpha * a @ b_t^T` on the tcgen05 8-bit float path: `a (M, K)`, `b_t (N, K)`, both row-major fp8
+    (e4m3 / e5m2, may differ), fp32 accumulation. `log2_scale`: optional device scalar."""
+    if a.dtype not in _FP8_E5M2 or b_t.dtype not in _FP8_E5M2 or a.dim() != 2 or b_t.dim() != 2:
+        return NotImplemented
+    if not (a.is_cuda and a.is_contiguous() and b_t.is_contiguous()) or a.shape[1] != b_t.shape[1]:
+        return NotImplemented
+    M, K = a.shape
+    N = b_t.shape[0]
+    if K % 16 or a.data_ptr() % 16 or b_t.data_ptr() % 16 or out_dtype not in _CODE:
+        return NotImplemented
+    out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    if (N * out.element_size()) % 16:
+        return NotImplemented
+    ls = None
+    if log2_scale is not None:
+        ls = log2_scale.float().reshape(1) if log2_scale.dtype != torch.float32 else log2_scale.reshape(1)
+    err = gemm_error_flag(a.device)
+    rc = _gemm_fp8(a.data_ptr(), b_t.data_ptr(), out.data_ptr(), M, N, K, K, K, N, _FP8_E5M2[a.dtype], _FP8_E5M2[b_t.dtype],
+                   _CODE[out_dtype], bias.data_ptr() if bias is not None else None,
+                   _CODE[bias.dtype] if bias is not None else 0, float(alpha), ls.data_ptr() if ls is not None else None,
+                   err.data_ptr(), _sms(a.device), _stream())
+    if rc < 0:
+        return NotImplemented
+    _check(rc, "gemm_tcgen05_fp8")
+    _count("gemm_tcgen05_fp8")
+    return out
+
+
+@native("matmul_pow2scaled")
+def matmul_pow2scaled_cuda(a, b, log2_scale, out_dt):
+    if a.dtype not in _FP8_E5M2 or b.dtype not in _FP8_E5M2 or b.dim() != 2 or log2_scale.numel() != 1:
+        return NotImplemented
+    out_dtype = out_dt.as_torch()
+    a2 = a.reshape(-1, a.shape[-1])
+    if not a2.is_contiguous():
+        a2 = a2.contiguous()
+    # the kernel takes both operands with the contraction index contiguous: B as (N, K)
+    b_t = b.t().contiguous() if b.stride(-1) == 1 else b.t()
+    res = gemm_fp8(a2, b_t, out_dtype=out_dtype, log2_scale=log2_scale)
+    if res is NotImplemented:
+        return res
+    return res.view(*a.shape[:-1], b.shape[-1])
+
+
+_MSE_SCRATCH: Dict[int, torch.Tensor] = {}
+
+
+def fp8_mse_scale_cuda(x, fmt_name, src_mantissa_bits):
+    from .fp8_mse_scale import _format_window
+    from .fp8_utils import FP8_FORMATS
+
+    if not _ok(x):
+        return NotImplemented
+    fmt = FP8_FORMATS[fmt_name]
+    lo, span = _format_window(fmt)
+    qerr = 2.0 ** (-2.0 * (src_mantissa_bits - fmt["mantissa_bits"]))
+    idx = x.device.index or 0
+    scratch = _MSE_SCRATCH.get(idx)
+    if scratch is None:
+        scratch = _MSE_SCRATCH[idx] = torch.zeros(256, dtype=torch.int32, device=x.device)
+    out = torch.empty((), dtype=torch.int32, device=x.device)
+    _check(_mse_scale(x.data_ptr(), _CODE[x.dtype], x.numel(), scratch.data_ptr(), int(lo), int(span), float(qerr),
+                      out.data_ptr(), _stream()), "fp8_mse_scale")
+    _count("fp8_mse_scale")
+    return out
+
+
+def dense_csr_matmul_cuda(lhs, indptr, indices, values, n_rows, n_cols):
+    if not _ok(lhs) or not (indptr.is_cuda and indices.is_cuda and values.is_cuda) or values.dtype != torch.float32:
+        return NotImplemented
+    if indptr.dtype != torch.int32 or indices.dtype != torch.int32 or n_cols * 4 > 48 * 1024:
+        return NotImplemented
+    x2 = lhs.reshape(-1, lhs.shape[-1])
+    y = torch.empty((x2.shape[0], n_cols), dtype=lhs.dtype, device=lhs.device)
+    rc = _csr_mm(x2.data_ptr(), _CODE[lhs.dtype], indptr.data_ptr(), indices.data_ptr(), values.data_ptr(), y.data_ptr(),
+                 x2.shape[0], n_rows, n_cols, int(values.numel()), _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "dense_csr_matmul")
+    _count("dense_csr_matmul")
+    return y.view(*lhs.shape[:-1], n_cols)
+
+
+@native("gather")
+def gather_cuda(w, idx, axis, zero_OOR):
+    if axis != 0 or w.dim() != 2 or not _ok(w) or idx.dtype != torch.int32 or not idx.is_contiguous():
+        return NotImplemented
+    out = torch.empty((*idx.shape, w.shape[1]), dtype=w.dtype, device=w.device)
+    _check(_gather_rows(w.data_ptr(), _CODE[w.dtype], idx.data_ptr(), out.data_ptr(), idx.numel(), w.shape[0], w.shape[1],
+                        _stream()), "gather_rows")
+    _count("gather_rows")
+    return out
+
+
+@native("gather_grad")
+def gather_grad_cuda(g, idx, axis, zero_OOR, w_shape):
+    if axis != 0 or len(w_shape) != 2 or not _ok(g) or idx.dtype != torch.int32 or not idx.is_contiguous():
+        return NotImplemented
+    acc = torch.zeros(tuple(w_shape), dtype=torch.float32, device=g.device)
+    _check(_scatter_rows(g.data_ptr(), _CODE[g.dtype], idx.data_ptr(), acc.data_ptr(), idx.numel(), w_shape[0], w_shape[1],
+                         _stream()), "scatter_add_rows")
+    _count("scatter_add_rows")
+    return acc if g.dtype == torch.float32 else acc.to(g.dtype)
+
+
+def row_sum_sumsq(x):
+    """`(2, rows)` fp32: per-row sum and sum of squares of a 2-D tensor (local part of a hidden-sharded LayerNorm)."""
+    stats = torch.empty((2, x.shape[0]), dtype=torch.float32, device=x.device)
+    _check(_row_sum_sumsq(x.data_ptr(), _CODE[x.dtype], stats.data_ptr(), x.shape[0], x.shape[1], _stream()), "row_stats")
+    _count("row_sum_sumsq")
+    return stats
+
+
+def ln_apply_stats(x, stats, w, b, hidden, eps):
+    """LayerNorm of hidden-sharded rows given the all-reduced `(2, rows)` sums; returns `(y, mean, rstd)`."""
+    rows, cols = x.shape
+    y = torch.empty_like(x)
+    mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _check(_ln_apply_stats(x.data_ptr(), _CODE[x.dtype], stats.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(),
+                           mean.data_ptr(), rstd.data_ptr(), rows, cols, float(hidden), float(eps), _stream()), "ln_apply")
+    _count("ln_apply_stats")
+    return y, mean, rstd
+
+
+def ce_shard_row_max(x):
+    out = torch.empty(x.shape[0], dtype=torch.float32, device=x.device)
+    _check(_row_max(x.data_ptr(), _CODE[x.dtype], out.data_ptr(), x.shape[0], x.shape[1], _stream()), "row_max")
+    _count("row_max")
+    return out
+
+
+def ce_shard_sumexp(x, gmax, labels):
+    """`(2, rows)` fp32: sum of exp(x - gmax) over this vocabulary shard, and x[label] - gmax where the (shard-local)
+    label falls into the shard, else 0."""
+    out = torch.empty((2, x.shape[0]), dtype=torch.float32, device=x.device)
+    _check(_ce_shard_sumexp(x.data_ptr(), _CODE[x.dtype], gmax.data_ptr(), labels.data_ptr(), out.data_ptr(), x.shape[0],
+                            x.shape[1], _stream()), "ce_shard_sumexp")
+    _count("ce_shard_sumexp")
+    return out
+
+
+def ce_shard_grad(x, gmax, gsum, labels, row_scale):
+    dx = torch.empty_like(x)
+    _check(_ce_shard_grad(x.data_ptr(), _CODE[x.dtype], gmax.data_ptr(), gsum.data_ptr(), labels.data_ptr(),
+                          row_scale.data_ptr(), dx.data_ptr(), x.shape[0], x.shape[1], _stream()), "ce_shard_grad")
+    _count("ce_shard_grad")
+    return dx
+
+
 # ---- registration of ops defined outside xl.ops ------------------------------------------------------------------------
 def _register_late():
     from . import grad_reduce_square_add as _g, group_quantize_decompress as _q  # noqa: F401  (define the OpDefs)
 
     OPS["grad_reduce_square_add"].native["cuda"] = grad_sumsq_cuda
     OPS["group_quantize_decompress"].native["cuda"] = gq_decompress_cuda
+    from . import fp8_mse_scale as _m, static_sparse_ops as _s  # noqa: F401
+
+    OPS["fp8_mse_scale"].native["cuda"] = fp8_mse_scale_cuda
+    OPS["dense_csr_matmul"].native["cuda"] = dense_csr_matmul_cuda
 
     from ..layers import linear_gq as _lgq  # noqa: F401
 

@@ -316,6 +316,20 @@ def rts_adam(ex, op, w_vals, acc_vals, master_vals, m_vals, v_vals, step_vals):
     return True
 
 
+def layer_norm_distributed_fwd(ex, op, x_vals, w_vals, b_vals):
+    """Hidden-sharded LayerNorm: local (sum, sum of squares) per row in one kernel, one small all-reduce over the group,
+    normalisation with the group statistics in a second kernel."""
+    nat = _lib()
+    x, w, b = x_vals[0], w_vals[0], b_vals[0]
+    group = op.attrs["group"]
+    if x.dim() != 2 or not nat._ok(x, w, b) or w.dtype != x.dtype or b.dtype != x.dtype:
+        return NotImplemented
+    stats = nat.row_sum_sumsq(x)
+    (stats,) = ex.comm.all_reduce([stats], group, "add", inplace=True)
+    y, mean, rstd = nat.ln_apply_stats(x, stats, w, b, x.shape[1] * group.group_size, op.attrs["eps"])
+    return [y], [mean], [rstd]
+
+
 def ar_add_layer_norm(ex, op, x_vals, delta_vals, *rest):
     """All-reduce of the partial layer output + residual update + LayerNorm in one kernel (token-by-token decoding)."""
     nat = _lib()
@@ -345,7 +359,8 @@ def ar_add_layer_norm(ex, op, x_vals, delta_vals, *rest):
     return [h]
 
 
-_TABLE = {"matmul_all_reduce": matmul_all_reduce, "ar_add_layer_norm": ar_add_layer_norm, "matmul2_all_reduce": matmul2_all_reduce, "rts_adam": rts_adam}
+_TABLE = {"matmul_all_reduce": matmul_all_reduce, "ar_add_layer_norm": ar_add_layer_norm,
+          "layer_norm_distributed_fwd": layer_norm_distributed_fwd, "matmul2_all_reduce": matmul2_all_reduce, "rts_adam": rts_adam}
 
 
 def lookup(name: str, session):
