@@ -452,3 +452,40 @@ def test_pipeline_training_with_stash_equals_sequential():
         return s.get_tensor_data(dw.accum.weight).copy()
 
     np.testing.assert_almost_equal(sequential(), pipelined())
+
+
+# ---- graph passes of the multi-GPU runtime ------------------------------------------------------------------------
+
+
+def test_matmul_sum_and_collective_fusion_passes_keep_the_numbers():
+    """`a1 @ w1 + a2 @ w2` becomes one accumulate-in-epilogue op, `all_reduce(a1 @ w1 + a2 @ w2)` one fused collective
+    op; both must give the results (and gradients) of the plain composition."""
+    from popxl_addons_b200.parallel import fuse_gemm_collectives, fuse_matmul_sums
+    from popxl_addons_b200.testing_utils import ops_of_type
+
+    rs = np.random.RandomState(5)
+    a1, a2 = rs.normal(size=(2, 6, 8)).astype(np.float32), rs.normal(size=(2, 6, 4)).astype(np.float32)
+    w1, w2 = rs.normal(size=(8, 5)).astype(np.float32), rs.normal(size=(4, 5)).astype(np.float32)
+
+    def run(fuse_ar, fuse_sum):
+        ir = popxl.Ir(replication=2)
+        with ir.main_graph:
+            s1, s2 = popxl.h2d_stream((6, 8), popxl.float32), popxl.h2d_stream((6, 4), popxl.float32)
+            x1, x2 = ops.host_load(s1), ops.host_load(s2)
+            v1, v2 = popxl.variable(w1, name="w1"), popxl.variable(w2, name="w2")
+            y = ops.collectives.replicated_all_reduce(x1 @ v1 + x2 @ v2, "add", ir.replica_grouping())
+            z = (x1 @ v1) + (x2 @ v2)
+            out_y, out_z = addons.host_store(y), addons.host_store(z)
+        n_ar = fuse_gemm_collectives(ir) if fuse_ar else 0
+        n_sum = fuse_matmul_sums(ir) if fuse_sum else 0
+        names = [op.opdef.name for op in ir.main_graph.ops]
+        res = popxl.Session(ir, "cpu").run({s1: a1, s2: a2})
+        return res[out_y], res[out_z], n_ar, n_sum, names
+
+    y0, z0, *_ = run(False, False)
+    y1, z1, n_ar, n_sum, names = run(True, True)
+    assert n_ar == 1 and n_sum == 1 and "matmul2_all_reduce" in names and "matmul_add" in names
+    np.testing.assert_allclose(y1, y0, rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(z1, z0, rtol=1e-5, atol=1e-5)
+    want = (a1 @ w1 + a2 @ w2).sum(axis=0)
+    np.testing.assert_allclose(y0[0], want, rtol=1e-5, atol=1e-5)
