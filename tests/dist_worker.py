@@ -90,6 +90,25 @@ def main():
                   and np.allclose(out[streams[3]], data.mean(0)))
         n = 6 // world
         ok = ok and bool(np.allclose(out[streams[2]], data.mean(0)[rank * n:(rank + 1) * n]))
+        # hidden-sharded LayerNorm (native kernels + one small all-reduce on the GPU) against the full-width LayerNorm
+        from popxl_addons_b200.ops.layer_norm_distributed import layer_norm_distributed
+
+        rs = np.random.RandomState(7)
+        full = rs.normal(size=(5, 16 * world)).astype(np.float32)
+        gamma, beta = rs.normal(size=16 * world).astype(np.float32), rs.normal(size=16 * world).astype(np.float32)
+        ir2 = popxl.Ir(replication="popdist")
+        with ir2.main_graph:
+            hx = popxl.h2d_stream((5, 16), popxl.float32)
+            hw, hb = popxl.h2d_stream((16,), popxl.float32), popxl.h2d_stream((16,), popxl.float32)
+            y = layer_norm_distributed(ops.host_load(hx), ops.host_load(hw), ops.host_load(hb), 1e-5,
+                                       ir2.replica_grouping())
+            out_y = addons.host_store(y)
+        s2 = popxl.Session(ir2, args.device)
+        sl = slice(16 * rank, 16 * (rank + 1))
+        got = s2.run({hx: full[:, sl], hw: gamma[sl], hb: beta[sl]})[out_y]
+        mu, var = full.mean(-1, keepdims=True), full.var(-1, keepdims=True)
+        want = ((full - mu) / np.sqrt(var + 1e-5) * gamma + beta)[:, sl]
+        ok = ok and bool(np.allclose(got, want, rtol=1e-4, atol=1e-4))
         flag = torch.tensor([int(ok)], device=s.device)
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if rank == 0:
