@@ -5,7 +5,7 @@ Typical use: `from popxl_addons_b200 import xl as popxl; from popxl_addons_b200.
 from . import dtypes
 from .dtypes import (dtype, float64, float32, float16, bfloat16, float8_143, float8_152, int64, int32, int16, int8,
                      uint64, uint32, uint16, uint8, bool_)
-from .core import (Ir, Graph, Op, Tensor, Variable, Constant, TensorSpec, TensorByRef, ReplicaGrouping, gcg, gir, gmg,
+from .core import (Ir, Graph, Op, Options, Tensor, Variable, Constant, TensorSpec, TensorByRef, ReplicaGrouping, gcg, gir, gmg,
                    get_current_graph, name_scope, in_sequence, ipu, device, io_tiles, main_tiles, graph_input,
                    graph_output, variable, constant, replica_sharded_variable, LazyInit)
 from .buffers import (HostToDeviceStream, DeviceToHostStream, RemoteBuffer, h2d_stream, d2h_stream, remote_buffer,

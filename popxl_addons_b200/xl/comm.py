@@ -103,7 +103,9 @@ class DistComm:
             import os
 
             # a collective that waits longer than this ends with an error instead of blocking the job for good
-            timeout = datetime.timedelta(seconds=float(os.environ.get("XL_COLLECTIVE_TIMEOUT_S", "600")))
+            from .core import Options
+
+            timeout = datetime.timedelta(seconds=float(Options.from_env().collective_timeout_s))
             dist.init_process_group(backend=backend, device_id=device if device.type == "cuda" else None,
                                     timeout=timeout)
         self.dist = dist

@@ -13,6 +13,7 @@ variable_factory.py:9-14, transforms/*.py): `Ir`, `Graph`, `Tensor`, `TensorSpec
 """
 import contextlib
 import inspect
+import dataclasses
 import itertools
 import math
 from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Tuple, Union
@@ -660,6 +661,45 @@ class Graph:
         return "\n".join(repr(o) for o in self.ops)
 
 
+@dataclasses.dataclass
+class Options:
+    """Typed run-time options of an `Ir` (read by the `Session` that executes it). Every field can be overridden from the
+    environment (`XL_<FIELD NAME IN CAPITALS>`, e.g. `XL_NATIVE_KERNELS=0`); the reference has no configuration system
+    beyond constructor arguments and a few environment variables (popxl_addons/debugging.py:21,
+    named_replica_grouping.py:78-85)."""
+
+    native_kernels: bool = True        # run the sm_100a kernels on CUDA sessions (False: torch reference everywhere)
+    cuda_graphs: bool = True           # capture `repeat(..., cuda_graph=True)` bodies and replay them
+    profile_ops: bool = False          # time every op (CUDA events / perf_counter) into `Session.profile`
+    nvtx: bool = False                 # NVTX range per op, named `<graph>/<op>`
+    collective_timeout_s: float = 600.0  # process-group timeout: a collective that waits longer ends with an error
+
+    @classmethod
+    def from_env(cls) -> "Options":
+        import os
+
+        o = cls()
+        for f in dataclasses.fields(cls):
+            raw = os.environ.get("XL_" + f.name.upper())
+            if raw is None:
+                continue
+            setattr(o, f.name, raw.lower() not in ("0", "false", "no", "") if f.type is bool or f.type == "bool"
+                    else float(raw))
+        # older spellings
+        if os.environ.get("XL_NATIVE") is not None:
+            o.native_kernels = os.environ["XL_NATIVE"] != "0"
+        return o
+
+    # dict-style access for scripts that poke session options by name
+    def __getitem__(self, key):
+        return getattr(self, key)
+
+    def __setitem__(self, key, value):
+        if not hasattr(self, key):
+            raise KeyError(f"unknown option {key!r}; known: {[f.name for f in dataclasses.fields(self)]}")
+        setattr(self, key, value)
+
+
 class _PbIrShim:
     """Minimal stand-in for the handful of low-level IR queries that user scripts written for the reference make."""
 
@@ -711,7 +751,7 @@ class Ir:
         self.initial_values: Dict[Variable, Any] = {}
         self.remote_buffers: List[Any] = []
         self.streams: List[Any] = []
-        self.options: Dict[str, Any] = {}
+        self.options: Options = Options.from_env()
 
     # -- replication ----------------------------------------------------------------------------------------------
     @property

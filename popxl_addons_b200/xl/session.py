@@ -11,6 +11,7 @@ Parity: the `popxl.Session` surface used by popxl_addons/task_session.py:52-53,8
 """
 import os
 import sys
+import time
 from typing import Any, Dict, Iterable, List, Mapping, Optional
 
 import numpy as np
@@ -45,7 +46,7 @@ class Session:
         self.distributed = bool(ir.distributed) and int(os.environ.get("WORLD_SIZE", "1")) > 1
         self.num_replicas = ir.replication_factor
         if use_native is None:
-            use_native = os.environ.get("XL_NATIVE", "1") != "0"
+            use_native = ir.options.native_kernels
         self.slots = int(getattr(ir, "devices_per_replica", 1)) if self.distributed else 1
         self.slot: Optional[int] = None  # device slot (pipeline stage GPU) this process executes; None: all of them
         self._frame_dev: List[Optional[int]] = []
@@ -82,7 +83,10 @@ class Session:
         self._capture_outputs = None
         self.h2d_bytes = 0  # host->device / device->host traffic of `run` so far (bytes of the tensors copied)
         self.d2h_bytes = 0
-        self.profile: Optional[Dict[str, List[float]]] = None
+        # per-op timing: None = off, else a list of (graph name, op name, start, end) with CUDA events (or host
+        # timestamps on CPU); summarised by `profile_summary()`
+        self.profile: Optional[list] = [] if ir.options.profile_ops else None
+        self._nvtx = bool(ir.options.nvtx) and self.device.type == "cuda"
         self._init_state()
 
     # ------------------------------------------------------------------------------------------------------
@@ -415,6 +419,35 @@ class Session:
             return a.elapsed_time(b)
         return (b - a) * 1e3
 
+    # -- per-op profile ----------------------------------------------------------------------------------------------
+    def _now(self):
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            return ev
+        return time.perf_counter()
+
+    def start_profile(self):
+        """Time every op from now on (loop bodies run eagerly while profiling, CUDA-graph replay is bypassed)."""
+        self.profile = []
+
+    def profile_summary(self, stop: bool = True) -> Dict[str, Dict[str, float]]:
+        """`{op name: {"count", "ms"}}` over everything executed since profiling started, slowest first. On CUDA the
+        times are between events on the launching stream: an op's time includes the wait for its own launch when the
+        host runs behind the device."""
+        if self.profile is None:
+            raise RuntimeError("profiling is off: set `ir.options.profile_ops` or call `start_profile()`")
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        agg: Dict[str, Dict[str, float]] = {}
+        for _g, name, a, b in self.profile:
+            ms = a.elapsed_time(b) if self.device.type == "cuda" else (b - a) * 1e3
+            e = agg.setdefault(name, {"count": 0, "ms": 0.0})
+            e["count"] += 1
+            e["ms"] += ms
+        self.profile = None if stop else []
+        return dict(sorted(agg.items(), key=lambda kv: -kv[1]["ms"]))
+
     def native_collective(self, name: str):
         """Fused compute+collective kernel registered under `name` for this session's transport, or None (then the
         op runs its reference composition over `self.comm`)."""
@@ -501,6 +534,11 @@ class Session:
                 if self._effective_device(op, frame) != self.slot:
                     continue
                 self.comm.flush_p2p()  # received tensors may be read from here on
+            timed = self.profile is not None and od.name not in ("call", "repeat", "conditional")
+            if timed:
+                t_start = self._now()
+            if self._nvtx:
+                torch.cuda.nvtx.range_push(f"{graph.name}/{od.name}")
             if od.special is not None:
                 for t in op.inputs:
                     if t not in env:
@@ -520,6 +558,10 @@ class Session:
                     outs_per_replica.append((res,) if isinstance(res, torch.Tensor) else tuple(res or ()))
                 for j, t in enumerate(op.outputs):
                     env[t] = [outs_per_replica[r][j] for r in range(self.num_local)]
+            if self._nvtx:
+                torch.cuda.nvtx.range_pop()
+            if timed:
+                self.profile.append((graph.name, od.name, t_start, self._now()))
             self._free_dead(frees, i, env)
         if staged:
             self.comm.flush_p2p()
@@ -540,7 +582,7 @@ class Session:
         n_out = len(graph._outputs)
         count = op.attrs["count"]
         if (op.attrs.get("cuda_graph") and self.device.type == "cuda" and n_out == 0 and self.num_local == 1
-                and os.environ.get("XL_CUDA_GRAPHS", "1") != "0"):
+                and self.ir.options.cuda_graphs and self.profile is None):
             self._run_repeat_captured(op, graph, vals, count)
             return
         outs = vals[:n_out]

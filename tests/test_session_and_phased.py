@@ -276,3 +276,27 @@ def test_named_replica_grouping_helpers(monkeypatch):
         assert groups.index_in_group(6) == 1 and groups.num_groups == 8
         with pytest.raises(ValueError):
             ir.replica_grouping(stride=3, group_size=4)
+
+
+def test_options_and_per_op_profile(monkeypatch):
+    """Typed options with environment overrides; the per-op profile counts and times what ran."""
+    monkeypatch.setenv("XL_CUDA_GRAPHS", "0")
+    monkeypatch.setenv("XL_COLLECTIVE_TIMEOUT_S", "42")
+    o = popxl.Options.from_env()
+    assert o.cuda_graphs is False and o.collective_timeout_s == 42.0 and o.native_kernels is True
+    with pytest.raises(KeyError):
+        o["no_such_option"] = 1
+    ir = popxl.Ir()
+    ir.options.profile_ops = True
+    with ir.main_graph:
+        x = popxl.variable(np.ones((4, 4), np.float32), name="x")
+        g = ir.create_empty_graph("body")
+        with g:
+            a = popxl.graph_input((4, 4), popxl.float32, "a", by_ref=True)
+            ops.var_updates.copy_var_update_(a, ops.gelu(a @ a))
+        ops.repeat(g, 3, inputs_dict={a: x})
+    s = popxl.Session(ir, "cpu")
+    s.run({})
+    summary = s.profile_summary()
+    assert summary["matmul"]["count"] == 3 and summary["gelu"]["count"] == 3 and summary["matmul"]["ms"] >= 0.0
+    assert "repeat" not in summary and s.profile is None
