@@ -673,6 +673,7 @@ class Options:
     profile_ops: bool = False          # time every op (CUDA events / perf_counter) into `Session.profile`
     nvtx: bool = False                 # NVTX range per op, named `<graph>/<op>`
     collective_timeout_s: float = 600.0  # process-group timeout: a collective that waits longer ends with an error
+    hints: Dict[str, Any] = dataclasses.field(default_factory=dict)  # recorded planner hints (memory proportion, fc pass)
 
     @classmethod
     def from_env(cls) -> "Options":
@@ -681,7 +682,7 @@ class Options:
         o = cls()
         for f in dataclasses.fields(cls):
             raw = os.environ.get("XL_" + f.name.upper())
-            if raw is None:
+            if raw is None or f.name == "hints":
                 continue
             setattr(o, f.name, raw.lower() not in ("0", "false", "no", "") if f.type is bool or f.type == "bool"
                     else float(raw))
@@ -690,14 +691,30 @@ class Options:
             o.native_kernels = os.environ["XL_NATIVE"] != "0"
         return o
 
-    # dict-style access for scripts that poke session options by name
+    # dict-style access: typed fields by name, anything else is kept as a hint (what the IPU planner knobs of the
+    # reference become here: recorded, readable, without effect on the result)
     def __getitem__(self, key):
-        return getattr(self, key)
+        return getattr(self, key) if key in self._fields() else self.hints[key]
 
     def __setitem__(self, key, value):
-        if not hasattr(self, key):
-            raise KeyError(f"unknown option {key!r}; known: {[f.name for f in dataclasses.fields(self)]}")
-        setattr(self, key, value)
+        if key in self._fields():
+            setattr(self, key, value)
+        else:
+            self.hints[key] = value
+
+    def __contains__(self, key):
+        return key in self._fields() or key in self.hints
+
+    def get(self, key, default=None):
+        return self[key] if key in self else default
+
+    def setdefault(self, key, default=None):
+        if key not in self:
+            self[key] = default
+        return self[key]
+
+    def _fields(self):
+        return {f.name for f in dataclasses.fields(self)} - {"hints"}
 
 
 class _PbIrShim:
