@@ -87,8 +87,19 @@ class TaskSession(xl.Session):
         self.session_state.update(info)
 
     # -- state access -----------------------------------------------------------------------------------------
+    def _owned_state(self) -> Dict[str, Any]:
+        """State variables this process holds: all of them, unless replicas span several processes (pipeline
+        stages), in which case every process holds the variables of its device slot."""
+        return {k: v for k, v in self.state.to_dict().items() if self.owns(v)}
+
+    def _is_writer(self) -> bool:
+        """Whether this process writes checkpoint files: the process(es) of replica 0 (one per device slot)."""
+        if self.slot is None:
+            return _rank() == 0
+        return self.comm.rank == 0
+
     def get_named_tensors_data(self) -> NamedTensorData:
-        named = self.state.to_dict()
+        named = self._owned_state()
         data = self.get_tensors_data(list(named.values()))
         return NamedTensorData.from_dict({k: data[t] for k, t in named.items()})
 
@@ -112,7 +123,7 @@ class TaskSession(xl.Session):
         At most `max_checkpoints` directories written by this session are kept (oldest removed first)."""
         with timer("Fetching state for checkpoint", log_to_wandb=False):
             data = self.get_named_tensors_data().to_dict()  # collective: all ranks
-        if _rank() != 0:
+        if not self._is_writer():
             return
         with timer("Saving checkpoint", log_to_wandb=False):
             if checkpoint_dir.startswith(_WANDB_PREFIX):
@@ -127,7 +138,7 @@ class TaskSession(xl.Session):
                 return
             while self.max_checkpoints and len(self._saved) >= self.max_checkpoints:
                 old = self._saved.popleft()
-                if os.path.isdir(old) and os.path.abspath(old) != os.path.abspath(checkpoint_dir):
+                if _rank() == 0 and os.path.isdir(old) and os.path.abspath(old) != os.path.abspath(checkpoint_dir):
                     logger.info("Removing old checkpoint %s", old)
                     shutil.rmtree(old, ignore_errors=True)
             self._write_checkpoint(checkpoint_dir, data)
@@ -144,6 +155,8 @@ class TaskSession(xl.Session):
                 np.save(os.path.join(model_dir, f"{name}.npy"), np.asarray(array))
             else:
                 np.savez(os.path.join(model_dir, f"{name}.npz"), **{name: array})
+        if _rank() != 0:
+            return  # the files every checkpoint has once are written by one process
         if self._dataloader is not None:
             self._dataloader.save(os.path.join(checkpoint_dir, "dataloader.bin"))
         with open(os.path.join(checkpoint_dir, "session_info.json"), "w") as f:
@@ -188,9 +201,9 @@ class TaskSession(xl.Session):
     def _load_named(self, loaded: Mapping[str, np.ndarray], report_missing: str):
         if report_missing not in ("none", "warn", "error"):
             raise ValueError(f"report_missing must be one of none, warn, error. Not: {report_missing}")
-        named = self.state.to_dict()
+        named = self._owned_state()
         missing = sorted(set(named) - set(loaded))
-        extra = sorted(set(loaded) - set(named))
+        extra = sorted(set(loaded) - set(self.state.to_dict()))
         if (missing or extra) and report_missing != "none":
             msg = ""
             if missing:

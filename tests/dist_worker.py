@@ -32,6 +32,7 @@ def main():
     ap.add_argument("--gemm-k", dest="k", type=int, default=4096)
     ap.add_argument("--n-copy", type=int, default=16)
     ap.add_argument("--slots", type=int, default=2)
+    ap.add_argument("--ckpt", default="")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -369,10 +370,23 @@ def main():
             tok = torch.randint(0, cfg.vocab_size, (6, dp, 1, cfg.seq_len + 1), generator=g, dtype=torch.int32)
             loss = tr.step(tok[:, replica:replica + 1])
             losses.append(loss)
+        ckpt_ok = None
+        if args.ckpt:
+            # every process writes the variables of its own device slot into one directory and restores them from it
+            sess = tr.session
+            before = {k: v.copy() for k, v in sess.get_named_tensors_data().to_dict().items()}
+            sess.save_checkpoint(args.ckpt)
+            dist.barrier()
+            for var in sess._owned_state().values():
+                sess.write_variable_data(var, np.zeros(var.shape_on_host, dtype=np.float32))
+            sess.load_checkpoint(args.ckpt, report_missing="error")
+            after = sess.get_named_tensors_data().to_dict()
+            ckpt_ok = bool(set(before) == set(after) and all(np.array_equal(before[k], after[k]) for k in before))
         gathered = [None] * world
-        dist.all_gather_object(gathered, {"rank": rank, "losses": losses})
+        dist.all_gather_object(gathered, {"rank": rank, "losses": losses, "ckpt_ok": ckpt_ok,
+                                          "n_owned": len(tr.session._owned_state())})
         if rank == 0:
-            print(json.dumps({"ranks": gathered}))
+            print(json.dumps({"ranks": gathered, "n_state": len(tr.state.to_dict())}))
     elif args.mode == "fail":
         # rank 1 stops between steps; rank 0 notices on the host before launching anything that would wait for it
         from datetime import timedelta

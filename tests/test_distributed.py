@@ -141,7 +141,7 @@ def test_pipeline_stages_on_separate_processes(nproc):
 
 
 @pytest.mark.parametrize("nproc", [2, 4])
-def test_pipeline_trainer_on_separate_processes_matches_simulation(nproc):
+def test_pipeline_trainer_on_separate_processes_matches_simulation(nproc, tmp_path):
     """Llama-shaped model, 2 device slots per replica, 1 or 2 data-parallel replicas: the losses of three optimizer steps
     must match the same trainer run in one process (all slots and replicas simulated in-process)."""
     from popxl_addons_b200.models import decoder as dec
@@ -158,8 +158,14 @@ def test_pipeline_trainer_on_separate_processes_matches_simulation(nproc):
         tok = torch.randint(0, cfg.vocab_size, (6, dp, 1, cfg.seq_len + 1), generator=g, dtype=torch.int32)
         out = tr.session.run({tr.inputs.tokens: tok, tr.inputs.labels: tok})[tr.outputs.loss]
         want.append(np.asarray(out).reshape(6, dp).mean(axis=0))  # per replica
-    res = launch(nproc, "--mode", "pp_train", "--slots", "2", "--dtype", "float32", timeout=400)
+    ckpt = str(tmp_path / "ckpt")
+    res = launch(nproc, "--mode", "pp_train", "--slots", "2", "--dtype", "float32", "--ckpt", ckpt, timeout=400)
+    # checkpoint: one directory, every variable exactly once (written by the slot that owns it), restored bit-exactly
+    files = {os.path.basename(p)[:-4] for p in os.listdir(os.path.join(ckpt, "model"))}
+    assert len(files) == res["n_state"] and os.path.exists(os.path.join(ckpt, "session_info.json"))
+    assert sum(i["n_owned"] for i in res["ranks"][:2]) == res["n_state"]
     for info in res["ranks"]:
+        assert info["ckpt_ok"] is True
         replica, slot = info["rank"] // 2, info["rank"] % 2
         if slot == 1:
             np.testing.assert_allclose(info["losses"], [w[replica] for w in want], rtol=1e-4)
