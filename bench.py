@@ -229,6 +229,8 @@ def main():
                          "pipeline: pipeline x data parallel training (--stages device slots per replica)")
     ap.add_argument("--tp", type=int, default=0, help="train mode: tensor-parallel width (default min(gpus, 4))")
     ap.add_argument("--stages", type=int, default=4, help="pipeline mode: device slots (GPUs) per replica")
+    ap.add_argument("--sequence-parallel", action="store_true",
+                    help="train mode: shard the residual stream over the tokens inside the TP group")
     ap.add_argument("--batch", type=int, default=16, help="decode mode: sequences per batch")
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--new-tokens", type=int, default=128)
@@ -274,6 +276,7 @@ def main():
         cfg.layers = args.layers
     if args.emulate_tp:
         _shrink(cfg, args.emulate_tp)
+    cfg.sequence_parallel = bool(args.sequence_parallel)
     W = max(args.warmup, 3)
     K = args.steps
     t0 = time.perf_counter()
@@ -392,7 +395,7 @@ def main():
                                     (", state sharded over dp (RTS)" if dp > 1 else ""),
                        "recompute": "per layer", "l2": "each step streams >100 GB of weights, optimizer state and "
                                                        "activations, far beyond the 126 MB L2; no flush needed",
-                       "emulate_tp": args.emulate_tp or None,
+                       "emulate_tp": args.emulate_tp or None, "sequence_parallel": bool(args.sequence_parallel),
                        "headline": (not args.layers and not args.emulate_tp and args.model == "gptj_6b" and not pipeline
                                     and not args.tp
                                     and args.micro_batch_size == 1 and args.micro_batches == 16)},

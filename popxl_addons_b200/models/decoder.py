@@ -42,6 +42,14 @@ class DecoderConfig:
     init_std: float = 0.02
     tp: int = 1
     dp: int = 1
+    # Sequence parallelism inside the TP group: the residual stream, the norms and the residual adds work on
+    # `tokens / tp` rows per rank; the TP all-reduces become reduce-scatter (after the row-parallel linears) and
+    # all-gather (before the column-parallel ones): same bytes on the wire, 1/tp of the elementwise work.
+    sequence_parallel: bool = False
+
+    @property
+    def sp(self) -> bool:
+        return self.sequence_parallel and self.tp > 1
 
     @property
     def xl_dtype(self) -> xl.dtype:
@@ -118,6 +126,20 @@ class _Parallel:
     def sharded_rg(self):
         """Grouping for a tensor-parallel shard: identical across DP."""
         return self.dp_group if self.tp > 1 else None
+
+
+def _gather_tokens(h_s: xl.Tensor, par: "_Parallel") -> xl.Tensor:
+    """`(tokens/tp, hidden)` rows of every TP rank -> `(tokens, hidden)`; gradient: reduce-scatter."""
+    rows, hidden = h_s.shape
+    return ops.collectives.replicated_all_gather(h_s, par.tp_group, output_shape=(rows * par.tp, hidden))
+
+
+def _scatter_tokens(s: xl.Tensor, par: "_Parallel") -> xl.Tensor:
+    """Sum of the ranks' partial `(tokens, hidden)` results, this rank's `tokens/tp` rows; gradient: all-gather."""
+    rows, hidden = s.shape
+    if rows % par.tp:
+        raise ValueError(f"sequence parallelism needs the token count ({rows}) to be a multiple of tp={par.tp}")
+    return ops.reshape(ops.collectives.replicated_reduce_scatter(s, "add", par.tp_group), (rows // par.tp, hidden))
 
 
 class DecoderBlock(Module):
@@ -207,6 +229,21 @@ class DecoderBlock(Module):
     def build(self, x: xl.Tensor, sin: xl.Tensor, cos: xl.Tensor) -> xl.Tensor:
         cfg = self.cfg
         par = _Parallel(cfg)
+        if cfg.sp:
+            # x holds this rank's tokens/tp rows; gather before the column-parallel linears, scatter after the
+            # row-parallel ones
+            if cfg.family == "gptj":
+                h = _gather_tokens(self._norm("ln_1", x), par)
+                o = self._attention(h, sin, cos, par, collectives=False)
+                y, b2 = self._mlp(h, par, collectives=False)
+                return x + _scatter_tokens(o + y, par) + b2
+            if cfg.family == "gpt2":
+                raise NotImplementedError("sequence parallelism is implemented for the gptj and llama blocks")
+            h = _gather_tokens(self._norm("ln_1", x), par)
+            x = x + _scatter_tokens(self._attention(h, sin, cos, par, collectives=False), par)
+            h = _gather_tokens(self._norm("ln_2", x), par)
+            y, _ = self._mlp(h, par, collectives=False)
+            return x + _scatter_tokens(y, par)
         if cfg.family == "gptj":
             # parallel residual: attention and feed-forward read the same normalised input
             h = self._norm("ln_1", x)
@@ -238,6 +275,10 @@ class DecoderEmbedding(Module):
                                     cfg.xl_dtype, replica_grouping=par.sharded_rg, overwrite=True)
         idx = tokens if shard_offset is None else tokens - shard_offset
         x = ops.gather(w, idx, axis=0, zero_OOR=par.tp > 1)
+        if cfg.sp:
+            if cfg.family == "gpt2":
+                raise NotImplementedError("sequence parallelism is implemented for the gptj and llama blocks")
+            return _scatter_tokens(x, par)
         if par.tp > 1:
             x = replicated_all_reduce_identical_grad_inputs(x, group=par.tp_group)
         if cfg.family == "gpt2":
@@ -267,7 +308,9 @@ class DecoderHead(Module):
             b = self.add_variable_input("ln_f.bias", _const_init("zeros", (cfg.hidden,), cfg.np_dtype), cfg.xl_dtype,
                                         overwrite=True)
             h = ops.layer_norm(x, w, b, eps=cfg.eps)
-        if par.tp > 1:
+        if cfg.sp:
+            h = _gather_tokens(h, par)
+        elif par.tp > 1:
             h = replicated_all_reduce_identical_inputs(h, group=par.tp_group)
         shard = Embedding.get_vocab_shard_size(cfg.vocab_size, par.tp)
         wl = self.add_variable_input("lm_head.weight", _normal((cfg.hidden, shard), cfg.init_std, cfg.np_dtype),

@@ -37,12 +37,16 @@ from .decoder import DecoderBlock, DecoderConfig, DecoderEmbedding, DecoderHead,
 __all__ = ["DecoderTrainer"]
 
 
-def build_optimizer(ir, cfg, par, groups, hp, state_dtype, shard_optimizer, fused_collectives, slot_of=None):
+def build_optimizer(ir, cfg, par, groups, hp, state_dtype, shard_optimizer, fused_collectives, slot_of=None,
+                    reduce_replicated_over=None):
     """Emit the AdamW update of every parameter of `groups` (`(name, weights, accumulators)` triples) into the
     current graph: fp32 master weights and moments, sharded over the data-parallel group when `shard_optimizer`
     (as one fused reduce-scatter + AdamW + all-gather kernel per parameter when `fused_collectives`), otherwise a
     gradient all-reduce followed by a replicated update. `slot_of(name)` places a group's update on a device slot
-    (pipeline parallel). Returns `(master weights by name, optimizer state by name)`."""
+    (pipeline parallel). `reduce_replicated_over`: replica grouping over which the gradients of parameters that are
+    replicated across it are only partial sums and have to be added up first (the TP group under sequence
+    parallelism, where norm weights and output biases see tokens/tp rows per rank).
+    Returns `(master weights by name, optimizer state by name)`."""
     import contextlib
 
     def placed(name):
@@ -60,6 +64,9 @@ def build_optimizer(ir, cfg, par, groups, hp, state_dtype, shard_optimizer, fuse
             for pname, w in wd.items():
                 g = ad[pname]
                 full = f"{group_name}.{pname}"
+                if reduce_replicated_over is not None and (w.replica_grouping is None
+                                                           or w.replica_grouping.num_groups == 1):
+                    g = ops.collectives.replicated_all_reduce_(g, "add", reduce_replicated_over)
                 decay = hp["weight_decay"] if w.rank >= 2 else 0.0
                 host = ir.initial_values[w]
                 if isinstance(host, xl.LazyInit):
@@ -155,6 +162,11 @@ class DecoderTrainer:
             from ..parallel import fuse_gemm_collectives
 
             self.fused_gemm_collectives = fuse_gemm_collectives(self.ir)
+        self.fused_sequence_parallel = 0
+        if fused_collectives and cfg.sp and os.environ.get("XL_FUSE_SP", "1") != "0":
+            from ..parallel import fuse_sequence_parallel_collectives
+
+            self.fused_sequence_parallel = fuse_sequence_parallel_collectives(self.ir)
         from ..parallel import fuse_matmul_sums
 
         self.fused_matmul_sums = fuse_matmul_sums(self.ir)  # what the collective fusion left: c = a1 @ w1 + a2 @ w2
@@ -172,7 +184,7 @@ class DecoderTrainer:
             self.inputs = InputStreams(tokens=((self.micro_batch_size, cfg.seq_len + 1), xl.int32))
             self.outputs = OutputStreams(loss=((), xl.float32))
             sin, cos = rotary_tables(cfg)
-            x_spec = xl.TensorSpec((T, cfg.hidden), dt)
+            x_spec = xl.TensorSpec((T // cfg.tp if cfg.sp else T, cfg.hidden), dt)  # rows of the residual stream
             tok_spec = xl.TensorSpec((T,), xl.int32)
 
             # ---- graphs (one per distinct computation, shared by all layers) -----------------------------------
@@ -251,7 +263,8 @@ class DecoderTrainer:
             groups = ([("embedding", emb_vars, emb_acc), ("head", head_vars, head_acc)] +
                       [(f"layer{i}", blk_vars[i], blk_acc[i]) for i in range(cfg.layers)])
             self.master, opt_state = build_optimizer(ir, cfg, par, groups, self.hp, self.state_dtype,
-                                                     self.shard_optimizer, self.fused_collectives)
+                                                     self.shard_optimizer, self.fused_collectives,
+                                                     reduce_replicated_over=par.tp_group if cfg.sp else None)
             for atree in [emb_acc, head_acc] + blk_acc:
                 ops.var_updates.accumulator_zero_(atree.mean_accum_counter)
 

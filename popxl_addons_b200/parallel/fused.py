@@ -140,6 +140,43 @@ def matmul2_all_reduce(ex, op, a1_vals, w1_vals, a2_vals, w2_vals):
     return NotImplemented if out is None else [out]
 
 
+def matmuls_reduce_scatter(ex, op, *vals):
+    """`reduce_scatter(a1 @ w1 [+ a2 @ w2])` over the rows: every GEMM's epilogue adds its tiles into the shard of the
+    rank that owns the rows (`red.add` over NVLink). Returns the flat shard."""
+    nat = _lib()
+    ctx = runtime(ex).context(op.attrs["group"])
+    pairs = [(vals[i][0], vals[i + 1][0]) for i in range(0, len(vals), 2)]
+    a0, w0 = pairs[0]
+    M, N = a0.shape[0], w0.shape[-1]
+    if ctx.world == 1 or M % ctx.world or N % 8 or a0.dtype not in (torch.bfloat16, torch.float16):
+        return NotImplemented
+    shard = ctx.arena.ring((M // ctx.world, N), a0.dtype)
+    shard.zero_()
+    dst = _peer_ptr_tensor(ctx, shard)
+    for i, (a, w) in enumerate(pairs):
+        if nat.gemm(a, w, out=shard, accumulate=4, comm=ctx, rs_dst=dst) is NotImplemented:
+            if i:
+                raise RuntimeError("a GEMM of a fused group was rejected after an earlier one ran")
+            return NotImplemented
+    return [shard.reshape(-1).clone()]
+
+
+def all_gather_matmul(ex, op, hs_vals, w_vals):
+    """`all_gather(h_s) @ w`: the GEMM's copy CTAs pull the peers' rows into this rank's full-size operand while its
+    other CTAs start on the local rows. Returns `(product, gathered operand)`."""
+    ctx = runtime(ex).context(op.attrs["group"])
+    h_s, w = hs_vals[0], w_vals[0]
+    rows, k = h_s.shape
+    if ctx.world == 1 or rows % 128 or h_s.dtype not in (torch.bfloat16, torch.float16) or w.dtype != h_s.dtype:
+        return NotImplemented
+    full, own = gathered_operand(ctx, rows * ctx.world, k, h_s.dtype, 128, "sp")
+    own.copy_(h_s)
+    y = all_gather_gemm(ctx, full, w, sharded="a")
+    if y is NotImplemented:
+        return NotImplemented
+    return [y], [full.clone()]
+
+
 def _peer_ptr_tensor(ctx: GroupContext, t: torch.Tensor) -> torch.Tensor:
     """int64 device tensor with the address of arena tensor `t` in every rank's memory (cached per buffer)."""
     cache = ctx.__dict__.setdefault("_peer_ptr_cache", {})
@@ -360,7 +397,8 @@ def ar_add_layer_norm(ex, op, x_vals, delta_vals, *rest):
 
 
 _TABLE = {"matmul_all_reduce": matmul_all_reduce, "ar_add_layer_norm": ar_add_layer_norm,
-          "layer_norm_distributed_fwd": layer_norm_distributed_fwd, "matmul2_all_reduce": matmul2_all_reduce, "rts_adam": rts_adam}
+          "layer_norm_distributed_fwd": layer_norm_distributed_fwd,
+          "matmuls_reduce_scatter": matmuls_reduce_scatter, "all_gather_matmul": all_gather_matmul, "matmul2_all_reduce": matmul2_all_reduce, "rts_adam": rts_adam}
 
 
 def lookup(name: str, session):

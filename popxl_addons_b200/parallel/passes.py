@@ -148,6 +148,200 @@ def fuse_matmul_sums(ir: xl.Ir) -> int:
     return n
 
 
+# ---- sequence-parallel forms: GEMM(s) -> reduce-scatter, all-gather -> GEMM ---------------------------------------------
+
+
+def _special_matmuls_reduce_scatter(ex, op, env):
+    vals = [env[t] for t in op.inputs]
+    native = ex.native_collective("matmuls_reduce_scatter")
+    if native is not None:
+        res = native(ex, op, *vals)
+        if res is not NotImplemented:
+            env[op.outputs[0]] = res
+            return
+    mm = OPS["matmul"]
+    fn = mm.native.get(ex.device.type) if ex.use_native else None
+
+    def product(a, w):
+        y = fn(a, w) if fn is not None else NotImplemented
+        return mm.impl(a, w) if y is NotImplemented else y
+
+    outs = []
+    for r in range(ex.num_local):
+        y = product(vals[0][r], vals[1][r])
+        for i in range(2, len(vals), 2):
+            y = y + product(vals[i][r], vals[i + 1][r])
+        outs.append(y)
+    env[op.outputs[0]] = ex.comm.reduce_scatter(outs, op.attrs["group"], "add")
+
+
+def _vjp_matmuls_reduce_scatter(ctx, op, gs):
+    from ..xl.ops import matmul, reshape, transpose
+
+    a0, w0 = op.inputs[0], op.inputs[1]
+    rows, cols = a0.shape[0], w0.shape[-1]
+    g = reshape(emit1_all_gather(gs[0], op.attrs["group"]), (rows, cols))
+    grads = []
+    for i in range(0, len(op.inputs), 2):
+        a, w = op.inputs[i], op.inputs[i + 1]
+        grads += [matmul(g, transpose(ctx.fwd(w))), matmul(transpose(ctx.fwd(a)), g)]
+    return grads
+
+
+def emit1_all_gather(t, group):
+    from ..xl.opdef import emit1
+
+    return emit1("all_gather", [t], dict(group=group))
+
+
+OpDef("matmuls_reduce_scatter", special=_special_matmuls_reduce_scatter, vjp=_vjp_matmuls_reduce_scatter, collective=True,
+      infer=lambda op: [((op.inputs[0].shape[0] * op.inputs[1].shape[-1] // op.attrs["group"].group_size,),
+                         op.inputs[0].dtype, ())],
+      flops=lambda op: sum(2 * op.inputs[i].shape[-1] * op.inputs[0].shape[0] * op.inputs[1].shape[-1]
+                           for i in range(0, len(op.inputs), 2)))
+
+
+def _special_all_gather_matmul(ex, op, env):
+    hs, w = env[op.inputs[0]], env[op.inputs[1]]
+    native = ex.native_collective("all_gather_matmul")
+    if native is not None:
+        res = native(ex, op, hs, w)
+        if res is not NotImplemented:
+            env[op.outputs[0]], env[op.outputs[1]] = res
+            return
+    rows, k = op.inputs[0].shape
+    full = [f.reshape(rows * op.attrs["group"].group_size, k) for f in ex.comm.all_gather(hs, op.attrs["group"])]
+    mm = OPS["matmul"]
+    fn = mm.native.get(ex.device.type) if ex.use_native else None
+    ys = []
+    for r in range(ex.num_local):
+        y = fn(full[r], w[r]) if fn is not None else NotImplemented
+        ys.append(mm.impl(full[r], w[r]) if y is NotImplemented else y)
+    env[op.outputs[0]], env[op.outputs[1]] = ys, full
+
+
+def _vjp_all_gather_matmul(ctx, op, gs):
+    from ..xl.opdef import emit1
+    from ..xl.ops import add, matmul, reshape, transpose
+
+    h_s, w = op.inputs
+    y, h_full = op.outputs
+    gy, gh = gs  # gradient of the product and of the gathered operand (other consumers), either may be None
+    parts = []
+    if gy is not None:
+        parts.append(matmul(gy, transpose(ctx.fwd(w))))
+    if gh is not None:
+        parts.append(gh)
+    g_full = parts[0] if len(parts) == 1 else add(parts[0], parts[1])
+    g_s = reshape(emit1("reduce_scatter", [g_full], dict(group=op.attrs["group"], op="add", rts=False)), h_s.shape)
+    gw = matmul(transpose(ctx.fwd(h_full)), gy) if gy is not None else None
+    return [g_s, gw]
+
+
+OpDef("all_gather_matmul", special=_special_all_gather_matmul, vjp=_vjp_all_gather_matmul, collective=True,
+      infer=lambda op: [((op.inputs[0].shape[0] * op.attrs["group"].group_size, op.inputs[1].shape[-1]),
+                         op.inputs[0].dtype, ()),
+                        ((op.inputs[0].shape[0] * op.attrs["group"].group_size, op.inputs[0].shape[1]),
+                         op.inputs[0].dtype, ())],
+      flops=lambda op: 2 * op.inputs[0].shape[1] * op.outputs[0].nelms)
+
+
+def fuse_sequence_parallel_collectives(ir: xl.Ir) -> int:
+    """Rewrites of the sequence-parallel graphs: `reduce_scatter(a1 @ w1 [+ a2 @ w2])` -> `matmuls_reduce_scatter`
+    (GEMM epilogues add into the owner's shard) and `reshape(all_gather(h)) @ w` -> `all_gather_matmul` (the first GEMM
+    that reads the gathered rows pulls them from the peers itself; its second output, the gathered operand, serves the
+    other readers). Returns the number of rewrites."""
+    n = 0
+    for g in ir.graphs:
+        consumers = {}
+        for op in g.ops:
+            for t in op.inputs:
+                consumers.setdefault(t, []).append(op)
+        drop = set()
+
+        def single_use_matmul(t):
+            m = t.producer
+            return (m is not None and m.opdef.name == "matmul" and m.graph is g and m.uid not in drop
+                    and len(consumers.get(t, [])) == 1 and t not in g._outputs and m.inputs[0].rank == 2
+                    and m.inputs[1].rank == 2)
+
+        for rs in g.ops:
+            if rs.opdef.name != "reduce_scatter" or rs.attrs["op"] != "add" or rs.attrs["group"].group_size <= 1:
+                continue
+            src = rs.inputs[0]
+            prod = src.producer
+            if prod is None or prod.graph is not g or len(consumers.get(src, [])) != 1 or src in g._outputs:
+                continue
+            through = []
+            if prod.opdef.name == "reshape":  # a view between the sum and the (flattening) reduce-scatter
+                through, src = [prod], prod.inputs[0]
+                prod = src.producer
+                if prod is None or prod.graph is not g or len(consumers.get(src, [])) != 1 or src in g._outputs:
+                    continue
+            if prod.opdef.name == "matmul" and single_use_matmul(src):
+                ins, gone = [prod.inputs[0], prod.inputs[1]], [prod]
+            elif prod.opdef.name == "add" and all(single_use_matmul(t) for t in prod.inputs) \
+                    and prod.inputs[0].producer is not prod.inputs[1].producer \
+                    and prod.inputs[0].shape == prod.inputs[1].shape:
+                m1, m2 = prod.inputs[0].producer, prod.inputs[1].producer
+                ins, gone = [m1.inputs[0], m1.inputs[1], m2.inputs[0], m2.inputs[1]], [prod, m1, m2]
+            else:
+                continue
+            if ins[0].shape[0] % rs.attrs["group"].group_size:
+                continue
+            rs.opdef = OPS["matmuls_reduce_scatter"]
+            rs.name = "matmuls_reduce_scatter"
+            rs.inputs = ins
+            rs.attrs = {"group": rs.attrs["group"]}
+            drop.update(o.uid for o in gone + through)
+            n += 1
+        # all_gather -> reshape -> matmul(lhs)
+        new_ops = []
+        for ag in g.ops:
+            if ag.uid in drop:
+                continue
+            new_ops.append(ag)
+            if ag.opdef.name != "all_gather" or ag.attrs["group"].group_size <= 1:
+                continue
+            h_s, pre = ag.inputs[0], None
+            if h_s.rank == 1 and h_s.producer is not None and h_s.producer.opdef.name == "reshape" \
+                    and h_s.producer.graph is g and len(consumers.get(h_s, [])) == 1 and h_s not in g._outputs \
+                    and h_s.producer.inputs[0].rank == 2:
+                pre, h_s = h_s.producer, h_s.producer.inputs[0]  # flattened for the collective: look through the view
+            if h_s.rank != 2:
+                continue
+            users = consumers.get(ag.outputs[0], [])
+            if len(users) != 1 or users[0].opdef.name != "reshape" or ag.outputs[0] in g._outputs:
+                continue
+            rsh = users[0]
+            h_full = rsh.outputs[0]
+            rows, k = h_s.shape
+            if tuple(h_full.shape) != (rows * ag.attrs["group"].group_size, k):
+                continue
+            mms = [u for u in consumers.get(h_full, []) if u.opdef.name == "matmul" and u.inputs[0] is h_full
+                   and u.inputs[1].rank == 2 and u.uid not in drop]
+            if not mms:
+                continue
+            first = min(mms, key=lambda o: g.ops.index(o))
+            at = g.ops.index(first)
+            if any(g.ops.index(u) < at for u in consumers.get(h_full, []) if u is not first):
+                continue  # some other reader of the gathered rows runs before the first product
+            # the fused op sits where the first product was; the all-gather and the reshape go away
+            first.opdef = OPS["all_gather_matmul"]
+            first.name = "all_gather_matmul"
+            first.inputs = [h_s, first.inputs[1]]
+            first.attrs = {"group": ag.attrs["group"]}
+            y = first.outputs[0]
+            h_full.producer = first
+            first.outputs = [y, h_full]
+            drop.update({ag.uid, rsh.uid} | ({pre.uid} if pre is not None else set()))
+            new_ops.pop()  # the all_gather just appended
+            n += 1
+        if drop:
+            g.ops = [o for o in g.ops if o.uid not in drop]
+    return n
+
+
 def _fuse_pairs(g) -> int:
     """`all_reduce(matmul(a1, w1) + matmul(a2, w2))` -> one op: both GEMMs push their tiles into the same output."""
     consumers = {}

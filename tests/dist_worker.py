@@ -33,6 +33,7 @@ def main():
     ap.add_argument("--n-copy", type=int, default=16)
     ap.add_argument("--slots", type=int, default=2)
     ap.add_argument("--ckpt", default="")
+    ap.add_argument("--sp", type=int, default=0)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -47,6 +48,7 @@ def main():
 
         cfg = (GPTJConfig.tiny(dtype=args.dtype, tp=args.tp, dp=args.dp) if args.big
                else DecoderConfig.tiny("gptj", dtype=args.dtype, tp=args.tp, dp=args.dp))
+        cfg.sequence_parallel = bool(args.sp)
         trainer = DecoderTrainer(cfg, micro_batches=2, device=args.device, lr=1e-2,
                                  fused_collectives=bool(args.fused))
         losses = []

@@ -171,3 +171,26 @@ def test_pipeline_trainer_on_separate_processes_matches_simulation(nproc, tmp_pa
             np.testing.assert_allclose(info["losses"], [w[replica] for w in want], rtol=1e-4)
         else:
             assert info["losses"] == [None] * 3
+
+
+def test_sequence_parallel_equals_plain_tensor_parallel():
+    """Residual stream sharded over the tokens inside the TP group (reduce-scatter / all-gather instead of all-reduce):
+    same losses as the plain TP program, in the in-process simulation and with one process per replica (gloo)."""
+    import dataclasses
+
+    from popxl_addons_b200.models import decoder as dec
+    from popxl_addons_b200.models.decoder import DecoderConfig
+    from popxl_addons_b200.models.trainer import DecoderTrainer
+    sys.path.insert(0, HERE)
+    from dist_worker import global_tokens
+
+    results = {}
+    for family in ("gptj", "llama"):
+        cfg = DecoderConfig.tiny(family, dtype="float32", tp=2, dp=1)
+        for sp in (False, True):
+            dec._SEED[0] = 0
+            tr = DecoderTrainer(dataclasses.replace(cfg, sequence_parallel=sp), micro_batches=2, device="cpu", lr=1e-2)
+            results[family, sp] = [tr.step(global_tokens(cfg, 2, seed=s)) for s in range(3)]
+        np.testing.assert_allclose(results[family, True], results[family, False], rtol=1e-5)
+    got = launch(2, "--device", "cpu", "--tp", "2", "--dp", "1", "--dtype", "float32", "--sp", "1")
+    np.testing.assert_allclose(got["losses"], results["gptj", False], rtol=1e-4)
