@@ -85,7 +85,8 @@ def run_reference(args):
                    "(the reference is a layer on Graphcore's Poplar SDK, which exists only for IPU systems)")
     if why is None:
         why = "the reference imported, but it can only execute on Graphcore IPU hardware (popxl.Session needs an IPU)"
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    if int(os.environ.get("RANK", "0")) == 0:  # one line per job, also when launched with one process per GPU
+        print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
 
