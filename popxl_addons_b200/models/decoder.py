@@ -189,11 +189,13 @@ class DecoderBlock(Module):
         o = a @ wo
         if par.tp > 1 and collectives:
             o = replicated_all_reduce_identical_grad_inputs(o, group=par.tp_group)
+        bo = None
         if bias:
             bo = self.add_variable_input("attention.out.bias", _const_init("zeros", (cfg.hidden,), cfg.np_dtype),
                                          cfg.xl_dtype, overwrite=True)
-            o = o + bo
-        return o
+        if not collectives:
+            return o, bo  # partial result: the caller reduces it and adds the bias once
+        return o + bo if bo is not None else o
 
     def _mlp(self, h, par, collectives: bool = True):
         """With `collectives=False` returns `(partial result, output bias)`: the caller reduces and adds the bias."""
@@ -234,16 +236,18 @@ class DecoderBlock(Module):
             # row-parallel ones
             if cfg.family == "gptj":
                 h = _gather_tokens(self._norm("ln_1", x), par)
-                o = self._attention(h, sin, cos, par, collectives=False)
+                o, _ = self._attention(h, sin, cos, par, collectives=False)
                 y, b2 = self._mlp(h, par, collectives=False)
                 return x + _scatter_tokens(o + y, par) + b2
-            if cfg.family == "gpt2":
-                raise NotImplementedError("sequence parallelism is implemented for the gptj and llama blocks")
             h = _gather_tokens(self._norm("ln_1", x), par)
-            x = x + _scatter_tokens(self._attention(h, sin, cos, par, collectives=False), par)
+            o, bo = self._attention(h, sin, cos, par, collectives=False)
+            x = x + _scatter_tokens(o, par)
+            if bo is not None:
+                x = x + bo
             h = _gather_tokens(self._norm("ln_2", x), par)
-            y, _ = self._mlp(h, par, collectives=False)
-            return x + _scatter_tokens(y, par)
+            y, b2 = self._mlp(h, par, collectives=False)
+            x = x + _scatter_tokens(y, par)
+            return x + b2 if b2 is not None else x
         if cfg.family == "gptj":
             # parallel residual: attention and feed-forward read the same normalised input
             h = self._norm("ln_1", x)
@@ -252,7 +256,7 @@ class DecoderBlock(Module):
             # one identity / all-reduce pair around both branches: a single all-reduce per layer in the forward pass
             # (of the summed partial results) and a single one in the backward pass (of the summed input gradients)
             h = replicated_all_reduce_identical_inputs(h, group=par.tp_group)
-            o = self._attention(h, sin, cos, par, collectives=False)
+            o, _ = self._attention(h, sin, cos, par, collectives=False)
             y, b2 = self._mlp(h, par, collectives=False)
             s = replicated_all_reduce_identical_grad_inputs(o + y, group=par.tp_group)
             return x + s + b2
@@ -277,7 +281,13 @@ class DecoderEmbedding(Module):
         x = ops.gather(w, idx, axis=0, zero_OOR=par.tp > 1)
         if cfg.sp:
             if cfg.family == "gpt2":
-                raise NotImplementedError("sequence parallelism is implemented for the gptj and llama blocks")
+                # learned positions: every rank adds 1/tp of them to its partial lookup, the scatter sums them up
+                wpe = self.add_variable_input("wpe.weight",
+                                              _normal((cfg.seq_len, cfg.hidden), cfg.init_std, cfg.np_dtype),
+                                              cfg.xl_dtype, overwrite=True)
+                reps = tokens.shape[0] // cfg.seq_len
+                pos = wpe if reps == 1 else ops.tile(wpe, (reps, 1))
+                x = x + pos * (1.0 / par.tp)
             return _scatter_tokens(x, par)
         if par.tp > 1:
             x = replicated_all_reduce_identical_grad_inputs(x, group=par.tp_group)

@@ -185,7 +185,7 @@ def test_sequence_parallel_equals_plain_tensor_parallel():
     from dist_worker import global_tokens
 
     results = {}
-    for family in ("gptj", "llama"):
+    for family in ("gptj", "llama", "gpt2"):
         cfg = DecoderConfig.tiny(family, dtype="float32", tp=2, dp=1)
         for sp in (False, True):
             dec._SEED[0] = 0
