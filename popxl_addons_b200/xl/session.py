@@ -252,6 +252,8 @@ class Session:
                 else:
                     per_group.append(per_replica[members[0]].reshape(var.shape))
             res = torch.stack(per_group) if rg.num_groups > 1 else per_group[0]
+            if res.device.type == "cpu" and self.device.type == "cpu" and rg.num_groups == 1:
+                res = res.clone()  # on the CPU backend the gathered value is the live storage: hand out a copy
             out[var] = _dt.to_numpy(res)
         return out
 

@@ -300,3 +300,44 @@ def test_options_and_per_op_profile(monkeypatch):
     summary = s.profile_summary()
     assert summary["matmul"]["count"] == 3 and summary["gelu"]["count"] == 3 and summary["matmul"]["ms"] >= 0.0
     assert "repeat" not in summary and s.profile is None
+
+
+def test_run_to_run_determinism_check():
+    """The bitwise repeat-run comparison passes for an ordinary training step and reports a program whose result
+    depends on something outside its inputs and state."""
+    from popxl_addons_b200.debugging import check_run_to_run_determinism
+    from popxl_addons_b200.models.decoder import DecoderConfig
+    from popxl_addons_b200.models.trainer import DecoderTrainer
+
+    cfg = DecoderConfig.tiny("gptj", dtype="float32", tp=2, dp=1)
+    tr = DecoderTrainer(cfg, micro_batches=2, device="cpu", lr=1e-2)
+    tok = tr.synthetic_tokens(seed=0, pinned=False)
+    assert check_run_to_run_determinism(tr.session, {tr.inputs.tokens: tok}) == []
+    # a program that draws fresh random numbers each run is reported
+    ir = popxl.Ir()
+    with ir.main_graph:
+        seed = popxl.variable(np.array([1, 2], np.uint32), popxl.uint32, name="seed")
+        acc = popxl.variable(np.zeros(4, np.float32), name="acc")
+        noise = ops.random_normal(seed, (4,))
+        ops.var_updates.accumulate_(acc, noise)
+        new_seed, _ = ops.split_random_seed(seed)
+        out = addons.host_store(noise)
+    s = popxl.Session(ir, "cpu")
+    assert check_run_to_run_determinism(s, {}) == []  # same seed variable restored before each run -> same numbers
+    import torch
+
+    calls = {"n": 0}
+    from popxl_addons_b200.xl.opdef import OPS
+
+    orig = OPS["random_normal"].impl
+
+    def unseeded(*a, **k):
+        calls["n"] += 1
+        r = orig(*a, **k)
+        return r + calls["n"] if r.device.type != "meta" else r
+
+    OPS["random_normal"].impl = unseeded
+    try:
+        assert "acc" in " ".join(check_run_to_run_determinism(s, {}))
+    finally:
+        OPS["random_normal"].impl = orig
