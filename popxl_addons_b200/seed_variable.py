@@ -2,8 +2,6 @@
 Parity: popxl_addons/seed_variable.py:13-33."""
 from typing import Optional, Tuple
 
-import numpy as np
-
 from . import xl
 
 __all__ = ["seed_variable"]
@@ -11,13 +9,11 @@ __all__ = ["seed_variable"]
 
 def seed_variable(seed: int, replica_grouping: Optional[xl.ReplicaGrouping] = None) -> Tuple[xl.Variable, xl.Tensor]:
     """Returns `(variable, tensor to use in the graph)`. Each replica group gets its own seed pair derived from
-    `seed` (shape `(2,)` uint32); replicas inside a group share it."""
+    `seed` (shape `(2,)` uint32); replicas inside a group share it. Without a grouping every replica draws its own
+    (groups of one replica, as in the reference)."""
     ir = xl.gcg().ir
-    rg = replica_grouping or ir.replica_grouping()
-    rng = np.random.Generator(np.random.PCG64(seed))
-    data = rng.integers(0, 2 ** 32, size=(rg.num_groups, 2), dtype=np.uint64).astype(np.uint32)
-    if rg.num_groups == 1:
-        data = data[0]
+    rg = replica_grouping or ir.replica_grouping(group_size=1)
+    data = xl.create_seeds(seed, replicas=rg.num_groups)
     with ir.main_graph:
         var = xl.variable(data, xl.uint32, "seed", replica_grouping=rg)
     return var, var

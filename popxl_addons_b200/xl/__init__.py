@@ -18,3 +18,14 @@ from .ops.control import CallSiteInfo
 
 bool = bool_  # noqa: A001  (popxl exposes the boolean dtype under this name)
 Module = object
+
+
+def create_seeds(seed: int, offset: int = 0, batches_per_step: int = 1, replicas: int = 1):
+    """Seed pairs for `replicas` replicas (and `batches_per_step` host transfers): uint32 `(..., 2)`, distinct per
+    replica, a pure function of `(seed, offset)`. Counterpart of popxl.create_seeds as used by
+    popxl_addons/seed_variable.py:22."""
+    import numpy as _np
+
+    rng = _np.random.Generator(_np.random.PCG64([int(seed), int(offset)]))
+    shape = ((batches_per_step,) if batches_per_step > 1 else ()) + ((replicas,) if replicas > 1 else ()) + (2,)
+    return rng.integers(0, 2 ** 32, size=shape, dtype=_np.uint64).astype(_np.uint32)

@@ -1347,3 +1347,4 @@ def cross_entropy_with_grad(logits: Tensor, labels: Tensor, loss_grad=1.0, reduc
 from .decode import (rotary_kv_append_, attention_decode_packed, argmax_rows, advance_position_, store_row_,  # noqa: E402
                      kv_cache_fill_, timestamp, attention_decode_into_, add_layer_norm_,
                      all_reduce_add_layer_norm_)
+from .extra import *  # noqa: E402,F401,F403

@@ -195,3 +195,68 @@ def _vjp_tp_identity(ctx, op, gs):
 
 OpDef("tp_identity", impl=lambda a, **kw: a, vjp=_vjp_tp_identity, keeps_meta=True,
       infer=lambda op: [(op.inputs[0].shape, op.inputs[0].dtype, op.inputs[0].meta_shape)])
+
+
+# ---- all-reduce over the device slots of one replica ---------------------------------------------------------------
+
+
+def _slot_all_reduce_ref(*ts, op, identity, mode=None):
+    if identity:
+        return tuple(ts)
+    import torch
+
+    stacked = torch.stack([t.to(ts[0].device).float() for t in ts])
+    red = {"add": stacked.sum(0), "mean": stacked.mean(0), "max": stacked.amax(0), "min": stacked.amin(0),
+           "mul": stacked.prod(0)}[op]
+    return tuple(red.to(device=t.device, dtype=t.dtype) for t in ts)
+
+
+def _vjp_slot_all_reduce(ctx, op, gs):
+    a = op.attrs
+    if a["op"] not in ("add", "mean"):
+        raise NotImplementedError("Only add/mean all-reduce is differentiable")
+    from . import init
+
+    gs = [g if g is not None else init(o.shape, o.dtype, "zero_grad", "zero") for g, o in zip(gs, op.outputs)]
+    mode = a["mode"]
+    if mode == "identical_grad_inputs":  # forward all-reduce / backward identity
+        return list(gs)
+    back = "identical_grad_inputs" if mode == "identical_inputs" else "both"
+    return list(emit("slot_all_reduce", gs, dict(op=a["op"], mode=back, identity=False)))
+
+
+OpDef("slot_all_reduce", impl=_slot_all_reduce_ref, vjp=_vjp_slot_all_reduce,
+      infer=lambda op: [(t.shape, t.dtype, t.meta_shape) for t in op.inputs])
+
+
+def _slot_all_reduce(ts, operation, ipus, mode):
+    ts = list(ts)
+    if not ts:
+        raise ValueError("all_reduce needs at least one tensor")
+    if ipus is not None and len(list(ipus)) != len(ts):
+        raise ValueError("Number of specified IPUs does not equal number of input tensors")
+    if any(t.shape != ts[0].shape or t.dtype != ts[0].dtype for t in ts):
+        raise ValueError("all_reduce takes tensors of one shape and dtype")
+    if gcg().ir.devices_per_replica > 1:
+        raise NotImplementedError(
+            "With one process per device slot an all-reduce over the slots of a replica has no single launching "
+            "process: shard over replicas instead (a tensor-parallel ReplicaGrouping and `replicated_all_reduce`).")
+    return tuple(emit("slot_all_reduce", ts, dict(op=_norm_op(operation), mode=mode,
+                                                  identity=(mode == "identical_inputs"))))
+
+
+def all_reduce(ts, operation="add", ipus=None):
+    """All-reduce the tensors `ts`, one per device slot (`ipu(i)`) of a replica; returns the reduced value once per
+    input. The backward pass all-reduces the gradients."""
+    return _slot_all_reduce(ts, operation, ipus, "both")
+
+
+def all_reduce_identical_inputs(ts, operation="add", ipus=None):
+    """Identity in the forward pass (the inputs are known to be equal), all-reduce of the gradients in the backward
+    pass."""
+    return _slot_all_reduce(ts, operation, ipus, "identical_inputs")
+
+
+def all_reduce_identical_grad_inputs(ts, operation="add", ipus=None):
+    """All-reduce in the forward pass, identity in the backward pass (the gradients are known to be equal)."""
+    return _slot_all_reduce(ts, operation, ipus, "identical_grad_inputs")

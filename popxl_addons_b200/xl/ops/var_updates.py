@@ -128,6 +128,41 @@ def accumulator_scale_(t: Tensor, f: Scalar) -> Tensor:
     return emit1("accumulator_scale_", ins, attrs)
 
 
+def _acc_square_ref(t, X, *extra, **attrs):
+    if t.device.type == "meta":
+        return t
+    f = _unpack(extra, attrs)["f"]
+    xf = X.float()
+    return t.add_((xf * xf * (1.0 if f is None else f)).to(t.dtype))
+
+
+def _sparse_accumulate_ref(t, X, indices, *extra, axis, **attrs):
+    if t.device.type == "meta":
+        return t
+    f = _unpack(extra, attrs)["f"]
+    upd = (X.float() * (1.0 if f is None else f)).to(t.dtype)
+    return t.index_add_(axis, indices.long().reshape(-1), upd.reshape(*t.shape[:axis], -1, *t.shape[axis + 1:]))
+
+
+OpDef("accumulate_square_", impl=_acc_square_ref, inplace=True, keeps_meta=True)
+OpDef("sparse_accumulate_", impl=_sparse_accumulate_ref, inplace=True, keeps_meta=True)
+
+
+def accumulate_square_(t: Tensor, X: Tensor, f: Optional[Scalar] = None) -> Tensor:
+    """`t += f * X^2`."""
+    ins, attrs = _pack([t, X], f=f)
+    return emit1("accumulate_square_", ins, attrs)
+
+
+def sparse_accumulate_(t: Tensor, X: Tensor, indices: Tensor, axis: int = 0, f: Optional[Scalar] = None,
+                       W: Optional[Tensor] = None) -> Tensor:
+    """`t[indices] += f * X` along `axis`: the accumulator update for the gradient of a gather, touching only the
+    gathered rows (`W`, the tied weight the reference substrate uses to pick a layout, is accepted and ignored)."""
+    ins, attrs = _pack([t, X, indices], f=f)
+    attrs["axis"] = axis % t.rank
+    return emit1("sparse_accumulate_", ins, attrs)
+
+
 def copy_var_update_(t: Tensor, X: Tensor) -> Tensor:
     return emit1("copy_var_update_", [t, X])
 
@@ -176,6 +211,64 @@ def adam_updater(acc_first_order: Tensor, acc_second_order: Tensor, weight: Opti
     ins, attrs = _pack(ins, weight_decay=weight_decay, beta1=beta1, beta2=beta2, epsilon=epsilon)
     attrs.update(has_weight=weight is not None, has_step=time_step is not None)
     return emit1("adam_updater", ins, attrs)
+
+
+def _lamb_updater_ref(m, v, *rest, has_weight, has_step, **attrs):
+    # the LAMB direction is Adam's, without the learning rate: the trust ratio is applied by the caller
+    return _adam_updater_ref(m, v, *rest, has_weight=has_weight, has_step=has_step, **attrs)
+
+
+def _adamax_updater_ref(m, v, *rest, has_weight, has_step, **attrs):
+    rest = list(rest)
+    w = rest.pop(0) if has_weight else None
+    step = rest.pop(0) if has_step else None
+    if m.device.type == "meta":
+        return torch.empty(m.shape, dtype=torch.float32, device="meta")
+    s = _unpack(rest, attrs)
+    mf = m.float()
+    if step is not None:
+        step.add_(1)
+        mf = mf / (1.0 - s["beta1"] ** step.float())
+    upd = mf / (v.float() + s["epsilon"])
+    wd = s["weight_decay"]
+    if w is not None and wd is not None and not (isinstance(wd, float) and wd == 0.0):
+        upd = upd + w.float() * wd
+    return upd
+
+
+OpDef("lamb_updater", impl=_lamb_updater_ref, keeps_meta=True)
+OpDef("adamax_updater", impl=_adamax_updater_ref, keeps_meta=True)
+
+
+def lamb_updater(acc_first_order: Tensor, acc_second_order: Tensor, weight: Optional[Tensor] = None,
+                 time_step: Optional[Tensor] = None, weight_decay: Optional[Scalar] = None,
+                 beta1: Optional[Scalar] = None, beta2: Optional[Scalar] = None, epsilon: Scalar = 1e-07) -> Tensor:
+    """The LAMB update direction `m_hat / (sqrt(v_hat) + eps) + wd * w` (to be scaled by `lr * |w| / |direction|`)."""
+    if time_step is not None and (beta1 is None or beta2 is None):
+        raise ValueError("Bias correction requires both beta1 and beta2")
+    if weight_decay is not None and weight is None:
+        raise ValueError("Weight decay requires the weight tensor")
+    ins = [acc_first_order, acc_second_order] + ([weight] if weight is not None else []) + \
+        ([time_step] if time_step is not None else [])
+    ins, attrs = _pack(ins, weight_decay=weight_decay, beta1=beta1, beta2=beta2, epsilon=epsilon)
+    attrs.update(has_weight=weight is not None, has_step=time_step is not None)
+    return emit1("lamb_updater", ins, attrs)
+
+
+def adamax_updater(acc_first_order: Tensor, acc_second_order: Tensor, weight: Optional[Tensor] = None,
+                   time_step: Optional[Tensor] = None, weight_decay: Optional[Scalar] = None,
+                   beta1: Optional[Scalar] = None, epsilon: Scalar = 1e-07) -> Tensor:
+    """Adamax direction `m_hat / (u + eps) + wd * w`, with `u` the running infinity norm held in
+    `acc_second_order`; with `time_step` the counter is incremented and `m` bias-corrected."""
+    if time_step is not None and beta1 is None:
+        raise ValueError("Bias correction requires beta1")
+    if weight_decay is not None and weight is None:
+        raise ValueError("Weight decay requires the weight tensor")
+    ins = [acc_first_order, acc_second_order] + ([weight] if weight is not None else []) + \
+        ([time_step] if time_step is not None else [])
+    ins, attrs = _pack(ins, weight_decay=weight_decay, beta1=beta1, epsilon=epsilon)
+    attrs.update(has_weight=weight is not None, has_step=time_step is not None)
+    return emit1("adamax_updater", ins, attrs)
 
 
 def _adam_fused_ref(w, g, m, v, *rest, has_step, has_master, bias_correction, **attrs):
