@@ -34,6 +34,7 @@ class GroupContext:
 
     def check(self):
         code = int(self.err.item())
+        self.arena.check_guards()  # no-op unless the arena was built with canaries
         if code:
             self.err.zero_()
             names = {101: "a peer never consumed this rank's previous signal", 102: "a peer's signal never arrived",

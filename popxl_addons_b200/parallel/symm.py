@@ -19,6 +19,58 @@ PAD_WORDS = 8 * 1024          # uint32 signal slots at the start of the header
 LOCAL_SYNC_OFFSET = 48 * 1024  # byte offset of the kernels' local scratch words inside the header
 
 
+_GUARD_BYTES = 256
+_GUARD_PATTERN = 0xA5
+
+
+class BumpAllocator:
+    """Carves aligned tensors out of one byte buffer, in call order. With `guards`, a 256-byte canary block filled with
+    a fixed pattern follows every allocation; `check_guards()` reads them back on the host and names the allocation
+    whose canary was overwritten (a kernel wrote past the end of its buffer, on this rank or from a peer). Guards
+    change the offsets, so either every rank of a group uses them or none (`XL_DEBUG_CANARIES=1` in the environment
+    of all ranks)."""
+
+    def __init__(self, buf: torch.Tensor, start: int = 0, guards: bool = False):
+        if buf.dtype != torch.uint8 or buf.dim() != 1:
+            raise TypeError("BumpAllocator takes a flat uint8 buffer")
+        self.buf = buf
+        self.nbytes = buf.numel()
+        self.cursor = start
+        self.guards = guards
+        self.allocations: List[Tuple[int, int, tuple, torch.dtype]] = []  # (start, nbytes, shape, dtype)
+
+    def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        start = self.cursor
+        end = start + ((nbytes + _ALIGN - 1) // _ALIGN) * _ALIGN
+        if self.guards:
+            end += _GUARD_BYTES
+        if end > self.nbytes:
+            raise MemoryError(f"symmetric arena exhausted: need {end} bytes, have {self.nbytes}")
+        self.cursor = end
+        if self.guards:
+            self.buf[start + nbytes:end].fill_(_GUARD_PATTERN)  # alignment slack and the canary block
+            self.allocations.append((start, nbytes, tuple(shape), dtype))
+        return self.buf[start:start + nbytes].view(dtype).view(tuple(shape))
+
+    def check_guards(self) -> None:
+        """Raise if any canary differs from the pattern. Synchronises with the device the buffer lives on."""
+        if not self.guards:
+            return
+        for i, (start, nbytes, shape, dtype) in enumerate(self.allocations):
+            end = start + ((nbytes + _ALIGN - 1) // _ALIGN) * _ALIGN + _GUARD_BYTES
+            guard = self.buf[start + nbytes:end]
+            bad = (guard != _GUARD_PATTERN).nonzero()
+            if bad.numel():
+                first = int(bad[0])
+                raise RuntimeError(
+                    f"buffer overrun: allocation #{i} ({tuple(shape)}, {dtype}, {nbytes} bytes at offset {start}) was "
+                    f"written {first} byte(s) past its end ({int(bad.numel())} guard bytes changed)")
+
+
 class SymmArena:
     def __init__(self, nbytes: int, pg, device: torch.device, use_multicast: Optional[bool] = None):
         import torch.distributed as dist
@@ -42,23 +94,22 @@ class SymmArena:
         self.pads_dev = torch.tensor(self.base_ptrs, dtype=torch.int64, device=device)  # pad = start of each arena
         self.bases_dev = self.pads_dev
         self.local_sync = self.buf[LOCAL_SYNC_OFFSET:LOCAL_SYNC_OFFSET + 64].view(torch.int32)
-        self.cursor = _HEADER
+        self._bump = BumpAllocator(self.buf, _HEADER, guards=os.environ.get("XL_DEBUG_CANARIES") == "1")
         self.epoch = 0
         self._rings: Dict[Tuple, List[torch.Tensor]] = {}
         self._ring_pos: Dict[Tuple, int] = {}
 
     # -- allocation ----------------------------------------------------------------------------------------------
+    @property
+    def cursor(self) -> int:
+        return self._bump.cursor
+
     def alloc(self, shape, dtype: torch.dtype) -> torch.Tensor:
-        n = 1
-        for s in shape:
-            n *= int(s)
-        nbytes = n * torch.empty((), dtype=dtype).element_size()
-        start = self.cursor
-        end = start + ((nbytes + _ALIGN - 1) // _ALIGN) * _ALIGN
-        if end > self.nbytes:
-            raise MemoryError(f"symmetric arena exhausted: need {end} bytes, have {self.nbytes}")
-        self.cursor = end
-        return self.buf[start:start + nbytes].view(dtype).view(tuple(shape))
+        return self._bump.alloc(shape, dtype)
+
+    def check_guards(self) -> None:
+        """With `XL_DEBUG_CANARIES=1`: verify the canary after every tensor of the arena (host read; synchronises)."""
+        self._bump.check_guards()
 
     def ring(self, shape, dtype: torch.dtype, depth: int = 2) -> torch.Tensor:
         """Next buffer of a small ring of same-shaped arena tensors (outputs of fused collectives)."""

@@ -341,3 +341,28 @@ def test_run_to_run_determinism_check():
         assert "acc" in " ".join(check_run_to_run_determinism(s, {}))
     finally:
         OPS["random_normal"].impl = orig
+
+
+def test_bump_allocator_canaries_name_the_overrun_allocation():
+    import torch
+    from popxl_addons_b200.parallel.symm import BumpAllocator
+
+    plain = BumpAllocator(torch.zeros(1 << 16, dtype=torch.uint8), start=1024)
+    a = plain.alloc((100,), torch.float32)
+    b = plain.alloc((3, 5), torch.bfloat16)
+    assert b.data_ptr() - a.data_ptr() == 512  # 400 bytes round up to 512
+    plain.check_guards()
+    guarded = BumpAllocator(torch.zeros(1 << 16, dtype=torch.uint8), start=1024, guards=True)
+    a = guarded.alloc((100,), torch.float32)
+    b = guarded.alloc((3, 5), torch.bfloat16)
+    assert b.data_ptr() - a.data_ptr() == 512 + 256
+    a.fill_(1.0)
+    b.fill_(2.0)
+    guarded.check_guards()
+    # a write that runs 8 bytes over the end of `b`
+    flat = guarded.buf[b.data_ptr() - guarded.buf.data_ptr():][:30 + 8]
+    flat.fill_(0)
+    with pytest.raises(RuntimeError, match=r"allocation #1 .*8 guard bytes changed"):
+        guarded.check_guards()
+    with pytest.raises(MemoryError):
+        guarded.alloc((1 << 16,), torch.uint8)
