@@ -48,6 +48,32 @@ def test_strided_collectives(stride, size, rf, op):
         np.testing.assert_allclose(out[s_ag][r], flat, rtol=1e-5)
 
 
+def test_two_stage_reduction_equals_one_all_reduce():
+    """Reduce-scatter inside a group of consecutive replicas (one node), all-reduce of the shards across the groups,
+    all-gather inside the group: the sum over all replicas, with only 1/group_size of the data crossing groups
+    (the reference's tests/integration/test_distributed_collectives.py:56-69 builds the same chain)."""
+    from popxl_addons_b200.ops.replicated_strided_collectives import (replicated_all_gather_strided,
+                                                                     replicated_all_reduce_strided,
+                                                                     replicated_reduce_scatter_strided)
+
+    rf, local = 8, 4
+    data = np.random.RandomState(5).rand(rf, 5, 7).astype(np.float32)  # 35 elements: not a multiple of the group size
+    ir = popxl.Ir(replication=rf)
+    with ir.main_graph:
+        h2d = popxl.h2d_stream((5, 7), popxl.float32)
+        x = ops.host_load(h2d)
+        inside = ir.replica_grouping(stride=1, group_size=local)
+        across = inside.transpose()
+        assert (across.stride, across.group_size) == (local, rf // local)
+        shard = replicated_reduce_scatter_strided(x, "add", inside)
+        assert shard.shape == (9,)
+        shard = replicated_all_reduce_strided(shard, "add", across)
+        full = replicated_all_gather_strided(shard, inside)
+        st = addons.host_store(ops.reshape(full[:35], (5, 7)))
+    out = _run(ir, {h2d: data})
+    np.testing.assert_allclose(out[st], np.tile(data.sum(0), (rf, 1, 1)), rtol=1e-5)
+
+
 def test_tensor_parallel_all_reduce_pairs_and_pattern():
     from popxl_addons_b200.ops.replicated_all_reduce_TP import (replicated_all_reduce_identical_grad_inputs,
                                                               replicated_all_reduce_identical_inputs)
