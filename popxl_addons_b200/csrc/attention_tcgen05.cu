@@ -1,0 +1,531 @@
+// Causal softmax attention forward in one kernel on the 5th-generation tensor cores (tcgen05) for sm_100a.
+//
+//   O = softmax(scale * Q K^T + causal mask) V        per (batch, head); Q, K, V: (S x D) 16-bit, D in {64, 128, 256}
+//
+// Q, K and V are column windows of one packed row-major matrix (rows = batch * S tokens), as the fused qkv projection
+// leaves them; O is a column window of the (tokens x heads*D) output matrix. The S x S score matrix never leaves the
+// chip: one CTA owns 128 query rows and walks the key / value rows in blocks of BKV.
+//
+//   warp 0      TMA producer : Q tile once, then K / V blocks into a 2-stage shared-memory ring
+//   warp 1      MMA issuer   : S_j = Q K_j^T into one of two TMEM score buffers, then O += P_j V_j into the TMEM output
+//                              accumulator (S_{j+1} is issued before P_j is awaited, so it overlaps the softmax of block j)
+//   warps 2..5  softmax      : one thread per query row. tcgen05.ld the score row, running max / sum (base-2 exponent),
+//                              rescale the output accumulator in TMEM when the running max moved (tcgen05.ld / st),
+//                              write P_j as a 128-byte-swizzled 16-bit tile to shared memory for the second MMA,
+//                              finally O / l to global memory and the log-sum-exp of every row.
+//
+// TMEM columns: [0, D) output accumulator, [D, D + 2*BKV) two score buffers; 512 columns are allocated, one CTA per SM.
+// Every wait on an mbarrier is bounded: when a wait gives up the kernel records a code in `*err`, raises a CTA-wide abort
+// flag, all roles leave their loops, TMEM is released and the kernel returns normally.
+#include "common.cuh"
+
+#include <cuda.h>
+
+namespace {
+
+constexpr int BLOCK_Q = 128;
+constexpr int UMMA_K = 16;
+constexpr int KV_STAGES = 2;
+constexpr int NUM_SOFTMAX_WARPS = 4;
+constexpr int NUM_THREADS = 64 + 32 * NUM_SOFTMAX_WARPS;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr uint32_t TMEM_COLS = 512;
+
+enum { ERR_Q_WAIT = 11, ERR_KV_FULL_WAIT = 12, ERR_KV_EMPTY_WAIT = 13, ERR_S_FULL_WAIT = 14, ERR_S_EMPTY_WAIT = 15,
+       ERR_P_FULL_WAIT = 16, ERR_PV_DONE_WAIT = 17 };
+
+struct AttnParams {
+  int B, S, H, D;
+  int q_col, k_col, v_col;  // first column of head 0 of Q / K / V in the packed matrix
+  void* out;                // (B*S x ldo) 16-bit; head h occupies columns [h*D, (h+1)*D)
+  long long ldo;
+  float* lse;               // (B, H, S) fp32: log-sum-exp of the scaled scores of every row (natural log)
+  float scale;
+  int causal;
+  int is_fp16;
+  int* err;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait for the completion with the given parity. False (and the abort flag raised) if it did not come in time
+// or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+  for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  if (err) atomicCAS(err, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// writes to shared memory by ordinary stores become visible to the tensor core's (async proxy) reads
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// Shared-memory matrix descriptor for a 128-byte-swizzled tile (version 1 = Blackwell, layout type 2 = SWIZZLE_128B).
+//   K-major : rows of 128 bytes, groups of 8 rows every 1024 bytes           -> SBO = 1024, LBO unused (16)
+//   MN-major: 64-element (128 B) column blocks `lbo_bytes` apart, K groups of 8 rows -> SBO = 1024, LBO = lbo_bytes
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)(1024u >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+template <int D, int BKV>
+struct AttnSmem {
+  static constexpr int Q_BYTES = BLOCK_Q * D * 2;       // D/64 k-blocks of (128 rows x 128 B)
+  static constexpr int K_BYTES = BKV * D * 2;           // D/64 k-blocks of (BKV rows x 128 B)
+  static constexpr int V_BYTES = BKV * D * 2;           // BKV/64 k-blocks of D/64 boxes of (64 rows x 128 B)
+  static constexpr int P_BYTES = BLOCK_Q * BKV * 2;     // BKV/64 k-blocks of (128 rows x 128 B)
+  static constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
+  static constexpr int TILE_BYTES = Q_BYTES + KV_STAGES * STAGE_BYTES + P_BYTES;
+  static constexpr int NEEDED = TILE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  // more than half of an SM's shared memory, so that two CTAs (each holding all 512 TMEM columns) never share an SM
+  static constexpr int TOTAL = NEEDED > 120 * 1024 ? NEEDED : 120 * 1024;
+};
+
+template <int D, int BKV>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    attn_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+  using L = AttnSmem<D, BKV>;
+  static_assert(D % 64 == 0 && D <= 256 && BKV % 64 == 0 && D + 2 * BKV <= (int)TMEM_COLS, "unsupported tile");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sKV = smem + L::Q_BYTES;
+  uint8_t* sP = sKV + KV_STAGES * L::STAGE_BYTES;
+  uint64_t* bars = (uint64_t*)(smem + L::TILE_BYTES);
+  uint64_t* q_full = bars;                 // [1]
+  uint64_t* kv_full = bars + 1;            // [KV_STAGES]
+  uint64_t* kv_empty = bars + 3;           // [KV_STAGES]
+  uint64_t* s_full = bars + 5;             // [2]
+  uint64_t* s_empty = bars + 7;            // [2]
+  uint64_t* p_full = bars + 9;             // [1]
+  uint64_t* pv_done = bars + 10;           // [1]
+  uint32_t* tmem_base_slot = (uint32_t*)(bars + 11);
+  volatile int* abort_flag = (volatile int*)(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_qblocks = (p.S + BLOCK_Q - 1) / BLOCK_Q;
+  const int qb = n_qblocks - 1 - (int)blockIdx.x;  // the blocks with the most keys start first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qb * BLOCK_Q;
+  const int kv_end = p.causal ? min(p.S, q0 + BLOCK_Q) : p.S;  // keys [0, kv_end) can be attended by this block
+  const int n_kv = (kv_end + BKV - 1) / BKV;
+  const int row0 = b * p.S;  // first token row of this batch entry in the packed matrix
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&s_empty[s], NUM_SOFTMAX_WARPS);
+    }
+    mbar_init(p_full, NUM_SOFTMAX_WARPS);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  const uint32_t tmem_o = tmem_base;          // columns [0, D)
+  const uint32_t tmem_s = tmem_base + D;      // two buffers of BKV columns
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer ------------------------------------------------
+    if (elect_one()) {
+      mbar_expect_tx(q_full, L::Q_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < D / 64; ++kb)  // boxes {64 features, 128 rows}
+        tma_load_2d(sQ + kb * (BLOCK_Q * 128), &map_q, q_full, p.q_col + h * D + kb * 64, row0 + q0);
+      bool ok = true;
+      int issued = 0;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int stage = j % KV_STAGES;
+        if (j >= KV_STAGES) {
+          ok = mbar_wait(&kv_empty[stage], (uint32_t)(j / KV_STAGES - 1) & 1u, abort_flag, p.err, ERR_KV_EMPTY_WAIT);
+          if (!ok) break;
+        }
+        uint8_t* sK = sKV + stage * L::STAGE_BYTES;
+        uint8_t* sV = sK + L::K_BYTES;
+        mbar_expect_tx(&kv_full[stage], L::STAGE_BYTES);
+        const int k0 = row0 + j * BKV;
+#pragma unroll
+        for (int kb = 0; kb < D / 64; ++kb)  // boxes {64 features, BKV rows}
+          tma_load_2d(sK + kb * (BKV * 128), &map_k, &kv_full[stage], p.k_col + h * D + kb * 64, k0);
+#pragma unroll
+        for (int kk = 0; kk < BKV / 64; ++kk)
+#pragma unroll
+          for (int jn = 0; jn < D / 64; ++jn)  // boxes {64 features, 64 rows}
+            tma_load_2d(sV + (kk * (D / 64) + jn) * 8192, &map_v, &kv_full[stage], p.v_col + h * D + jn * 64,
+                        k0 + kk * 64);
+        issued = j + 1;
+      }
+      if (!ok || *abort_flag) {
+        // loads in flight target this CTA's shared memory: give them a bounded time to land before the CTA ends
+        for (uint32_t i = 0; i < SPIN_LIMIT && !mbar_try_wait(q_full, 0); ++i) {}
+        for (int j = max(0, issued - KV_STAGES); j < issued; ++j)
+          for (uint32_t i = 0; i < SPIN_LIMIT && !mbar_try_wait(&kv_full[j % KV_STAGES], (uint32_t)(j / KV_STAGES) & 1u); ++i) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer --------------------------------------------------
+    if (elect_one()) {
+      const uint32_t fmt = p.is_fp16 ? 0u : 1u;
+      // S = Q K^T: both operands K-major, N = BKV.   O += P V: P K-major, V MN-major (bit 16), N = D.
+      const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BKV >> 3) << 17) |
+                               ((uint32_t)(BLOCK_Q >> 4) << 24);
+      const uint32_t idesc_o = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) |
+                               ((uint32_t)(BLOCK_Q >> 4) << 24);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.err, ERR_Q_WAIT);
+      auto issue_scores = [&](int j) -> bool {
+        const int stage = j % KV_STAGES, sb = j & 1;
+        if (!mbar_wait(&kv_full[stage], (uint32_t)(j / KV_STAGES) & 1u, abort_flag, p.err, ERR_KV_FULL_WAIT)) return false;
+        if (j >= 2 && !mbar_wait(&s_empty[sb], (uint32_t)(j / 2 - 1) & 1u, abort_flag, p.err, ERR_S_EMPTY_WAIT))
+          return false;
+        tcgen05_fence_after();
+        const uint32_t q_addr = smem_u32(sQ);
+        const uint32_t k_addr = smem_u32(sKV + stage * L::STAGE_BYTES);
+#pragma unroll
+        for (int kb = 0; kb < D / 64; ++kb)
+#pragma unroll
+          for (int k = 0; k < 64 / UMMA_K; ++k) {
+            const uint64_t da = make_smem_desc(q_addr + kb * (BLOCK_Q * 128) + k * (UMMA_K * 2), 16);
+            const uint64_t db = make_smem_desc(k_addr + kb * (BKV * 128) + k * (UMMA_K * 2), 16);
+            tcgen05_mma_f16(tmem_s + sb * BKV, da, db, idesc_s, (kb | k) ? 1u : 0u);
+          }
+        tcgen05_commit(&s_full[sb]);
+        return true;
+      };
+      if (ok && n_kv > 0) ok = issue_scores(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) {
+          ok = issue_scores(j + 1);
+          if (!ok) break;
+        }
+        ok = mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, p.err, ERR_P_FULL_WAIT);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const int stage = j % KV_STAGES;
+        const uint32_t p_addr = smem_u32(sP);
+        const uint32_t v_addr = smem_u32(sKV + stage * L::STAGE_BYTES + L::K_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < BKV / 64; ++kk)
+#pragma unroll
+          for (int k = 0; k < 64 / UMMA_K; ++k) {
+            const uint64_t da = make_smem_desc(p_addr + kk * (BLOCK_Q * 128) + k * (UMMA_K * 2), 16);
+            const uint64_t db = make_smem_desc(v_addr + kk * (D / 64) * 8192 + k * (UMMA_K * 128), 8192);
+            tcgen05_mma_f16(tmem_o, da, db, idesc_o, (j | kk | k) ? 1u : 0u);
+          }
+        tcgen05_commit(&kv_empty[stage]);  // K / V stage free once these MMAs have read it
+        tcgen05_commit(pv_done);           // output accumulator and the P tile are free again
+      }
+    }
+  } else {
+    // ------------------------------------------------ softmax -----------------------------------------------------
+    const int qtr = warp & 3;  // TMEM lane quarter this warp may access
+    const int r = qtr * 32 + lane;  // query row inside the block
+    const int qrow = q0 + r;        // query position inside the sequence
+    const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
+    const float c = p.scale * 1.4426950408889634f;  // scores are exponentiated in base 2
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int sb = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (uint32_t)(j / 2) & 1u, abort_flag, p.err, ERR_S_FULL_WAIT));
+      if (!ok) break;
+      tcgen05_fence_after();
+      float s[BKV];
+#pragma unroll
+      for (int ch = 0; ch < BKV / 32; ++ch) {
+        uint32_t raw[32];
+        tmem_ld_32x32b_x32(tmem_s + lane_base + sb * BKV + ch * 32, raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[ch * 32 + i] = __uint_as_float(raw[i]);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[sb]);  // the score buffer may be overwritten
+      const int col0 = j * BKV;
+      const int limit = p.causal ? min(qrow, p.S - 1) : p.S - 1;  // last key this row may attend
+      float m_blk = -INFINITY;
+      if (col0 + BKV - 1 > limit) {
+#pragma unroll
+        for (int i = 0; i < BKV; ++i)
+          if (col0 + i > limit) s[i] = -INFINITY;
+      }
+#pragma unroll
+      for (int i = 0; i < BKV; ++i) m_blk = fmaxf(m_blk, s[i]);
+      const float m_new = fmaxf(m, m_blk);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row with no admissible key yet keeps p = 0
+      const float alpha = m == -INFINITY ? 0.f : exp2f((m - m_use) * c);
+      float sum = 0.f;
+      const float mc = m_use * c;
+#pragma unroll
+      for (int i = 0; i < BKV; ++i) {
+        s[i] = exp2f(fmaf(s[i], c, -mc));
+        sum += s[i];
+      }
+      l = l * alpha + sum;
+      m = m_new;
+      if (j > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (uint32_t)(j - 1) & 1u, abort_flag, p.err, ERR_PV_DONE_WAIT));
+        if (!ok) break;
+        tcgen05_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+          for (int ch = 0; ch < D / 32; ++ch) {
+            uint32_t raw[32];
+            tmem_ld_32x32b_x32(tmem_o + lane_base + ch * 32, raw);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * alpha);
+            tmem_st_32x32b_x32(tmem_o + lane_base + ch * 32, raw);
+          }
+          tmem_st_wait();
+        }
+      }
+      // P_j -> shared memory, 16-bit, 128-byte swizzle (16-byte chunk index xor row mod 8), one 64-key k-block per 16 KB
+#pragma unroll
+      for (int ch = 0; ch < BKV / 8; ++ch) {
+        uint4 o;
+        uint16_t* oe = (uint16_t*)&o;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float v = s[ch * 8 + e];
+          oe[e] = p.is_fp16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+        }
+        *(uint4*)(sP + (ch >> 3) * (BLOCK_Q * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = o;
+      }
+      fence_proxy_async_smem();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    // ---- epilogue: O / l -> global memory, log-sum-exp ---------------------------------------------------------------
+    if (ok && n_kv > 0)
+      ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (uint32_t)(n_kv - 1) & 1u, abort_flag, p.err, ERR_PV_DONE_WAIT));
+    if (ok && n_kv > 0) {
+      tcgen05_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const bool row_ok = qrow < p.S;
+      uint16_t* orow = (uint16_t*)p.out + (long long)(row0 + qrow) * p.ldo + h * D;
+#pragma unroll 1
+      for (int ch = 0; ch < D / 32; ++ch) {
+        uint32_t raw[32];
+        tmem_ld_32x32b_x32(tmem_o + lane_base + ch * 32, raw);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            uint16_t* oe = (uint16_t*)&o;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float v = __uint_as_float(raw[g * 8 + e]) * inv;
+              oe[e] = p.is_fp16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+            }
+            *(uint4*)(orow + ch * 32 + g * 8) = o;
+          }
+        }
+      }
+      if (row_ok && p.lse)
+        p.lse[((long long)b * p.H + h) * p.S + qrow] = l > 0.f ? m * p.scale + logf(l) : -INFINITY;
+    }
+  }
+
+  // ---- teardown: every role arrives here, also after an abort --------------------------------------------------------
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = (EncodeTiledFn)ptr;
+  return fn;
+}
+
+// 2-D map over the packed row-major matrix (rows x cols, leading dimension ld elements), boxes of {64, box_rows}
+int make_map(CUtensorMap* map, const void* ptr, int is_fp16, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, is_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)ptr, dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+template <int D, int BKV>
+int launch(const void* qkv, long long rows, long long cols, long long ld, const AttnParams& p, cudaStream_t s) {
+  using L = AttnSmem<D, BKV>;
+  CUtensorMap mq, mk, mv;
+  int r = make_map(&mq, qkv, p.is_fp16, rows, cols, ld, BLOCK_Q);
+  if (r) return r;
+  r = make_map(&mk, qkv, p.is_fp16, rows, cols, ld, BKV);
+  if (r) return r;
+  r = make_map(&mv, qkv, p.is_fp16, rows, cols, ld, 64);
+  if (r) return r;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_tcgen05_kernel<D, BKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         L::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((p.S + BLOCK_Q - 1) / BLOCK_Q, p.H, p.B);
+  attn_fwd_tcgen05_kernel<D, BKV><<<grid, NUM_THREADS, L::TOTAL, s>>>(mq, mk, mv, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// Causal (or full) softmax attention forward over a packed projection matrix.
+//   qkv: (B*S x cols) row-major 16-bit matrix with leading dimension ld (elements); head h of Q / K / V occupies columns
+//        [x_col + h*D, x_col + (h+1)*D) for x in {q, k, v}. All column offsets and ld must be multiples of 8.
+//   out: (B*S x ldo) 16-bit, head h in columns [h*D, (h+1)*D); ldo a multiple of 8, out 16-byte aligned.
+//   lse: (B, H, S) fp32, may be null.      D in {64, 128, 256}.
+//   err: device int that receives a non-zero code if a bounded wait inside the kernel gave up (may be null).
+// Returns 0, a CUDA error code, or a negative value when the arguments are not supported by this kernel.
+XL_API int xl_attn_fwd_tcgen05(const void* qkv, long long ld, long long cols, void* out, long long ldo, float* lse, int B,
+                               int S, int H, int D, int q_col, int k_col, int v_col, float scale, int causal,
+                               int is_fp16, int* err, cudaStream_t s) {
+  if (B <= 0 || S <= 0 || H <= 0 || B > 65535 || H > 65535) return -1;
+  if ((((uintptr_t)qkv) & 15) || (((uintptr_t)out) & 15) || (ld % 8) || (ldo % 8)) return -1;
+  if ((q_col % 8) || (k_col % 8) || (v_col % 8) || q_col < 0 || k_col < 0 || v_col < 0) return -1;
+  const long long need = (long long)H * D;
+  if (q_col + need > cols || k_col + need > cols || v_col + need > cols || cols > ld || ldo < need) return -1;
+  if (!(scale > 0.f)) return -1;
+  AttnParams p;
+  p.B = B; p.S = S; p.H = H; p.D = D;
+  p.q_col = q_col; p.k_col = k_col; p.v_col = v_col;
+  p.out = out; p.ldo = ldo; p.lse = lse; p.scale = scale; p.causal = causal ? 1 : 0; p.is_fp16 = is_fp16 ? 1 : 0;
+  p.err = err;
+  const long long rows = (long long)B * S;
+  if (D == 256) return launch<256, 64>(qkv, rows, cols, ld, p, s);
+  if (D == 128) return launch<128, 128>(qkv, rows, cols, ld, p, s);
+  if (D == 64) return launch<64, 128>(qkv, rows, cols, ld, p, s);
+  return -1;
+}

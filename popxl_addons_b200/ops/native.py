@@ -66,6 +66,8 @@ _rotary = _sig("xl_rotary", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_in
                _c_ll, _c_ll, _c_ll, _c_ll, _c_ll, _c_p)
 _gq = _sig("xl_gq_decompress", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p)
 _sm_fwd = _sig("xl_attn_softmax_fwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p)
+_attn_flash = _sig("xl_attn_fwd_tcgen05", _c_p, _c_ll, _c_ll, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                   _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p)
 _sm_bwd = _sig("xl_attn_softmax_bwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p)
 _ce = _sig("xl_ce_fwd_bwd", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p, _c_f, _c_int, _c_p)
 _gemm = _sig("xl_gemm_tcgen05", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll,
@@ -178,7 +180,11 @@ def check_gemm_errors():
         if code != 0:
             flag.zero_()
             names = {1: "operand tiles never arrived (TMA)", 2: "shared-memory stage was never released",
-                     3: "accumulator never completed", 4: "accumulator buffer was never drained"}
+                     3: "accumulator never completed", 4: "accumulator buffer was never drained",
+                     11: "attention: query tile never arrived", 12: "attention: key / value block never arrived",
+                     13: "attention: key / value stage was never released", 14: "attention: scores never completed",
+                     15: "attention: score buffer was never drained", 16: "attention: probabilities never arrived",
+                     17: "attention: output accumulation never completed"}
             raise RuntimeError(f"tcgen05 GEMM on cuda:{idx} gave up waiting: {names.get(code, code)}")
 
 
@@ -672,6 +678,27 @@ def _heads_view(mat, col0, B, S, H, D):
 
 # the masked half of causal attention products is not computed (XL_CAUSAL_SKIP=0 computes the full products)
 _CAUSAL_SKIP = os.environ.get("XL_CAUSAL_SKIP", "1") != "0"
+# XL_FLASH_ATTENTION=1: the forward pass of `attention_qkv` runs as one kernel that keeps the scores on chip
+_FLASH_ATTENTION = os.environ.get("XL_FLASH_ATTENTION", "0") == "1"
+
+
+def flash_attention_fwd(packed, q_col, k_col, v_col, B, S, H, D, scale, causal, out=None):
+    """softmax(scale * Q K^T [+ causal mask]) V for the heads stored as column windows of `packed (B*S, cols)`; one
+    tcgen05 kernel, scores never leave the chip. Returns `(out (B*S, H*D), lse (B, H, S))` or NotImplemented."""
+    if packed.dtype not in (torch.bfloat16, torch.float16) or not packed.is_cuda or packed.dim() != 2 \
+            or packed.stride(1) != 1 or D not in (64, 128, 256) or packed.shape[0] != B * S:
+        return NotImplemented
+    if out is None:
+        out = torch.empty((B * S, H * D), dtype=packed.dtype, device=packed.device)
+    lse = torch.empty((B, H, S), dtype=torch.float32, device=packed.device)
+    rc = _attn_flash(packed.data_ptr(), packed.stride(0), packed.shape[1], out.data_ptr(), out.stride(0), lse.data_ptr(),
+                     B, S, H, D, q_col, k_col, v_col, float(scale), int(bool(causal)),
+                     int(packed.dtype == torch.float16), gemm_error_flag(packed.device).data_ptr(), _stream())
+    if rc < 0:
+        return NotImplemented
+    _check(rc, "attn_fwd_tcgen05")
+    _count("attn_fwd_tcgen05")
+    return out, lse
 
 
 @native("attention_qkv")
@@ -688,6 +715,10 @@ def attention_qkv_cuda(qkv, sin, cos, seq_len, n_heads, head_dim, rotary_dim, ca
             return NotImplemented
         rotary_launch(q, sin, cos, q, rotary_dim, False)
         rotary_launch(k, sin, cos, k, rotary_dim, False)
+    if _FLASH_ATTENTION:
+        res = flash_attention_fwd(rot, 0, hd, 2 * hd, B, S, H, D, scale, causal)
+        if res is not NotImplemented:
+            return res[0], rot, res[1]
     out = torch.empty((T, hd), dtype=qkv.dtype, device=qkv.device)
     o = _heads_view(out, 0, B, S, H, D)
     lse = torch.empty((B, H, S), dtype=torch.float32, device=qkv.device)

@@ -1,6 +1,7 @@
 """Every CUDA kernel against the plain-PyTorch fp32 reference of the same op (the op's own reference implementation,
 evaluated in fp32 on the same inputs)."""
 import math
+import os
 
 import numpy as np
 import pytest
@@ -270,6 +271,30 @@ def test_attention_forward_backward(nat):
     for got, ref in ((dq, rdq), (dk, rdk), (dv, rdv)):
         torch.testing.assert_close(got.float(), ref, rtol=5e-2, atol=5e-2)
     nat.check_gemm_errors()
+
+
+@pytest.mark.skipif(os.environ.get("XL_FLASH_ATTENTION") != "1",
+                    reason="the single-kernel attention forward is opt-in (XL_FLASH_ATTENTION=1)")
+@pytest.mark.parametrize("B,S,H,D,causal,dtype", [(2, 256, 2, 64, True, torch.bfloat16), (1, 384, 2, 128, True, torch.float16),
+                                                  (1, 512, 1, 256, True, torch.bfloat16), (1, 300, 2, 64, False, torch.bfloat16),
+                                                  (2, 200, 1, 256, True, torch.bfloat16)])
+def test_single_kernel_attention_forward(nat, B, S, H, D, causal, dtype):
+    """Heads as column windows of a packed (tokens, 3*H*D) matrix; output and log-sum-exp against fp32 PyTorch."""
+    torch.manual_seed(21)
+    hd = H * D
+    qkv = (torch.randn(B * S, 3 * hd, device="cuda") * 0.7).to(dtype)
+    scale = 1.0 / math.sqrt(D)
+    res = nat.flash_attention_fwd(qkv, 0, hd, 2 * hd, B, S, H, D, scale, causal)
+    assert res is not NotImplemented
+    out, lse = res
+    nat.check_gemm_errors()
+    q, k, v = (qkv[:, i * hd:(i + 1) * hd].float().reshape(B, S, H, D).transpose(1, 2) for i in range(3))
+    s = q @ k.transpose(-1, -2) * scale
+    if causal:
+        s = s.masked_fill(~torch.ones(S, S, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+    want = (torch.softmax(s, -1) @ v).transpose(1, 2).reshape(B * S, hd)
+    torch.testing.assert_close(out.float(), want, rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(lse, torch.logsumexp(s, -1), rtol=1e-3, atol=1e-2)
 
 
 def test_bounded_wait_on_a_peer_gives_up_and_reports(nat):
