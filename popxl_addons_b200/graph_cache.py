@@ -19,12 +19,14 @@ def tensor_hash(t) -> int:
 
 
 def argument_hash(arg: Any) -> int:
-    from .graph import BoundGraph
+    from .graph import BoundGraph, GraphWithNamedArgs
 
     if isinstance(arg, (xl.Tensor, xl.TensorSpec)):
         return tensor_hash(arg)
     if isinstance(arg, BoundGraph):
         return hash((id(arg.graph), tuple(sorted((a.uid, b.uid) for a, b in arg.args.items()))))
+    if isinstance(arg, GraphWithNamedArgs):
+        return hash(id(arg.graph))
     if isinstance(arg, Mapping):
         return hash(tuple((argument_hash(k), argument_hash(v)) for k, v in arg.items()))
     if isinstance(arg, (list, tuple)):
@@ -46,7 +48,12 @@ def get_function_hash(fn: Callable, *args, **kwargs) -> int:
     """Hash of (function identity, placement context, hash of every bound argument)."""
     from .xl.core import current_device, current_tile_set
 
-    parts = [id(fn) if not inspect.isroutine(fn) else hash(fn), current_device(), current_tile_set()]
+    # the callable's own hash: two module instances that define equal `__hash__` (same configuration) share graphs
+    try:
+        fn_hash = hash(fn)
+    except TypeError:
+        fn_hash = id(fn)
+    parts = [fn_hash, current_device(), current_tile_set()]
     for name, value in bound_arguments(fn, *args, **kwargs).items():
         parts.append((name, argument_hash(value)))
     return hash(tuple(parts))

@@ -326,7 +326,8 @@ class Module(metaclass=NameScopeMeta):
             fwd_graph, grads_provided, grads_required)
         ir = fwd_graph.graph.ir
         self.aux = fwd_graph.aux.copy() if fwd_graph.aux is not None else _Aux()
-        self.var_grad = _VarGrads(required_vars)
+        # any variable of the forward graph may be given a gradient; only the required ones become outputs
+        self.var_grad = _VarGrads(OrderedDict(fwd_graph.args.to_dict()))
         with _building(_BUILD_GRAD_STACK, self):
             grad_graph = ir.create_graph(self.build_grad, *[t.spec for t in provided])
         grad_graph.name = fwd_graph.graph.name.split("_subgraph")[0] + "_grad" + grad_graph.name[

@@ -70,25 +70,45 @@ def route_tensor_into_graph(t: xl.Tensor, graph: Optional[xl.Graph] = None, modi
         raise ValueError(f"{t} is not in the graph {src.name}")
     paths = called_graph_paths(src, graph)
     if not paths:
-        raise ValueError(f"{t} is not in a known parent graph of {graph.name}: "
-                         f"{src.name} does not (transitively) call it")
+        raise ValueError(f"{t} is not in the graph {graph.name}. Additionally, the tensor is not in a known parent "
+                         f"graph so cannot be moved into the graph ({src.name} does not, transitively, call it).")
     routed: Dict[xl.Graph, xl.Tensor] = {src: t}
 
-    def input_of(g: xl.Graph) -> xl.Tensor:
-        if g not in routed:
-            with g:
-                routed[g] = xl.graph_input(t.shape, t.dtype, t.name.split("/")[-1], by_ref=modified,
-                                           meta_shape=t.meta_shape)
-        return routed[g]
+    def already_passed(caller: xl.Graph, callee: xl.Graph) -> Optional[xl.Tensor]:
+        """The input of `callee` that every call site in `caller` already feeds with the routed tensor, if any."""
+        sites = [op for op in caller.ops if _called(op) is callee]
+        index = None
+        for op in sites:
+            hits = [i for i, x in enumerate(op.inputs[:len(callee._inputs)]) if x is routed[caller]]
+            if not hits or (index is not None and hits[0] != index):
+                return None
+            index = hits[0]
+        return callee._inputs[index] if index is not None else None
+
+    def input_of(caller: xl.Graph, callee: xl.Graph) -> xl.Tensor:
+        if callee not in routed:
+            existing = already_passed(caller, callee)
+            if existing is not None:
+                routed[callee] = existing
+                if modified:
+                    callee._by_ref.add(existing)
+                    for op in caller.ops:
+                        if _called(op) is callee:
+                            op.attrs.setdefault("modified", set()).add(routed[caller])
+            else:
+                with callee:
+                    routed[callee] = xl.graph_input(t.shape, t.dtype, t.name.split("/")[-1], by_ref=modified,
+                                                    meta_shape=t.meta_shape)
+        return routed[callee]
 
     wired: Set[int] = set()
     for chain in paths:
         caller = src
         for callee in chain:
-            new_in = input_of(callee)
+            input_of(caller, callee)
             for op in caller.ops:
                 if _called(op) is callee and op.uid not in wired:
-                    # inputs are positional: the new graph input was appended last, so append the caller's tensor
+                    # inputs are positional: a new graph input was appended last, so append the caller's tensor
                     if len(op.inputs) < len(callee._inputs):
                         _add_call_input(op, routed[caller], modified)
                     wired.add(op.uid)

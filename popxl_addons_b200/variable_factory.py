@@ -73,7 +73,10 @@ class VariableFactory:
         """`data_iter` is either a callable returning one array per call, or an iterable of arrays. A callable is
         invoked once immediately (to fail early and to learn the shape)."""
         if callable(data_iter):
-            first = data_iter()
+            try:
+                first = data_iter()
+            except Exception as e:
+                raise ValueError("Passed callable via `data_iter` throws error.") from e
             if not isinstance(first, (np.ndarray, np.generic, xl.LazyInit)) and not hasattr(first, "shape"):
                 raise ValueError("`data_iter` must return an array. "
                                  f"Got {type(first)} from {getattr(data_iter, '__name__', data_iter)}")

@@ -517,7 +517,7 @@ class Op:
     """One recorded operation: `outputs = opdef(inputs, **attrs)`."""
 
     __slots__ = ("opdef", "inputs", "outputs", "attrs", "graph", "name", "device_index", "device_explicit", "tile_set", "stage",
-                 "debug", "uid", "attrs_hint", "__weakref__")
+                 "debug", "uid", "id", "attrs_hint", "__weakref__")
     _counter = itertools.count()
 
     def __init__(self, opdef, inputs, attrs, graph):
@@ -540,6 +540,7 @@ class Op:
         self.debug = None
         self.attrs_hint = None
         self.uid = next(Op._counter)
+        self.id = graph.ir._next_op_id() if graph is not None else self.uid  # per Ir, from 100, in creation order
 
     @property
     def op_type(self) -> str:
@@ -600,6 +601,10 @@ class Graph:
     @property
     def variables(self) -> Tuple[Variable, ...]:
         return tuple(t for t in self._tensors if isinstance(t, Variable))
+
+    @property
+    def _pb_graph(self) -> "_PbGraph":
+        return _PbGraph(self)
 
     @property
     def constants(self) -> Tuple[Constant, ...]:
@@ -717,6 +722,119 @@ class Options:
         return {f.name for f in dataclasses.fields(self)} - {"hints"}
 
 
+_PB_TYPE_NAMES = {"matmul": "MatMul", "add": "Add", "sub": "Sub", "mul": "Mul", "div": "Div",
+                  "group_norm": "GroupNormalization", "call": "Call", "repeat": "Loop", "host_load": "HostLoad",
+                  "host_store": "HostStore", "ipu_copy": "IpuCopy", "remote_load": "RemoteLoad",
+                  "remote_store": "RemoteStore", "accumulate_": "Accumulate", "accumulate_mean_": "Accumulate",
+                  "accumulate_moving_average_": "Accumulate", "accumulate_moving_average_square_": "Accumulate",
+                  "all_reduce": "ReplicatedAllReduce", "reduce_scatter": "ReplicatedReduceScatter",
+                  "all_gather": "ReplicatedAllGather", "init": "Init"}
+
+
+def pb_op_type(op: "Op") -> str:
+    """Op type under popart's naming (`MatMul`, `Add`, `Call`, ...): CamelCase of the op name where popart has none."""
+    name = op.opdef.name
+    if name in _PB_TYPE_NAMES:
+        return _PB_TYPE_NAMES[name]
+    return "".join(p.capitalize() for p in name.rstrip("_").split("_")) + ("Inplace" if name.endswith("_") else "")
+
+
+class _PbTensorInfo:
+    def __init__(self, t):
+        self._t = t
+
+    def shape(self):
+        return list(self._t.shape)
+
+    def nelms(self):
+        return self._t.nelms
+
+
+class _PbTensor:
+    def __init__(self, t):
+        self._t = t
+        self.id = t.id
+        self.info = _PbTensorInfo(t)
+
+
+class _PbOp:
+    """Read-only view of an op with the accessors of popart's `Op` that scripts written for the reference use."""
+
+    def __init__(self, op: "Op"):
+        self._op = op
+        self.id = op.id
+
+    def opType(self) -> str:
+        return pb_op_type(self._op)
+
+    def name(self) -> str:
+        return self._op.name
+
+    def getInputTensors(self):
+        return [_PbTensor(t) for t in self._op.inputs]
+
+    def getOutputTensors(self):
+        return [_PbTensor(t) for t in self._op.outputs]
+
+    def debugName(self) -> str:
+        return f"{self.opType()}.{self.id}"
+
+
+class _PbCallOp(_PbOp):
+    def getCalledGraph(self):
+        return _PbGraph(self._op.attrs["graph"])
+
+
+class _PbLoopOp(_PbCallOp):
+    def getTripCountValue(self) -> int:
+        return int(self._op.attrs.get("count", 1))
+
+
+class _PbMatMulOp(_PbOp):
+    """Matmul-class ops carry the 'keep a pre-transposed weight for the backward passes' flag."""
+
+    def useFullyConnectedPass(self) -> bool:
+        per_op = self._op.graph.hints.get("fc_pass", {})
+        if self._op.uid in per_op:
+            return bool(per_op[self._op.uid])
+        return bool(self._op.graph.ir.options.hints.get("use_fc_pass", True))
+
+    def setUseFullyConnectedPass(self, value: bool) -> None:
+        self._op.graph.hints.setdefault("fc_pass", {})[self._op.uid] = bool(value)
+
+
+def _pb_op(op: "Op") -> _PbOp:
+    name = op.opdef.name
+    if name == "repeat":
+        return _PbLoopOp(op)
+    if name == "call":
+        return _PbCallOp(op)
+    if name in ("matmul", "linear_bias_act", "matmul_pow2scaled"):
+        return _PbMatMulOp(op)
+    return _PbOp(op)
+
+
+class _PbGraph:
+    def __init__(self, graph: "Graph"):
+        self._graph = graph
+        self.id = graph.id
+
+    def getOps(self):
+        return [_pb_op(op) for op in self._graph.ops]
+
+    def getInputIds(self):
+        return [t.id for t in self._graph.inputs]
+
+    def getOutputIds(self):
+        return [t.id for t in self._graph.outputs]
+
+    def __eq__(self, other):
+        return isinstance(other, _PbGraph) and other._graph is self._graph
+
+    def __hash__(self):
+        return hash(id(self._graph))
+
+
 class _PbIrShim:
     """Minimal stand-in for the handful of low-level IR queries that user scripts written for the reference make."""
 
@@ -725,7 +843,7 @@ class _PbIrShim:
         self._options = type("SessionOptions", (), {})()
 
     def getAllGraphs(self):
-        return list(self._ir.graphs)
+        return [g._pb_graph for g in self._ir.graphs]
 
     def getSessionOptions(self):
         return self._options
@@ -749,6 +867,7 @@ class Ir:
         self.devices_per_replica = int(devices_per_replica)
         self.graphs: List[Graph] = []
         self._graph_counter = itertools.count()
+        self._op_ids = itertools.count(100)
         self.main_graph = Graph(self, "main")
         self.graphs.append(self.main_graph)
         self.distributed = False
@@ -852,6 +971,9 @@ class Ir:
                     raise ValueError(f"Graph outputs must be tensors, got {type(out)} from {base}")
                 graph_output(out)
         return g
+
+    def _next_op_id(self) -> int:
+        return next(self._op_ids)
 
     def __repr__(self):
         return f"Ir(graphs={len(self.graphs)}, replication_factor={self._replication_factor})"

@@ -1348,3 +1348,7 @@ from .decode import (rotary_kv_append_, attention_decode_packed, argmax_rows, ad
                      kv_cache_fill_, timestamp, attention_decode_into_, add_layer_norm_,
                      all_reduce_add_layer_norm_)
 from .extra import *  # noqa: E402,F401,F403
+# module paths of popxl (`ops.call`, `ops.utils`): loaded here so that a later `from ...ops.call import CallSiteInfo`
+# finds the submodule already imported and the name `call` stays bound to the function
+from . import utils  # noqa: E402,F401
+from .call import call, call_with_info  # noqa: E402,F401,F811

@@ -1,7 +1,7 @@
 """`xl.transforms`: graph-to-graph transforms of the substrate (autodiff, exchange-merging annotations)."""
 import contextlib
 
-from .autodiff import ExpectedConnection, ExpectedConnectionType, GradGraphInfo, autodiff  # noqa: F401
+from .autodiff import ExpectedConnection, ExpectedConnectionType, GradGraphInfo, autodiff  # noqa: F401  (the function shadows the submodule, as in popxl)
 
 
 @contextlib.contextmanager
@@ -13,7 +13,7 @@ def merge_exchange():
 @contextlib.contextmanager
 def io_tile_exchange():
     """`merge_exchange()` + `io_tiles()`."""
-    from .core import io_tiles
+    from ..core import io_tiles
 
     with io_tiles():
         yield

@@ -463,9 +463,12 @@ def test_cross_entropy_ops_and_misc_utils(capsys):
         addons.disable_fc_pass(ir)
         addons.set_available_memory_proportion_by_ipu(ir, [0.3])
         table = addons.print_FLOPs(ir)
-    assert n_mm == 1 and addons.total_FLOPs(ir) - flops_before == 2 * 9 * 6 * 5 and table["matmul"] == 540
+    assert n_mm == 1 and addons.total_FLOPs(ir) - flops_before == 2 * 9 * 6 * 5 and table["MatMul"] == 540
+    breakdown = addons.evaluate_FLOPs(ir.main_graph)
+    assert list(breakdown["MatMul"].values()) == [540] and breakdown["TOT"] == addons.total_FLOPs(ir)
     assert ir.options["use_fc_pass"] is False and ir.main_graph.hints["available_memory_proportion"] == {0: 0.3}
-    assert addons.format_flops_scientific(2.5e12) == "2.50T"
+    assert addons.format_flops_scientific(2.5e12) == "2.500E+12" and addons.format_flops_scientific(9072) == "9.072E+03"
+    assert addons.format_flops_scientific(64, "K") == "0.064E+03"
     out = _run(ir)
     tl = torch.tensor(logits, requires_grad=True)
     ref = torch.nn.functional.cross_entropy(tl, torch.tensor(labels).long())
