@@ -6,6 +6,8 @@ from typing import Dict, Optional
 import numpy as np
 
 from .. import xl
+from ..utils import WeightsDict
+from ..xl.utils import to_numpy
 from ..module import Module
 from ..named_tensors import NamedTensors
 from ..xl import ops
@@ -33,6 +35,6 @@ class GroupNorm(Module):
         return ops.group_norm(x, w, b, num_groups=self.num_groups, eps=self.eps)
 
     @staticmethod
-    def torch_mapping(variables: NamedTensors, nn_layer) -> Dict[xl.Tensor, np.ndarray]:
-        return {variables.weight: nn_layer.weight.data.detach().cpu().numpy().copy(),
-                variables.bias: nn_layer.bias.data.detach().cpu().numpy().copy()}
+    def torch_mapping(variables: NamedTensors, nn_layer, dtype: xl.dtype = xl.float32) -> WeightsDict:
+        return WeightsDict({variables.weight: to_numpy(nn_layer.weight.data, dtype),
+                            variables.bias: to_numpy(nn_layer.bias.data, dtype)})

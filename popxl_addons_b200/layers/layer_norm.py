@@ -6,6 +6,8 @@ from typing import Dict
 import numpy as np
 
 from .. import xl
+from ..utils import WeightsDict
+from ..xl.utils import to_numpy
 from ..module import Module
 from ..named_tensors import NamedTensors
 from ..xl import ops
@@ -27,6 +29,7 @@ class LayerNorm(Module):
         return ops.layer_norm(x, w, b, eps=self.eps)
 
     @staticmethod
-    def torch_mapping(variables: NamedTensors, nn_layer) -> Dict[xl.Tensor, np.ndarray]:
-        return {variables.weight: nn_layer.weight.data.detach().cpu().numpy().reshape(-1).copy(),
-                variables.bias: nn_layer.bias.data.detach().cpu().numpy().reshape(-1).copy()}
+    def torch_mapping(variables: NamedTensors, nn_layer, dtype: xl.dtype = xl.float32) -> WeightsDict:
+        """A torch LayerNorm over several trailing axes maps onto this layer's flattened last axis."""
+        return WeightsDict({variables.weight: to_numpy(nn_layer.weight.data, dtype).reshape(variables.weight.shape),
+                            variables.bias: to_numpy(nn_layer.bias.data, dtype).reshape(variables.bias.shape)})

@@ -11,6 +11,8 @@ from typing import Dict, Optional
 import numpy as np
 
 from .. import xl
+from ..utils import WeightsDict
+from ..xl.utils import to_numpy
 from ..module import Module
 from ..named_tensors import NamedTensors
 
@@ -44,9 +46,9 @@ class Linear(Module):
         return y
 
     @staticmethod
-    def torch_mapping(variables: NamedTensors, nn_layer) -> Dict[xl.Tensor, np.ndarray]:
-        """Host data for `variables` from a `torch.nn.Linear` (whose weight is `(out, in)`)."""
-        out = {variables.weight: nn_layer.weight.data.detach().cpu().numpy().T.copy()}
+    def torch_mapping(variables: NamedTensors, nn_layer, dtype: xl.dtype = xl.float32) -> WeightsDict:
+        """Host data for `variables` from a `torch.nn.Linear` (whose weight is `(out, in)`), converted to `dtype`."""
+        out = {variables.weight: np.ascontiguousarray(to_numpy(nn_layer.weight.data, dtype).T)}
         if nn_layer.bias is not None and "bias" in variables:
-            out[variables.bias] = nn_layer.bias.data.detach().cpu().numpy().copy()
-        return out
+            out[variables.bias] = to_numpy(nn_layer.bias.data, dtype)
+        return WeightsDict(out)

@@ -77,3 +77,14 @@ class LinearFP8(Module):
         if self.aux["has_bias"]:
             self.var_grad["bias"] = ops.sum(dLdy, axis=0)
         return dLdx
+
+    @staticmethod
+    def torch_mapping(variables, nn_layer, dtype: xl.dtype = xl.float32):
+        """Host data for `variables` from a `torch.nn.Linear` (whose weight is `(out, in)`), converted to `dtype`."""
+        from ..utils import WeightsDict
+        from ..xl.utils import to_numpy
+
+        out = {variables.weight: np.ascontiguousarray(to_numpy(nn_layer.weight.data, dtype).T)}
+        if "bias" in variables.keys():
+            out[variables.bias] = to_numpy(nn_layer.bias.data, dtype)
+        return WeightsDict(out)

@@ -11,6 +11,8 @@ from typing import Dict, Optional
 import numpy as np
 
 from .. import xl
+from ..utils import WeightsDict
+from ..xl.utils import to_numpy
 from ..module import Module
 from ..named_tensors import NamedTensors
 from ..ops.group_quantize_decompress import group_quantize_compress_numpy
@@ -135,13 +137,14 @@ class LinearGQ(Module):
         return emit1("linear_gq", ins, {"dim": self.dim})
 
     @staticmethod
-    def torch_mapping(variables: NamedTensors, nn_layer, group_size: int = 64, dim: int = -1,
-                      dtype=np.float16) -> Dict[xl.Tensor, np.ndarray]:
-        """Compress a `torch.nn.Linear` weight (stored `(out, in)`) into the layer's variables."""
-        w = nn_layer.weight.data.detach().cpu().float().numpy().T.astype(dtype)  # (in, out)
+    def torch_mapping(variables: NamedTensors, nn_layer, dtype: xl.dtype = xl.float16, group_size: int = 64,
+                      dim: int = -1) -> WeightsDict:
+        """Compress a `torch.nn.Linear` weight (stored `(out, in)`) into the layer's variables; scales, zero points
+        and the bias are converted to `dtype`, the dtype of the layer's input."""
+        w = nn_layer.weight.data.detach().cpu().float().numpy().T  # (in, out)
         packed, scale, bias = group_quantize_compress_numpy(w, group_size, dim)
-        out = {variables.weight_compressed: packed, variables.weight_decompression_scale: scale.astype(dtype),
-               variables.weight_decompression_bias: bias.astype(dtype)}
+        out = {variables.weight_compressed: packed, variables.weight_decompression_scale: to_numpy(scale, dtype),
+               variables.weight_decompression_bias: to_numpy(bias, dtype)}
         if nn_layer.bias is not None and "bias" in variables:
-            out[variables.bias] = nn_layer.bias.data.detach().cpu().numpy().astype(dtype)
-        return out
+            out[variables.bias] = to_numpy(nn_layer.bias.data, dtype)
+        return WeightsDict(out)

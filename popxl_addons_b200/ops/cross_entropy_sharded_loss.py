@@ -187,3 +187,8 @@ def cross_entropy_sharded_wr_loss(logits: List[xl.Tensor], indices: List[xl.Tens
         raise ValueError("You must provide the same number of logits and indices.")
     outs = emit("ce_sharded_wr", [*logits, *indices], {"n": len(logits)})
     return outs[0]
+
+
+from ._paths import also_importable_as  # noqa: E402
+
+also_importable_as(__name__)

@@ -4,3 +4,8 @@ across-replica sibling."""
 from .cross_entropy_sharded_loss import cross_entropy_sharded_wr_loss
 
 __all__ = ["cross_entropy_sharded_wr_loss"]
+
+
+from ._paths import also_importable_as  # noqa: E402
+
+also_importable_as(__name__)

@@ -82,3 +82,8 @@ def fp8_mse_scale(src: xl.Tensor, dtype: xl.dtype = xl.float8_143) -> xl.Tensor:
         raise RuntimeError(f"dtype {src.dtype} not currently supported.")
     mant = {"float32": 23, "float16": 10, "bfloat16": 7}[src.dtype.name]
     return emit1("fp8_mse_scale", [src.flatten()], {"fmt_name": dtype.name, "src_mantissa_bits": mant})
+
+
+from ._paths import also_importable_as  # noqa: E402
+
+also_importable_as(__name__)

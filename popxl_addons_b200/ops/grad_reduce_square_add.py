@@ -31,3 +31,8 @@ def grad_reduce_square_add(t: xl.Tensor, loss_scaling: Union[int, float, xl.Tens
     else:
         scale = xl.constant(1.0 / (float(loss_scaling) * float(loss_scaling)), xl.float32)
     return emit1("grad_reduce_square_add", [t, scale], out_name="grad_reduced")
+
+
+from ._paths import also_importable_as  # noqa: E402
+
+also_importable_as(__name__)

@@ -53,37 +53,50 @@ def group_quantize_decompress(t: xl.Tensor, group_scale: xl.Tensor, group_bias: 
 
 def group_quantize_decompress_numpy(t: np.ndarray, group_scale: np.ndarray, group_bias: np.ndarray,
                                     dim: int = -1) -> np.ndarray:
+    """`(*leading, n_groups, group_size / 4)` packed uint16 -> `(*leading, n_groups * group_size)` values
+    `code * scale + bias`, computed in the dtype of the scales (for float16 scales: product and sum each rounded to
+    float16, as the reference's helper does). The decompressed axis is last; `dim != -1` moves it to `dim`."""
     t = np.asarray(t).astype(np.uint16)
     codes = np.stack([(t >> s) & 0xF for s in _SHIFTS], axis=-1)
-    r, g, w, _ = codes.shape
-    vals = codes.reshape(r, g, w * 4).astype(np.float32) * group_scale.astype(np.float32) \
-        + group_bias.astype(np.float32)
-    out = vals.reshape(r, g * w * 4).astype(group_scale.dtype)
-    return out if dim in (-1, 1) else out.T
+    *lead, g, w, _ = codes.shape
+    dt = np.asarray(group_scale).dtype
+    vals = codes.reshape(*lead, g, w * 4).astype(dt) * group_scale + group_bias
+    out = vals.reshape(*lead, g * w * 4).astype(dt)
+    if dim != -1:
+        out = np.moveaxis(out, -1, dim)
+    return out
 
 
 def group_quantize_compress_numpy(t: np.ndarray, group_size: int = 64,
                                   dim: int = -1) -> Tuple[np.ndarray, np.ndarray, np.ndarray]:
-    """Quantise a 2-D matrix to 4 bits in groups of `group_size` along axis `dim`. Per group: `bias = min`,
-    `scale = (max - min) / 15`, `code = round((x - bias) / scale)`. Returns `(packed uint16, scale, bias)`."""
-    if t.ndim != 2:
-        raise ValueError("Only 2-D matrices can be compressed")
+    """Quantise to 4 bits in groups of `group_size` along axis `dim` (moved last in the result). Per group:
+    `bias = min`, `scale = (max - min) / 15`, `code = round((x - bias) / scale)`, in the arithmetic of the input's
+    dtype. Returns `(packed uint16 (*other, n_groups, group_size / 4), scale, bias (*other, n_groups, 1))`."""
     if group_size % 4:
         raise ValueError("group_size must be a multiple of 4")
-    x = np.asarray(t, dtype=np.float32)
-    if dim not in (-1, 1):
-        x = x.T
-    r, c = x.shape
+    x = np.asarray(t)
+    if not np.issubdtype(x.dtype, np.floating):
+        x = x.astype(np.float32)
+    if dim != -1:
+        x = np.moveaxis(x, dim, -1)
+    if not np.isfinite(x).all():
+        raise ValueError("Cannot compress t which contains non-finite values")
+    *lead, c = x.shape
     if c % group_size:
         raise ValueError(f"The quantised axis ({c}) must be divisible by group_size ({group_size})")
-    g = x.reshape(r, c // group_size, group_size)
+    g = x.reshape(*lead, c // group_size, group_size)
     lo = g.min(axis=-1, keepdims=True)
     hi = g.max(axis=-1, keepdims=True)
-    scale = (hi - lo) / 15.0
-    safe = np.where(scale == 0, 1.0, scale)
+    scale = ((hi - lo) / 15).astype(x.dtype)
+    safe = np.where(scale == 0, np.ones_like(scale), scale)
     codes = np.clip(np.rint((g - lo) / safe), 0, 15).astype(np.uint16)
-    codes = codes.reshape(r, c // group_size, group_size // 4, 4)
+    codes = codes.reshape(*lead, c // group_size, group_size // 4, 4)
     packed = np.zeros(codes.shape[:-1], dtype=np.uint16)
     for i, s in enumerate(_SHIFTS):
         packed |= codes[..., i] << s
-    return packed, scale.astype(t.dtype), lo.astype(t.dtype)
+    return packed, scale, lo.astype(x.dtype)
+
+
+from ._paths import also_importable_as  # noqa: E402
+
+also_importable_as(__name__)

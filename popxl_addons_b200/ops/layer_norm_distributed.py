@@ -81,3 +81,8 @@ def layer_norm_distributed(t: xl.Tensor, w: xl.Tensor, b: xl.Tensor, epsilon: fl
     group = group if group is not None else xl.gcg().ir.replica_grouping()
     return emit("layer_norm_distributed", [t, w, b], {"eps": float(epsilon), "group": group},
                 ["outputs", "mean", "std"])[0]
+
+
+from ._paths import also_importable_as  # noqa: E402
+
+also_importable_as(__name__)

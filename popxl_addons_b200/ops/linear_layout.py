@@ -17,3 +17,8 @@ OpDef("linear_layout", impl=lambda t, bs: t.contiguous().clone() if t.device.typ
 
 def linear_layout(t: xl.Tensor, bs: int = 1) -> xl.Tensor:
     return emit1("linear_layout", [t], {"bs": int(bs)})
+
+
+from ._paths import also_importable_as  # noqa: E402
+
+also_importable_as(__name__)

@@ -35,3 +35,8 @@ def replicated_all_reduce_identical_inputs(t: xl.Tensor, op="add",
 def replicated_all_reduce_identical_grad_inputs(t: xl.Tensor, op="add",
                                                 group: Optional[xl.ReplicaGrouping] = None) -> xl.Tensor:
     return _c.replicated_all_reduce(t, _check(op), group, identical_grad_inputs=True)
+
+
+from ._paths import also_importable_as  # noqa: E402
+
+also_importable_as(__name__)

@@ -68,3 +68,19 @@ def replicated_all_reduce_strided_graph(tensors, op="add", group: Optional[xl.Re
             names.append(name)
             xl.graph_output(replicated_all_reduce_strided(gi, op=op, group=group))
     return GraphWithNamedArgs(graph, NamedTensors.from_dict(args)), names
+
+
+# the reference keeps each collective in a submodule named after it; load those now so that importing one later
+# (`from ...replicated_strided_collectives.replicated_all_reduce_strided import ...`) does not rebind the function
+# names of this package to the submodules
+def _load_submodules():
+    import importlib
+
+    keep = {name: globals()[name] for name in __all__}
+    for sub in ("replicated_all_gather_strided", "replicated_all_reduce_strided", "replicated_reduce_scatter_strided"):
+        importlib.import_module(f"{__name__}.{sub}")
+    globals().update(keep)
+
+
+_load_submodules()
+del _load_submodules

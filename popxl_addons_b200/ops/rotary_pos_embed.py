@@ -28,3 +28,8 @@ def rotary_pos_embed(t: xl.Tensor, sin: xl.Tensor, cos: xl.Tensor, rotary_dim: i
     """Rotate the first `rotary_dim` features of `t (batch, heads, seq, head_dim)` pairwise:
     `(x0, x1) -> (x0 cos - x1 sin, x1 cos + x0 sin)`; `sin`/`cos` are `(1|batch, seq, rotary_dim/2)`."""
     return ops.rotary_pos_embed(t, sin, cos, rotary_dim)
+
+
+from ._paths import also_importable_as  # noqa: E402
+
+also_importable_as(__name__)

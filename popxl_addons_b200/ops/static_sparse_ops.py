@@ -19,7 +19,8 @@ def random_sparse(dense: np.ndarray, density: float = 0.5):
 
     mask = np.random.rand(*dense.shape) < density
     masked = (dense * mask).astype(dense.dtype)
-    return masked, csr_matrix(masked)
+    # scipy has no 16-bit float sparse matrices: those are held as float32 (exact)
+    return masked, csr_matrix(masked.astype(np.float32) if masked.dtype.itemsize < 4 else masked)
 
 
 def _impl(lhs, indptr, indices, values, n_rows, n_cols):
@@ -45,3 +46,8 @@ def dense_const_sparse_matmul(lhs: xl.Tensor, rhs, output_cols: int = None) -> x
     indices = xl.constant(rhs.indices.astype(np.int32), xl.int32, "csr_indices")
     values = xl.constant(rhs.data.astype(np.float32), xl.float32, "csr_values")
     return emit1("dense_csr_matmul", [lhs, indptr, indices, values], {"n_rows": k, "n_cols": n})
+
+
+from ._paths import also_importable_as  # noqa: E402
+
+also_importable_as(__name__, "dense_sparse_matmul")

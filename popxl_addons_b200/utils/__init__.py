@@ -89,7 +89,12 @@ class WeightsDict(MutableMapping):
         from ..xl.dtypes import dtype as _dtype
 
         array_dtype = _dtype.as_dtype(array.dtype)
-        if var.dtype != array_dtype:
+        try:
+            var.dtype.as_numpy()
+            host_float32_ok = False
+        except TypeError:  # bf16 / fp8 variables take float32 host data
+            host_float32_ok = array.dtype == np.float32
+        if var.dtype != array_dtype and not host_float32_ok:
             raise ValueError(f"{var}: tensor and weight dtypes do not equal {var.dtype} != {array_dtype}")
         if tuple(var.shape_on_host) != tuple(array.shape):
             raise ValueError(f"{var}: tensor and weight shapes do not equal {var.shape_on_host} != {array.shape}")

@@ -157,6 +157,8 @@ def remote_variable(data, remote_buffer: RemoteBuffer, offset: int = 0, dtype: O
     v = Variable(g.ir.main_graph, shape, dt, name or "remote_variable", replica_grouping=rg,
                  remote_buffer=remote_buffer, entry=int(offset))
     g.ir.initial_values[v] = host
+    if isinstance(host, np.memmap):
+        v._memmap_arr = host
     return v
 
 
@@ -178,4 +180,6 @@ def remote_replica_sharded_variable(data, remote_buffer: RemoteBuffer, offset: i
                  meta_shape=remote_buffer.meta_shape, replica_grouping=rg, remote_buffer=remote_buffer,
                  entry=int(offset), shard_group=remote_buffer.shard_group)
     g.ir.initial_values[v] = host
+    if isinstance(host, np.memmap):
+        v._memmap_arr = host
     return v

@@ -479,6 +479,9 @@ class Variable(Tensor):
         # replica group whose members may access this variable's storage directly over NVLink (the session then
         # places it in that group's symmetric-memory arena when it runs one process per GPU)
         self.symmetric_group: Optional[ReplicaGrouping] = None
+        # the host array when the variable was initialised from a numpy memmap: host reads of the variable are written
+        # through to it and return it
+        self._memmap_arr = None
 
     @property
     def shape_on_host(self) -> Tuple[int, ...]:
@@ -822,6 +825,19 @@ class _PbGraph:
     def getOps(self):
         return [_pb_op(op) for op in self._graph.ops]
 
+    def getOpSchedule(self, *_args, **_kwargs):
+        """Ops run in the order they were recorded."""
+        return self.getOps()
+
+    def getCalledGraphs(self):
+        seen, out = set(), []
+        for op in self._graph.ops:
+            callee = op.attrs.get("graph")
+            if isinstance(callee, Graph) and id(callee) not in seen:
+                seen.add(id(callee))
+                out.append(_PbGraph(callee))
+        return out
+
     def getInputIds(self):
         return [t.id for t in self._graph.inputs]
 
@@ -847,6 +863,19 @@ class _PbIrShim:
 
     def getSessionOptions(self):
         return self._options
+
+    def setPatterns(self, patterns) -> None:
+        """Accepted for scripts that configure popart's pattern sets by hand; the rewrite passes of this substrate are
+        fixed (`applyPreAliasPatterns`)."""
+        self._patterns = patterns
+
+    def applyPreAliasPatterns(self, graph) -> int:
+        from ..patterns import apply_patterns_to_graph
+
+        return apply_patterns_to_graph(graph._graph if isinstance(graph, _PbGraph) else graph)
+
+    def applyInplacePattern(self, graph) -> None:
+        """Buffers are reused by the allocator, not by rewriting ops: nothing to do."""
 
     def logIr(self):
         for g in self._ir.graphs:
@@ -957,7 +986,8 @@ class Ir:
                 elif param.kind == inspect.Parameter.VAR_KEYWORD:
                     for k, v in value.items():
                         new_kwargs[k] = convert(v, k, by_ref)
-                elif param.kind == inspect.Parameter.KEYWORD_ONLY:
+                elif param.kind == inspect.Parameter.KEYWORD_ONLY or pname in kwargs:
+                    # given by keyword: passed on by keyword (a defaulted parameter before it may have been left out)
                     new_kwargs[pname] = convert(value, pname, by_ref)
                 else:
                     new_args.append(convert(value, pname, by_ref))
@@ -1088,6 +1118,8 @@ def variable(data, dtype: Optional[dtype] = None, name: Optional[str] = None, do
         shape = full_shape
     v = Variable(g, shape, dt, name or "variable", replica_grouping=rg)
     g.ir.initial_values[v] = host
+    if isinstance(host, np.memmap):
+        v._memmap_arr = host
     return v
 
 

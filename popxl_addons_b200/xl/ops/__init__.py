@@ -89,9 +89,29 @@ def _vjp_div(ctx, op, gs):
     return [_unbroadcast(ga, a.shape), _unbroadcast(gb, b.shape)]
 
 
-register("add", vjp=_vjp_add, keeps_meta=True)(lambda a, b: torch.add(a, b))
-register("sub", vjp=_vjp_sub, keeps_meta=True)(lambda a, b: torch.sub(a, b))
-register("mul", vjp=_vjp_mul, keeps_meta=True)(lambda a, b: torch.mul(a, b))
+_WIDE_UNSIGNED = (torch.uint16, torch.uint32, torch.uint64)
+
+
+def _uint_safe(fn):
+    """torch has no arithmetic for 16/32/64-bit unsigned tensors: compute such operands in int64 and cast back (wraps
+    modulo 2^n like the unsigned type)."""
+
+    def f(a, b):
+        if a.dtype in _WIDE_UNSIGNED or b.dtype in _WIDE_UNSIGNED:
+            dt = a.dtype if a.dtype in _WIDE_UNSIGNED else b.dtype
+            if a.device.type == "meta":
+                return torch.empty(torch.broadcast_shapes(a.shape, b.shape), dtype=dt, device="meta")
+            return fn(a.to(torch.int64), b.to(torch.int64)).to(dt)
+        return fn(a, b)
+
+    return f
+
+
+register("add", vjp=_vjp_add, keeps_meta=True)(_uint_safe(torch.add))
+register("sub", vjp=_vjp_sub, keeps_meta=True)(_uint_safe(torch.sub))
+register("mul", vjp=_vjp_mul, keeps_meta=True)(_uint_safe(torch.mul))
+
+
 def _div_ref(a, b):
     # integer operands divide like C (truncation), floats divide exactly
     if not a.dtype.is_floating_point and not b.dtype.is_floating_point:
@@ -861,8 +881,9 @@ OpDef("conv_grad", impl=_conv_grad_ref, infer=_infer_like_inputs(2))
 
 
 def conv(t: Tensor, weight: Tensor, stride=(1, 1), padding=(0, 0, 0, 0), dilation=(1, 1), groups: int = 1,
-         pad_type: str = "not_set", available_memory_proportion=None, partials_type=None,
-         enable_conv_dithering=None, output_type=None, cycle_back_off=None) -> Tensor:
+         pad_type: str = "not_set", available_memory_proportions=None, partials_types=None,
+         enable_conv_dithering=None, output_type=None, cycle_back_off=None, available_memory_proportion=None,
+         partials_type=None) -> Tensor:
     """2-D convolution, NCHW. `padding` is explicit `(top, left, bottom, right)`; `pad_type` may be
     `same_upper`, `same_lower` or `valid` to derive it. Planner knobs are accepted for API parity and ignored."""
     stride, dilation = tuple(stride), tuple(dilation)

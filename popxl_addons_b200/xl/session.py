@@ -255,6 +255,14 @@ class Session:
             if res.device.type == "cpu" and self.device.type == "cpu" and rg.num_groups == 1:
                 res = res.clone()  # on the CPU backend the gathered value is the live storage: hand out a copy
             out[var] = _dt.to_numpy(res)
+            mm = getattr(var, "_memmap_arr", None)
+            if mm is not None and tuple(mm.shape) == tuple(out[var].shape):
+                # memmap-backed variable: the host file is the variable's host copy
+                if mm.flags.writeable:
+                    mm[...] = out[var].astype(mm.dtype, copy=False)
+                    out[var] = mm
+                elif np.array_equal(mm, out[var]):
+                    out[var] = mm
         return out
 
     def write_variable_data(self, tensor: Variable, data) -> None:

@@ -22,7 +22,13 @@ def to_numpy(x, dtype: Optional["_dt.dtype"] = None, downcast: bool = True, copy
     else:
         arr = np.asarray(x)
     if dtype is not None:
-        want = dtype.as_numpy() if hasattr(dtype, "as_numpy") else np.dtype(dtype)
+        if hasattr(dtype, "as_numpy"):
+            try:
+                want = dtype.as_numpy()
+            except TypeError:  # bf16 / fp8: numpy cannot hold them; round through torch and keep float32
+                return _dt.to_numpy(torch.as_tensor(arr.astype(np.float32)).to(dtype.as_torch()))
+        else:
+            want = np.dtype(dtype)
         if arr.dtype != want:
             return arr.astype(want)
     elif downcast and arr.dtype in downcast_np_dtypes:

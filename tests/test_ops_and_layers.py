@@ -372,7 +372,7 @@ def test_layers_match_torch():
     np.testing.assert_allclose(y, gn(torch.tensor(img)).detach().numpy(), rtol=1e-3, atol=1e-4)
     for kw, tkw in [(dict(kernel_size=3, paddings=1), dict(padding=1)),
                     (dict(kernel_size=(3, 2), strides=2, dilations=1, groups=2), dict(stride=2, groups=2)),
-                    (dict(kernel_size=3, pad_type="same_upper"), dict(padding="same"))]:
+                    (dict(kernel_size=3, paddings="same_upper"), dict(padding="same"))]:
         conv = torch.nn.Conv2d(4, 6, kw["kernel_size"], **tkw)
         (y,) = run_module(Conv2D(6, **kw), TensorInput(img), device="cpu",
                           weights=partial(Conv2D.torch_mapping, nn_layer=conv))
