@@ -211,14 +211,14 @@ def test_rotary_matches_gptj_formula():
 
     b, h, s, d, rot = 2, 3, 7, 16, 8
     rng = np.random.RandomState(5)
-    x = rng.randn(b, h, s, d).astype(np.float32)
+    x = rng.randn(b, s, h, d).astype(np.float32)  # (batch, seq, heads, head_dim), the layout of the reference's op
     sin, cos = trig_tables(s, rot)
 
     def hf_gptj(x):
         # rotate_every_two formulation of the GPT-J reference implementation
         xr, xp = x[..., :rot], x[..., rot:]
-        sin_i = np.repeat(sin, 2, axis=-1)[None, None]
-        cos_i = np.repeat(cos, 2, axis=-1)[None, None]
+        sin_i = np.repeat(sin, 2, axis=-1)[None, :, None]
+        cos_i = np.repeat(cos, 2, axis=-1)[None, :, None]
         x1, x2 = xr[..., ::2], xr[..., 1::2]
         rotated = np.stack((-x2, x1), axis=-1).reshape(xr.shape)
         return np.concatenate([xr * cos_i + rotated * sin_i, xp], axis=-1)
@@ -226,7 +226,7 @@ def test_rotary_matches_gptj_formula():
     ir = popxl.Ir()
     with ir.main_graph:
         xv = popxl.variable(x)
-        sv, cv = popxl.constant(sin[None]), popxl.constant(cos[None])
+        sv, cv = popxl.constant(sin), popxl.constant(cos)  # rank 2 and rank 3 tables are both accepted
         g = ir.create_graph(lambda t, a, c: rotary_pos_embed(t, a, c, rot), xv, sv, cv)
         dg = popxl.transforms.autodiff(g, grads_required=[g.inputs[0]])
         info = ops.call_with_info(g, xv, sv, cv)
