@@ -851,12 +851,42 @@ class _PbGraph:
         return hash(id(self._graph))
 
 
+class _RecordedOptions:
+    """Session options of the reference substrate are IPU compiler / engine settings. Programs set them through
+    attribute and item assignment (`opts.numIOTiles = 64`, `opts.engineOptions["x"] = "y"`,
+    `opts.replicatedCollectivesSettings.prepareScheduleForMergingCollectives = True`); every such assignment is accepted
+    and recorded, none changes what runs."""
+
+    def __init__(self):
+        object.__setattr__(self, "_values", {})
+
+    def __getattr__(self, name):
+        if name.startswith("__"):
+            raise AttributeError(name)
+        return self._values.setdefault(name, _RecordedOptions())
+
+    def __setattr__(self, name, value):
+        self._values[name] = value
+
+    def __getitem__(self, key):
+        return self._values.setdefault(key, _RecordedOptions())
+
+    def __setitem__(self, key, value):
+        self._values[key] = value
+
+    def __contains__(self, key):
+        return key in self._values
+
+    def __repr__(self):
+        return f"Options({self._values})"
+
+
 class _PbIrShim:
     """Minimal stand-in for the handful of low-level IR queries that user scripts written for the reference make."""
 
     def __init__(self, ir):
         self._ir = ir
-        self._options = type("SessionOptions", (), {})()
+        self._options = _RecordedOptions()
 
     def getAllGraphs(self):
         return [g._pb_graph for g in self._ir.graphs]

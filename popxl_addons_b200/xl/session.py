@@ -288,6 +288,50 @@ class Session:
     def weights_from_host(self):
         pass
 
+    # -- the rest of popxl.Session's host interface -----------------------------------------------------------------
+    def _streams(self, kind):
+        seen, out = set(), []
+
+        def walk(graph):
+            if id(graph) in seen:
+                return
+            seen.add(id(graph))
+            for op in graph.ops:
+                st = op.attrs.get("stream")
+                if isinstance(st, kind) and st not in out:
+                    out.append(st)
+                callee = op.attrs.get("graph")
+                if callee is not None and hasattr(callee, "ops"):
+                    walk(callee)
+
+        walk(self.ir.main_graph)
+        return out
+
+    def expected_inputs(self) -> List[HostToDeviceStream]:
+        """The host-to-device streams the program loads from, in order of first use."""
+        return self._streams(HostToDeviceStream)
+
+    def create_host_outputs(self) -> Dict[DeviceToHostStream, np.ndarray]:
+        """Zero-filled arrays of the shapes `run` returns, one per device-to-host stream of the program."""
+        T, R = int(self.ir.num_host_transfers), self.num_replicas
+        lead = ((T,) if T > 1 else ()) + ((R,) if R > 1 else ())
+        return {st: np.zeros(lead + tuple(st.shape), dtype=_dt.to_numpy(torch.zeros((), dtype=st.dtype.as_torch())).dtype)
+                for st in self._streams(DeviceToHostStream)}
+
+    def run_with_outputs(self, inputs: Optional[Mapping[HostToDeviceStream, Any]] = None,
+                         outputs: Optional[Dict[DeviceToHostStream, np.ndarray]] = None,
+                         downcast_inputs: bool = True) -> None:
+        """`run`, with the results written into caller-provided arrays (`create_host_outputs()` makes them)."""
+        res = self.run(inputs, downcast_inputs=downcast_inputs)
+        for st, arr in (outputs or {}).items():
+            if st not in res:
+                raise ValueError(f"{st} is not written by this program")
+            arr[...] = np.asarray(res[st]).reshape(arr.shape)
+
+    @property
+    def ir_(self):
+        return self.ir
+
     def __enter__(self):
         self.is_attached = True
         return self

@@ -366,3 +366,27 @@ def test_bump_allocator_canaries_name_the_overrun_allocation():
         guarded.check_guards()
     with pytest.raises(MemoryError):
         guarded.alloc((1 << 16,), torch.uint8)
+
+
+def test_session_host_interface_and_recorded_options():
+    """`expected_inputs`, `create_host_outputs`, `run_with_outputs`, and the IPU session options that programs set
+    through `ir._pb_ir.getSessionOptions()` (recorded, without effect)."""
+    ir = popxl.Ir(2)
+    opts = ir._pb_ir.getSessionOptions()
+    opts.numIOTiles = 64
+    opts.engineOptions["debug.allowOutOfMemory"] = "true"
+    opts.replicatedCollectivesSettings.prepareScheduleForMergingCollectives = True
+    assert opts.numIOTiles == 64 and opts.engineOptions["debug.allowOutOfMemory"] == "true"
+    with ir.main_graph:
+        h = popxl.h2d_stream((3,), popxl.float32, "x")
+        x = ops.host_load(h)
+        d = popxl.d2h_stream((3,), popxl.float32, "y")
+        ops.host_store(d, x * 2.0)
+    with popxl.Session(ir, "ipu_model") as s:
+        assert s.is_attached and s.expected_inputs() == [h]
+        outs = s.create_host_outputs()
+        assert {k: v.shape for k, v in outs.items()} == {d: (2, 3)}
+        data = np.arange(6, dtype=np.float32).reshape(2, 3)
+        s.run_with_outputs({h: data}, outs)
+        np.testing.assert_array_equal(outs[d], data * 2)
+    assert not s.is_attached
