@@ -5,8 +5,8 @@ None of these is on a hot path of the add-ons (the reference's layers, transform
 here so that programs written against popxl find them. Each runs as the PyTorch expression of its definition on
 either backend; the gradient ops differentiate that expression with torch.autograd, recomputing the forward from the
 op's inputs. Parity: popxl `ops.{scatter, tied_gather, average_pool, max_pool, interpolate, batch_norm_inference,
-bitwise_*, logsum, logsumexp, median, histogram, subsample, shaped_dropout, conv_transpose, normalize_image, exp_,
-relu_, swish_}`.
+bitwise_*, logsum, logsumexp, median, histogram, subsample, shaped_dropout, conv_transpose, normalize_image, roi_align,
+exp_, relu_, swish_, detach_}`.
 """
 from typing import Iterable, List, Optional, Sequence, Tuple, Union
 
@@ -19,7 +19,8 @@ from ..opdef import OpDef, emit, emit1
 
 __all__ = ["scatter", "tied_gather", "average_pool", "max_pool", "interpolate", "batch_norm_inference", "bitwise_and",
            "bitwise_or", "bitwise_xor", "bitwise_not", "logical_xor", "logsum", "logsumexp", "median", "histogram",
-           "subsample", "shaped_dropout", "conv_transpose", "normalize_image", "exp_", "relu_", "swish_", "erf", "nop"]
+           "subsample", "shaped_dropout", "conv_transpose", "normalize_image", "exp_", "relu_", "swish_", "erf", "nop",
+           "detach_", "roi_align"]
 
 
 def _differentiable(name: str, fn, n_diff: int):
@@ -382,3 +383,33 @@ def swish_(t: Tensor) -> Tensor:
     from . import swish
 
     return swish(t)
+
+
+def detach_(t: Tensor) -> Tensor:
+    from . import detach
+
+    return detach(t)
+
+
+def _roi_align_ref(x, rois, batch_index, output_size, spatial_scale, sampling_ratio):
+    if x.device.type == "meta":
+        return torch.empty((rois.shape[0], x.shape[1], *output_size), dtype=x.dtype, device="meta")
+    from torchvision.ops import roi_align as _tv_roi_align
+
+    boxes = torch.cat([batch_index.to(x.dtype).reshape(-1, 1), rois.to(x.dtype)], dim=1)
+    return _tv_roi_align(x, boxes, tuple(output_size), float(spatial_scale), int(sampling_ratio), aligned=False)
+
+
+_differentiable("roi_align", _roi_align_ref, 1)
+
+
+def roi_align(t: Tensor, rois: Tensor, batch_index: Tensor, output_size: Sequence[int], spatial_scale: float,
+              sampling_ratio: int) -> Tensor:
+    """Region-of-interest align (Mask R-CNN): `t (N, C, H, W)`, `rois (K, 4)` as `(x1, y1, x2, y2)` in input
+    coordinates times `1 / spatial_scale`, `batch_index (K,)`; bilinear samples on a `sampling_ratio` grid per output
+    bin, averaged. Result `(K, C, *output_size)`."""
+    if t.rank != 4 or rois.rank != 2 or rois.shape[1] != 4 or batch_index.shape != (rois.shape[0],):
+        raise ValueError("roi_align takes t (N, C, H, W), rois (K, 4) and batch_index (K,)")
+    return emit1("roi_align", [t, rois, batch_index],
+                 {"output_size": tuple(int(v) for v in output_size), "spatial_scale": float(spatial_scale),
+                  "sampling_ratio": int(sampling_ratio)})

@@ -35,7 +35,7 @@ def _torch(fn, *arrays):
     ts = [torch.tensor(a, requires_grad=a.dtype == np.float32) for a in arrays]
     y = fn(*ts)
     gs = torch.autograd.grad(y.sum(), [t for t in ts if t.requires_grad], allow_unused=True)
-    return [y.detach().numpy()] + [g.numpy() for g in gs]
+    return [y.detach().numpy()] + [None if g is None else g.numpy() for g in gs]
 
 
 def _check(got, want, tol=1e-5):
@@ -63,6 +63,21 @@ def test_pooling_and_resize():
            _torch(lambda x: F.interpolate(x, size=(16, 15), mode="bilinear", align_corners=False), IMG))
     with pytest.raises(ValueError):
         _run(lambda x: ops.interpolate(x, (2, 1, 1, 1)), IMG)
+
+
+def test_roi_align():
+    from torchvision.ops import roi_align as tv
+
+    rois = np.array([[0.5, 1.0, 6.0, 5.5], [2.0, 0.0, 9.0, 7.0], [1.0, 1.0, 4.0, 4.0]], np.float32)
+    bidx = np.array([0, 1, 1], np.int32)
+    got = _run(lambda x, r, b: ops.roi_align(x, r, b, (3, 2), 0.5, 2), IMG, rois, bidx)
+
+    def want(x, r):
+        boxes = torch.cat([torch.tensor(bidx).float()[:, None], r], 1)
+        return tv(x, boxes, (3, 2), 0.5, 2, aligned=False)
+
+    ref = _torch(want, IMG, rois)
+    _check(got[:2], ref[:2], 1e-5)  # value and the gradient with respect to the feature map
 
 
 def test_conv_transpose_and_batch_norm_inference():
