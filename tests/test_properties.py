@@ -1,0 +1,158 @@
+"""Property-based tests (hypothesis) of the host-side building blocks: containers, array layout helpers, replica
+groupings, the strided collectives of the in-process backend, 4-bit group quantisation and FP8 scale selection."""
+import numpy as np
+import pytest
+from hypothesis import given, settings, strategies as st
+
+import popxl_addons_b200 as addons
+from popxl_addons_b200 import xl as popxl
+from popxl_addons_b200.dot_tree import DotTree
+from popxl_addons_b200.xl import ops
+
+FAST = settings(max_examples=40, deadline=None)
+SLOW = settings(max_examples=12, deadline=None)
+
+_ident = st.from_regex(r"[a-z][a-z0-9_]{0,5}", fullmatch=True).filter(lambda s: not hasattr(DotTree, s))
+_key = st.lists(st.one_of(_ident, st.integers(0, 9).map(str)), min_size=1, max_size=3).map(".".join)
+
+
+@FAST
+@given(st.dictionaries(_key, st.integers(), min_size=1, max_size=8))
+def test_dot_tree_round_trip(flat):
+    # drop keys that are a prefix of another key (a node cannot be both a leaf and a subtree)
+    keys = sorted(flat)
+    flat = {k: v for k, v in flat.items() if not any(o != k and o.startswith(k + ".") for o in keys)}
+    tree = DotTree.from_dict(flat)
+    assert dict(tree.to_dict()) == flat
+    assert tree.len_flat() == len(flat)
+    names, values = tree.unpack()
+    assert list(names) == sorted(names) and dict(zip(names, values)) == flat
+    again = DotTree.pack(names, values)
+    assert dict(again.to_dict()) == flat
+    for k, v in flat.items():
+        assert k in tree and tree.get(k) == v
+    doubled = tree.map(lambda v: 2 * v)
+    assert dict(doubled.to_dict()) == {k: 2 * v for k, v in flat.items()}
+    with pytest.raises(ValueError):
+        tree.insert(next(iter(flat)), 0)  # duplicates need overwrite=True
+
+
+@FAST
+@given(st.integers(1, 4), st.integers(1, 4), st.integers(1, 3), st.integers(0, 2), st.data())
+def test_shard_unshard_and_repeat_shard(n, per, other, axis, data):
+    shape = [other, other + 1, other + 2]
+    shape[axis] = n * per
+    x = np.arange(int(np.prod(shape))).reshape(shape)
+    parts = addons.shard(x, n, axis)
+    assert parts.shape == (n, *[per if i == axis else s for i, s in enumerate(shape)])
+    np.testing.assert_array_equal(addons.unshard(parts, axis), x)
+    np.testing.assert_array_equal(addons.unshard_arrays([p[None] for p in parts], axis), x)
+    r = data.draw(st.integers(1, 3))
+    for mode in ("contiguous", "strided"):
+        rs = addons.repeat_shard(x, r, n, axis, mode)
+        assert rs.shape[0] == r * n
+        for i in range(r * n):
+            shard_idx = i % n if mode == "contiguous" else i // r  # s0 s1 s0 s1 against s0 s0 s1 s1
+            np.testing.assert_array_equal(rs[i], parts[shard_idx])
+    neg = axis - x.ndim
+    np.testing.assert_array_equal(addons.shard(x, n, neg), parts)
+
+
+@FAST
+@given(st.sampled_from([1, 2, 3, 4, 6, 8, 12, 16]), st.data())
+def test_replica_grouping_partitions_and_transpose(rf, data):
+    divisors = [d for d in range(1, rf + 1) if rf % d == 0]
+    stride = data.draw(st.sampled_from(divisors))
+    size = data.draw(st.sampled_from([d for d in divisors if rf % (stride * d) == 0]))
+    ir = popxl.Ir(rf)
+    rg = ir.replica_grouping(stride=stride, group_size=size)
+    assert rg.group_size == size and rg.num_groups == rf // size
+    groups = [list(g) for g in rg.groups]
+    assert sorted(r for g in groups for r in g) == list(range(rf))  # a partition of the replicas
+    for g in groups:
+        assert len(g) == size and all(b - a == stride for a, b in zip(g, g[1:]))
+        block = g[0] // (stride * size)
+        assert all(r // (stride * size) == block and r % stride == g[0] % stride for r in g)
+    assign = rg.assignment
+    assert all(assign[r] == gi for gi, g in enumerate(groups) for r in g)
+    tr = rg.transpose()
+    assert tr.group_size == rg.num_groups and tr.num_groups == size
+    # every transposed group picks exactly one member of each group
+    for tg in tr.groups:
+        assert sorted(assign[r] for r in tg) == list(range(rg.num_groups))
+    assert tr.transpose() == rg
+
+
+@SLOW
+@given(st.sampled_from([(4, 1, 4), (4, 2, 2), (8, 2, 2), (8, 1, 2), (8, 4, 2), (6, 3, 2), (6, 1, 3)]),
+       st.sampled_from(["add", "mean"]), st.integers(1, 7))
+def test_strided_collectives_match_numpy(cfg, op, nelms):
+    from popxl_addons_b200.ops.replicated_strided_collectives import (replicated_all_gather_strided,
+                                                                     replicated_all_reduce_strided,
+                                                                     replicated_reduce_scatter_strided)
+
+    rf, stride, size = cfg
+    data = np.random.RandomState(nelms).rand(rf, nelms).astype(np.float32)
+    ir = popxl.Ir(rf)
+    with ir.main_graph:
+        h = popxl.h2d_stream((nelms,), popxl.float32)
+        x = ops.host_load(h)
+        rg = ir.replica_grouping(stride=stride, group_size=size)
+        s_ar = addons.host_store(replicated_all_reduce_strided(x, op, rg))
+        rs = replicated_reduce_scatter_strided(x, op, rg)
+        s_rs = addons.host_store(rs)
+        s_ag = addons.host_store(replicated_all_gather_strided(rs, rg))
+    with popxl.Session(ir, "cpu") as s:
+        out = s.run({h: data})
+    red = np.sum if op == "add" else np.mean
+    n = -(-nelms // size)
+    for r in range(rf):
+        block = r // (stride * size)
+        members = [block * stride * size + r % stride + j * stride for j in range(size)]
+        want = red(data[members], axis=0)
+        np.testing.assert_allclose(out[s_ar][r], want, rtol=1e-5)
+        flat = np.concatenate([want, np.zeros(n * size - nelms, np.float32)])
+        i = members.index(r)
+        np.testing.assert_allclose(out[s_rs][r], flat[i * n:(i + 1) * n], rtol=1e-5)
+        np.testing.assert_allclose(out[s_ag][r], flat, rtol=1e-5)
+
+
+@FAST
+@given(st.integers(1, 4), st.integers(1, 3), st.sampled_from([4, 8, 64]), st.sampled_from([-1, 0]), st.integers(0, 1000))
+def test_group_quantisation_error_is_at_most_half_a_step(rows, groups, gs, dim, seed):
+    from popxl_addons_b200.ops.group_quantize_decompress import (group_quantize_compress_numpy,
+                                                                group_quantize_decompress_numpy)
+
+    x = np.random.RandomState(seed).randn(rows, groups * gs).astype(np.float32)
+    if dim == 0:
+        x = np.ascontiguousarray(x.T)
+    packed, scale, bias = group_quantize_compress_numpy(x, gs, dim)
+    assert packed.dtype == np.uint16 and packed.shape == (rows, groups, gs // 4) and scale.shape == (rows, groups, 1)
+    back = group_quantize_decompress_numpy(packed, scale, bias, dim)
+    assert back.shape == x.shape
+    step = np.repeat(scale[..., 0], gs, axis=-1)
+    step = step if dim == -1 else step.T
+    assert np.all(np.abs(back - x) <= 0.5 * step + 1e-6)
+    # the extremes of every group are reproduced exactly (codes 0 and 15)
+    g = (x if dim == -1 else x.T).reshape(rows, groups, gs)
+    b = (back if dim == -1 else back.T).reshape(rows, groups, gs)
+    np.testing.assert_allclose(b.min(-1), g.min(-1), atol=1e-6)
+    np.testing.assert_allclose(b.max(-1), g.max(-1), rtol=1e-5, atol=1e-5)
+
+
+@FAST
+@given(st.floats(1e-6, 1e6), st.sampled_from(["float8_143", "float8_152"]), st.integers(0, 100))
+def test_fp8_amax_scale_uses_the_top_octave_without_overflow(magnitude, fmt, seed):
+    from popxl_addons_b200.ops.fp8_utils import FP8_FORMATS
+
+    data = (np.random.RandomState(seed).rand(16).astype(np.float32) - 0.5) * np.float32(magnitude)
+    ir = popxl.Ir()
+    with ir.main_graph:
+        sc = addons.host_store(addons.fp8_amax_scale(popxl.variable(data), getattr(popxl, fmt)))
+    with popxl.Session(ir, "cpu") as s:
+        scale = int(s.run({})[sc])
+    assert -31 <= scale <= 31
+    amax, fmax = float(np.abs(data).max()), FP8_FORMATS[fmt]["max"]
+    if -31 < scale < 31:
+        assert amax * 2.0 ** scale <= fmax * (1 + 1e-6)      # no overflow after scaling
+        assert amax * 2.0 ** (scale + 1) > fmax * (1 - 1e-6)  # and one more octave would overflow
