@@ -4,6 +4,7 @@
     import popxl                             # -> popxl_addons_b200.xl
     import popxl_addons as addons            # -> popxl_addons_b200
     from popxl_addons.layers import Linear   # any submodule path of either package
+    import popdist                           # -> launcher queries answered from the torchrun environment
 
 The aliases are import-system entries only: `popxl.X` is the module `popxl_addons_b200.xl.X`, `popxl_addons.X` is
 `popxl_addons_b200.X`; nothing is copied or wrapped. A real `popxl` installation, if there is one, is left alone
@@ -41,6 +42,29 @@ class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
 _FINDER = None
 
 
+def _popdist_module():
+    """The launcher queries programs make through `popdist`, answered from the `torchrun` environment: an "instance"
+    is a process, and every process hosts `devices_per_replica` = 1 device of one replica unless the program's `Ir`
+    says otherwise."""
+    import os
+    import types
+
+    def _env(name, default):
+        return int(os.environ.get(name, default))
+
+    m = types.ModuleType("popdist")
+    m.__doc__ = _popdist_module.__doc__
+    m.isPopdistEnvSet = lambda: _env("WORLD_SIZE", 1) > 1
+    m.getInstanceIndex = lambda: _env("RANK", 0)
+    m.getNumInstances = lambda: _env("WORLD_SIZE", 1)
+    m.getNumTotalReplicas = lambda: _env("WORLD_SIZE", 1)
+    m.getNumLocalReplicas = lambda: 1
+    m.getReplicaIndexOffset = lambda: _env("RANK", 0)
+    m.getNumIpusPerReplica = lambda: 1
+    m.getDeviceId = lambda: _env("LOCAL_RANK", 0)
+    return m
+
+
 def install(force: bool = False) -> None:
     """Make `import popxl` and `import popxl_addons` (and their submodules) resolve to this package. Submodules that
     are already imported are registered at once, so a later `from popxl.ops.call import ...` neither re-imports them
@@ -61,6 +85,13 @@ def install(force: bool = False) -> None:
             except Exception:  # optional pieces (native library on a machine without it, ...): resolved lazily
                 continue
             sys.modules.setdefault(alias + info.name[len(real):], mod)
+    if force or "popdist" not in sys.modules:
+        try:
+            if force:
+                raise ImportError
+            importlib.import_module("popdist")  # a genuine launcher library wins
+        except ImportError:
+            sys.modules["popdist"] = _popdist_module()
     if _FINDER is None:
         _FINDER = _AliasFinder()
         sys.meta_path.insert(0, _FINDER)

@@ -390,3 +390,49 @@ def test_session_host_interface_and_recorded_options():
         s.run_with_outputs({h: data}, outs)
         np.testing.assert_array_equal(outs[d], data * 2)
     assert not s.is_attached
+
+
+def test_import_aliases_resolve_to_this_package():
+    """`import popxl_addons_b200.compat` lets an unedited popxl / popxl_addons program import and run."""
+    import subprocess
+    import sys
+    import textwrap
+
+    prog = textwrap.dedent("""
+        import numpy as np
+        import popxl_addons_b200.compat
+        import popxl, popdist
+        from popxl import ops
+        import popxl.ops as ops2
+        import popxl_addons as addons
+        from popxl_addons.layers import Linear
+        from popxl.tensor import Variable
+        from popxl.utils import to_numpy
+        from popxl.ops.call import CallSiteInfo
+        from popxl.transforms.autodiff import GradGraphInfo
+        from popxl_addons.ops.rotary_pos_embed.rotary_pos_embed import rotary_pos_embed
+        from popxl_addons.ops.replicated_strided_collectives.replicated_all_reduce_strided import (
+            replicated_all_reduce_strided)
+        from popxl_addons.ops.replicated_strided_collectives import replicated_all_reduce_strided as again
+        import popxl_addons_b200
+        assert popxl is popxl_addons_b200.xl and addons is popxl_addons_b200 and ops is ops2
+        assert callable(ops.call) and callable(again) and again is replicated_all_reduce_strided
+        assert callable(addons.transforms.autodiff) and callable(popxl.transforms.autodiff)
+        assert not popdist.isPopdistEnvSet() and popdist.getNumInstances() == 1
+        ir = popxl.Ir()
+        with ir.main_graph:
+            x = popxl.variable(np.ones((2, 3), np.float32))
+            assert isinstance(x, Variable)
+            facts, graph = Linear(4).create_graph(x)
+            (y,) = graph.bind(facts.init()).call(x)
+            st = addons.host_store(y)
+        with popxl.Session(ir, "ipu_model") as session:
+            print(session.run()[st].shape)
+    """)
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=repo)
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    res = subprocess.run([sys.executable, "-c", prog], capture_output=True, text=True, env=env, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert res.stdout.strip().endswith("(2, 4)")
