@@ -136,13 +136,15 @@ class TaskSession(xl.Session):
                     artifact.add_dir(tmp)
                     wandb.log_artifact(artifact)
                 return
-            while self.max_checkpoints and len(self._saved) >= self.max_checkpoints:
+            # the new checkpoint is complete (its session_info.json is written last) before an old one is removed, so a
+            # failure while writing never leaves the job without a checkpoint to restart from
+            self._write_checkpoint(checkpoint_dir, data)
+            self._saved.append(checkpoint_dir)
+            while self.max_checkpoints and len(self._saved) > self.max_checkpoints:
                 old = self._saved.popleft()
                 if _rank() == 0 and os.path.isdir(old) and os.path.abspath(old) != os.path.abspath(checkpoint_dir):
                     logger.info("Removing old checkpoint %s", old)
                     shutil.rmtree(old, ignore_errors=True)
-            self._write_checkpoint(checkpoint_dir, data)
-            self._saved.append(checkpoint_dir)
 
     def _write_checkpoint(self, checkpoint_dir: str, data: Dict[str, np.ndarray]):
         model_dir = os.path.join(checkpoint_dir, "model")

@@ -389,6 +389,49 @@ def main():
                                           "n_owned": len(tr.session._owned_state())})
         if rank == 0:
             print(json.dumps({"ranks": gathered, "n_state": len(tr.state.to_dict())}))
+    elif args.mode == "elastic":
+        # data-parallel training under the restart supervisor: checkpoints every 2 steps, heartbeats between steps; on
+        # the first attempt rank 1 stops after step 3 (a host-side failure, nothing in flight)
+        from popxl_addons_b200.models import decoder as dec
+        from popxl_addons_b200.models.decoder import DecoderConfig
+        from popxl_addons_b200.models.trainer import DecoderTrainer
+        from popxl_addons_b200.parallel.elastic import latest_checkpoint
+        from popxl_addons_b200.parallel.health import Heartbeat, PeerLost
+
+        attempt = int(os.environ.get("XL_RESTART_COUNT", "0"))
+        inject = os.environ.get("XL_TEST_INJECT_FAILURE") == "1" and attempt == 0
+        dec._SEED[0] = 0
+        cfg = DecoderConfig.tiny("gptj", dtype="float32", tp=1, dp=world)
+        trainer = DecoderTrainer(cfg, micro_batches=2, device="cpu", lr=1e-2)
+        hb = Heartbeat(dist.distributed_c10d._get_default_store(), rank, world)
+        start = 0
+        ck = latest_checkpoint(args.ckpt)
+        if ck is not None:
+            trainer.session.load_checkpoint(ck, report_missing="error")
+            start = int(trainer.session.session_state["steps"])
+        losses = {}
+        try:
+            for step in range(start, args.steps):
+                if step > start:
+                    hb.check_peers(step - 1, timeout=20.0)
+                losses[step] = trainer.step(global_tokens(cfg, 2, seed=step)[:, rank:rank + 1])
+                if inject and rank == 1 and step == 3:
+                    hb.beat(step, "failed")
+                    os._exit(7)
+                hb.beat(step)
+                if (step + 1) % 2 == 0:
+                    hb.check_peers(step, timeout=20.0)  # the checkpoint gathers over all ranks
+                    trainer.session.save_checkpoint(os.path.join(args.ckpt, f"step{step + 1}"))
+        except PeerLost:
+            os._exit(3)
+        w = trainer.session.get_tensor_data(trainer.weights.layer0.get("mlp.fc_in.weight"))
+        if rank == 0:
+            with open(os.path.join(args.ckpt, "result.json"), "w") as f:
+                json.dump({"attempt": attempt, "resumed_from": start, "losses": losses,
+                           "w": np.asarray(w, np.float64).ravel()[:64].tolist(), "w_sum": float(np.abs(w).sum()),
+                           "steps": int(trainer.session.session_state["steps"])}, f)
+        dist.barrier()
+        os._exit(0)
     elif args.mode == "fail":
         # rank 1 stops between steps; rank 0 notices on the host before launching anything that would wait for it
         from datetime import timedelta

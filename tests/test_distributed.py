@@ -66,6 +66,36 @@ def test_rank_loss_is_detected_on_the_host():
     assert res["detected"] and res["missing"] == [1] and res["step"] == 2
 
 
+def test_supervisor_restarts_from_the_latest_checkpoint(tmp_path):
+    """Rank 1 fails on the host after step 3 of the first attempt: rank 0 learns it from the heartbeat and leaves, the
+    supervisor starts the job again, both ranks resume from the checkpoint of step 2 and finish. The result equals the
+    uninterrupted run bit for bit (CPU ranks over gloo)."""
+    from popxl_addons_b200.parallel.elastic import Supervisor, latest_checkpoint
+
+    worker = os.path.join(HERE, "dist_worker.py")
+    results = {}
+    for name, inject in (("plain", "0"), ("interrupted", "1")):
+        root = tmp_path / name
+        root.mkdir()
+        sup = Supervisor([worker, "--mode", "elastic", "--steps", "6", "--ckpt", str(root)], nproc=2, max_restarts=2,
+                         env={"XL_TEST_INJECT_FAILURE": inject}, grace_s=30.0, log=lambda m: None)
+        assert sup.run() == 0
+        with open(root / "result.json") as f:
+            results[name] = (json.load(f), sup.attempts)
+        assert latest_checkpoint(str(root)).endswith("step6")
+    plain, attempts = results["plain"]
+    assert attempts == [[0, 0]] and plain["attempt"] == 0 and plain["resumed_from"] == 0 and plain["steps"] == 6
+    got, attempts = results["interrupted"]
+    assert len(attempts) == 2 and attempts[0] == [3, 7] and attempts[1] == [0, 0]
+    assert got["attempt"] == 1 and got["resumed_from"] == 2 and got["steps"] == 6
+    assert got["w"] == plain["w"] and got["w_sum"] == plain["w_sum"]
+    assert [got["losses"][str(s)] for s in range(2, 6)] == [plain["losses"][str(s)] for s in range(2, 6)]
+    # a directory without session_info.json (a checkpoint that was being written) is not picked up
+    (tmp_path / "plain" / "step8" / "model").mkdir(parents=True)
+    assert latest_checkpoint(str(tmp_path / "plain")).endswith("step6")
+    assert latest_checkpoint(str(tmp_path / "nothing")) is None
+
+
 @pytest.mark.gpu
 @pytest.mark.multigpu
 @pytest.mark.parametrize("tp,dp", [(1, 2), (2, 1)])
