@@ -29,20 +29,24 @@ class BoundGraph:
     def call(self, *targs, args: Optional[Mapping[xl.Tensor, xl.Tensor]] = None) -> Tuple[xl.Tensor, ...]:
         return self.call_with_info(*targs, args=args).outputs
 
-    def bind(self, more: Mapping[xl.Tensor, xl.Tensor]) -> "BoundGraph":
-        """New BoundGraph with `more` (graph input -> caller tensor) connected on top of what is already bound."""
+    def bind(self, args: Mapping[xl.Tensor, xl.Tensor]) -> "BoundGraph":
+        """New BoundGraph with `args` (graph input -> caller tensor) connected on top of what is already bound."""
         merged = dict(self.args)
-        merged.update(more)
+        merged.update(args)
         return BoundGraph(self.graph, merged)
 
-    def subgraph_io_map(self, *targs, args: Optional[Mapping[xl.Tensor, xl.Tensor]] = None):
-        """`{graph input: caller tensor}` exactly as `call(*targs, args=args)` would connect them."""
+    def subgraph_io_map(self, *targs, args: Optional[Mapping[xl.Tensor, xl.Tensor]] = None,
+                        outs: Optional[Iterable[xl.Tensor]] = None):
+        """`{graph input: caller tensor}` exactly as `call(*targs, args=args)` would connect them, plus
+        `{graph output: caller tensor}` for the call's outputs `outs`, if given."""
         merged = dict(self.args)
         if args:
             merged.update(args)
         free = [t for t in self.graph.inputs if t not in merged]
         for g_in, t in zip(free, targs):
             merged[g_in] = t
+        for g_out, t in zip(self.graph.outputs, outs or ()):
+            merged[g_out] = t
         return merged
 
 

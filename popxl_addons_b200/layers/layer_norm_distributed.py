@@ -2,6 +2,8 @@
 Parity: popxl_addons/layers/layer_norm_distributed.py:13-35."""
 from functools import partial
 
+from typing import Optional
+
 import numpy as np
 
 from .. import xl
@@ -17,7 +19,8 @@ class LayerNormDistributed(Module):
         self.replica_grouping = replica_grouping
         self.eps = eps
 
-    def build(self, x: xl.Tensor) -> xl.Tensor:
+    def build(self, x: xl.Tensor, eps: Optional[float] = None) -> xl.Tensor:
+        """`eps` overrides the layer's own value for this graph (the reference passes it here, default 1e-5)."""
         np_dt = x.dtype.as_numpy() if x.dtype._numpy is not None else np.float32
         # parameters differ between the replicas of the group, i.e. they are identical across its transpose
         param_rg = self.replica_grouping.transpose()
@@ -25,4 +28,4 @@ class LayerNormDistributed(Module):
                                     replica_grouping=param_rg)
         b = self.add_variable_input("bias", partial(np.zeros, x.shape[-1], np_dt), x.dtype,
                                     replica_grouping=param_rg)
-        return layer_norm_distributed(x, w, b, self.eps, self.replica_grouping)
+        return layer_norm_distributed(x, w, b, self.eps if eps is None else eps, self.replica_grouping)

@@ -14,9 +14,28 @@ from . import xl
 from .xl.core import pb_op_type
 from .xl.utils import table_to_string
 
-__all__ = ["total_FLOPs", "evaluate_ir_FLOPs", "evaluate_FLOPs", "print_FLOPs", "format_flops_scientific"]
+__all__ = ["total_FLOPs", "evaluate_ir_FLOPs", "evaluate_FLOPs", "print_FLOPs", "format_flops_scientific",
+           "matmul_flops", "elementwise_binary_flops", "group_norm_flops"]
 
 _ELEMENTWISE = {"add", "sub", "mul", "div", "pow", "maximum", "minimum", "fmod", "add_", "scaled_add", "scaled_add_"}
+
+
+def _unwrap(op):
+    return getattr(op, "_op", op)  # popart-style view (`graph._pb_graph.getOps()`) or the op itself
+
+
+def matmul_flops(op) -> int:
+    """`2 * K * (elements of the result)`: 2m for a dot product, 2mn for matrix x vector, 2bmnp batched."""
+    op = _unwrap(op)
+    return int(2 * op.inputs[0].shape[-1] * op.outputs[0].nelms)
+
+
+def elementwise_binary_flops(op) -> int:
+    return int(_unwrap(op).outputs[0].nelms)
+
+
+def group_norm_flops(op) -> int:
+    return _group_norm_flops(_unwrap(op))
 
 
 def _group_norm_flops(op) -> int:

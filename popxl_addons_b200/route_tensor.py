@@ -35,8 +35,8 @@ def is_subgraph(parent: xl.Graph, subgraph: xl.Graph) -> bool:
     return False
 
 
-def called_graph_paths(parent: xl.Graph, subgraph: xl.Graph) -> Set[Tuple[xl.Graph, ...]]:
-    """All chains of graphs `(g1, ..., subgraph)` such that `parent` calls g1, g1 calls g2, ..."""
+def called_graph_paths(parent_graph: xl.Graph, subgraph: xl.Graph) -> Set[Tuple[xl.Graph, ...]]:
+    """All chains of graphs `(g1, ..., subgraph)` such that `parent_graph` calls g1, g1 calls g2, ..."""
     paths: Set[Tuple[xl.Graph, ...]] = set()
 
     def walk(g: xl.Graph, prefix: Tuple[xl.Graph, ...]):
@@ -47,7 +47,7 @@ def called_graph_paths(parent: xl.Graph, subgraph: xl.Graph) -> Set[Tuple[xl.Gra
             elif c not in prefix:
                 walk(c, chain)
 
-    walk(parent, ())
+    walk(parent_graph, ())
     return paths
 
 
@@ -57,9 +57,11 @@ def _add_call_input(op, tensor: xl.Tensor, modified: bool):
         op.attrs.setdefault("modified", set()).add(tensor)
 
 
-def route_tensor_into_graph(t: xl.Tensor, graph: Optional[xl.Graph] = None, modified: bool = False) -> xl.Tensor:
-    """Tensor inside `graph` (default: the current graph) that carries the value of `t`, which lives in a graph
+def route_tensor_into_graph(tensor: xl.Tensor, graph: Optional[xl.Graph] = None,
+                            modified: bool = False) -> xl.Tensor:
+    """Tensor inside `graph` (default: the current graph) that carries the value of `tensor`, which lives in a graph
     that (transitively) calls `graph`. `modified=True` marks it as written by the sub-graph (by-reference)."""
+    t = tensor
     graph = graph or xl.gcg()
     if not isinstance(t, xl.Tensor):
         raise TypeError(f"Not a tensor: {t}")

@@ -23,6 +23,7 @@ import numpy as np
 from . import xl
 from .named_tensors import NamedTensorData, NamedTensors
 from .streams import InputStreams, OutputStreams
+from .variable_factory import open_variable_file
 from .utils import timer
 
 try:  # optional
@@ -153,8 +154,10 @@ class TaskSession(xl.Session):
         for name, array in data.items():
             init = self.ir.initial_values.get(named[name])
             if isinstance(init, np.memmap) and getattr(init, "filename", None):
-                # keep memmap-backed variables as plain .npy files that can be memory-mapped again
-                np.save(os.path.join(model_dir, f"{name}.npy"), np.asarray(array))
+                # memmap-backed variables keep their file name and raw layout (as in the reference, which copies the
+                # memmap file), so the file can be put back into a memmap directory and mapped again
+                np.ascontiguousarray(np.asarray(array), dtype=init.dtype).tofile(
+                    os.path.join(model_dir, os.path.basename(str(init.filename))))
             else:
                 np.savez(os.path.join(model_dir, f"{name}.npz"), **{name: array})
         if _rank() != 0:
@@ -185,8 +188,18 @@ class TaskSession(xl.Session):
             with np.load(path, allow_pickle=True) as z:
                 loaded[name] = z[name] if name in z.files else z[z.files[0]]
         if not skip_memmap:
+            # files of memmap-backed variables are named after the variable's memmap file
+            by_file = {}
+            for key, var in self.state.to_dict().items():
+                mm = getattr(var, "_memmap_arr", None)
+                fname = os.path.basename(str(mm.filename)) if mm is not None and getattr(mm, "filename", None) else None
+                by_file[fname or f"{key}.npy"] = (key, var)
             for path in sorted(glob.glob(os.path.join(model_dir, "*.npy"))):
-                loaded[os.path.basename(path)[:-4]] = np.load(path, mmap_mode="r")
+                if os.path.basename(path) in by_file:
+                    key, var = by_file[os.path.basename(path)]
+                    loaded[key] = open_variable_file(path, var.dtype.as_numpy(), var.shape_on_host, "r")
+                else:
+                    loaded[os.path.basename(path)[:-4]] = np.load(path, mmap_mode="r")
         self._load_named(loaded, report_missing)
         dl_path = os.path.join(checkpoint_dir, "dataloader.bin")
         if self._dataloader is not None and os.path.exists(dl_path):

@@ -11,10 +11,10 @@ from .xl import ops
 __all__ = ["ops_of_type", "TensorInput", "run_module"]
 
 
-def ops_of_type(ops_: Iterable, op_type: Union[str, type]) -> int:
+def ops_of_type(ops: Iterable, op_type: Union[str, type]) -> int:
     """Number of ops whose type name equals `op_type` (a string such as `"matmul"`)."""
     name = op_type if isinstance(op_type, str) else getattr(op_type, "__name__", str(op_type))
-    return sum(1 for o in ops_ if o.opdef.name == name)
+    return sum(1 for o in ops if o.opdef.name == name)
 
 
 class TensorInput:

@@ -32,8 +32,8 @@ def autodiff(graph: GraphWithNamedArgs, grads_provided: Optional[Iterable[xl.Ten
 
 
 def autodiff_with_accumulation(graph: GraphWithNamedArgs, tensors_to_accumulate_grads: Iterable[xl.Tensor],
-                               grads_required: Optional[Iterable[xl.Tensor]] = None,
                                grads_provided: Optional[Iterable[xl.Tensor]] = None,
+                               grads_required: Optional[Iterable[xl.Tensor]] = None,
                                called_graphs_grad_info: Optional[Mapping[xl.Graph, GradGraphInfo]] = None,
                                replica_groupings=None,
                                accum_dtype: Optional[xl.dtype] = None, fuse_matmul: bool = True

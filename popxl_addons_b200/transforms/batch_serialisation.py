@@ -250,6 +250,24 @@ def batch_serialise(graph: GraphWithNamedArgs, steps: int,
     return _build(graph, steps, load_handles, store_streams, store_buffers, seed_input, rows, io_mode)
 
 
+def batch_serialise_non_overlapped(graph: GraphWithNamedArgs, steps: int, load_handles, store_streams, store_buffers,
+                                   seed_input: Optional[xl.Tensor] = None, rows: int = 1,
+                                   use_io_tiles: bool = False) -> BatchSerialResult:
+    """`batch_serialise` with loads, compute and stores of one micro-batch in sequence (`io_mode` "io" when
+    `use_io_tiles`, else "compute")."""
+    return batch_serialise(graph, steps, load_handles, store_streams, store_buffers, seed_input, rows,
+                           "io" if use_io_tiles else "compute")
+
+
+def batch_serialise_overlapped(graph: GraphWithNamedArgs, steps: int, load_handles, store_streams, store_buffers,
+                               seed_input: Optional[xl.Tensor] = None, rows: int = 1) -> BatchSerialResult:
+    """`batch_serialise` with the loop software-pipelined: load of micro-batch i+1, compute of i and store of i-1
+    overlap (`io_mode="io_overlapped"`, needs at least 2 steps)."""
+    if steps < 2:
+        raise ValueError("Overlapped batch serialisation needs at least 2 steps")
+    return batch_serialise(graph, steps, load_handles, store_streams, store_buffers, seed_input, rows, "io_overlapped")
+
+
 def batch_serialise_fwd_and_grad(forward_graph: GraphWithNamedArgs, gradient_graph: GraphWithNamedArgs,
                                  named_inputs_for_grad_graph: NamedTensors, steps: int,
                                  load_handles: Dict[xl.Tensor, Any], store_streams: Dict[xl.Tensor, Any],

@@ -9,11 +9,12 @@ from ..xl import ops
 __all__ = ["repeat_graph"]
 
 
-def repeat_graph(graph: xl.Graph, n: int) -> xl.Graph:
+def repeat_graph(graph: xl.Graph, repeat_count: int) -> xl.Graph:
     """In place: move every op of `graph` into a new sub-graph and replace them by one `repeat` of it. Variables and
     graph inputs that the ops touch are passed by reference, so state carried between iterations lives in them."""
+    n = int(repeat_count)
     if n < 1:
-        raise ValueError("n must be >= 1")
+        raise ValueError("repeat_count must be >= 1")
     ir = graph.ir
     body = ir.create_empty_graph(graph.name + "_repeat_body")
     moved = list(graph.ops)

@@ -64,13 +64,13 @@ def timer(title=None, log_to_wandb=True):
 class OrderedDict(collections.OrderedDict):
     """Ordered dict with positional access (`idx`) and a line-per-item repr."""
 
-    def idx(self, i: int):
+    def idx(self, idx: int):
         for n, v in enumerate(self.values()):
-            if n == i:
+            if n == idx:
                 return v
-        if i < 0:
-            return list(self.values())[i]
-        raise IndexError(i)
+        if idx < 0:
+            return list(self.values())[idx]
+        raise IndexError(idx)
 
     def __repr__(self):
         body = "".join(f"{k}: {v},\n" for k, v in self.items())

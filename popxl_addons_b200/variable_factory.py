@@ -66,6 +66,28 @@ def _process_rank() -> int:
     return int(os.environ.get("RANK", "0"))
 
 
+_NPY_MAGIC = b"\x93NUMPY"
+
+
+def open_variable_file(path: str, np_dtype, shape, mode: str = "r") -> np.memmap:
+    """Memory-map the host file of a variable: a raw array (what `np.memmap` and the reference write) or a `.npy` file
+    with a numpy header. Shape and dtype are checked against the variable (for raw files: the file size)."""
+    np_dtype, shape = np.dtype(np_dtype), tuple(int(d) for d in shape)
+    with open(path, "rb") as f:
+        has_header = f.read(len(_NPY_MAGIC)) == _NPY_MAGIC
+    if has_header:
+        mm = np.lib.format.open_memmap(path, mode=mode)
+        if tuple(mm.shape) != shape or mm.dtype != np_dtype:
+            raise ValueError(f"Existing memmap {path} has shape {mm.shape} / dtype {mm.dtype}; "
+                             f"expected {shape} / {np_dtype}")
+        return mm
+    nbytes = int(np.prod(shape, dtype=np.int64)) * np_dtype.itemsize
+    if os.path.getsize(path) != nbytes:
+        raise ValueError(f"Existing memmap {path} holds {os.path.getsize(path)} bytes; expected {nbytes} "
+                         f"({shape} / {np_dtype})")
+    return np.memmap(path, dtype=np_dtype, shape=shape, mode=mode)
+
+
 class VariableFactory:
     def __init__(self, data_iter: Union[Callable[[], np.ndarray], Iterable[np.ndarray]],
                  dtype: Optional[xl.dtype] = None, name: Optional[str] = None, by_ref: bool = False,
@@ -118,8 +140,17 @@ class VariableFactory:
         return xl.graph_input(self.shape, self.dtype, name, by_ref=self.by_ref, meta_shape=self.meta_shape)
 
     # -- variable side ------------------------------------------------------------------------------------------
-    def next_data(self) -> np.ndarray:
+    def _host_shape(self):
         n = self.replica_grouping.num_groups
+        full = self.meta_shape if self.replica_sharded else self.shape
+        return (n, *full) if n > 1 else tuple(full)
+
+    def next_data(self, empty: bool = False) -> np.ndarray:
+        """Host data for the next variable: one draw per replica group, stacked on a leading axis when there is more
+        than one group. `empty=True` skips the draws and returns uninitialised memory of the right shape."""
+        n = self.replica_grouping.num_groups
+        if empty:
+            return np.empty(self._host_shape(), self.dtype.as_numpy() if self.dtype._numpy is not None else np.float32)
         first = next(self.data_iter)
         if isinstance(first, xl.LazyInit):
             return first.with_groups(n) if n > 1 else first
@@ -127,38 +158,35 @@ class VariableFactory:
             return np.stack([np.asarray(first)] + [np.asarray(next(self.data_iter)) for _ in range(n - 1)])
         return np.asarray(first)
 
-    def next_memmap(self, path: str, empty: bool = False, read_only_if_exists: bool = False) -> np.memmap:
-        """Backing `.npy` file for the variable: opened if it exists, else created (by process 0) and filled."""
-        n = self.replica_grouping.num_groups
-        full = self.meta_shape if self.replica_sharded else self.shape
-        shape = (n, *full) if n > 1 else tuple(full)
+    def next_memmap(self, memmap_dir: str, name: str, empty: bool = False,
+                    read_only_if_exists: bool = False) -> np.memmap:
+        """Backing file `<memmap_dir>/<name>.npy` of the variable: opened if it exists, else created (by process 0)
+        and filled with the next data. New files are raw arrays without a header, the layout the reference writes
+        (`np.memmap`), so memmap directories and the memmap files inside checkpoints are interchangeable with it;
+        files that carry a numpy header are read as well."""
+        path = os.path.join(memmap_dir, name + ".npy")
+        shape = self._host_shape()
         np_dtype = self.dtype.as_numpy()
-        exists = os.path.exists(path)
-        if exists:
-            mode = "r" if read_only_if_exists else "r+"
-            mm = np.lib.format.open_memmap(path, mode=mode)
-            if tuple(mm.shape) != tuple(shape) or mm.dtype != np_dtype:
-                raise ValueError(f"Existing memmap {path} has shape {mm.shape} / dtype {mm.dtype}; "
-                                 f"expected {shape} / {np_dtype}")
+        if os.path.exists(path):
             _barrier()
-            return mm
+            return open_variable_file(path, np_dtype, shape, "r" if read_only_if_exists else "r+")
         if _process_rank() == 0:
-            os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
-            mm = np.lib.format.open_memmap(path, mode="w+", dtype=np_dtype, shape=tuple(shape))
+            os.makedirs(memmap_dir, exist_ok=True)
+            mm = np.memmap(path, dtype=np_dtype, shape=tuple(shape), mode="w+")
             if not empty:
-                mm[...] = self.next_data().astype(np_dtype).reshape(shape)
+                mm[...] = np.asarray(self.next_data()).astype(np_dtype).reshape(shape)
             mm.flush()
             _barrier()
         else:
             if not empty:
                 self.next_data()  # keep the data stream aligned across processes
             _barrier()
-            mm = np.lib.format.open_memmap(path, mode="r+")
+            mm = open_variable_file(path, np_dtype, shape, "r+")
         return mm
 
     def _data_for(self, name, empty, memmap_dir, read_only_if_exists):
         if memmap_dir is not None:
-            return self.next_memmap(os.path.join(memmap_dir, f"{name}.npy"), empty, read_only_if_exists)
+            return self.next_memmap(memmap_dir, name, empty, read_only_if_exists)
         if empty:
             n = self.replica_grouping.num_groups
             full = self.meta_shape if self.replica_sharded else self.shape

@@ -103,7 +103,9 @@ def test_memmap_backed_variables(tmp_path):
     s, v = _linear_session(memmap_dir=mm)
     assert sorted(os.listdir(mm)) == ["bias.npy", "weight.npy"]
     w = s.get_tensor_data(v.weight)
-    np.testing.assert_array_equal(np.load(os.path.join(mm, "weight.npy")), w)
+    # raw arrays without a header: the layout the reference's `np.memmap` files have
+    np.testing.assert_array_equal(np.fromfile(os.path.join(mm, "weight.npy"), np.float32).reshape(w.shape), w)
+    assert w is v.weight._memmap_arr and isinstance(w, np.memmap)
     s2, v2 = _linear_session(memmap_dir=mm)  # existing files are re-opened, not re-initialised
     np.testing.assert_array_equal(s2.get_tensor_data(v2.weight), w)
     s.save_checkpoint(str(tmp_path / "ck"))
@@ -113,6 +115,16 @@ def test_memmap_backed_variables(tmp_path):
     np.testing.assert_array_equal(s3.get_tensor_data(v3.weight), w)
     s3.load_checkpoint(str(tmp_path / "ck"))
     np.testing.assert_array_equal(s3.get_tensor_data(v3.weight), w)
+    # files with a numpy header are accepted too, and a file of the wrong size is refused
+    mm3 = tmp_path / "mm3"
+    mm3.mkdir()
+    np.save(mm3 / "weight.npy", np.asarray(w))
+    np.save(mm3 / "bias.npy", np.asarray(s.get_tensor_data(v.bias)))
+    s4, v4 = _linear_session(memmap_dir=str(mm3))
+    np.testing.assert_array_equal(s4.get_tensor_data(v4.weight), w)
+    np.asarray(w).ravel()[:-1].tofile(mm3 / "weight.npy")
+    with pytest.raises(ValueError, match="expected"):
+        _linear_session(memmap_dir=str(mm3))
 
 
 def test_seed_variable_identical_within_group_and_checkpointed():
