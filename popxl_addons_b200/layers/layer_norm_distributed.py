@@ -14,10 +14,15 @@ __all__ = ["LayerNormDistributed"]
 
 
 class LayerNormDistributed(Module):
-    def __init__(self, replica_grouping: xl.ReplicaGrouping, eps: float = 1e-5):
+    def __init__(self, replica_grouping: Optional[xl.ReplicaGrouping] = None, eps: float = 1e-5):
+        """`replica_grouping`: the replicas the hidden axis is sharded over (default: all replicas)."""
         super().__init__()
-        self.replica_grouping = replica_grouping
+        self._replica_grouping = replica_grouping
         self.eps = eps
+
+    @property
+    def replica_grouping(self) -> xl.ReplicaGrouping:
+        return self._replica_grouping if self._replica_grouping is not None else xl.gcg().ir.replica_grouping()
 
     def build(self, x: xl.Tensor, eps: Optional[float] = None) -> xl.Tensor:
         """`eps` overrides the layer's own value for this graph (the reference passes it here, default 1e-5)."""

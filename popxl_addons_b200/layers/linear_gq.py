@@ -137,7 +137,7 @@ class LinearGQ(Module):
         return emit1("linear_gq", ins, {"dim": self.dim})
 
     @staticmethod
-    def torch_mapping(variables: NamedTensors, nn_layer, dtype: xl.dtype = xl.float16, group_size: int = 64,
+    def torch_mapping(variables: NamedTensors, nn_layer, dtype: xl.dtype = xl.float32, group_size: int = 64,
                       dim: int = -1) -> WeightsDict:
         """Compress a `torch.nn.Linear` weight (stored `(out, in)`) into the layer's variables; scales, zero points
         and the bias are converted to `dtype`, the dtype of the layer's input."""

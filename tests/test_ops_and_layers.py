@@ -263,7 +263,7 @@ def test_group_quantize_and_linear_gq(dim):
     lin = torch.nn.Linear(128, 64)
     x = (rng.randn(4, 128) * 0.3).astype(np.float16)
     (y,) = run_module(LinearGQ(64, group_size=64, dim=dim), TensorInput(x, popxl.float16), device="cpu",
-                      weights=partial(LinearGQ.torch_mapping, nn_layer=lin, group_size=64, dim=dim))
+                      weights=partial(LinearGQ.torch_mapping, nn_layer=lin, dtype=popxl.float16, group_size=64, dim=dim))
     np.testing.assert_allclose(y.astype(np.float32), lin(torch.tensor(x).float()).detach().numpy(), atol=0.1)
 
 
