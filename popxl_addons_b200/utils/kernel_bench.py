@@ -103,6 +103,33 @@ def main():
     gemm_row("gemm attn pv", 2048, 256, 2048, batch=16)
     gemm_row("gemm square 8192", 8192, 8192, 8192)
 
+    def attention_row(name, S, H, D):
+        """Causal attention forward of one GPT-J micro-batch: the default path (scores GEMM with causal tile skipping,
+        fused softmax, PV GEMM) and, with XL_FLASH_ATTENTION=1, the single-kernel forward on the same packed qkv."""
+        if not want(name):
+            return
+        hd = H * D
+        qkv = (torch.randn(S, 3 * hd, device="cuda") * 0.5).to(bf)
+        sin = torch.zeros(1, S, 1, device="cuda", dtype=bf)
+        scale = D ** -0.5
+        fl = 2.0 * 2 * S * S * D * H / 2  # two products, half of each masked
+        opt_in, nat._FLASH_ATTENTION = nat._FLASH_ATTENTION, False
+        try:
+            default = time_ms(lambda: nat.attention_qkv_cuda(qkv, sin, sin, S, H, D, 0, True, scale, True),
+                              iters=args.iters)
+        finally:
+            nat._FLASH_ATTENTION = opt_in
+        rows.append(dict(kernel=name + " (GEMM + softmax + GEMM)", shape=f"{H}x{S}x{S}x{D}", ms=default,
+                         tflops=fl / default / 1e9, frac_of_peak=fl / default / 1e9 / peaks["bf16_tflops"],
+                         lib_ms=default, lib_tflops=fl / default / 1e9, vs_lib=1.0))
+        if opt_in:
+            one = time_ms(lambda: nat.flash_attention_fwd(qkv, 0, hd, 2 * hd, 1, S, H, D, scale, True), iters=args.iters)
+            rows.append(dict(kernel=name + " (single kernel)", shape=f"{H}x{S}x{S}x{D}", ms=one, tflops=fl / one / 1e9,
+                             frac_of_peak=fl / one / 1e9 / peaks["bf16_tflops"], lib_ms=default,
+                             lib_tflops=fl / default / 1e9, vs_lib=default / one))
+
+    attention_row("attention fwd causal gptj", 2048, 16, 256)
+
     def mem_row(name, fn, nbytes):
         if not want(name):
             return
