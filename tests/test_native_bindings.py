@@ -48,3 +48,36 @@ def test_ctypes_signatures_match_the_c_prototypes():
         assert want == got, f"{name}: C prototype takes {want}, ctypes declares {got}"
         checked += 1
     assert checked >= 45
+
+
+def test_every_call_site_passes_as_many_arguments_as_the_binding_declares():
+    """Most launches sit on GPU-only branches: a wrong argument count there would first show as a TypeError on the GPU
+    box. The call sites are counted from the source instead."""
+    import ast
+
+    from popxl_addons_b200.ops import native
+
+    root = os.path.dirname(HERE)
+    files = ["popxl_addons_b200/ops/native.py", "popxl_addons_b200/parallel/fused.py",
+             "popxl_addons_b200/models/generator.py", "popxl_addons_b200/xl/session.py",
+             "popxl_addons_b200/utils/kernel_bench.py", "tests/test_gpu_kernels.py", "tests/test_gpu_decode.py",
+             "tests/test_gpu_misc.py", "tests/dist_worker.py", "bench.py"]
+    calls = 0
+    for rel in files:
+        tree = ast.parse(open(os.path.join(root, rel)).read())
+        for node in ast.walk(tree):
+            if not isinstance(node, ast.Call):
+                continue
+            f = node.func
+            name = f.id if isinstance(f, ast.Name) else (
+                f.attr if isinstance(f, ast.Attribute) and isinstance(f.value, ast.Name)
+                and f.value.id in ("nat", "native", "_native") else None)
+            fn = getattr(native, name, None) if name else None
+            if not isinstance(fn, ctypes._CFuncPtr) or fn.argtypes is None:
+                continue
+            if any(isinstance(a, ast.Starred) for a in node.args):
+                continue
+            calls += 1
+            assert not node.keywords and len(node.args) == len(fn.argtypes), \
+                f"{rel}:{node.lineno}: {name} is called with {len(node.args)} arguments, declared with {len(fn.argtypes)}"
+    assert calls >= 50
