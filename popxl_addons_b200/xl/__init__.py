@@ -29,3 +29,20 @@ def create_seeds(seed: int, offset: int = 0, batches_per_step: int = 1, replicas
     rng = _np.random.Generator(_np.random.PCG64([int(seed), int(offset)]))
     shape = ((batches_per_step,) if batches_per_step > 1 else ()) + ((replicas,) if replicas > 1 else ()) + (2,)
     return rng.integers(0, 2 ** 32, size=shape, dtype=_np.uint64).astype(_np.uint32)
+
+
+# ---- further names and module paths of popxl ------------------------------------------------------------------------
+import enum as _enum  # noqa: E402
+
+from . import context, errors, fp8_utils, graph, streams, tensor, utils  # noqa: E402,F401
+from .context import get_current_context, get_main_graph, op_debug_context  # noqa: E402,F401
+from .transforms import io_tile_exchange, merge_exchange  # noqa: E402,F401
+
+half, double = float16, float64
+
+
+class TileSet(_enum.Enum):
+    """Where an op runs: on the compute stream or on the IO / copy stream (`io_tiles()`)."""
+
+    Compute = "compute"
+    IO = "io"
