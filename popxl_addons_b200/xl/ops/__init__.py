@@ -1373,3 +1373,5 @@ from .extra import *  # noqa: E402,F401,F403
 # finds the submodule already imported and the name `call` stays bound to the function
 from . import utils  # noqa: E402,F401
 from .call import call, call_with_info  # noqa: E402,F401,F811
+from .conv import conv  # noqa: E402,F401,F811  (`ops.conv` stays the function, `ops.conv.PadType` is reached by path)
+from . import negative_log_likelihood  # noqa: E402,F401

@@ -11,8 +11,8 @@ from typing import Optional
 
 import numpy as np
 
-from ..core import ReplicaGrouping, Tensor, gcg
-from ..opdef import OpDef, emit, emit1
+from ...core import ReplicaGrouping, Tensor, gcg
+from ...opdef import OpDef, emit, emit1
 
 _REDUCE_OPS = ("add", "mean", "max", "min", "mul")
 
@@ -96,10 +96,10 @@ def _vjp_reduce_scatter(ctx, op, gs):
     t = op.inputs[0]
     full = emit1("all_gather", [gs[0]], dict(group=op.attrs["group"]))
     if full.nelms != t.nelms:
-        from . import slice as _slice
+        from .. import slice as _slice
 
         full = _slice(full, [0], [t.nelms], [1], [0])
-    from . import reshape
+    from .. import reshape
 
     return [reshape(full, t.shape)]
 
@@ -130,7 +130,7 @@ def _infer_all_gather(op):
 
 def _vjp_all_gather(ctx, op, gs):
     g = emit1("reduce_scatter", [gs[0]], dict(group=op.attrs["group"], op="add", rts=False))
-    from . import reshape
+    from .. import reshape
 
     return [reshape(g, op.inputs[0].shape)]
 
@@ -144,7 +144,7 @@ def replicated_all_gather(t: Tensor, group: Optional[ReplicaGrouping] = None, ou
     out = emit1("all_gather", [t], dict(group=_group(group)))
     target = tuple(output_shape) if output_shape is not None else (t.meta_shape or None)
     if target:
-        from . import reshape
+        from .. import reshape
 
         out = reshape(out, target)
     return out
@@ -215,7 +215,7 @@ def _vjp_slot_all_reduce(ctx, op, gs):
     a = op.attrs
     if a["op"] not in ("add", "mean"):
         raise NotImplementedError("Only add/mean all-reduce is differentiable")
-    from . import init
+    from .. import init
 
     gs = [g if g is not None else init(o.shape, o.dtype, "zero_grad", "zero") for g, o in zip(gs, op.outputs)]
     mode = a["mode"]

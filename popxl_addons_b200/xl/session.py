@@ -23,6 +23,11 @@ from .comm import DistComm, SimComm
 from .core import Constant, Graph, Ir, LazyInit, Tensor, Variable
 
 
+# what `run` takes and returns (popxl/session.py exports the same two names)
+h2dStreamBufferMaps = Mapping[HostToDeviceStream, Any]
+d2hStreamBufferMaps = Mapping[DeviceToHostStream, np.ndarray]
+
+
 def _resolve_device(device_desc: str) -> torch.device:
     d = (device_desc or "auto").lower()
     if d in ("cpu", "ipu_model"):
