@@ -6,6 +6,7 @@ summed by the tensor-parallel all-reduce that follows.
 Parity: popxl_addons/layers/embedding.py:17-79.
 """
 import math
+from functools import partial
 from typing import Dict, List, Optional
 
 import numpy as np
@@ -14,10 +15,23 @@ from .. import xl
 from ..module import Module
 from ..named_tensors import NamedTensors
 from ..xl import ops
+from .linear import truncnorm_init
 
 __all__ = ["Embedding"]
 
 _SHARD_MULTIPLE = 16
+
+
+def model_vocab_shard_size(vocab_size: int, n_shards: int) -> int:
+    """Rows per vocabulary shard in the decoder models of this package: padded to a multiple of 16 only when the
+    vocabulary is actually sharded."""
+    if n_shards <= 1:
+        return vocab_size
+    return Embedding.get_vocab_shard_size(vocab_size, n_shards)
+
+
+def model_vocab_offsets(vocab_size: int, n_shards: int) -> np.ndarray:
+    return np.arange(n_shards, dtype=np.int64) * model_vocab_shard_size(vocab_size, n_shards)
 
 
 class Embedding(Module):
@@ -35,8 +49,8 @@ class Embedding(Module):
 
     @staticmethod
     def get_vocab_shard_size(vocab_size: int, n_shards: int) -> int:
-        if n_shards <= 1:
-            return vocab_size
+        """Rows per shard: `ceil(vocab_size / n_shards)` rounded up to a multiple of 16, also for a single shard (the
+        reference's rule, popxl_addons/layers/embedding.py:48-52: a checkpoint of its embedding has that many rows)."""
         return _SHARD_MULTIPLE * math.ceil(math.ceil(vocab_size / n_shards) / _SHARD_MULTIPLE)
 
     @staticmethod
@@ -52,7 +66,7 @@ class Embedding(Module):
         """`indices` must already have this shard's offset subtracted when the vocabulary is sharded."""
         np_dt = self.dtype.as_numpy() if self.dtype._numpy is not None else np.float32
         shape = (self.vocab_shard_size, self.hidden_size)
-        w = self.add_variable_input("weight", lambda: np.random.normal(0, 0.02, shape).astype(np_dt), self.dtype,
+        w = self.add_variable_input("weight", partial(truncnorm_init, shape, 0.02, np_dt), self.dtype,
                                     replica_grouping=self.replica_grouping)
         return ops.gather(w, indices, axis=self.axis, zero_OOR=self.n_shards > 1)
 
@@ -60,7 +74,8 @@ class Embedding(Module):
     def torch_mapping(variables: NamedTensors, nn_layer, n_shards: int = 1) -> Dict[xl.Tensor, np.ndarray]:
         """Pads the vocabulary to `n_shards * shard_size` rows and splits it into a leading shard axis."""
         w = nn_layer.weight.data.detach().cpu().numpy()
+        size = Embedding.get_vocab_shard_size(w.shape[0], n_shards)
+        w = np.pad(w, ((0, size * n_shards - w.shape[0]), (0, 0)))
         if n_shards > 1:
-            size = Embedding.get_vocab_shard_size(w.shape[0], n_shards)
-            w = np.pad(w, ((0, size * n_shards - w.shape[0]), (0, 0))).reshape(n_shards, size, w.shape[1])
+            w = w.reshape(n_shards, size, w.shape[1])
         return {variables.weight: w.copy()}

@@ -15,7 +15,7 @@ from typing import Optional
 import numpy as np
 
 from .. import xl
-from ..layers.embedding import Embedding
+from ..layers.embedding import Embedding, model_vocab_offsets, model_vocab_shard_size
 from ..module import Module
 from ..ops.cross_entropy_sharded_loss import cross_entropy_sharded_loss
 from ..ops.replicated_all_reduce_TP import (replicated_all_reduce_identical_grad_inputs,
@@ -274,7 +274,7 @@ class DecoderEmbedding(Module):
     def build(self, tokens: xl.Tensor, shard_offset: Optional[xl.Tensor] = None) -> xl.Tensor:
         cfg = self.cfg
         par = _Parallel(cfg)
-        shard = Embedding.get_vocab_shard_size(cfg.vocab_size, par.tp)
+        shard = model_vocab_shard_size(cfg.vocab_size, par.tp)
         w = self.add_variable_input("wte.weight", _normal((shard, cfg.hidden), cfg.init_std, cfg.np_dtype),
                                     cfg.xl_dtype, replica_grouping=par.sharded_rg, overwrite=True)
         idx = tokens if shard_offset is None else tokens - shard_offset
@@ -322,7 +322,7 @@ class DecoderHead(Module):
             h = _gather_tokens(h, par)
         elif par.tp > 1:
             h = replicated_all_reduce_identical_inputs(h, group=par.tp_group)
-        shard = Embedding.get_vocab_shard_size(cfg.vocab_size, par.tp)
+        shard = model_vocab_shard_size(cfg.vocab_size, par.tp)
         wl = self.add_variable_input("lm_head.weight", _normal((cfg.hidden, shard), cfg.init_std, cfg.np_dtype),
                                      cfg.xl_dtype, replica_grouping=par.sharded_rg, overwrite=True)
         if cfg.family == "gptj":

@@ -20,7 +20,7 @@ import numpy as np
 import torch
 
 from .. import xl
-from ..layers.embedding import Embedding
+from ..layers.embedding import Embedding, model_vocab_offsets, model_vocab_shard_size
 from ..layers.linear_gq import interleave_scale_zero, linear_gq_window_t
 from ..named_tensors import NamedTensors
 from ..ops.group_quantize_decompress import group_quantize_compress_numpy
@@ -132,7 +132,7 @@ class DecoderGenerator:
             sin_np, cos_np = trig_tables(S, cfg.rotary_dim)
             sin_tab, cos_tab = xl.constant(sin_np, dt, "sin_table"), xl.constant(cos_np, dt, "cos_table")
             sin_p, cos_p = xl.constant(sin_np[None, :P], dt, "sin_prompt"), xl.constant(cos_np[None, :P], dt, "cos_prompt")
-            vshard = Embedding.get_vocab_shard_size(cfg.vocab_size, cfg.tp)
+            vshard = model_vocab_shard_size(cfg.vocab_size, cfg.tp)
             n = rg.num_groups if rg is not None else 1
 
             def rep(a):
@@ -142,7 +142,7 @@ class DecoderGenerator:
             self.ln_f = (xl.variable(np.ones(cfg.hidden, np.float32), dt, "ln_f.weight"),
                          xl.variable(np.zeros(cfg.hidden, np.float32), dt, "ln_f.bias"))
             self.head = _GQ("lm_head", vshard, cfg.hidden, self.gs, dt, rg, bias=True, scale_dtype=sdt)
-            offs = Embedding.get_offsets(cfg.vocab_size, cfg.tp).astype(np.int32)
+            offs = model_vocab_offsets(cfg.vocab_size, cfg.tp).astype(np.int32)
             self.vocab_offset = xl.variable(offs if cfg.tp > 1 else offs[0], xl.int32, "vocab_offset", replica_grouping=rg)
             self.layers = []
             for i in range(cfg.layers):

@@ -30,7 +30,7 @@ from ..task_session import TaskSession
 from ..transforms.autodiff import autodiff_with_accumulation
 from ..transforms.recomputation import recompute_graph
 from ..streams import InputStreams, OutputStreams
-from ..layers.embedding import Embedding
+from ..layers.embedding import Embedding, model_vocab_offsets, model_vocab_shard_size
 from ..xl import ops
 from .decoder import DecoderBlock, DecoderConfig, DecoderEmbedding, DecoderHead, _Parallel, rotary_tables
 
@@ -210,7 +210,7 @@ class DecoderTrainer:
             blk_acc = [blk_dfacts.init(f"layer{i}.grad") for i in range(cfg.layers)]
             offset_var = None
             if cfg.tp > 1:
-                offs = Embedding.get_offsets(cfg.vocab_size, cfg.tp).astype(np.int32)
+                offs = model_vocab_offsets(cfg.vocab_size, cfg.tp).astype(np.int32)
                 offset_var = xl.variable(offs, xl.int32, "vocab_offset", replica_grouping=par.dp_group)
 
             # ---- micro-batch graph -----------------------------------------------------------------------------

@@ -70,8 +70,9 @@ def group_quantize_decompress_numpy(t: np.ndarray, group_scale: np.ndarray, grou
 def group_quantize_compress_numpy(t: np.ndarray, group_size: int = 64,
                                   dim: int = -1) -> Tuple[np.ndarray, np.ndarray, np.ndarray]:
     """Quantise to 4 bits in groups of `group_size` along axis `dim` (moved last in the result). Per group:
-    `bias = min`, `scale = (max - min) / 15`, `code = round((x - bias) / scale)`, in the arithmetic of the input's
-    dtype. Returns `(packed uint16 (*other, n_groups, group_size / 4), scale, bias (*other, n_groups, 1))`."""
+    `bias = min`, `scale = (max - min) / 15` (both rounded to float16, as in the reference's helper),
+    `code = round((x - bias) / scale)`. Returns `(packed uint16 (*other, n_groups, group_size / 4), scale, bias
+    (*other, n_groups, 1) float16)`."""
     if group_size % 4:
         raise ValueError("group_size must be a multiple of 4")
     x = np.asarray(t)
@@ -85,16 +86,17 @@ def group_quantize_compress_numpy(t: np.ndarray, group_size: int = 64,
     if c % group_size:
         raise ValueError(f"The quantised axis ({c}) must be divisible by group_size ({group_size})")
     g = x.reshape(*lead, c // group_size, group_size)
-    lo = g.min(axis=-1, keepdims=True)
-    hi = g.max(axis=-1, keepdims=True)
-    scale = ((hi - lo) / 15).astype(x.dtype)
+    # scale and bias are float16, whatever the input's dtype: that is what the decompression op consumes
+    lo = g.min(axis=-1, keepdims=True).astype(np.float16)
+    hi = g.max(axis=-1, keepdims=True).astype(np.float16)
+    scale = (hi - lo) / np.float16(15)
     safe = np.where(scale == 0, np.ones_like(scale), scale)
     codes = np.clip(np.rint((g - lo) / safe), 0, 15).astype(np.uint16)
     codes = codes.reshape(*lead, c // group_size, group_size // 4, 4)
     packed = np.zeros(codes.shape[:-1], dtype=np.uint16)
     for i, s in enumerate(_SHIFTS):
         packed |= codes[..., i] << s
-    return packed, scale, lo.astype(x.dtype)
+    return packed, scale, lo
 
 
 from ._paths import also_importable_as  # noqa: E402

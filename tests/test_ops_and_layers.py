@@ -383,6 +383,7 @@ def test_layers_match_torch():
                       weights=partial(Embedding.torch_mapping, nn_layer=emb))
     np.testing.assert_allclose(y, emb(torch.tensor(idx).long()).detach().numpy(), rtol=1e-6)
     assert Embedding.get_vocab_shard_size(50, 4) == 16 and list(Embedding.get_offsets(50, 4)) == [0, 16, 32, 48]
+    assert Embedding.get_vocab_shard_size(50, 1) == 64  # padded to a multiple of 16 also when not sharded
 
 
 def test_sharded_embedding_partial_sums():

@@ -132,12 +132,13 @@ def test_group_quantisation_error_is_at_most_half_a_step(rows, groups, gs, dim, 
     assert back.shape == x.shape
     step = np.repeat(scale[..., 0], gs, axis=-1)
     step = step if dim == -1 else step.T
-    assert np.all(np.abs(back - x) <= 0.5 * step + 1e-6)
+    # half a quantisation step, plus the float16 rounding of the group's scale and bias
+    assert np.all(np.abs(back.astype(np.float32) - x) <= 0.5 * step.astype(np.float32) + 4e-3 * (1 + np.abs(x)))
     # the extremes of every group are reproduced exactly (codes 0 and 15)
     g = (x if dim == -1 else x.T).reshape(rows, groups, gs)
     b = (back if dim == -1 else back.T).reshape(rows, groups, gs)
-    np.testing.assert_allclose(b.min(-1), g.min(-1), atol=1e-6)
-    np.testing.assert_allclose(b.max(-1), g.max(-1), rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(b.min(-1), g.min(-1), rtol=1e-3, atol=1e-3)
+    np.testing.assert_allclose(b.max(-1), g.max(-1), rtol=4e-3, atol=4e-3)
 
 
 @FAST
