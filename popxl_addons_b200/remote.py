@@ -45,7 +45,8 @@ def create_remote_buffer(spec: xl.TensorSpec, entries: int = 1,
         nelms = int(np.prod(spec.shape)) if spec.shape else 1
         if nelms % shard_over != 0:
             raise ValueError(f"Can't shard tensor with {nelms} elements over {shard_over} replicas")
-        return xl.replica_sharded_buffer(spec.shape, spec.dtype, rg, shard_over, entries, location=location)
+        shape = (rg.num_groups, *spec.shape) if rg.num_groups > 1 else tuple(spec.shape)  # host shape: group axis first
+        return xl.replica_sharded_buffer(shape, spec.dtype, rg, shard_over, entries, location=location)
     return xl.remote_buffer(spec.shape, spec.dtype, entries, location=location)
 
 

@@ -19,11 +19,20 @@ class _Streams:
             self._streams[name] = type(self)._factory(shape, dt, name)
 
     @classmethod
-    def from_streams(cls, streams: Mapping[str, object]):
+    def from_streams(cls, streams: Union[Iterable, Mapping[str, object]]):
+        """From existing streams: an iterable of streams (named by their `tensor_id`, as in the reference) or a mapping
+        name -> stream."""
         self = cls()
-        for name, s in streams.items():
-            self._streams[name] = s
+        if isinstance(streams, Mapping):
+            for name, s in streams.items():
+                self._streams[name] = s
+        else:
+            for s in streams:
+                self._streams[s.tensor_id] = s
         return self
+
+    def __contains__(self, name) -> bool:
+        return name in self._streams
 
     def __getattr__(self, name):
         if name.startswith("_"):

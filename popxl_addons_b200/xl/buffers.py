@@ -125,10 +125,17 @@ def remote_buffer(tensor_shape: Iterable[int], tensor_dtype: dtype, entries: int
 def replica_sharded_buffer(full_tensor_shape: Iterable[int], tensor_dtype: dtype,
                            replica_group: Optional[ReplicaGrouping] = None, shard_over: Optional[int] = None,
                            entries: int = 1, location: str = "device", shard_grouping=None) -> RemoteBuffer:
-    """Buffer whose rows are flat `nelms/shard_over` shards of tensors of `full_tensor_shape`."""
+    """Buffer whose rows are flat `nelms/shard_over` shards of tensors of `full_tensor_shape`. As in popxl, the shape
+    is the host shape of the variable the buffer is for: when `replica_group` has more than one group it starts with
+    the group axis, which is not part of a row."""
     ir = gcg().ir
     full = tuple(int(s) for s in full_tensor_shape)
     rg = replica_group or ir.replica_grouping()
+    if rg.num_groups > 1:
+        if not full or full[0] != rg.num_groups:
+            raise ValueError(f"The shape of a buffer for a grouping with {rg.num_groups} groups must start with the "
+                             f"group axis; got {full}")
+        full = full[1:]
     if shard_grouping is None:
         shard_grouping = _shard_grouping_within(rg, shard_over or rg.group_size)
     n = shard_grouping.group_size

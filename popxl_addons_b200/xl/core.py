@@ -610,6 +610,11 @@ class Graph:
         return _PbGraph(self)
 
     @property
+    def _by_ref_inputs(self) -> set:
+        """The graph inputs that were declared by reference (popxl keeps them under this name)."""
+        return self._by_ref
+
+    @property
     def constants(self) -> Tuple[Constant, ...]:
         return tuple(t for t in self._tensors if isinstance(t, Constant))
 

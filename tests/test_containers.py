@@ -195,3 +195,14 @@ def test_graph_cache_and_function_decorator():
         st = addons.host_store(z)
     out = popxl.Session(ir, "cpu").run()
     np.testing.assert_array_equal(out[st], np.full((2, 2), 2.0))
+
+
+def test_streams_from_an_iterable_of_streams():
+    ir = popxl.Ir()
+    with ir.main_graph:
+        a = popxl.h2d_stream((2,), popxl.float32, "a")
+        b = popxl.h2d_stream((3,), popxl.int32, "b")
+    ins = addons.InputStreams.from_streams([a, b])
+    assert list(ins) == [a, b] and ins[0] is a and ins[a.tensor_id] is a and a.tensor_id in ins and len(ins) == 2
+    named = addons.InputStreams.from_streams({"x": a})
+    assert named.x is a

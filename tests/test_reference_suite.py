@@ -69,9 +69,48 @@ _BOOT = textwrap.dedent('''
             hf.fixed_pos_embedding, hf.apply_rotary_pos_emb = fixed_pos_embedding, apply_rotary_pos_emb
     except Exception:
         pass
+    # second mode: modules of the reference that are written against popxl alone are loaded from the checkout and run
+    # on this package's substrate, in place of this package's own implementations
+    import importlib.util, itertools, os
+    ref_modules = os.environ.get("XL_REFERENCE_MODULES", "").split()
+    if ref_modules:
+        for name, attrs in (("mpi4py", {}), ("more_itertools", {})):
+            try:
+                __import__(name)
+            except ImportError:
+                sys.modules[name] = types.ModuleType(name)
+        if not hasattr(sys.modules["mpi4py"], "MPI"):
+            comm = types.SimpleNamespace(Barrier=lambda: None, Get_rank=lambda: 0, Get_size=lambda: 1)
+            sys.modules["mpi4py"].MPI = types.SimpleNamespace(COMM_WORLD=comm)
+        mi = sys.modules["more_itertools"]
+        if not hasattr(mi, "peekable"):
+            class peekable:
+                def __init__(self, it): self._it, self._cache = iter(it), []
+                def __iter__(self): return self
+                def __next__(self): return self._cache.pop(0) if self._cache else next(self._it)
+                def peek(self):
+                    if not self._cache: self._cache.append(next(self._it))
+                    return self._cache[0]
+            mi.peekable = peekable
+            mi.flatten = itertools.chain.from_iterable
+            mi.sliced = lambda seq, n: (seq[i:i + n] for i in range(0, len(seq), n))
+        package_dir = os.environ["XL_REFERENCE_PACKAGE"]
+        for rel in ref_modules:
+            name = "popxl_addons." + rel.replace("/", ".")
+            spec = importlib.util.spec_from_file_location(name, os.path.join(package_dir, rel + ".py"))
+            mod = importlib.util.module_from_spec(spec)
+            sys.modules[name] = mod
+            spec.loader.exec_module(mod)
     import pytest
     sys.exit(pytest.main(sys.argv[1:]))
 ''')
+
+# modules of the reference that use nothing but popxl and other add-on modules (no popart internals)
+PURE_POPXL_MODULES = ("rts remote transforms/batch_serialisation optimizers/adam layers/linear layers/layer_norm "
+                      "layers/embedding layers/group_norm layers/conv layers/linear_fp8 layers/linear_gq "
+                      "layers/layer_norm_distributed named_tensors graph_cache dot_tree utils streams variable_factory "
+                      "named_replica_grouping performance_utils ops/cross_entropy ops/fp8_amax_scale ops/streams "
+                      "array_munging task_session testing_utils")
 
 
 def _synthetic_mnist(root):
@@ -96,11 +135,17 @@ def _synthetic_mnist(root):
 
 @pytest.mark.skipif(not REF_TESTS or not os.path.isdir(REF_TESTS or ""),
                     reason="set POPXL_ADDONS_REFERENCE_TESTS to the tests directory of a popxl-addons checkout")
-def test_reference_test_files_pass_against_this_package(tmp_path):
+@pytest.mark.parametrize("reference_modules", ["", PURE_POPXL_MODULES], ids=["own-implementations", "reference-modules"])
+def test_reference_test_files_pass_against_this_package(tmp_path, reference_modules):
+    """`own-implementations`: every add-on module is this package's. `reference-modules`: the 26 modules of the
+    reference that are written against popxl alone (RTS, remote buffers, batch serialisation, Adam, all layers, the
+    containers, the variable factories, TaskSession, the FLOP estimator, ...) are loaded from the checkout and run on
+    this package's substrate instead: the same tests must pass, which checks the substrate against popxl itself."""
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     _synthetic_mnist(str(tmp_path / "datasets"))
     env = dict(os.environ, PYTHONPATH=repo + os.pathsep + os.environ.get("PYTHONPATH", ""), PYTHONDONTWRITEBYTECODE="1",
-               MNIST_DATASET_LOCATION=str(tmp_path / "datasets"))
+               MNIST_DATASET_LOCATION=str(tmp_path / "datasets"), XL_REFERENCE_MODULES=reference_modules,
+               XL_REFERENCE_PACKAGE=os.path.join(os.path.dirname(os.path.abspath(REF_TESTS)), "popxl_addons"))
     args = [sys.executable, "-c", _BOOT, REF_TESTS, "-q", "-p", "no:cacheprovider", "-rf"]
     args += [f"--ignore={os.path.join(REF_TESTS, p)}" for p in IGNORED]
     res = subprocess.run(args, cwd=str(tmp_path), env=env, capture_output=True, text=True, timeout=1800)
