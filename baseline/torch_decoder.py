@@ -6,7 +6,6 @@ checkpointing, bf16 compute (autocast) over fp32 parameters, fused AdamW with fp
 parallelism (column/row-parallel linears with NCCL all-reduce, vocabulary-sharded embedding / head / cross-entropy) and
 data parallelism by gradient all-reduce.  `python bench.py --impl torch` drives it.
 """
-import math
 import os
 
 import torch

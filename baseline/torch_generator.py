@@ -8,7 +8,6 @@ no longer an int4 model at run time) and shows the upper bound of the library pa
 graph in both variants (the position is a device tensor), as any tuned PyTorch serving loop would do.
 `python bench.py --mode decode --impl torch` drives it.
 """
-import math
 import os
 
 import torch

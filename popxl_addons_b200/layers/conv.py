@@ -1,7 +1,7 @@
 """2-D convolution layer (NCHW).
 Parity: popxl_addons/layers/conv.py:17-141. The IPU planner knobs of the reference constructor
 (`available_memory_proportions`, `partials_type`, `enable_conv_dithering`) are accepted and ignored."""
-from typing import Dict, Iterable, Optional, Tuple, Union
+from typing import Optional, Tuple, Union
 
 from functools import partial
 

@@ -7,7 +7,7 @@ Parity: popxl_addons/layers/embedding.py:17-79.
 """
 import math
 from functools import partial
-from typing import Dict, List, Optional
+from typing import Dict, Optional
 
 import numpy as np
 

@@ -1,7 +1,7 @@
 """GroupNorm over channel axis 1.
 Parity: popxl_addons/layers/group_norm.py:16-68."""
 from functools import partial
-from typing import Dict, Optional
+from typing import Optional
 
 import numpy as np
 

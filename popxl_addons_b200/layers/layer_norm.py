@@ -1,7 +1,7 @@
 """LayerNorm over the last axis of a 2-D `(N, C)` tensor.
 Parity: popxl_addons/layers/layer_norm.py:14-54."""
 from functools import partial
-from typing import Dict, Optional
+from typing import Optional
 
 import numpy as np
 

@@ -6,7 +6,7 @@ tensor-parallel one).
 Parity: popxl_addons/layers/linear.py:17-65.
 """
 from functools import partial
-from typing import Dict, Optional
+from typing import Optional
 
 import numpy as np
 

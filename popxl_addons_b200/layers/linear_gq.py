@@ -6,7 +6,7 @@
 Parity: popxl_addons/layers/linear_gq.py:19-136.
 """
 from functools import partial
-from typing import Dict, Optional
+from typing import Optional
 
 import numpy as np
 

@@ -8,8 +8,7 @@ the forward-identity all-reduce and row-parallel layers are followed by the back
 (tests/integration/test_batch_serialisation.py:463-492 of popxl_addons shows the pattern on a feed-forward block).
 """
 import math
-from dataclasses import dataclass, field, replace
-from functools import partial
+from dataclasses import dataclass, replace
 from typing import Optional
 
 import numpy as np

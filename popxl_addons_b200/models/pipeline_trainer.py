@@ -20,7 +20,7 @@ Parity: the reference composes the same program from popxl_addons/transforms/pip
 restore) with its autodiff / recomputation transforms; its device slots are the IPUs of one replica.
 """
 import os
-from typing import Dict, List, Optional
+from typing import List, Optional
 
 import numpy as np
 import torch

@@ -14,7 +14,7 @@ the same program runs all replicas in-process (CPU oracle / tests).
 """
 import os
 import time
-from typing import Dict, List, Optional
+from typing import Dict, Optional
 
 import numpy as np
 import torch

@@ -11,7 +11,7 @@ Parity: popxl_addons/module.py:66-753.
 import contextlib
 import inspect
 import warnings
-from typing import Any, Callable, Dict, Iterable, List, Optional, Set, Tuple, Union
+from typing import Any, Callable, Dict, List, Optional, Set, Tuple, Union
 
 from . import xl
 from .graph import BoundGraph, GraphWithNamedArgs

@@ -11,7 +11,6 @@ Algorithm (restated from popxl_addons/ops/fp8_mse_scale/README.md:1-24 and fp8_m
 On CUDA the histogram is one kernel (exponent extraction + shared-memory atomics) and the candidate scan runs in one
 warp of the same launch's last block.
 """
-from typing import Optional
 
 import numpy as np
 import torch

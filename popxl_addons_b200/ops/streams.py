@@ -2,7 +2,6 @@
 
 Parity: popxl_addons/ops/streams.py:13-23.
 """
-from typing import Tuple
 
 import numpy as np
 

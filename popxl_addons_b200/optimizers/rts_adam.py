@@ -11,7 +11,7 @@ The reference expresses the same step as separate graphs (rts.py:132-147 reduce,
 rts.py:39-62 gather).
 """
 from functools import partial
-from typing import Optional, Union
+from typing import Optional
 
 import numpy as np
 import torch

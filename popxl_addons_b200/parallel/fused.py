@@ -3,7 +3,7 @@ replica group, placement of variables in symmetric memory, a communicator that s
 NVLink kernel and everything else from NCCL)."""
 import ctypes
 import os
-from typing import Dict, List, Optional
+from typing import Dict, Optional
 
 import torch
 

@@ -6,7 +6,7 @@ paths, so the tensor arrives wherever the target is executed.
 
 Parity: popxl_addons/route_tensor.py:11-221.
 """
-from typing import Dict, Iterable, List, Optional, Set, Tuple
+from typing import Dict, Optional, Set, Tuple
 
 from . import xl
 

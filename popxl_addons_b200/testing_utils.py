@@ -1,6 +1,6 @@
 """Helpers for tests: count ops, and build-and-run a module in one call.
 Parity: popxl_addons/testing_utils.py:15-107."""
-from typing import Callable, Dict, Iterable, Optional, Tuple, Union
+from typing import Callable, Iterable, Optional, Tuple, Union
 
 import numpy as np
 

@@ -2,7 +2,7 @@
 
 Parity: popxl_addons/transforms/autodiff.py:26-228.
 """
-from typing import Dict, Iterable, Mapping, Optional, Tuple
+from typing import Iterable, Mapping, Optional, Tuple
 
 import numpy as np
 

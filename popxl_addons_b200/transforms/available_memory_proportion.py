@@ -6,7 +6,7 @@ analogue is a workspace / tile-configuration budget for the GEMM kernels of a de
 
 Parity: popxl_addons/transforms/available_memory_proportion.py:13-67.
 """
-from typing import Dict, Union
+from typing import Dict
 
 from .. import xl
 

@@ -19,7 +19,7 @@ Parity: popxl_addons/transforms/pipelining.py:26-508.
 from collections import defaultdict
 from contextlib import contextmanager
 from functools import partial
-from typing import Dict, Iterable, List, Optional
+from typing import Dict, List, Optional
 
 import numpy as np
 

@@ -9,7 +9,7 @@
 Every `(stride, size)` grouping is just a rank list on an NVSwitch box, so none of the orthogonal / consecutive /
 masked special cases of popxl_addons/ops/replicated_strided_collectives/mgcl.cpp:210-293 exist here.
 """
-from typing import Dict, List, Sequence, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 

@@ -15,7 +15,6 @@ import contextlib
 import inspect
 import dataclasses
 import itertools
-import math
 from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Tuple, Union
 
 import numpy as np

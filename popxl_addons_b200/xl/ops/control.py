@@ -4,7 +4,7 @@ caller's tensors (needed to feed a gradient graph with the activations of one pa
 Parity: popxl `ops.call/_with_info`, `ops.repeat/_with_info` as used by popxl_addons/graph.py:26-57 and
 transforms/batch_serialisation.py:355-409.
 """
-from typing import Dict, Iterable, List, Mapping, Optional, Tuple, Union
+from typing import List, Mapping, Optional, Tuple
 
 import numpy as np
 

@@ -6,7 +6,7 @@ Rotary parity: popxl_addons/ops/rotary_pos_embed/rotary_pos_embedx.cpp:49-70,104
 `rotary_dim` features; gradient = inverse rotation).
 """
 import math
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
 
