@@ -348,6 +348,26 @@ class Tensor:
     def in_sync_with(self):
         return self
 
+    def strides(self, shape=None) -> Tuple[int, ...]:
+        """Strides in bytes of a contiguous array of `shape` (default: this tensor's shape) and this dtype."""
+        shape = tuple(self.shape if shape is None else shape)
+        out, step = [], _dt.itemsize(self.dtype) if hasattr(_dt, "itemsize") else self.dtype.as_torch().itemsize
+        for n in reversed(shape):
+            out.append(step)
+            step *= int(n)
+        return tuple(reversed(out))
+
+    @property
+    def location_info(self):
+        """`(device slot, tile set)` the tensor was created on."""
+        return self.device_index, getattr(self.producer, "tile_set", "compute") if self.producer is not None else "compute"
+
+    @property
+    def in_sync_with_ipu(self) -> bool:
+        """Host data of a variable is written to the device when the session is created and read back on request: the
+        two never drift apart silently."""
+        return True
+
     def __repr__(self):
         ms = f", meta_shape={self.meta_shape}" if self.meta_shape else ""
         return f"Tensor[{self.id} {self._dtype} {self._shape}{ms}]"
