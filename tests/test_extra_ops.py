@@ -217,3 +217,29 @@ def test_seed_variable_default_gives_each_replica_its_own_seed():
     np.testing.assert_array_equal(popxl.create_seeds(11, replicas=4), popxl.create_seeds(11, replicas=4))
     assert popxl.create_seeds(11, batches_per_step=3, replicas=2).shape == (3, 2, 2)
     from popxl_addons_b200.ops.cross_entropy_sharded_wr_loss import cross_entropy_sharded_wr_loss  # noqa: F401
+
+
+def test_host_fp8_helpers():
+    from popxl_addons_b200.xl.fp8_utils import (host_fp8_mse_scale, host_pow2scale_cast_from_fp8,
+                                                host_pow2scale_cast_to_fp8)
+
+    x = np.array([0.0, 0.5, -1.75, 3.0, 100.0, -448.0], np.float32)
+    b = host_pow2scale_cast_to_fp8(x, popxl.float8_143, 0)
+    assert b.dtype == np.uint8 and b.shape == x.shape
+    back = host_pow2scale_cast_from_fp8(b, popxl.float32, 0, popxl.float8_143)
+    np.testing.assert_allclose(back, [0.0, 0.5, -1.75, 3.0, 96.0, -448.0])  # 100 rounds to 96 with 3 mantissa bits
+    # a power-of-two scale on the way in is undone by its negative on the way out
+    b2 = host_pow2scale_cast_to_fp8(x[:4], popxl.float8_152, 3)
+    np.testing.assert_allclose(host_pow2scale_cast_from_fp8(b2, popxl.float16, -3, popxl.float8_152), x[:4])
+    # overflow: NaN by default, the largest finite value when saturating
+    big = np.array([1000.0], np.float32)
+    assert np.isnan(host_pow2scale_cast_from_fp8(host_pow2scale_cast_to_fp8(big, popxl.float8_143, 0), popxl.float32, 0))
+    sat = host_pow2scale_cast_to_fp8(big, popxl.float8_143, 0, nan_on_overflow=False)
+    assert host_pow2scale_cast_from_fp8(sat, popxl.float32, 0)[0] == 448.0
+    with pytest.raises(ValueError):
+        host_pow2scale_cast_to_fp8(x, popxl.float8_143, 40)
+    data = np.random.RandomState(0).uniform(-64, -32, 10).astype(np.float16)
+    enc, scale = host_fp8_mse_scale(data, popxl.float8_143)
+    assert enc.dtype == np.uint8 and -31 <= scale <= 31
+    dec = host_pow2scale_cast_from_fp8(enc, popxl.float32, -scale)
+    assert np.abs(dec - data.astype(np.float32)).max() <= np.abs(data).max() * 2.0 ** -3  # within one e4m3 step
