@@ -13,14 +13,15 @@ from ..xl.opdef import OpDef, emit1
 __all__ = ["random_sparse", "dense_const_sparse_matmul"]
 
 
-def random_sparse(dense: np.ndarray, density: float = 0.5):
-    """Zero out a random `1 - density` fraction of `dense`; returns `(masked dense, scipy csr_matrix)`."""
-    from scipy.sparse import csr_matrix
-
-    mask = np.random.rand(*dense.shape) < density
-    masked = (dense * mask).astype(dense.dtype)
-    # scipy has no 16-bit float sparse matrices: those are held as float32 (exact)
-    return masked, csr_matrix(masked.astype(np.float32) if masked.dtype.itemsize < 4 else masked)
+def random_sparse(dense: np.ndarray, density: float = 0.5) -> np.ndarray:
+    """Zero a random `1 - density` fraction of `dense` **in place** (at least one element is kept) and return it, as the
+    reference's helper does; build the sparse operand from it with `scipy.sparse.csr_matrix(dense)` (16-bit floats:
+    `csr_matrix(dense.astype(np.float32))`, scipy has no 16-bit sparse matrices)."""
+    drop = np.random.rand(*dense.shape) < (1.0 - density)
+    if np.all(drop):
+        drop.reshape(-1)[0] = False
+    dense[drop] = 0
+    return dense
 
 
 def _impl(lhs, indptr, indices, values, n_rows, n_cols):

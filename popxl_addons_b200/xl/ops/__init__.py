@@ -425,8 +425,8 @@ OpDef("transpose", impl=lambda a, perm: a.permute(perm), vjp=_vjp_transpose)
 def transpose(t: Tensor, permutation: Optional[Iterable[int]] = None) -> Tensor:
     perm = tuple(permutation) if permutation is not None else tuple(reversed(range(t.rank)))
     perm = tuple(p % t.rank for p in perm)
-    if perm == tuple(range(t.rank)):
-        return t
+    if perm == tuple(range(t.rank)) and t.rank != 1:
+        return t  # nothing moves: no op (a rank-1 `.T` still records one, as popxl does, so op ids line up)
     return emit1("transpose", [t], {"perm": perm})
 
 

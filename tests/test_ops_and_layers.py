@@ -336,7 +336,12 @@ def test_sparse_matmul_grad_square_add_linear_layout():
 
     rng = np.random.RandomState(9)
     lhs = rng.randn(1, 2, 3).astype(np.float32)
-    dense, csr = random_sparse(rng.randn(3, 4).astype(np.float32), 0.5)
+    from scipy.sparse import csr_matrix
+
+    dense = rng.randn(3, 4).astype(np.float32)
+    np.random.seed(3)
+    assert random_sparse(dense, 0.5) is dense and 0 < (dense == 0).sum() < dense.size  # sparsified in place
+    csr = csr_matrix(dense)
     g = rng.randn(7, 5).astype(np.float32)
     ir = popxl.Ir()
     with ir.main_graph:

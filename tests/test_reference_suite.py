@@ -28,7 +28,6 @@ EXPECTED_FAILURES = {
     "test_sparse_matmul.py::test_dense_sparse_matmul_fp16",
     "test_repeat_graph.py::test_topological_constraints",
     "test_adam.py::test_adam_correctness",
-    "test_perf_utils.py::test_matmul_flops",
     "test_group_norm.py::test_group_norm_2D",  # unseeded data against eps 1e-5 / 1e-6: passes or fails by draw
 }
 
@@ -157,4 +156,4 @@ def test_reference_test_files_pass_against_this_package(tmp_path, reference_modu
     assert not re.search(r"^ERROR ", out, flags=re.M), out[-3000:]
     unexpected = failed - EXPECTED_FAILURES
     assert not unexpected, f"unexpected failures: {sorted(unexpected)}\n{out[-3000:]}"
-    assert int(summary.group(1)) >= 178, out[-2000:]
+    assert int(summary.group(1)) >= 179, out[-2000:]
