@@ -224,3 +224,34 @@ def test_sequence_parallel_equals_plain_tensor_parallel():
         np.testing.assert_allclose(results[family, True], results[family, False], rtol=1e-5)
     got = launch(2, "--device", "cpu", "--tp", "2", "--dp", "1", "--dtype", "float32", "--sp", "1")
     np.testing.assert_allclose(got["losses"], results["gptj", False], rtol=1e-4)
+
+
+def test_supervisor_policies(tmp_path):
+    """Restart budget, workers that outlive a failed peer (stopped by their own pids after the grace period) and
+    workers that die from a signal, with plain scripts in place of training processes."""
+    from popxl_addons_b200.parallel.elastic import Supervisor
+
+    script = tmp_path / "worker.py"
+    script.write_text(
+        "import os, signal, sys, time\n"
+        "rank, attempt, mode = int(os.environ['RANK']), int(os.environ['XL_RESTART_COUNT']), sys.argv[1]\n"
+        "assert os.environ['WORLD_SIZE'] == '2' and os.environ['MASTER_ADDR'] == '127.0.0.1'\n"
+        "if mode == 'flaky' and attempt < 2 and rank == 1: sys.exit(5)\n"
+        "if mode == 'always' and rank == 0: sys.exit(9)\n"
+        "if mode == 'hang' and attempt == 0:\n"
+        "    if rank == 0: sys.exit(4)\n"
+        "    time.sleep(600)\n"
+        "if mode == 'signal' and attempt == 0 and rank == 1: os.kill(os.getpid(), signal.SIGKILL)\n"
+        "open(os.path.join(os.path.dirname(__file__), f'done_{mode}_{rank}'), 'w').write(str(attempt))\n")
+    quiet = dict(log=lambda m: None, poll_s=0.02)
+    flaky = Supervisor([str(script), "flaky"], nproc=2, max_restarts=3, grace_s=5.0, **quiet)
+    assert flaky.run() == 0 and len(flaky.attempts) == 3 and flaky.attempts[-1] == [0, 0]
+    assert (tmp_path / "done_flaky_1").read_text() == "2"
+    always = Supervisor([str(script), "always"], nproc=2, max_restarts=1, grace_s=5.0, **quiet)
+    assert always.run() == 9 and len(always.attempts) == 2  # the budget is spent, the failing status is returned
+    hang = Supervisor([str(script), "hang"], nproc=2, max_restarts=1, grace_s=0.3, **quiet)
+    assert hang.run() == 0 and hang.attempts[0][0] == 4 and hang.attempts[0][1] < 0  # the sleeper was signalled
+    sig = Supervisor([str(script), "signal"], nproc=2, max_restarts=1, grace_s=5.0, **quiet)
+    assert sig.run() == 0 and sig.attempts[0][1] == -9 and sig.attempts[1] == [0, 0]
+    none = Supervisor([str(script), "always"], nproc=2, max_restarts=0, grace_s=1.0, **quiet)
+    assert none.run() == 9 and len(none.attempts) == 1
