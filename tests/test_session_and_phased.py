@@ -448,3 +448,52 @@ def test_import_aliases_resolve_to_this_package():
     res = subprocess.run([sys.executable, "-c", prog], capture_output=True, text=True, env=env, timeout=300)
     assert res.returncode == 0, res.stderr[-2000:]
     assert res.stdout.strip().endswith("(2, 4)")
+
+
+def test_weights_and_biases_paths_with_a_stand_in(tmp_path, monkeypatch):
+    """Timer summaries, per-variable histograms with non-finite counts and `wandb://` checkpoints, against a stand-in
+    for the optional wandb module that records what it is given."""
+    import types
+
+    import popxl_addons_b200.task_session as ts
+    import popxl_addons_b200.utils as ut
+
+    logged, artifacts = [], {}
+
+    class Artifact:
+        def __init__(self, name, type):
+            self.name, self.type, self.dir = name, type, None
+
+        def add_dir(self, d):
+            import shutil
+
+            self.dir = str(tmp_path / f"artifact_{self.name}")
+            shutil.copytree(d, self.dir)
+
+        def download(self):
+            return self.dir
+
+    fake = types.SimpleNamespace(
+        run=types.SimpleNamespace(summary={}), Histogram=lambda data: ("hist", len(data)),
+        log=lambda d, step=None: logged.append((d, step)), Artifact=Artifact,
+        log_artifact=lambda a: artifacts.__setitem__(a.name, a), use_artifact=lambda name, type=None: artifacts[name])
+    monkeypatch.setattr(ts, "wandb", fake)
+    monkeypatch.setattr(ut, "wandb", fake)
+    monkeypatch.setattr(ut, "_HAVE_WANDB", True)
+    with addons.timer("Unit Test Phase"):
+        pass
+    assert "unit_test_phase_mins" in fake.run.summary
+    s, v = _linear_session()
+    s.write_variable_data(v.bias, np.array([1.0, np.nan, np.inf], np.float32))
+    s.wandb_variable_histograms(step=7)
+    by_name = {k: (val, step) for d, step in logged for k, val in d.items()}
+    assert by_name["bias"] == (("hist", 1), 7) and by_name["bias_nonfinite"] == (2, 7)
+    assert by_name["weight_nonfinite"][0] == 0
+    s.run({s.inputs.x: np.ones((2, 4), np.float32)})
+    w = s.get_tensor_data(v.weight).copy()
+    s.save_checkpoint("wandb://ckpt")
+    assert sorted(os.listdir(os.path.join(artifacts["ckpt"].dir, "model"))) == ["bias.npz", "weight.npz"]
+    s2, v2 = _linear_session()
+    s2.load_checkpoint("wandb://ckpt")
+    np.testing.assert_array_equal(s2.get_tensor_data(v2.weight), w)
+    assert s2.session_state["steps"] == 1
