@@ -332,3 +332,23 @@ def test_route_tensor_into_nested_graphs():
             route_tensor_into_graph(1.0, inner)
         st = addons.host_store(y)
     np.testing.assert_array_equal(popxl.Session(ir, "cpu").run()[st], np.full((2,), 13.0))
+
+
+def test_graph_common_normalises_graph_like_keys():
+    from popxl_addons_b200.graph_common import normalise_called_graphs_grad_info
+
+    class Scale(addons.Module):
+        def build(self, x):
+            return x * self.add_variable_input("scale", lambda: np.ones(x.shape, np.float32), x.dtype)
+
+    ir = popxl.Ir()
+    with ir.main_graph:
+        x = popxl.variable(np.ones((2, 2), np.float32))
+        facts, graph = Scale().create_graph(x)
+        dgraph = addons.autodiff(graph)
+        bound = graph.bind(facts.init())
+    info = dgraph.grad_graph_info
+    for key, val in ((graph, dgraph), (graph.graph, info), (bound, dgraph)):
+        out = normalise_called_graphs_grad_info({key: val})
+        assert list(out.keys()) == [graph.graph] and out[graph.graph] is info
+    assert normalise_called_graphs_grad_info(None) == {}
