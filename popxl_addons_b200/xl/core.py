@@ -648,6 +648,26 @@ class Graph:
     def is_by_ref(self, t: Tensor) -> bool:
         return t in self._by_ref
 
+    def get_main_graph(self) -> "Graph":
+        return self.ir.main_graph
+
+    def get_tensor(self, tensor_id: str) -> Tensor:
+        """The tensor of this graph with the given id."""
+        for t in self._tensors:
+            if t.id == tensor_id:
+                return t
+        raise KeyError(f"There is no tensor with id '{tensor_id}' in the graph {self.name}")
+
+    def get_variable(self, tensor_id: str) -> Variable:
+        t = self.get_tensor(tensor_id)
+        if not isinstance(t, Variable):
+            raise TypeError(f"Tensor '{tensor_id}' is not a variable")
+        return t
+
+    def _create_tensor_id(self, name: Optional[str] = None) -> str:
+        """A tensor id of this graph that is not in use yet, derived from `name`."""
+        return self._unique_tensor_id(name or "t")
+
     def get_input_tensors(self):
         return self.inputs
 
@@ -1058,6 +1078,29 @@ class Ir:
 
     def _next_op_id(self) -> int:
         return next(self._op_ids)
+
+    def get_all_h2d_streams(self) -> List[Any]:
+        from .buffers import HostToDeviceStream
+
+        return [st for st in self.streams if isinstance(st, HostToDeviceStream)]
+
+    def get_all_d2h_streams(self) -> List[Any]:
+        from .buffers import DeviceToHostStream
+
+        return [st for st in self.streams if isinstance(st, DeviceToHostStream)]
+
+    @property
+    def num_device_iterations(self) -> int:
+        """Host transfers per `Session.run` (the name newer popxl releases use for `num_host_transfers`)."""
+        return self.num_host_transfers
+
+    @num_device_iterations.setter
+    def num_device_iterations(self, n: int):
+        self.num_host_transfers = int(n)
+
+    def dot_checkpoint(self, check: str = "") -> None:
+        """The reference substrate dumps a Graphviz file of the IR here when asked to through an environment variable;
+        `ir._pb_ir.logIr()` prints this substrate's graphs instead."""
 
     def __repr__(self):
         return f"Ir(graphs={len(self.graphs)}, replication_factor={self._replication_factor})"
