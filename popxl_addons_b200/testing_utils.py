@@ -12,9 +12,19 @@ __all__ = ["ops_of_type", "TensorInput", "run_module"]
 
 
 def ops_of_type(ops: Iterable, op_type: Union[str, type]) -> int:
-    """Number of ops whose type name equals `op_type` (a string such as `"matmul"`)."""
+    """Number of ops of type `op_type`: an op name of this package (`"matmul"`), a popart-style type name (`"MatMul"`,
+    `"Accumulate"`) or a class whose name is one of those with an `Op` suffix. `ops` may be a graph's `ops` or the
+    popart-style views `graph._pb_graph.getOps()` returns."""
+    from .xl.core import pb_op_type
+
     name = op_type if isinstance(op_type, str) else getattr(op_type, "__name__", str(op_type))
-    return sum(1 for o in ops if o.opdef.name == name)
+    names = {name, name[:-2] if name.endswith("Op") else name}
+    count = 0
+    for o in ops:
+        o = getattr(o, "_op", o)
+        if o.opdef.name in names or pb_op_type(o) in names:
+            count += 1
+    return count
 
 
 class TensorInput:
