@@ -157,3 +157,41 @@ def test_fp8_amax_scale_uses_the_top_octave_without_overflow(magnitude, fmt, see
     if -31 < scale < 31:
         assert amax * 2.0 ** scale <= fmax * (1 + 1e-6)      # no overflow after scaling
         assert amax * 2.0 ** (scale + 1) > fmax * (1 - 1e-6)  # and one more octave would overflow
+
+
+@SLOW
+@given(st.integers(2, 5), st.integers(0, 3), st.integers(0, 100), st.booleans())
+def test_pipelined_chain_equals_sequential_chain(n_stages, extra_steps, seed, with_stash):
+    """A chain of `n_stages` affine stages on as many device slots, with an optional skip connection from the first
+    stage to the last through a stash, pipelined over `2 * n_stages + extra` micro-batches: same outputs as applying
+    the stages one after the other."""
+    steps = 2 * n_stages + extra_steps
+    rs = np.random.RandomState(seed)
+    data = rs.normal(0, 1, (steps, 3)).astype(np.float32)
+    scales, shifts = rs.uniform(0.5, 1.5, n_stages).astype(np.float32), rs.normal(0, 1, n_stages).astype(np.float32)
+    ir = popxl.Ir()
+    with ir.main_graph:
+        with addons.pipelined_execution(steps) as p:
+            with p.stage(0), popxl.ipu(0):
+                _, x_stream, x = addons.host_load(data[0], popxl.float32, "x")
+                first = x
+                x = (x * float(scales[0]) + float(shifts[0])).copy_to_ipu(1)
+            for s in range(1, n_stages):
+                with p.stage(s), popxl.ipu(s):
+                    x = x * float(scales[s]) + float(shifts[s])
+                    if s < n_stages - 1:
+                        x = x.copy_to_ipu(s + 1)
+                    else:
+                        if with_stash:
+                            # the first stage's input, kept in a ring buffer until this micro-batch reaches the last stage
+                            x = x + p.stash_and_restore_tensor(first, from_stage=0)
+                        out = addons.host_store(x)
+    ir.num_host_transfers = steps
+    with popxl.Session(ir, "cpu") as sess:
+        got = sess.run({x_stream: data})[out]
+    want = data.copy()
+    for s in range(n_stages):
+        want = want * scales[s] + shifts[s]
+    if with_stash:
+        want = want + data
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
