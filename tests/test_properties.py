@@ -195,3 +195,42 @@ def test_pipelined_chain_equals_sequential_chain(n_stages, extra_steps, seed, wi
     if with_stash:
         want = want + data
     np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+
+
+@SLOW
+@given(st.integers(1, 4), st.integers(1, 3), st.integers(0, 2), st.sampled_from(["compute", "io", "io_overlapped"]),
+       st.integers(0, 50))
+def test_batch_serialised_rows_equal_the_plain_computation(steps, rows, offset, io_mode, seed):
+    """`rows` layers x `steps` micro-batches through one serialised loop graph, input rows read from a remote buffer at
+    a row offset, outputs written to another buffer: every entry equals the plain computation on that entry."""
+    from functools import partial
+
+    from popxl_addons_b200.transforms.batch_serialisation import RemoteHandle, batch_serial_buffer, batch_serialise
+
+    class Affine(addons.Module):
+        def build(self, x):
+            w = self.add_variable_input("w", partial(np.full, x.shape, 3.0, np.float32), x.dtype)
+            return x * w + 1.0
+
+    data = np.random.RandomState(seed).normal(0, 1, (rows + offset, steps, 2, 3)).astype(np.float32)
+    ir = popxl.Ir()
+    with ir.main_graph:
+        facts, graph = Affine().create_graph(popxl.TensorSpec((2, 3), popxl.float32))
+        x_in, y_out = graph.graph.inputs[0], graph.graph.outputs[0]
+        in_buffer = batch_serial_buffer(x_in, steps=steps, rows=rows + offset)
+        out_buffer = batch_serial_buffer(y_out, steps=steps, rows=rows)
+        result = batch_serialise(graph, steps, {x_in: RemoteHandle(in_buffer, offset)}, {},
+                                 {y_out: RemoteHandle(out_buffer, 0)}, rows=rows, io_mode=io_mode)
+        w = facts.init()
+        for r in range(rows + offset):
+            for i in range(steps):
+                ops.remote_store(in_buffer, r * steps + i, popxl.constant(data[r, i]))
+        loop = result.graph.bind(w)
+        for r in range(rows):
+            loop.call(r)
+        streams = [addons.host_store(ops.remote_load(out_buffer, r * steps + i)) for r in range(rows) for i in range(steps)]
+    assert in_buffer.entries == steps * (rows + offset) and out_buffer.entries == steps * rows
+    with popxl.Session(ir, "cpu") as s:
+        out = s.run()
+    got = np.stack([out[st] for st in streams]).reshape(rows, steps, 2, 3)
+    np.testing.assert_allclose(got, data[offset:] * 3.0 + 1.0, rtol=1e-6)
