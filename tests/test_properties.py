@@ -2,6 +2,7 @@
 groupings, the strided collectives of the in-process backend, 4-bit group quantisation and FP8 scale selection."""
 import numpy as np
 import pytest
+import torch
 from hypothesis import given, settings, strategies as st
 
 import popxl_addons_b200 as addons
@@ -234,3 +235,84 @@ def test_batch_serialised_rows_equal_the_plain_computation(steps, rows, offset, 
         out = s.run()
     got = np.stack([out[st] for st in streams]).reshape(rows, steps, 2, 3)
     np.testing.assert_allclose(got, data[offset:] * 3.0 + 1.0, rtol=1e-6)
+
+
+_UNARY = {
+    "exp": (lambda t: ops.exp(t * 0.3), lambda t: torch.exp(t * 0.3)),
+    "tanh": (ops.tanh, torch.tanh),
+    "sigmoid": (ops.sigmoid, torch.sigmoid),
+    "gelu": (ops.gelu, lambda t: torch.nn.functional.gelu(t)),
+    "relu": (ops.relu, torch.relu),
+    "swish": (ops.swish, torch.nn.functional.silu),
+    "sin": (ops.sin, torch.sin),
+    "cos": (ops.cos, torch.cos),
+    "negate": (ops.negate, torch.neg),
+    "abs": (ops.abs, torch.abs),
+    "sqrt": (lambda t: ops.sqrt(ops.abs(t) + 1.0), lambda t: torch.sqrt(t.abs() + 1.0)),
+    "log": (lambda t: ops.log(ops.abs(t) + 1.0), lambda t: torch.log(t.abs() + 1.0)),
+    "softmax": (lambda t: ops.softmax(t, axis=-1), lambda t: torch.softmax(t, -1)),
+    "transpose": (lambda t: ops.transpose(ops.transpose(t) * 2.0), lambda t: (t.t() * 2.0).t()),
+    "reshape": (lambda t: ops.reshape(ops.reshape(t, (4, 3)) + 1.0, (3, 4)), lambda t: (t.reshape(4, 3) + 1.0).reshape(3, 4)),
+    "slice_concat": (lambda t: ops.concat([t[:, 2:], t[:, :2] * 3.0], axis=1), lambda t: torch.cat([t[:, 2:], t[:, :2] * 3.0], 1)),
+    "mean_center": (lambda t: t - ops.mean(t, axis=1, keepdims=True) if hasattr(ops.mean, "__call__") else t,
+                    lambda t: t - t.mean(1, keepdim=True)),
+    "sum_rows": (lambda t: t + ops.sum(t, axis=0, keepdims=True) * 0.1, lambda t: t + t.sum(0, keepdim=True) * 0.1),
+    "self_matmul": (lambda t: (t @ ops.transpose(t)) @ t * 0.1, lambda t: (t @ t.t()) @ t * 0.1),
+    "clip": (lambda t: ops.clip(t, -0.5, 0.5), lambda t: t.clamp(-0.5, 0.5)),
+    "cumsum": (lambda t: ops.cumsum(t, dim=1) * 0.5, lambda t: torch.cumsum(t, 1) * 0.5),
+}
+_BINARY = {
+    "add": (lambda a, b: a + b, lambda a, b: a + b),
+    "sub": (lambda a, b: a - b, lambda a, b: a - b),
+    "mul": (lambda a, b: a * b, lambda a, b: a * b),
+    "div": (lambda a, b: a / (ops.abs(b) + 1.0), lambda a, b: a / (b.abs() + 1.0)),
+    "maximum": (ops.maximum, torch.maximum),
+    "minimum": (ops.minimum, torch.minimum),
+    "row_broadcast": (lambda a, b: a * b[0:1, :], lambda a, b: a * b[0:1, :]),
+    "where": (lambda a, b: ops.where(ops.greater(a, b), a, b * 2.0), lambda a, b: torch.where(a > b, a, b * 2.0)),
+}
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.lists(st.one_of(st.tuples(st.just("u"), st.sampled_from(sorted(_UNARY)), st.integers(0, 9)),
+                          st.tuples(st.just("b"), st.sampled_from(sorted(_BINARY)), st.integers(0, 9), st.integers(0, 9))),
+                min_size=1, max_size=7), st.integers(0, 1000))
+def test_autodiff_of_random_programs_matches_torch_autograd(program, seed):
+    """Random programs over the differentiable ops: the values and the gradients from the graph autodiff equal those of
+    torch.autograd on the same expression (every intermediate value is a candidate operand of later ops, and the result
+    sums all of them so that every op's vjp rule takes part)."""
+    rs = np.random.RandomState(seed)
+    a0, b0 = rs.normal(0, 1, (3, 4)).astype(np.float32), rs.normal(0, 1, (3, 4)).astype(np.float32)
+
+    def run(values, table_index):
+        for step in program:
+            if step[0] == "u":
+                values.append(_UNARY[step[1]][table_index](values[step[2] % len(values)]))
+            else:
+                values.append(_BINARY[step[1]][table_index](values[step[2] % len(values)], values[step[3] % len(values)]))
+        total = values[0]
+        for v in values[1:]:
+            total = total + v
+        return total
+
+    ta, tb = torch.tensor(a0, requires_grad=True), torch.tensor(b0, requires_grad=True)
+    ty = run([ta, tb], 1)
+    ga, gb = torch.autograd.grad(ty.sum(), (ta, tb), allow_unused=True)
+    ir = popxl.Ir()
+    with ir.main_graph:
+        xa, xb = popxl.variable(a0, name="a"), popxl.variable(b0, name="b")
+        g = ir.create_graph(lambda a, b: run([a, b], 0), xa, xb)
+        info = ops.call_with_info(g, xa, xb)
+        dg = popxl.transforms.autodiff(g)
+        grads = ops.call(dg.graph, popxl.constant(np.ones((3, 4), np.float32)), inputs_dict=dg.inputs_dict(info))
+        grads = grads if isinstance(grads, (tuple, list)) else (grads,)
+        sy = addons.host_store(info.outputs[0])
+        sg = [addons.host_store(t) for t in grads]
+    with popxl.Session(ir, "cpu") as s:
+        out = s.run()
+    np.testing.assert_allclose(out[sy], ty.detach().numpy(), rtol=1e-4, atol=1e-5)
+    by_input = dict(zip([ec.fwd_tensor for ec in dg.expected_outputs], sg))
+    for gin, want in zip(g.inputs, (ga, gb)):
+        want = np.zeros((3, 4), np.float32) if want is None else want.numpy()
+        assert gin in by_input
+        np.testing.assert_allclose(out[by_input[gin]], want, rtol=1e-3, atol=1e-4)
