@@ -316,3 +316,65 @@ def test_autodiff_of_random_programs_matches_torch_autograd(program, seed):
         want = np.zeros((3, 4), np.float32) if want is None else want.numpy()
         assert gin in by_input
         np.testing.assert_allclose(out[by_input[gin]], want, rtol=1e-3, atol=1e-4)
+
+
+@settings(max_examples=25, deadline=None)
+@given(st.lists(st.one_of(st.tuples(st.just("u"), st.sampled_from(sorted(_UNARY)), st.integers(0, 9)),
+                          st.tuples(st.just("b"), st.sampled_from(sorted(_BINARY)), st.integers(0, 9), st.integers(0, 9))),
+                min_size=1, max_size=6), st.integers(0, 1000), st.integers(1, 3))
+def test_recomputation_and_accumulation_of_random_programs(program, seed, calls):
+    """For a random program with one parameter: the recomputing gradient graph (which only takes the forward inputs) gives
+    the gradients of the plain one, and the accumulating gradient graph leaves the mean of the per-call gradients."""
+    from functools import partial
+
+    rs = np.random.RandomState(seed)
+    w0 = rs.normal(0, 1, (3, 4)).astype(np.float32)
+    xs = rs.normal(0, 1, (calls, 3, 4)).astype(np.float32)
+
+    class Net(addons.Module):
+        def build(self, x):
+            values = [x, self.add_variable_input("w", partial(np.copy, w0), x.dtype)]
+            for step in program:
+                if step[0] == "u":
+                    values.append(_UNARY[step[1]][0](values[step[2] % len(values)]))
+                else:
+                    values.append(_BINARY[step[1]][0](values[step[2] % len(values)], values[step[3] % len(values)]))
+            total = values[0]
+            for v in values[1:]:
+                total = total + v
+            return total
+
+    ir = popxl.Ir()
+    with ir.main_graph:
+        x0 = popxl.variable(xs[0])
+        facts, graph = Net().create_graph(x0)
+        plain = addons.autodiff(graph)
+        facts2, graph2 = Net().create_graph(x0)
+        recomputed = addons.recompute_graph(addons.autodiff(graph2))
+        facts3, graph3 = Net().create_graph(x0)
+        acc_facts, accumulating = addons.autodiff_with_accumulation(graph3, [graph3.args.w], grads_required=[])
+        w = facts.init()
+        acc = acc_facts.init()
+        seed_grad = popxl.constant(np.ones((3, 4), np.float32))
+        streams = []
+        for c in range(calls):
+            x = popxl.variable(xs[c], name=f"x{c}")
+            i1 = graph.bind(w).call_with_info(x)
+            g1 = plain.call(seed_grad, args=plain.grad_graph_info.inputs_dict(i1))
+            i2 = graph2.bind(w).call_with_info(x)
+            g2 = recomputed.call(seed_grad, args=recomputed.grad_graph_info.inputs_dict(i2))
+            i3 = graph3.bind(w).call_with_info(x)
+            accumulating.bind(acc).call(seed_grad, args=accumulating.grad_graph_info.inputs_dict(i3))
+            streams.append(([addons.host_store(t) for t in g1], [addons.host_store(t) for t in g2]))
+        # which output of the plain gradient graph belongs to the parameter
+        w_index = [ec.fwd_tensor for ec in plain.grad_graph_info.expected_outputs].index(graph.args.w)
+    with popxl.Session(ir, "cpu") as s:
+        out = s.run()
+        mean_grad = s.get_tensor_data(acc.accum.w)
+    per_call = []
+    for a, b in streams:
+        assert len(a) == len(b)
+        for sa, sb in zip(a, b):
+            np.testing.assert_allclose(out[sb], out[sa], rtol=1e-5, atol=1e-6)
+        per_call.append(out[a[w_index]])
+    np.testing.assert_allclose(mean_grad, np.mean(per_call, axis=0), rtol=1e-4, atol=1e-5)
