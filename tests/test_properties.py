@@ -378,3 +378,39 @@ def test_recomputation_and_accumulation_of_random_programs(program, seed, calls)
             np.testing.assert_allclose(out[sb], out[sa], rtol=1e-5, atol=1e-6)
         per_call.append(out[a[w_index]])
     np.testing.assert_allclose(mean_grad, np.mean(per_call, axis=0), rtol=1e-4, atol=1e-5)
+
+
+@SLOW
+@given(st.sampled_from([(4, 1, 4, 1, 2), (4, 1, 4, 1, 4), (8, 1, 8, 1, 2), (8, 2, 4, 2, 2), (8, 2, 4, 2, 4), (8, 1, 4, 1, 2),
+                        (8, 1, 8, 2, 2), (4, 1, 2, 1, 2), (8, 4, 2, 4, 2)]),
+       st.sampled_from(["add", "mean"]), st.sampled_from([8, 12, 16]), st.integers(0, 100))
+def test_rts_reduce_then_gather_over_nested_groups(cfg, op, nelms, seed):
+    """Gradient-style reduction over a replica group that leaves every replica with its shard inside a shard group
+    (equal to the replica group or a subset of it), then the all-gather over the shard group: every replica ends up
+    with the full reduced tensor of its replica group."""
+    from popxl_addons_b200.rts import gather_replica_sharded_tensor, reduce_replica_sharded_tensor
+
+    rf, r_stride, r_size, s_stride, s_size = cfg
+    data = np.random.RandomState(seed).rand(rf, nelms).astype(np.float32)
+    ir = popxl.Ir(rf)
+    with ir.main_graph:
+        h = popxl.h2d_stream((nelms,), popxl.float32)
+        x = ops.host_load(h)
+        rg = ir.replica_grouping(stride=r_stride, group_size=r_size)
+        sg = ir.replica_grouping(stride=s_stride, group_size=s_size)
+        shard = reduce_replica_sharded_tensor(x, op, replica_group=rg, shard_group=sg)
+        assert shard.shape == (nelms // s_size,) and tuple(shard.meta_shape) == (nelms,)
+        full = gather_replica_sharded_tensor(shard, replica_group=sg)
+        s_shard, s_full = addons.host_store(shard), addons.host_store(full)
+    with popxl.Session(ir, "cpu") as s:
+        out = s.run({h: data})
+    red = np.sum if op == "add" else np.mean
+    for r in range(rf):
+        block = r // (r_stride * r_size)
+        members = [block * r_stride * r_size + r % r_stride + j * r_stride for j in range(r_size)]
+        want = red(data[members], axis=0)
+        sblock = r // (s_stride * s_size)
+        smembers = [sblock * s_stride * s_size + r % s_stride + j * s_stride for j in range(s_size)]
+        i, n = smembers.index(r), nelms // s_size
+        np.testing.assert_allclose(out[s_shard][r], want[i * n:(i + 1) * n], rtol=1e-5)
+        np.testing.assert_allclose(out[s_full][r].reshape(-1), want, rtol=1e-5)
