@@ -76,6 +76,8 @@ _gemm = _sig("xl_gemm_tcgen05", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int
 _gemm_fused = _sig("xl_gemm_tcgen05_fused", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
                    _c_ll, _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_p,
                    _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p)
+_gemm_pair = _sig("xl_gemm2cta_tcgen05", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
+                  _c_ll, _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_p)
 _gq_small = _sig("xl_gq_gemm_small_m", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
                  _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p)
 _rot_append = _sig("xl_rotary_append", _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -184,7 +186,11 @@ def check_gemm_errors():
                      11: "attention: query tile never arrived", 12: "attention: key / value block never arrived",
                      13: "attention: key / value stage was never released", 14: "attention: scores never completed",
                      15: "attention: score buffer was never drained", 16: "attention: probabilities never arrived",
-                     17: "attention: output accumulation never completed"}
+                     17: "attention: output accumulation never completed",
+                     21: "CTA-pair GEMM: operand tiles never arrived (TMA)",
+                     22: "CTA-pair GEMM: shared-memory stage was never released",
+                     23: "CTA-pair GEMM: accumulator never completed",
+                     24: "CTA-pair GEMM: accumulator buffer was never drained"}
             raise RuntimeError(f"tcgen05 GEMM on cuda:{idx} gave up waiting: {names.get(code, code)}")
 
 
@@ -466,6 +472,11 @@ def _major(t: torch.Tensor, contraction_last: bool):
     return None
 
 
+# XL_GEMM_CTA_PAIRS=1: plain GEMMs with N > 128 run on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); collective
+# epilogues, the all-gather prologue and causal products keep the single-CTA kernel
+_GEMM_CTA_PAIRS = os.environ.get("XL_GEMM_CTA_PAIRS", "0") == "1"
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = None, act: int = 0,
          out: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None, accumulate: int = 0,
          step: Optional[torch.Tensor] = None, alpha: float = 1.0, comm=None, rs_dst: Optional[torch.Tensor] = None,
@@ -539,6 +550,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
             g_mode, src_ptrs, flags, g_bps, g_copy = gather
             g_src, g_flags = src_ptrs.data_ptr(), flags.data_ptr()
             g_dst = a.data_ptr() if g_mode == 1 else b.data_ptr()
+    if _GEMM_CTA_PAIRS and accumulate <= 2 and gather is None and not causal and N > 128:
+        rc = _gemm_pair(a.data_ptr(), b.data_ptr(), out_ptr, M, N, K, batch, a_mn, b_mn, lda, ldb, ldc, sa, sb, stride_c,
+                        int(a.dtype == torch.float16), _CODE[out.dtype], bias.data_ptr() if bias is not None else None,
+                        _CODE[bias.dtype] if bias is not None else 0, act, accumulate,
+                        step.data_ptr() if step is not None else None, float(alpha), err.data_ptr(), 0, _stream())
+        if rc >= 0:
+            _check(rc, "gemm2cta_tcgen05")
+            _count("gemm2cta_tcgen05")
+            return out
     rc = _gemm_fused(a.data_ptr(), b.data_ptr(), out_ptr, M, N, K, batch, a_mn, b_mn, lda, ldb, ldc, sa, sb, stride_c,
                      int(a.dtype == torch.float16), _CODE[out.dtype], bias.data_ptr() if bias is not None else None,
                      _CODE[bias.dtype] if bias is not None else 0, act, accumulate,

@@ -89,7 +89,8 @@ def main():
         ours = time_ms(lambda: nat.gemm(av, bv), iters=args.iters)
         lib = time_ms(lambda: torch.matmul(av, bv), iters=args.iters) if args.only is None else ours
         fl = 2.0 * M * N * K * batch
-        rows.append(dict(kernel=name, shape=f"{batch}x{M}x{N}x{K}", ms=ours, tflops=fl / ours / 1e9,
+        tag = " [CTA pairs]" if nat._GEMM_CTA_PAIRS and N > 128 else ""
+        rows.append(dict(kernel=name + tag, shape=f"{batch}x{M}x{N}x{K}", ms=ours, tflops=fl / ours / 1e9,
                          frac_of_peak=fl / ours / 1e9 / peaks["bf16_tflops"], lib_ms=lib, lib_tflops=fl / lib / 1e9,
                          vs_lib=lib / ours))
 

@@ -297,6 +297,45 @@ def test_single_kernel_attention_forward(nat, B, S, H, D, causal, dtype):
     torch.testing.assert_close(lse, torch.logsumexp(s, -1), rtol=1e-3, atol=1e-2)
 
 
+@pytest.mark.skipif(os.environ.get("XL_GEMM_CTA_PAIRS") != "1",
+                    reason="the CTA-pair GEMM is opt-in (XL_GEMM_CTA_PAIRS=1)")
+@pytest.mark.parametrize("M,N,K,batch,ta,tb,dtype", [
+    (256, 256, 64, 1, False, False, torch.bfloat16),      # one tile, one k-block
+    (512, 512, 512, 1, False, False, torch.bfloat16),     # the ring wraps (8 k-blocks over 6 stages)
+    (384, 640, 200, 1, False, False, torch.float16),      # ragged M (peer half empty), N and K
+    (512, 768, 256, 1, True, False, torch.bfloat16),      # A stored (K, M)
+    (512, 768, 256, 1, False, True, torch.bfloat16),      # B stored (N, K)
+    (512, 768, 256, 1, True, True, torch.bfloat16),
+    (300, 264, 128, 3, False, False, torch.bfloat16),     # batched
+    (4096, 4096, 1024, 1, False, True, torch.bfloat16),   # more tiles than CTA pairs: both accumulator buffers cycle
+])
+def test_cta_pair_gemm(nat, M, N, K, batch, ta, tb, dtype):
+    """256 x 256 tiles on CTA pairs against an fp32 product; every epilogue form on one shape."""
+    torch.manual_seed(5)
+    lead = (batch,) if batch > 1 else ()
+    a = torch.randn(*lead, K, M, device="cuda").to(dtype).transpose(-1, -2) if ta else torch.randn(*lead, M, K, device="cuda").to(dtype)
+    b = torch.randn(*lead, N, K, device="cuda").to(dtype).transpose(-1, -2) if tb else torch.randn(*lead, K, N, device="cuda").to(dtype)
+    want = a.float() @ b.float()
+    before = nat.LAUNCHES["by_kernel"].get("gemm2cta_tcgen05", 0)
+    out = nat.gemm(a, b)
+    assert out is not NotImplemented
+    nat.check_gemm_errors()
+    assert nat.LAUNCHES["by_kernel"].get("gemm2cta_tcgen05", 0) == before + 1, "the CTA-pair kernel did not run"
+    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    if (M, N, K) == (512, 512, 512):
+        bias = torch.randn(N, device="cuda").to(dtype)
+        got = nat.gemm(a, b, bias=bias, act=3, alpha=0.5, out_dtype=torch.float32)
+        torch.testing.assert_close(got, torch.relu(0.5 * want + bias.float()), rtol=2e-2, atol=0.5)
+        acc = torch.ones(M, N, device="cuda")
+        nat.gemm(a, b, out=acc, accumulate=1)
+        torch.testing.assert_close(acc, want + 1.0, rtol=2e-2, atol=0.5)
+        step = torch.full((1,), 3.0, device="cuda")
+        mean = torch.full((M, N), 4.0, device="cuda")
+        nat.gemm(a, b, out=mean, accumulate=2, step=step)
+        torch.testing.assert_close(mean, 4.0 * 0.75 + want * 0.25, rtol=2e-2, atol=0.5)
+        nat.check_gemm_errors()
+
+
 def test_bounded_wait_on_a_peer_gives_up_and_reports(nat):
     """Failure detection on the device without a fault: a barrier whose peer never signals (a flag nothing sets) must
     run out of its poll budget, record the reason in the status word and return; the context stays usable."""
