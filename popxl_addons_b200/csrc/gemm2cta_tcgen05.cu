@@ -117,7 +117,7 @@ __device__ __forceinline__ void tcgen05_mma_f16_pair(uint32_t tmem_d, uint64_t d
       : "memory");
 }
 // Tiled load into this CTA's shared memory whose transaction bytes complete on a barrier that may live in the peer CTA
-// (`bar_cluster_addr`). One source, one destination: no multicast.
+// (`bar_cluster_addr`). Each CTA loads its own tile: one source, one destination.
 __device__ __forceinline__ void tma_load_3d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0,
                                                  int c1, int c2) {
   asm volatile(
