@@ -81,3 +81,37 @@ def test_every_call_site_passes_as_many_arguments_as_the_binding_declares():
             assert not node.keywords and len(node.args) == len(fn.argtypes), \
                 f"{rel}:{node.lineno}: {name} is called with {len(node.args)} arguments, declared with {len(fn.argtypes)}"
     assert calls >= 50
+
+
+def test_gemm_entry_points_reject_unsupported_arguments_on_the_host():
+    """Shapes and alignments a kernel does not take are refused before any CUDA call (return -1), so the caller can
+    fall back; nothing here touches a device."""
+    from popxl_addons_b200.ops import native
+
+    ok = dict(a=256, b=512, c=1024, M=256, N=256, K=64, batch=1, a_mn=0, b_mn=0, lda=64, ldb=64, ldc=256, sa=0, sb=0,
+              sc=0, fp16=0, cdt=2)
+
+    def pair(**kw):
+        v = {**ok, **kw}
+        return native._gemm_pair(v["a"], v["b"], v["c"], v["M"], v["N"], v["K"], v["batch"], v["a_mn"], v["b_mn"],
+                                 v["lda"], v["ldb"], v["ldc"], v["sa"], v["sb"], v["sc"], v["fp16"], v["cdt"], None, 0, 0,
+                                 v.get("accumulate", 0), None, 1.0, None, 0, None)
+
+    assert pair(N=128) == -1              # narrow outputs stay on the single-CTA kernel
+    assert pair(M=0) == -1
+    assert pair(a=260) == -1              # operand not 16-byte aligned
+    assert pair(lda=60) == -1             # leading dimension not a multiple of 8 elements
+    assert pair(batch=2, sa=12) == -1
+    assert pair(accumulate=3) == -1       # collective epilogues are not implemented on CTA pairs
+    assert pair(accumulate=2) == -1       # running mean without a step counter
+
+    def single(**kw):
+        v = {**ok, **kw}
+        return native._gemm(v["a"], v["b"], v["c"], v["M"], v["N"], v["K"], v["batch"], v["a_mn"], v["b_mn"], v["lda"],
+                            v["ldb"], v["ldc"], v["sa"], v["sb"], v["sc"], v["fp16"], v["cdt"], None, 0, 0,
+                            v.get("accumulate", 0), None, 1.0, None, 148, None, 0, 1, None, None)
+
+    assert single(K=0) == -1
+    assert single(b=516) == -1
+    assert single(accumulate=4) == -1     # reduce-scatter needs the full entry point
+    assert single(accumulate=3) < 0       # all-reduce without signal pads (or no driver to encode tensor maps)
