@@ -45,7 +45,8 @@ class PipelineTrainer:
                  device: str = "auto", seed: int = 0, lr: float = 1e-4, weight_decay: float = 0.01, beta1: float = 0.9,
                  beta2: float = 0.95, eps: float = 1e-5, recompute: bool = True,
                  optimizer_state_dtype: xl.dtype = xl.float32, shard_optimizer: bool = True,
-                 fused_collectives: bool = True, use_native: Optional[bool] = None):
+                 fused_collectives: bool = True, use_native: Optional[bool] = None,
+                 prune_recompute: Optional[bool] = None):
         if cfg.tp != 1:
             raise ValueError("PipelineTrainer combines pipeline and data parallelism (tp must be 1)")
         if cfg.layers % stages:
@@ -65,6 +66,9 @@ class PipelineTrainer:
                    else xl.Ir(replication=cfg.dp))
         self.hp = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay)
         self.recompute = recompute
+        # the recomputed forward pass leaves out what only leads to the block's output (XL_PRUNE_RECOMPUTE=1)
+        self.prune_recompute = (os.environ.get("XL_PRUNE_RECOMPUTE", "0") == "1") if prune_recompute is None \
+            else bool(prune_recompute)
         self.state_dtype = optimizer_state_dtype
         self.shard_optimizer = shard_optimizer and cfg.dp > 1
         self.fused_collectives = fused_collectives
@@ -97,7 +101,7 @@ class PipelineTrainer:
                                                               grads_required=[blk_graph.graph.inputs[0]],
                                                               accum_dtype=f32)
             if self.recompute:
-                blk_grad = recompute_graph(blk_grad)
+                blk_grad = recompute_graph(blk_grad, prune_forward=self.prune_recompute)
             head_dfacts, head_grad = autodiff_with_accumulation(head_graph, head_graph.args.tensors,
                                                                 grads_required=[head_graph.graph.inputs[0]],
                                                                 accum_dtype=f32)

@@ -135,7 +135,8 @@ class DecoderTrainer:
     def __init__(self, cfg: DecoderConfig, micro_batches: int = 16, micro_batch_size: int = 1, device: str = "auto",
                  seed: int = 0, lr: float = 1e-4, weight_decay: float = 0.01, beta1: float = 0.9, beta2: float = 0.95,
                  eps: float = 1e-5, recompute: bool = True, optimizer_state_dtype: xl.dtype = xl.float32,
-                 shard_optimizer: bool = True, use_native: Optional[bool] = None, fused_collectives: bool = True, cuda_graphs: bool = True):
+                 shard_optimizer: bool = True, use_native: Optional[bool] = None, fused_collectives: bool = True, cuda_graphs: bool = True,
+                 prune_recompute: Optional[bool] = None):
         self.cfg = cfg
         self.micro_batches = micro_batches
         self.micro_batch_size = micro_batch_size
@@ -147,6 +148,9 @@ class DecoderTrainer:
         self.ir = xl.Ir(replication="popdist" if distributed else cfg.tp * cfg.dp)
         self.hp = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps, weight_decay=weight_decay)
         self.recompute = recompute
+        # the recomputed forward pass leaves out what only leads to the block's output (XL_PRUNE_RECOMPUTE=1)
+        self.prune_recompute = (os.environ.get("XL_PRUNE_RECOMPUTE", "0") == "1") if prune_recompute is None \
+            else bool(prune_recompute)
         self.state_dtype = optimizer_state_dtype
         self.shard_optimizer = shard_optimizer and cfg.dp > 1
         self.fused_collectives = fused_collectives
@@ -198,7 +202,7 @@ class DecoderTrainer:
                                                               grads_required=[blk_graph.graph.inputs[0]],
                                                               accum_dtype=f32)
             if self.recompute:
-                blk_grad = recompute_graph(blk_grad)
+                blk_grad = recompute_graph(blk_grad, prune_forward=self.prune_recompute)
             head_dfacts, head_grad = autodiff_with_accumulation(head_graph, head_graph.args.tensors,
                                                                 grads_required=[head_graph.graph.inputs[0]],
                                                                 accum_dtype=f32)

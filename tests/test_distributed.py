@@ -57,6 +57,13 @@ def test_cpu_ranks_match_simulation(tp, dp):
     np.testing.assert_allclose(got["losses"], ref, rtol=2e-4)
 
 
+def test_cpu_ranks_with_pruned_recomputation_match_simulation():
+    """Every rank leaves the same all-reduce out of its recomputed forward pass, so the ranks stay in step."""
+    ref = simulated(2, 1, "float32")
+    got = launch(2, "--device", "cpu", "--tp", "2", "--dp", "1", "--dtype", "float32", env={"XL_PRUNE_RECOMPUTE": "1"})
+    np.testing.assert_allclose(got["losses"], ref, rtol=2e-4)
+
+
 def test_cpu_rank_collectives():
     assert launch(2, "--mode", "collectives", "--device", "cpu")["ok"]
 

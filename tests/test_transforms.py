@@ -489,3 +489,71 @@ def test_matmul_sum_and_collective_fusion_passes_keep_the_numbers():
     np.testing.assert_allclose(z1, z0, rtol=1e-5, atol=1e-5)
     want = (a1 @ w1 + a2 @ w2).sum(axis=0)
     np.testing.assert_allclose(y0[0], want, rtol=1e-5, atol=1e-5)
+
+
+def test_pruned_recomputation_gives_identical_training_with_less_work():
+    """The recomputed forward pass reduced to what the gradient graph reads: same losses and same weights bit for bit
+    for every model family (plain, tensor-parallel with and without fused collectives, sequence-parallel, pipelined),
+    and the block's output projections, their all-reduce and the residual add are gone from the second pass."""
+    import dataclasses
+    import os
+    import sys
+
+    from popxl_addons_b200.models import decoder as dec
+    from popxl_addons_b200.models.decoder import DecoderConfig
+    from popxl_addons_b200.models.trainer import DecoderTrainer
+
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from dist_worker import global_tokens
+
+    def run(cfg, prune, **kw):
+        dec._SEED[0] = 0
+        tr = DecoderTrainer(cfg, micro_batches=2, device="cpu", lr=1e-2, prune_recompute=prune, **kw)
+        tr.session.start_profile()
+        losses = [tr.step(global_tokens(cfg, 2, seed=s)) for s in range(2)]
+        counts = {k: v["count"] for k, v in tr.session.profile_summary().items()}
+        weights = {k: np.array(v) for k, v in tr.session.get_named_tensors_data().to_dict().items()}
+        names = {g.name: [o.opdef.name for o in g.ops] for g in tr.ir.graphs}
+        return losses, weights, counts, names
+
+    cases = [(DecoderConfig.tiny("gptj", dtype="float32", tp=1, dp=1), {}),
+             (DecoderConfig.tiny("gptj", dtype="float32", tp=2, dp=1), {}),
+             (DecoderConfig.tiny("gptj", dtype="float32", tp=2, dp=2), dict(fused_collectives=False)),
+             (DecoderConfig.tiny("llama", dtype="float32", tp=2, dp=1), {}),
+             (DecoderConfig.tiny("gpt2", dtype="float32", tp=1, dp=2), {}),
+             (dataclasses.replace(DecoderConfig.tiny("gptj", dtype="float32", tp=2, dp=1), sequence_parallel=True), {})]
+    for cfg, kw in cases:
+        l0, w0, c0, _ = run(cfg, False, **kw)
+        l1, w1, c1, names = run(cfg, True, **kw)
+        assert l0 == l1, (cfg.family, cfg.tp, cfg.dp)
+        assert w0.keys() == w1.keys()
+        for k in w0:
+            np.testing.assert_array_equal(w0[k], w1[k], err_msg=k)
+        gemms = lambda c: sum(v for k, v in c.items() if "matmul" in k or "linear" in k)  # noqa: E731
+        assert gemms(c1) < gemms(c0), (cfg.family, cfg.tp, cfg.dp, cfg.sequence_parallel, sorted(c0.items()), sorted(c1.items()))
+        if cfg.tp > 1:
+            comm = lambda c: sum(v for k, v in c.items() if "all_reduce" in k or "reduce_scatter" in k)  # noqa: E731
+            assert comm(c1) < comm(c0), (c0, c1)
+        pruned = [n for n in names if "recomp_fwd" in n]
+        assert len(pruned) == 1
+
+    # pipelined: the recomputing block graph runs inside the pipeline stages
+    import torch
+
+    from popxl_addons_b200.models.pipeline_trainer import PipelineTrainer
+
+    cfg = DecoderConfig.tiny("llama", layers=4, dtype="float32", tp=1, dp=1)
+    outs = []
+    for prune in (False, True):
+        dec._SEED[0] = 0
+        tr = PipelineTrainer(cfg, stages=2, micro_batches=6, device="cpu", lr=1e-2, prune_recompute=prune)
+        losses = []
+        for step in range(2):
+            g = torch.Generator().manual_seed(step)
+            tok = torch.randint(0, cfg.vocab_size, (6, 1, 1, cfg.seq_len + 1), generator=g, dtype=torch.int32)
+            losses.append(np.asarray(tr.session.run({tr.inputs.tokens: tok, tr.inputs.labels: tok})[tr.outputs.loss]))
+        outs.append((losses, {k: np.array(v) for k, v in tr.session.get_named_tensors_data().to_dict().items()}))
+    for a, b in zip(outs[0][0], outs[1][0]):
+        np.testing.assert_array_equal(a, b)
+    for k in outs[0][1]:
+        np.testing.assert_array_equal(outs[0][1][k], outs[1][1][k], err_msg=k)
