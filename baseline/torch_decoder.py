@@ -78,9 +78,10 @@ class Block(nn.Module):
 
 
 class Model(nn.Module):
-    def __init__(self, cfg, tp, group, tp_rank):
+    def __init__(self, cfg, tp, group, tp_rank, recompute=True):
         super().__init__()
         self.cfg, self.tp, self.group, self.tp_rank = cfg, tp, group, tp_rank
+        self.recompute = recompute
         self.vshard = -(-cfg.vocab_size // tp)
         self.wte = nn.Embedding(self.vshard, cfg.hidden)
         self.blocks = nn.ModuleList([Block(cfg, tp, group) for _ in range(cfg.layers)])
@@ -99,7 +100,7 @@ class Model(nn.Module):
         if self.tp > 1:
             x = _ReduceFromTP.apply(x, self.group)
         for blk in self.blocks:
-            x = checkpoint(blk, x, self.sin, self.cos, use_reentrant=False)
+            x = checkpoint(blk, x, self.sin, self.cos, use_reentrant=False) if self.recompute else blk(x, self.sin, self.cos)
         h = self.ln_f(x)
         if self.tp > 1:
             h = _CopyToTP.apply(h, self.group)
@@ -118,7 +119,7 @@ class Model(nn.Module):
 
 
 class TorchTrainer:
-    def __init__(self, cfg, micro_batches=16, lr=1e-4):
+    def __init__(self, cfg, micro_batches=16, lr=1e-4, recompute=True):
         self.cfg, self.micro_batches = cfg, micro_batches
         world = int(os.environ.get("WORLD_SIZE", "1"))
         rank = int(os.environ.get("RANK", "0"))
@@ -140,7 +141,7 @@ class TorchTrainer:
                     self.dp_group = grp
         torch.manual_seed(1234 + rank % tp)
         with torch.device("cuda"):
-            self.model = Model(cfg, tp, self.tp_group, rank % tp)
+            self.model = Model(cfg, tp, self.tp_group, rank % tp, recompute=recompute)
         for p in self.model.parameters():
             if p.dim() >= 2:
                 nn.init.normal_(p, std=0.02)

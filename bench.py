@@ -232,6 +232,9 @@ def main():
     ap.add_argument("--stages", type=int, default=4, help="pipeline mode: device slots (GPUs) per replica")
     ap.add_argument("--sequence-parallel", action="store_true",
                     help="train mode: shard the residual stream over the tokens inside the TP group")
+    ap.add_argument("--no-recompute", action="store_true",
+                    help="train / pipeline mode, both arms: keep the activations of every layer instead of running each "
+                         "block's forward pass a second time (a micro-batch of 2048 tokens keeps about 6 GB at TP1)")
     ap.add_argument("--prune-recompute", action="store_true",
                     help="train / pipeline mode: the recomputed forward pass of a block leaves out the ops that only lead "
                          "to the block's output (also XL_PRUNE_RECOMPUTE=1); the gradients are bit-identical")
@@ -297,7 +300,7 @@ def main():
                 pass
 
         native = _NoNative
-        tt = TorchTrainer(cfg, micro_batches=args.micro_batches)
+        tt = TorchTrainer(cfg, micro_batches=args.micro_batches, recompute=not args.no_recompute)
 
         class _Adapter:
             tokens_per_step = tt.tokens_per_step
@@ -326,10 +329,11 @@ def main():
 
         trainer = PipelineTrainer(cfg, stages=stages, micro_batches=args.micro_batches,
                                   micro_batch_size=args.micro_batch_size, device="cuda", seed=0, lr=1e-4,
+                                  recompute=not args.no_recompute,
                                   prune_recompute=True if args.prune_recompute else None)
     else:
         trainer = DecoderTrainer(cfg, micro_batches=args.micro_batches, micro_batch_size=args.micro_batch_size,
-                                 device="cuda", seed=0, lr=1e-4,
+                                 device="cuda", seed=0, lr=1e-4, recompute=not args.no_recompute,
                                  prune_recompute=True if args.prune_recompute else None)
         from popxl_addons_b200.ops import native
     setup_s = time.perf_counter() - t0
@@ -399,8 +403,9 @@ def main():
                        "parallelism": (f"pp{stages}xdp{dp}" if pipeline else f"tp{tp}xdp{dp}"), "micro_batches": args.micro_batches, "micro_batch_size": args.micro_batch_size,
                        "optimizer": "AdamW, fp32 master weights + fp32 moments" +
                                     (", state sharded over dp (RTS)" if dp > 1 else ""),
-                       "recompute": "per layer" + (", second forward pass reduced to what the backward pass reads"
-                                                     if trainer.prune_recompute else ""), "l2": "each step streams >100 GB of weights, optimizer state and "
+                       "recompute": "none (activations kept)" if args.no_recompute else "per layer" + (
+                           ", second forward pass reduced to what the backward pass reads"
+                           if args.impl == "ours" and trainer.prune_recompute else ""), "l2": "each step streams >100 GB of weights, optimizer state and "
                                                        "activations, far beyond the 126 MB L2; no flush needed",
                        "emulate_tp": args.emulate_tp or None, "sequence_parallel": bool(args.sequence_parallel),
                        "headline": (not args.layers and not args.emulate_tp and args.model == "gptj_6b" and not pipeline
