@@ -412,6 +412,7 @@ def main():
                                     and not args.tp
                                     and args.micro_batch_size == 1 and args.micro_batches == 16)},
             "clocks": clocks.summary(),
+            "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": int(h2d),
                     "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches),
