@@ -21,11 +21,19 @@ _PURE_SPECIAL = {"all_reduce", "all_gather", "reduce_scatter", "matmul_all_reduc
                  "matmuls_reduce_scatter", "all_gather_matmul", "replica_sharded_slice", "init"}
 
 
-def _is_pure(op) -> bool:
-    """True if the op may be dropped when nothing reads its outputs."""
+def _is_pure(op, _seen=None) -> bool:
+    """True if the op may be dropped when nothing reads its outputs. A call is pure if the called graph takes nothing by
+    reference and holds only pure ops."""
     d = op.opdef
     if d.inplace or d.name.endswith("_") or op.attrs.get("inplace"):
         return False
+    if d.name == "call":
+        callee = op.attrs["graph"]
+        seen = _seen if _seen is not None else set()
+        if callee in seen:  # recursion: be conservative
+            return False
+        seen.add(callee)
+        return not callee._by_ref and not op.attrs.get("modified") and all(_is_pure(o, seen) for o in callee.ops)
     return d.special is None or d.name in _PURE_SPECIAL
 
 

@@ -321,10 +321,11 @@ def test_autodiff_of_random_programs_matches_torch_autograd(program, seed):
 @settings(max_examples=25, deadline=None)
 @given(st.lists(st.one_of(st.tuples(st.just("u"), st.sampled_from(sorted(_UNARY)), st.integers(0, 9)),
                           st.tuples(st.just("b"), st.sampled_from(sorted(_BINARY)), st.integers(0, 9), st.integers(0, 9))),
-                min_size=1, max_size=6), st.integers(0, 1000), st.integers(1, 3))
-def test_recomputation_and_accumulation_of_random_programs(program, seed, calls):
-    """For a random program with one parameter: the recomputing gradient graph (which only takes the forward inputs) gives
-    the gradients of the plain one, and the accumulating gradient graph leaves the mean of the per-call gradients."""
+                min_size=1, max_size=6), st.integers(0, 1000), st.integers(1, 3), st.booleans())
+def test_recomputation_and_accumulation_of_random_programs(program, seed, calls, prune):
+    """For a random program with one parameter: the recomputing gradient graph (which only takes the forward inputs; with
+    `prune` its second forward pass is cut down to what the gradient graph reads) gives the gradients of the plain one,
+    and the accumulating gradient graph leaves the mean of the per-call gradients."""
     from functools import partial
 
     rs = np.random.RandomState(seed)
@@ -350,7 +351,10 @@ def test_recomputation_and_accumulation_of_random_programs(program, seed, calls)
         facts, graph = Net().create_graph(x0)
         plain = addons.autodiff(graph)
         facts2, graph2 = Net().create_graph(x0)
-        recomputed = addons.recompute_graph(addons.autodiff(graph2))
+        recomputed = addons.recompute_graph(addons.autodiff(graph2), prune_forward=prune)
+        if prune:  # the final sum only leads to the output: it is never part of the second pass
+            second_pass = recomputed.graph.ops[0].attrs["graph"]
+            assert len(second_pass.ops) < len(graph2.graph.ops)
         facts3, graph3 = Net().create_graph(x0)
         acc_facts, accumulating = addons.autodiff_with_accumulation(graph3, [graph3.args.w], grads_required=[])
         w = facts.init()
@@ -375,6 +379,8 @@ def test_recomputation_and_accumulation_of_random_programs(program, seed, calls)
     for a, b in streams:
         assert len(a) == len(b)
         for sa, sb in zip(a, b):
+            if prune:
+                np.testing.assert_array_equal(out[sb], out[sa])
             np.testing.assert_allclose(out[sb], out[sa], rtol=1e-5, atol=1e-6)
         per_call.append(out[a[w_index]])
     np.testing.assert_allclose(mean_grad, np.mean(per_call, axis=0), rtol=1e-4, atol=1e-5)

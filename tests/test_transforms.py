@@ -557,3 +557,51 @@ def test_pruned_recomputation_gives_identical_training_with_less_work():
         np.testing.assert_array_equal(a, b)
     for k in outs[0][1]:
         np.testing.assert_array_equal(outs[0][1][k], outs[1][1][k], err_msg=k)
+
+
+def test_prune_graph_keeps_effects_and_drops_pure_calls():
+    """`prune_graph`: calls to graphs without effects are dropped when nothing reads them; ops with an effect of their own
+    (an in-place update here) stay with everything they depend on; tensors of other graphs are refused."""
+    from popxl_addons_b200.transforms.recomputation import prune_graph
+
+    ir = popxl.Ir()
+
+    def inner(a, w):
+        return ops.gelu(a @ w)
+
+    def outer(x, w1, w2, counter: popxl.TensorByRef):
+        gi = ir.create_graph(inner, x, w1)
+        (h,) = ops.call(gi, x, w1)
+        (y,) = ops.call(gi, h, w2)
+        ops.var_updates.accumulate_(counter, ops.sum(y))  # an effect: stays, and keeps the second call alive
+        return x + y, h
+
+    def outer_pure(x, w1, w2):
+        gi = ir.create_graph(inner, x, w1)
+        (h,) = ops.call(gi, x, w1)
+        (y,) = ops.call(gi, h, w2)
+        return x + y, h
+
+    rs = np.random.RandomState(0)
+    with ir.main_graph:
+        x, w1, w2 = (popxl.variable(rs.normal(0, 1, (4, 4)).astype(np.float32), name=n) for n in ("x", "w1", "w2"))
+        c1 = popxl.variable(np.zeros((), np.float32), name="c1")
+        c2 = popxl.variable(np.zeros((), np.float32), name="c2")
+        g = ir.create_graph(outer, x, w1, w2, c1)
+        gp = ir.create_graph(outer_pure, x, w1, w2)
+        pruned, tmap = prune_graph(g, [g.outputs[1]])
+        pruned_pure, _ = prune_graph(gp, [gp.outputs[1]])
+        assert [o.opdef.name for o in pruned_pure.ops] == ["call"]
+        assert [o.opdef.name for o in pruned.ops] == ["call", "call", "sum", "accumulate_"]
+        assert pruned.is_by_ref(pruned.inputs[3]) and len(pruned.outputs) == 1 and tmap[g.inputs[0]] is pruned.inputs[0]
+        with pytest.raises(ValueError):
+            prune_graph(g, [gp.outputs[1]])
+        _, h_full = ops.call(g, x, w1, w2, c1)
+        (h_pruned,) = ops.call(pruned, x, w1, w2, c2)
+        (h_pure,) = ops.call(pruned_pure, x, w1, w2)
+        streams = [addons.host_store(t) for t in (h_full, h_pruned, h_pure)]
+    with popxl.Session(ir, "cpu") as s:
+        out = s.run()
+        np.testing.assert_array_equal(out[streams[0]], out[streams[1]])
+        np.testing.assert_array_equal(out[streams[0]], out[streams[2]])
+        assert s.get_tensor_data(c1) == s.get_tensor_data(c2) != 0
