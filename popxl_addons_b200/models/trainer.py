@@ -174,8 +174,18 @@ class DecoderTrainer:
         from ..parallel import fuse_matmul_sums
 
         self.fused_matmul_sums = fuse_matmul_sums(self.ir)  # what the collective fusion left: c = a1 @ w1 + a2 @ w2
+        # XL_ASYNC_COLLECTIVES=1: all-reduces run asynchronously, and each graph is reordered so that the ops that do not
+        # need an all-reduce's result (the weight-gradient GEMMs of a block) are issued before the ops that do
+        self.async_collectives = cfg.tp > 1 and os.environ.get("XL_ASYNC_COLLECTIVES", "0") == "1"
+        self.overlap_moves = 0
+        if self.async_collectives:
+            from ..parallel import schedule_collective_overlap
+
+            self.overlap_moves = schedule_collective_overlap(self.ir)
         self.build_seconds = time.perf_counter() - t0
         self.session = TaskSession(self.inputs, self.outputs, self.state, 1, self.ir, device, use_native=use_native)
+        if self.async_collectives and hasattr(self.session.comm, "async_collectives"):
+            self.session.comm.async_collectives = True
         self.tokens_per_step = micro_batches * micro_batch_size * cfg.seq_len * cfg.dp
 
     # ------------------------------------------------------------------------------------------------------------

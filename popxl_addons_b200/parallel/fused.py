@@ -290,7 +290,7 @@ class FusedComm(DistComm):
         super().__init__(num_replicas, device, devices_per_replica)
         self._session = session
 
-    def all_reduce(self, vals, grouping, op, inplace=False):
+    def all_reduce(self, vals, grouping, op, inplace=False, async_ok=False):
         t = vals[0]
         if t.dtype == torch.float32 and t.numel() <= _SMALL_ALL_REDUCE_ELEMS and op in ("add", "max") \
                 and grouping.group_size > 1 and t.is_contiguous():
@@ -310,7 +310,7 @@ class FusedComm(DistComm):
                     t.copy_(out)
                     return [t]
                 return [out]
-        return super().all_reduce(vals, grouping, op, inplace)
+        return super().all_reduce(vals, grouping, op, inplace, async_ok)
 
 
 def group_barrier(ctx: GroupContext, channel: int = 4):

@@ -411,3 +411,59 @@ def fuse_gemm_collectives(ir: xl.Ir) -> int:
             new_ops.append(op)
         g.ops = [o for o in new_ops if o.uid not in skip]
     return fused
+
+
+# ---- overlap: ops that do not need an all-reduce's result move in front of the ops that do ---------------------------------
+
+def _written_operands(op):
+    """Tensors of the op's graph that the op writes: [] for a pure op, None for an op nothing may move across."""
+    from ..transforms.recomputation import _is_pure
+
+    if _is_pure(op):
+        return []
+    name = op.opdef.name
+    if name == "call":
+        callee = op.attrs["graph"]
+        return [op.inputs[i] for i, t in enumerate(callee._inputs) if callee.is_by_ref(t)]
+    if op.opdef.inplace:
+        return [op.inputs[0]]  # the in-place ops of this package update their first operand
+    return None
+
+
+def schedule_collective_overlap(ir: xl.Ir) -> int:
+    """Reorder every graph so that an `all_reduce` is followed first by the ops that do not depend on it and only then
+    by its consumers. With asynchronous collectives (`comm.async_collectives`) the all-reduce of a tensor-parallel
+    block's input gradient then runs under the block's weight-gradient GEMMs. Data dependencies and the order of
+    updates to one tensor are kept, so every op computes what it computed before. Returns the number of ops moved."""
+    moved = 0
+    for g in ir.graphs:
+        start = 0
+        while True:
+            idx = next((i for i in range(start, len(g.ops)) if g.ops[i].opdef.name == "all_reduce"
+                        and g.ops[i].attrs["group"].group_size > 1), None)
+            if idx is None:
+                break
+            start = idx + 1
+            tainted = set(g.ops[idx].outputs)          # values that exist only after the all-reduce
+            read_late, written_late = set(), set()     # operands of the ops that stay behind it
+            early, late = [], []
+            tail = g.ops[idx + 1:]
+            stop = len(tail)
+            for j, op in enumerate(tail):
+                writes = _written_operands(op)
+                if writes is None:
+                    stop = j
+                    break
+                depends = any(t in tainted or t in written_late for t in op.inputs) \
+                    or any(t in read_late or t in written_late for t in writes)
+                if depends:
+                    late.append(op)
+                    tainted.update(op.outputs)
+                    read_late.update(op.inputs)
+                    written_late.update(writes)
+                else:
+                    if late:
+                        moved += 1
+                    early.append(op)
+            g.ops[idx + 1:] = early + late + tail[stop:]
+    return moved

@@ -41,12 +41,18 @@ def _pad_flat(t: torch.Tensor, size: int) -> Tuple[torch.Tensor, int]:
 class SimComm:
     """All replicas in one process. `vals[r]` is replica r's tensor."""
 
+    pending: Dict[int, tuple] = {}  # collectives in flight: always empty here (the simulation is synchronous)
+
     def __init__(self, num_replicas: int):
         self.num_replicas = num_replicas
         self.rank = 0
         self.world_size = 1
 
-    def all_reduce(self, vals: List[torch.Tensor], grouping: ReplicaGrouping, op: str, inplace: bool = False):
+    def wait_all(self):
+        pass
+
+    def all_reduce(self, vals: List[torch.Tensor], grouping: ReplicaGrouping, op: str, inplace: bool = False,
+                   async_ok: bool = False):
         out = list(vals)
         for members in grouping.groups:
             acc_dtype = torch.float32 if vals[members[0]].dtype in (torch.float16, torch.bfloat16) else None
@@ -121,6 +127,9 @@ class DistComm:
         self._p2p: list = []
         self.device = device
         self._groups: Dict[tuple, object] = {}
+        # all-reduces as asynchronous operations that overlap the ops issued after them (off by default)
+        self.async_collectives = False
+        self.pending: Dict[int, tuple] = {}
 
     def group_for(self, grouping: ReplicaGrouping):
         """Process group of this rank within `grouping` (creating, collectively, all groups of the grouping)."""
@@ -139,14 +148,27 @@ class DistComm:
             self._groups[key] = mine
         return self._groups[key]
 
-    def all_reduce(self, vals, grouping, op, inplace=False):
+    def all_reduce(self, vals, grouping, op, inplace=False, async_ok=False):
+        """`async_ok`: the caller does not read the result itself (the executor joins the operation before the first op
+        that does), so with `async_collectives` the all-reduce may stay in flight when this returns."""
         pg, members = self.group_for(grouping)
         t = vals[0] if inplace else vals[0].clone()
         if len(members) > 1:
+            if async_ok and self.async_collectives and op != "mean":
+                # issued on the library's own stream; the executor waits right before the first op that reads `t`
+                work = self.dist.all_reduce(t, op=getattr(self.dist.ReduceOp, self._REDUCE[op]), group=pg, async_op=True)
+                self.pending[id(t)] = (work, t)  # holding `t` keeps its id unique while the entry exists
+                return [t]
             self.dist.all_reduce(t, op=getattr(self.dist.ReduceOp, self._REDUCE[op]), group=pg)
             if op == "mean":
                 t.div_(len(members))
         return [t]
+
+    def wait_all(self):
+        """Join every collective still in flight (end of a run, end of a captured loop body)."""
+        while self.pending:
+            _, (work, _t) = self.pending.popitem()
+            work.wait()
 
     # -- point-to-point between the device slots of one replica (pipeline stage boundaries) ------------------------
     def send_to_slot(self, t: torch.Tensor, slot: int):

@@ -38,7 +38,8 @@ def _special_all_reduce(ex, op, env):
             "An all-reduce with identical inputs is an identity in the forward pass: run "
             "`apply_pre_alias_patterns(ir)` (OpToIdentityPattern) before creating the session.")
     vals = env[op.inputs[0]]
-    env[op.outputs[0]] = ex.comm.all_reduce(vals, op.attrs["group"], op.attrs["op"], inplace=op.attrs["inplace"])
+    env[op.outputs[0]] = ex.comm.all_reduce(vals, op.attrs["group"], op.attrs["op"], inplace=op.attrs["inplace"],
+                                            async_ok=True)
 
 
 def _vjp_all_reduce(ctx, op, gs):

@@ -593,6 +593,14 @@ class Session:
                 if self._effective_device(op, frame) != self.slot:
                     continue
                 self.comm.flush_p2p()  # received tensors may be read from here on
+            pending = self.comm.pending
+            if pending and od.name not in ("call", "repeat", "conditional"):
+                # an all-reduce still in flight is joined right before the first op that reads its result
+                for t in op.inputs:
+                    for x in env.get(t) or ():
+                        entry = pending.pop(id(x), None)
+                        if entry is not None:
+                            entry[0].wait()
             timed = self.profile is not None and od.name not in ("call", "repeat", "conditional")
             if timed:
                 t_start = self._now()
@@ -647,6 +655,7 @@ class Session:
         outs = vals[:n_out]
         for _ in range(count):
             outs = self.run_graph(graph, vals)
+            self.comm.wait_all()
             vals = list(outs) + list(vals[n_out:])
         for t, v in zip(op.outputs, outs):
             env[t] = v
@@ -668,6 +677,7 @@ class Session:
 
         if state is None:
             self.run_graph(graph, vals)  # eager warm-up iteration
+            self.comm.wait_all()
             note("eager iteration done")
             it = 1
             if count == 1:
@@ -716,6 +726,7 @@ class Session:
         try:
             with torch.cuda.graph(g, capture_error_mode="thread_local"):
                 self.run_graph(graph, vals)
+                self.comm.wait_all()  # every stream forked inside the body joins before the capture ends
         finally:
             _native._RECORDING.pop()
             outs = self._capture_outputs
@@ -745,6 +756,7 @@ class Session:
         env: Dict[Tensor, List[torch.Tensor]] = {}
         with torch.no_grad():
             self._exec_ops(main, env)
+            self.comm.wait_all()
         out = self._collect_outputs(fetch)
         if self.use_native and fetch:
             from ..ops import native as _native

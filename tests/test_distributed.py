@@ -64,6 +64,16 @@ def test_cpu_ranks_with_pruned_recomputation_match_simulation():
     np.testing.assert_allclose(got["losses"], ref, rtol=2e-4)
 
 
+def test_cpu_ranks_with_asynchronous_all_reduces_match_simulation():
+    """All-reduces issued asynchronously and joined before their first reader, in graphs reordered so that the
+    weight-gradient GEMMs run in between (also together with the pruned second forward pass)."""
+    ref = simulated(2, 1, "float32")
+    for extra in ({}, {"XL_PRUNE_RECOMPUTE": "1"}):
+        got = launch(2, "--device", "cpu", "--tp", "2", "--dp", "1", "--dtype", "float32",
+                     env={"XL_ASYNC_COLLECTIVES": "1", "XL_FUSE_GEMM_AR": "0", **extra})
+        np.testing.assert_allclose(got["losses"], ref, rtol=2e-4)
+
+
 def test_cpu_rank_collectives():
     assert launch(2, "--mode", "collectives", "--device", "cpu")["ok"]
 

@@ -605,3 +605,50 @@ def test_prune_graph_keeps_effects_and_drops_pure_calls():
         np.testing.assert_array_equal(out[streams[0]], out[streams[1]])
         np.testing.assert_array_equal(out[streams[0]], out[streams[2]])
         assert s.get_tensor_data(c1) == s.get_tensor_data(c2) != 0
+
+
+def test_schedule_collective_overlap_keeps_dependencies_and_update_order():
+    """The ops that do not need an all-reduce's result move in front of its consumers; an update of a tensor that a
+    consumer reads, and anything behind an op with an unknown effect, stays where it is. Results are unchanged."""
+    from popxl_addons_b200.parallel import schedule_collective_overlap
+
+    def build(ir):
+        rg = ir.replica_grouping()
+
+        def body(x, w, acc1: popxl.TensorByRef, acc2: popxl.TensorByRef):
+            s = ops.collectives.replicated_all_reduce(x, "add", rg)
+            y = ops.gelu(s)                                   # consumer of the all-reduce
+            ops.var_updates.accumulate_(acc1, y)              # depends on it
+            g = x @ w                                         # independent: moves up
+            ops.var_updates.accumulate_(acc2, g)              # independent update of another tensor: moves up
+            z = y + acc2                                      # reads acc2 after its update: must stay behind it
+            ops.var_updates.accumulate_(acc1, g)              # second update of acc1: stays behind the first one
+            return z
+
+        with ir.main_graph:
+            x = popxl.variable(np.arange(32, dtype=np.float32).reshape(2, 4, 4) / 10, name="x",
+                               replica_grouping=ir.replica_grouping(group_size=1))
+            w = popxl.variable(np.eye(4, dtype=np.float32) * 2, name="w")
+            a1 = popxl.variable(np.zeros((4, 4), np.float32), name="a1")
+            a2 = popxl.variable(np.zeros((4, 4), np.float32), name="a2")
+            g = ir.create_graph(body, x, w, a1, a2)
+            (z,) = ops.call(g, x, w, a1, a2)
+            out = addons.host_store(z)
+        return g, out, a1, a2
+
+    results = []
+    for reorder in (False, True):
+        ir = popxl.Ir(replication=2)
+        g, out, a1, a2 = build(ir)
+        before = [o.opdef.name for o in g.ops]
+        assert before == ["all_reduce", "gelu", "accumulate_", "matmul", "accumulate_", "add", "accumulate_"]
+        if reorder:
+            assert schedule_collective_overlap(ir) == 2
+            assert [o.opdef.name for o in g.ops] == ["all_reduce", "matmul", "accumulate_", "gelu", "accumulate_", "add",
+                                                     "accumulate_"]
+            assert g.ops[2].inputs[0] is g.inputs[3] and g.ops[4].inputs[0] is g.inputs[2] and g.ops[6].inputs[0] is g.inputs[2]
+        with popxl.Session(ir, "cpu") as s:
+            o = s.run()
+            results.append((o[out], s.get_tensor_data(a1), s.get_tensor_data(a2)))
+    for a, b in zip(*results):
+        np.testing.assert_array_equal(a, b)
