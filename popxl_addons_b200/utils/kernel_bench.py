@@ -103,6 +103,11 @@ def main():
     gemm_row("gemm attn scores", 2048, 2048, 256, b_t=True, batch=16)
     gemm_row("gemm attn pv", 2048, 256, 2048, batch=16)
     gemm_row("gemm square 8192", 8192, 8192, 8192)
+    # one rank's shapes at TP4: 192 to 256 tiles of 128 x 256 on 148 SMs (the second wave is partly empty)
+    gemm_row("gemm tp4 fwd qkv", 2048, 3072, 4096)
+    gemm_row("gemm tp4 fwd out", 2048, 4096, 1024)
+    gemm_row("gemm tp4 fwd fc_in", 2048, 4096, 4096)
+    gemm_row("gemm tp4 wgrad fc_in (A,B MN-major)", 4096, 4096, 2048, a_t=True)
 
     def attention_row(name, S, H, D):
         """Causal attention forward of one GPT-J micro-batch: the default path (scores GEMM with causal tile skipping,
