@@ -1,10 +1,12 @@
 """Plain PyTorch (+cuBLAS, flash SDPA, NCCL) implementation of the benchmark configuration: the number this framework
 has to match or beat on the same machine (the reference itself cannot run without Graphcore hardware).
 
-Same model shape, same step: 16 micro-batches of 1 x 2048 tokens with gradient accumulation, per-layer activation
-checkpointing, bf16 compute (autocast) over fp32 parameters, fused AdamW with fp32 moments, Megatron-style tensor
-parallelism (column/row-parallel linears with NCCL all-reduce, vocabulary-sharded embedding / head / cross-entropy) and
-data parallelism by gradient all-reduce.  `python bench.py --impl torch` drives it.
+Same model shape, same step: 16 micro-batches of 1 x 2048 tokens with gradient accumulation (optionally per-layer
+activation checkpointing), bf16 parameters and compute with fp32 master weights and fp32 moments (fused AdamW on the
+master copy, no per-micro-batch re-cast of the weights), Megatron-style tensor parallelism (column/row-parallel linears
+with NCCL all-reduce, vocabulary-sharded embedding / head / cross-entropy), data parallelism as ONE all-reduce of a flat
+gradient buffer per step, and the micro-batch (forward + backward) captured in a CUDA graph and replayed, as this
+package's arm does. What a competent PyTorch user would run.  `python bench.py --impl torch` drives it.
 """
 import os
 
@@ -100,11 +102,11 @@ class Model(nn.Module):
         if self.tp > 1:
             x = _ReduceFromTP.apply(x, self.group)
         for blk in self.blocks:
-            x = checkpoint(blk, x, self.sin, self.cos, use_reentrant=False) if self.recompute else blk(x, self.sin, self.cos)
+            x = checkpoint(blk, x, self.sin, self.cos, use_reentrant=False, preserve_rng_state=False) if self.recompute else blk(x, self.sin, self.cos)
         h = self.ln_f(x)
         if self.tp > 1:
             h = _CopyToTP.apply(h, self.group)
-        logits = self.head(h).float().view(-1, self.vshard)
+        logits = self.head(h).float().view(-1, self.vshard)  # loss in fp32
         if self.tp == 1:
             return F.cross_entropy(logits, labels.view(-1))
         # vocabulary-sharded cross entropy
@@ -119,7 +121,7 @@ class Model(nn.Module):
 
 
 class TorchTrainer:
-    def __init__(self, cfg, micro_batches=16, lr=1e-4, recompute=True):
+    def __init__(self, cfg, micro_batches=16, lr=1e-4, recompute=True, cuda_graph=True):
         self.cfg, self.micro_batches = cfg, micro_batches
         world = int(os.environ.get("WORLD_SIZE", "1"))
         rank = int(os.environ.get("RANK", "0"))
@@ -140,32 +142,87 @@ class TorchTrainer:
                 if rank in ranks:
                     self.dp_group = grp
         torch.manual_seed(1234 + rank % tp)
-        with torch.device("cuda"):
-            self.model = Model(cfg, tp, self.tp_group, rank % tp, recompute=recompute)
-        for p in self.model.parameters():
+        dev = self.device = "cuda" if torch.cuda.is_available() else "cpu"  # the CPU path only smoke-tests the logic
+        with torch.device(dev):
+            self.model = Model(cfg, tp, self.tp_group, rank % tp, recompute=recompute).to(torch.bfloat16)
+        params = sorted(self.model.parameters(), key=lambda p: p.dim() < 2)  # matrices (decayed) first, stable
+        for p in params:
             if p.dim() >= 2:
                 nn.init.normal_(p, std=0.02)
-        decay = [p for p in self.model.parameters() if p.dim() >= 2]
-        no_decay = [p for p in self.model.parameters() if p.dim() < 2]
-        self.opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.01}, {"params": no_decay, "weight_decay": 0.0}],
-                                     lr=lr, betas=(0.9, 0.95), eps=1e-5, fused=True)
+        # bf16 parameters and gradients as views of two flat buffers (one collective per step, static addresses for the
+        # captured graph); fp32 master copy for the optimizer
+        total = sum(p.numel() for p in params)
+        self.flat_w = torch.empty(total, dtype=torch.bfloat16, device=dev)
+        self.flat_g = torch.zeros(total, dtype=torch.bfloat16, device=dev)
+        off = 0
+        for p in params:
+            n = p.numel()
+            self.flat_w[off:off + n].copy_(p.data.reshape(-1))
+            p.data = self.flat_w[off:off + n].view_as(p)
+            p.grad = self.flat_g[off:off + n].view_as(p)
+            off += n
+        n_decay = sum(p.numel() for p in params if p.dim() >= 2)
+        self.master = self.flat_w.float()
+        self.master_grad = torch.zeros_like(self.master)
+        groups = []
+        for lo, hi, wd in ((0, n_decay, 0.01), (n_decay, total, 0.0)):
+            parts = []
+            for a in range(lo, hi, 1 << 30):  # pieces below 2^31 elements
+                b = min(a + (1 << 30), hi)
+                part = self.master[a:b]
+                part.grad = self.master_grad[a:b]
+                parts.append(part)
+            if parts:
+                groups.append({"params": parts, "weight_decay": wd})
+        self.opt = torch.optim.AdamW(groups, lr=lr, betas=(0.9, 0.95), eps=1e-5, fused=dev == "cuda")
         self.tokens_per_step = micro_batches * cfg.seq_len * dp
+        self.cuda_graph = bool(cuda_graph) and dev == "cuda"
+        self.graph = None
+        self.graph_note = "off"
+        self._static_tokens = torch.zeros(1, cfg.seq_len + 1, dtype=torch.long, device=dev)
+        self._static_loss = None
+        self._eager_steps = 0
+
+    def _micro_batch(self, t):
+        loss = self.model(t[:, :-1], t[:, 1:])
+        (loss / self.micro_batches).backward()  # accumulates into the flat bf16 gradient buffer
+        return loss.detach()
+
+    def _try_capture(self):
+        """Capture one micro-batch (forward + backward, collectives included) after a warm-up on a side stream."""
+        try:
+            g = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g):
+                self._static_loss = self._micro_batch(self._static_tokens)
+            self.graph, self.graph_note = g, "micro-batch replayed from a CUDA graph"
+        except Exception as e:  # capture is not always possible (an op that synchronises): stay eager and say so
+            self.graph, self.graph_note = None, f"eager ({type(e).__name__} during capture)"
+            self.cuda_graph = False
+            torch.cuda.synchronize()
+        self.flat_g.zero_()
 
     def step_device(self, tokens):
         """tokens: (micro_batches, 1, 1, seq+1) int32 on the device. Returns per-micro-batch losses (device)."""
+        if self.cuda_graph and self.graph is None and self._eager_steps >= 1:
+            self._try_capture()
         losses = []
         for i in range(self.micro_batches):
             t = tokens[i].reshape(1, -1).long()
-            with torch.autocast("cuda", dtype=torch.bfloat16):
-                loss = self.model(t[:, :-1], t[:, 1:])
-            (loss / self.micro_batches).backward()
-            losses.append(loss.detach())
+            if self.graph is not None:
+                self._static_tokens.copy_(t)
+                self.graph.replay()
+                losses.append(self._static_loss.clone())
+            else:
+                losses.append(self._micro_batch(t))
+        self._eager_steps += 1
         if self.cfg.dp > 1:
-            for p in self.model.parameters():
-                dist.all_reduce(p.grad, op=dist.ReduceOp.AVG, group=self.dp_group)
+            dist.all_reduce(self.flat_g, op=dist.ReduceOp.AVG, group=self.dp_group)  # one flat bucket
+        self.master_grad.copy_(self.flat_g)
+        self.flat_g.zero_()
         self.opt.step()
-        self.opt.zero_grad(set_to_none=False)
+        self.flat_w.copy_(self.master)
         return torch.stack(losses)
 
     def step(self, host_tokens):
-        return float(self.step_device(host_tokens.cuda(non_blocking=True)).float().mean().item())
+        return float(self.step_device(host_tokens.to(self.device, non_blocking=True)).float().mean().item())

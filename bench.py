@@ -112,10 +112,11 @@ def _shutdown(dist):
         os._exit(0)
 
 
-def run_decode(args):
+def run_decode(args, standalone: bool = True):
     """Int4 group-quantised greedy generation: weights N(0, 0.02) quantised in groups of 64 along the input dimension
     with fp16 scale and bias, bf16 activations and KV cache, tensor parallel over all GPUs. One step = one whole
-    `generate` call (prefill of the prompts + `new_tokens - 1` single-token steps)."""
+    `generate` call (prefill of the prompts + `new_tokens - 1` single-token steps). With `standalone=False` the record
+    is returned (rank 0; None elsewhere) instead of printed, and the process is not ended."""
     import numpy as np
     import torch
 
@@ -181,6 +182,7 @@ def run_decode(args):
     dev_ms, e2e_ms, prefill_ms, decode_ms = (float(t) for t in times)
     if args.impl != "torch":
         native.check_gemm_errors()
+    line = None
     if rank == 0:
         toks = B * N * K
         line = {
@@ -209,9 +211,106 @@ def run_decode(args):
             "ms_per_decode_step": decode_ms / K / (N - 1),
             "sample_tokens": [int(t) for t in np.asarray(out)[0, :8]], "setup_seconds": setup_s,
         }
+    del gen
+    _free_device_memory()
+    if not standalone:
+        return line
+    if rank == 0:
         print(json.dumps(line))
     _shutdown(dist)
     return 0
+
+
+def _free_device_memory():
+    import gc
+
+    import torch
+
+    gc.collect()
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+
+
+def _torch_train_arm(args, cfg, tp, K, W, rank, local_rank, dist_barrier, dist):
+    """The PyTorch (+cuBLAS, flash SDPA, NCCL) implementation of the same step on the same GPUs: the number to beat on
+    this machine. Returns `(adapter with step / step_device / synthetic_tokens / tokens_per_step, trainer)`."""
+    import torch
+
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+    from torch_decoder import TorchTrainer
+
+    tt = TorchTrainer(cfg, micro_batches=args.micro_batches, recompute=args.recompute,
+                      cuda_graph=not args.no_cuda_graphs)
+
+    class _Adapter:
+        tokens_per_step = tt.tokens_per_step
+        prune_recompute = False
+
+        class session:
+            h2d_bytes = 0
+            d2h_bytes = 0
+
+        def synthetic_tokens(self, seed=0):
+            g = torch.Generator().manual_seed(seed + rank // max(tp, 1))
+            return torch.randint(0, cfg.vocab_size, (args.micro_batches, 1, 1, cfg.seq_len + 1), generator=g,
+                                 dtype=torch.int32).pin_memory()
+
+        def step(self, t):
+            _Adapter.session.h2d_bytes += t.numel() * 4
+            _Adapter.session.d2h_bytes += 4
+            return tt.step(t)
+
+        def step_device(self, t):
+            return tt.step_device(t)
+
+    return _Adapter(), tt
+
+
+def _time_steps(trainer, K, W, barrier, local_rank, dist, native=None, e2e=True, pipeline_stages=0):
+    """W untimed steps, then K steps timed on the device (inputs resident, CUDA events, max over ranks) and, if `e2e`, K
+    more through the public `step` call (tokens from pinned host memory in, losses out), by wall clock between
+    barriers."""
+    import torch
+
+    host_tokens = [trainer.synthetic_tokens(seed=i) for i in range(W + K)]
+    dev_tokens = [t.cuda(non_blocking=True) for t in host_tokens]
+    losses = []
+    for i in range(W):
+        losses.append(trainer.step(host_tokens[i]))
+    losses = [l if l is not None else float("nan") for l in losses]
+    launches0 = native.LAUNCHES["count"] if native is not None else 0
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        start.record()
+        for i in range(K):
+            trainer.step_device(dev_tokens[W + i])
+        end.record()
+        barrier()
+    dev_ms = start.elapsed_time(end)
+    launches = (native.LAUNCHES["count"] - launches0) if native is not None else 0
+    if native is not None:
+        native.check_gemm_errors()
+    e2e_s, h2d, d2h = float("nan"), 0, 0
+    if e2e:
+        h2d0, d2h0 = trainer.session.h2d_bytes, trainer.session.d2h_bytes
+        barrier()
+        t1 = time.perf_counter()
+        for i in range(K):
+            losses.append(trainer.step(host_tokens[W + i]))
+        barrier()
+        e2e_s = time.perf_counter() - t1
+        h2d = (trainer.session.h2d_bytes - h2d0) // K
+        d2h = (trainer.session.d2h_bytes - d2h0) // K
+    if pipeline_stages and dist is not None:
+        box = [losses]
+        dist.broadcast_object_list(box, src=pipeline_stages - 1)  # the last slot of replica 0 computes the loss
+        losses = box[0]
+    times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    return {"dev_ms": float(times[0]), "e2e_ms": float(times[1]), "launches": int(launches), "h2d": int(h2d),
+            "d2h": int(d2h), "losses": losses, "clocks": clocks.summary()}
 
 
 def main():
@@ -226,22 +325,29 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (diagnostics only; such a run is "
                                                          "labelled and is not the headline configuration)")
     ap.add_argument("--mode", default="train", choices=["train", "decode", "pipeline"],
-                    help="train: the training step (default, headline); decode: int4 greedy generation, TP over all GPUs; "
-                         "pipeline: pipeline x data parallel training (--stages device slots per replica)")
+                    help="train: the training step (default, headline), followed by the PyTorch arm of the same step and "
+                         "the int4 decode benchmark as secondary records; decode: int4 greedy generation, TP over all "
+                         "GPUs; pipeline: pipeline x data parallel training (--stages device slots per replica)")
     ap.add_argument("--tp", type=int, default=0, help="train mode: tensor-parallel width (default min(gpus, 4))")
     ap.add_argument("--stages", type=int, default=4, help="pipeline mode: device slots (GPUs) per replica")
     ap.add_argument("--sequence-parallel", action="store_true",
                     help="train mode: shard the residual stream over the tokens inside the TP group")
-    ap.add_argument("--no-recompute", action="store_true",
-                    help="train / pipeline mode, both arms: keep the activations of every layer instead of running each "
-                         "block's forward pass a second time (a micro-batch of 2048 tokens keeps about 6 GB at TP1)")
+    ap.add_argument("--recompute", action="store_true",
+                    help="train / pipeline mode, both arms: run each block's forward pass a second time in the backward "
+                         "pass instead of keeping its activations (the reference needs this on IPUs; 180 GB of HBM do "
+                         "not: a micro-batch of 2048 tokens keeps about 6 GB at TP1, the default keeps them)")
+    ap.add_argument("--no-recompute", action="store_true", help="the default since activations fit; kept for old commands")
     ap.add_argument("--prune-recompute", action="store_true",
-                    help="train / pipeline mode: the recomputed forward pass of a block leaves out the ops that only lead "
+                    help="with --recompute: the recomputed forward pass of a block leaves out the ops that only lead "
                          "to the block's output (also XL_PRUNE_RECOMPUTE=1); the gradients are bit-identical")
     ap.add_argument("--batch", type=int, default=16, help="decode mode: sequences per batch")
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--new-tokens", type=int, default=128)
     ap.add_argument("--no-cuda-graphs", action="store_true")
+    ap.add_argument("--no-baseline", action="store_true",
+                    help="train mode, --impl ours: skip the PyTorch arm that is otherwise timed first on the same GPUs")
+    ap.add_argument("--no-decode", action="store_true",
+                    help="train mode, --impl ours: skip the int4 decode benchmark that otherwise follows as a secondary record")
     ap.add_argument("--emulate-tp", type=int, default=0,
                     help="diagnostics: run ONE rank's shard shapes of a K-way tensor-parallel layout (heads, ffn and "
                          "vocabulary divided by K, no collectives) to separate kernel time from communication")
@@ -256,7 +362,6 @@ def main():
     import torch
 
     from popxl_addons_b200.models.decoder import DecoderConfig
-    from popxl_addons_b200.models.trainer import DecoderTrainer
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -269,9 +374,8 @@ def main():
     if args.tp:
         tp, dp = args.tp, args.gpus // args.tp
     pipeline = args.mode == "pipeline"
+    stages = 0
     if pipeline:
-        if args.impl != "ours":
-            raise SystemExit("pipeline mode has no --impl torch arm")
         stages = min(args.stages, args.gpus)
         tp, dp = 1, args.gpus // stages
         if args.model == "gptj_6b":
@@ -286,140 +390,161 @@ def main():
     cfg.sequence_parallel = bool(args.sequence_parallel)
     W = max(args.warmup, 3)
     K = args.steps
-    t0 = time.perf_counter()
-    if args.impl == "torch":
-        # PyTorch + cuBLAS + flash SDPA + NCCL implementation of the same step (the number to beat on this machine)
-        sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
-        from torch_decoder import TorchTrainer
-
-        class _NoNative:
-            LAUNCHES = {"count": 0, "by_kernel": {}}
-
-            @staticmethod
-            def check_gemm_errors():
-                pass
-
-        native = _NoNative
-        tt = TorchTrainer(cfg, micro_batches=args.micro_batches, recompute=not args.no_recompute)
-
-        class _Adapter:
-            tokens_per_step = tt.tokens_per_step
-
-            class session:
-                h2d_bytes = 0
-                d2h_bytes = 0
-
-            def synthetic_tokens(self, seed=0):
-                g = torch.Generator().manual_seed(seed + rank // max(tp, 1))
-                return torch.randint(0, cfg.vocab_size, (args.micro_batches, 1, 1, cfg.seq_len + 1), generator=g,
-                                     dtype=torch.int32).pin_memory()
-
-            def step(self, t):
-                _Adapter.session.h2d_bytes += t.numel() * 4
-                _Adapter.session.d2h_bytes += 4
-                return tt.step(t)
-
-            def step_device(self, t):
-                return tt.step_device(t)
-
-        trainer = _Adapter()
-    elif pipeline:
-        from popxl_addons_b200.models.pipeline_trainer import PipelineTrainer
-        from popxl_addons_b200.ops import native
-
-        trainer = PipelineTrainer(cfg, stages=stages, micro_batches=args.micro_batches,
-                                  micro_batch_size=args.micro_batch_size, device="cuda", seed=0, lr=1e-4,
-                                  recompute=not args.no_recompute,
-                                  prune_recompute=True if args.prune_recompute else None)
-    else:
-        trainer = DecoderTrainer(cfg, micro_batches=args.micro_batches, micro_batch_size=args.micro_batch_size,
-                                 device="cuda", seed=0, lr=1e-4, recompute=not args.no_recompute,
-                                 prune_recompute=True if args.prune_recompute else None)
-        from popxl_addons_b200.ops import native
-    setup_s = time.perf_counter() - t0
-
-    dist = torch.distributed if world > 1 else None
+    headline = (not args.layers and not args.emulate_tp and args.model == "gptj_6b" and not pipeline and not args.tp
+                and args.micro_batch_size == 1 and args.micro_batches == 16)
+    dist_holder = {"dist": None}
 
     def barrier():
-        if dist is not None:
-            dist.barrier()
+        d = dist_holder["dist"]
+        if d is not None:
+            d.barrier()
         torch.cuda.synchronize()
 
-    host_tokens = [trainer.synthetic_tokens(seed=i) for i in range(W + K)]
-    dev_tokens = [t.cuda(non_blocking=True) for t in host_tokens]
-    losses = []
-    for i in range(W):
-        losses.append(trainer.step(host_tokens[i]))
-    if pipeline:
-        # only the last slot of a replica sees the loss: share it for the report
-        losses = [l if l is not None else float("nan") for l in losses]
+    def current_dist():
+        d = torch.distributed if (world > 1 and torch.distributed.is_initialized()) else None
+        dist_holder["dist"] = d
+        return d
 
-    # ---- device-timed region: K steps, inputs resident, CUDA events, max over ranks ----------------------------------
-    launches0 = native.LAUNCHES["count"]
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
-        barrier()
-        start.record()
-        last = None
-        for i in range(K):
-            last = trainer.step_device(dev_tokens[W + i])
-        end.record()
-        barrier()
-    dev_ms = start.elapsed_time(end)
-    launches = native.LAUNCHES["count"] - launches0
-    native.check_gemm_errors()
+    # ---- the PyTorch arm of the same step, timed first on the same GPUs (its memory is released afterwards) ----------
+    baseline = None
+    run_baseline = args.impl == "ours" and not args.no_baseline and not pipeline and not args.emulate_tp \
+        and not args.sequence_parallel
+    if args.impl == "torch" or run_baseline:
+        t0 = time.perf_counter()
+        adapter, tt = _torch_train_arm(args, cfg, tp, K, W, rank, local_rank, barrier, None)
+        torch_setup_s = time.perf_counter() - t0
+        dist = current_dist()
+        kb = K if args.impl == "torch" else min(K, 3)
+        res = _time_steps(adapter, kb, W, barrier, local_rank, dist, e2e=True)
+        res.update(steps=kb, setup_s=torch_setup_s, tokens=adapter.tokens_per_step, graph_note=tt.graph_note)
+        baseline = res
+        if args.impl == "ours":
+            del adapter, tt
+            _free_device_memory()
 
-    # ---- end to end through the public API: H2D of the tokens from pinned memory + D2H of the losses, every step ---------
-    h2d0, d2h0 = trainer.session.h2d_bytes, trainer.session.d2h_bytes
-    barrier()
-    t1 = time.perf_counter()
-    for i in range(K):
-        losses.append(trainer.step(host_tokens[W + i]))
-    barrier()
-    e2e_s = time.perf_counter() - t1
-    if pipeline and dist is not None:
-        box = [losses]
-        dist.broadcast_object_list(box, src=stages - 1)  # the last slot of replica 0 computes the loss
-        losses = box[0]
-    h2d = (trainer.session.h2d_bytes - h2d0) // K
-    d2h = (trainer.session.d2h_bytes - d2h0) // K
+    native = None
+    ours = None
+    setup_s = 0.0
+    trainer = None
+    if args.impl == "ours":
+        t0 = time.perf_counter()
+        from popxl_addons_b200.ops import native
 
-    times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
-    if dist is not None:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms = float(times[0]), float(times[1])
-    tokens = trainer.tokens_per_step
-    value = tokens * K / (dev_ms / 1e3)
-    e2e_value = tokens * K / (e2e_ms / 1e3)
+        native.STRICT[0] = True  # a hot op that falls back to the library implementation on this GPU is an error
+        if pipeline:
+            from popxl_addons_b200.models.pipeline_trainer import PipelineTrainer
+
+            trainer = PipelineTrainer(cfg, stages=stages, micro_batches=args.micro_batches,
+                                      micro_batch_size=args.micro_batch_size, device="cuda", seed=0, lr=1e-4,
+                                      recompute=args.recompute,
+                                      prune_recompute=True if args.prune_recompute else None)
+        else:
+            from popxl_addons_b200.models.trainer import DecoderTrainer
+
+            trainer = DecoderTrainer(cfg, micro_batches=args.micro_batches, micro_batch_size=args.micro_batch_size,
+                                     device="cuda", seed=0, lr=1e-4, recompute=args.recompute,
+                                     prune_recompute=True if args.prune_recompute else None,
+                                     cuda_graphs=not args.no_cuda_graphs)
+        setup_s = time.perf_counter() - t0
+        dist = current_dist()
+        ours = _time_steps(trainer, K, W, barrier, local_rank, dist, native=native, e2e=True,
+                           pipeline_stages=stages if pipeline else 0)
+        ours["kernels"] = dict(native.LAUNCHES["by_kernel"])
+        ours["fallbacks"] = dict(native.FALLBACKS)
+        ours["tokens"] = trainer.tokens_per_step
+        ours["prune"] = bool(getattr(trainer, "prune_recompute", False))
+        ours["peak_gb"] = round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)
+    main_res = ours if args.impl == "ours" else baseline
+    dist = current_dist()
+
+    # ---- secondary record: int4 greedy generation, tensor parallel over all GPUs (the second headline metric) ----------
+    decode = None
+    if args.impl == "ours" and headline and not args.no_decode:
+        del trainer
+        _free_device_memory()
+        dargs = argparse.Namespace(**vars(args))
+        dargs.mode, dargs.steps, dargs.warmup = "decode", min(K, 2), 3
+        before = dict(native.LAUNCHES["by_kernel"])
+        dec_lines = {}
+        for impl, dense in (("torch", True), ("ours", False)):
+            dargs.impl, dargs.torch_dense = impl, dense
+            try:
+                dec_lines[impl] = run_decode(dargs, standalone=False)
+            except Exception as e:  # the secondary record must not take the headline down with it
+                dec_lines[impl] = {"error": f"{type(e).__name__}: {e}"} if rank == 0 else None
+        if rank == 0:
+            d_ours, d_torch = dec_lines["ours"], dec_lines["torch"]
+            if d_ours and "kernels" in d_ours:
+                d_ours["kernels"] = {k: v - before.get(k, 0) for k, v in d_ours["kernels"].items()
+                                     if v - before.get(k, 0) > 0}
+            decode = d_ours
+            if d_ours and d_torch and "value" in d_ours and "value" in d_torch:
+                decode["vs_baseline"] = d_ours["value"] / d_torch["value"]
+                decode["baseline"] = {"impl": "PyTorch + cuBLAS, CUDA-graph-replayed decode step, bf16 copy of every "
+                                              "weight (4x the memory of the int4 model: the upper bound of the library path)",
+                                      "value": d_torch["value"], "ms_per_step": d_torch["ms_per_step"],
+                                      "ms_per_decode_step": d_torch["ms_per_decode_step"], "steps": d_torch["steps"]}
+            elif d_torch:
+                decode = decode or {}
+                decode["baseline"] = d_torch
+
     if rank == 0:
+        tokens = main_res["tokens"]
+        kk = main_res.get("steps", K)
+        value = tokens * kk / (main_res["dev_ms"] / 1e3)
+        e2e_value = tokens * kk / (main_res["e2e_ms"] / 1e3)
+        # model FLOPs only: 6 x parameters x tokens plus the attention products; a recomputed forward pass is not counted
         flops_per_token = 6 * cfg.param_count() + 6 * cfg.layers * cfg.seq_len * cfg.heads * cfg.head_dim
+        vs, vs_detail = None, None
+        if args.impl == "ours" and baseline is not None:
+            bval = baseline["tokens"] * baseline["steps"] / (baseline["dev_ms"] / 1e3)
+            be2e = baseline["tokens"] * baseline["steps"] / (baseline["e2e_ms"] / 1e3)
+            vs = value / bval
+            vs_detail = {"impl": "PyTorch + cuBLAS + flash SDPA + NCCL, same step on the same GPUs in this run "
+                                 "(baseline/torch_decoder.py)", "value": bval, "ratio": vs, "e2e_value": be2e,
+                         "e2e_ratio": e2e_value / be2e, "steps": baseline["steps"], "warmup": W,
+                         "ms_per_step": baseline["dev_ms"] / baseline["steps"], "cuda_graph": baseline["graph_note"],
+                         "clocks": baseline["clocks"]}
         line = {
-            "impl": args.impl, "metric": PIPELINE_METRIC if pipeline else METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
-            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "impl": args.impl, "metric": PIPELINE_METRIC if pipeline else METRIC, "value": value, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": kk, "warmup": W, "ms_per_step": main_res["dev_ms"] / kk,
+            "higher_is_better": True,
+            # tensor parallel up to 4 GPUs keeps the global batch (strong scaling); beyond that data-parallel replicas
+            # are added and the global batch grows with them (weak scaling)
+            "scaling": "strong" if dp == 1 else "weak",
+            "scaling_note": f"global batch = {args.micro_batches * args.micro_batch_size} sequences x dp ({dp}); "
+                            f"tp{tp} splits one replica's work",
+            "vs_baseline": vs, "vs_baseline_detail": vs_detail,
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)",
             "config": {"model": f"{args.model} ({cfg.layers} layers, hidden {cfg.hidden}, {cfg.heads} heads x "
                                 f"{cfg.head_dim}, ffn {cfg.ffn}, vocab {cfg.vocab_size})",
                        "global_batch": args.micro_batches * args.micro_batch_size * dp, "seq_len": cfg.seq_len,
-                       "parallelism": (f"pp{stages}xdp{dp}" if pipeline else f"tp{tp}xdp{dp}"), "micro_batches": args.micro_batches, "micro_batch_size": args.micro_batch_size,
+                       "parallelism": (f"pp{stages}xdp{dp}" if pipeline else f"tp{tp}xdp{dp}"),
+                       "micro_batches": args.micro_batches, "micro_batch_size": args.micro_batch_size,
                        "optimizer": "AdamW, fp32 master weights + fp32 moments" +
                                     (", state sharded over dp (RTS)" if dp > 1 else ""),
-                       "recompute": "none (activations kept)" if args.no_recompute else "per layer" + (
-                           ", second forward pass reduced to what the backward pass reads"
-                           if args.impl == "ours" and trainer.prune_recompute else ""), "l2": "each step streams >100 GB of weights, optimizer state and "
-                                                       "activations, far beyond the 126 MB L2; no flush needed",
+                       "recompute": ("per layer" + (", second forward pass reduced to what the backward pass reads"
+                                                    if main_res.get("prune") else "")) if args.recompute
+                       else "none (activations kept: they fit in HBM; both arms)",
+                       "l2": "each step streams >100 GB of weights, optimizer state and activations, far beyond the "
+                             "126 MB L2; no flush needed",
                        "emulate_tp": args.emulate_tp or None, "sequence_parallel": bool(args.sequence_parallel),
-                       "headline": (not args.layers and not args.emulate_tp and args.model == "gptj_6b" and not pipeline
-                                    and not args.tp
-                                    and args.micro_batch_size == 1 and args.micro_batches == 16)},
-            "clocks": clocks.summary(),
-            "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
-            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": int(h2d),
-                    "d2h_bytes_per_step": int(d2h)},
-            "gpu_launches": int(launches),
-            "kernels": native.LAUNCHES["by_kernel"],
+                       "headline": headline},
+            "clocks": main_res["clocks"],
+            "peak_memory_gb": main_res.get("peak_gb", round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)),
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "ms_per_step": main_res["e2e_ms"] / kk,
+                    "h2d_bytes_per_step": main_res["h2d"], "d2h_bytes_per_step": main_res["d2h"]},
+            "gpu_launches": main_res["launches"],
+            "kernels": main_res.get("kernels", {}),
+            "fallbacks": main_res.get("fallbacks", {}),
             "model_tflops_per_gpu": flops_per_token * value / args.gpus / 1e12,
-            "loss_first_last": [losses[0], losses[-1]], "setup_seconds": setup_s, "mode": args.mode,
+            "flops_note": "model FLOPs (6 x parameters + attention) per token; recomputed passes are not counted",
+            "loss_first_last": [main_res["losses"][0], main_res["losses"][-1]],
+            "setup_seconds": setup_s if args.impl == "ours" else baseline["setup_s"], "mode": args.mode,
+            "secondary": decode,
         }
+        if args.impl == "torch":
+            line["config"]["cuda_graph"] = baseline["graph_note"]
         print(json.dumps(line))
     _shutdown(dist)
     return 0

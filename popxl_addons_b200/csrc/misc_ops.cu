@@ -218,8 +218,8 @@ XL_API int xl_scatter_add_rows(const void* grad_out, int dtype, const int* idx, 
 
 // ------------------------------------------------------------------------------------------------------------------
 // Row statistics for ops whose rows are sharded over ranks: per row (sum, sum of squares) for the hidden-sharded
-// LayerNorm, (max) and (sum of exp(x - gmax), x[label]) for the vocabulary-sharded cross-entropy. The tiny per-row
-// results are all-reduced by the caller between the kernels. One CTA per row.
+// LayerNorm's forward pass (its backward pass and the vocabulary-sharded cross-entropy are in sharded_ops.cu). The tiny
+// per-row results are all-reduced by the caller between the kernels. One CTA per row.
 // ------------------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ float block_sum_256(float v, float* red) {
   v = xl_warp_sum(v);
@@ -284,67 +284,6 @@ XL_API int xl_ln_apply_stats(const void* x, int dtype, const float* stats, const
   XL_DISPATCH_DTYPE(dtype, T, {
     ln_apply_stats_kernel<T><<<rows, 256, 0, s>>>((const T*)x, stats, (const T*)w, (const T*)b, (T*)y, mean_out, rstd_out,
                                                  rows, cols, hidden, eps);
-  });
-  return (int)cudaGetLastError();
-}
-
-// vocabulary-sharded cross-entropy, step 1: local row maximum
-template <typename T>
-__global__ void __launch_bounds__(256) row_max_kernel(const T* __restrict__ x, float* __restrict__ out, int cols) {
-  __shared__ float red[8];
-  const int r = blockIdx.x;
-  float m = -INFINITY;
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) m = fmaxf(m, xl_to_float(x[(long long)r * cols + c]));
-  m = block_max_256(m, red);
-  if (threadIdx.x == 0) out[r] = m;
-}
-// step 2: out (2, rows) = [sum of exp(x - gmax) | x[label] - gmax if the label is in this shard else 0]
-template <typename T>
-__global__ void __launch_bounds__(256)
-    ce_shard_sumexp_kernel(const T* __restrict__ x, const float* __restrict__ gmax, const int* __restrict__ labels,
-                           float* __restrict__ out, int rows, int cols) {
-  __shared__ float red[8];
-  const int r = blockIdx.x;
-  const float g = gmax[r];
-  float s = 0.f;
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) s += __expf(xl_to_float(x[(long long)r * cols + c]) - g);
-  s = block_sum_256(s, red);
-  if (threadIdx.x == 0) {
-    out[r] = s;
-    const int l = labels[r];
-    out[rows + r] = (l >= 0 && l < cols) ? xl_to_float(x[(long long)r * cols + l]) - g : 0.f;
-  }
-}
-// step 3: dlogits = (exp(x - gmax) / gsum - onehot(label in shard)) * scale[r]
-template <typename T>
-__global__ void __launch_bounds__(256)
-    ce_shard_grad_kernel(const T* __restrict__ x, const float* __restrict__ gmax, const float* __restrict__ gsum,
-                         const int* __restrict__ labels, const float* __restrict__ row_scale, T* __restrict__ dx, int cols) {
-  const int r = blockIdx.x;
-  const float g = gmax[r], inv = 1.f / gsum[r], sc = row_scale[r];
-  const int l = labels[r];
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
-    float p = __expf(xl_to_float(x[(long long)r * cols + c]) - g) * inv;
-    if (c == l) p -= 1.f;
-    dx[(long long)r * cols + c] = xl_from_float<T>(p * sc);
-  }
-}
-
-XL_API int xl_row_max(const void* x, int dtype, float* out, int rows, int cols, cudaStream_t s) {
-  XL_DISPATCH_DTYPE(dtype, T, { row_max_kernel<T><<<rows, 256, 0, s>>>((const T*)x, out, cols); });
-  return (int)cudaGetLastError();
-}
-XL_API int xl_ce_shard_sumexp(const void* x, int dtype, const float* gmax, const int* labels, float* out, int rows, int cols,
-                              cudaStream_t s) {
-  XL_DISPATCH_DTYPE(dtype, T, {
-    ce_shard_sumexp_kernel<T><<<rows, 256, 0, s>>>((const T*)x, gmax, labels, out, rows, cols);
-  });
-  return (int)cudaGetLastError();
-}
-XL_API int xl_ce_shard_grad(const void* x, int dtype, const float* gmax, const float* gsum, const int* labels,
-                            const float* row_scale, void* dx, int rows, int cols, cudaStream_t s) {
-  XL_DISPATCH_DTYPE(dtype, T, {
-    ce_shard_grad_kernel<T><<<rows, 256, 0, s>>>((const T*)x, gmax, gsum, labels, row_scale, (T*)dx, cols);
   });
   return (int)cudaGetLastError();
 }

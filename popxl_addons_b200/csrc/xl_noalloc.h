@@ -23,6 +23,11 @@
 //   * All calls on one device share the array. Two calls whose kernels can overlap on the GPU (different streams
 //     without an ordering between them) race on it; calls ordered on one stream are safe, and a call never reads what
 //     an earlier call left behind.
+//   * The array that is used belongs to the device that is current when the call is made, so that device must be the
+//     one stream s was created on (cudaSetDevice first in a multi-GPU process); the entry point does not check this,
+//     and a stream of another device makes the launch fail or use the wrong device's array.
+//   * The looked-up address is cached per device in plain host memory without a lock. Two host threads that make the
+//     first call on a device at the same time both look it up and both store the same value, which is harmless.
 //   * The entry point itself never calls cudaMalloc, cudaFree or any allocating library routine.
 #pragma once
 #include <cuda_runtime.h>

@@ -67,6 +67,42 @@ def _vjp_ce(ctx, op, gs):
     return [emit("ce_sharded_grad", [nls, idx, gs[0]])[0], None]
 
 
+def _special_ce_with_grad(ex, op, env):
+    """`(loss per row, dlogits)` from `(logits, labels, per-row loss gradient)` in one op: the softmax is never kept."""
+    group = op.attrs["group"]
+    logits, idx, dl = env[op.inputs[0]], env[op.inputs[1]], env[op.inputs[2]]
+    native = ex.native_collective("ce_sharded_with_grad")
+    if native is not None:
+        res = native(ex, op, logits, idx, dl)
+        if res is not NotImplemented:
+            dt = logits[0].dtype
+            env[op.outputs[0]] = [r.to(dt) for r in res[0]]
+            env[op.outputs[1]] = res[1]
+            return
+    local_max = [l.float().amax(dim=-1) for l in logits]
+    gmax = ex.comm.all_reduce(local_max, group, "max")
+    shifted = [l.float() - m.unsqueeze(-1) for l, m in zip(logits, gmax)]
+    gsum = ex.comm.all_reduce([torch.exp(s).sum(dim=-1) for s in shifted], group, "add")
+    picked, hot = [], []
+    for s, i in zip(shifted, idx):
+        il = i.long()
+        ok = (il >= 0) & (il < s.shape[-1])
+        picked.append(s.gather(1, il.clamp(0, s.shape[-1] - 1).unsqueeze(1)).squeeze(1) * ok.float())
+        hot.append((il.clamp(0, s.shape[-1] - 1), ok))
+    gpicked = ex.comm.all_reduce(picked, group, "add")
+    dt = logits[0].dtype
+    env[op.outputs[0]] = [(torch.log(z) - p).to(dt) for z, p in zip(gsum, gpicked)]
+    grads = []
+    for s, z, d, (il, ok) in zip(shifted, gsum, dl, hot):
+        g = torch.exp(s) / z.unsqueeze(-1)
+        g.scatter_add_(1, il.unsqueeze(1), -ok.float().unsqueeze(1))
+        grads.append((g * d.float().unsqueeze(-1)).to(dt))
+    env[op.outputs[1]] = grads
+
+
+OpDef("ce_sharded_with_grad", special=_special_ce_with_grad, collective=True,
+      infer=lambda op: [((op.inputs[0].shape[0],), op.inputs[0].dtype, ()),
+                        (op.inputs[0].shape, op.inputs[0].dtype, ())])
 OpDef("ce_sharded", special=_special_ce_fwd, vjp=_vjp_ce, collective=True,
       infer=lambda op: [((op.inputs[0].shape[0],), op.inputs[0].dtype, ()),
                         (op.inputs[0].shape, op.inputs[0].dtype, ())])
@@ -109,8 +145,6 @@ def cross_entropy_sharded_with_grad(logits: xl.Tensor, indices: xl.Tensor, loss_
     """Vocabulary-sharded counterpart of `cross_entropy_with_grad`: returns `(loss, d(loss*loss_scaling)/dlogits)`
     where the gradient is this replica's slice. No separate backward graph is needed for the loss."""
     group = replica_grouping if replica_grouping is not None else xl.gcg().ir.replica_grouping()
-    rows, _nls = emit("ce_sharded", [logits, indices], {"group": group, "root_only": False},
-                      ["cross_entropy_sharded_out", "cross_entropy_sharded_soft_max_out"])
     n = logits.shape[0]
     scale = loss_scaling if isinstance(loss_scaling, xl.Tensor) else xl.constant(float(loss_scaling), xl.float32)
     if ignore_index is not None:
@@ -128,8 +162,9 @@ def cross_entropy_sharded_with_grad(logits: xl.Tensor, indices: xl.Tensor, loss_
     dl = ops.expand(ops.reshape(per_row, (1,)), (n,)) if per_row.shape == () else per_row
     if mask is not None:
         dl = dl * mask
-    dl = ops.cast(dl, logits.dtype)
-    (dlogits,) = emit("ce_sharded_grad", [_nls, indices, dl])
+    dl = ops.cast(dl, xl.float32)
+    rows, dlogits = emit("ce_sharded_with_grad", [logits, indices, dl], {"group": group},
+                         ["cross_entropy_sharded_out", "cross_entropy_sharded_grad"])
     return _reduce_loss(rows, indices, ignore_index, reduction), dlogits
 
 

@@ -41,6 +41,12 @@ def _special_fwd(ex, op, env):
 def _special_bwd(ex, op, env):
     group = op.attrs["group"]
     xs, ws, means, rstds, gs = (env[t] for t in op.inputs)
+    native = ex.native_collective("layer_norm_distributed_bwd")
+    if native is not None:
+        res = native(ex, op, xs, ws, means, rstds, gs)
+        if res is not NotImplemented:
+            env[op.outputs[0]], env[op.outputs[1]], env[op.outputs[2]] = res
+            return
     hidden = xs[0].shape[-1] * group.group_size
     xhats, gws, stats = [], [], []
     for x, w, m, r, g in zip(xs, ws, means, rstds, gs):

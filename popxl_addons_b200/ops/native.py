@@ -12,7 +12,7 @@ from typing import Dict, Optional, Tuple
 import torch
 
 from ..xl import dtypes as _dt
-from ..xl.opdef import OPS, native
+from ..xl.opdef import FALLBACKS, OPS, STRICT, NativeFallback, native, note_fallback  # noqa: F401  (re-exported)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libxlb200.so")
@@ -102,9 +102,17 @@ _gather_rows = _sig("xl_gather_rows", _c_p, _c_int, _c_p, _c_p, _c_ll, _c_int, _
 _scatter_rows = _sig("xl_scatter_add_rows", _c_p, _c_int, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p)
 _row_sum_sumsq = _sig("xl_row_sum_sumsq", _c_p, _c_int, _c_p, _c_int, _c_int, _c_p)
 _ln_apply_stats = _sig("xl_ln_apply_stats", _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_f, _c_f, _c_p)
-_row_max = _sig("xl_row_max", _c_p, _c_int, _c_p, _c_int, _c_int, _c_p)
-_ce_shard_sumexp = _sig("xl_ce_shard_sumexp", _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p)
-_ce_shard_grad = _sig("xl_ce_shard_grad", _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p)
+_ce_stats = _sig("xl_ce_shard_stats", _c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_int, _c_p)
+_ce_rescale = _sig("xl_ce_shard_rescale", _c_p, _c_p, _c_p, _c_int, _c_p)
+_ce_combine = _sig("xl_ce_shard_combine", _c_p, _c_p, _c_int, _c_int, _c_p)
+_ce_grad_loss = _sig("xl_ce_shard_grad_loss", _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int,
+                     _c_int, _c_p)
+_ce_nls = _sig("xl_ce_shard_nls", _c_p, _c_int, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p)
+_ce_nls_grad = _sig("xl_ce_nls_grad", _c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_int, _c_int, _c_p)
+_ln_shard_bwd_stats = _sig("xl_ln_shard_bwd_stats", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p)
+_ln_shard_bwd_parts = _sig("xl_ln_shard_bwd_parts", _c_int)
+_ln_shard_bwd_apply = _sig("xl_ln_shard_bwd_apply", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int,
+                           _c_int, _c_f, _c_int, _c_p)
 _set_spin = _sig("xl_set_comm_spin_limit", ctypes.c_uint)
 _symm_barrier = _sig("xl_symm_barrier", _c_p, _c_int, _c_int, _c_int, _c_p, _c_p)
 _symm_all_reduce = _sig("xl_symm_all_reduce", _c_p, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p,
@@ -1174,29 +1182,135 @@ def ln_apply_stats(x, stats, w, b, hidden, eps):
     return y, mean, rstd
 
 
-def ce_shard_row_max(x):
-    out = torch.empty(x.shape[0], dtype=torch.float32, device=x.device)
-    _check(_row_max(x.data_ptr(), _CODE[x.dtype], out.data_ptr(), x.shape[0], x.shape[1], _stream()), "row_max")
-    _count("row_max")
+def _labels_i32(labels):
+    lab = labels.reshape(-1)
+    return lab if lab.dtype == torch.int32 and lab.is_contiguous() else lab.to(torch.int32).contiguous()
+
+
+def ce_shard_stats(x, labels, label_offset: int = 0, out=None):
+    """`(3, rows)` fp32 of one vocabulary shard: row maximum, sum of exp(x - that maximum), and `x[label - offset]` where
+    that column belongs to the shard (else 0). One pass over the shard."""
+    rows, cols = x.shape
+    stats = out if out is not None else torch.empty((3, rows), dtype=torch.float32, device=x.device)
+    _check(_ce_stats(x.data_ptr(), _CODE[x.dtype], _labels_i32(labels).data_ptr(), int(label_offset), stats.data_ptr(),
+                     rows, cols, _stream()), "ce_shard_stats")
+    _count("ce_shard_stats")
+    return stats
+
+
+def ce_shard_rescale(stats, gmax):
+    """`(2, rows)`: the shard's sum rescaled to the group maximum, and its picked logit: what is summed over the group."""
+    rows = stats.shape[1]
+    out = torch.empty((2, rows), dtype=torch.float32, device=stats.device)
+    _check(_ce_rescale(stats.data_ptr(), gmax.data_ptr(), out.data_ptr(), rows, _stream()), "ce_shard_rescale")
+    _count("ce_shard_rescale")
     return out
 
 
-def ce_shard_sumexp(x, gmax, labels):
-    """`(2, rows)` fp32: sum of exp(x - gmax) over this vocabulary shard, and x[label] - gmax where the (shard-local)
-    label falls into the shard, else 0."""
-    out = torch.empty((2, x.shape[0]), dtype=torch.float32, device=x.device)
-    _check(_ce_shard_sumexp(x.data_ptr(), _CODE[x.dtype], gmax.data_ptr(), labels.data_ptr(), out.data_ptr(), x.shape[0],
-                            x.shape[1], _stream()), "ce_shard_sumexp")
-    _count("ce_shard_sumexp")
+def ce_shard_combine(stats_all):
+    """`(n_shards, 3, rows)` statistics of shards held by one device -> `(3, rows)` = group max, sum, picked logit."""
+    n, _, rows = stats_all.shape
+    out = torch.empty((3, rows), dtype=torch.float32, device=stats_all.device)
+    _check(_ce_combine(stats_all.data_ptr(), out.data_ptr(), n, rows, _stream()), "ce_shard_combine")
+    _count("ce_shard_combine")
     return out
 
 
-def ce_shard_grad(x, gmax, gsum, labels, row_scale):
+def ce_shard_grad_loss(x, gmax, gsum, gpicked, labels, label_offset, row_scale, want_loss=True):
+    """`dlogits = (softmax - onehot) * row_scale[row]` for this shard and, with `want_loss`, the fp32 loss per row."""
+    rows, cols = x.shape
     dx = torch.empty_like(x)
-    _check(_ce_shard_grad(x.data_ptr(), _CODE[x.dtype], gmax.data_ptr(), gsum.data_ptr(), labels.data_ptr(),
-                          row_scale.data_ptr(), dx.data_ptr(), x.shape[0], x.shape[1], _stream()), "ce_shard_grad")
-    _count("ce_shard_grad")
+    loss = torch.empty(rows, dtype=torch.float32, device=x.device) if want_loss else None
+    _check(_ce_grad_loss(x.data_ptr(), _CODE[x.dtype], gmax.data_ptr(), gsum.data_ptr(), gpicked.data_ptr(),
+                         _labels_i32(labels).data_ptr(), int(label_offset), row_scale.data_ptr(), dx.data_ptr(),
+                         loss.data_ptr() if want_loss else None, rows, cols, _stream()), "ce_shard_grad_loss")
+    _count("ce_shard_grad_loss")
+    return dx, loss
+
+
+def ce_shard_nls(x, gmax, gsum, gpicked, want_loss=True):
+    """Negative log-softmax of this shard (dtype of x) and, with `want_loss`, the loss per row (dtype of x)."""
+    rows, cols = x.shape
+    nls = torch.empty_like(x)
+    loss = torch.empty(rows, dtype=x.dtype, device=x.device) if want_loss else None
+    _check(_ce_nls(x.data_ptr(), _CODE[x.dtype], gmax.data_ptr(), gsum.data_ptr(), gpicked.data_ptr(), nls.data_ptr(),
+                   loss.data_ptr() if want_loss else None, rows, cols, _stream()), "ce_shard_nls")
+    _count("ce_shard_nls")
+    return nls, loss
+
+
+def ce_nls_grad(nls, labels, label_offset, dloss):
+    rows, cols = nls.shape
+    dx = torch.empty_like(nls)
+    _check(_ce_nls_grad(nls.data_ptr(), _CODE[nls.dtype], _labels_i32(labels).data_ptr(), int(label_offset),
+                        dloss.data_ptr(), dx.data_ptr(), rows, cols, _stream()), "ce_nls_grad")
+    _count("ce_nls_grad")
     return dx
+
+
+def ce_sharded_grad_cuda(nls, idx, dloss):
+    if not _ok(nls, dloss) or nls.dim() != 2 or dloss.dtype != nls.dtype or not idx.is_cuda:
+        return NotImplemented
+    return ce_nls_grad(nls, idx, 0, dloss)
+
+
+def ce_sharded_wr_cuda(*tensors, n):
+    """All shards are tensors of this device: statistics per shard (labels offset by the columns before it), one combine
+    kernel, then the negative log-softmax of every shard; the loss comes with the first shard's pass."""
+    logits, indices = tensors[:n], tensors[n:]
+    if not _ok(*logits) or any(l.dim() != 2 or l.dtype != logits[0].dtype for l in logits):
+        return NotImplemented
+    rows = logits[0].shape[0]
+    stats_all = torch.empty((n, 3, rows), dtype=torch.float32, device=logits[0].device)
+    off = 0
+    for i, (l, idx) in enumerate(zip(logits, indices)):
+        ce_shard_stats(l, idx, off, out=stats_all[i])
+        off += l.shape[1]
+    g = ce_shard_combine(stats_all)
+    outs, loss = [], None
+    for i, l in enumerate(logits):
+        nls, lo = ce_shard_nls(l, g[0], g[1], g[2], want_loss=(i == 0))
+        outs.append(nls)
+        loss = lo if i == 0 else loss
+    return (loss, *outs)
+
+
+def ce_sharded_wr_grad_cuda(*tensors, n):
+    nls, indices, dloss = tensors[:n], tensors[n:2 * n], tensors[2 * n]
+    if not _ok(*nls, dloss) or any(x.dtype != dloss.dtype for x in nls):
+        return NotImplemented
+    outs, off = [], 0
+    for x, idx in zip(nls, indices):
+        outs.append(ce_nls_grad(x, idx, off, dloss))
+        off += x.shape[1]
+    return tuple(outs)
+
+
+def ln_shard_bwd_stats(x, w, mean, rstd, g):
+    """`(2, rows)` fp32: sums over this rank's columns of `g*w` and `g*w*xhat` (hidden-sharded LayerNorm backward)."""
+    rows, cols = x.shape
+    stats = torch.empty((2, rows), dtype=torch.float32, device=x.device)
+    _check(_ln_shard_bwd_stats(x.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(), g.data_ptr(),
+                               stats.data_ptr(), rows, cols, _CODE[x.dtype], _stream()), "ln_shard_bwd_stats")
+    _count("ln_shard_bwd_stats")
+    return stats
+
+
+def ln_shard_bwd_apply(x, w, mean, rstd, g, gstats, hidden):
+    """`(dx, dw, db)` of a hidden-sharded LayerNorm given the group sums `gstats (2, rows)`; NotImplemented if the shard
+    is wider than the kernel's register tiling."""
+    rows, cols = x.shape
+    dx, dw, db = torch.empty_like(x), torch.empty_like(w), torch.empty_like(w)
+    parts = _ln_shard_bwd_parts(rows)
+    ws = workspace(parts * 2 * cols * 4, x.device, "ln_shard_bwd")
+    rc = _ln_shard_bwd_apply(x.data_ptr(), w.data_ptr(), mean.data_ptr(), rstd.data_ptr(), g.data_ptr(),
+                             gstats.data_ptr(), dx.data_ptr(), dw.data_ptr(), db.data_ptr(), ws.data_ptr(), rows, cols,
+                             float(hidden), _CODE[x.dtype], _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "ln_shard_bwd_apply")
+    _count("ln_shard_bwd_apply")
+    return dx, dw, db
 
 
 # ---- registration of ops defined outside xl.ops ------------------------------------------------------------------------
@@ -1208,6 +1322,11 @@ def _register_late():
     from . import fp8_mse_scale as _m, static_sparse_ops as _s  # noqa: F401
 
     OPS["fp8_mse_scale"].native["cuda"] = fp8_mse_scale_cuda
+    from . import cross_entropy_sharded_loss as _ce  # noqa: F401
+
+    OPS["ce_sharded_grad"].native["cuda"] = ce_sharded_grad_cuda
+    OPS["ce_sharded_wr"].native["cuda"] = ce_sharded_wr_cuda
+    OPS["ce_sharded_wr_grad"].native["cuda"] = ce_sharded_wr_grad_cuda
     OPS["dense_csr_matmul"].native["cuda"] = dense_csr_matmul_cuda
 
     from ..layers import linear_gq as _lgq  # noqa: F401

@@ -358,14 +358,74 @@ def layer_norm_distributed_fwd(ex, op, x_vals, w_vals, b_vals):
     """Hidden-sharded LayerNorm: local (sum, sum of squares) per row in one kernel, one small all-reduce over the group,
     normalisation with the group statistics in a second kernel."""
     nat = _lib()
-    x, w, b = x_vals[0], w_vals[0], b_vals[0]
     group = op.attrs["group"]
-    if x.dim() != 2 or not nat._ok(x, w, b) or w.dtype != x.dtype or b.dtype != x.dtype:
+    for x, w, b in zip(x_vals, w_vals, b_vals):
+        if x.dim() != 2 or not nat._ok(x, w, b) or w.dtype != x.dtype or b.dtype != x.dtype:
+            return NotImplemented
+    stats = [nat.row_sum_sumsq(x) for x in x_vals]
+    stats = ex.comm.all_reduce(stats, group, "add", inplace=True)
+    hidden = x_vals[0].shape[1] * group.group_size
+    res = [nat.ln_apply_stats(x, st, w, b, hidden, op.attrs["eps"]) for x, st, w, b in zip(x_vals, stats, w_vals, b_vals)]
+    return [r[0] for r in res], [r[1] for r in res], [r[2] for r in res]
+
+
+def layer_norm_distributed_bwd(ex, op, x_vals, w_vals, mean_vals, rstd_vals, g_vals):
+    """Backward of the hidden-sharded LayerNorm: per row the sums of `g*w` and `g*w*xhat` over the local columns in one
+    kernel, one small all-reduce over the group, then `dx` and the (local) `dw`, `db` in a second kernel.
+    Parity: popxl_addons/ops/layer_norm_distributed/layer_norm_distributedx.cpp:140-152."""
+    nat = _lib()
+    group = op.attrs["group"]
+    for x, w, m, r, g in zip(x_vals, w_vals, mean_vals, rstd_vals, g_vals):
+        if x.dim() != 2 or not nat._ok(x, w, g) or w.dtype != x.dtype or g.dtype != x.dtype \
+                or m.dtype != torch.float32 or r.dtype != torch.float32 or x.shape[1] > 8192:
+            return NotImplemented
+    stats = [nat.ln_shard_bwd_stats(x, w, m, r, g) for x, w, m, r, g in zip(x_vals, w_vals, mean_vals, rstd_vals, g_vals)]
+    stats = ex.comm.all_reduce(stats, group, "add", inplace=True)
+    hidden = x_vals[0].shape[1] * group.group_size
+    res = [nat.ln_shard_bwd_apply(x, w, m, r, g, st, hidden)
+           for x, w, m, r, g, st in zip(x_vals, w_vals, mean_vals, rstd_vals, g_vals, stats)]
+    if any(r is NotImplemented for r in res):
         return NotImplemented
-    stats = nat.row_sum_sumsq(x)
-    (stats,) = ex.comm.all_reduce([stats], group, "add", inplace=True)
-    y, mean, rstd = nat.ln_apply_stats(x, stats, w, b, x.shape[1] * group.group_size, op.attrs["eps"])
-    return [y], [mean], [rstd]
+    return [r[0] for r in res], [r[1] for r in res], [r[2] for r in res]
+
+
+def _ce_group_stats(ex, group, logits, idx):
+    """Per local replica: `(gmax, gsum, gpicked)` of the vocabulary-sharded rows. Two passes' worth of exchange: the
+    row maxima (max over the group), then the rescaled sums and the picked logits (sum over the group)."""
+    nat = _lib()
+    stats = [nat.ce_shard_stats(l, i) for l, i in zip(logits, idx)]
+    gmax = ex.comm.all_reduce([st[0].contiguous() for st in stats], group, "max")
+    resc = [nat.ce_shard_rescale(st, gm) for st, gm in zip(stats, gmax)]
+    resc = ex.comm.all_reduce(resc, group, "add", inplace=True)
+    return [(gm, rs[0], rs[1]) for gm, rs in zip(gmax, resc)]
+
+
+def _ce_operands_ok(logits, idx):
+    nat = _lib()
+    return all(l.dim() == 2 and nat._ok(l) and i.is_cuda and i.numel() == l.shape[0] for l, i in zip(logits, idx))
+
+
+def ce_sharded_fwd(ex, op, logits, idx):
+    """Vocabulary-sharded cross-entropy, forward: `(loss per row, negative log-softmax of the shard)`.
+    Parity: popxl_addons/ops/cross_entropy_sharded_loss/crossentropyshardedx.cpp:88-214."""
+    nat = _lib()
+    if not _ce_operands_ok(logits, idx):
+        return NotImplemented
+    g = _ce_group_stats(ex, op.attrs["group"], logits, idx)
+    res = [nat.ce_shard_nls(l, gm, gs, gp) for l, (gm, gs, gp) in zip(logits, g)]
+    return [r[1] for r in res], [r[0] for r in res]
+
+
+def ce_sharded_with_grad(ex, op, logits, idx, row_scale):
+    """Loss per row and `d(loss * row_scale)/dlogits` of this shard without keeping the softmax: statistics pass, two
+    small all-reduces, gradient pass."""
+    nat = _lib()
+    if not _ce_operands_ok(logits, idx):
+        return NotImplemented
+    row_scale = [rs.float().contiguous() for rs in row_scale]  # may arrive as a broadcast view of one scalar
+    g = _ce_group_stats(ex, op.attrs["group"], logits, idx)
+    res = [nat.ce_shard_grad_loss(l, gm, gs, gp, i, 0, rs) for l, i, rs, (gm, gs, gp) in zip(logits, idx, row_scale, g)]
+    return [r[1] for r in res], [r[0] for r in res]
 
 
 def ar_add_layer_norm(ex, op, x_vals, delta_vals, *rest):
@@ -397,8 +457,13 @@ def ar_add_layer_norm(ex, op, x_vals, delta_vals, *rest):
     return [h]
 
 
+# entries that only need `ex.comm` (no symmetric arena): also used when all replicas of a group live in this process
+LOCAL_OK = {"layer_norm_distributed_fwd", "layer_norm_distributed_bwd", "ce_sharded_fwd", "ce_sharded_with_grad"}
+
 _TABLE = {"matmul_all_reduce": matmul_all_reduce, "ar_add_layer_norm": ar_add_layer_norm,
           "layer_norm_distributed_fwd": layer_norm_distributed_fwd,
+          "layer_norm_distributed_bwd": layer_norm_distributed_bwd,
+          "ce_sharded_fwd": ce_sharded_fwd, "ce_sharded_with_grad": ce_sharded_with_grad,
           "matmuls_reduce_scatter": matmuls_reduce_scatter, "all_gather_matmul": all_gather_matmul, "matmul2_all_reduce": matmul2_all_reduce, "rts_adam": rts_adam}
 
 

@@ -11,6 +11,15 @@ from .. import xl
 from ..xl.opdef import OPS, OpDef
 
 
+def _reference_matmul(mm, a, w, native_fn):
+    """The torch implementation of a product whose device kernel refused the operands (counted as a fallback)."""
+    if native_fn is not None:
+        from ..xl.opdef import note_fallback
+
+        note_fallback("matmul", f"{tuple(a.shape)} x {tuple(w.shape)} {a.dtype}")
+    return mm.impl(a, w)
+
+
 def _special_matmul_all_reduce(ex, op, env):
     a, w = env[op.inputs[0]], env[op.inputs[1]]
     native = ex.native_collective("matmul_all_reduce")
@@ -25,7 +34,7 @@ def _special_matmul_all_reduce(ex, op, env):
     for r in range(ex.num_local):
         y = fn(a[r], w[r]) if fn is not None else NotImplemented
         if y is NotImplemented:
-            y = mm.impl(a[r], w[r])
+            y = _reference_matmul(mm, a[r], w[r], fn)
         outs.append(y)
     env[op.outputs[0]] = ex.comm.all_reduce(outs, op.attrs["group"], "add", inplace=True)
 
@@ -60,7 +69,7 @@ def _special_matmul2_all_reduce(ex, op, env):
 
     def product(a, w):
         y = fn(a, w) if fn is not None else NotImplemented
-        return mm.impl(a, w) if y is NotImplemented else y
+        return _reference_matmul(mm, a, w, fn) if y is NotImplemented else y
 
     outs = []
     for r in range(ex.num_local):
@@ -164,7 +173,7 @@ def _special_matmuls_reduce_scatter(ex, op, env):
 
     def product(a, w):
         y = fn(a, w) if fn is not None else NotImplemented
-        return mm.impl(a, w) if y is NotImplemented else y
+        return _reference_matmul(mm, a, w, fn) if y is NotImplemented else y
 
     outs = []
     for r in range(ex.num_local):
@@ -415,6 +424,29 @@ def fuse_gemm_collectives(ir: xl.Ir) -> int:
 
 # ---- overlap: ops that do not need an all-reduce's result move in front of the ops that do ---------------------------------
 
+def _callee_only_updates_operands(callee, _seen=None) -> bool:
+    """True if every op of `callee` (and of the graphs it calls) is pure or a plain in-place update of a tensor: such a
+    call touches nothing but its own operands. Host streams, remote buffers, collectives and anything else with an
+    executor of its own make the call a barrier."""
+    seen = _seen if _seen is not None else set()
+    if callee in seen:
+        return False
+    seen.add(callee)
+    from ..transforms.recomputation import _is_pure
+
+    for o in callee.ops:
+        if _is_pure(o, set()):
+            continue
+        if o.opdef.name == "call":
+            if not _callee_only_updates_operands(o.attrs["graph"], seen):
+                return False
+            continue
+        if o.opdef.inplace and o.opdef.special is None:
+            continue
+        return False
+    return True
+
+
 def _written_operands(op):
     """Tensors of the op's graph that the op writes: [] for a pure op, None for an op nothing may move across."""
     from ..transforms.recomputation import _is_pure
@@ -424,8 +456,10 @@ def _written_operands(op):
     name = op.opdef.name
     if name == "call":
         callee = op.attrs["graph"]
+        if not _callee_only_updates_operands(callee):
+            return None  # host / remote transfers or collectives inside: their order is part of the program
         return [op.inputs[i] for i, t in enumerate(callee._inputs) if callee.is_by_ref(t)]
-    if op.opdef.inplace:
+    if op.opdef.inplace and op.opdef.special is None:
         return [op.inputs[0]]  # the in-place ops of this package update their first operand
     return None
 

@@ -111,8 +111,11 @@ class TaskSession(xl.Session):
     def wandb_histogram(self, name: str, step: int, data: np.ndarray):
         if wandb is None or wandb.run is None:
             return
+        data = np.asarray(data, dtype=np.float32).reshape(-1)
         finite = data[np.isfinite(data)]
-        wandb.log({name: wandb.Histogram(finite), f"{name}_nonfinite": int(data.size - finite.size)}, step=step)
+        # key names as in popxl_addons/task_session.py:115-121, so dashboards built for one read the other
+        wandb.log({f"{name}:histogram": wandb.Histogram(finite), f"{name}:not_finite": int(data.size - finite.size)},
+                  step=step)
 
     def wandb_variable_histograms(self, step: int = 0):
         for name, data in self.get_named_tensors_data().to_dict().items():
@@ -121,33 +124,44 @@ class TaskSession(xl.Session):
     # -- checkpoints ------------------------------------------------------------------------------------------
     def save_checkpoint(self, checkpoint_dir: str):
         """Write a checkpoint. `wandb://<name>` uploads it as a W&B artifact instead of keeping a directory.
-        At most `max_checkpoints` directories written by this session are kept (oldest removed first)."""
+        At most `max_checkpoints` directories written by this session are kept (oldest removed first).
+        Collective when the session spans several processes: every rank must call it."""
         with timer("Fetching state for checkpoint", log_to_wandb=False):
             data = self.get_named_tensors_data().to_dict()  # collective: all ranks
-        if not self._is_writer():
-            return
+        writer = self._is_writer()
         with timer("Saving checkpoint", log_to_wandb=False):
             if checkpoint_dir.startswith(_WANDB_PREFIX):
+                if not writer:
+                    return
                 if wandb is None:
                     raise RuntimeError("wandb is not installed")
                 name = checkpoint_dir[len(_WANDB_PREFIX):]
                 with tempfile.TemporaryDirectory() as tmp:
-                    self._write_checkpoint(tmp, data)
-                    artifact = wandb.Artifact(name=name, type="model")
+                    self._write_model_files(tmp, data)
+                    self._write_completion_marker(tmp)
+                    # the artifact type popxl_addons/task_session.py:152,197 saves and looks up
+                    artifact = wandb.Artifact(name=name, type="checkpoints")
                     artifact.add_dir(tmp)
                     wandb.log_artifact(artifact)
                 return
-            # the new checkpoint is complete (its session_info.json is written last) before an old one is removed, so a
-            # failure while writing never leaves the job without a checkpoint to restart from
-            self._write_checkpoint(checkpoint_dir, data)
-            self._saved.append(checkpoint_dir)
-            while self.max_checkpoints and len(self._saved) > self.max_checkpoints:
-                old = self._saved.popleft()
-                if _rank() == 0 and os.path.isdir(old) and os.path.abspath(old) != os.path.abspath(checkpoint_dir):
-                    logger.info("Removing old checkpoint %s", old)
-                    shutil.rmtree(old, ignore_errors=True)
+            if writer:
+                self._write_model_files(checkpoint_dir, data)
+            if self.slot is not None:
+                # one writer per device slot: `session_info.json` marks the checkpoint as complete, so it may only
+                # appear (and an older checkpoint may only go) once every slot's files are on disk
+                self.comm.barrier()
+            if _rank() == 0:
+                self._write_completion_marker(checkpoint_dir)
+                self._saved.append(checkpoint_dir)
+                while self.max_checkpoints and len(self._saved) > self.max_checkpoints:
+                    old = self._saved.popleft()
+                    if os.path.isdir(old) and os.path.abspath(old) != os.path.abspath(checkpoint_dir):
+                        logger.info("Removing old checkpoint %s", old)
+                        shutil.rmtree(old, ignore_errors=True)
+            if self.slot is not None:
+                self.comm.barrier()  # the checkpoint is complete when any process returns
 
-    def _write_checkpoint(self, checkpoint_dir: str, data: Dict[str, np.ndarray]):
+    def _write_model_files(self, checkpoint_dir: str, data: Dict[str, np.ndarray]):
         model_dir = os.path.join(checkpoint_dir, "model")
         os.makedirs(model_dir, exist_ok=True)
         named = self.state.to_dict()
@@ -160,12 +174,19 @@ class TaskSession(xl.Session):
                     os.path.join(model_dir, os.path.basename(str(init.filename))))
             else:
                 np.savez(os.path.join(model_dir, f"{name}.npz"), **{name: array})
-        if _rank() != 0:
-            return  # the files every checkpoint has once are written by one process
+
+    def _write_completion_marker(self, checkpoint_dir: str):
+        """The files a checkpoint has once; `session_info.json` comes last and appears atomically: a directory that
+        has it is a complete checkpoint (`parallel.elastic.latest_checkpoint` relies on that)."""
+        os.makedirs(checkpoint_dir, exist_ok=True)
         if self._dataloader is not None:
             self._dataloader.save(os.path.join(checkpoint_dir, "dataloader.bin"))
-        with open(os.path.join(checkpoint_dir, "session_info.json"), "w") as f:
+        tmp = os.path.join(checkpoint_dir, f".session_info.json.tmp{os.getpid()}")
+        with open(tmp, "w") as f:
             json.dump(self.session_state, f)
+            f.flush()
+            os.fsync(f.fileno())
+        os.replace(tmp, os.path.join(checkpoint_dir, "session_info.json"))
 
     def load_checkpoint(self, checkpoint_dir: str, report_missing: str = "warn", skip_memmap: bool = False):
         """Restore state from a checkpoint directory (or `wandb://artifact`). `report_missing`: what to do when the
@@ -174,7 +195,7 @@ class TaskSession(xl.Session):
             if checkpoint_dir.startswith(_WANDB_PREFIX):
                 if wandb is None:
                     raise RuntimeError("wandb is not installed")
-                artifact = wandb.use_artifact(checkpoint_dir[len(_WANDB_PREFIX):], type="model")
+                artifact = wandb.use_artifact(checkpoint_dir[len(_WANDB_PREFIX):], type="checkpoints")
                 checkpoint_dir = artifact.download()
             self._read_checkpoint(checkpoint_dir, report_missing, skip_memmap)
 

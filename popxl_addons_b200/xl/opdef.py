@@ -14,6 +14,26 @@ from .dtypes import dtype as _dtype
 
 OPS: Dict[str, "OpDef"] = {}
 
+# Ops that ran their torch reference on a CUDA session although a device kernel is registered for them (the kernel
+# refused the operands), by op name. `STRICT[0] = True` turns such a fallback of a hot op into an error, so that a
+# regression which sends e.g. the GEMMs to the library is noticed at once (the benchmark and the GPU tests switch it on).
+FALLBACKS: Dict[str, int] = {}
+STRICT = [False]
+_HOT_PREFIXES = ("matmul", "linear_bias_act", "attention", "cross_entropy", "ce_", "layer_norm", "rms_norm", "gelu",
+                 "swiglu", "gather", "adam", "rts_adam")
+
+
+class NativeFallback(RuntimeError):
+    """A hot op ran (or was about to run) its library / eager implementation on a GPU while strict mode is on."""
+
+
+def note_fallback(name: str, detail: str = "") -> None:
+    FALLBACKS[name] = FALLBACKS.get(name, 0) + 1
+    if STRICT[0] and name.startswith(_HOT_PREFIXES):
+        raise NativeFallback(f"op `{name}` fell back to its torch implementation on a CUDA session"
+                             + (f" ({detail})" if detail else "")
+                             + "; its device kernel refused the operands (dtype, alignment or layout)")
+
 
 class OpDef:
     def __init__(self, name: str, impl: Optional[Callable] = None, vjp: Optional[Callable] = None,

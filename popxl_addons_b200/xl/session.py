@@ -21,6 +21,7 @@ from . import dtypes as _dt
 from .buffers import DeviceToHostStream, HostToDeviceStream, RemoteBuffer
 from .comm import DistComm, SimComm
 from .core import Constant, Graph, Ir, LazyInit, Tensor, Variable
+from .opdef import note_fallback as _note_fallback
 
 
 # what `run` takes and returns (popxl/session.py exports the same two names)
@@ -510,11 +511,23 @@ class Session:
     def native_collective(self, name: str):
         """Fused compute+collective kernel registered under `name` for this session's transport, or None (then the
         op runs its reference composition over `self.comm`)."""
-        if not self.use_native or not self.distributed:
+        if not self.use_native:
             return None
         from ..parallel import fused
 
-        return fused.lookup(name, self)
+        if not self.distributed and name not in fused.LOCAL_OK:
+            return None
+        fn = fused.lookup(name, self)
+        if fn is None:
+            return None
+
+        def counted(*args, **kw):
+            res = fn(*args, **kw)
+            if res is NotImplemented:
+                _note_fallback("fused:" + name)  # the op then runs as its own kernels + a library collective
+            return res
+
+        return counted
 
     # ------------------------------------------------------------------------------------------------------
     # interpreter
@@ -620,6 +633,10 @@ class Session:
                     res = NotImplemented
                     if fn is not None:
                         res = fn(*args, **op.attrs)
+                        if res is NotImplemented:
+                            _note_fallback(od.name, ", ".join(
+                                f"{tuple(a.shape)} {str(a.dtype).replace('torch.', '')}" for a in args
+                                if isinstance(a, torch.Tensor)))
                     if res is NotImplemented:
                         res = od.impl(*args, **op.attrs)
                     outs_per_replica.append((res,) if isinstance(res, torch.Tensor) else tuple(res or ()))
@@ -666,6 +683,9 @@ class Session:
         (lazy initialisation: arenas, workspaces, library handles), the second is captured into a CUDA graph, all
         later ones (in this and every following `run`) replay it. Host-stream reads inside the body go through a
         static staging tensor that is refreshed before each replay; host-stream writes are copied out after it."""
+        # an all-reduce issued outside the loop may still be in flight: its join must not land inside the capture (a wait
+        # on an event recorded outside a capture is not part of the replayed graph)
+        self.comm.wait_all()
         state = self._captured.get(op.uid)
         it = 0
         debug = os.environ.get("XL_DEBUG_CAPTURE") == "1"

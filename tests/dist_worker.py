@@ -377,8 +377,8 @@ def main():
             # every process writes the variables of its own device slot into one directory and restores them from it
             sess = tr.session
             before = {k: v.copy() for k, v in sess.get_named_tensors_data().to_dict().items()}
-            sess.save_checkpoint(args.ckpt)
-            dist.barrier()
+            sess.save_checkpoint(args.ckpt)  # returns once every slot's files and the completion marker are written
+            assert os.path.exists(os.path.join(args.ckpt, "session_info.json"))
             for var in sess._owned_state().values():
                 sess.write_variable_data(var, np.zeros(var.shape_on_host, dtype=np.float32))
             sess.load_checkpoint(args.ckpt, report_missing="error")

@@ -109,16 +109,24 @@ def test_row_statistics_kernels(nat):
     y, mean, rstd = nat.ln_apply_stats(x, stats, w, b, 1000, 1e-5)
     want = torch.nn.functional.layer_norm(x.float(), (1000,), w.float(), b.float(), 1e-5)
     torch.testing.assert_close(y.float(), want, rtol=2e-2, atol=3e-2)
-    # vocabulary-sharded cross-entropy pieces on one "shard" = the whole vocabulary
+    # vocabulary-sharded cross-entropy kernels on two uneven "shards" of one device
     labels = torch.randint(0, 1000, (64,), device="cuda", dtype=torch.int32)
-    gmax = nat.ce_shard_row_max(x)
-    torch.testing.assert_close(gmax, x.float().amax(-1))
-    se = nat.ce_shard_sumexp(x, gmax, labels)
-    loss = torch.log(se[0]) - se[1]
+    shards, offs = [x[:, :600].contiguous(), x[:, 600:].contiguous()], [0, 600]
+    stats = torch.stack([nat.ce_shard_stats(sh, labels, off) for sh, off in zip(shards, offs)])
+    torch.testing.assert_close(stats[0, 0], shards[0].float().amax(-1))
+    g = nat.ce_shard_combine(stats)
+    torch.testing.assert_close(g[0], x.float().amax(-1))
+    torch.testing.assert_close(g[1], torch.exp(x.float() - g[0][:, None]).sum(-1), rtol=1e-4, atol=1e-4)
     want_loss = torch.nn.functional.cross_entropy(x.float(), labels.long(), reduction="none")
-    torch.testing.assert_close(loss, want_loss, rtol=1e-3, atol=1e-3)
     scale = torch.full((64,), 0.5, device="cuda")
-    dx = nat.ce_shard_grad(x, gmax, se[0], labels, scale)
     xf = x.float().requires_grad_(True)
     (torch.nn.functional.cross_entropy(xf, labels.long(), reduction="none") * 0.5).sum().backward()
-    torch.testing.assert_close(dx.float(), xf.grad, rtol=2e-2, atol=2e-3)
+    for sh, off in zip(shards, offs):
+        dx, loss = nat.ce_shard_grad_loss(sh, g[0], g[1], g[2], labels, off, scale)
+        torch.testing.assert_close(loss, want_loss, rtol=1e-3, atol=1e-3)
+        torch.testing.assert_close(dx.float(), xf.grad[:, off:off + sh.shape[1]], rtol=2e-2, atol=2e-3)
+        nls, loss16 = nat.ce_shard_nls(sh, g[0], g[1], g[2])
+        want_nls = -torch.log_softmax(x.float(), -1)[:, off:off + sh.shape[1]]
+        torch.testing.assert_close(nls.float(), want_nls, rtol=2e-2, atol=5e-2)
+        back = nat.ce_nls_grad(nls, labels, off, scale.to(nls.dtype))
+        torch.testing.assert_close(back.float(), xf.grad[:, off:off + sh.shape[1]], rtol=5e-2, atol=5e-3)

@@ -476,7 +476,8 @@ def test_weights_and_biases_paths_with_a_stand_in(tmp_path, monkeypatch):
     fake = types.SimpleNamespace(
         run=types.SimpleNamespace(summary={}), Histogram=lambda data: ("hist", len(data)),
         log=lambda d, step=None: logged.append((d, step)), Artifact=Artifact,
-        log_artifact=lambda a: artifacts.__setitem__(a.name, a), use_artifact=lambda name, type=None: artifacts[name])
+        log_artifact=lambda a: artifacts.__setitem__(a.name, a),
+        use_artifact=lambda name, type=None: {a.name: a for a in artifacts.values() if a.type == type}[name])
     monkeypatch.setattr(ts, "wandb", fake)
     monkeypatch.setattr(ut, "wandb", fake)
     monkeypatch.setattr(ut, "_HAVE_WANDB", True)
@@ -487,11 +488,13 @@ def test_weights_and_biases_paths_with_a_stand_in(tmp_path, monkeypatch):
     s.write_variable_data(v.bias, np.array([1.0, np.nan, np.inf], np.float32))
     s.wandb_variable_histograms(step=7)
     by_name = {k: (val, step) for d, step in logged for k, val in d.items()}
-    assert by_name["bias"] == (("hist", 1), 7) and by_name["bias_nonfinite"] == (2, 7)
-    assert by_name["weight_nonfinite"][0] == 0
+    # key names of the reference (popxl_addons/task_session.py:115-121)
+    assert by_name["bias:histogram"] == (("hist", 1), 7) and by_name["bias:not_finite"] == (2, 7)
+    assert by_name["weight:not_finite"][0] == 0
     s.run({s.inputs.x: np.ones((2, 4), np.float32)})
     w = s.get_tensor_data(v.weight).copy()
     s.save_checkpoint("wandb://ckpt")
+    assert artifacts["ckpt"].type == "checkpoints"  # what the reference saves and looks up
     assert sorted(os.listdir(os.path.join(artifacts["ckpt"].dir, "model"))) == ["bias.npz", "weight.npz"]
     s2, v2 = _linear_session()
     s2.load_checkpoint("wandb://ckpt")

@@ -652,3 +652,61 @@ def test_schedule_collective_overlap_keeps_dependencies_and_update_order():
             results.append((o[out], s.get_tensor_data(a1), s.get_tensor_data(a2)))
     for a, b in zip(*results):
         np.testing.assert_array_equal(a, b)
+
+
+def test_schedule_collective_overlap_does_not_reorder_calls_with_transfers():
+    """Calls whose graphs store to a host stream, or load from / store to a remote buffer, keep their order: the
+    sequence of host items and of buffer accesses is part of the program, whatever the data dependencies say."""
+    from popxl_addons_b200.parallel import schedule_collective_overlap
+
+    # two calls that each hold a host_store: the items must come out in program order
+    ir = popxl.Ir(replication=2)
+    rg = ir.replica_grouping()
+    with ir.main_graph:
+        x = popxl.variable(np.full((2, 2), 1.0, np.float32), name="x", replica_grouping=ir.replica_grouping(group_size=1))
+        w = popxl.variable(np.full((2,), 5.0, np.float32), name="w")
+        stream = popxl.d2h_stream((2,), popxl.float32, "out")
+
+        def store(t):
+            ops.host_store(stream, t)
+
+        s = ops.collectives.replicated_all_reduce(x, "add", rg)
+        y = s + 1
+        sg = ir.create_graph(store, y)
+        ops.call(sg, y)
+        ops.call(sg, w)
+    ir.num_host_transfers = 2
+    main_before = [o.opdef.name for o in ir.main_graph.ops]
+    schedule_collective_overlap(ir)
+    assert [o.opdef.name for o in ir.main_graph.ops] == main_before
+    with popxl.Session(ir, "cpu") as sess:
+        out = sess.run()[stream]
+    np.testing.assert_array_equal(np.asarray(out).reshape(2, 2, 2)[:, 0], [[3, 3], [5, 5]])
+
+    # a call that loads from a remote buffer may not jump ahead of the call that stores to it
+    ir = popxl.Ir(replication=2)
+    rg = ir.replica_grouping()
+    with ir.main_graph:
+        x = popxl.variable(np.full((2, 2), 1.0, np.float32), name="x", replica_grouping=ir.replica_grouping(group_size=1))
+        buf = popxl.remote_buffer((2,), popxl.float32, 1)
+        res = popxl.d2h_stream((2,), popxl.float32, "res")
+
+        def put(t):
+            ops.remote_store(buf, 0, t)
+
+        def get():
+            return ops.remote_load(buf, 0)
+
+        s = ops.collectives.replicated_all_reduce(x, "add", rg)
+        y = s * 4
+        pg = ir.create_graph(put, y)
+        gg = ir.create_graph(get)
+        ops.call(pg, y)
+        (back,) = ops.call(gg)
+        ops.host_store(res, back)
+    names = [o.opdef.name for o in ir.main_graph.ops]
+    schedule_collective_overlap(ir)
+    assert [o.opdef.name for o in ir.main_graph.ops] == names
+    with popxl.Session(ir, "cpu") as sess:
+        out = sess.run()[res]
+    np.testing.assert_array_equal(np.asarray(out).reshape(2, 2)[0], [8, 8])
