@@ -348,6 +348,9 @@ def main():
                     help="train mode, --impl ours: skip the PyTorch arm that is otherwise timed first on the same GPUs")
     ap.add_argument("--no-decode", action="store_true",
                     help="train mode, --impl ours: skip the int4 decode benchmark that otherwise follows as a secondary record")
+    ap.add_argument("--profile-ops", action="store_true",
+                    help="diagnostics, --impl ours: after the timed regions run one more step with per-op CUDA-event timing "
+                         "(eagerly, no graph replay) and print the per-op totals as a second line starting with PROFILE")
     ap.add_argument("--emulate-tp", type=int, default=0,
                     help="diagnostics: run ONE rank's shard shapes of a K-way tensor-parallel layout (heads, ffn and "
                          "vocabulary divided by K, no collectives) to separate kernel time from communication")
@@ -454,6 +457,14 @@ def main():
         ours["tokens"] = trainer.tokens_per_step
         ours["prune"] = bool(getattr(trainer, "prune_recompute", False))
         ours["peak_gb"] = round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)
+        if args.profile_ops:
+            trainer.session.start_profile()
+            trainer.step(trainer.synthetic_tokens(seed=99))
+            prof = trainer.session.profile_summary()
+            if rank == 0:
+                total = sum(v["ms"] for v in prof.values())
+                print("PROFILE " + json.dumps({"total_ms": total, "ops": {k: {"count": v["count"], "ms": round(v["ms"], 2)}
+                                                                          for k, v in list(prof.items())[:40]}}))
     main_res = ours if args.impl == "ours" else baseline
     dist = current_dist()
 

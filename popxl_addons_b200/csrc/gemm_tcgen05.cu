@@ -31,6 +31,9 @@ constexpr uint32_t SPIN_LIMIT = 1u << 22;
 constexpr int EPI_STAGE_BYTES = 4096;  // per epilogue warp, only in the modes that push tiles to peers
 
 enum { ERR_FULL_WAIT = 1, ERR_EMPTY_WAIT = 2, ERR_TMEM_FULL_WAIT = 3, ERR_TMEM_EMPTY_WAIT = 4 };
+constexpr int AR_ITEMS_PER_TILE = 8;     // a reduce work item = BLOCK_M / 8 = 16 rows of one tile
+constexpr int AR_SYNC_QUEUE = 8, AR_SYNC_DONE = 9;  // words of local_sync used by the pull all-reduce
+constexpr int AR_CHANNEL = 2;            // signal channel of its closing barrier
 
 struct GemmParams {
   int M, N, K, batch;
@@ -77,6 +80,21 @@ struct GemmParams {
   // (0 = e4m3, 1 = e5m2). A k-block is then 128 elements, still one 128-byte swizzle row.
   int fp8_a, fp8_b;
   const float* alpha_log2;  // optional device scalar: the result is also multiplied by 2^(*alpha_log2)
+  // second operand pair (map_a2, map_b2; same layouts as the first) contracted into the same accumulator:
+  // C = A * B + A2 * B2. 0: none.
+  int K2;
+  // all-reduce by pulling (accumulate == 5). Every rank writes its partial product into its own buffer C (symmetric
+  // memory) with plain stores and, tile by tile, tells the rank that owns the tile's rows (rows are split evenly over
+  // the ranks) that its part is there. The owner adds the `world` copies of a tile inside NVSwitch with one
+  // multimem.ld_reduce per 16 bytes of the partial buffers' multicast address and writes the sums into every rank's
+  // result buffer with multimem.st. Reducing is done by the first `n_copy` CTAs of the launch from the start and by the
+  // epilogue warps of the other CTAs once they have run out of tiles; work items (an eighth of a tile) are handed out
+  // by a counter.
+  const uint8_t* ar_src_mc;         // multicast address of the partial buffers (C on every rank)
+  uint8_t* ar_dst_mc;               // multicast address of the result buffers
+  unsigned int* const* ar_flags;    // device array [world]: per rank, 2 * tiles words: [tile] parts arrived (written
+                                    //   by all ranks), [tiles + tile] eighths reduced (owner only). All zero between launches.
+  int ar_rows;                      // rows owned by each rank (a multiple of BLOCK_M)
 };
 
 // k-block range of a tile under the causal modes; false: the tile is skipped altogether
@@ -141,9 +159,113 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   nb = in_group / rows;
 }
 
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* ptr) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add_u32(unsigned int* ptr, unsigned int v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(ptr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 multimem_ld_reduce_16bit(const void* mc_addr, bool bf16) {
+  uint4 v;
+  if (bf16)
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  else
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  return v;
+}
+
+// Reduce work loop of the pull all-reduce, run by whole warps. Returns when no work item is left (or after a wait ran
+// out). Tiles of this rank's rows are taken in the order in which the GEMM CTAs of every rank finish them (columns
+// outermost), an eighth of a tile per item.
+template <int BLOCK_N>
+__device__ __forceinline__ void ar_pull_reduce(const GemmParams& p, int tiles_m, int tiles_n, volatile int* abort_flag) {
+  const int lane = threadIdx.x & 31;
+  const int mpr = p.ar_rows / BLOCK_M;  // row blocks per rank
+  const unsigned int items = (unsigned int)(mpr * tiles_n * AR_ITEMS_PER_TILE);
+  const int total_tiles = tiles_m * tiles_n;
+  unsigned int* flags = p.ar_flags[p.comm_rank];
+  const unsigned int expect = (unsigned int)(NUM_EPI_WARPS * p.comm_world);
+  const bool bf = p.c_dtype == XL_BF16;
+  constexpr int CHUNKS_PER_ROW = BLOCK_N / 8;                              // 16-byte chunks
+  constexpr int ROWS = BLOCK_M / AR_ITEMS_PER_TILE;                        // 16
+  constexpr int ITERS = ROWS * CHUNKS_PER_ROW / 32;                        // 16 (BLOCK_N 256) or 8 (128)
+  for (;;) {
+    if (*abort_flag) break;  // a wait of this CTA ran out: the remaining items would each wait as long
+    unsigned int item = 0;
+    if (lane == 0) item = atomicAdd(p.local_sync + AR_SYNC_QUEUE, 1u);
+    item = __shfl_sync(0xffffffffu, item, 0);
+    if (item >= items) break;
+    const int q = (int)(item / AR_ITEMS_PER_TILE), sub = (int)(item % AR_ITEMS_PER_TILE);
+    const int nb = q / mpr, mb = p.comm_rank * mpr + q % mpr;
+    const int tile_id = mb * tiles_n + nb;
+    int ready = 0;
+    if (lane == 0) {
+      for (unsigned int i = 0; i < p.comm_spin_limit && !ready; ++i) {
+        ready = ld_acquire_sys_u32(flags + tile_id) >= expect;
+        if (!ready && (i & 1023u) == 1023u && *abort_flag) break;
+      }
+    }
+    ready = __shfl_sync(0xffffffffu, ready, 0);
+    if (!ready) {
+      if (lane == 0) {
+        *abort_flag = 1;
+        if (p.err) atomicCAS(p.err, 0, (int)XL_COMM_TIMEOUT_FLAG);
+      }
+      break;
+    }
+    __syncwarp();
+    __threadfence_system();  // every lane's loads below come after the flag that lane 0 saw
+    const int row0 = mb * BLOCK_M + sub * ROWS, col0 = nb * BLOCK_N;
+    uint4 v[ITERS];
+    long long off[ITERS];
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int c = it * 32 + lane;
+      const int row = row0 + c / CHUNKS_PER_ROW, col = col0 + (c % CHUNKS_PER_ROW) * 8;
+      off[it] = (row < p.M && col < p.N) ? ((long long)row * p.ldc + col) * 2 : -1;
+      if (off[it] >= 0) v[it] = multimem_ld_reduce_16bit(p.ar_src_mc + off[it], bf);
+    }
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it)
+      if (off[it] >= 0) xl_multimem_st_b128(p.ar_dst_mc + off[it], v[it]);
+    __syncwarp();
+    if (lane == 0) {
+      const unsigned int prev = atomicAdd(flags + total_tiles + tile_id, 1u);
+      if (prev == AR_ITEMS_PER_TILE - 1) {  // the tile is complete: both of its words go back to zero for the next launch
+        flags[total_tiles + tile_id] = 0;
+        *((volatile unsigned int*)(flags + tile_id)) = 0;
+      }
+    }
+  }
+}
+
+// End of the pull all-reduce on this rank: every warp that took part fences its multicast stores and checks in; the last
+// one re-arms the two control words and runs the closing barrier (no rank may reuse the partial buffers, or read its
+// result buffer, before every rank has finished reducing).
+__device__ __forceinline__ void ar_pull_finish(const GemmParams& p, unsigned int participants) {
+  const int lane = threadIdx.x & 31;
+  __threadfence_system();
+  unsigned int prev = 0;
+  if (lane == 0) prev = atomicAdd(p.local_sync + AR_SYNC_DONE, 1u);
+  prev = __shfl_sync(0xffffffffu, prev, 0);
+  if (prev == participants - 1) {
+    if (lane == 0) {
+      p.local_sync[AR_SYNC_DONE] = 0;
+      p.local_sync[AR_SYNC_QUEUE] = 0;
+      __threadfence();
+    }
+    xl_group_barrier(p.pads, p.comm_rank, p.comm_world, AR_CHANNEL, p.err, p.comm_spin_limit);
+  }
+}
+
 template <int BLOCK_N>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        const __grid_constant__ CUtensorMap map_a2, const __grid_constant__ CUtensorMap map_b2,
                         const GemmParams p) {
   using L = SmemLayout<BLOCK_N>;
   constexpr uint32_t TMEM_COLS = 2 * BLOCK_N;  // two accumulator buffers (power of two: 256 or 512)
@@ -160,21 +282,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   // the first n_copy CTAs of a launch with an all-gather prologue only move data; the others are the GEMM's CTAs
-  const int n_copy = p.gather_mode ? p.n_copy : 0;
-  const bool is_copy = (int)blockIdx.x < n_copy;
+  const bool ar_pull = p.accumulate == 5;
+  const int n_copy = (p.gather_mode || ar_pull) ? p.n_copy : 0;
+  const bool is_copy = p.gather_mode && (int)blockIdx.x < n_copy;
+  const bool is_reducer = ar_pull && (int)blockIdx.x < n_copy;
   const int cta = (int)blockIdx.x - n_copy, ncta = (int)gridDim.x - n_copy;
-  const int raster_group = p.gather_mode == 1 ? min(8, p.gather_bps) : 8;
   const int gather_rot = p.gather_mode ? p.comm_rank * p.gather_bps : 0;  // own shard's row blocks come first
   const int tiles_m = (p.M + BLOCK_M - 1) / BLOCK_M;
   const int tiles_n = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int num_tiles = tiles_m * tiles_n * p.batch;
+  // pull all-reduce: every wave of tiles covers the rows of all ranks, so that all ranks have tiles to reduce throughout
+  const int raster_group = p.gather_mode == 1 ? min(8, p.gather_bps) : (ar_pull ? tiles_m : 8);
   const bool fp8 = p.fp8_a >= 0;
   const int k_elems = fp8 ? 2 * BLOCK_K : BLOCK_K;  // elements per k-block: always 128 bytes
   const int k_blocks = (p.K + k_elems - 1) / k_elems;
+  const int k_blocks2 = (p.K2 + k_elems - 1) / k_elems;  // second operand pair (0 if none)
 
   if (threadIdx.x == 0) {
     if (is_copy) {
       for (int s = 0; s < 2 * STAGES + 4; ++s) mbar_init(&bars[s], 1);  // one barrier per slot of the copy ring
+    } else if (is_reducer) {
+      // no barriers: a reducer CTA only polls flags in global memory
     } else {
       for (int s = 0; s < STAGES; ++s) {
         mbar_init(&full_bar[s], 1);
@@ -197,7 +325,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
 
-  if (is_copy) {
+  if (is_reducer) {
+    // ------------------------------------------------ all-reduce reducer CTA: all ten warps reduce ----------------
+    ar_pull_reduce<BLOCK_N>(p, tiles_m, tiles_n, abort_flag);
+    ar_pull_finish(p, (unsigned int)(n_copy * (NUM_THREADS / 32) + ncta * NUM_EPI_WARPS));
+  } else if (is_copy) {
     // ------------------------------------------------ all-gather copy CTA -----------------------------------------
     // Lane 0 of warp 0 streams this CTA's share of the remote row blocks peer -> shared-memory ring -> local matrix
     // with bulk async copies and raises the block's flag once its bytes have landed. Remote blocks are visited in
@@ -326,8 +458,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int m0 = mb * BLOCK_M, n0 = nb * BLOCK_N;
         int kb0, kb1;
         if (!tile_k_range(p, mb, nb, k_blocks, BLOCK_N, kb0, kb1)) continue;
-        for (int kb_i = kb0; kb_i < kb1; ++kb_i) {
+        for (int kb_i = kb0; kb_i < kb1 + k_blocks2; ++kb_i) {
           int kb = kb_i;
+          const bool second = kb_i >= kb1;  // k-blocks of the second operand pair follow those of the first
+          const CUtensorMap* ma = second ? &map_a2 : &map_a;
+          const CUtensorMap* mb_ = second ? &map_b2 : &map_b;
+          if (second) kb = kb_i - kb1;
           if (p.gather_mode == 2) {
             kb = (kb_i + gather_rot) % k_blocks;
             ok = wait_block(kb);
@@ -340,18 +476,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
           const int k0 = kb * k_elems;
           if (!p.a_mn) {
-            tma_load_3d(sa, &map_a, &full_bar[stage], k0, m0, b);  // box {64 k, 128 m}
+            tma_load_3d(sa, ma, &full_bar[stage], k0, m0, b);  // box {64 k, 128 m}
           } else {
 #pragma unroll
-            for (int j = 0; j < BLOCK_M / 64; ++j)                  // boxes {64 m, 64 k}
-              tma_load_3d(sa + j * (BLOCK_K * 128), &map_a, &full_bar[stage], m0 + j * 64, k0, b);
+            for (int j = 0; j < BLOCK_M / 64; ++j)              // boxes {64 m, 64 k}
+              tma_load_3d(sa + j * (BLOCK_K * 128), ma, &full_bar[stage], m0 + j * 64, k0, b);
           }
           if (!p.b_mn) {
-            tma_load_3d(sb, &map_b, &full_bar[stage], k0, n0, b);  // box {64 k, BLOCK_N n}
+            tma_load_3d(sb, mb_, &full_bar[stage], k0, n0, b);  // box {64 k, BLOCK_N n}
           } else {
 #pragma unroll
-            for (int j = 0; j < BLOCK_N / 64; ++j)                  // boxes {64 n, 64 k}
-              tma_load_3d(sb + j * (BLOCK_K * 128), &map_b, &full_bar[stage], n0 + j * 64, k0, b);
+            for (int j = 0; j < BLOCK_N / 64; ++j)              // boxes {64 n, 64 k}
+              tma_load_3d(sb + j * (BLOCK_K * 128), mb_, &full_bar[stage], n0 + j * 64, k0, b);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -385,7 +521,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (!ok) break;
         tcgen05_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BLOCK_N;
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; kb < kb1 + k_blocks2; ++kb) {
           ok = mbar_wait(&full_bar[stage], phase, abort_flag, p.err, ERR_FULL_WAIT);
           if (!ok) break;
           tcgen05_fence_after();
@@ -414,13 +550,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     float mean_a = 0.f, mean_b = 1.f;
+    const bool push = p.accumulate == 3 || p.accumulate == 4;  // tiles are pushed into the peers' buffers
+    const int acc_mode = ar_pull ? 0 : p.accumulate;           // the pull all-reduce stores plain partial tiles
     const float alpha_eff = p.alpha_log2 ? p.alpha * exp2f(*p.alpha_log2) : p.alpha;
     if (p.accumulate == 2) {
       const float t = *p.step;
       mean_a = t / (t + 1.f);
       mean_b = 1.f / (t + 1.f);
     }
-    if (p.accumulate >= 3) {
+    if (push) {
       // Nobody may push into a peer's output before that peer has zeroed it, i.e. before it has entered this kernel:
       // the first epilogue warp of the first GEMM CTA runs the cross-rank barrier and publishes it to the other CTAs.
       if (cta == 0 && warp == 2) {
@@ -457,7 +595,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       } else {
         crow = (uint8_t*)p.C + ((long long)b * p.batch_stride_c + (long long)row * p.ldc) * (p.c_dtype == XL_F32 ? 4 : 2);
       }
-      if (p.accumulate >= 3) {
+      if (push) {
         // Pushes over NVLink should be whole 128-byte lines. TMEM hands every lane one row, so the tile goes through
         // a per-warp staging area in shared memory (32 rows x 64 columns, 16-byte chunks swizzled by row): written by
         // rows, read back with eight lanes covering 128 contiguous bytes of one row.
@@ -553,9 +691,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
               float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-              if (p.accumulate) {
+              if (acc_mode) {
                 const float4 old = *(const float4*)(dst + j);
-                if (p.accumulate == 1) { o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+                if (acc_mode == 1) { o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
                 else { o.x = old.x * mean_a + o.x * mean_b; o.y = old.y * mean_a + o.y * mean_b;
                        o.z = old.z * mean_a + o.z * mean_b; o.w = old.w * mean_a + o.w * mean_b; }
               }
@@ -564,8 +702,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           } else {
             for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
               float o = v[j];
-              if (p.accumulate == 1) o += dst[j];
-              else if (p.accumulate == 2) o = dst[j] * mean_a + o * mean_b;
+              if (acc_mode == 1) o += dst[j];
+              else if (acc_mode == 2) o = dst[j] * mean_a + o * mean_b;
               dst[j] = o;
             }
           }
@@ -576,16 +714,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
               uint4 old;
-              if (p.accumulate) old = *(const uint4*)(dst + j);
+              if (acc_mode) old = *(const uint4*)(dst + j);
               uint4 o;
               uint16_t* oe = (uint16_t*)&o;
               const uint16_t* ol = (const uint16_t*)&old;
 #pragma unroll
               for (int e = 0; e < 8; ++e) {
                 float val = v[j + e];
-                if (p.accumulate) {
+                if (acc_mode) {
                   const float prev = bf ? __bfloat162float(__ushort_as_bfloat16(ol[e])) : __half2float(__ushort_as_half(ol[e]));
-                  val = p.accumulate == 1 ? prev + val : prev * mean_a + val * mean_b;
+                  val = acc_mode == 1 ? prev + val : prev * mean_a + val * mean_b;
                 }
                 oe[e] = bf ? __bfloat16_as_ushort(__float2bfloat16_rn(val)) : __half_as_ushort(__float2half_rn(val));
               }
@@ -594,9 +732,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           } else {
             for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
               float val = v[j];
-              if (p.accumulate) {
+              if (acc_mode) {
                 const float prev = bf ? __bfloat162float(__ushort_as_bfloat16(dst[j])) : __half2float(__ushort_as_half(dst[j]));
-                val = p.accumulate == 1 ? prev + val : prev * mean_a + val * mean_b;
+                val = acc_mode == 1 ? prev + val : prev * mean_a + val * mean_b;
               }
               dst[j] = bf ? __bfloat16_as_ushort(__float2bfloat16_rn(val)) : __half_as_ushort(__float2half_rn(val));
             }
@@ -608,8 +746,22 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      if (ar_pull) {
+        // this warp's part of the partial tile is in this rank's buffer: tell the rank that reduces these rows
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int owner = (mb * BLOCK_M) / p.ar_rows;
+          red_release_sys_add_u32(p.ar_flags[owner] + (mb * tiles_n + nb), 1u);
+        }
+      }
     }
-    if (p.accumulate >= 3) {
+    if (ar_pull) {
+      // out of tiles: help with the reduction of this rank's rows until nothing is left, then check in
+      if (ok) ar_pull_reduce<BLOCK_N>(p, tiles_m, tiles_n, abort_flag);
+      ar_pull_finish(p, (unsigned int)(n_copy * (NUM_THREADS / 32) + ncta * NUM_EPI_WARPS));
+    }
+    if (push) {
       // The kernel may only finish once every rank's pushes have landed here: the last epilogue warp of this rank
       // to finish runs the closing cross-rank barrier (each warp fences its own pushes first).
       __threadfence_system();
@@ -654,7 +806,8 @@ int make_map(CUtensorMap* map, const void* ptr, int is_fp16, long long rows, lon
 }
 
 template <int BLOCK_N>
-int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int sm_count, cudaStream_t s) {
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int sm_count, cudaStream_t s,
+           const CUtensorMap* ma2 = nullptr, const CUtensorMap* mb2 = nullptr) {
   using L = SmemLayout<BLOCK_N>;
   static bool configured = false;
   constexpr int TOTAL_COMM = L::TOTAL + NUM_EPI_WARPS * EPI_STAGE_BYTES;
@@ -664,12 +817,14 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int smem_bytes = p.accumulate >= 3 ? TOTAL_COMM : L::TOTAL;
+  const int smem_bytes = (p.accumulate == 3 || p.accumulate == 4) ? TOTAL_COMM : L::TOTAL;
   const int tiles = ((p.M + BLOCK_M - 1) / BLOCK_M) * ((p.N + BLOCK_N - 1) / BLOCK_N) * p.batch;
-  const int n_copy = p.gather_mode ? p.n_copy : 0;  // copy CTAs and GEMM CTAs wait on one another: all must be resident
+  // copy / reducer CTAs and GEMM CTAs wait on one another: all must be resident
+  const int n_copy = (p.gather_mode || p.accumulate == 5) ? p.n_copy : 0;
   const int gemm_ctas = tiles < sm_count - n_copy ? tiles : sm_count - n_copy;
   const int grid = gemm_ctas + n_copy;
-  gemm_tcgen05_kernel<BLOCK_N><<<grid, NUM_THREADS, smem_bytes, s>>>(ma, mb, p);
+  // without a second operand pair the kernel never touches the second pair of maps: pass the first pair again
+  gemm_tcgen05_kernel<BLOCK_N><<<grid, NUM_THREADS, smem_bytes, s>>>(ma, mb, ma2 ? *ma2 : ma, mb2 ? *mb2 : mb, p);
   return (int)cudaGetLastError();
 }
 
@@ -732,6 +887,7 @@ XL_API int xl_gemm_tcgen05_fused(const void* a, const void* b, void* c, int M, i
   p.gather_block_bytes = 0;
   p.fp8_a = p.fp8_b = -1;
   p.alpha_log2 = nullptr;
+  p.K2 = 0; p.ar_src_mc = nullptr; p.ar_dst_mc = nullptr; p.ar_flags = nullptr; p.ar_rows = 0;
   p.causal = causal;
   if (causal < 0 || causal > 3 || (causal && (gather_mode || accumulate >= 3))) return -1;
   if (causal && (M != N && causal == 1)) return -1;
@@ -786,6 +942,7 @@ XL_API int xl_gemm_tcgen05_fp8(const void* a, const void* b, void* c, int M, int
   p.gather_flags = nullptr; p.gather_block_bytes = 0;
   p.causal = 0;
   p.fp8_a = fmt_a; p.fp8_b = fmt_b; p.alpha_log2 = alpha_log2;
+  p.K2 = 0; p.ar_src_mc = nullptr; p.ar_dst_mc = nullptr; p.ar_flags = nullptr; p.ar_rows = 0;
   if (sm_count <= 0) sm_count = 148;
   if (block_n == 128) return launch<128>(ma, mb, p, sm_count, s);
   return launch<256>(ma, mb, p, sm_count, s);
@@ -803,4 +960,69 @@ XL_API int xl_gemm_tcgen05(const void* a, const void* b, void* c, int M, int N, 
                                ab_is_fp16, c_dtype, bias, bias_dtype, act, accumulate, step, alpha, err, sm_count,
                                comm_pads, comm_rank, comm_world, comm_local_sync, nullptr, 0, 0, nullptr, nullptr,
                                nullptr, 0, 0, 0, s);
+}
+
+// all_reduce over the ranks of a group of (A * B [+ A2 * B2]), 16-bit operands and result, fp32 accumulation, in one kernel
+// that pulls: see GemmParams::ar_src_mc. Operand conventions as xl_gemm_tcgen05 (a2 / b2 have the layouts of a / b;
+// K2 = 0 and null pointers: a single product).
+//   partial      this rank's buffer for its partial product (M x ldc, symmetric memory), partial_mc its multicast address
+//   result_mc    multicast address of the (M x ldc) result buffers: after the kernel every rank's buffer holds the sum
+//   flags        device array [world] with every rank's flag words (2 * tiles words each, symmetric memory, zero before
+//                the first launch; the kernel leaves them zero), tiles = (M / 128) * ceil(N / 256 or 128)
+//   rows are split evenly: M must be a multiple of 128 * world. n_red: CTAs that only reduce (at least 1).
+//   Uses comm_local_sync[8..9] and signal channel 2; no launch argument changes between calls (graph replay is fine).
+// Returns 0, a CUDA error code, or a negative value when the arguments are not supported.
+XL_API int xl_gemm_tcgen05_ar_pull(const void* a, const void* b, const void* a2, const void* b2, void* partial,
+                                   const void* partial_mc, void* result_mc, int M, int N, int K, int K2, int a_mn, int b_mn,
+                                   long long lda, long long ldb, long long lda2, long long ldb2, long long ldc,
+                                   int ab_is_fp16, int c_dtype, float alpha, int* err, int sm_count, const void* comm_pads,
+                                   int comm_rank, int comm_world, unsigned int* comm_local_sync, const void* flags,
+                                   int n_red, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || K <= 0 || K2 < 0) return -1;
+  if ((((uintptr_t)a) & 15) || (((uintptr_t)b) & 15) || (lda % 8) || (ldb % 8)) return -1;
+  if (K2 && ((((uintptr_t)a2) & 15) || (((uintptr_t)b2) & 15) || (lda2 % 8) || (ldb2 % 8) || !a2 || !b2)) return -1;
+  if (comm_pads == nullptr || comm_local_sync == nullptr || flags == nullptr || partial == nullptr ||
+      partial_mc == nullptr || result_mc == nullptr)
+    return -1;
+  if (comm_world < 2 || comm_world > 32 || (N % 8) || (ldc % 8) || c_dtype == XL_F32 || n_red < 1) return -1;
+  if (M % (BLOCK_M * comm_world)) return -1;
+  if ((((uintptr_t)partial) & 15) || (((uintptr_t)partial_mc) & 15) || (((uintptr_t)result_mc) & 15)) return -1;
+  if (sm_count <= 0) sm_count = 148;
+  if (n_red > sm_count / 2) return -1;
+  const int block_n = (N <= 128) ? 128 : 256;
+  CUtensorMap ma, mb, ma2, mb2;
+  int r;
+  if (!a_mn) r = make_map(&ma, a, ab_is_fp16, M, K, lda, 1, 0, BLOCK_K, BLOCK_M);
+  else r = make_map(&ma, a, ab_is_fp16, K, M, lda, 1, 0, 64, BLOCK_K);
+  if (r) return r;
+  if (!b_mn) r = make_map(&mb, b, ab_is_fp16, N, K, ldb, 1, 0, BLOCK_K, block_n);
+  else r = make_map(&mb, b, ab_is_fp16, K, N, ldb, 1, 0, 64, BLOCK_K);
+  if (r) return r;
+  if (K2) {
+    if (!a_mn) r = make_map(&ma2, a2, ab_is_fp16, M, K2, lda2, 1, 0, BLOCK_K, BLOCK_M);
+    else r = make_map(&ma2, a2, ab_is_fp16, K2, M, lda2, 1, 0, 64, BLOCK_K);
+    if (r) return r;
+    if (!b_mn) r = make_map(&mb2, b2, ab_is_fp16, N, K2, ldb2, 1, 0, BLOCK_K, block_n);
+    else r = make_map(&mb2, b2, ab_is_fp16, K2, N, ldb2, 1, 0, 64, BLOCK_K);
+    if (r) return r;
+  }
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K; p.batch = 1;
+  p.a_mn = a_mn; p.b_mn = b_mn;
+  p.C = partial; p.ldc = ldc; p.batch_stride_c = 0; p.c_dtype = c_dtype;
+  p.bias = nullptr; p.bias_dtype = 0; p.act = 0; p.accumulate = 5; p.step = nullptr;
+  p.alpha = alpha; p.is_fp16 = ab_is_fp16; p.err = err;
+  p.pads = (unsigned int* const*)comm_pads; p.comm_rank = comm_rank; p.comm_world = comm_world;
+  p.local_sync = comm_local_sync; p.comm_spin_limit = xl_host_comm_spin_limit;
+  p.rs_dst = nullptr; p.rs_rows = 0;
+  p.gather_mode = 0; p.n_copy = n_red; p.gather_bps = 0; p.gather_src = nullptr; p.gather_dst = nullptr;
+  p.gather_flags = nullptr; p.gather_block_bytes = 0;
+  p.causal = 0;
+  p.fp8_a = p.fp8_b = -1;
+  p.alpha_log2 = nullptr;
+  p.K2 = K2;
+  p.ar_src_mc = (const uint8_t*)partial_mc; p.ar_dst_mc = (uint8_t*)result_mc;
+  p.ar_flags = (unsigned int* const*)flags; p.ar_rows = M / comm_world;
+  if (block_n == 128) return launch<128>(ma, mb, p, sm_count, s, K2 ? &ma2 : nullptr, K2 ? &mb2 : nullptr);
+  return launch<256>(ma, mb, p, sm_count, s, K2 ? &ma2 : nullptr, K2 ? &mb2 : nullptr);
 }

@@ -159,9 +159,9 @@ class DecoderTrainer:
         self._build()
         apply_pre_alias_patterns(self.ir)
         self.fused_gemm_collectives = 0
-        # GEMM + all-reduce fusion pays up to this TP width (measured: 1.01x of GEMM + NCCL at 2 ranks, 0.90x at 4, where
-        # the epilogue's pushes cost more than NCCL's in-switch all-reduce); wider groups keep GEMM and NCCL separate
-        fuse_up_to = int(os.environ.get("XL_FUSE_GEMM_AR_MAX_TP", "2"))
+        # GEMM + all-reduce as one kernel (the pulling form: partial tiles stay local, NVSwitch adds them on the way into
+        # the rank that owns the rows) up to this TP width; XL_FUSE_GEMM_AR=0 keeps GEMM and NCCL all-reduce separate
+        fuse_up_to = int(os.environ.get("XL_FUSE_GEMM_AR_MAX_TP", "8"))
         if (fused_collectives and 1 < cfg.tp <= fuse_up_to and os.environ.get("XL_FUSE_GEMM_AR", "1") != "0"):
             from ..parallel import fuse_gemm_collectives
 

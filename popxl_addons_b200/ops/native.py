@@ -78,6 +78,9 @@ _gemm_fused = _sig("xl_gemm_tcgen05_fused", _c_p, _c_p, _c_p, _c_int, _c_int, _c
                    _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p)
 _gemm_pair = _sig("xl_gemm2cta_tcgen05", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
                   _c_ll, _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_p)
+_gemm_ar_pull = _sig("xl_gemm_tcgen05_ar_pull", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
+                     _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_f, _c_p, _c_int, _c_p, _c_int,
+                     _c_int, _c_p, _c_p, _c_int, _c_p)
 _gq_small = _sig("xl_gq_gemm_small_m", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
                  _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p)
 _rot_append = _sig("xl_rotary_append", _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -270,6 +273,8 @@ def swiglu_grad_cuda(gate, up, g):
 # ---- normalisation -------------------------------------------------------------------------------------------------
 @native("layer_norm")
 def layer_norm_cuda(x, w, b, eps):
+    if x.is_cuda and not x.is_contiguous():
+        x = x.contiguous()  # e.g. the last position of every sequence: a strided slice of the activations
     if not _ok(x, w, b) or not (x.dtype == w.dtype == b.dtype):
         return NotImplemented
     cols = x.shape[-1]
@@ -480,9 +485,10 @@ def _major(t: torch.Tensor, contraction_last: bool):
     return None
 
 
-# XL_GEMM_CTA_PAIRS=1: plain GEMMs with N > 128 run on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); collective
-# epilogues, the all-gather prologue and causal products keep the single-CTA kernel
-_GEMM_CTA_PAIRS = os.environ.get("XL_GEMM_CTA_PAIRS", "0") == "1"
+# Plain GEMMs with N > 128 run on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles: measured 1.15 to 1.22x the single-CTA
+# kernel on the transformer shapes); collective epilogues, the all-gather prologue and causal products keep the
+# single-CTA kernel. XL_GEMM_CTA_PAIRS=0 switches the pairs off.
+_GEMM_CTA_PAIRS = os.environ.get("XL_GEMM_CTA_PAIRS", "1") != "0"
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = None, act: int = 0,
@@ -578,6 +584,50 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
     _check(rc, "gemm_tcgen05")
     _count("gemm_tcgen05")
     return out
+
+
+def gemm_all_reduce_pull(pairs, comm, partial: torch.Tensor, result: torch.Tensor, flags_ptrs: torch.Tensor,
+                         n_red: int = 8, alpha: float = 1.0):
+    """`result <- all_reduce over the group of (sum of a @ b over pairs)` in one kernel (one or two operand pairs, all
+    with the same layouts). Every rank's GEMM CTAs store the partial product into `partial` (symmetric memory) and flag
+    each tile at the rank that owns its rows; that rank adds the copies of the tile inside NVSwitch
+    (`multimem.ld_reduce`) and writes the sum into every rank's `result` (`multimem.st`), tile by tile while the
+    remaining tiles are still being multiplied. `partial`, `result`: `(M, N)` arena tensors of the group `comm`;
+    `flags_ptrs`: int64 device tensor with every rank's address of the (zeroed) flag words (2 * tiles int32).
+    Returns `result` (valid once the kernel has finished) or NotImplemented."""
+    (a, b) = pairs[0]
+    a2, b2 = pairs[1] if len(pairs) > 1 else (None, None)
+    if len(pairs) > 2 or a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16) or a.dim() != 2 or b.dim() != 2:
+        return NotImplemented
+    ma, mb = _major(a, True), _major(b, False)
+    if ma is None or mb is None:
+        return NotImplemented
+    (a_mn, lda), (b_mn, ldb) = ma, mb
+    M, K = a.shape
+    N = b.shape[1]
+    K2, lda2, ldb2 = 0, 0, 0
+    if a2 is not None:
+        m2, n2 = _major(a2, True), _major(b2, False)
+        if m2 is None or n2 is None or m2[0] != a_mn or n2[0] != b_mn or a2.dtype != a.dtype or b2.dtype != a.dtype \
+                or a2.shape[0] != M or b2.shape[1] != N or a2.shape[1] != b2.shape[0]:
+            return NotImplemented
+        K2, lda2, ldb2 = a2.shape[1], m2[1], n2[1]
+    if partial.shape != (M, N) or result.shape != (M, N) or partial.dtype != a.dtype or result.dtype != a.dtype \
+            or partial.stride(1) != 1 or result.stride() != partial.stride():
+        return NotImplemented
+    mc_p, mc_r = comm.arena.multicast_ptr(partial), comm.arena.multicast_ptr(result)
+    if not mc_p or not mc_r or M % (128 * comm.world):
+        return NotImplemented
+    rc = _gemm_ar_pull(a.data_ptr(), b.data_ptr(), a2.data_ptr() if a2 is not None else None,
+                       b2.data_ptr() if b2 is not None else None, partial.data_ptr(), mc_p, mc_r, M, N, K, K2, a_mn, b_mn,
+                       lda, ldb, lda2, ldb2, partial.stride(0), int(a.dtype == torch.float16), _CODE[a.dtype], float(alpha),
+                       comm.err.data_ptr(), _sms(a.device), comm.arena.pads_dev.data_ptr(), comm.rank, comm.world,
+                       comm.arena.local_sync.data_ptr(), flags_ptrs.data_ptr(), int(n_red), _stream())
+    if rc < 0:
+        return NotImplemented
+    _check(rc, "gemm_ar_pull_tcgen05")
+    _count("gemm_ar_pull_tcgen05")
+    return result
 
 
 def _flatten_batch(t: torch.Tensor) -> Optional[torch.Tensor]:
@@ -706,8 +756,19 @@ def _heads_view(mat, col0, B, S, H, D):
 
 # the masked half of causal attention products is not computed (XL_CAUSAL_SKIP=0 computes the full products)
 _CAUSAL_SKIP = os.environ.get("XL_CAUSAL_SKIP", "1") != "0"
-# XL_FLASH_ATTENTION=1: the forward pass of `attention_qkv` runs as one kernel that keeps the scores on chip
-_FLASH_ATTENTION = os.environ.get("XL_FLASH_ATTENTION", "0") == "1"
+# The forward pass of `attention_qkv` runs as one kernel that keeps the scores on chip (measured 1.65x the GEMM + softmax
+# + GEMM path at 16 heads x 2048 x 256) when it has enough (batch, head, query block) work items to fill the SMs; with
+# fewer the batched GEMM path, which also spreads one head's keys over CTAs, is used. XL_FLASH_ATTENTION=0 / 1 forces it.
+_FLASH_ATTENTION = os.environ.get("XL_FLASH_ATTENTION", "auto")
+_FLASH_MIN_CTAS = 120
+
+
+def _use_flash(B, S, H):
+    if _FLASH_ATTENTION in ("0", "1"):
+        return _FLASH_ATTENTION == "1"
+    if _FLASH_ATTENTION is True or _FLASH_ATTENTION is False:  # set by tools
+        return bool(_FLASH_ATTENTION)
+    return B * H * ((S + 127) // 128) >= _FLASH_MIN_CTAS
 
 
 def flash_attention_fwd(packed, q_col, k_col, v_col, B, S, H, D, scale, causal, out=None):
@@ -741,9 +802,9 @@ def attention_qkv_cuda(qkv, sin, cos, seq_len, n_heads, head_dim, rotary_dim, ca
     if rotary_dim:
         if sin.dtype != qkv.dtype or not _ok(sin, cos):
             return NotImplemented
-        rotary_launch(q, sin, cos, q, rotary_dim, False)
-        rotary_launch(k, sin, cos, k, rotary_dim, False)
-    if _FLASH_ATTENTION:
+        qk = _heads_view(rot, 0, B, S, 2 * H, D)  # q and k heads are adjacent column windows: one launch rotates both
+        rotary_launch(qk, sin, cos, qk, rotary_dim, False)
+    if _use_flash(B, S, H):
         res = flash_attention_fwd(rot, 0, hd, 2 * hd, B, S, H, D, scale, causal)
         if res is not NotImplemented:
             return res[0], rot, res[1]
@@ -803,8 +864,8 @@ def attention_qkv_grad_cuda(qkv_rot, lse, dout, sin, cos, seq_len, n_heads, head
                 or gemm(dp.transpose(-1, -2), q[b], out=dk[b], causal=c3) is NotImplemented:
             return NotImplemented
     if rotary_dim:
-        rotary_launch(dq, sin, cos, dq, rotary_dim, True)
-        rotary_launch(dk, sin, cos, dk, rotary_dim, True)
+        dqk = _heads_view(dqkv, 0, B, S, 2 * H, D)
+        rotary_launch(dqk, sin, cos, dqk, rotary_dim, True)
     return dqkv
 
 
@@ -847,6 +908,10 @@ def ce_with_grad_cuda(logits, labels, loss_grad, ignore_index, reduction):
 def set_comm_spin_limit(polls: int) -> None:
     """Poll budget of every bounded wait on a peer in kernels launched from now on (0 restores the default)."""
     _set_spin(int(polls))
+
+
+if os.environ.get("XL_COMM_SPIN_LIMIT"):  # e.g. first runs of a new collective kernel: give up after seconds, not minutes
+    set_comm_spin_limit(int(os.environ["XL_COMM_SPIN_LIMIT"]))
 
 
 def _row_window_ok(t) -> bool:

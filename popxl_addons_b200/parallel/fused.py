@@ -100,8 +100,51 @@ def matmul_all_reduce(ex, op, a_vals, w_vals):
 _RS_AG_FROM_WORLD = int(os.environ.get("XL_RS_AG_FROM_WORLD", "4"))
 
 
+# GEMM + all-reduce by pulling (NVSwitch adds the ranks' partial tiles on the way into the rank that owns the rows, which
+# multicasts the sums): the form used from this group size on; XL_AR_PULL=0 switches it off, XL_AR_PULL_CTAS sets the
+# number of CTAs that only reduce
+_AR_PULL = os.environ.get("XL_AR_PULL", "1") != "0"
+_AR_PULL_FROM_WORLD = int(os.environ.get("XL_AR_PULL_FROM_WORLD", "2"))
+_AR_PULL_CTAS = int(os.environ.get("XL_AR_PULL_CTAS", "8"))
+
+
+def _pull_buffers(ctx: GroupContext, M: int, N: int, dtype):
+    """Arena buffers of the pull all-reduce for one output shape: the partial-product buffer, a ring of two result
+    buffers, and the flag words with their address on every rank."""
+    cache = ctx.__dict__.setdefault("_pull", {})
+    key = (M, N, dtype)
+    if key not in cache:
+        partial = ctx.arena.alloc((M, N), dtype)
+        results = [ctx.arena.alloc((M, N), dtype) for _ in range(2)]
+        tiles = (M // 128) * (-(-N // (128 if N <= 128 else 256)))
+        flags = ctx.arena.alloc((2 * tiles,), torch.int32)
+        flags.zero_()
+        torch.cuda.synchronize(flags.device)
+        torch.distributed.barrier(group=ctx.pg)  # nobody signals into flag words that are not zeroed yet
+        cache[key] = {"partial": partial, "results": results, "flags": _peer_ptr_tensor(ctx, flags), "pos": 0}
+    return cache[key]
+
+
+def gemm_all_reduce_pull(ctx: GroupContext, pairs, n_red: Optional[int] = None):
+    """`all_reduce(sum of a @ w over pairs)` (one or two pairs) as one pulling kernel; the result lives in a ring of two
+    arena buffers (valid until the second next call with the same shape). NotImplemented if unsupported."""
+    nat = _lib()
+    a0, w0 = pairs[0]
+    M, N = a0.shape[0], w0.shape[-1]
+    if not ctx.arena.mc_base or M % (128 * ctx.world) or N % 8 or a0.dtype not in (torch.bfloat16, torch.float16):
+        return NotImplemented
+    buf = _pull_buffers(ctx, M, N, a0.dtype)
+    result = buf["results"][buf["pos"]]
+    res = nat.gemm_all_reduce_pull(pairs, ctx, buf["partial"], result, buf["flags"],
+                                   n_red=_AR_PULL_CTAS if n_red is None else n_red)
+    if res is NotImplemented:
+        return NotImplemented
+    buf["pos"] ^= 1
+    return result
+
+
 def _gemms_all_reduce(ctx: GroupContext, pairs):
-    """`all_reduce(sum of a @ w over pairs)` with the reduction fused into the GEMM epilogues; None if unsupported."""
+    """`all_reduce(sum of a @ w over pairs)` with the reduction fused into the GEMM; None if unsupported."""
     nat = _lib()
     a0, w0 = pairs[0]
     M, N = a0.shape[0], w0.shape[-1]
@@ -109,6 +152,10 @@ def _gemms_all_reduce(ctx: GroupContext, pairs):
         return None
     if any(a.dtype != a0.dtype or a.shape[0] != M or w.shape[-1] != N for a, w in pairs):
         return None
+    if _AR_PULL and _MC_ALL_REDUCE and ctx.world >= _AR_PULL_FROM_WORLD and len(pairs) <= 2:
+        out = gemm_all_reduce_pull(ctx, pairs)
+        if out is not NotImplemented:
+            return out.clone()  # the ring buffer is reused two calls later; the graph may keep this value longer
     if ctx.world >= _RS_AG_FROM_WORLD and M % ctx.world == 0:
         # every tile is added into the shard of the rank that owns its rows, then the shards are gathered
         shard = ctx.arena.ring((M // ctx.world, N), a0.dtype)

@@ -78,21 +78,49 @@ def main():
     bf = torch.bfloat16
 
     def gemm_row(name, M, N, K, a_t=False, b_t=False, batch=1):
+        """Device time of one launch, from a replayed graph of back-to-back launches that walk round-robin through
+        enough operand sets to exceed L2 (so every launch streams its operands from HBM, as inside a training step, and
+        the host launch path of a short kernel is not in the number). Both tcgen05 kernels and cuBLAS on every shape."""
         if not want(name):
             return
-        a = torch.randn((batch, K, M) if a_t else (batch, M, K), device="cuda", dtype=bf)
-        b = torch.randn((batch, N, K) if b_t else (batch, K, N), device="cuda", dtype=bf)
-        av = a.transpose(-1, -2) if a_t else a
-        bv = b.transpose(-1, -2) if b_t else b
-        if batch == 1:
-            av, bv = av[0], bv[0]
-        ours = time_ms(lambda: nat.gemm(av, bv), iters=args.iters)
-        lib = time_ms(lambda: torch.matmul(av, bv), iters=args.iters) if args.only is None else ours
+        per_set = 2 * batch * (M * K + K * N + M * N)
+        n_sets = max(1, min(8, -(-300_000_000 // per_set)))
+        sets = []
+        for _ in range(n_sets):
+            a = torch.randn((batch, K, M) if a_t else (batch, M, K), device="cuda", dtype=bf)
+            b = torch.randn((batch, N, K) if b_t else (batch, K, N), device="cuda", dtype=bf)
+            av = a.transpose(-1, -2) if a_t else a
+            bv = b.transpose(-1, -2) if b_t else b
+            if batch == 1:
+                av, bv = av[0], bv[0]
+            sets.append((av, bv, torch.empty((batch, M, N) if batch > 1 else (M, N), device="cuda", dtype=bf)))
+        reps = max(n_sets, 24 // n_sets * n_sets)
+
+        def rotating(fn):
+            state = {"i": 0}
+
+            def call():
+                av, bv, out = sets[state["i"] % n_sets]
+                state["i"] += 1
+                return fn(av, bv, out)
+
+            return call
+
         fl = 2.0 * M * N * K * batch
-        tag = " [CTA pairs]" if nat._GEMM_CTA_PAIRS and N > 128 else ""
-        rows.append(dict(kernel=name + tag, shape=f"{batch}x{M}x{N}x{K}", ms=ours, tflops=fl / ours / 1e9,
-                         frac_of_peak=fl / ours / 1e9 / peaks["bf16_tflops"], lib_ms=lib, lib_tflops=fl / lib / 1e9,
-                         vs_lib=lib / ours))
+        lib = graph_time_ms(rotating(lambda av, bv, out: torch.matmul(av, bv, out=out)), reps=reps)
+        saved = nat._GEMM_CTA_PAIRS
+        try:
+            for pairs in (True, False):
+                nat._GEMM_CTA_PAIRS = pairs
+                if pairs and N <= 128:
+                    continue
+                ours = graph_time_ms(rotating(lambda av, bv, out: nat.gemm(av, bv, out=out)), reps=reps)
+                rows.append(dict(kernel=name + (" [CTA pairs]" if pairs else " [single CTA]"),
+                                 shape=f"{batch}x{M}x{N}x{K}", ms=ours, tflops=fl / ours / 1e9,
+                                 frac_of_peak=fl / ours / 1e9 / peaks["bf16_tflops"], lib_ms=lib,
+                                 lib_tflops=fl / lib / 1e9, vs_lib=lib / ours))
+        finally:
+            nat._GEMM_CTA_PAIRS = saved
 
     gemm_row("gemm fwd qkv", 2048, 12288, 4096)
     gemm_row("gemm fwd fc_in", 2048, 16384, 4096)
@@ -108,6 +136,8 @@ def main():
     gemm_row("gemm tp4 fwd out", 2048, 4096, 1024)
     gemm_row("gemm tp4 fwd fc_in", 2048, 4096, 4096)
     gemm_row("gemm tp4 wgrad fc_in (A,B MN-major)", 4096, 4096, 2048, a_t=True)
+    gemm_row("gemm tp4 dgrad out (B K-major)", 2048, 1024, 4096, b_t=True)
+    gemm_row("gemm tp4 wgrad out (A,B MN-major)", 1024, 4096, 2048, a_t=True)
 
     def attention_row(name, S, H, D):
         """Causal attention forward of one GPT-J micro-batch: the default path (scores GEMM with causal tile skipping,
@@ -119,22 +149,32 @@ def main():
         sin = torch.zeros(1, S, 1, device="cuda", dtype=bf)
         scale = D ** -0.5
         fl = 2.0 * 2 * S * S * D * H / 2  # two products, half of each masked
-        opt_in, nat._FLASH_ATTENTION = nat._FLASH_ATTENTION, False
+        saved, nat._FLASH_ATTENTION = nat._FLASH_ATTENTION, "0"
         try:
-            default = time_ms(lambda: nat.attention_qkv_cuda(qkv, sin, sin, S, H, D, 0, True, scale, True),
-                              iters=args.iters)
+            default = graph_time_ms(lambda: nat.attention_qkv_cuda(qkv, sin, sin, S, H, D, 0, True, scale, True), reps=8)
         finally:
-            nat._FLASH_ATTENTION = opt_in
+            nat._FLASH_ATTENTION = saved
         rows.append(dict(kernel=name + " (GEMM + softmax + GEMM)", shape=f"{H}x{S}x{S}x{D}", ms=default,
                          tflops=fl / default / 1e9, frac_of_peak=fl / default / 1e9 / peaks["bf16_tflops"],
-                         lib_ms=default, lib_tflops=fl / default / 1e9, vs_lib=1.0, lib_name="default path"))
-        if opt_in:
-            one = time_ms(lambda: nat.flash_attention_fwd(qkv, 0, hd, 2 * hd, 1, S, H, D, scale, True), iters=args.iters)
-            rows.append(dict(kernel=name + " (single kernel)", shape=f"{H}x{S}x{S}x{D}", ms=one, tflops=fl / one / 1e9,
-                             frac_of_peak=fl / one / 1e9 / peaks["bf16_tflops"], lib_ms=default,
-                             lib_tflops=fl / default / 1e9, vs_lib=default / one, lib_name="default path"))
+                         lib_ms=default, lib_tflops=fl / default / 1e9, vs_lib=1.0, lib_name="GEMM path"))
+        one = graph_time_ms(lambda: nat.flash_attention_fwd(qkv, 0, hd, 2 * hd, 1, S, H, D, scale, True), reps=8)
+        rows.append(dict(kernel=name + " (single kernel)", shape=f"{H}x{S}x{S}x{D}", ms=one, tflops=fl / one / 1e9,
+                         frac_of_peak=fl / one / 1e9 / peaks["bf16_tflops"], lib_ms=default,
+                         lib_tflops=fl / default / 1e9, vs_lib=default / one, lib_name="GEMM path"))
+        # fwd + bwd of the op as the training step runs it (forward as dispatched by default, backward GEMM-based)
+        do = torch.randn(S, hd, device="cuda", dtype=bf)
+
+        def fwd_bwd():
+            out, rot, lse = nat.attention_qkv_cuda(qkv, sin, sin, S, H, D, 0, True, scale, False)
+            return nat.attention_qkv_grad_cuda(rot, lse, do, sin, sin, S, H, D, 0, True, scale)
+
+        both = graph_time_ms(fwd_bwd, reps=4)
+        rows.append(dict(kernel=name.replace("fwd", "fwd+bwd") + " (as dispatched)", shape=f"{H}x{S}x{S}x{D}", ms=both,
+                         tflops=3.5 * fl / both / 1e9, frac_of_peak=3.5 * fl / both / 1e9 / peaks["bf16_tflops"],
+                         lib_ms=both, lib_tflops=3.5 * fl / both / 1e9, vs_lib=1.0, lib_name="itself"))
 
     attention_row("attention fwd causal gptj", 2048, 16, 256)
+    attention_row("attention fwd causal gptj tp4", 2048, 4, 256)
 
     def mem_row(name, fn, nbytes):
         if not want(name):

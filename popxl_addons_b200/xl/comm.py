@@ -180,12 +180,21 @@ class DistComm:
         return t
 
     def flush_p2p(self):
-        """Issue all queued sends and receives as one batch (concurrent, so their order between ranks cannot
-        deadlock) and order them before whatever this rank launches next."""
+        """Issue all queued sends and receives as one batch (concurrent, so their order between ranks cannot deadlock).
+        They run on the communication library's own stream: a received tensor is joined right before the first op that
+        reads it (`pending`, as for asynchronous all-reduces), a send is joined at the end of the loop iteration or run
+        (`wait_all`), so compute that does not depend on a transfer is not held up by it."""
         if self._p2p:
             ops, self._p2p = self._p2p, []
-            for w in self.dist.batch_isend_irecv(ops):
-                w.wait()
+            works = self.dist.batch_isend_irecv(ops)
+            if len(works) == len(ops):
+                for w, o in zip(works, ops):
+                    self.pending[id(o.tensor)] = (w, o.tensor)
+            else:  # the batch came back as one coalesced work item (NCCL): every tensor of the batch waits on it
+                for o in ops:
+                    self.pending[id(o.tensor)] = (works[0], o.tensor)
+                for w in works[1:]:
+                    self.pending[id(w)] = (w, None)
 
     def reduce_scatter(self, vals, grouping, op):
         pg, members = self.group_for(grouping)

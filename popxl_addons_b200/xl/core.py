@@ -722,6 +722,8 @@ class Options:
 
     native_kernels: bool = True        # run the sm_100a kernels on CUDA sessions (False: torch reference everywhere)
     cuda_graphs: bool = True           # capture `repeat(..., cuda_graph=True)` bodies and replay them
+    capture_loops: bool = True         # also capture every other `repeat` body (>= 3 iterations) that holds no op which
+                                       # reads a device value on the host; a body whose capture fails runs eagerly
     profile_ops: bool = False          # time every op (CUDA events / perf_counter) into `Session.profile`
     nvtx: bool = False                 # NVTX range per op, named `<graph>/<op>`
     collective_timeout_s: float = 600.0  # process-group timeout: a collective that waits longer ends with an error

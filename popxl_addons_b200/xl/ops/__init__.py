@@ -959,17 +959,32 @@ def onehot(t: Tensor, num_classes: int, values=None, axis: int = -1, dtype=None)
 # ---- dynamic slice / update (stash ring buffers) -------------------------------------------------------------
 
 
+def _dyn_positions(index, size):
+    """`index + [0, size)` as an int64 vector on the index's device: the slice is taken on the device, so a stash ring
+    inside a captured loop needs no host read."""
+    return index.reshape(-1)[:1].to(torch.int64) + torch.arange(size, device=index.device)
+
+
 def _dyn_slice_ref(t, index, axes, sizes):
     assert len(axes) == 1
-    i = int(index.reshape(-1)[0].item()) if index.device.type != "meta" else 0
-    return t.narrow(axes[0], i, sizes[0]).clone()
+    if index.device.type == "meta":
+        return t.narrow(axes[0], 0, sizes[0]).clone()
+    if index.device.type == "cpu":
+        i = int(index.reshape(-1)[0])
+        return t.narrow(axes[0], i, sizes[0]).clone()
+    pos = _dyn_positions(index, sizes[0]).clamp(0, t.shape[axes[0]] - 1)
+    return t.index_select(axes[0], pos)
 
 
 def _dyn_update_ref(t, index, update, axes, sizes):
     if t.device.type == "meta":
         return t
-    i = int(index.reshape(-1)[0].item())
-    t.narrow(axes[0], i, sizes[0]).copy_(update)
+    if index.device.type == "cpu":
+        i = int(index.reshape(-1)[0])
+        t.narrow(axes[0], i, sizes[0]).copy_(update)
+        return t
+    pos = _dyn_positions(index, sizes[0]).clamp(0, t.shape[axes[0]] - 1)
+    t.index_copy_(axes[0], pos, update.reshape(*t.shape[:axes[0]], sizes[0], *t.shape[axes[0] + 1:]))
     return t
 
 

@@ -93,6 +93,12 @@ class Session:
         # timestamps on CPU); summarised by `profile_summary()`
         self.profile: Optional[list] = [] if ir.options.profile_ops else None
         self._nvtx = bool(ir.options.nvtx) and self.device.type == "cuda"
+        # ops recorded under `io_tiles()` run on a second stream (loads, stores and exchanges that overlap the compute
+        # stream); values cross between the streams through events
+        self._io_stream = (torch.cuda.Stream(self.device) if self.device.type == "cuda"
+                           and os.environ.get("XL_IO_STREAM", "1") != "0" else None)
+        self._io_ready: Dict[int, tuple] = {}  # id(tensor) -> (event recorded on the IO stream, tensor)
+        self._uncapturable: set = set()        # loops whose capture failed once: they run eagerly from then on
         self._init_state()
 
     # ------------------------------------------------------------------------------------------------------
@@ -426,24 +432,38 @@ class Session:
     def _index(idx: torch.Tensor) -> int:
         return int(idx.reshape(-1)[0].item())
 
+    def _row_index(self, rb: RemoteBuffer, idx: torch.Tensor):
+        """Row selector of a slab access. Slabs in device memory are indexed on the device (no host read, so the access
+        can sit in a captured loop): a CUDA index is clamped into range, since an out-of-range one cannot be reported
+        without a synchronisation; on the CPU backend it is checked. Slabs in pinned host memory need the index on the
+        host."""
+        if rb.location == "host" or idx.device.type == "cpu":
+            i = self._index(idx)
+            if not 0 <= i < rb.entries:
+                raise IndexError(f"remote buffer index {i} out of range for {rb}")
+            return i
+        return idx.reshape(-1)[:1].to(torch.int64).clamp(0, rb.entries - 1)
+
     def remote_load(self, rb: RemoteBuffer, index: List[torch.Tensor]) -> List[torch.Tensor]:
         slabs = self._alloc_buffer(rb)
         out = []
         for r in range(self.num_local):
-            i = self._index(index[r])
-            if not 0 <= i < rb.entries:
-                raise IndexError(f"remote_load index {i} out of range for {rb}")
-            out.append(slabs[r][i].to(self.device, non_blocking=True).clone() if rb.location == "host"
-                       else slabs[r][i].clone())
+            i = self._row_index(rb, index[r])
+            if isinstance(i, int):
+                out.append(slabs[r][i].to(self.device, non_blocking=True).clone() if rb.location == "host"
+                           else slabs[r][i].clone())
+            else:
+                out.append(slabs[r].index_select(0, i).reshape(rb.tensor_shape))
         return out
 
     def remote_store(self, rb: RemoteBuffer, index: List[torch.Tensor], vals: List[torch.Tensor]):
         slabs = self._alloc_buffer(rb)
         for r in range(self.num_local):
-            i = self._index(index[r])
-            if not 0 <= i < rb.entries:
-                raise IndexError(f"remote_store index {i} out of range for {rb}")
-            slabs[r][i].copy_(vals[r].reshape(rb.tensor_shape), non_blocking=True)
+            i = self._row_index(rb, index[r])
+            if isinstance(i, int):
+                slabs[r][i].copy_(vals[r].reshape(rb.tensor_shape), non_blocking=True)
+            else:
+                slabs[r].index_copy_(0, i, vals[r].reshape(1, *rb.tensor_shape))
 
     def device_copy(self, vals, op):
         """Stage-boundary copy. One process per device slot: the source slot queues a send, the destination slot a
@@ -606,15 +626,34 @@ class Session:
                 if self._effective_device(op, frame) != self.slot:
                     continue
                 self.comm.flush_p2p()  # received tensors may be read from here on
+            control = od.name in ("call", "repeat", "conditional")
             pending = self.comm.pending
-            if pending and od.name not in ("call", "repeat", "conditional"):
-                # an all-reduce still in flight is joined right before the first op that reads its result
+            if pending and not control:
+                # a collective or receive still in flight is joined right before the first op that reads its result
                 for t in op.inputs:
                     for x in env.get(t) or ():
                         entry = pending.pop(id(x), None)
                         if entry is not None:
                             entry[0].wait()
-            timed = self.profile is not None and od.name not in ("call", "repeat", "conditional")
+            on_io = self._io_stream is not None and op.tile_set == "io" and not control
+            io_ctx = None
+            if on_io:
+                compute = torch.cuda.current_stream(self.device)
+                self._io_stream.wait_stream(compute)  # everything queued on the compute stream so far is visible
+                for t in op.inputs:
+                    for x in env.get(t) or ():
+                        if isinstance(x, torch.Tensor) and x.is_cuda:
+                            x.record_stream(self._io_stream)
+                io_ctx = torch.cuda.stream(self._io_stream)
+                io_ctx.__enter__()
+            elif self._io_ready and not control:
+                # a value produced on the IO stream is awaited by the compute stream at its first reader
+                for t in op.inputs:
+                    for x in env.get(t) or ():
+                        entry = self._io_ready.pop(id(x), None)
+                        if entry is not None:
+                            torch.cuda.current_stream(self.device).wait_event(entry[0])
+            timed = self.profile is not None and not control
             if timed:
                 t_start = self._now()
             if self._nvtx:
@@ -645,10 +684,27 @@ class Session:
             if self._nvtx:
                 torch.cuda.nvtx.range_pop()
             if timed:
-                self.profile.append((graph.name, od.name, t_start, self._now()))
+                self.profile.append((graph.name, od.name + (" [io]" if on_io else ""), t_start, self._now()))
+            if on_io:
+                ev = torch.cuda.Event()
+                ev.record(self._io_stream)
+                io_ctx.__exit__(None, None, None)
+                for t in op.outputs:
+                    for x in env.get(t) or ():
+                        if isinstance(x, torch.Tensor) and x.is_cuda:
+                            x.record_stream(compute)
+                            self._io_ready[id(x)] = (ev, x)  # holding `x` keeps its id unique while the entry exists
             self._free_dead(frees, i, env)
         if staged:
             self.comm.flush_p2p()
+
+    def _join_streams(self):
+        """The compute stream waits for everything queued on the IO stream and for every collective in flight (end of a
+        run, end of a loop iteration, end of a captured loop body)."""
+        self.comm.wait_all()
+        if self._io_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self._io_stream)
+            self._io_ready.clear()
 
     @staticmethod
     def _free_dead(frees, i, env):
@@ -662,30 +718,66 @@ class Session:
         self._exec_ops(graph, env)
         return [self._value(t, env) for t in graph._outputs]
 
+    # ops that read a device value on the host, or decide on the host what runs: a loop body holding one is not captured
+    _HOST_SYNC_OPS = frozenset({"conditional", "print_tensor", "dropout", "random_uniform", "random_normal",
+                                "shaped_dropout", "timestamp", "fp8_mse_scale", "histogram"})
+
+    def _capture_safe(self, graph: Graph, _seen=None) -> bool:
+        """Whether a loop body can be captured into a CUDA graph without being told so: nothing in it (or in the graphs
+        it calls) reads a device value on the host or touches a slab in pinned host memory."""
+        seen = _seen if _seen is not None else set()
+        if id(graph) in seen:
+            return True
+        seen.add(id(graph))
+        for o in graph.ops:
+            name = o.opdef.name
+            if name in self._HOST_SYNC_OPS:
+                return False
+            if name in ("remote_load", "remote_store") and o.attrs["buffer"].location == "host":
+                return False
+            for key in ("graph", "then_graph", "else_graph"):
+                callee = o.attrs.get(key)
+                if callee is not None and hasattr(callee, "ops") and not self._capture_safe(callee, seen):
+                    return False
+        return True
+
     def run_repeat(self, op, graph: Graph, vals: List[List[torch.Tensor]], env):
         n_out = len(graph._outputs)
         count = op.attrs["count"]
-        if (op.attrs.get("cuda_graph") and self.device.type == "cuda" and n_out == 0 and self.num_local == 1
-                and self.ir.options.cuda_graphs and self.profile is None):
-            self._run_repeat_captured(op, graph, vals, count)
-            return
+        want = op.attrs.get("cuda_graph") or (self.ir.options.capture_loops and count >= 3
+                                              and self._capture_safe(graph))
+        if (want and self.device.type == "cuda" and self.num_local == 1 and self.ir.options.cuda_graphs
+                and self.profile is None and op.uid not in self._uncapturable and not self._capturing):
+            outs = self._run_repeat_captured(op, graph, vals, count)
+            if outs is not None:
+                for t, v in zip(op.outputs, outs):
+                    env[t] = v
+                return
+            vals = self._repeat_resume  # the iterations that did run eagerly before the capture was given up
+            count = count - self._repeat_done
         outs = vals[:n_out]
         for _ in range(count):
             outs = self.run_graph(graph, vals)
-            self.comm.wait_all()
+            self._join_streams()
             vals = list(outs) + list(vals[n_out:])
         for t, v in zip(op.outputs, outs):
             env[t] = v
 
     # -- CUDA-graph replay of a loop body -----------------------------------------------------------------------
+    _capturing = False
+
     def _run_repeat_captured(self, op, graph: Graph, vals, count: int):
-        """Loop body without loop-carried values, host syncs or shape changes: the first iteration ever runs eagerly
-        (lazy initialisation: arenas, workspaces, library handles), the second is captured into a CUDA graph, all
-        later ones (in this and every following `run`) replay it. Host-stream reads inside the body go through a
-        static staging tensor that is refreshed before each replay; host-stream writes are copied out after it."""
-        # an all-reduce issued outside the loop may still be in flight: its join must not land inside the capture (a wait
+        """Loop body without host syncs or shape changes: the first iteration ever runs eagerly (lazy initialisation:
+        arenas, workspaces, library handles), the second is captured into a CUDA graph, all later ones (in this and
+        every following `run`) replay it. Loop-carried values live in static buffers: the captured body reads them and
+        copies its outputs back into them, so a replay continues where the previous one stopped. Host-stream reads
+        inside the body go through a static staging tensor that is refreshed before each replay; host-stream writes are
+        copied out after it. Returns the outputs of the last iteration, or None if the body could not be captured (the
+        loop then continues eagerly from `self._repeat_resume`)."""
+        # a collective issued outside the loop may still be in flight: its join must not land inside the capture (a wait
         # on an event recorded outside a capture is not part of the replayed graph)
-        self.comm.wait_all()
+        self._join_streams()
+        n_out = len(graph._outputs)
         state = self._captured.get(op.uid)
         it = 0
         debug = os.environ.get("XL_DEBUG_CAPTURE") == "1"
@@ -696,18 +788,31 @@ class Session:
                 print(f"[capture rank {os.environ.get('RANK', '0')}] {graph.name}: {msg}", file=sys.stderr, flush=True)
 
         if state is None:
-            self.run_graph(graph, vals)  # eager warm-up iteration
-            self.comm.wait_all()
+            outs = self.run_graph(graph, vals)  # eager warm-up iteration
+            self._join_streams()
             note("eager iteration done")
             it = 1
+            vals = list(outs[:n_out]) + list(vals[n_out:])
             if count == 1:
-                return
-            state = self._capture(op, graph, vals)
+                return outs
+            carried = [[v[0].clone()] for v in vals[:n_out]]
+            try:
+                state = self._capture(op, graph, vals, carried)
+            except Exception as e:  # an op that cannot be captured after all: remember it and go on eagerly
+                if op.attrs.get("cuda_graph"):
+                    raise
+                note(f"capture given up: {type(e).__name__}: {e}")
+                self._uncapturable.add(op.uid)
+                self._repeat_resume, self._repeat_done = vals, 1
+                return None
             note("captured and replayed once")
             self._captured[op.uid] = state
             self._after_replay(state)
             it = 2
-        ptrs = tuple(v[0].data_ptr() for v in vals)
+        else:
+            for buf, v in zip(state["carried"], vals[:n_out]):
+                buf[0].copy_(v[0])
+        ptrs = tuple(v[0].data_ptr() for v in vals[n_out:])
         if ptrs != state["ptrs"]:
             raise RuntimeError("inputs of a CUDA-graph-captured loop changed address between runs")
         from ..ops import native as _native
@@ -718,6 +823,7 @@ class Session:
             state["graph"].replay()
             _native.count_replay(state["kernels"])
             self._after_replay(state)
+        return [[buf[0].clone()] for buf in state["carried"]]
 
     def _next_host_item(self, stream):
         i = self._cursor[stream]
@@ -727,14 +833,29 @@ class Session:
         self._cursor[stream] = i + 1
         return data[i, 0]
 
-    def _capture(self, op, graph: Graph, vals):
+    def _host_loads_of(self, graph: Graph, found=None, _seen=None):
+        """Host-to-device streams read anywhere inside a loop body (also in the graphs it calls)."""
+        found = found if found is not None else []
+        seen = _seen if _seen is not None else set()
+        if id(graph) in seen:
+            return found
+        seen.add(id(graph))
+        for o in graph.ops:
+            if o.opdef.name == "host_load" and o.attrs["stream"] not in found:
+                found.append(o.attrs["stream"])
+            callee = o.attrs.get("graph")
+            if callee is not None and hasattr(callee, "ops"):
+                self._host_loads_of(callee, found, seen)
+        return found
+
+    def _capture(self, op, graph: Graph, vals, carried):
         from ..ops import native as _native
 
+        n_out = len(carried)
         static_in = {}
-        for o in graph.ops:
-            if o.opdef.name == "host_load":
-                st = o.attrs["stream"]
-                static_in[st] = torch.empty_like(self._inputs[st][0, 0])
+        cursors = dict(self._cursor)
+        for st in self._host_loads_of(graph):
+            static_in[st] = torch.empty_like(self._inputs[st][0, 0])
         for stream, static in static_in.items():
             static.copy_(self._next_host_item(stream), non_blocking=True)
         self._capture_inputs = static_in
@@ -743,21 +864,30 @@ class Session:
         _native._RECORDING.append(kernels)
         g = torch.cuda.CUDAGraph()
         torch.cuda.synchronize(self.device)
+        ok = False
+        self._capturing = True
         try:
             with torch.cuda.graph(g, capture_error_mode="thread_local"):
-                self.run_graph(graph, vals)
-                self.comm.wait_all()  # every stream forked inside the body joins before the capture ends
+                outs = self.run_graph(graph, carried + list(vals[n_out:]))
+                for buf, o in zip(carried, outs[:n_out]):
+                    buf[0].copy_(o[0])
+                self._join_streams()  # every stream forked inside the body joins before the capture ends
+            ok = True
         finally:
+            self._capturing = False
             _native._RECORDING.pop()
-            outs = self._capture_outputs
+            outs_rec = self._capture_outputs
             self._capture_inputs, self._capture_outputs = None, None
+            if not ok:
+                self._cursor = cursors  # the failed capture executed nothing: its host items are still unread
+                self._io_ready.clear()
         if os.environ.get("XL_DEBUG_CAPTURE") == "1":
             print(f"[capture rank {os.environ.get('RANK', '0')}] {graph.name}: capture ended, {len(kernels)} own kernels",
                   file=sys.stderr, flush=True)
         g.replay()  # capture records but does not execute
         _native.count_replay(kernels)
-        return {"graph": g, "static_in": static_in, "outputs": outs, "kernels": kernels,
-                "ptrs": tuple(v[0].data_ptr() for v in vals)}
+        return {"graph": g, "static_in": static_in, "outputs": outs_rec, "kernels": kernels, "carried": carried,
+                "ptrs": tuple(v[0].data_ptr() for v in vals[n_out:])}
 
     def _after_replay(self, state):
         for stream, tensors in state["outputs"]:
@@ -776,7 +906,7 @@ class Session:
         env: Dict[Tensor, List[torch.Tensor]] = {}
         with torch.no_grad():
             self._exec_ops(main, env)
-            self.comm.wait_all()
+            self._join_streams()
         out = self._collect_outputs(fetch)
         if self.use_native and fetch:
             from ..ops import native as _native

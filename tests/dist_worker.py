@@ -31,6 +31,7 @@ def main():
     ap.add_argument("--gemm-n", dest="n", type=int, default=4096)
     ap.add_argument("--gemm-k", dest="k", type=int, default=4096)
     ap.add_argument("--n-copy", type=int, default=16)
+    ap.add_argument("--n-red", type=int, default=8)
     ap.add_argument("--slots", type=int, default=2)
     ap.add_argument("--ckpt", default="")
     ap.add_argument("--sp", type=int, default=0)
@@ -46,9 +47,13 @@ def main():
         from popxl_addons_b200.models.gptj import GPTJConfig
         from popxl_addons_b200.models.trainer import DecoderTrainer
 
-        cfg = (GPTJConfig.tiny(dtype=args.dtype, tp=args.tp, dp=args.dp) if args.big
-               else DecoderConfig.tiny("gptj", dtype=args.dtype, tp=args.tp, dp=args.dp))
+        cfg = (GPTJConfig.tiny(dtype=args.dtype, tp=args.tp, dp=args.dp, **({"seq_len": 512} if args.big == 2 else {}))
+               if args.big else DecoderConfig.tiny("gptj", dtype=args.dtype, tp=args.tp, dp=args.dp))
         cfg.sequence_parallel = bool(args.sp)
+        if args.device == "cuda":
+            from popxl_addons_b200.ops import native
+
+            native.STRICT[0] = True  # a hot op that runs its torch implementation on the GPU is an error
         trainer = DecoderTrainer(cfg, micro_batches=2, device=args.device, lr=1e-2,
                                  fused_collectives=bool(args.fused))
         losses = []
@@ -67,6 +72,7 @@ def main():
             from popxl_addons_b200.ops import native
 
             extra["kernels"] = native.LAUNCHES["by_kernel"]
+            extra["fallbacks"] = dict(native.FALLBACKS)
         if rank == 0:
             print(json.dumps({"losses": losses, "w_sum": float(np.abs(w).sum()), "fused_pairs":
                               trainer.fused_gemm_collectives, **extra}))
@@ -186,6 +192,52 @@ def main():
         result["ar_err"] = float((got.float() - full).abs().max() / full.abs().max())
         result["ar_fused_ms"] = timed(fused_ar)
         result["ar_nccl_ms"] = timed(nccl_ar)
+        # GEMM + all-reduce by pulling: partial tiles stay local, NVSwitch adds them on the way into the owner of the rows
+        got = fused.gemm_all_reduce_pull(ctx, [(a, w)], n_red=args.n_red)
+        assert got is not NotImplemented
+        got = got.clone()
+        torch.cuda.synchronize()
+        result["ar_pull_err"] = float((got.float() - full).abs().max() / full.abs().max())
+        result["ar_pull_ms"] = timed(lambda: fused.gemm_all_reduce_pull(ctx, [(a, w)], n_red=args.n_red))
+        # two operand pairs contracted into one accumulator: all_reduce(a @ w + a2 @ w2), K2 = K / 4 (a block's attention
+        # and feed-forward output projections), and the transposed-weight form of the backward pass
+        K2 = max(64, K // 4)
+        a2 = (torch.randn(M, K2, device=dev) * 0.1).bfloat16()
+        w2 = (torch.randn(K2, N, device=dev) * 0.1).bfloat16()
+        full2 = a.float() @ w.float() + a2.float() @ w2.float()
+        dist.all_reduce(full2)
+        got = fused.gemm_all_reduce_pull(ctx, [(a, w), (a2, w2)], n_red=args.n_red)
+        assert got is not NotImplemented
+        got = got.clone()
+        torch.cuda.synchronize()
+        result["ar_pull2_err"] = float((got.float() - full2).abs().max() / full2.abs().max())
+        result["ar_pull2_ms"] = timed(lambda: fused.gemm_all_reduce_pull(ctx, [(a, w), (a2, w2)], n_red=args.n_red))
+        wt, w2t = w.t().contiguous(), w2.t().contiguous()  # stored (N, K): K-major right operands, as in a data gradient
+        got = fused.gemm_all_reduce_pull(ctx, [(a, wt.t()), (a2, w2t.t())], n_red=args.n_red)
+        assert got is not NotImplemented
+        got = got.clone()
+        torch.cuda.synchronize()
+        result["ar_pull2_t_err"] = float((got.float() - full2).abs().max() / full2.abs().max())
+        for _ in range(20):  # many launches back to back: the flag words and the work queue must come back to zero
+            got = fused.gemm_all_reduce_pull(ctx, [(a, w), (a2, w2)], n_red=args.n_red)
+        got = got.clone()
+        torch.cuda.synchronize()
+        result["ar_pull2_repeat_err"] = float((got.float() - full2).abs().max() / full2.abs().max())
+
+        def nccl_ar2():
+            y = native.gemm(a, w)
+            native.gemm(a2, w2, out=y, accumulate=1)
+            dist.all_reduce(y)
+            return y
+
+        def cublas_ar2():
+            y = torch.addmm(a @ w, a2, w2)
+            dist.all_reduce(y)
+            return y
+
+        result["ar_nccl2_ms"] = timed(nccl_ar2)
+        result["ar_cublas_nccl2_ms"] = timed(cublas_ar2)
+        result["gemm2_ms"] = timed(lambda: native.gemm(a2, w2, out=native.gemm(a, w), accumulate=1))
         ybuf = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
         result["nccl_all_reduce_only_ms"] = timed(lambda: dist.all_reduce(ybuf))
         small = torch.randn(2048, device=dev)

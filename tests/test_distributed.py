@@ -39,7 +39,8 @@ def simulated(tp, dp, dtype, steps=3, big=False, fused=True):
     from dist_worker import global_tokens
 
     dec._SEED[0] = 0
-    cfg = (GPTJConfig.tiny(dtype=dtype, tp=tp, dp=dp) if big else dec.DecoderConfig.tiny("gptj", dtype=dtype, tp=tp, dp=dp))
+    cfg = (GPTJConfig.tiny(dtype=dtype, tp=tp, dp=dp, **({"seq_len": 512} if big == 2 else {})) if big
+           else dec.DecoderConfig.tiny("gptj", dtype=dtype, tp=tp, dp=dp))
     t = DecoderTrainer(cfg, micro_batches=2, device="cpu", lr=1e-2, fused_collectives=fused)
     return [t.step(global_tokens(cfg, 2, seed=s)) for s in range(steps)]
 
@@ -113,21 +114,35 @@ def test_supervisor_restarts_from_the_latest_checkpoint(tmp_path):
     assert latest_checkpoint(str(tmp_path / "nothing")) is None
 
 
+def _need_gpus(n):
+    import torch
+
+    have = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    if have < n:
+        pytest.skip(f"needs {n} CUDA devices, {have} present")
+
+
 @pytest.mark.gpu
 @pytest.mark.multigpu
-@pytest.mark.parametrize("tp,dp", [(1, 2), (2, 1)])
+@pytest.mark.parametrize("tp,dp", [(1, 2), (2, 1), (2, 2), (4, 1), (4, 2)])
 def test_gpu_ranks_fused_collectives(tp, dp):
-    """bf16 on 2 GPUs: the fused NVLink kernels must have run and training must track the fp32-accumulating CPU
-    simulation of the same program."""
-    ref = simulated(tp, dp, "bfloat16", big=True)
-    got = launch(2, "--device", "cuda", "--tp", str(tp), "--dp", str(dp), "--dtype", "bfloat16", "--big", "1")
+    """bf16 on tp x dp GPUs (2, 4 or 8): the fused NVLink kernels must have run and two optimizer steps must track the
+    fp32-accumulating CPU simulation of the same program."""
+    _need_gpus(tp * dp)
+    big = 2 if tp > 1 else 1  # 512 tokens per micro-batch: whole 128-row blocks for every rank of the TP group
+    ref = simulated(tp, dp, "bfloat16", big=big)
+    got = launch(tp * dp, "--device", "cuda", "--tp", str(tp), "--dp", str(dp), "--dtype", "bfloat16", "--big", str(big),
+                 timeout=600)
     np.testing.assert_allclose(got["losses"], ref, rtol=3e-2)
     kernels = got["kernels"]
-    assert "gemm_tcgen05" in kernels
+    assert "gemm_tcgen05" in kernels or "gemm2cta_tcgen05" in kernels
     if dp > 1:
         assert kernels.get("rts_adam", 0) > 0 and kernels.get("symm_barrier", 0) > 0
     if tp > 1:
         assert got["fused_pairs"] > 0
+        assert kernels.get("gemm_ar_pull_tcgen05", 0) > 0, kernels  # the TP all-reduce ran inside the GEMM kernel
+        assert kernels.get("ce_shard_stats", 0) > 0 and kernels.get("ce_shard_grad_loss", 0) > 0, kernels
+        assert not got.get("fallbacks"), got.get("fallbacks")
 
 
 @pytest.mark.gpu
@@ -138,13 +153,21 @@ def test_gpu_rank_collectives():
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
-def test_gpu_gemm_reduce_scatter_and_all_gather_gemm():
-    """The tcgen05 GEMM with the reduce-scatter epilogue (`red.add` into the owner's shard) and with the all-gather
-    prologue (copy CTAs pulling peer row blocks) against NCCL + fp32 matmul on the same data."""
-    res = launch(2, "--mode", "fusedgemm", "--gemm-m", "1024", "--gemm-n", "1024", "--gemm-k", "1024", timeout=300,
+@pytest.mark.parametrize("nproc,m,n,k", [(2, 1024, 1024, 1024), (2, 512, 2304, 320), (4, 1024, 1024, 1024),
+                                         (4, 2048, 4096, 1024)])
+def test_gpu_gemm_reduce_scatter_and_all_gather_gemm(nproc, m, n, k):
+    """The tcgen05 GEMM fused with its collective, against NCCL + fp32 matmul on the same data, on 2 and 4 ranks and
+    more than one shape: the reduce-scatter epilogue (`red.add` into the owner's shard), the all-gather prologue (copy
+    CTAs pulling peer row blocks), the pushing all-reduce (`multimem.red`) and the pulling all-reduce
+    (`multimem.ld_reduce` / `multimem.st` by the owner of the rows; one and two operand pairs, both weight layouts,
+    many launches back to back)."""
+    _need_gpus(nproc)
+    res = launch(nproc, "--mode", "fusedgemm", "--gemm-m", str(m), "--gemm-n", str(n), "--gemm-k", str(k), timeout=300,
                  env={"XL_COLLECTIVE_TIMEOUT_S": "120"})
     assert res["errors"] is None
     assert res["rs_err"] < 2e-2 and res["ag_a_err"] < 2e-2 and res["ag_b_err"] < 2e-2 and res["ar_err"] < 2e-2
+    assert res["ar_pull_err"] < 2e-2 and res["ar_pull2_err"] < 2e-2 and res["ar_pull2_t_err"] < 2e-2, res
+    assert res["ar_pull2_repeat_err"] < 2e-2, res
     assert res["ag_a_gathered_ok"] and res["ag_b_gathered_ok"]
     assert res["ar_ln_err"] < 0.1  # bf16 rounding of the summed update (magnitudes ~ 4)
 

@@ -200,21 +200,38 @@ def _gemm_check(nat, a, b, **kw):
     return out
 
 
+def _gemm_tol(K, dtype=torch.bfloat16, sigma_a=1.0, sigma_b=1.0):
+    """Bound for a 16-bit result of an fp32-accumulated product of N(0, sigma) operands: the entries have standard
+    deviation sqrt(K) sigma_a sigma_b, rounding them to the output type costs half a unit in the last place (2^-9 for
+    bf16, 2^-12 for fp16) of their magnitude, and the fp32 accumulation order adds far less. Two bits of slack."""
+    ulp = 2.0 ** -7 if dtype == torch.bfloat16 else 2.0 ** -10
+    return dict(rtol=ulp, atol=ulp * math.sqrt(K) * sigma_a * sigma_b)
+
+
+@pytest.fixture(params=["cta_pairs", "single_cta"])
+def gemm_kernel(request, nat):
+    """Runs a GEMM test on both tcgen05 kernels: CTA pairs (default for plain products) and the single-CTA kernel."""
+    old = nat._GEMM_CTA_PAIRS
+    nat._GEMM_CTA_PAIRS = request.param == "cta_pairs"
+    yield request.param
+    nat._GEMM_CTA_PAIRS = old
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 128), (2048, 4096, 1024), (200, 328, 136),
                                    (16, 4096, 4096), (1000, 50400, 512)])
-def test_gemm_k_major_a_mn_major_b(nat, dtype, M, N, K):
+def test_gemm_k_major_a_mn_major_b(nat, gemm_kernel, dtype, M, N, K):
     """Forward layout: x (M,K) row-major @ w (K,N) row-major."""
     torch.manual_seed(10)
     a = torch.randn(M, K, device="cuda", dtype=dtype)
     b = torch.randn(K, N, device="cuda", dtype=dtype)
     out = _gemm_check(nat, a, b)
     ref = a.float() @ b.float()
-    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    torch.testing.assert_close(out.float(), ref, **_gemm_tol(K, dtype))
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 256), (2048, 1024, 4096), (136, 200, 328)])
-def test_gemm_all_operand_layouts(nat, M, N, K):
+def test_gemm_all_operand_layouts(nat, gemm_kernel, M, N, K):
     torch.manual_seed(11)
     dtype = torch.bfloat16
     a_km = torch.randn(M, K, device="cuda", dtype=dtype)          # K-major A
@@ -225,10 +242,10 @@ def test_gemm_all_operand_layouts(nat, M, N, K):
         for b in (b_mn, b_km):
             out = _gemm_check(nat, a, b)
             ref = a.float() @ b.float()
-            torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+            torch.testing.assert_close(out.float(), ref, **_gemm_tol(K))
 
 
-def test_gemm_batched_and_epilogues(nat):
+def test_gemm_batched_and_epilogues(nat, gemm_kernel):
     torch.manual_seed(12)
     dtype = torch.bfloat16
     q = torch.randn(6, 256, 128, device="cuda", dtype=dtype)
@@ -273,8 +290,6 @@ def test_attention_forward_backward(nat):
     nat.check_gemm_errors()
 
 
-@pytest.mark.skipif(os.environ.get("XL_FLASH_ATTENTION") != "1",
-                    reason="the single-kernel attention forward is opt-in (XL_FLASH_ATTENTION=1)")
 @pytest.mark.parametrize("B,S,H,D,causal,dtype", [(2, 256, 2, 64, True, torch.bfloat16), (1, 384, 2, 128, True, torch.float16),
                                                   (1, 512, 1, 256, True, torch.bfloat16), (1, 300, 2, 64, False, torch.bfloat16),
                                                   (2, 200, 1, 256, True, torch.bfloat16)])
@@ -297,8 +312,6 @@ def test_single_kernel_attention_forward(nat, B, S, H, D, causal, dtype):
     torch.testing.assert_close(lse, torch.logsumexp(s, -1), rtol=1e-3, atol=1e-2)
 
 
-@pytest.mark.skipif(os.environ.get("XL_GEMM_CTA_PAIRS") != "1",
-                    reason="the CTA-pair GEMM is opt-in (XL_GEMM_CTA_PAIRS=1)")
 @pytest.mark.parametrize("M,N,K,batch,ta,tb,dtype", [
     (256, 256, 64, 1, False, False, torch.bfloat16),      # one tile, one k-block
     (512, 512, 512, 1, False, False, torch.bfloat16),     # the ring wraps (8 k-blocks over 6 stages)
@@ -321,7 +334,7 @@ def test_cta_pair_gemm(nat, M, N, K, batch, ta, tb, dtype):
     assert out is not NotImplemented
     nat.check_gemm_errors()
     assert nat.LAUNCHES["by_kernel"].get("gemm2cta_tcgen05", 0) == before + 1, "the CTA-pair kernel did not run"
-    torch.testing.assert_close(out.float(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    torch.testing.assert_close(out.float(), want, **_gemm_tol(K, dtype))
     if (M, N, K) == (512, 512, 512):
         bias = torch.randn(N, device="cuda").to(dtype)
         got = nat.gemm(a, b, bias=bias, act=3, alpha=0.5, out_dtype=torch.float32)
