@@ -237,10 +237,16 @@ def _torch_train_arm(args, cfg, tp, K, W, rank, local_rank, dist_barrier, dist):
     import torch
 
     sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
-    from torch_decoder import TorchTrainer
+    if args.mode == "pipeline":
+        from torch_pipeline import TorchPipelineTrainer
 
-    tt = TorchTrainer(cfg, micro_batches=args.micro_batches, recompute=args.recompute,
-                      cuda_graph=not args.no_cuda_graphs)
+        tt = TorchPipelineTrainer(cfg, stages=min(args.stages, args.gpus), micro_batches=args.micro_batches)
+        tt.graph_note = "eager (1F1B schedule issued from Python)"
+    else:
+        from torch_decoder import TorchTrainer
+
+        tt = TorchTrainer(cfg, micro_batches=args.micro_batches, recompute=args.recompute,
+                          cuda_graph=not args.no_cuda_graphs)
 
     class _Adapter:
         tokens_per_step = tt.tokens_per_step
@@ -251,7 +257,9 @@ def _torch_train_arm(args, cfg, tp, K, W, rank, local_rank, dist_barrier, dist):
             d2h_bytes = 0
 
         def synthetic_tokens(self, seed=0):
-            g = torch.Generator().manual_seed(seed + rank // max(tp, 1))
+            # every process of one replica (its TP ranks, or its pipeline stages) sees the same tokens
+            per_replica = min(args.stages, args.gpus) if args.mode == "pipeline" else max(tp, 1)
+            g = torch.Generator().manual_seed(seed + rank // per_replica)
             return torch.randint(0, cfg.vocab_size, (args.micro_batches, 1, 1, cfg.seq_len + 1), generator=g,
                                  dtype=torch.int32).pin_memory()
 
@@ -410,7 +418,7 @@ def main():
 
     # ---- the PyTorch arm of the same step, timed first on the same GPUs (its memory is released afterwards) ----------
     baseline = None
-    run_baseline = args.impl == "ours" and not args.no_baseline and not pipeline and not args.emulate_tp \
+    run_baseline = args.impl == "ours" and not args.no_baseline and not args.emulate_tp \
         and not args.sequence_parallel
     if args.impl == "torch" or run_baseline:
         t0 = time.perf_counter()
@@ -418,7 +426,8 @@ def main():
         torch_setup_s = time.perf_counter() - t0
         dist = current_dist()
         kb = K if args.impl == "torch" else min(K, 3)
-        res = _time_steps(adapter, kb, W, barrier, local_rank, dist, e2e=True)
+        res = _time_steps(adapter, kb, W, barrier, local_rank, dist, e2e=True,
+                          pipeline_stages=stages if pipeline else 0)
         res.update(steps=kb, setup_s=torch_setup_s, tokens=adapter.tokens_per_step, graph_note=tt.graph_note)
         baseline = res
         if args.impl == "ours":
@@ -512,7 +521,7 @@ def main():
             be2e = baseline["tokens"] * baseline["steps"] / (baseline["e2e_ms"] / 1e3)
             vs = value / bval
             vs_detail = {"impl": "PyTorch + cuBLAS + flash SDPA + NCCL, same step on the same GPUs in this run "
-                                 "(baseline/torch_decoder.py)", "value": bval, "ratio": vs, "e2e_value": be2e,
+                                 + ("(baseline/torch_pipeline.py, 1F1B)" if pipeline else "(baseline/torch_decoder.py)"), "value": bval, "ratio": vs, "e2e_value": be2e,
                          "e2e_ratio": e2e_value / be2e, "steps": baseline["steps"], "warmup": W,
                          "ms_per_step": baseline["dev_ms"] / baseline["steps"], "cuda_graph": baseline["graph_note"],
                          "clocks": baseline["clocks"]}

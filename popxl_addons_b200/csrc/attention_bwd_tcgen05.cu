@@ -1,0 +1,466 @@
+// Causal softmax attention backward, first pass, in one kernel on the 5th-generation tensor cores (tcgen05) for sm_100a.
+//
+//   P  = softmax(scale * Q K^T + causal mask)          (recomputed from Q, K and the forward pass's log-sum-exp)
+//   dP = dO V^T
+//   dS = P o (dP - delta) * scale,   delta_i = sum_d dO_id O_id
+//   dQ = dS K                                           accumulated on chip over all key blocks
+//
+// One CTA owns 128 query rows of one (batch, head) and walks the key / value rows in blocks of BKV. The scores, dP and
+// the dQ accumulator never leave the chip; P and dS are written once, as 16-bit (B*H, S, S) matrices, for the two
+// remaining products of the backward pass (dV = P^T dO, dK = dS^T Q), which are plain batched GEMMs over the causal
+// half. That is the minimum of five products, against eight for a backward pass that recomputes the scores in a second,
+// key-stationary kernel: with head dimension 256 the dK and dV accumulators alone fill the 512 TMEM columns, so a
+// single kernel cannot hold them next to the score tiles.
+//
+//   warp 0      TMA producer : Q and dO tiles once, then K / V blocks into a 2-stage shared-memory ring
+//   warp 1      MMA issuer   : S_j = Q K_j^T and dP_j = dO V_j^T into one of two TMEM buffer pairs (block j+1 is issued
+//                              before dS_j is awaited, so it overlaps the element-wise work on block j), then
+//                              dQ += dS_j K_j (K_j consumed MN-major: no transpose)
+//   warps 2..5  element-wise : one thread per query row. tcgen05.ld of the score and dP rows, p = exp2(s*c - lse*log2e),
+//                              ds = p (dp - delta) scale, P and dS rows to global memory, dS as a 16-bit tile to shared
+//                              memory (two buffers) for the third product; finally dQ from TMEM to global memory.
+//
+// TMEM columns: [0, D) dQ accumulator, then two score buffers and two dP buffers of BKV columns each (512 allocated, one
+// CTA per SM). Every wait on an mbarrier is bounded: when a wait gives up the kernel records a code in `*err`, raises a
+// CTA-wide abort flag, all roles leave their loops, TMEM is released and the kernel returns normally.
+#include "tcgen05.cuh"
+
+namespace {
+
+constexpr int BLOCK_Q = 128;
+constexpr int UMMA_K = 16;
+constexpr int KV_STAGES = 2;
+constexpr int NUM_EW_WARPS = 4;
+constexpr int NUM_THREADS = 64 + 32 * NUM_EW_WARPS;
+constexpr uint32_t SPIN_LIMIT = xl_tc::MBAR_SPIN_LIMIT;
+constexpr uint32_t TMEM_COLS = 512;
+
+enum { ERR_QDO_WAIT = 31, ERR_KV_FULL_WAIT = 32, ERR_KV_EMPTY_WAIT = 33, ERR_SDP_FULL_WAIT = 34, ERR_SDP_EMPTY_WAIT = 35,
+       ERR_DS_FULL_WAIT = 36, ERR_DS_EMPTY_WAIT = 37, ERR_DQ_DONE_WAIT = 38 };
+
+struct AttnBwdParams {
+  int B, S, H, D;
+  int q_col, k_col, v_col;   // first column of head 0 of Q / K / V in the packed matrix
+  const void* out;           // forward output O (B*S x ldo), head h in columns [h*D, (h+1)*D)
+  long long ldo;
+  const void* dout;          // dO, same layout, leading dimension ld_do (read directly for delta; also behind map_do)
+  long long ld_do;
+  const float* lse;          // (B, H, S) natural-log log-sum-exp of the scaled scores, from the forward pass
+  void* P;                   // (B*H, S, S) 16-bit: probabilities, zero above the diagonal inside the blocks that are written
+  void* dS;                  // (B*H, S, S) 16-bit
+  void* dq;                  // dQ: (B*S x ld_dq) 16-bit, head h in columns [dq_col + h*D, ...)
+  long long ld_dq;
+  int dq_col;
+  float scale;
+  int causal;
+  int is_fp16;
+  int* err;
+};
+
+using namespace xl_tc;
+
+// Shared-memory matrix descriptor of a K-major operand stored without swizzle as 8-row x 16-byte core matrices:
+// `lbo` = byte distance between core matrices adjacent along K, `sbo` = between 8-row groups (layout type 0).
+__device__ __forceinline__ uint64_t make_smem_desc_noswizzle(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+// 128-byte-swizzled tile whose swizzle atoms (8 rows x 128 B) are `sbo` = 1024 bytes apart, column blocks `lbo` apart
+__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo) { return make_smem_desc(smem_addr, lbo); }
+
+template <int D, int BKV>
+struct BwdSmem {
+  static constexpr int Q_BYTES = BLOCK_Q * D * 2;       // D/64 k-blocks of (128 rows x 128 B)
+  static constexpr int K_BYTES = BKV * D * 2;           // D/64 boxes of (BKV rows x 128 B): K-major for S, MN-major for dQ
+  static constexpr int V_BYTES = BKV * D * 2;
+  static constexpr int DS_BYTES = BLOCK_Q * BKV * 2;    // BKV/8 chunk columns of 16 row groups of (8 rows x 16 B)
+  static constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
+  static constexpr int TILE_BYTES = 2 * Q_BYTES + KV_STAGES * STAGE_BYTES + 2 * DS_BYTES;
+  static constexpr int NEEDED = TILE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  // more than half of an SM's shared memory, so that two CTAs (each holding all 512 TMEM columns) never share an SM
+  static constexpr int TOTAL = NEEDED > 120 * 1024 ? NEEDED : 120 * 1024;
+};
+
+template <int D, int BKV>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    attn_bwd_dq_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                               const __grid_constant__ CUtensorMap map_kv, const AttnBwdParams p) {
+  using L = BwdSmem<D, BKV>;
+  static_assert(D % 64 == 0 && D <= 256 && BKV % 32 == 0 && BKV <= 64 && D + 4 * BKV <= (int)TMEM_COLS, "unsupported tile");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sDO = smem + L::Q_BYTES;
+  uint8_t* sKV = smem + 2 * L::Q_BYTES;
+  uint8_t* sDS = sKV + KV_STAGES * L::STAGE_BYTES;  // two buffers
+  uint64_t* bars = (uint64_t*)(smem + L::TILE_BYTES);
+  uint64_t* qdo_full = bars;               // [1]
+  uint64_t* kv_full = bars + 1;            // [KV_STAGES]
+  uint64_t* kv_empty = bars + 3;           // [KV_STAGES]
+  uint64_t* sdp_full = bars + 5;           // [2]  S and dP of a block are complete
+  uint64_t* sdp_empty = bars + 7;          // [2]  the element-wise warps have read them
+  uint64_t* ds_full = bars + 9;            // [2]  dS tile written to shared memory
+  uint64_t* ds_empty = bars + 11;          // [2]  the third product has read it
+  uint64_t* dq_done = bars + 13;           // [1]  all products complete (the accumulator is final)
+  uint32_t* tmem_base_slot = (uint32_t*)(bars + 14);
+  volatile int* abort_flag = (volatile int*)(tmem_base_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_qblocks = (p.S + BLOCK_Q - 1) / BLOCK_Q;
+  const int qb = n_qblocks - 1 - (int)blockIdx.x;  // the blocks with the most keys start first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qb * BLOCK_Q;
+  const int kv_end = p.causal ? min(p.S, q0 + BLOCK_Q) : p.S;
+  const int n_kv = (kv_end + BKV - 1) / BKV;
+  const int row0 = b * p.S;
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&sdp_full[s], 1);
+      mbar_init(&sdp_empty[s], NUM_EW_WARPS);
+      mbar_init(&ds_full[s], NUM_EW_WARPS);
+      mbar_init(&ds_empty[s], 1);
+    }
+    mbar_init(dq_done, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+  const uint32_t tmem_dq = tmem_base;                 // columns [0, D)
+  const uint32_t tmem_s = tmem_base + D;              // two buffers of BKV columns
+  const uint32_t tmem_dp = tmem_base + D + 2 * BKV;   // two buffers of BKV columns
+
+  if (warp == 0) {
+    // ------------------------------------------------ TMA producer ------------------------------------------------
+    if (elect_one()) {
+      mbar_expect_tx(qdo_full, 2 * L::Q_BYTES);
+#pragma unroll
+      for (int kb = 0; kb < D / 64; ++kb) {  // boxes {64 features, 128 rows}
+        tma_load_2d(sQ + kb * (BLOCK_Q * 128), &map_q, qdo_full, p.q_col + h * D + kb * 64, row0 + q0);
+        tma_load_2d(sDO + kb * (BLOCK_Q * 128), &map_do, qdo_full, h * D + kb * 64, row0 + q0);
+      }
+      bool ok = true;
+      int issued = 0;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        const int stage = j % KV_STAGES;
+        if (j >= KV_STAGES) {
+          ok = mbar_wait(&kv_empty[stage], (uint32_t)(j / KV_STAGES - 1) & 1u, abort_flag, p.err, ERR_KV_EMPTY_WAIT);
+          if (!ok) break;
+        }
+        uint8_t* sK = sKV + stage * L::STAGE_BYTES;
+        uint8_t* sV = sK + L::K_BYTES;
+        mbar_expect_tx(&kv_full[stage], L::STAGE_BYTES);
+        const int k0 = row0 + j * BKV;
+#pragma unroll
+        for (int kb = 0; kb < D / 64; ++kb) {  // boxes {64 features, BKV rows}
+          tma_load_2d(sK + kb * (BKV * 128), &map_kv, &kv_full[stage], p.k_col + h * D + kb * 64, k0);
+          tma_load_2d(sV + kb * (BKV * 128), &map_kv, &kv_full[stage], p.v_col + h * D + kb * 64, k0);
+        }
+        issued = j + 1;
+      }
+      if (!ok || *abort_flag) {
+        // loads in flight target this CTA's shared memory: give them a bounded time to land before the CTA ends
+        for (uint32_t i = 0; i < SPIN_LIMIT && !mbar_try_wait(qdo_full, 0); ++i) {}
+        for (int j = max(0, issued - KV_STAGES); j < issued; ++j)
+          for (uint32_t i = 0; i < SPIN_LIMIT && !mbar_try_wait(&kv_full[j % KV_STAGES], (uint32_t)(j / KV_STAGES) & 1u); ++i) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------ MMA issuer --------------------------------------------------
+    if (elect_one()) {
+      const uint32_t fmt = p.is_fp16 ? 0u : 1u;
+      // S = Q K^T and dP = dO V^T: both operands K-major, N = BKV.   dQ += dS K: dS K-major, K MN-major (bit 16), N = D.
+      const uint32_t idesc_s = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BKV >> 3) << 17) |
+                               ((uint32_t)(BLOCK_Q >> 4) << 24);
+      const uint32_t idesc_dq = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) |
+                                ((uint32_t)(BLOCK_Q >> 4) << 24);
+      bool ok = mbar_wait(qdo_full, 0, abort_flag, p.err, ERR_QDO_WAIT);
+      auto issue_scores = [&](int j) -> bool {
+        const int stage = j % KV_STAGES, sb = j & 1;
+        if (!mbar_wait(&kv_full[stage], (uint32_t)(j / KV_STAGES) & 1u, abort_flag, p.err, ERR_KV_FULL_WAIT)) return false;
+        if (j >= 2 && !mbar_wait(&sdp_empty[sb], (uint32_t)(j / 2 - 1) & 1u, abort_flag, p.err, ERR_SDP_EMPTY_WAIT))
+          return false;
+        tcgen05_fence_after();
+        const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
+        const uint32_t k_addr = smem_u32(sKV + stage * L::STAGE_BYTES);
+        const uint32_t v_addr = k_addr + L::K_BYTES;
+#pragma unroll
+        for (int kb = 0; kb < D / 64; ++kb)
+#pragma unroll
+          for (int k = 0; k < 64 / UMMA_K; ++k) {
+            const uint64_t da = make_smem_desc_sw128(q_addr + kb * (BLOCK_Q * 128) + k * (UMMA_K * 2), 16);
+            const uint64_t db = make_smem_desc_sw128(k_addr + kb * (BKV * 128) + k * (UMMA_K * 2), 16);
+            tcgen05_mma_f16(tmem_s + sb * BKV, da, db, idesc_s, (kb | k) ? 1u : 0u);
+          }
+#pragma unroll
+        for (int kb = 0; kb < D / 64; ++kb)
+#pragma unroll
+          for (int k = 0; k < 64 / UMMA_K; ++k) {
+            const uint64_t da = make_smem_desc_sw128(do_addr + kb * (BLOCK_Q * 128) + k * (UMMA_K * 2), 16);
+            const uint64_t db = make_smem_desc_sw128(v_addr + kb * (BKV * 128) + k * (UMMA_K * 2), 16);
+            tcgen05_mma_f16(tmem_dp + sb * BKV, da, db, idesc_s, (kb | k) ? 1u : 0u);
+          }
+        tcgen05_commit(&sdp_full[sb]);
+        return true;
+      };
+      if (ok && n_kv > 0) ok = issue_scores(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) {
+          ok = issue_scores(j + 1);
+          if (!ok) break;
+        }
+        const int db_i = j & 1;
+        ok = mbar_wait(&ds_full[db_i], (uint32_t)(j / 2) & 1u, abort_flag, p.err, ERR_DS_FULL_WAIT);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const int stage = j % KV_STAGES;
+        const uint32_t ds_addr = smem_u32(sDS + db_i * L::DS_BYTES);
+        const uint32_t k_addr = smem_u32(sKV + stage * L::STAGE_BYTES);
+#pragma unroll
+        for (int k = 0; k < BKV / UMMA_K; ++k) {
+          // dS: chunk column c (8 keys) starts at c * 2048 bytes; one product step spans two of them
+          const uint64_t da = make_smem_desc_noswizzle(ds_addr + k * 2 * 2048, 2048, 128);
+          // K_j as the MN-major operand: feature blocks (BKV rows x 128 B) are BKV * 128 bytes apart, 16 keys = 2048 bytes
+          const uint64_t dbk = make_smem_desc_sw128(k_addr + k * (UMMA_K * 128), BKV * 128);
+          tcgen05_mma_f16(tmem_dq, da, dbk, idesc_dq, (j | k) ? 1u : 0u);
+        }
+        tcgen05_commit(&kv_empty[stage]);   // K / V stage free once every product of this block has read it
+        tcgen05_commit(&ds_empty[db_i]);    // and the dS buffer
+        if (j == n_kv - 1) tcgen05_commit(dq_done);
+      }
+    }
+  } else {
+    // ------------------------------------------------ element-wise ------------------------------------------------
+    const int qtr = warp & 3;            // TMEM lane quarter this warp may access
+    const int r = qtr * 32 + lane;       // query row inside the block
+    const int qrow = q0 + r;             // query position inside the sequence
+    const bool row_ok = qrow < p.S;
+    const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
+    const float c = p.scale * 1.4426950408889634f;  // scores are exponentiated in base 2
+    // per-row constants: log-sum-exp (base 2) and delta = dO . O
+    float lse2 = 0.f, delta = 0.f;
+    if (row_ok) {
+      lse2 = p.lse[((long long)b * p.H + h) * p.S + qrow] * 1.4426950408889634f;
+      const uint16_t* orow = (const uint16_t*)p.out + (long long)(row0 + qrow) * p.ldo + h * D;
+      const uint16_t* grow = (const uint16_t*)p.dout + (long long)(row0 + qrow) * p.ld_do + h * D;
+#pragma unroll 4
+      for (int i = 0; i < D / 8; ++i) {
+        const uint4 ov = *(const uint4*)(orow + i * 8), gv = *(const uint4*)(grow + i * 8);
+        const uint16_t* oe = (const uint16_t*)&ov;
+        const uint16_t* ge = (const uint16_t*)&gv;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float of = p.is_fp16 ? __half2float(__ushort_as_half(oe[e])) : __bfloat162float(__ushort_as_bfloat16(oe[e]));
+          const float gf = p.is_fp16 ? __half2float(__ushort_as_half(ge[e])) : __bfloat162float(__ushort_as_bfloat16(ge[e]));
+          delta = fmaf(of, gf, delta);
+        }
+      }
+    }
+    const long long mat = ((long long)b * p.H + h) * p.S * (long long)p.S;  // start of this (batch, head)'s S x S matrices
+    uint16_t* prow = (uint16_t*)p.P + mat + (long long)qrow * p.S;
+    uint16_t* dsrow = (uint16_t*)p.dS + mat + (long long)qrow * p.S;
+    bool ok = true;
+    for (int j = 0; j < n_kv && ok; ++j) {
+      const int sb = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full[sb], (uint32_t)(j / 2) & 1u, abort_flag, p.err, ERR_SDP_FULL_WAIT));
+      if (!ok) break;
+      tcgen05_fence_after();
+      float s[BKV], dp[BKV];
+#pragma unroll
+      for (int ch = 0; ch < BKV / 32; ++ch) {
+        uint32_t raw[32];
+        tmem_ld_32x32b_x32(tmem_s + lane_base + sb * BKV + ch * 32, raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[ch * 32 + i] = __uint_as_float(raw[i]);
+        tmem_ld_32x32b_x32(tmem_dp + lane_base + sb * BKV + ch * 32, raw);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dp[ch * 32 + i] = __uint_as_float(raw[i]);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sdp_empty[sb]);  // both buffers may be overwritten
+      const int col0 = j * BKV;
+      const int limit = p.causal ? min(qrow, p.S - 1) : p.S - 1;  // last key this row may attend
+#pragma unroll
+      for (int i = 0; i < BKV; ++i) {
+        const float pr = (col0 + i <= limit && row_ok) ? exp2f(fmaf(s[i], c, -lse2)) : 0.f;
+        s[i] = pr;
+        dp[i] = pr * (dp[i] - delta) * p.scale;
+      }
+      // P and dS rows to global memory (16-bit): 2 * BKV bytes each, contiguous per thread
+      if (row_ok) {
+#pragma unroll
+        for (int ch = 0; ch < BKV / 8; ++ch) {
+          uint4 po, dso;
+          uint16_t* pe = (uint16_t*)&po;
+          uint16_t* de = (uint16_t*)&dso;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            pe[e] = p.is_fp16 ? __half_as_ushort(__float2half_rn(s[ch * 8 + e]))
+                              : __bfloat16_as_ushort(__float2bfloat16_rn(s[ch * 8 + e]));
+            de[e] = p.is_fp16 ? __half_as_ushort(__float2half_rn(dp[ch * 8 + e]))
+                              : __bfloat16_as_ushort(__float2bfloat16_rn(dp[ch * 8 + e]));
+          }
+          if (col0 + ch * 8 + 8 <= p.S) {
+            *(uint4*)(prow + col0 + ch * 8) = po;
+            *(uint4*)(dsrow + col0 + ch * 8) = dso;
+          } else {
+            for (int e = 0; e < 8 && col0 + ch * 8 + e < p.S; ++e) {
+              prow[col0 + ch * 8 + e] = pe[e];
+              dsrow[col0 + ch * 8 + e] = de[e];
+            }
+          }
+        }
+      }
+      // dS_j -> shared memory for the third product: 16-bit, no swizzle, [chunk column][row group][8 rows x 16 B]
+      const int db_i = j & 1;
+      if (j >= 2) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&ds_empty[db_i], (uint32_t)(j / 2 - 1) & 1u, abort_flag, p.err,
+                                                ERR_DS_EMPTY_WAIT));
+        if (!ok) break;
+      }
+      uint8_t* ds_tile = sDS + db_i * L::DS_BYTES;
+#pragma unroll
+      for (int ch = 0; ch < BKV / 8; ++ch) {
+        uint4 o;
+        uint16_t* oe = (uint16_t*)&o;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float v = dp[ch * 8 + e];
+          oe[e] = p.is_fp16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+        }
+        *(uint4*)(ds_tile + ch * 2048 + (r >> 3) * 128 + (r & 7) * 16) = o;
+      }
+      fence_proxy_async_smem();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ds_full[db_i]);
+    }
+    // ---- epilogue: dQ -> global memory -------------------------------------------------------------------------------
+    if (ok && n_kv > 0) ok = __all_sync(0xffffffffu, mbar_wait(dq_done, 0, abort_flag, p.err, ERR_DQ_DONE_WAIT));
+    if (ok && n_kv > 0) {
+      tcgen05_fence_after();
+      uint16_t* qrow_out = (uint16_t*)p.dq + (long long)(row0 + qrow) * p.ld_dq + p.dq_col + h * D;
+#pragma unroll 1
+      for (int ch = 0; ch < D / 32; ++ch) {
+        uint32_t raw[32];
+        tmem_ld_32x32b_x32(tmem_dq + lane_base + ch * 32, raw);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            uint16_t* oe = (uint16_t*)&o;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float v = __uint_as_float(raw[g * 8 + e]);
+              oe[e] = p.is_fp16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
+            }
+            *(uint4*)(qrow_out + ch * 32 + g * 8) = o;
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown: every role arrives here, also after an abort --------------------------------------------------------
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// 2-D map over a row-major matrix (rows x cols, leading dimension ld elements), boxes of {64, box_rows}, 128-byte swizzle
+int make_map(CUtensorMap* map, const void* ptr, int is_fp16, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, is_fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)ptr, dims,
+                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+template <int D, int BKV>
+int launch(const void* qkv, long long rows, long long cols, long long ld, const AttnBwdParams& p, cudaStream_t s) {
+  using L = BwdSmem<D, BKV>;
+  CUtensorMap mq, mdo, mkv;
+  int r = make_map(&mq, qkv, p.is_fp16, rows, cols, ld, BLOCK_Q);
+  if (r) return r;
+  r = make_map(&mdo, p.dout, p.is_fp16, rows, (long long)p.H * D, p.ld_do, BLOCK_Q);
+  if (r) return r;
+  r = make_map(&mkv, qkv, p.is_fp16, rows, cols, ld, BKV);
+  if (r) return r;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_dq_tcgen05_kernel<D, BKV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         L::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid((p.S + BLOCK_Q - 1) / BLOCK_Q, p.H, p.B);
+  attn_bwd_dq_tcgen05_kernel<D, BKV><<<grid, NUM_THREADS, L::TOTAL, s>>>(mq, mdo, mkv, p);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace
+
+// First pass of the attention backward over a packed projection matrix (see the top of this file).
+//   qkv:  (B*S x cols) row-major 16-bit with leading dimension ld: the (rotated) q | k | v of the forward pass
+//   out, dout: forward output and its gradient, (B*S x ldo / ld_do), head h in columns [h*D, (h+1)*D)
+//   lse:  (B, H, S) fp32 from the forward pass
+//   P, dS: (B*H, S, S) 16-bit outputs. Rows of a query block are written for all key columns below the end of that block
+//          (zeros above the diagonal); columns beyond are left untouched (the causal GEMMs never read them).
+//   dq:   (B*S x ld_dq) 16-bit output, head h in columns [dq_col + h*D, ...)
+//   All column offsets and leading dimensions must be multiples of 8, pointers 16-byte aligned, S a multiple of 8.
+// Returns 0, a CUDA error code, or a negative value when the arguments are not supported by this kernel.
+XL_API int xl_attn_bwd_dq_tcgen05(const void* qkv, long long ld, long long cols, const void* out, long long ldo,
+                                  const void* dout, long long ld_do, const float* lse, void* P, void* dS, void* dq,
+                                  long long ld_dq, int dq_col, int B, int S, int H, int D, int q_col, int k_col, int v_col,
+                                  float scale, int causal, int is_fp16, int* err, cudaStream_t s) {
+  if (B <= 0 || S <= 0 || H <= 0 || B > 65535 || H > 65535 || (S % 8)) return -1;
+  if ((((uintptr_t)qkv) & 15) || (((uintptr_t)out) & 15) || (((uintptr_t)dout) & 15) || (((uintptr_t)P) & 15) ||
+      (((uintptr_t)dS) & 15) || (((uintptr_t)dq) & 15))
+    return -1;
+  if ((ld % 8) || (ldo % 8) || (ld_do % 8) || (ld_dq % 8) || (dq_col % 8) || dq_col < 0) return -1;
+  if ((q_col % 8) || (k_col % 8) || (v_col % 8) || q_col < 0 || k_col < 0 || v_col < 0) return -1;
+  const long long need = (long long)H * D;
+  if (q_col + need > cols || k_col + need > cols || v_col + need > cols || cols > ld || ldo < need || ld_do < need ||
+      dq_col + need > ld_dq)
+    return -1;
+  if (!(scale > 0.f) || lse == nullptr) return -1;
+  AttnBwdParams p;
+  p.B = B; p.S = S; p.H = H; p.D = D;
+  p.q_col = q_col; p.k_col = k_col; p.v_col = v_col;
+  p.out = out; p.ldo = ldo; p.dout = dout; p.ld_do = ld_do; p.lse = lse; p.P = P; p.dS = dS; p.dq = dq; p.ld_dq = ld_dq;
+  p.dq_col = dq_col; p.scale = scale; p.causal = causal ? 1 : 0; p.is_fp16 = is_fp16 ? 1 : 0; p.err = err;
+  const long long rows = (long long)B * S;
+  if (D == 256) return launch<256, 32>(qkv, rows, cols, ld, p, s);
+  if (D == 128) return launch<128, 64>(qkv, rows, cols, ld, p, s);
+  if (D == 64) return launch<64, 64>(qkv, rows, cols, ld, p, s);
+  return -1;
+}

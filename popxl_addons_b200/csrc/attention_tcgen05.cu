@@ -243,9 +243,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       }
 #pragma unroll
       for (int i = 0; i < BKV; ++i) m_blk = fmaxf(m_blk, s[i]);
-      const float m_new = fmaxf(m, m_blk);
+      // Lazy rescaling: `m` is the reference maximum of the exponent, not the exact running maximum. It only moves (and
+      // the sum and the output accumulator are only rescaled) when the block's maximum exceeds it by more than
+      // RESCALE_LOG2 in the base-2 exponent, so probabilities stay below 2^RESCALE_LOG2 (exact in fp32 sums, and with the
+      // usual relative precision as 16-bit operands of the second product) and the TMEM round trip of the accumulator,
+      // which would otherwise run in almost every block (some row of a warp finds a new maximum), becomes rare.
+      constexpr float RESCALE_LOG2 = 8.f;
+      const bool move = m_blk > -INFINITY && (m == -INFINITY || (m_blk - m) * c > RESCALE_LOG2);
+      const float m_new = move ? m_blk : m;
       const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row with no admissible key yet keeps p = 0
-      const float alpha = m == -INFINITY ? 0.f : exp2f((m - m_use) * c);
+      const float alpha = (move && m != -INFINITY) ? exp2f((m - m_use) * c) : 1.f;
       float sum = 0.f;
       const float mc = m_use * c;
 #pragma unroll

@@ -150,6 +150,181 @@ XL_API int xl_rts_adam(const void* const* grads, void* const* weights, int w_dty
   return (int)cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Replicated-tensor-sharding optimizer step over a bucket of parameters (one launch per bucket, e.g. per layer).
+// Every parameter of the bucket is a segment: its 16-bit weight and its fp32 gradient accumulator live at the same offset
+// of every rank's symmetric arena; this rank owns elements [shard_off, shard_off + shard_n) of it, together with the
+// fp32 master weights and the moments of that range. Work is cut into chunks of RTS_CHUNK elements of the owned ranges,
+// numbered across the segments; a CTA finds a chunk's segment in the (short) table.
+//   mode 0  reduce-scatter (mean over the ranks, read from every rank's accumulator) + AdamW + all-gather (16-bit
+//           weights written into every rank's weight), all in one pass
+//   mode 1  reduce-scatter only: the mean goes into this rank's own accumulator (its owned range), and the sum of
+//           squares of (mean * grad_scale) over the owned ranges is added to *sumsq (per-CTA partials, summed in a
+//           fixed order by a second tiny kernel: deterministic). For global-norm clipping: the caller all-reduces the sums
+//           of all buckets, derives the clip factor, then runs mode 2.
+//   mode 2  AdamW + all-gather from the reduced gradient that mode 1 left in the own accumulator, scaled by
+//           grad_scale * (*dyn_scale) (dyn_scale: device scalar, e.g. the clip factor; may be null)
+// ---------------------------------------------------------------------------------------------------------------------
+constexpr int RTS_CHUNK = 4096;  // elements per chunk: 256 threads x 4 vectors of 4
+
+struct RtsSegment {            // one parameter of the bucket (device memory, 64 bytes)
+  long long acc_off;           // byte offset of the fp32 accumulator in every rank's arena
+  long long w_off;             // byte offset of the 16-bit weight in every rank's arena
+  float* master;               // this rank's shard of the fp32 master weights
+  void* m;                     // first moment of the shard (fp32 / fp16 / bf16)
+  float* v;                    // second moment of the shard
+  long long shard_off;         // first owned element
+  long long shard_n;           // owned elements (multiple of 4)
+  float weight_decay;
+  int chunk0;                  // number of the segment's first chunk
+};
+
+template <typename TM> struct RtsVec4;
+template <> struct RtsVec4<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&o)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    o[0] = t.x; o[1] = t.y; o[2] = t.z; o[3] = t.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&o)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+  }
+};
+template <typename T16> struct RtsVec4_16 {  // four 16-bit values as one 8-byte access
+  static __device__ __forceinline__ void load(const T16* p, float (&o)[4]) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const T16* e = reinterpret_cast<const T16*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o[k] = xl_to_float(e[k]);
+  }
+  static __device__ __forceinline__ void store(T16* p, const float (&o)[4]) {
+    uint2 raw;
+    T16* e = reinterpret_cast<T16*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) e[k] = xl_from_float<T16>(o[k]);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+};
+template <> struct RtsVec4<__half> : RtsVec4_16<__half> {};
+template <> struct RtsVec4<__nv_bfloat16> : RtsVec4_16<__nv_bfloat16> {};
+
+template <typename TW, typename TM>
+__global__ void __launch_bounds__(256)
+    rts_adam_multi_kernel(const RtsSegment* __restrict__ segs, int n_seg, int total_chunks, uint8_t* const* bases, int rank,
+                          int world, int mode, const float* __restrict__ step, const float* __restrict__ dyn_scale,
+                          float* __restrict__ partials, RtsAdamArgs a) {
+  __shared__ float red[32];
+  float c1 = 1.f, c2 = 1.f;
+  if (step != nullptr && a.bias_correction) {
+    const float t = *step;
+    c1 = 1.f / (1.f - powf(a.beta1, t));
+    c2 = 1.f / (1.f - powf(a.beta2, t));
+  }
+  const float inv_world = 1.f / world;
+  const float gscale = a.grad_scale * (dyn_scale != nullptr ? *dyn_scale : 1.f);
+  float sq = 0.f;
+  for (int chunk = blockIdx.x; chunk < total_chunks; chunk += gridDim.x) {
+    int si = 0;
+    while (si + 1 < n_seg && segs[si + 1].chunk0 <= chunk) ++si;
+    const RtsSegment sg = segs[si];
+    const long long e0 = (long long)(chunk - sg.chunk0) * RTS_CHUNK;
+#pragma unroll
+    for (int u = 0; u < RTS_CHUNK / (256 * 4); ++u) {
+      const long long e = e0 + ((long long)u * 256 + threadIdx.x) * 4;
+      if (e >= sg.shard_n) continue;
+      float g[4] = {0.f, 0.f, 0.f, 0.f};
+      if (mode == 2) {  // already reduced into the own accumulator
+        RtsVec4<float>::load(reinterpret_cast<const float*>(bases[rank] + sg.acc_off) + sg.shard_off + e, g);
+      } else {
+        for (int p = 0; p < world; ++p) {  // reduce-scatter: my range of every rank's accumulator
+          float t[4];
+          RtsVec4<float>::load(reinterpret_cast<const float*>(bases[p] + sg.acc_off) + sg.shard_off + e, t);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) g[k] += t[k];
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) g[k] *= inv_world;
+      }
+      if (mode == 1) {
+        RtsVec4<float>::store(reinterpret_cast<float*>(bases[rank] + sg.acc_off) + sg.shard_off + e, g);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) sq += (g[k] * a.grad_scale) * (g[k] * a.grad_scale);
+        continue;
+      }
+      float wv[4], vv[4], mv[4], wq[4];
+      RtsVec4<float>::load(sg.master + e, wv);
+      RtsVec4<float>::load(sg.v + e, vv);
+      RtsVec4<TM>::load(reinterpret_cast<const TM*>(sg.m) + e, mv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float gf = g[k] * gscale;
+        // the moment is rounded to its storage type before it is used, so the update equals one computed from the
+        // stored state
+        mv[k] = xl_to_float(xl_from_float<TM>(mv[k] * a.beta1 + gf * (1.f - a.beta1)));
+        vv[k] = vv[k] * a.beta2 + gf * gf * (1.f - a.beta2);
+        const float upd = (mv[k] * c1) / (sqrtf(vv[k] * c2) + a.eps) + wv[k] * sg.weight_decay;
+        wv[k] -= a.lr * upd;
+        wq[k] = wv[k];
+      }
+      RtsVec4<float>::store(sg.master + e, wv);
+      RtsVec4<float>::store(sg.v + e, vv);
+      RtsVec4<TM>::store(reinterpret_cast<TM*>(sg.m) + e, mv);
+      uint2 packed;
+      {
+        TW* q = reinterpret_cast<TW*>(&packed);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) q[k] = xl_from_float<TW>(wq[k]);
+      }
+      for (int p = 0; p < world; ++p)  // all-gather: my range into every rank's weight
+        *reinterpret_cast<uint2*>(reinterpret_cast<TW*>(bases[p] + sg.w_off) + sg.shard_off + e) = packed;
+    }
+  }
+  if (mode == 1) {
+    sq = xl_block_sum(sq, red);
+    if (threadIdx.x == 0) partials[blockIdx.x] = sq;
+  }
+}
+
+__global__ void rts_sumsq_finish_kernel(const float* __restrict__ partials, int n, float* __restrict__ sumsq) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < n; ++i) t += partials[i];
+    *sumsq += t;
+  }
+}
+
+// Grid size (= number of per-CTA partial sums of mode 1) for a bucket of `total_chunks` chunks.
+XL_API int xl_rts_adam_multi_grid(int total_chunks) { return xl_grid_for(total_chunks, 1, 148 * 8); }
+
+// segs: device array of n_seg RtsSegment; bases: device array [world] with every rank's arena base; step: device scalar
+// incremented by this call in modes 0 and 2 (may be null); partials: xl_rts_adam_multi_grid(total_chunks) floats of scratch
+// (mode 1); sumsq: device scalar that mode 1 adds to. Call between barriers as xl_rts_adam.
+XL_API int xl_rts_adam_multi(const void* segs, int n_seg, int total_chunks, const void* bases, int rank, int world, int mode,
+                             int w_dtype, int m_dtype, float* step, const float* dyn_scale, float* partials, float* sumsq,
+                             float lr, float beta1, float beta2, float eps, float grad_scale, int bias_correction,
+                             cudaStream_t s) {
+  if (n_seg <= 0 || total_chunks <= 0 || world < 1 || world > 64 || mode < 0 || mode > 2) return -1;
+  if (w_dtype != XL_BF16 && w_dtype != XL_F16) return -1;
+  if (mode == 1 && (partials == nullptr || sumsq == nullptr)) return -1;
+  RtsAdamArgs a{lr, beta1, beta2, eps, 0.f, grad_scale, bias_correction};
+  if (step && mode != 1) rts_step_increment_kernel<<<1, 1, 0, s>>>(step);
+  const int grid = xl_rts_adam_multi_grid(total_chunks);
+#define XL_RTS_MULTI(TW, TM)                                                                                             \
+  rts_adam_multi_kernel<TW, TM><<<grid, 256, 0, s>>>((const RtsSegment*)segs, n_seg, total_chunks, (uint8_t* const*)bases, \
+                                                     rank, world, mode, step, dyn_scale, partials, a)
+  if (w_dtype == XL_BF16) {
+    if (m_dtype == XL_F32) XL_RTS_MULTI(__nv_bfloat16, float);
+    else if (m_dtype == XL_BF16) XL_RTS_MULTI(__nv_bfloat16, __nv_bfloat16);
+    else XL_RTS_MULTI(__nv_bfloat16, __half);
+  } else {
+    if (m_dtype == XL_F32) XL_RTS_MULTI(__half, float);
+    else if (m_dtype == XL_BF16) XL_RTS_MULTI(__half, __nv_bfloat16);
+    else XL_RTS_MULTI(__half, __half);
+  }
+#undef XL_RTS_MULTI
+  if (mode == 1) rts_sumsq_finish_kernel<<<1, 32, 0, s>>>(partials, grid, sumsq);
+  return (int)cudaGetLastError();
+}
+
 // One-shot all-reduce (sum) of a small 16-bit tensor, latency-bound (the 128 KiB activations of token-by-token decoding).
 // Every rank copies its input into one half of a staging buffer in symmetric memory, the ranks meet at a barrier, and
 // every rank reads the sum of all replicas of that half through the multicast address (`multimem.ld_reduce`: NVSwitch

@@ -111,23 +111,34 @@ def build_optimizer(ir, cfg, par, groups, hp, state_dtype, shard_optimizer, fuse
                 if shardable:
                     new_w = ops.collectives.replicated_all_gather(new_w, par.dp_group, output_shape=w.shape)
                 ops.var_updates.copy_var_update_(w, new_w)
-    # one fused kernel per parameter: reduce-scatter + AdamW + all-gather; only the first call waits for all
-    # replicas' accumulators and only the last one for all replicas' weight shards
-    for j, (w, g, master, decay, full, rg, group_name) in enumerate(fused_jobs):
-        # barriers are per process: the first / last fused update of every device slot carries them
-        same = [k for k, job in enumerate(fused_jobs) if slot_of is None or slot_of(job[6]) == slot_of(group_name)]
+    # one fused kernel per bucket (= per group: a layer, the embedding, the head): reduce-scatter + AdamW + all-gather of
+    # all its parameters; only the first call of a device slot waits for all replicas' accumulators and only the last one
+    # for all replicas' weight shards
+    from ..optimizers.rts_adam import RTSAdamBucketStep
+
+    buckets: Dict[str, list] = {}
+    for job in fused_jobs:
+        buckets.setdefault(job[6], []).append(job)
+    order = list(buckets)
+    for j, group_name in enumerate(order):
+        jobs = buckets[group_name]
+        same = [k for k, gname in enumerate(order) if slot_of is None or slot_of(gname) == slot_of(group_name)]
         first, last = j == same[0], j == same[-1]
-        key = ("fused", tuple(w.shape), decay, first, last)
+        ws, gs, ms_ = [job[0] for job in jobs], [job[1] for job in jobs], [job[2] for job in jobs]
+        decays = tuple(job[3] for job in jobs)
+        names = [job[4][len(group_name) + 1:] for job in jobs]
+        rgs = [job[5] for job in jobs]
+        key = ("bucket", tuple(tuple(w.shape) for w in ws), decays, tuple(names), first, last)
         if key not in opt_graphs:
             with xl.ipu(None):
-                opt_graphs[key] = RTSAdamStep().create_graph(
-                    w, g, master, par.dp_group, rg, lr=hp["lr"], beta1=hp["beta1"], beta2=hp["beta2"], eps=hp["eps"],
-                    weight_decay=decay, first_order_dtype=state_dtype, sync_before=first, sync_after=last)
+                opt_graphs[key] = RTSAdamBucketStep().create_graph(
+                    ws, gs, ms_, names, par.dp_group, rgs, lr=hp["lr"], weight_decays=decays, beta1=hp["beta1"],
+                    beta2=hp["beta2"], eps=hp["eps"], first_order_dtype=state_dtype, sync_before=first, sync_after=last)
         ofacts, ograph = opt_graphs[key]
         with placed(group_name):
-            ostate = ofacts.init(f"adam.{full}")
-            ograph.bind(ostate).call(w, g, master)
-        opt_state[full] = ostate
+            ostate = ofacts.init(f"adam.{group_name}")
+            ograph.bind(ostate).call(*ws, *gs, *ms_)
+        opt_state[group_name] = ostate
     return masters, opt_state
 
 

@@ -68,6 +68,8 @@ _gq = _sig("xl_gq_decompress", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c
 _sm_fwd = _sig("xl_attn_softmax_fwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p)
 _attn_flash = _sig("xl_attn_fwd_tcgen05", _c_p, _c_ll, _c_ll, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                    _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p)
+_attn_bwd_dq = _sig("xl_attn_bwd_dq_tcgen05", _c_p, _c_ll, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int,
+                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p)
 _sm_bwd = _sig("xl_attn_softmax_bwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p)
 _ce = _sig("xl_ce_fwd_bwd", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p, _c_f, _c_int, _c_p)
 _gemm = _sig("xl_gemm_tcgen05", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll,
@@ -78,6 +80,9 @@ _gemm_fused = _sig("xl_gemm_tcgen05_fused", _c_p, _c_p, _c_p, _c_int, _c_int, _c
                    _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p)
 _gemm_pair = _sig("xl_gemm2cta_tcgen05", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
                   _c_ll, _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_p)
+_rts_multi_grid = _sig("xl_rts_adam_multi_grid", _c_int)
+_rts_adam_multi = _sig("xl_rts_adam_multi", _c_p, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p,
+                       _c_p, _c_p, _c_f, _c_f, _c_f, _c_f, _c_f, _c_int, _c_p)
 _gemm_ar_pull = _sig("xl_gemm_tcgen05_ar_pull", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
                      _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_f, _c_p, _c_int, _c_p, _c_int,
                      _c_int, _c_p, _c_p, _c_int, _c_p)
@@ -827,8 +832,35 @@ def attention_qkv_cuda(qkv, sin, cos, seq_len, n_heads, head_dim, rotary_dim, ca
     return out, rot, lse
 
 
+# XL_FLASH_ATTENTION_BWD=0: the backward pass recomputes the scores with a GEMM and runs the two softmax kernels instead
+# of the single kernel that keeps the scores on chip
+_FLASH_ATTENTION_BWD = os.environ.get("XL_FLASH_ATTENTION_BWD", "1") != "0"
+
+
+def flash_attention_bwd_dq(qkv_rot, out, dout, lse, dqkv, B, S, H, D, scale, causal):
+    """First pass of the attention backward as one tcgen05 kernel: recomputes P from q, k and `lse`, forms dP = dO V^T and
+    dS = P o (dP - dO . O) * scale on chip, accumulates dQ = dS K into the q window of `dqkv`, and writes P and dS once
+    as `(B*H, S, S)` 16-bit matrices for the two remaining products. Returns `(P, dS)` or NotImplemented."""
+    hd = H * D
+    if D not in (64, 128, 256) or S % 8 or qkv_rot.dtype not in (torch.bfloat16, torch.float16) or lse.dtype != torch.float32:
+        return NotImplemented
+    if not (out.is_cuda and out.stride(1) == 1 and dout.stride(1) == 1 and lse.is_contiguous()):
+        return NotImplemented
+    P = torch.empty((B * H, S, S), dtype=qkv_rot.dtype, device=qkv_rot.device)
+    dS = torch.empty_like(P)
+    rc = _attn_bwd_dq(qkv_rot.data_ptr(), qkv_rot.stride(0), qkv_rot.shape[1], out.data_ptr(), out.stride(0),
+                      dout.data_ptr(), dout.stride(0), lse.data_ptr(), P.data_ptr(), dS.data_ptr(), dqkv.data_ptr(),
+                      dqkv.stride(0), 0, B, S, H, D, 0, hd, 2 * hd, float(scale), int(bool(causal)),
+                      int(qkv_rot.dtype == torch.float16), gemm_error_flag(qkv_rot.device).data_ptr(), _stream())
+    if rc < 0:
+        return NotImplemented
+    _check(rc, "attn_bwd_dq_tcgen05")
+    _count("attn_bwd_dq_tcgen05")
+    return P, dS
+
+
 @native("attention_qkv_grad")
-def attention_qkv_grad_cuda(qkv_rot, lse, dout, sin, cos, seq_len, n_heads, head_dim, rotary_dim, causal, scale):
+def attention_qkv_grad_cuda(qkv_rot, lse, dout, sin, cos, *fwd_out, seq_len, n_heads, head_dim, rotary_dim, causal, scale):
     if qkv_rot.dtype not in (torch.bfloat16, torch.float16) or not (qkv_rot.is_contiguous() and dout.is_contiguous()):
         return NotImplemented
     if dout.dtype != qkv_rot.dtype:
@@ -840,29 +872,40 @@ def attention_qkv_grad_cuda(qkv_rot, lse, dout, sin, cos, seq_len, n_heads, head
     do = _heads_view(dout, 0, B, S, H, D)
     dqkv = torch.empty_like(qkv_rot)
     dq, dk, dv = (_heads_view(dqkv, i * hd, B, S, H, D) for i in range(3))
-    tmp_lse = torch.empty((H, S), dtype=torch.float32, device=qkv_rot.device)
     c1, c2, c3 = (1, 2, 3) if causal and _CAUSAL_SKIP else (0, 0, 0)
-    for b in range(B):
-        p = gemm(q[b], k[b].transpose(-1, -2), causal=c1)
-        if p is NotImplemented:
-            return NotImplemented
-        rc = _sm_fwd(p.data_ptr(), tmp_lse.data_ptr(), H * S, S, S, float(scale), int(bool(causal)), _CODE[p.dtype],
-                     _stream())
-        if rc == -1:
-            return NotImplemented
-        _check(rc, "attn_softmax_fwd")
-        _count("attn_softmax_fwd")
-        if gemm(p.transpose(-1, -2), do[b], out=dv[b], causal=c3) is NotImplemented:
-            return NotImplemented
-        dp = gemm(do[b], v[b].transpose(-1, -2), causal=c1)
-        if dp is NotImplemented:
-            return NotImplemented
-        _check(_sm_bwd(p.data_ptr(), dp.data_ptr(), H * S, S, S, float(scale), int(bool(causal)), _CODE[p.dtype],
-                       _stream()), "attn_softmax_bwd")
-        _count("attn_softmax_bwd")
-        if gemm(dp, k[b], out=dq[b], causal=c2) is NotImplemented \
-                or gemm(dp.transpose(-1, -2), q[b], out=dk[b], causal=c3) is NotImplemented:
-            return NotImplemented
+    fused = NotImplemented
+    if _FLASH_ATTENTION_BWD and fwd_out and causal and fwd_out[0].dtype == qkv_rot.dtype:
+        fused = flash_attention_bwd_dq(qkv_rot, fwd_out[0], dout, lse, dqkv, B, S, H, D, scale, causal)
+    if fused is not NotImplemented:
+        # dQ is done; the two remaining products read P and dS over the causal half (contraction from the tile's first row)
+        P, dS = (t.view(B, H, S, S) for t in fused)
+        for b in range(B):
+            if gemm(P[b].transpose(-1, -2), do[b], out=dv[b], causal=c3) is NotImplemented \
+                    or gemm(dS[b].transpose(-1, -2), q[b], out=dk[b], causal=c3) is NotImplemented:
+                return NotImplemented
+    else:
+        tmp_lse = torch.empty((H, S), dtype=torch.float32, device=qkv_rot.device)
+        for b in range(B):
+            p = gemm(q[b], k[b].transpose(-1, -2), causal=c1)
+            if p is NotImplemented:
+                return NotImplemented
+            rc = _sm_fwd(p.data_ptr(), tmp_lse.data_ptr(), H * S, S, S, float(scale), int(bool(causal)), _CODE[p.dtype],
+                         _stream())
+            if rc == -1:
+                return NotImplemented
+            _check(rc, "attn_softmax_fwd")
+            _count("attn_softmax_fwd")
+            if gemm(p.transpose(-1, -2), do[b], out=dv[b], causal=c3) is NotImplemented:
+                return NotImplemented
+            dp = gemm(do[b], v[b].transpose(-1, -2), causal=c1)
+            if dp is NotImplemented:
+                return NotImplemented
+            _check(_sm_bwd(p.data_ptr(), dp.data_ptr(), H * S, S, S, float(scale), int(bool(causal)), _CODE[p.dtype],
+                           _stream()), "attn_softmax_bwd")
+            _count("attn_softmax_bwd")
+            if gemm(dp, k[b], out=dq[b], causal=c2) is NotImplemented \
+                    or gemm(dp.transpose(-1, -2), q[b], out=dk[b], causal=c3) is NotImplemented:
+                return NotImplemented
     if rotary_dim:
         dqk = _heads_view(dqkv, 0, B, S, 2 * H, D)
         rotary_launch(dqk, sin, cos, dqk, rotary_dim, True)

@@ -401,6 +401,105 @@ def rts_adam(ex, op, w_vals, acc_vals, master_vals, m_vals, v_vals, step_vals):
     return True
 
 
+def _rts_bucket_table(ctx: GroupContext, key, ws, accs, masters, ms, vs, decays):
+    """Device table of the bucket's segments (64 bytes each, see RtsSegment in csrc/comm.cu), built once per op."""
+    import struct
+
+    cache = ctx.__dict__.setdefault("_rts_tables", {})
+    if key in cache:
+        return cache[key]
+    blob, chunk = b"", 0
+    for w, acc, master, m, v, decay in zip(ws, accs, masters, ms, vs, decays):
+        shard_n = master.numel()
+        blob += struct.pack("<qqQQQqqfi", ctx.arena.offset_of(acc), ctx.arena.offset_of(w), master.data_ptr(),
+                            m.data_ptr(), v.data_ptr(), ctx.rank * shard_n, shard_n, float(decay), chunk)
+        chunk += -(-shard_n // 4096)
+    table = torch.frombuffer(bytearray(blob), dtype=torch.uint8).to(ws[0].device)
+    nat = _lib()
+    grid = nat._rts_multi_grid(chunk)
+    entry = {"table": table, "chunks": chunk, "partials": torch.zeros(grid, dtype=torch.float32, device=ws[0].device),
+             "keep": (ws, accs, masters, ms, vs)}
+    cache[key] = entry
+    return entry
+
+
+def _rts_bucket_ok(ctx, ws, accs, masters, ms, vs):
+    if ctx.world == 1 or ctx.world > 64:
+        return False
+    m_dtype = ms[0].dtype
+    for w, acc, master, m, v in zip(ws, accs, masters, ms, vs):
+        if not (ctx.arena.contains(w) and ctx.arena.contains(acc)):
+            return False
+        if w.dtype != ws[0].dtype or w.dtype not in (torch.bfloat16, torch.float16) or acc.dtype != torch.float32 \
+                or v.dtype != torch.float32 or master.dtype != torch.float32 or m.dtype != m_dtype:
+            return False
+        if master.numel() % 4 or master.numel() * ctx.world != w.numel() or not (w.is_contiguous() and acc.is_contiguous()):
+            return False
+    return True
+
+
+def rts_reduce_bucket(ex, op, acc_vals):
+    """Mode 1 of the bucket kernel: group mean of every accumulator into its owned range + sum of squares."""
+    nat = _lib()
+    a = op.attrs
+    ctx = runtime(ex).context(a["group"])
+    accs = [v[0] for v in acc_vals]
+    if ctx.world == 1 or any(not ctx.arena.contains(t) or t.dtype != torch.float32 or t.numel() % (4 * ctx.world)
+                             for t in accs):
+        return NotImplemented
+    import struct
+
+    cache = ctx.__dict__.setdefault("_rts_tables", {})
+    key = ("reduce", op.uid)
+    if key not in cache:
+        blob, chunk = b"", 0
+        for acc in accs:
+            shard_n = acc.numel() // ctx.world
+            blob += struct.pack("<qqQQQqqfi", ctx.arena.offset_of(acc), 0, 0, 0, 0, ctx.rank * shard_n, shard_n, 0.0, chunk)
+            chunk += -(-shard_n // 4096)
+        cache[key] = {"table": torch.frombuffer(bytearray(blob), dtype=torch.uint8).to(accs[0].device), "chunks": chunk,
+                      "partials": torch.zeros(nat._rts_multi_grid(chunk), dtype=torch.float32, device=accs[0].device)}
+    e = cache[key]
+    sumsq = torch.zeros((), dtype=torch.float32, device=accs[0].device)
+    if a["sync_before"]:
+        group_barrier(ctx, 4)
+    rc = nat._rts_adam_multi(e["table"].data_ptr(), len(accs), e["chunks"], ctx.arena.bases_dev.data_ptr(), ctx.rank,
+                             ctx.world, 1, nat.BF16, nat.F32, None, None, e["partials"].data_ptr(), sumsq.data_ptr(),
+                             0.0, 0.0, 0.0, 0.0, a["grad_scale"], 0, nat._stream())
+    nat._check(rc, "rts_adam_multi")
+    nat._count("rts_reduce_bucket")
+    return [sumsq]
+
+
+def rts_adam_bucket(ex, op, w_vals, acc_vals, master_vals, m_vals, v_vals, step_vals, scale_vals):
+    """One launch for the whole bucket: gradient reduce-scatter + AdamW on the owned ranges + all-gather of the new
+    16-bit weights (or, after `rts_reduce_bucket`, AdamW + all-gather from the already reduced gradients)."""
+    nat = _lib()
+    a = op.attrs
+    ctx = runtime(ex).context(a["group"])
+    ws, accs, masters, ms, vs = ([v[0] for v in vals] for vals in (w_vals, acc_vals, master_vals, m_vals, v_vals))
+    step = step_vals[0]
+    if not _rts_bucket_ok(ctx, ws, accs, masters, ms, vs) or step.dtype != torch.float32:
+        return NotImplemented
+    e = _rts_bucket_table(ctx, ("adam", op.uid), ws, accs, masters, ms, vs, a["weight_decays"])
+    scale = scale_vals[0] if scale_vals is not None else None
+    if scale is not None and (scale.dtype != torch.float32 or scale.numel() != 1):
+        return NotImplemented
+    if a["sync_before"]:
+        group_barrier(ctx, 4)
+    rc = nat._rts_adam_multi(e["table"].data_ptr(), len(ws), e["chunks"], ctx.arena.bases_dev.data_ptr(), ctx.rank,
+                             ctx.world, 2 if a["reduced"] else 0, nat._CODE[ws[0].dtype], nat._CODE[ms[0].dtype],
+                             step.data_ptr(), scale.data_ptr() if scale is not None else None, None, None, a["lr"],
+                             a["beta1"], a["beta2"], a["eps"], a["grad_scale"], int(a["bias_correction"]), nat._stream())
+    if rc == -1:
+        return NotImplemented
+    nat._check(rc, "rts_adam_multi")
+    nat._count("rts_adam_bucket")
+    if a["sync_after"]:
+        group_barrier(ctx, 5)
+    return True
+
+
 def layer_norm_distributed_fwd(ex, op, x_vals, w_vals, b_vals):
     """Hidden-sharded LayerNorm: local (sum, sum of squares) per row in one kernel, one small all-reduce over the group,
     normalisation with the group statistics in a second kernel."""
@@ -511,7 +610,8 @@ _TABLE = {"matmul_all_reduce": matmul_all_reduce, "ar_add_layer_norm": ar_add_la
           "layer_norm_distributed_fwd": layer_norm_distributed_fwd,
           "layer_norm_distributed_bwd": layer_norm_distributed_bwd,
           "ce_sharded_fwd": ce_sharded_fwd, "ce_sharded_with_grad": ce_sharded_with_grad,
-          "matmuls_reduce_scatter": matmuls_reduce_scatter, "all_gather_matmul": all_gather_matmul, "matmul2_all_reduce": matmul2_all_reduce, "rts_adam": rts_adam}
+          "matmuls_reduce_scatter": matmuls_reduce_scatter, "all_gather_matmul": all_gather_matmul, "matmul2_all_reduce": matmul2_all_reduce, "rts_adam": rts_adam,
+          "rts_adam_bucket": rts_adam_bucket, "rts_reduce_bucket": rts_reduce_bucket}
 
 
 def lookup(name: str, session):

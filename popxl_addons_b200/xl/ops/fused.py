@@ -222,7 +222,9 @@ def _attn_qkv_fwd_ref(qkv, sin, cos, seq_len, n_heads, head_dim, rotary_dim, cau
     return o.permute(0, 2, 1, 3).reshape(T, n_heads * head_dim), rot, lse
 
 
-def _attn_qkv_bwd_ref(qkv_rot, lse, dout, sin, cos, seq_len, n_heads, head_dim, rotary_dim, causal, scale):
+def _attn_qkv_bwd_ref(qkv_rot, lse, dout, sin, cos, *fwd_out, seq_len, n_heads, head_dim, rotary_dim, causal, scale):
+    """`fwd_out` (optional): the forward pass's output, which device kernels use for the row sums `dO . O`; this
+    reference recomputes it."""
     if qkv_rot.device.type == "meta":
         return torch.empty_like(qkv_rot)
     (q, k, v), B = _split_heads(qkv_rot, seq_len, n_heads, head_dim)
@@ -241,7 +243,8 @@ def _vjp_attn_qkv(ctx, op, gs):
     qkv, sin, cos = op.inputs
     out, rot, lse = op.outputs
     a = {k: v for k, v in op.attrs.items() if k != "inplace"}
-    return [emit1("attention_qkv_grad", [ctx.fwd(rot), ctx.fwd(lse), gs[0], ctx.fwd(sin), ctx.fwd(cos)], a), None, None]
+    return [emit1("attention_qkv_grad", [ctx.fwd(rot), ctx.fwd(lse), gs[0], ctx.fwd(sin), ctx.fwd(cos), ctx.fwd(out)], a),
+            None, None]
 
 
 def _attn_qkv_flops(op):

@@ -54,7 +54,7 @@ def main():
             from popxl_addons_b200.ops import native
 
             native.STRICT[0] = True  # a hot op that runs its torch implementation on the GPU is an error
-        trainer = DecoderTrainer(cfg, micro_batches=2, device=args.device, lr=1e-2,
+        trainer = DecoderTrainer(cfg, micro_batches=2, device=args.device, lr=1e-2 if args.big < 2 else 2e-3,
                                  fused_collectives=bool(args.fused))
         losses = []
         for step in range(args.steps):
@@ -441,6 +441,71 @@ def main():
                                           "n_owned": len(tr.session._owned_state())})
         if rank == 0:
             print(json.dumps({"ranks": gathered, "n_state": len(tr.state.to_dict())}))
+    elif args.mode == "rtsclip":
+        # bucketed RTS optimizer on the device: (a) one fused launch per bucket, (b) reduce + global norm + clipped update,
+        # both against a numpy AdamW on the averaged gradients
+        from popxl_addons_b200 import xl as popxl
+        from popxl_addons_b200.xl import ops
+        if args.device == "cuda":
+            from popxl_addons_b200.ops import native
+        from popxl_addons_b200.optimizers.rts_adam import rts_adam_bucket_, rts_reduce_bucket_
+
+        shapes, decays, lr, max_norm = [(256, 192), (4096,), (512, 64)], (0.01, 0.0, 0.01), 1e-2, 0.5
+        rs = np.random.RandomState(3)
+        w0 = [rs.randn(*sh).astype(np.float32) * 0.1 for sh in shapes]
+        w0 = [torch.tensor(w).bfloat16().float().numpy() for w in w0]
+        grads = [[rs.randn(*sh).astype(np.float32) for sh in shapes] for _ in range(world)]
+        mean_g = [np.mean([grads[r][k] for r in range(world)], axis=0) for k in range(len(shapes))]
+        norm = float(np.sqrt(sum((g.astype(np.float64) ** 2).sum() for g in mean_g)))
+
+        def adamw(w, g, decay, scale):
+            g = g * scale
+            m, v = 0.1 * g, 0.05 * g * g
+            upd = (m / (1 - 0.9)) / (np.sqrt(v / (1 - 0.95)) + 1e-5) + w * decay
+            return w - lr * upd
+
+        results = {}
+        for clip in (False, True):
+            ir = popxl.Ir(replication="popdist")
+            with ir.main_graph:
+                rg = ir.replica_grouping()
+                one = ir.replica_grouping(group_size=1)
+                ws, accs, masters, ms, vs = [], [], [], [], []
+                for k, sh in enumerate(shapes):
+                    w = popxl.variable(w0[k], popxl.bfloat16, f"w{k}")
+                    acc = popxl.variable(np.stack([grads[r][k] for r in range(world)]), popxl.float32, f"acc{k}",
+                                         replica_grouping=one)
+                    w.symmetric_group = rg
+                    acc.symmetric_group = rg
+                    master, _ = popxl.replica_sharded_variable(w0[k], popxl.float32, f"master{k}", shard_grouping=rg)
+                    m, _ = popxl.replica_sharded_variable(np.zeros(sh, np.float32), popxl.float32, f"m{k}", shard_grouping=rg)
+                    v, _ = popxl.replica_sharded_variable(np.zeros(sh, np.float32), popxl.float32, f"v{k}", shard_grouping=rg)
+                    ws.append(w), accs.append(acc), masters.append(master), ms.append(m), vs.append(v)
+                step = popxl.variable(np.zeros((), np.float32), popxl.float32, "step")
+                if clip:
+                    sumsq = rts_reduce_bucket_(accs, rg)
+                    total = ops.collectives.replicated_all_reduce(sumsq, "add", rg)
+                    gmax = popxl.constant(max_norm, popxl.float32)
+                    factor = ops.div(gmax, ops.maximum(ops.sqrt(total), gmax))
+                    rts_adam_bucket_(ws, accs, masters, ms, vs, step, rg, lr=lr, weight_decays=decays, beta1=0.9, beta2=0.95,
+                                     eps=1e-5, scale=factor, reduced=True)
+                else:
+                    rts_adam_bucket_(ws, accs, masters, ms, vs, step, rg, lr=lr, weight_decays=decays, beta1=0.9, beta2=0.95,
+                                     eps=1e-5)
+            sess = popxl.Session(ir, args.device)
+            sess.run()
+            scale = min(1.0, max_norm / norm) if clip else 1.0
+            err = 0.0
+            for k in range(len(shapes)):
+                got = sess.get_tensor_data(ws[k]).astype(np.float32)
+                want = adamw(w0[k], mean_g[k], decays[k], scale)
+                err = max(err, float(np.abs(got - want).max() / np.abs(want).max()))
+                mgot = sess.get_tensor_data(masters[k])
+                err = max(err, 10 * float(np.abs(mgot - want).max() / np.abs(want).max()))  # fp32 master: 10x tighter
+            results["clip" if clip else "fused"] = err
+        if rank == 0:
+            print(json.dumps({"errors": results, "norm": norm,
+                              "kernels": native.LAUNCHES["by_kernel"] if args.device == "cuda" else {}}))
     elif args.mode == "elastic":
         # data-parallel training under the restart supervisor: checkpoints every 2 steps, heartbeats between steps; on
         # the first attempt rank 1 stops after step 3 (a host-side failure, nothing in flight)

@@ -41,7 +41,7 @@ def simulated(tp, dp, dtype, steps=3, big=False, fused=True):
     dec._SEED[0] = 0
     cfg = (GPTJConfig.tiny(dtype=dtype, tp=tp, dp=dp, **({"seq_len": 512} if big == 2 else {})) if big
            else dec.DecoderConfig.tiny("gptj", dtype=dtype, tp=tp, dp=dp))
-    t = DecoderTrainer(cfg, micro_batches=2, device="cpu", lr=1e-2, fused_collectives=fused)
+    t = DecoderTrainer(cfg, micro_batches=2, device="cpu", lr=1e-2 if big != 2 else 2e-3, fused_collectives=fused)
     return [t.step(global_tokens(cfg, 2, seed=s)) for s in range(steps)]
 
 
@@ -143,6 +143,18 @@ def test_gpu_ranks_fused_collectives(tp, dp):
         assert kernels.get("gemm_ar_pull_tcgen05", 0) > 0, kernels  # the TP all-reduce ran inside the GEMM kernel
         assert kernels.get("ce_shard_stats", 0) > 0 and kernels.get("ce_shard_grad_loss", 0) > 0, kernels
         assert not got.get("fallbacks"), got.get("fallbacks")
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@pytest.mark.parametrize("nproc", [2, 4])
+def test_gpu_rts_bucket_optimizer_with_and_without_clipping(nproc):
+    """One launch per bucket: reduce-scatter + AdamW + all-gather fused, and the clipped form (reduce + sum of squares,
+    global norm, update from the reduced gradients), against numpy AdamW on the averaged gradients."""
+    _need_gpus(nproc)
+    res = launch(nproc, "--mode", "rtsclip", "--device", "cuda", timeout=300)
+    assert res["errors"]["fused"] < 1e-2 and res["errors"]["clip"] < 1e-2, res  # bf16 weights: 2^-8 relative
+    assert res["kernels"].get("rts_adam_bucket", 0) == 2 and res["kernels"].get("rts_reduce_bucket", 0) == 1, res
 
 
 @pytest.mark.gpu

@@ -312,6 +312,52 @@ def test_single_kernel_attention_forward(nat, B, S, H, D, causal, dtype):
     torch.testing.assert_close(lse, torch.logsumexp(s, -1), rtol=1e-3, atol=1e-2)
 
 
+@pytest.mark.parametrize("B,S,H,D,rot,dtype", [(1, 256, 2, 64, 32, torch.bfloat16), (2, 384, 2, 128, 0, torch.float16),
+                                                (1, 512, 2, 256, 64, torch.bfloat16), (1, 2048, 1, 256, 64, torch.bfloat16),
+                                                (2, 200, 1, 256, 0, torch.bfloat16)])
+def test_attention_on_packed_qkv_forward_and_fused_backward(nat, B, S, H, D, rot, dtype):
+    """`attention_qkv` and its gradient as the training step runs them (rotary in place, single-kernel forward, backward
+    with scores, dP and the dQ accumulator on chip + two causal GEMMs) against the fp32 reference of the same ops."""
+    from popxl_addons_b200.ops.rotary_pos_embed import trig_tables
+
+    torch.manual_seed(31)
+    hd = H * D
+    qkv = (torch.randn(B * S, 3 * hd, device="cuda") * 0.6).to(dtype)
+    dout = (torch.randn(B * S, hd, device="cuda") * 0.5).to(dtype)
+    sin_np, cos_np = trig_tables(S, rot if rot else 2)
+    sin, cos = (torch.tensor(t[None]).to(dtype).cuda() for t in (sin_np, cos_np))
+    scale = 1.0 / math.sqrt(D)
+    kw = dict(seq_len=S, n_heads=H, head_dim=D, rotary_dim=rot, causal=True, scale=scale)
+    saved = nat._FLASH_ATTENTION
+    nat._FLASH_ATTENTION = "1"
+    try:
+        out, qkv_rot, lse = nat.attention_qkv_cuda(qkv, sin, cos, inplace=False, **kw)
+    finally:
+        nat._FLASH_ATTENTION = saved
+    r_out, r_rot, r_lse = _ref("attention_qkv")(qkv.float(), sin.float(), cos.float(), inplace=False, **kw)
+    torch.testing.assert_close(out.float(), r_out, rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(lse, r_lse, rtol=1e-3, atol=1e-2)
+    before = nat.LAUNCHES["by_kernel"].get("attn_bwd_dq_tcgen05", 0)
+    dqkv = nat.attention_qkv_grad_cuda(qkv_rot, lse, dout, sin, cos, out, **kw)
+    assert dqkv is not NotImplemented
+    nat.check_gemm_errors()
+    assert nat.LAUNCHES["by_kernel"].get("attn_bwd_dq_tcgen05", 0) == before + 1, "the fused backward kernel did not run"
+    r_dqkv = _ref("attention_qkv_grad")(r_rot, r_lse, dout.float(), sin.float(), cos.float(), **kw)
+    # gradients are sums over up to S keys of 16-bit products: compare relative to the largest entry of each third
+    for i, name in enumerate(("dq", "dk", "dv")):
+        got, want = dqkv[:, i * hd:(i + 1) * hd].float(), r_dqkv[:, i * hd:(i + 1) * hd]
+        err = (got - want).abs().max() / want.abs().max()
+        assert err < 3e-2, f"{name}: relative error {float(err):.4f}"
+    # the GEMM-based backward (scores recomputed, two softmax kernels) must agree as well
+    saved_bwd, nat._FLASH_ATTENTION_BWD = nat._FLASH_ATTENTION_BWD, False
+    try:
+        dqkv2 = nat.attention_qkv_grad_cuda(qkv_rot, lse, dout, sin, cos, out, **kw)
+    finally:
+        nat._FLASH_ATTENTION_BWD = saved_bwd
+    err = (dqkv2.float() - r_dqkv).abs().max() / r_dqkv.abs().max()
+    assert err < 3e-2, f"GEMM-based backward: relative error {float(err):.4f}"
+
+
 @pytest.mark.parametrize("M,N,K,batch,ta,tb,dtype", [
     (256, 256, 64, 1, False, False, torch.bfloat16),      # one tile, one k-block
     (512, 512, 512, 1, False, False, torch.bfloat16),     # the ring wraps (8 k-blocks over 6 stages)

@@ -482,3 +482,67 @@ def test_cross_entropy_ops_and_misc_utils(capsys):
     np.testing.assert_allclose(out[s_plain], ref.item(), rtol=1e-5)
     np.testing.assert_allclose(out[s_loss], ref.item(), rtol=1e-5)
     np.testing.assert_allclose(out[s_dl], tl.grad.numpy(), rtol=1e-4, atol=1e-6)
+
+
+def test_rts_bucket_step_with_norm_clipping_equals_adam_with_global_norm():
+    """Bucketed RTS optimizer with clipping: reduce-scatter of every accumulator + sum of squares of the owned ranges,
+    all-reduce of the sums -> global norm -> clip factor, update from the reduced gradients. Must equal the reference's
+    composition: gradients averaged over the replicas, `AdamOptimizerStep(global_norm=..., global_norm_max=...)` on
+    fp32 weights (popxl_addons/optimizers/adam.py:37-48)."""
+    from popxl_addons_b200.optimizers import AdamOptimizerStep
+    from popxl_addons_b200.optimizers.rts_adam import rts_adam_bucket_, rts_reduce_bucket_
+
+    dp, max_norm, lr = 2, 0.5, 1e-2
+    rng = np.random.RandomState(7)
+    shapes = [(8, 6), (16,)]
+    w0 = [rng.randn(*s).astype(np.float32) for s in shapes]
+    grads = [[rng.randn(*s).astype(np.float32) for s in shapes] for _ in range(dp)]  # per replica
+    decays = (0.01, 0.0)
+
+    # reference composition on one replica with the averaged gradients
+    mean_g = [np.mean([grads[r][k] for r in range(dp)], axis=0) for k in range(len(shapes))]
+    norm = float(np.sqrt(sum((g.astype(np.float64) ** 2).sum() for g in mean_g)))
+    ir = popxl.Ir()
+    with ir.main_graph:
+        gn = popxl.constant(norm, popxl.float32)
+        ref_vars = []
+        for k, s in enumerate(shapes):
+            w = popxl.variable(w0[k], popxl.float32, f"w{k}")
+            g = popxl.constant(mean_g[k], popxl.float32)
+            facts, graph = AdamOptimizerStep().create_graph(w, g, lr=lr, beta1=0.9, beta2=0.95, eps=1e-5,
+                                                            weight_decay=decays[k], first_order_dtype=popxl.float32,
+                                                            global_norm=gn, global_norm_max=max_norm)
+            graph.bind(facts.init(f"opt{k}")).call(w, g, gn)
+            ref_vars.append(w)
+    with popxl.Session(ir, "cpu") as s:
+        s.run()
+        want = [s.get_tensor_data(w).copy() for w in ref_vars]
+    assert norm > max_norm  # the clip is active
+
+    # bucketed RTS composition over dp replicas
+    ir = popxl.Ir(replication=dp)
+    with ir.main_graph:
+        rg = ir.replica_grouping()
+        one = ir.replica_grouping(group_size=1)
+        ws, accs, masters, ms, vs = [], [], [], [], []
+        for k, s in enumerate(shapes):
+            ws.append(popxl.variable(w0[k].astype(np.float32), popxl.float32, f"w{k}"))
+            accs.append(popxl.variable(np.stack([grads[r][k] for r in range(dp)]), popxl.float32, f"acc{k}",
+                                       replica_grouping=one))
+            master, _ = popxl.replica_sharded_variable(w0[k], popxl.float32, f"master{k}", shard_grouping=rg)
+            m, _ = popxl.replica_sharded_variable(np.zeros(s, np.float32), popxl.float32, f"m{k}", shard_grouping=rg)
+            v, _ = popxl.replica_sharded_variable(np.zeros(s, np.float32), popxl.float32, f"v{k}", shard_grouping=rg)
+            masters.append(master), ms.append(m), vs.append(v)
+        step = popxl.variable(np.zeros((), np.float32), popxl.float32, "step")
+        sumsq = rts_reduce_bucket_(accs, rg)
+        total = ops.collectives.replicated_all_reduce(sumsq, "add", rg)
+        gmax = popxl.constant(max_norm, popxl.float32)
+        clip = ops.div(gmax, ops.maximum(ops.sqrt(total), gmax))
+        rts_adam_bucket_(ws, accs, masters, ms, vs, step, rg, lr=lr, weight_decays=decays, beta1=0.9, beta2=0.95, eps=1e-5,
+                         scale=clip, reduced=True)
+    with popxl.Session(ir, "cpu") as s:
+        s.run()
+        for k in range(len(shapes)):
+            got = s.get_tensor_data(ws[k])
+            np.testing.assert_allclose(got, want[k], rtol=1e-5, atol=1e-6)
+        assert float(s.get_tensor_data(step)) == 1.0
