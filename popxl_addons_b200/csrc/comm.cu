@@ -325,6 +325,41 @@ XL_API int xl_rts_adam_multi(const void* segs, int n_seg, int total_chunks, cons
   return (int)cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// All-gather by multicast: every rank stores its shard (nbytes, a multiple of 16) at byte offset rank * nbytes of a
+// buffer in every rank's symmetric memory with multimem.st (one store per 16 bytes reaches all ranks through NVSwitch),
+// then the ranks meet at a barrier, so that when the kernel has finished on a rank the whole buffer is valid there.
+// state: one zero-initialised device word of this rank (the kernel leaves it zero); uses signal channel `channel`.
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(512)
+    symm_all_gather_mc_kernel(const uint4* __restrict__ src, char* dst_mc, long long nvec, unsigned int* state,
+                              unsigned int* const* pads, int rank, int world, int channel, int* err, unsigned int limit) {
+  __shared__ int last_s;
+  char* dst = dst_mc + (long long)rank * nvec * 16;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x)
+    xl_multimem_st_b128(dst + i * 16, src[i]);
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int ticket = atomicAdd(state, 1u);
+    last_s = ticket == gridDim.x - 1;
+    if (last_s) *state = 0;
+  }
+  __syncthreads();
+  if (last_s && threadIdx.x < 32) xl_group_barrier(pads, rank, world, channel, err, limit);
+}
+
+XL_API int xl_symm_all_gather_mc(const void* src, void* dst_mc, long long nbytes, unsigned int* state, const void* pads_dev,
+                                 int rank, int world, int channel, int* err, cudaStream_t s) {
+  if (world > 32 || nbytes <= 0 || (nbytes & 15) || (((uintptr_t)src) & 15) || (((uintptr_t)dst_mc) & 15)) return -1;
+  const long long nvec = nbytes / 16;
+  const int grid = xl_grid_for(nvec, 512 * 4, 64);
+  symm_all_gather_mc_kernel<<<grid, 512, 0, s>>>((const uint4*)src, (char*)dst_mc, nvec, state,
+                                                 (unsigned int* const*)pads_dev, rank, world, channel, err,
+                                                 xl_host_comm_spin_limit);
+  return (int)cudaGetLastError();
+}
+
 // One-shot all-reduce (sum) of a small 16-bit tensor, latency-bound (the 128 KiB activations of token-by-token decoding).
 // Every rank copies its input into one half of a staging buffer in symmetric memory, the ranks meet at a barrier, and
 // every rank reads the sum of all replicas of that half through the multicast address (`multimem.ld_reduce`: NVSwitch

@@ -91,7 +91,8 @@ struct GemmParams {
   // epilogue warps of the other CTAs once they have run out of tiles; work items (an eighth of a tile) are handed out
   // by a counter.
   const uint8_t* ar_src_mc;         // multicast address of the partial buffers (C on every rank)
-  uint8_t* ar_dst_mc;               // multicast address of the result buffers
+  uint8_t* ar_dst_mc;               // multicast address of the result buffers; with accumulate == 6 (reduce-scatter:
+                                    //   every rank keeps only the sums of its own rows) this rank's (ar_rows x ldc) shard
   unsigned int* const* ar_flags;    // device array [world]: per rank, 2 * tiles words: [tile] parts arrived (written
                                     //   by all ranks), [tiles + tile] eighths reduced (owner only). All zero between launches.
   int ar_rows;                      // rows owned by each rank (a multiple of BLOCK_M)
@@ -229,9 +230,16 @@ __device__ __forceinline__ void ar_pull_reduce(const GemmParams& p, int tiles_m,
       off[it] = (row < p.M && col < p.N) ? ((long long)row * p.ldc + col) * 2 : -1;
       if (off[it] >= 0) v[it] = multimem_ld_reduce_16bit(p.ar_src_mc + off[it], bf);
     }
+    if (p.accumulate == 6) {  // reduce-scatter: plain stores into this rank's shard (rows are relative to its first row)
+      const long long shard0 = (long long)p.comm_rank * p.ar_rows * p.ldc * 2;
 #pragma unroll
-    for (int it = 0; it < ITERS; ++it)
-      if (off[it] >= 0) xl_multimem_st_b128(p.ar_dst_mc + off[it], v[it]);
+      for (int it = 0; it < ITERS; ++it)
+        if (off[it] >= 0) *reinterpret_cast<uint4*>(p.ar_dst_mc + (off[it] - shard0)) = v[it];
+    } else {
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it)
+        if (off[it] >= 0) xl_multimem_st_b128(p.ar_dst_mc + off[it], v[it]);
+    }
     __syncwarp();
     if (lane == 0) {
       const unsigned int prev = atomicAdd(flags + total_tiles + tile_id, 1u);
@@ -282,7 +290,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   // the first n_copy CTAs of a launch with an all-gather prologue only move data; the others are the GEMM's CTAs
-  const bool ar_pull = p.accumulate == 5;
+  const bool ar_pull = p.accumulate == 5 || p.accumulate == 6;  // 6: the owner keeps the sums (reduce-scatter)
   const int n_copy = (p.gather_mode || ar_pull) ? p.n_copy : 0;
   const bool is_copy = p.gather_mode && (int)blockIdx.x < n_copy;
   const bool is_reducer = ar_pull && (int)blockIdx.x < n_copy;
@@ -820,7 +828,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, in
   const int smem_bytes = (p.accumulate == 3 || p.accumulate == 4) ? TOTAL_COMM : L::TOTAL;
   const int tiles = ((p.M + BLOCK_M - 1) / BLOCK_M) * ((p.N + BLOCK_N - 1) / BLOCK_N) * p.batch;
   // copy / reducer CTAs and GEMM CTAs wait on one another: all must be resident
-  const int n_copy = (p.gather_mode || p.accumulate == 5) ? p.n_copy : 0;
+  const int n_copy = (p.gather_mode || p.accumulate >= 5) ? p.n_copy : 0;
   const int gemm_ctas = tiles < sm_count - n_copy ? tiles : sm_count - n_copy;
   const int grid = gemm_ctas + n_copy;
   // without a second operand pair the kernel never touches the second pair of maps: pass the first pair again
@@ -966,7 +974,9 @@ XL_API int xl_gemm_tcgen05(const void* a, const void* b, void* c, int M, int N, 
 // that pulls: see GemmParams::ar_src_mc. Operand conventions as xl_gemm_tcgen05 (a2 / b2 have the layouts of a / b;
 // K2 = 0 and null pointers: a single product).
 //   partial      this rank's buffer for its partial product (M x ldc, symmetric memory), partial_mc its multicast address
-//   result_mc    multicast address of the (M x ldc) result buffers: after the kernel every rank's buffer holds the sum
+//   result_mc    multicast address of the (M x ldc) result buffers: after the kernel every rank's buffer holds the sum.
+//                With scatter != 0 (reduce-scatter) instead this rank's own (M / world x ldc) result shard (an ordinary
+//                address): after the kernel it holds the sums of this rank's rows
 //   flags        device array [world] with every rank's flag words (2 * tiles words each, symmetric memory, zero before
 //                the first launch; the kernel leaves them zero), tiles = (M / 128) * ceil(N / 256 or 128)
 //   rows are split evenly: M must be a multiple of 128 * world. n_red: CTAs that only reduce (at least 1).
@@ -977,7 +987,7 @@ XL_API int xl_gemm_tcgen05_ar_pull(const void* a, const void* b, const void* a2,
                                    long long lda, long long ldb, long long lda2, long long ldb2, long long ldc,
                                    int ab_is_fp16, int c_dtype, float alpha, int* err, int sm_count, const void* comm_pads,
                                    int comm_rank, int comm_world, unsigned int* comm_local_sync, const void* flags,
-                                   int n_red, cudaStream_t s) {
+                                   int n_red, int scatter, cudaStream_t s) {
   if (M <= 0 || N <= 0 || K <= 0 || K2 < 0) return -1;
   if ((((uintptr_t)a) & 15) || (((uintptr_t)b) & 15) || (lda % 8) || (ldb % 8)) return -1;
   if (K2 && ((((uintptr_t)a2) & 15) || (((uintptr_t)b2) & 15) || (lda2 % 8) || (ldb2 % 8) || !a2 || !b2)) return -1;
@@ -1010,7 +1020,7 @@ XL_API int xl_gemm_tcgen05_ar_pull(const void* a, const void* b, const void* a2,
   p.M = M; p.N = N; p.K = K; p.batch = 1;
   p.a_mn = a_mn; p.b_mn = b_mn;
   p.C = partial; p.ldc = ldc; p.batch_stride_c = 0; p.c_dtype = c_dtype;
-  p.bias = nullptr; p.bias_dtype = 0; p.act = 0; p.accumulate = 5; p.step = nullptr;
+  p.bias = nullptr; p.bias_dtype = 0; p.act = 0; p.accumulate = scatter ? 6 : 5; p.step = nullptr;
   p.alpha = alpha; p.is_fp16 = ab_is_fp16; p.err = err;
   p.pads = (unsigned int* const*)comm_pads; p.comm_rank = comm_rank; p.comm_world = comm_world;
   p.local_sync = comm_local_sync; p.comm_spin_limit = xl_host_comm_spin_limit;

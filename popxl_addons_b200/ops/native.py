@@ -85,7 +85,8 @@ _rts_adam_multi = _sig("xl_rts_adam_multi", _c_p, _c_int, _c_int, _c_p, _c_int, 
                        _c_p, _c_p, _c_f, _c_f, _c_f, _c_f, _c_f, _c_int, _c_p)
 _gemm_ar_pull = _sig("xl_gemm_tcgen05_ar_pull", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
                      _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_f, _c_p, _c_int, _c_p, _c_int,
-                     _c_int, _c_p, _c_p, _c_int, _c_p)
+                     _c_int, _c_p, _c_p, _c_int, _c_int, _c_p)
+_symm_all_gather_mc = _sig("xl_symm_all_gather_mc", _c_p, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p)
 _gq_small = _sig("xl_gq_gemm_small_m", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
                  _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p)
 _rot_append = _sig("xl_rotary_append", _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -592,14 +593,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
 
 
 def gemm_all_reduce_pull(pairs, comm, partial: torch.Tensor, result: torch.Tensor, flags_ptrs: torch.Tensor,
-                         n_red: int = 8, alpha: float = 1.0):
+                         n_red: int = 8, alpha: float = 1.0, scatter: bool = False):
     """`result <- all_reduce over the group of (sum of a @ b over pairs)` in one kernel (one or two operand pairs, all
     with the same layouts). Every rank's GEMM CTAs store the partial product into `partial` (symmetric memory) and flag
     each tile at the rank that owns its rows; that rank adds the copies of the tile inside NVSwitch
     (`multimem.ld_reduce`) and writes the sum into every rank's `result` (`multimem.st`), tile by tile while the
     remaining tiles are still being multiplied. `partial`, `result`: `(M, N)` arena tensors of the group `comm`;
     `flags_ptrs`: int64 device tensor with every rank's address of the (zeroed) flag words (2 * tiles int32).
-    Returns `result` (valid once the kernel has finished) or NotImplemented."""
+    `scatter=True` is the reduce-scatter form: `result` is `(M / world, N)` (any device memory) and receives only the
+    sums of this rank's rows. Returns `result` (valid once the kernel has finished) or NotImplemented."""
     (a, b) = pairs[0]
     a2, b2 = pairs[1] if len(pairs) > 1 else (None, None)
     if len(pairs) > 2 or a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16) or a.dim() != 2 or b.dim() != 2:
@@ -617,21 +619,23 @@ def gemm_all_reduce_pull(pairs, comm, partial: torch.Tensor, result: torch.Tenso
                 or a2.shape[0] != M or b2.shape[1] != N or a2.shape[1] != b2.shape[0]:
             return NotImplemented
         K2, lda2, ldb2 = a2.shape[1], m2[1], n2[1]
-    if partial.shape != (M, N) or result.shape != (M, N) or partial.dtype != a.dtype or result.dtype != a.dtype \
+    rows_out = M // comm.world if scatter else M
+    if partial.shape != (M, N) or result.shape != (rows_out, N) or partial.dtype != a.dtype or result.dtype != a.dtype \
             or partial.stride(1) != 1 or result.stride() != partial.stride():
         return NotImplemented
-    mc_p, mc_r = comm.arena.multicast_ptr(partial), comm.arena.multicast_ptr(result)
+    mc_p = comm.arena.multicast_ptr(partial)
+    mc_r = result.data_ptr() if scatter else comm.arena.multicast_ptr(result)
     if not mc_p or not mc_r or M % (128 * comm.world):
         return NotImplemented
     rc = _gemm_ar_pull(a.data_ptr(), b.data_ptr(), a2.data_ptr() if a2 is not None else None,
                        b2.data_ptr() if b2 is not None else None, partial.data_ptr(), mc_p, mc_r, M, N, K, K2, a_mn, b_mn,
                        lda, ldb, lda2, ldb2, partial.stride(0), int(a.dtype == torch.float16), _CODE[a.dtype], float(alpha),
                        comm.err.data_ptr(), _sms(a.device), comm.arena.pads_dev.data_ptr(), comm.rank, comm.world,
-                       comm.arena.local_sync.data_ptr(), flags_ptrs.data_ptr(), int(n_red), _stream())
+                       comm.arena.local_sync.data_ptr(), flags_ptrs.data_ptr(), int(n_red), int(bool(scatter)), _stream())
     if rc < 0:
         return NotImplemented
-    _check(rc, "gemm_ar_pull_tcgen05")
-    _count("gemm_ar_pull_tcgen05")
+    _check(rc, "gemm_rs_pull_tcgen05" if scatter else "gemm_ar_pull_tcgen05")
+    _count("gemm_rs_pull_tcgen05" if scatter else "gemm_ar_pull_tcgen05")
     return result
 
 

@@ -188,9 +188,26 @@ def matmul2_all_reduce(ex, op, a1_vals, w1_vals, a2_vals, w2_vals):
     return NotImplemented if out is None else [out]
 
 
+def gemm_reduce_scatter_pull(ctx: GroupContext, pairs, n_red: Optional[int] = None):
+    """Rows `[rank*M/world, (rank+1)*M/world)` of `sum over ranks (sum of a @ w over pairs)` as one pulling kernel: the
+    partial products stay in each rank's buffer, the owner of a row block adds the ranks' copies inside NVSwitch
+    (`multimem.ld_reduce`) and keeps the sums. Returns a fresh `(M / world, N)` tensor or NotImplemented."""
+    nat = _lib()
+    a0, w0 = pairs[0]
+    M, N = a0.shape[0], w0.shape[-1]
+    if not ctx.arena.mc_base or M % (128 * ctx.world) or N % 8 or a0.dtype not in (torch.bfloat16, torch.float16):
+        return NotImplemented
+    buf = _pull_buffers(ctx, M, N, a0.dtype)
+    out = torch.empty((M // ctx.world, N), dtype=a0.dtype, device=a0.device)
+    res = nat.gemm_all_reduce_pull(pairs, ctx, buf["partial"], out, buf["flags"],
+                                   n_red=_AR_PULL_CTAS if n_red is None else n_red, scatter=True)
+    return out if res is not NotImplemented else NotImplemented
+
+
 def matmuls_reduce_scatter(ex, op, *vals):
-    """`reduce_scatter(a1 @ w1 [+ a2 @ w2])` over the rows: every GEMM's epilogue adds its tiles into the shard of the
-    rank that owns the rows (`red.add` over NVLink). Returns the flat shard."""
+    """`reduce_scatter(a1 @ w1 [+ a2 @ w2])` over the rows as one kernel: pulling (NVSwitch adds the partial tiles on the
+    way into the owner of the rows) where multicast is available, else every GEMM's epilogue adds its tiles into the
+    owner's shard (`red.add` over NVLink). Returns the flat shard."""
     nat = _lib()
     ctx = runtime(ex).context(op.attrs["group"])
     pairs = [(vals[i][0], vals[i + 1][0]) for i in range(0, len(vals), 2)]
@@ -198,6 +215,10 @@ def matmuls_reduce_scatter(ex, op, *vals):
     M, N = a0.shape[0], w0.shape[-1]
     if ctx.world == 1 or M % ctx.world or N % 8 or a0.dtype not in (torch.bfloat16, torch.float16):
         return NotImplemented
+    if _AR_PULL and _MC_ALL_REDUCE and len(pairs) <= 2:
+        out = gemm_reduce_scatter_pull(ctx, pairs)
+        if out is not NotImplemented:
+            return [out.reshape(-1)]
     shard = ctx.arena.ring((M // ctx.world, N), a0.dtype)
     shard.zero_()
     dst = _peer_ptr_tensor(ctx, shard)
@@ -209,13 +230,43 @@ def matmuls_reduce_scatter(ex, op, *vals):
     return [shard.reshape(-1).clone()]
 
 
+def all_gather_multicast(ctx: GroupContext, shard: torch.Tensor) -> Optional[torch.Tensor]:
+    """All-gather of equally sized 16-byte-multiple shards along the first axis: every rank multicasts its shard into the
+    full buffer of all ranks (`multimem.st`), one kernel including the closing barrier. The result lives in a ring of two
+    arena buffers (valid until the second next gather of the same shape). None if unsupported."""
+    nat = _lib()
+    nbytes = shard.numel() * shard.element_size()
+    if not ctx.arena.mc_base or not _MC_ALL_REDUCE or nbytes % 16 or not shard.is_contiguous() or shard.data_ptr() % 16:
+        return None
+    full = ctx.arena.ring((shard.shape[0] * ctx.world, *shard.shape[1:]), shard.dtype)
+    state = ctx.arena.local_sync[12:13]
+    rc = nat._symm_all_gather_mc(shard.data_ptr(), ctx.arena.multicast_ptr(full), nbytes, state.data_ptr(),
+                                 ctx.arena.pads_dev.data_ptr(), ctx.rank, ctx.world, 3, ctx.err.data_ptr(), nat._stream())
+    if rc == -1:
+        return None
+    nat._check(rc, "symm_all_gather_mc")
+    nat._count("symm_all_gather_mc")
+    return full
+
+
 def all_gather_matmul(ex, op, hs_vals, w_vals):
-    """`all_gather(h_s) @ w`: the GEMM's copy CTAs pull the peers' rows into this rank's full-size operand while its
-    other CTAs start on the local rows. Returns `(product, gathered operand)`."""
+    """`all_gather(h_s) @ w`. Returns `(product, gathered operand)`. Where multicast is available the rows are gathered by
+    one multicast kernel (each rank stores its rows into every rank's buffer) and the product is a plain GEMM; else the
+    GEMM's copy CTAs pull the peers' rows into this rank's full-size operand while its other CTAs start on the local
+    rows."""
+    nat = _lib()
     ctx = runtime(ex).context(op.attrs["group"])
     h_s, w = hs_vals[0], w_vals[0]
     rows, k = h_s.shape
-    if ctx.world == 1 or rows % 128 or h_s.dtype not in (torch.bfloat16, torch.float16) or w.dtype != h_s.dtype:
+    if ctx.world == 1 or h_s.dtype not in (torch.bfloat16, torch.float16) or w.dtype != h_s.dtype:
+        return NotImplemented
+    full = all_gather_multicast(ctx, h_s) if _AR_PULL else None
+    if full is not None:
+        y = nat.gemm(full, w)
+        if y is NotImplemented:
+            return NotImplemented
+        return [y], [full.clone()]  # the ring buffer is reused two gathers later; the graph keeps this value longer
+    if rows % 128:
         return NotImplemented
     full, own = gathered_operand(ctx, rows * ctx.world, k, h_s.dtype, 128, "sp")
     own.copy_(h_s)
@@ -358,6 +409,21 @@ class FusedComm(DistComm):
                     return [t]
                 return [out]
         return super().all_reduce(vals, grouping, op, inplace, async_ok)
+
+
+def _fused_all_gather(self, vals, grouping):
+    """`DistComm.all_gather` served by the multicast kernel where it applies."""
+    t = vals[0]
+    if grouping.group_size > 1 and _AR_PULL and t.is_cuda:
+        ctx = runtime(self._session).context(grouping)
+        flat = t.reshape(-1).contiguous()
+        full = all_gather_multicast(ctx, flat)
+        if full is not None:
+            return [full.clone()]
+    return DistComm.all_gather(self, vals, grouping)
+
+
+FusedComm.all_gather = _fused_all_gather
 
 
 def group_barrier(ctx: GroupContext, channel: int = 4):

@@ -152,6 +152,8 @@ def main():
         saved, nat._FLASH_ATTENTION = nat._FLASH_ATTENTION, "0"
         try:
             default = graph_time_ms(lambda: nat.attention_qkv_cuda(qkv, sin, sin, S, H, D, 0, True, scale, True), reps=8)
+        except Exception:
+            raise
         finally:
             nat._FLASH_ATTENTION = saved
         rows.append(dict(kernel=name + " (GEMM + softmax + GEMM)", shape=f"{H}x{S}x{S}x{D}", ms=default,
@@ -164,14 +166,39 @@ def main():
         # fwd + bwd of the op as the training step runs it (forward as dispatched by default, backward GEMM-based)
         do = torch.randn(S, hd, device="cuda", dtype=bf)
 
-        def fwd_bwd():
-            out, rot, lse = nat.attention_qkv_cuda(qkv, sin, sin, S, H, D, 0, True, scale, False)
-            return nat.attention_qkv_grad_cuda(rot, lse, do, sin, sin, S, H, D, 0, True, scale)
+        kw = dict(seq_len=S, n_heads=H, head_dim=D, rotary_dim=0, causal=True, scale=scale)
 
-        both = graph_time_ms(fwd_bwd, reps=4)
-        rows.append(dict(kernel=name.replace("fwd", "fwd+bwd") + " (as dispatched)", shape=f"{H}x{S}x{S}x{D}", ms=both,
-                         tflops=3.5 * fl / both / 1e9, frac_of_peak=3.5 * fl / both / 1e9 / peaks["bf16_tflops"],
-                         lib_ms=both, lib_tflops=3.5 * fl / both / 1e9, vs_lib=1.0, lib_name="itself"))
+        def fwd_bwd():
+            out, rot, lse = nat.attention_qkv_cuda(qkv, sin, sin, inplace=False, **kw)
+            return nat.attention_qkv_grad_cuda(rot, lse, do, sin, sin, out, **kw)
+
+        # 7 products of 2*S*S*D/2 FLOPs per head: 2 forward, 5 backward (scores and dP recomputed / formed once)
+        for fused_bwd in (False, True):
+            saved_bwd, nat._FLASH_ATTENTION_BWD = nat._FLASH_ATTENTION_BWD, fused_bwd
+            try:
+                both = graph_time_ms(fwd_bwd, reps=4)
+            finally:
+                nat._FLASH_ATTENTION_BWD = saved_bwd
+            tag = "backward with scores on chip" if fused_bwd else "backward from GEMMs + softmax kernels"
+            rows.append(dict(kernel=name.replace("fwd", "fwd+bwd") + f" ({tag})", shape=f"{H}x{S}x{S}x{D}", ms=both,
+                             tflops=3.5 * fl / both / 1e9, frac_of_peak=3.5 * fl / both / 1e9 / peaks["bf16_tflops"],
+                             lib_ms=both, lib_tflops=3.5 * fl / both / 1e9, vs_lib=1.0, lib_name="itself"))
+        # PyTorch's fused scaled-dot-product attention on the same problem (forward + backward), for reference
+        q4, k4, v4 = (qkv[:, i * hd:(i + 1) * hd].reshape(1, S, H, D).transpose(1, 2).detach().clone().requires_grad_(True)
+                      for i in range(3))
+        do4 = do.reshape(1, S, H, D).transpose(1, 2)
+
+        def sdpa():
+            o4 = torch.nn.functional.scaled_dot_product_attention(q4, k4, v4, is_causal=True, scale=scale)
+            return torch.autograd.grad(o4, (q4, k4, v4), do4)
+
+        try:
+            lib = graph_time_ms(sdpa, reps=4)
+            rows.append(dict(kernel=name.replace("fwd", "fwd+bwd") + " (torch SDPA)", shape=f"{H}x{S}x{S}x{D}", ms=lib,
+                             tflops=3.5 * fl / lib / 1e9, frac_of_peak=3.5 * fl / lib / 1e9 / peaks["bf16_tflops"],
+                             lib_ms=lib, lib_tflops=3.5 * fl / lib / 1e9, vs_lib=1.0, lib_name="itself"))
+        except Exception as e:  # the library may not capture or may not take this head size
+            print(f"torch SDPA row skipped: {type(e).__name__}: {e}")
 
     attention_row("attention fwd causal gptj", 2048, 16, 256)
     attention_row("attention fwd causal gptj tp4", 2048, 4, 256)

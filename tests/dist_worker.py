@@ -224,6 +224,27 @@ def main():
         torch.cuda.synchronize()
         result["ar_pull2_repeat_err"] = float((got.float() - full2).abs().max() / full2.abs().max())
 
+        # reduce-scatter by pulling (the owner keeps the sums) and all-gather by multicast
+        mine2 = fused.gemm_reduce_scatter_pull(ctx, [(a, w), (a2, w2)], n_red=args.n_red)
+        assert mine2 is not NotImplemented
+        torch.cuda.synchronize()
+        want2 = full2[rank * (M // world):(rank + 1) * (M // world)]
+        result["rs_pull2_err"] = float((mine2.float() - want2).abs().max() / want2.abs().max())
+        result["rs_pull2_ms"] = timed(lambda: fused.gemm_reduce_scatter_pull(ctx, [(a, w), (a2, w2)], n_red=args.n_red))
+        shard_rows = (torch.randn(M // world, N, device=dev) * 0.1).bfloat16()
+        gathered_ref = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        dist.all_gather_into_tensor(gathered_ref, shard_rows)
+        got = fused.all_gather_multicast(ctx, shard_rows)
+        assert got is not None
+        torch.cuda.synchronize()
+        result["ag_mc_ok"] = bool(torch.equal(got, gathered_ref))
+        for _ in range(9):  # the ring of two buffers and the barrier channel, many calls back to back
+            got = fused.all_gather_multicast(ctx, shard_rows)
+        torch.cuda.synchronize()
+        result["ag_mc_repeat_ok"] = bool(torch.equal(got, gathered_ref))
+        result["ag_mc_ms"] = timed(lambda: fused.all_gather_multicast(ctx, shard_rows))
+        result["ag_nccl_ms"] = timed(lambda: dist.all_gather_into_tensor(gathered_ref, shard_rows))
+
         def nccl_ar2():
             y = native.gemm(a, w)
             native.gemm(a2, w2, out=y, accumulate=1)

@@ -31,7 +31,7 @@ def launch(nproc, *worker_args, timeout=600, env=None):
     return json.loads(lines[-1])
 
 
-def simulated(tp, dp, dtype, steps=3, big=False, fused=True):
+def simulated(tp, dp, dtype, steps=3, big=False, fused=True, sp=False):
     from popxl_addons_b200.models import decoder as dec
     from popxl_addons_b200.models.gptj import GPTJConfig
     from popxl_addons_b200.models.trainer import DecoderTrainer
@@ -41,6 +41,7 @@ def simulated(tp, dp, dtype, steps=3, big=False, fused=True):
     dec._SEED[0] = 0
     cfg = (GPTJConfig.tiny(dtype=dtype, tp=tp, dp=dp, **({"seq_len": 512} if big == 2 else {})) if big
            else dec.DecoderConfig.tiny("gptj", dtype=dtype, tp=tp, dp=dp))
+    cfg.sequence_parallel = bool(sp)
     t = DecoderTrainer(cfg, micro_batches=2, device="cpu", lr=1e-2 if big != 2 else 2e-3, fused_collectives=fused)
     return [t.step(global_tokens(cfg, 2, seed=s)) for s in range(steps)]
 
@@ -147,6 +148,23 @@ def test_gpu_ranks_fused_collectives(tp, dp):
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
+@pytest.mark.parametrize("tp", [2, 4])
+def test_gpu_ranks_sequence_parallel(tp):
+    """Sequence parallelism on GPUs: the residual stream sharded over the tokens of the TP group, reduce-scatter by
+    pulling inside the row-parallel GEMMs, all-gather by multicast before the column-parallel ones; must track the CPU
+    simulation of the same program."""
+    _need_gpus(tp)
+    ref = simulated(tp, 1, "bfloat16", big=2, sp=True)
+    got = launch(tp, "--device", "cuda", "--tp", str(tp), "--dp", "1", "--dtype", "bfloat16", "--big", "2", "--sp", "1",
+                 timeout=600)
+    np.testing.assert_allclose(got["losses"], ref, rtol=3e-2)
+    kernels = got["kernels"]
+    assert kernels.get("gemm_rs_pull_tcgen05", 0) > 0 and kernels.get("symm_all_gather_mc", 0) > 0, kernels
+    assert not got.get("fallbacks") or all(k.startswith("fused:") for k in got["fallbacks"]), got.get("fallbacks")
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
 @pytest.mark.parametrize("nproc", [2, 4])
 def test_gpu_rts_bucket_optimizer_with_and_without_clipping(nproc):
     """One launch per bucket: reduce-scatter + AdamW + all-gather fused, and the clipped form (reduce + sum of squares,
@@ -180,6 +198,7 @@ def test_gpu_gemm_reduce_scatter_and_all_gather_gemm(nproc, m, n, k):
     assert res["rs_err"] < 2e-2 and res["ag_a_err"] < 2e-2 and res["ag_b_err"] < 2e-2 and res["ar_err"] < 2e-2
     assert res["ar_pull_err"] < 2e-2 and res["ar_pull2_err"] < 2e-2 and res["ar_pull2_t_err"] < 2e-2, res
     assert res["ar_pull2_repeat_err"] < 2e-2, res
+    assert res["rs_pull2_err"] < 2e-2 and res["ag_mc_ok"] and res["ag_mc_repeat_ok"], res
     assert res["ag_a_gathered_ok"] and res["ag_b_gathered_ok"]
     assert res["ar_ln_err"] < 0.1  # bf16 rounding of the summed update (magnitudes ~ 4)
 
