@@ -12,7 +12,7 @@
 // key-stationary kernel: with head dimension 256 the dK and dV accumulators alone fill the 512 TMEM columns, so a
 // single kernel cannot hold them next to the score tiles.
 //
-//   warp 0      TMA producer : Q and dO tiles once, then K / V blocks into a 2-stage shared-memory ring
+//   warp 0      TMA producer : Q and dO tiles once, then K blocks and V blocks into two 2-stage shared-memory rings
 //   warp 1      MMA issuer   : S_j = Q K_j^T and dP_j = dO V_j^T into one of two TMEM buffer pairs (block j+1 is issued
 //                              before dS_j is awaited, so it overlaps the element-wise work on block j), then
 //                              dQ += dS_j K_j (K_j consumed MN-major: no transpose)
@@ -29,7 +29,8 @@ namespace {
 
 constexpr int BLOCK_Q = 128;
 constexpr int UMMA_K = 16;
-constexpr int KV_STAGES = 2;
+constexpr int K_STAGES = 3;  // a K block is held until the third product of its keys: one more stage than V
+constexpr int V_STAGES = 2;
 constexpr int NUM_EW_WARPS = 4;
 constexpr int NUM_THREADS = 64 + 32 * NUM_EW_WARPS;
 constexpr uint32_t SPIN_LIMIT = xl_tc::MBAR_SPIN_LIMIT;
@@ -78,8 +79,7 @@ struct BwdSmem {
   static constexpr int K_BYTES = BKV * D * 2;           // D/64 boxes of (BKV rows x 128 B): K-major for S, MN-major for dQ
   static constexpr int V_BYTES = BKV * D * 2;
   static constexpr int DS_BYTES = BLOCK_Q * BKV * 2;    // BKV/8 chunk columns of 16 row groups of (8 rows x 16 B)
-  static constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
-  static constexpr int TILE_BYTES = 2 * Q_BYTES + KV_STAGES * STAGE_BYTES + 2 * DS_BYTES;
+  static constexpr int TILE_BYTES = 2 * Q_BYTES + K_STAGES * K_BYTES + V_STAGES * V_BYTES + 2 * DS_BYTES;
   static constexpr int NEEDED = TILE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
   // more than half of an SM's shared memory, so that two CTAs (each holding all 512 TMEM columns) never share an SM
   static constexpr int TOTAL = NEEDED > 120 * 1024 ? NEEDED : 120 * 1024;
@@ -95,18 +95,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
   uint8_t* sDO = smem + L::Q_BYTES;
-  uint8_t* sKV = smem + 2 * L::Q_BYTES;
-  uint8_t* sDS = sKV + KV_STAGES * L::STAGE_BYTES;  // two buffers
+  uint8_t* sK = smem + 2 * L::Q_BYTES;              // K_STAGES blocks
+  uint8_t* sV = sK + K_STAGES * L::K_BYTES;          // V_STAGES blocks
+  uint8_t* sDS = sV + V_STAGES * L::V_BYTES;         // two buffers
   uint64_t* bars = (uint64_t*)(smem + L::TILE_BYTES);
   uint64_t* qdo_full = bars;               // [1]
-  uint64_t* kv_full = bars + 1;            // [KV_STAGES]
-  uint64_t* kv_empty = bars + 3;           // [KV_STAGES]
-  uint64_t* sdp_full = bars + 5;           // [2]  S and dP of a block are complete
-  uint64_t* sdp_empty = bars + 7;          // [2]  the element-wise warps have read them
-  uint64_t* ds_full = bars + 9;            // [2]  dS tile written to shared memory
-  uint64_t* ds_empty = bars + 11;          // [2]  the third product has read it
-  uint64_t* dq_done = bars + 13;           // [1]  all products complete (the accumulator is final)
-  uint32_t* tmem_base_slot = (uint32_t*)(bars + 14);
+  uint64_t* k_full = bars + 1;             // [K_STAGES]  K and V blocks have rings of their own: a V block is free as
+  uint64_t* k_empty = bars + 4;            // [K_STAGES]  soon as dP is computed, a K block only after the third product
+  uint64_t* v_full = bars + 7;             // [V_STAGES]
+  uint64_t* v_empty = bars + 9;            // [V_STAGES]
+  uint64_t* sdp_full = bars + 11;          // [2]  S and dP of a block are complete
+  uint64_t* sdp_empty = bars + 13;         // [2]  the element-wise warps have read them
+  uint64_t* ds_full = bars + 15;           // [2]  dS tile written to shared memory
+  uint64_t* ds_empty = bars + 17;          // [2]  the third product has read it
+  uint64_t* dq_done = bars + 19;           // [1]  all products complete (the accumulator is final)
+  uint32_t* tmem_base_slot = (uint32_t*)(bars + 20);
   volatile int* abort_flag = (volatile int*)(tmem_base_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -121,9 +124,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+    for (int s = 0; s < K_STAGES; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+    }
+    for (int s = 0; s < V_STAGES; ++s) {
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&sdp_full[s], 1);
@@ -149,37 +156,43 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
   if (warp == 0) {
     // ------------------------------------------------ TMA producer ------------------------------------------------
-    if (elect_one()) {
-      mbar_expect_tx(qdo_full, 2 * L::Q_BYTES);
+    // lane 0 loads Q and dO and streams the K blocks, lane 1 streams the V blocks: each waits only on its own ring
+    if (lane < 2) {
+      const bool for_k = lane == 0;
+      if (for_k) {
+        mbar_expect_tx(qdo_full, 2 * L::Q_BYTES);
 #pragma unroll
-      for (int kb = 0; kb < D / 64; ++kb) {  // boxes {64 features, 128 rows}
-        tma_load_2d(sQ + kb * (BLOCK_Q * 128), &map_q, qdo_full, p.q_col + h * D + kb * 64, row0 + q0);
-        tma_load_2d(sDO + kb * (BLOCK_Q * 128), &map_do, qdo_full, h * D + kb * 64, row0 + q0);
+        for (int kb = 0; kb < D / 64; ++kb) {  // boxes {64 features, 128 rows}
+          tma_load_2d(sQ + kb * (BLOCK_Q * 128), &map_q, qdo_full, p.q_col + h * D + kb * 64, row0 + q0);
+          tma_load_2d(sDO + kb * (BLOCK_Q * 128), &map_do, qdo_full, h * D + kb * 64, row0 + q0);
+        }
       }
+      uint64_t* full = for_k ? k_full : v_full;
+      uint64_t* empty = for_k ? k_empty : v_empty;
+      const int stages = for_k ? K_STAGES : V_STAGES;
       bool ok = true;
       int issued = 0;
       for (int j = 0; j < n_kv && ok; ++j) {
-        const int stage = j % KV_STAGES;
-        if (j >= KV_STAGES) {
-          ok = mbar_wait(&kv_empty[stage], (uint32_t)(j / KV_STAGES - 1) & 1u, abort_flag, p.err, ERR_KV_EMPTY_WAIT);
+        const int stage = j % stages;
+        if (j >= stages) {
+          ok = mbar_wait(&empty[stage], (uint32_t)(j / stages - 1) & 1u, abort_flag, p.err, ERR_KV_EMPTY_WAIT);
           if (!ok) break;
         }
-        uint8_t* sK = sKV + stage * L::STAGE_BYTES;
-        uint8_t* sV = sK + L::K_BYTES;
-        mbar_expect_tx(&kv_full[stage], L::STAGE_BYTES);
+        uint8_t* dst = for_k ? sK + stage * L::K_BYTES : sV + stage * L::V_BYTES;
+        mbar_expect_tx(&full[stage], L::K_BYTES);
         const int k0 = row0 + j * BKV;
+        const int col = (for_k ? p.k_col : p.v_col) + h * D;
 #pragma unroll
-        for (int kb = 0; kb < D / 64; ++kb) {  // boxes {64 features, BKV rows}
-          tma_load_2d(sK + kb * (BKV * 128), &map_kv, &kv_full[stage], p.k_col + h * D + kb * 64, k0);
-          tma_load_2d(sV + kb * (BKV * 128), &map_kv, &kv_full[stage], p.v_col + h * D + kb * 64, k0);
-        }
+        for (int kb = 0; kb < D / 64; ++kb)  // boxes {64 features, BKV rows}
+          tma_load_2d(dst + kb * (BKV * 128), &map_kv, &full[stage], col + kb * 64, k0);
         issued = j + 1;
       }
       if (!ok || *abort_flag) {
         // loads in flight target this CTA's shared memory: give them a bounded time to land before the CTA ends
-        for (uint32_t i = 0; i < SPIN_LIMIT && !mbar_try_wait(qdo_full, 0); ++i) {}
-        for (int j = max(0, issued - KV_STAGES); j < issued; ++j)
-          for (uint32_t i = 0; i < SPIN_LIMIT && !mbar_try_wait(&kv_full[j % KV_STAGES], (uint32_t)(j / KV_STAGES) & 1u); ++i) {}
+        if (for_k)
+          for (uint32_t i = 0; i < SPIN_LIMIT && !mbar_try_wait(qdo_full, 0); ++i) {}
+        for (int j = max(0, issued - stages); j < issued; ++j)
+          for (uint32_t i = 0; i < SPIN_LIMIT && !mbar_try_wait(&full[j % stages], (uint32_t)(j / stages) & 1u); ++i) {}
       }
     }
   } else if (warp == 1) {
@@ -193,14 +206,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                 ((uint32_t)(BLOCK_Q >> 4) << 24);
       bool ok = mbar_wait(qdo_full, 0, abort_flag, p.err, ERR_QDO_WAIT);
       auto issue_scores = [&](int j) -> bool {
-        const int stage = j % KV_STAGES, sb = j & 1;
-        if (!mbar_wait(&kv_full[stage], (uint32_t)(j / KV_STAGES) & 1u, abort_flag, p.err, ERR_KV_FULL_WAIT)) return false;
+        const int ks = j % K_STAGES, vs = j % V_STAGES, sb = j & 1;
+        if (!mbar_wait(&k_full[ks], (uint32_t)(j / K_STAGES) & 1u, abort_flag, p.err, ERR_KV_FULL_WAIT)) return false;
+        if (!mbar_wait(&v_full[vs], (uint32_t)(j / V_STAGES) & 1u, abort_flag, p.err, ERR_KV_FULL_WAIT)) return false;
         if (j >= 2 && !mbar_wait(&sdp_empty[sb], (uint32_t)(j / 2 - 1) & 1u, abort_flag, p.err, ERR_SDP_EMPTY_WAIT))
           return false;
         tcgen05_fence_after();
         const uint32_t q_addr = smem_u32(sQ), do_addr = smem_u32(sDO);
-        const uint32_t k_addr = smem_u32(sKV + stage * L::STAGE_BYTES);
-        const uint32_t v_addr = k_addr + L::K_BYTES;
+        const uint32_t k_addr = smem_u32(sK + ks * L::K_BYTES);
+        const uint32_t v_addr = smem_u32(sV + vs * L::V_BYTES);
 #pragma unroll
         for (int kb = 0; kb < D / 64; ++kb)
 #pragma unroll
@@ -217,6 +231,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const uint64_t db = make_smem_desc_sw128(v_addr + kb * (BKV * 128) + k * (UMMA_K * 2), 16);
             tcgen05_mma_f16(tmem_dp + sb * BKV, da, db, idesc_s, (kb | k) ? 1u : 0u);
           }
+        tcgen05_commit(&v_empty[vs]);  // the V block is free once dP is computed
         tcgen05_commit(&sdp_full[sb]);
         return true;
       };
@@ -230,9 +245,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         ok = mbar_wait(&ds_full[db_i], (uint32_t)(j / 2) & 1u, abort_flag, p.err, ERR_DS_FULL_WAIT);
         if (!ok) break;
         tcgen05_fence_after();
-        const int stage = j % KV_STAGES;
+        const int ks = j % K_STAGES;
         const uint32_t ds_addr = smem_u32(sDS + db_i * L::DS_BYTES);
-        const uint32_t k_addr = smem_u32(sKV + stage * L::STAGE_BYTES);
+        const uint32_t k_addr = smem_u32(sK + ks * L::K_BYTES);
 #pragma unroll
         for (int k = 0; k < BKV / UMMA_K; ++k) {
           // dS: chunk column c (8 keys) starts at c * 2048 bytes; one product step spans two of them
@@ -241,7 +256,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           const uint64_t dbk = make_smem_desc_sw128(k_addr + k * (UMMA_K * 128), BKV * 128);
           tcgen05_mma_f16(tmem_dq, da, dbk, idesc_dq, (j | k) ? 1u : 0u);
         }
-        tcgen05_commit(&kv_empty[stage]);   // K / V stage free once every product of this block has read it
+        tcgen05_commit(&k_empty[ks]);       // the K block is free once the third product has read it
         tcgen05_commit(&ds_empty[db_i]);    // and the dS buffer
         if (j == n_kv - 1) tcgen05_commit(dq_done);
       }

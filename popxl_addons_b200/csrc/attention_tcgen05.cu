@@ -6,7 +6,8 @@
 // leaves them; O is a column window of the (tokens x heads*D) output matrix. The S x S score matrix never leaves the
 // chip: one CTA owns 128 query rows and walks the key / value rows in blocks of BKV.
 //
-//   warp 0      TMA producer : Q tile once, then K / V blocks into a 2-stage shared-memory ring
+//   warp 0      TMA producer : Q tile once, then K blocks and V blocks into two 2-stage shared-memory rings (a K block is
+//                              released as soon as its scores are computed, so the next K load overlaps the softmax)
 //   warp 1      MMA issuer   : S_j = Q K_j^T into one of two TMEM score buffers, then O += P_j V_j into the TMEM output
 //                              accumulator (S_{j+1} is issued before P_j is awaited, so it overlaps the softmax of block j)
 //   warps 2..5  softmax      : one thread per query row. tcgen05.ld the score row, running max / sum (base-2 exponent),
@@ -72,13 +73,15 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   uint8_t* sP = sKV + KV_STAGES * L::STAGE_BYTES;
   uint64_t* bars = (uint64_t*)(smem + L::TILE_BYTES);
   uint64_t* q_full = bars;                 // [1]
-  uint64_t* kv_full = bars + 1;            // [KV_STAGES]
-  uint64_t* kv_empty = bars + 3;           // [KV_STAGES]
-  uint64_t* s_full = bars + 5;             // [2]
-  uint64_t* s_empty = bars + 7;            // [2]
-  uint64_t* p_full = bars + 9;             // [1]
-  uint64_t* pv_done = bars + 10;           // [1]
-  uint32_t* tmem_base_slot = (uint32_t*)(bars + 11);
+  uint64_t* k_full = bars + 1;             // [KV_STAGES]  K and V blocks have rings of their own: a K block is free as
+  uint64_t* k_empty = bars + 3;            // [KV_STAGES]  soon as its scores are computed, long before the V block of
+  uint64_t* v_full = bars + 5;             // [KV_STAGES]  the same keys, so the next K load overlaps the softmax
+  uint64_t* v_empty = bars + 7;            // [KV_STAGES]
+  uint64_t* s_full = bars + 9;             // [2]
+  uint64_t* s_empty = bars + 11;           // [2]
+  uint64_t* p_full = bars + 13;            // [1]
+  uint64_t* pv_done = bars + 14;           // [1]
+  uint32_t* tmem_base_slot = (uint32_t*)(bars + 15);
   volatile int* abort_flag = (volatile int*)(tmem_base_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -94,8 +97,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
@@ -119,39 +124,50 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
   if (warp == 0) {
     // ------------------------------------------------ TMA producer ------------------------------------------------
-    if (elect_one()) {
-      mbar_expect_tx(q_full, L::Q_BYTES);
+    // lane 0 loads Q and streams the K blocks, lane 1 streams the V blocks: each waits only on its own ring
+    if (lane < 2) {
+      const bool for_k = lane == 0;
+      if (for_k) {
+        mbar_expect_tx(q_full, L::Q_BYTES);
 #pragma unroll
-      for (int kb = 0; kb < D / 64; ++kb)  // boxes {64 features, 128 rows}
-        tma_load_2d(sQ + kb * (BLOCK_Q * 128), &map_q, q_full, p.q_col + h * D + kb * 64, row0 + q0);
+        for (int kb = 0; kb < D / 64; ++kb)  // boxes {64 features, 128 rows}
+          tma_load_2d(sQ + kb * (BLOCK_Q * 128), &map_q, q_full, p.q_col + h * D + kb * 64, row0 + q0);
+      }
+      uint64_t* full = for_k ? k_full : v_full;
+      uint64_t* empty = for_k ? k_empty : v_empty;
       bool ok = true;
       int issued = 0;
       for (int j = 0; j < n_kv && ok; ++j) {
         const int stage = j % KV_STAGES;
         if (j >= KV_STAGES) {
-          ok = mbar_wait(&kv_empty[stage], (uint32_t)(j / KV_STAGES - 1) & 1u, abort_flag, p.err, ERR_KV_EMPTY_WAIT);
+          ok = mbar_wait(&empty[stage], (uint32_t)(j / KV_STAGES - 1) & 1u, abort_flag, p.err, ERR_KV_EMPTY_WAIT);
           if (!ok) break;
         }
         uint8_t* sK = sKV + stage * L::STAGE_BYTES;
         uint8_t* sV = sK + L::K_BYTES;
-        mbar_expect_tx(&kv_full[stage], L::STAGE_BYTES);
         const int k0 = row0 + j * BKV;
+        if (for_k) {
+          mbar_expect_tx(&full[stage], L::K_BYTES);
 #pragma unroll
-        for (int kb = 0; kb < D / 64; ++kb)  // boxes {64 features, BKV rows}
-          tma_load_2d(sK + kb * (BKV * 128), &map_k, &kv_full[stage], p.k_col + h * D + kb * 64, k0);
+          for (int kb = 0; kb < D / 64; ++kb)  // boxes {64 features, BKV rows}
+            tma_load_2d(sK + kb * (BKV * 128), &map_k, &full[stage], p.k_col + h * D + kb * 64, k0);
+        } else {
+          mbar_expect_tx(&full[stage], L::V_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < BKV / 64; ++kk)
+          for (int kk = 0; kk < BKV / 64; ++kk)
 #pragma unroll
-          for (int jn = 0; jn < D / 64; ++jn)  // boxes {64 features, 64 rows}
-            tma_load_2d(sV + (kk * (D / 64) + jn) * 8192, &map_v, &kv_full[stage], p.v_col + h * D + jn * 64,
-                        k0 + kk * 64);
+            for (int jn = 0; jn < D / 64; ++jn)  // boxes {64 features, 64 rows}
+              tma_load_2d(sV + (kk * (D / 64) + jn) * 8192, &map_v, &full[stage], p.v_col + h * D + jn * 64,
+                          k0 + kk * 64);
+        }
         issued = j + 1;
       }
       if (!ok || *abort_flag) {
         // loads in flight target this CTA's shared memory: give them a bounded time to land before the CTA ends
-        for (uint32_t i = 0; i < SPIN_LIMIT && !mbar_try_wait(q_full, 0); ++i) {}
+        if (for_k)
+          for (uint32_t i = 0; i < SPIN_LIMIT && !mbar_try_wait(q_full, 0); ++i) {}
         for (int j = max(0, issued - KV_STAGES); j < issued; ++j)
-          for (uint32_t i = 0; i < SPIN_LIMIT && !mbar_try_wait(&kv_full[j % KV_STAGES], (uint32_t)(j / KV_STAGES) & 1u); ++i) {}
+          for (uint32_t i = 0; i < SPIN_LIMIT && !mbar_try_wait(&full[j % KV_STAGES], (uint32_t)(j / KV_STAGES) & 1u); ++i) {}
       }
     }
   } else if (warp == 1) {
@@ -166,7 +182,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err, ERR_Q_WAIT);
       auto issue_scores = [&](int j) -> bool {
         const int stage = j % KV_STAGES, sb = j & 1;
-        if (!mbar_wait(&kv_full[stage], (uint32_t)(j / KV_STAGES) & 1u, abort_flag, p.err, ERR_KV_FULL_WAIT)) return false;
+        if (!mbar_wait(&k_full[stage], (uint32_t)(j / KV_STAGES) & 1u, abort_flag, p.err, ERR_KV_FULL_WAIT)) return false;
         if (j >= 2 && !mbar_wait(&s_empty[sb], (uint32_t)(j / 2 - 1) & 1u, abort_flag, p.err, ERR_S_EMPTY_WAIT))
           return false;
         tcgen05_fence_after();
@@ -180,6 +196,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const uint64_t db = make_smem_desc(k_addr + kb * (BKV * 128) + k * (UMMA_K * 2), 16);
             tcgen05_mma_f16(tmem_s + sb * BKV, da, db, idesc_s, (kb | k) ? 1u : 0u);
           }
+        tcgen05_commit(&k_empty[stage]);  // the K block is free once its scores are computed
         tcgen05_commit(&s_full[sb]);
         return true;
       };
@@ -189,10 +206,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           ok = issue_scores(j + 1);
           if (!ok) break;
         }
+        const int stage = j % KV_STAGES;
+        ok = mbar_wait(&v_full[stage], (uint32_t)(j / KV_STAGES) & 1u, abort_flag, p.err, ERR_KV_FULL_WAIT);
+        if (!ok) break;
         ok = mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, p.err, ERR_P_FULL_WAIT);
         if (!ok) break;
         tcgen05_fence_after();
-        const int stage = j % KV_STAGES;
         const uint32_t p_addr = smem_u32(sP);
         const uint32_t v_addr = smem_u32(sKV + stage * L::STAGE_BYTES + L::K_BYTES);
 #pragma unroll
@@ -203,7 +222,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             const uint64_t db = make_smem_desc(v_addr + kk * (D / 64) * 8192 + k * (UMMA_K * 128), 8192);
             tcgen05_mma_f16(tmem_o, da, db, idesc_o, (j | kk | k) ? 1u : 0u);
           }
-        tcgen05_commit(&kv_empty[stage]);  // K / V stage free once these MMAs have read it
+        tcgen05_commit(&v_empty[stage]);   // the V block is free once these MMAs have read it
         tcgen05_commit(pv_done);           // output accumulator and the P tile are free again
       }
     }

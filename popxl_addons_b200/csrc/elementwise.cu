@@ -369,18 +369,31 @@ __global__ void __launch_bounds__(NORM_THREADS)
   }
 }
 
+// One CTA per 32 columns: 8 groups of 32 threads walk the per-CTA partial rows with stride 8 (coalesced 128-byte reads),
+// then the 8 group sums are added in a fixed order (deterministic).
 template <typename T>
-__global__ void norm_bwd_finish_kernel(const float* __restrict__ partial, T* __restrict__ dw, T* __restrict__ db,
-                                       int nparts, int cols) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
-  float sw = 0.f, sb = 0.f;
-  for (int p = 0; p < nparts; ++p) {
-    sw += partial[(long long)p * 2 * cols + c];
-    if (db) sb += partial[(long long)p * 2 * cols + cols + c];
+__global__ void __launch_bounds__(256)
+    norm_bwd_finish_kernel(const float* __restrict__ partial, T* __restrict__ dw, T* __restrict__ db, int nparts, int cols) {
+  __shared__ float sw[8][33], sb[8][33];
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  float aw = 0.f, ab = 0.f;
+  if (c < cols) {
+    for (int p = grp; p < nparts; p += 8) {
+      aw += partial[(long long)p * 2 * cols + c];
+      if (db) ab += partial[(long long)p * 2 * cols + cols + c];
+    }
   }
-  dw[c] = xl_from_float<T>(sw);
-  if (db) db[c] = xl_from_float<T>(sb);
+  sw[grp][lane] = aw;
+  sb[grp][lane] = ab;
+  __syncthreads();
+  if (grp == 0 && c < cols) {
+    float tw = 0.f, tb = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) { tw += sw[g][lane]; tb += sb[g][lane]; }
+    dw[c] = xl_from_float<T>(tw);
+    if (db) db[c] = xl_from_float<T>(tb);
+  }
 }
 
 // Number of CTAs (= rows of the scratch buffer) the backward kernels use for `rows` rows.
@@ -396,7 +409,7 @@ static int norm_bwd_launch(const void* x, const void* w, const float* mean, cons
   XL_DISPATCH_DTYPE(dtype, T, XL_DISPATCH_ITERS(iters, IT, {
     norm_bwd_kernel<T, RMS, IT><<<parts, NORM_THREADS, 0, s>>>((const T*)x, (const T*)w, mean, rstd, (const T*)g,
                                                               (T*)dx, partial, rows, cols);
-    norm_bwd_finish_kernel<T><<<(cols + 255) / 256, 256, 0, s>>>(partial, (T*)dw, (T*)db, parts, cols);
+    norm_bwd_finish_kernel<T><<<(cols + 31) / 32, 256, 0, s>>>(partial, (T*)dw, (T*)db, parts, cols);
   }));
   return (int)cudaGetLastError();
 }

@@ -226,17 +226,30 @@ __global__ void __launch_bounds__(ROW_THREADS)
 }
 
 template <typename T>
-__global__ void ln_shard_bwd_finish_kernel(const float* __restrict__ partial, T* __restrict__ dw, T* __restrict__ db,
-                                           int nparts, int cols) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
-  float sw = 0.f, sb = 0.f;
-  for (int p = 0; p < nparts; ++p) {
-    sw += partial[(long long)p * 2 * cols + c];
-    sb += partial[(long long)p * 2 * cols + cols + c];
+__global__ void __launch_bounds__(256)
+    ln_shard_bwd_finish_kernel(const float* __restrict__ partial, T* __restrict__ dw, T* __restrict__ db, int nparts,
+                               int cols) {
+  // one CTA per 32 columns; 8 groups of 32 threads walk the partial rows with stride 8, group sums added in a fixed order
+  __shared__ float sw[8][33], sb[8][33];
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + lane;
+  float aw = 0.f, ab = 0.f;
+  if (c < cols) {
+    for (int p = grp; p < nparts; p += 8) {
+      aw += partial[(long long)p * 2 * cols + c];
+      ab += partial[(long long)p * 2 * cols + cols + c];
+    }
   }
-  dw[c] = xl_from_float<T>(sw);
-  db[c] = xl_from_float<T>(sb);
+  sw[grp][lane] = aw;
+  sb[grp][lane] = ab;
+  __syncthreads();
+  if (grp == 0 && c < cols) {
+    float tw = 0.f, tb = 0.f;
+#pragma unroll
+    for (int g = 0; g < 8; ++g) { tw += sw[g][lane]; tb += sb[g][lane]; }
+    dw[c] = xl_from_float<T>(tw);
+    db[c] = xl_from_float<T>(tb);
+  }
 }
 
 }  // namespace
@@ -314,7 +327,7 @@ XL_API int xl_ln_shard_bwd_apply(const void* x, const void* w, const float* mean
   XL_DISPATCH_DTYPE(dtype, T, {
     ln_shard_bwd_apply_kernel<T><<<parts, ROW_THREADS, 0, s>>>((const T*)x, (const T*)w, mean, rstd, (const T*)g, gstats,
                                                               (T*)dx, scratch, rows, cols, hidden);
-    ln_shard_bwd_finish_kernel<T><<<(cols + 255) / 256, 256, 0, s>>>(scratch, (T*)dw, (T*)db, parts, cols);
+    ln_shard_bwd_finish_kernel<T><<<(cols + 31) / 32, 256, 0, s>>>(scratch, (T*)dw, (T*)db, parts, cols);
   });
   return (int)cudaGetLastError();
 }

@@ -98,6 +98,7 @@ class Session:
         self._io_stream = (torch.cuda.Stream(self.device) if self.device.type == "cuda"
                            and os.environ.get("XL_IO_STREAM", "1") != "0" else None)
         self._io_ready: Dict[int, tuple] = {}  # id(tensor) -> (event recorded on the IO stream, tensor)
+        self._io_dirty = False                 # an op ran on the IO stream since the streams were last joined
         self._uncapturable: set = set()        # loops whose capture failed once: they run eagerly from then on
         self._init_state()
 
@@ -640,6 +641,7 @@ class Session:
             if on_io:
                 compute = torch.cuda.current_stream(self.device)
                 self._io_stream.wait_stream(compute)  # everything queued on the compute stream so far is visible
+                self._io_dirty = True
                 for t in op.inputs:
                     for x in env.get(t) or ():
                         if isinstance(x, torch.Tensor) and x.is_cuda:
@@ -702,9 +704,12 @@ class Session:
         """The compute stream waits for everything queued on the IO stream and for every collective in flight (end of a
         run, end of a loop iteration, end of a captured loop body)."""
         self.comm.wait_all()
-        if self._io_stream is not None:
+        if self._io_stream is not None and self._io_dirty:
+            # only when an op ran there since the last join: inside a graph capture a wait on a stream that never forked
+            # from the capturing stream would invalidate the capture
             torch.cuda.current_stream(self.device).wait_stream(self._io_stream)
             self._io_ready.clear()
+            self._io_dirty = False
 
     @staticmethod
     def _free_dead(frees, i, env):
