@@ -96,6 +96,7 @@ struct GemmParams {
   unsigned int* const* ar_flags;    // device array [world]: per rank, 2 * tiles words: [tile] parts arrived (written
                                     //   by all ranks), [tiles + tile] eighths reduced (owner only). All zero between launches.
   int ar_rows;                      // rows owned by each rank (a multiple of BLOCK_M)
+  unsigned long long* dbg;          // optional: 4 timestamps (ns) per CTA: start, tiles done, reduce done, finish done
 };
 
 // k-block range of a tile under the causal modes; false: the tile is skipped altogether
@@ -160,6 +161,11 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   nb = in_group / rows;
 }
 
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* ptr) {
   unsigned int v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
@@ -335,8 +341,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 
   if (is_reducer) {
     // ------------------------------------------------ all-reduce reducer CTA: all ten warps reduce ----------------
+    if (p.dbg && threadIdx.x == 0) p.dbg[blockIdx.x * 4] = p.dbg[blockIdx.x * 4 + 1] = global_timer_ns();
     ar_pull_reduce<BLOCK_N>(p, tiles_m, tiles_n, abort_flag);
+    if (p.dbg && threadIdx.x == 0) p.dbg[blockIdx.x * 4 + 2] = global_timer_ns();
     ar_pull_finish(p, (unsigned int)(n_copy * (NUM_THREADS / 32) + ncta * NUM_EPI_WARPS));
+    if (p.dbg && threadIdx.x == 0) p.dbg[blockIdx.x * 4 + 3] = global_timer_ns();
   } else if (is_copy) {
     // ------------------------------------------------ all-gather copy CTA -----------------------------------------
     // Lane 0 of warp 0 streams this CTA's share of the remote row blocks peer -> shared-memory ring -> local matrix
@@ -558,6 +567,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     float mean_a = 0.f, mean_b = 1.f;
+    if (p.dbg && ar_pull && warp == 2 && lane == 0) p.dbg[blockIdx.x * 4] = global_timer_ns();
     const bool push = p.accumulate == 3 || p.accumulate == 4;  // tiles are pushed into the peers' buffers
     const int acc_mode = ar_pull ? 0 : p.accumulate;           // the pull all-reduce stores plain partial tiles
     const float alpha_eff = p.alpha_log2 ? p.alpha * exp2f(*p.alpha_log2) : p.alpha;
@@ -766,8 +776,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     }
     if (ar_pull) {
       // out of tiles: help with the reduction of this rank's rows until nothing is left, then check in
+      const bool stamp = p.dbg && warp == 2 && lane == 0;
+      if (stamp) p.dbg[blockIdx.x * 4 + 1] = global_timer_ns();
       if (ok) ar_pull_reduce<BLOCK_N>(p, tiles_m, tiles_n, abort_flag);
+      if (stamp) p.dbg[blockIdx.x * 4 + 2] = global_timer_ns();
       ar_pull_finish(p, (unsigned int)(n_copy * (NUM_THREADS / 32) + ncta * NUM_EPI_WARPS));
+      if (stamp) p.dbg[blockIdx.x * 4 + 3] = global_timer_ns();
     }
     if (push) {
       // The kernel may only finish once every rank's pushes have landed here: the last epilogue warp of this rank
@@ -895,7 +909,7 @@ XL_API int xl_gemm_tcgen05_fused(const void* a, const void* b, void* c, int M, i
   p.gather_block_bytes = 0;
   p.fp8_a = p.fp8_b = -1;
   p.alpha_log2 = nullptr;
-  p.K2 = 0; p.ar_src_mc = nullptr; p.ar_dst_mc = nullptr; p.ar_flags = nullptr; p.ar_rows = 0;
+  p.K2 = 0; p.ar_src_mc = nullptr; p.ar_dst_mc = nullptr; p.ar_flags = nullptr; p.ar_rows = 0; p.dbg = nullptr;
   p.causal = causal;
   if (causal < 0 || causal > 3 || (causal && (gather_mode || accumulate >= 3))) return -1;
   if (causal && (M != N && causal == 1)) return -1;
@@ -950,7 +964,7 @@ XL_API int xl_gemm_tcgen05_fp8(const void* a, const void* b, void* c, int M, int
   p.gather_flags = nullptr; p.gather_block_bytes = 0;
   p.causal = 0;
   p.fp8_a = fmt_a; p.fp8_b = fmt_b; p.alpha_log2 = alpha_log2;
-  p.K2 = 0; p.ar_src_mc = nullptr; p.ar_dst_mc = nullptr; p.ar_flags = nullptr; p.ar_rows = 0;
+  p.K2 = 0; p.ar_src_mc = nullptr; p.ar_dst_mc = nullptr; p.ar_flags = nullptr; p.ar_rows = 0; p.dbg = nullptr;
   if (sm_count <= 0) sm_count = 148;
   if (block_n == 128) return launch<128>(ma, mb, p, sm_count, s);
   return launch<256>(ma, mb, p, sm_count, s);
@@ -980,6 +994,8 @@ XL_API int xl_gemm_tcgen05(const void* a, const void* b, void* c, int M, int N, 
 //   flags        device array [world] with every rank's flag words (2 * tiles words each, symmetric memory, zero before
 //                the first launch; the kernel leaves them zero), tiles = (M / 128) * ceil(N / 256 or 128)
 //   rows are split evenly: M must be a multiple of 128 * world. n_red: CTAs that only reduce (at least 1).
+//   timestamps: optional device array of 4 x grid 64-bit words: per CTA the global timer (ns) at its start, when it ran
+//   out of tiles, when it ran out of reduce work and when it had checked in (for tuning; null in production).
 //   Uses comm_local_sync[8..9] and signal channel 2; no launch argument changes between calls (graph replay is fine).
 // Returns 0, a CUDA error code, or a negative value when the arguments are not supported.
 XL_API int xl_gemm_tcgen05_ar_pull(const void* a, const void* b, const void* a2, const void* b2, void* partial,
@@ -987,7 +1003,7 @@ XL_API int xl_gemm_tcgen05_ar_pull(const void* a, const void* b, const void* a2,
                                    long long lda, long long ldb, long long lda2, long long ldb2, long long ldc,
                                    int ab_is_fp16, int c_dtype, float alpha, int* err, int sm_count, const void* comm_pads,
                                    int comm_rank, int comm_world, unsigned int* comm_local_sync, const void* flags,
-                                   int n_red, int scatter, cudaStream_t s) {
+                                   int n_red, int scatter, unsigned long long* timestamps, cudaStream_t s) {
   if (M <= 0 || N <= 0 || K <= 0 || K2 < 0) return -1;
   if ((((uintptr_t)a) & 15) || (((uintptr_t)b) & 15) || (lda % 8) || (ldb % 8)) return -1;
   if (K2 && ((((uintptr_t)a2) & 15) || (((uintptr_t)b2) & 15) || (lda2 % 8) || (ldb2 % 8) || !a2 || !b2)) return -1;
@@ -1032,7 +1048,7 @@ XL_API int xl_gemm_tcgen05_ar_pull(const void* a, const void* b, const void* a2,
   p.alpha_log2 = nullptr;
   p.K2 = K2;
   p.ar_src_mc = (const uint8_t*)partial_mc; p.ar_dst_mc = (uint8_t*)result_mc;
-  p.ar_flags = (unsigned int* const*)flags; p.ar_rows = M / comm_world;
+  p.ar_flags = (unsigned int* const*)flags; p.ar_rows = M / comm_world; p.dbg = timestamps;
   if (block_n == 128) return launch<128>(ma, mb, p, sm_count, s, K2 ? &ma2 : nullptr, K2 ? &mb2 : nullptr);
   return launch<256>(ma, mb, p, sm_count, s, K2 ? &ma2 : nullptr, K2 ? &mb2 : nullptr);
 }

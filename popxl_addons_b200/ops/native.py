@@ -85,7 +85,7 @@ _rts_adam_multi = _sig("xl_rts_adam_multi", _c_p, _c_int, _c_int, _c_p, _c_int, 
                        _c_p, _c_p, _c_f, _c_f, _c_f, _c_f, _c_f, _c_int, _c_p)
 _gemm_ar_pull = _sig("xl_gemm_tcgen05_ar_pull", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
                      _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_f, _c_p, _c_int, _c_p, _c_int,
-                     _c_int, _c_p, _c_p, _c_int, _c_int, _c_p)
+                     _c_int, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p)
 _symm_all_gather_mc = _sig("xl_symm_all_gather_mc", _c_p, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p)
 _gq_small = _sig("xl_gq_gemm_small_m", _c_p, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
                  _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p)
@@ -593,7 +593,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
 
 
 def gemm_all_reduce_pull(pairs, comm, partial: torch.Tensor, result: torch.Tensor, flags_ptrs: torch.Tensor,
-                         n_red: int = 8, alpha: float = 1.0, scatter: bool = False):
+                         n_red: int = 8, alpha: float = 1.0, scatter: bool = False, timestamps: Optional[torch.Tensor] = None):
     """`result <- all_reduce over the group of (sum of a @ b over pairs)` in one kernel (one or two operand pairs, all
     with the same layouts). Every rank's GEMM CTAs store the partial product into `partial` (symmetric memory) and flag
     each tile at the rank that owns its rows; that rank adds the copies of the tile inside NVSwitch
@@ -631,7 +631,8 @@ def gemm_all_reduce_pull(pairs, comm, partial: torch.Tensor, result: torch.Tenso
                        b2.data_ptr() if b2 is not None else None, partial.data_ptr(), mc_p, mc_r, M, N, K, K2, a_mn, b_mn,
                        lda, ldb, lda2, ldb2, partial.stride(0), int(a.dtype == torch.float16), _CODE[a.dtype], float(alpha),
                        comm.err.data_ptr(), _sms(a.device), comm.arena.pads_dev.data_ptr(), comm.rank, comm.world,
-                       comm.arena.local_sync.data_ptr(), flags_ptrs.data_ptr(), int(n_red), int(bool(scatter)), _stream())
+                       comm.arena.local_sync.data_ptr(), flags_ptrs.data_ptr(), int(n_red), int(bool(scatter)),
+                       timestamps.data_ptr() if timestamps is not None else None, _stream())
     if rc < 0:
         return NotImplemented
     _check(rc, "gemm_rs_pull_tcgen05" if scatter else "gemm_ar_pull_tcgen05")

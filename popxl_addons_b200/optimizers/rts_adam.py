@@ -236,10 +236,10 @@ class RTSAdamBucketStep(Module):
             key = name.replace(".", "_")
             ms.append(self.add_replica_sharded_variable_input(f"{key}.first_order", partial(np.zeros, shape, np_m),
                                                               first_order_dtype, by_ref=True, replica_grouping=rg,
-                                                              shard_over=group.group_size))
+                                                              shard_over=group.group_size, overwrite=True))
             vs.append(self.add_replica_sharded_variable_input(f"{key}.second_order", partial(np.zeros, shape, np.float32),
                                                               xl.float32, by_ref=True, replica_grouping=rg,
-                                                              shard_over=group.group_size))
+                                                              shard_over=group.group_size, overwrite=True))
         step = self.add_variable_input("step", partial(np.zeros, (), np.float32), xl.float32, by_ref=True)
         rts_adam_bucket_(weights, grad_accums, master_shards, ms, vs, step, group, lr=lr, weight_decays=weight_decays,
                          beta1=beta1, beta2=beta2, eps=eps, grad_scale=1.0 / float(loss_scaling),

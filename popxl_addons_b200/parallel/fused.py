@@ -125,7 +125,7 @@ def _pull_buffers(ctx: GroupContext, M: int, N: int, dtype):
     return cache[key]
 
 
-def gemm_all_reduce_pull(ctx: GroupContext, pairs, n_red: Optional[int] = None):
+def gemm_all_reduce_pull(ctx: GroupContext, pairs, n_red: Optional[int] = None, timestamps=None):
     """`all_reduce(sum of a @ w over pairs)` (one or two pairs) as one pulling kernel; the result lives in a ring of two
     arena buffers (valid until the second next call with the same shape). NotImplemented if unsupported."""
     nat = _lib()
@@ -136,7 +136,7 @@ def gemm_all_reduce_pull(ctx: GroupContext, pairs, n_red: Optional[int] = None):
     buf = _pull_buffers(ctx, M, N, a0.dtype)
     result = buf["results"][buf["pos"]]
     res = nat.gemm_all_reduce_pull(pairs, ctx, buf["partial"], result, buf["flags"],
-                                   n_red=_AR_PULL_CTAS if n_red is None else n_red)
+                                   n_red=_AR_PULL_CTAS if n_red is None else n_red, timestamps=timestamps)
     if res is NotImplemented:
         return NotImplemented
     buf["pos"] ^= 1

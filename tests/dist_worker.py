@@ -199,6 +199,24 @@ def main():
         torch.cuda.synchronize()
         result["ar_pull_err"] = float((got.float() - full).abs().max() / full.abs().max())
         result["ar_pull_ms"] = timed(lambda: fused.gemm_all_reduce_pull(ctx, [(a, w)], n_red=args.n_red))
+        # where the time of the pulling kernel goes: per-CTA timestamps of one launch (start, tiles done, reduce work
+        # done, checked in), relative to the earliest start, in microseconds
+        stamps = torch.zeros(148 * 4, dtype=torch.int64, device=dev)
+        fused.gemm_all_reduce_pull(ctx, [(a, w)], n_red=args.n_red, timestamps=stamps)
+        torch.cuda.synchronize()
+        st = stamps.view(148, 4).cpu().numpy().astype(np.int64)
+        used = st[:, 0] > 0
+        t0 = st[used, 0].min()
+        rel = (st[used] - t0) / 1e3
+        red = rel[:args.n_red]
+        gem = rel[args.n_red:]
+        result["pull_timeline_us"] = {
+            "reducer_ctas": {"reduce_done": [float(red[:, 2].min()), float(red[:, 2].max())],
+                             "finish": [float(red[:, 3].min()), float(red[:, 3].max())]},
+            "gemm_ctas": {"start": [float(gem[:, 0].min()), float(gem[:, 0].max())],
+                          "tiles_done": [float(gem[:, 1].min()), float(np.median(gem[:, 1])), float(gem[:, 1].max())],
+                          "reduce_done": [float(gem[:, 2].min()), float(np.median(gem[:, 2])), float(gem[:, 2].max())],
+                          "finish": [float(gem[:, 3].min()), float(gem[:, 3].max())]}}
         # two operand pairs contracted into one accumulator: all_reduce(a @ w + a2 @ w2), K2 = K / 4 (a block's attention
         # and feed-forward output projections), and the transposed-weight form of the backward pass
         K2 = max(64, K // 4)
