@@ -43,9 +43,16 @@ struct AttnParams {
   int causal;
   int is_fp16;
   int* err;
+  long long* trace;  // optional (tuning): clock64 stamps of CTA (0, 0, 0): [role 0 MMA thread | role 1 softmax warp][block][8]
 };
 
 using namespace xl_tc;
+
+#define XL_ATTN_STAMP(role, j, point)                                                                  \
+  do {                                                                                                 \
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 64)       \
+      p.trace[((role) * 64 + (j)) * 8 + (point)] = clock64();                                          \
+  } while (0)
 
 template <int D, int BKV>
 struct AttnSmem {
@@ -202,15 +209,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       };
       if (ok && n_kv > 0) ok = issue_scores(0);
       for (int j = 0; j < n_kv && ok; ++j) {
+        XL_ATTN_STAMP(0, j, 0);
         if (j + 1 < n_kv) {
           ok = issue_scores(j + 1);
           if (!ok) break;
         }
+        XL_ATTN_STAMP(0, j, 1);
         const int stage = j % KV_STAGES;
         ok = mbar_wait(&v_full[stage], (uint32_t)(j / KV_STAGES) & 1u, abort_flag, p.err, ERR_KV_FULL_WAIT);
         if (!ok) break;
+        XL_ATTN_STAMP(0, j, 2);
         ok = mbar_wait(p_full, (uint32_t)j & 1u, abort_flag, p.err, ERR_P_FULL_WAIT);
         if (!ok) break;
+        XL_ATTN_STAMP(0, j, 3);
         tcgen05_fence_after();
         const uint32_t p_addr = smem_u32(sP);
         const uint32_t v_addr = smem_u32(sKV + stage * L::STAGE_BYTES + L::K_BYTES);
@@ -224,6 +235,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           }
         tcgen05_commit(&v_empty[stage]);   // the V block is free once these MMAs have read it
         tcgen05_commit(pv_done);           // output accumulator and the P tile are free again
+        XL_ATTN_STAMP(0, j, 4);
       }
     }
   } else {
@@ -237,8 +249,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int sb = j & 1;
+      if (warp == 2 && lane == 0) XL_ATTN_STAMP(1, j, 0);
       ok = __all_sync(0xffffffffu, mbar_wait(&s_full[sb], (uint32_t)(j / 2) & 1u, abort_flag, p.err, ERR_S_FULL_WAIT));
       if (!ok) break;
+      if (warp == 2 && lane == 0) XL_ATTN_STAMP(1, j, 1);
       tcgen05_fence_after();
       float s[BKV];
 #pragma unroll
@@ -252,6 +266,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);  // the score buffer may be overwritten
+      if (warp == 2 && lane == 0) XL_ATTN_STAMP(1, j, 2);
       const int col0 = j * BKV;
       const int limit = p.causal ? min(qrow, p.S - 1) : p.S - 1;  // last key this row may attend
       float m_blk = -INFINITY;
@@ -281,6 +296,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       }
       l = l * alpha + sum;
       m = m_new;
+      if (warp == 2 && lane == 0) XL_ATTN_STAMP(1, j, 3);
       if (j > 0) {
         ok = __all_sync(0xffffffffu, mbar_wait(pv_done, (uint32_t)(j - 1) & 1u, abort_flag, p.err, ERR_PV_DONE_WAIT));
         if (!ok) break;
@@ -298,6 +314,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           tmem_st_wait();
         }
       }
+      if (warp == 2 && lane == 0) XL_ATTN_STAMP(1, j, 4);
       // P_j -> shared memory, 16-bit, 128-byte swizzle (16-byte chunk index xor row mod 8), one 64-key k-block per 16 KB
 #pragma unroll
       for (int ch = 0; ch < BKV / 8; ++ch) {
@@ -314,6 +331,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
+      if (warp == 2 && lane == 0) XL_ATTN_STAMP(1, j, 5);
     }
     // ---- epilogue: O / l -> global memory, log-sum-exp ---------------------------------------------------------------
     if (ok && n_kv > 0)
@@ -401,10 +419,11 @@ int launch(const void* qkv, long long rows, long long cols, long long ld, const 
 //   out: (B*S x ldo) 16-bit, head h in columns [h*D, (h+1)*D); ldo a multiple of 8, out 16-byte aligned.
 //   lse: (B, H, S) fp32, may be null.      D in {64, 128, 256}.
 //   err: device int that receives a non-zero code if a bounded wait inside the kernel gave up (may be null).
+//   trace: null, or 2 * 64 * 8 64-bit words that receive clock stamps of the first CTA's roles (tuning aid).
 // Returns 0, a CUDA error code, or a negative value when the arguments are not supported by this kernel.
 XL_API int xl_attn_fwd_tcgen05(const void* qkv, long long ld, long long cols, void* out, long long ldo, float* lse, int B,
                                int S, int H, int D, int q_col, int k_col, int v_col, float scale, int causal,
-                               int is_fp16, int* err, cudaStream_t s) {
+                               int is_fp16, int* err, long long* trace, cudaStream_t s) {
   if (B <= 0 || S <= 0 || H <= 0 || B > 65535 || H > 65535) return -1;
   if ((((uintptr_t)qkv) & 15) || (((uintptr_t)out) & 15) || (ld % 8) || (ldo % 8)) return -1;
   if ((q_col % 8) || (k_col % 8) || (v_col % 8) || q_col < 0 || k_col < 0 || v_col < 0) return -1;
@@ -416,6 +435,7 @@ XL_API int xl_attn_fwd_tcgen05(const void* qkv, long long ld, long long cols, vo
   p.q_col = q_col; p.k_col = k_col; p.v_col = v_col;
   p.out = out; p.ldo = ldo; p.lse = lse; p.scale = scale; p.causal = causal ? 1 : 0; p.is_fp16 = is_fp16 ? 1 : 0;
   p.err = err;
+  p.trace = trace;
   const long long rows = (long long)B * S;
   if (D == 256) return launch<256, 64>(qkv, rows, cols, ld, p, s);
   if (D == 128) return launch<128, 128>(qkv, rows, cols, ld, p, s);

@@ -67,7 +67,7 @@ _rotary = _sig("xl_rotary", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_in
 _gq = _sig("xl_gq_decompress", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p)
 _sm_fwd = _sig("xl_attn_softmax_fwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p)
 _attn_flash = _sig("xl_attn_fwd_tcgen05", _c_p, _c_ll, _c_ll, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
-                   _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p)
+                   _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p, _c_p)
 _attn_bwd_dq = _sig("xl_attn_bwd_dq_tcgen05", _c_p, _c_ll, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int,
                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p)
 _sm_bwd = _sig("xl_attn_softmax_bwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p)
@@ -781,7 +781,7 @@ def _use_flash(B, S, H):
     return B * H * ((S + 127) // 128) >= _FLASH_MIN_CTAS
 
 
-def flash_attention_fwd(packed, q_col, k_col, v_col, B, S, H, D, scale, causal, out=None):
+def flash_attention_fwd(packed, q_col, k_col, v_col, B, S, H, D, scale, causal, out=None, trace=None):
     """softmax(scale * Q K^T [+ causal mask]) V for the heads stored as column windows of `packed (B*S, cols)`; one
     tcgen05 kernel, scores never leave the chip. Returns `(out (B*S, H*D), lse (B, H, S))` or NotImplemented."""
     if packed.dtype not in (torch.bfloat16, torch.float16) or not packed.is_cuda or packed.dim() != 2 \
@@ -792,7 +792,8 @@ def flash_attention_fwd(packed, q_col, k_col, v_col, B, S, H, D, scale, causal, 
     lse = torch.empty((B, H, S), dtype=torch.float32, device=packed.device)
     rc = _attn_flash(packed.data_ptr(), packed.stride(0), packed.shape[1], out.data_ptr(), out.stride(0), lse.data_ptr(),
                      B, S, H, D, q_col, k_col, v_col, float(scale), int(bool(causal)),
-                     int(packed.dtype == torch.float16), gemm_error_flag(packed.device).data_ptr(), _stream())
+                     int(packed.dtype == torch.float16), gemm_error_flag(packed.device).data_ptr(),
+                     trace.data_ptr() if trace is not None else None, _stream())
     if rc < 0:
         return NotImplemented
     _check(rc, "attn_fwd_tcgen05")

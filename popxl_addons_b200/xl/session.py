@@ -99,6 +99,8 @@ class Session:
                            and os.environ.get("XL_IO_STREAM", "1") != "0" else None)
         self._io_ready: Dict[int, tuple] = {}  # id(tensor) -> (event recorded on the IO stream, tensor)
         self._io_dirty = False                 # an op ran on the IO stream since the streams were last joined
+        self._slab_events: Dict[RemoteBuffer, tuple] = {}  # last access of a remote-buffer slab: (event, stream id)
+        self._slab_pending = None
         self._uncapturable: set = set()        # loops whose capture failed once: they run eagerly from then on
         self._init_state()
 
@@ -445,7 +447,41 @@ class Session:
             return i
         return idx.reshape(-1)[:1].to(torch.int64).clamp(0, rb.entries - 1)
 
+    def _order_slab_access(self, rb: RemoteBuffer):
+        """A slab is not an operand the executor can see, so accesses from the two streams are ordered here: the
+        stream that touches a slab first waits for the last access made from the other stream."""
+        if self._io_stream is None:
+            return
+        cur = torch.cuda.current_stream(self.device)
+        last = self._slab_events.get(rb)
+        if last is not None and last[1] != cur.cuda_stream:
+            cur.wait_event(last[0])
+        ev = torch.cuda.Event()
+        self._slab_pending = (rb, ev, cur)
+
+    def _slab_access_done(self):
+        pend = getattr(self, "_slab_pending", None)
+        if pend is not None:
+            rb, ev, cur = pend
+            ev.record(cur)
+            self._slab_events[rb] = (ev, cur.cuda_stream)
+            self._slab_pending = None
+
     def remote_load(self, rb: RemoteBuffer, index: List[torch.Tensor]) -> List[torch.Tensor]:
+        self._order_slab_access(rb)
+        try:
+            return self._remote_load(rb, index)
+        finally:
+            self._slab_access_done()
+
+    def remote_store(self, rb: RemoteBuffer, index: List[torch.Tensor], vals: List[torch.Tensor]):
+        self._order_slab_access(rb)
+        try:
+            self._remote_store(rb, index, vals)
+        finally:
+            self._slab_access_done()
+
+    def _remote_load(self, rb: RemoteBuffer, index: List[torch.Tensor]) -> List[torch.Tensor]:
         slabs = self._alloc_buffer(rb)
         out = []
         for r in range(self.num_local):
@@ -457,7 +493,7 @@ class Session:
                 out.append(slabs[r].index_select(0, i).reshape(rb.tensor_shape))
         return out
 
-    def remote_store(self, rb: RemoteBuffer, index: List[torch.Tensor], vals: List[torch.Tensor]):
+    def _remote_store(self, rb: RemoteBuffer, index: List[torch.Tensor], vals: List[torch.Tensor]):
         slabs = self._alloc_buffer(rb)
         for r in range(self.num_local):
             i = self._row_index(rb, index[r])
@@ -704,11 +740,14 @@ class Session:
         """The compute stream waits for everything queued on the IO stream and for every collective in flight (end of a
         run, end of a loop iteration, end of a captured loop body)."""
         self.comm.wait_all()
+        if not self._io_dirty:
+            self._slab_events.clear()  # every access so far was made from the compute stream: already ordered
         if self._io_stream is not None and self._io_dirty:
             # only when an op ran there since the last join: inside a graph capture a wait on a stream that never forked
             # from the capturing stream would invalidate the capture
             torch.cuda.current_stream(self.device).wait_stream(self._io_stream)
             self._io_ready.clear()
+            self._slab_events.clear()
             self._io_dirty = False
 
     @staticmethod
@@ -874,9 +913,10 @@ class Session:
         try:
             with torch.cuda.graph(g, capture_error_mode="thread_local"):
                 outs = self.run_graph(graph, carried + list(vals[n_out:]))
+                # every stream forked inside the body joins before its results are read back and the capture ends
+                self._join_streams()
                 for buf, o in zip(carried, outs[:n_out]):
                     buf[0].copy_(o[0])
-                self._join_streams()  # every stream forked inside the body joins before the capture ends
             ok = True
         finally:
             self._capturing = False
