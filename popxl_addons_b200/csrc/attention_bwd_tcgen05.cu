@@ -269,6 +269,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const bool row_ok = qrow < p.S;
     const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
     const float c = p.scale * 1.4426950408889634f;  // scores are exponentiated in base 2
+    const bool is_fp16 = p.is_fp16 != 0;
     // per-row constants: log-sum-exp (base 2) and delta = dO . O
     float lse2 = 0.f, delta = 0.f;
     if (row_ok) {
@@ -317,7 +318,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       const int limit = p.causal ? min(qrow, p.S - 1) : p.S - 1;  // last key this row may attend
 #pragma unroll
       for (int i = 0; i < BKV; ++i) {
-        const float pr = (col0 + i <= limit && row_ok) ? exp2f(fmaf(s[i], c, -lse2)) : 0.f;
+        const float pr = (col0 + i <= limit && row_ok) ? fast_exp2(fmaf(s[i], c, -lse2)) : 0.f;
         s[i] = pr;
         dp[i] = pr * (dp[i] - delta) * p.scale;
       }
@@ -325,16 +326,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       if (row_ok) {
 #pragma unroll
         for (int ch = 0; ch < BKV / 8; ++ch) {
-          uint4 po, dso;
-          uint16_t* pe = (uint16_t*)&po;
-          uint16_t* de = (uint16_t*)&dso;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            pe[e] = p.is_fp16 ? __half_as_ushort(__float2half_rn(s[ch * 8 + e]))
-                              : __bfloat16_as_ushort(__float2bfloat16_rn(s[ch * 8 + e]));
-            de[e] = p.is_fp16 ? __half_as_ushort(__float2half_rn(dp[ch * 8 + e]))
-                              : __bfloat16_as_ushort(__float2bfloat16_rn(dp[ch * 8 + e]));
-          }
+          const uint4 po = pack8_16bit(s + ch * 8, is_fp16), dso = pack8_16bit(dp + ch * 8, is_fp16);
+          const uint16_t* pe = (const uint16_t*)&po;
+          const uint16_t* de = (const uint16_t*)&dso;
           if (col0 + ch * 8 + 8 <= p.S) {
             *(uint4*)(prow + col0 + ch * 8) = po;
             *(uint4*)(dsrow + col0 + ch * 8) = dso;
@@ -356,13 +350,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       uint8_t* ds_tile = sDS + db_i * L::DS_BYTES;
 #pragma unroll
       for (int ch = 0; ch < BKV / 8; ++ch) {
-        uint4 o;
-        uint16_t* oe = (uint16_t*)&o;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float v = dp[ch * 8 + e];
-          oe[e] = p.is_fp16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
-        }
+        const uint4 o = pack8_16bit(dp + ch * 8, is_fp16);
         *(uint4*)(ds_tile + ch * 2048 + (r >> 3) * 128 + (r & 7) * 16) = o;
       }
       fence_proxy_async_smem();
@@ -383,14 +371,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (row_ok) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            uint4 o;
-            uint16_t* oe = (uint16_t*)&o;
+            float v[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float v = __uint_as_float(raw[g * 8 + e]);
-              oe[e] = p.is_fp16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
-            }
-            *(uint4*)(qrow_out + ch * 32 + g * 8) = o;
+            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(raw[g * 8 + e]);
+            *(uint4*)(qrow_out + ch * 32 + g * 8) = pack8_16bit(v, is_fp16);
           }
         }
       }

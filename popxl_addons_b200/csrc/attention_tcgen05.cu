@@ -245,6 +245,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const int qrow = q0 + r;        // query position inside the sequence
     const uint32_t lane_base = (uint32_t)(qtr * 32) << 16;
     const float c = p.scale * 1.4426950408889634f;  // scores are exponentiated in base 2
+    const bool is_fp16 = p.is_fp16 != 0;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
@@ -286,12 +287,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       const bool move = m_blk > -INFINITY && (m == -INFINITY || (m_blk - m) * c > RESCALE_LOG2);
       const float m_new = move ? m_blk : m;
       const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row with no admissible key yet keeps p = 0
-      const float alpha = (move && m != -INFINITY) ? exp2f((m - m_use) * c) : 1.f;
+      const float alpha = (move && m != -INFINITY) ? fast_exp2((m - m_use) * c) : 1.f;
       float sum = 0.f;
       const float mc = m_use * c;
 #pragma unroll
       for (int i = 0; i < BKV; ++i) {
-        s[i] = exp2f(fmaf(s[i], c, -mc));
+        s[i] = fast_exp2(fmaf(s[i], c, -mc));
         sum += s[i];
       }
       l = l * alpha + sum;
@@ -318,13 +319,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       // P_j -> shared memory, 16-bit, 128-byte swizzle (16-byte chunk index xor row mod 8), one 64-key k-block per 16 KB
 #pragma unroll
       for (int ch = 0; ch < BKV / 8; ++ch) {
-        uint4 o;
-        uint16_t* oe = (uint16_t*)&o;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float v = s[ch * 8 + e];
-          oe[e] = p.is_fp16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
-        }
+        const uint4 o = pack8_16bit(s + ch * 8, is_fp16);
         *(uint4*)(sP + (ch >> 3) * (BLOCK_Q * 128) + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = o;
       }
       fence_proxy_async_smem();
@@ -349,14 +344,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         if (row_ok) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            uint4 o;
-            uint16_t* oe = (uint16_t*)&o;
+            float v[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const float v = __uint_as_float(raw[g * 8 + e]) * inv;
-              oe[e] = p.is_fp16 ? __half_as_ushort(__float2half_rn(v)) : __bfloat16_as_ushort(__float2bfloat16_rn(v));
-            }
-            *(uint4*)(orow + ch * 32 + g * 8) = o;
+            for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(raw[g * 8 + e]) * inv;
+            *(uint4*)(orow + ch * 32 + g * 8) = pack8_16bit(v, is_fp16);
           }
         }
       }

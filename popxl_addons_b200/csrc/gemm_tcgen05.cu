@@ -17,6 +17,7 @@
 #include "tcgen05.cuh"
 
 #include <cuda.h>
+#include <cstdlib>
 #include <stdio.h>
 
 namespace {
@@ -96,7 +97,8 @@ struct GemmParams {
   unsigned int* const* ar_flags;    // device array [world]: per rank, 2 * tiles words: [tile] parts arrived (written
                                     //   by all ranks), [tiles + tile] eighths reduced (owner only). All zero between launches.
   int ar_rows;                      // rows owned by each rank (a multiple of BLOCK_M)
-  unsigned long long* dbg;          // optional: 4 timestamps (ns) per CTA: start, tiles done, reduce done, finish done
+  unsigned long long* dbg;          // optional: 4 timestamps (ns) per CTA (start, tiles done, reduce done, finish done),
+                                    // then 3 per reduce item (taken, tile ready, reduced; 4 words apart)
 };
 
 // k-block range of a tile under the causal modes; false: the tile is skipped altogether
@@ -206,6 +208,8 @@ __device__ __forceinline__ void ar_pull_reduce(const GemmParams& p, int tiles_m,
     if (lane == 0) item = atomicAdd(p.local_sync + AR_SYNC_QUEUE, 1u);
     item = __shfl_sync(0xffffffffu, item, 0);
     if (item >= items) break;
+    unsigned long long* item_dbg = (p.dbg && lane == 0) ? p.dbg + (size_t)gridDim.x * 4 + (size_t)item * 4 : nullptr;
+    if (item_dbg) item_dbg[0] = global_timer_ns();
     const int q = (int)(item / AR_ITEMS_PER_TILE), sub = (int)(item % AR_ITEMS_PER_TILE);
     const int nb = q / mpr, mb = p.comm_rank * mpr + q % mpr;
     const int tile_id = mb * tiles_n + nb;
@@ -224,8 +228,12 @@ __device__ __forceinline__ void ar_pull_reduce(const GemmParams& p, int tiles_m,
       }
       break;
     }
+    if (item_dbg) item_dbg[1] = global_timer_ns();
     __syncwarp();
-    __threadfence_system();  // every lane's loads below come after the flag that lane 0 saw
+    // Every lane reads the flag itself with acquire semantics: its loads below then come after the producers' releases.
+    // (A system-scope fence here would also wait for this warp's multicast stores of the previous item to be
+    // acknowledged by every rank, several microseconds per item.)
+    (void)ld_acquire_sys_u32(flags + tile_id);
     const int row0 = mb * BLOCK_M + sub * ROWS, col0 = nb * BLOCK_N;
     uint4 v[ITERS];
     long long off[ITERS];
@@ -246,6 +254,7 @@ __device__ __forceinline__ void ar_pull_reduce(const GemmParams& p, int tiles_m,
       for (int it = 0; it < ITERS; ++it)
         if (off[it] >= 0) xl_multimem_st_b128(p.ar_dst_mc + off[it], v[it]);
     }
+    if (item_dbg) item_dbg[2] = global_timer_ns();
     __syncwarp();
     if (lane == 0) {
       const unsigned int prev = atomicAdd(flags + total_tiles + tile_id, 1u);
@@ -1015,7 +1024,9 @@ XL_API int xl_gemm_tcgen05_ar_pull(const void* a, const void* b, const void* a2,
   if ((((uintptr_t)partial) & 15) || (((uintptr_t)partial_mc) & 15) || (((uintptr_t)result_mc) & 15)) return -1;
   if (sm_count <= 0) sm_count = 148;
   if (n_red > sm_count / 2) return -1;
-  const int block_n = (N <= 128) ? 128 : 256;
+  // narrower tiles give more waves per launch (less left to reduce after the last one) at some cost in MMA efficiency
+  static const int forced_block_n = [] { const char* e = getenv("XL_AR_PULL_BLOCK_N"); return e ? atoi(e) : 0; }();
+  const int block_n = (N <= 128 || forced_block_n == 128) ? 128 : 256;
   CUtensorMap ma, mb, ma2, mb2;
   int r;
   if (!a_mn) r = make_map(&ma, a, ab_is_fp16, M, K, lda, 1, 0, BLOCK_K, BLOCK_M);

@@ -125,6 +125,25 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t 
 }
 
 
+// 2^x by the special-function unit alone (no range handling: results below 2^-126 flush to zero)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// eight fp32 values -> eight 16-bit values (fp16 or bf16, round to nearest), two per conversion instruction
+__device__ __forceinline__ uint4 pack8_16bit(const float* v, bool is_fp16) {
+  uint32_t w[4];
+  if (is_fp16) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(v[2 * e + 1]), "f"(v[2 * e]));
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(v[2 * e + 1]), "f"(v[2 * e]));
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // writes to shared memory by ordinary stores become visible to the tensor core's (async proxy) reads
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 

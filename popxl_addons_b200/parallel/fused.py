@@ -116,7 +116,7 @@ def _pull_buffers(ctx: GroupContext, M: int, N: int, dtype):
     if key not in cache:
         partial = ctx.arena.alloc((M, N), dtype)
         results = [ctx.arena.alloc((M, N), dtype) for _ in range(2)]
-        tiles = (M // 128) * (-(-N // (128 if N <= 128 else 256)))
+        tiles = (M // 128) * (-(-N // 128))  # enough for either tile width of the kernel
         flags = ctx.arena.alloc((2 * tiles,), torch.int32)
         flags.zero_()
         torch.cuda.synchronize(flags.device)

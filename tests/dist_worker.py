@@ -201,15 +201,27 @@ def main():
         result["ar_pull_ms"] = timed(lambda: fused.gemm_all_reduce_pull(ctx, [(a, w)], n_red=args.n_red))
         # where the time of the pulling kernel goes: per-CTA timestamps of one launch (start, tiles done, reduce work
         # done, checked in), relative to the earliest start, in microseconds
-        stamps = torch.zeros(148 * 4, dtype=torch.int64, device=dev)
-        fused.gemm_all_reduce_pull(ctx, [(a, w)], n_red=args.n_red, timestamps=stamps)
+        bn = 128 if os.environ.get("XL_AR_PULL_BLOCK_N") == "128" else 256
+        n_items = (M // ctx.world // 128) * ((N + bn - 1) // bn) * 8
+        stamps = torch.zeros((148 + n_items) * 4, dtype=torch.int64, device=dev)
+        for it in range(4):  # launches close with a barrier over the ranks: the last one starts on all ranks together
+            fused.gemm_all_reduce_pull(ctx, [(a, w)], n_red=args.n_red, timestamps=stamps if it == 3 else None)
         torch.cuda.synchronize()
-        st = stamps.view(148, 4).cpu().numpy().astype(np.int64)
+        if os.environ.get("XL_DUMP_TIMELINE"):
+            np.save(f"{os.environ['XL_DUMP_TIMELINE']}_rank{ctx.rank}.npy", stamps.cpu().numpy())
+        st = stamps[:148 * 4].view(148, 4).cpu().numpy().astype(np.int64)
         used = st[:, 0] > 0
         t0 = st[used, 0].min()
         rel = (st[used] - t0) / 1e3
         red = rel[:args.n_red]
         gem = rel[args.n_red:]
+        items = stamps[148 * 4:].view(n_items, 4).cpu().numpy().astype(np.int64)
+        items = (items[items[:, 0] > 0, :3] - t0) / 1e3
+        wait, work = items[:, 1] - items[:, 0], items[:, 2] - items[:, 1]
+        result["pull_items_us"] = {"n": int(len(items)), "taken": [float(items[:, 0].min()), float(np.median(items[:, 0])), float(items[:, 0].max())],
+                                   "wait_for_tile": [float(np.median(wait)), float(wait.max())],
+                                   "reduce": [float(work.min()), float(np.median(work)), float(work.max())],
+                                   "last_done": float(items[:, 2].max())}
         result["pull_timeline_us"] = {
             "reducer_ctas": {"reduce_done": [float(red[:, 2].min()), float(red[:, 2].max())],
                              "finish": [float(red[:, 3].min()), float(red[:, 3].max())]},
