@@ -24,6 +24,7 @@
 // CTA per SM). Every wait on an mbarrier is bounded: when a wait gives up the kernel records a code in `*err`, raises a
 // CTA-wide abort flag, all roles leave their loops, TMEM is released and the kernel returns normally.
 #include "tcgen05.cuh"
+#include "attention_split.cuh"
 
 namespace {
 
@@ -56,9 +57,23 @@ struct AttnBwdParams {
   int causal;
   int is_fp16;
   int* err;
+  // Key-range splitting (chunk > 0): a query block's key blocks are divided evenly over ceil(n / chunk) CTAs. Each writes
+  // its partial dQ (fp32) to the workspace; a second kernel adds the partials of every row up and writes dQ.
+  int chunk;
+  int items;               // CTAs per head and batch entry (grid y)
+  float* part_dq;          // [B*H*items][128][D]
+  float* delta;            // (B, H, S) scratch: dO . O of every row, filled by a first kernel of the launch
+  long long* trace;        // optional (tuning): clock64 stamps of CTA (0, 0, 0): [role 0 MMA thread | role 1 warp 2][block][8]
 };
 
+#define XL_ATTN_BWD_STAMP(role, j, point)                                                              \
+  do {                                                                                                 \
+    if (p.trace != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (j) < 64)       \
+      p.trace[((role) * 64 + (j)) * 8 + (point)] = clock64();                                          \
+  } while (0)
+
 using namespace xl_tc;
+using namespace xl_attn_split;
 
 // Shared-memory matrix descriptor of a K-major operand stored without swizzle as 8-row x 16-byte core matrices:
 // `lbo` = byte distance between core matrices adjacent along K, `sbo` = between 8-row groups (layout type 0).
@@ -115,11 +130,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_qblocks = (p.S + BLOCK_Q - 1) / BLOCK_Q;
-  const int qb = n_qblocks - 1 - (int)blockIdx.x;  // the blocks with the most keys start first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // grid: x = head, y = work item (query block and part of its keys; the blocks with the most keys come first), z = batch
+  const int h = blockIdx.x, b = blockIdx.z;
+  int qb = n_qblocks - 1, part = (int)blockIdx.y, first_slot = 0, n_kv_all = 0, n_parts = 1;
+  for (;; --qb) {
+    n_kv_all = attn_kv_blocks(qb, p.S, p.causal, BKV);
+    n_parts = attn_chunks(n_kv_all, p.chunk);
+    if (part < n_parts || qb == 0) break;
+    part -= n_parts;
+    first_slot += n_parts;
+  }
   const int q0 = qb * BLOCK_Q;
-  const int kv_end = p.causal ? min(p.S, q0 + BLOCK_Q) : p.S;
-  const int n_kv = (kv_end + BKV - 1) / BKV;
+  const int j0 = (int)(((long long)part * n_kv_all) / n_parts);           // this CTA's key blocks: [j0, j0 + n_kv)
+  const int n_kv = (int)(((long long)(part + 1) * n_kv_all) / n_parts) - j0;
   const int row0 = b * p.S;
 
   if (threadIdx.x == 0) {
@@ -180,7 +203,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         uint8_t* dst = for_k ? sK + stage * L::K_BYTES : sV + stage * L::V_BYTES;
         mbar_expect_tx(&full[stage], L::K_BYTES);
-        const int k0 = row0 + j * BKV;
+        const int k0 = row0 + (j0 + j) * BKV;
         const int col = (for_k ? p.k_col : p.v_col) + h * D;
 #pragma unroll
         for (int kb = 0; kb < D / 64; ++kb)  // boxes {64 features, BKV rows}
@@ -237,13 +260,16 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       };
       if (ok && n_kv > 0) ok = issue_scores(0);
       for (int j = 0; j < n_kv && ok; ++j) {
+        XL_ATTN_BWD_STAMP(0, j, 0);
         if (j + 1 < n_kv) {
           ok = issue_scores(j + 1);
           if (!ok) break;
         }
+        XL_ATTN_BWD_STAMP(0, j, 1);
         const int db_i = j & 1;
         ok = mbar_wait(&ds_full[db_i], (uint32_t)(j / 2) & 1u, abort_flag, p.err, ERR_DS_FULL_WAIT);
         if (!ok) break;
+        XL_ATTN_BWD_STAMP(0, j, 2);
         tcgen05_fence_after();
         const int ks = j % K_STAGES;
         const uint32_t ds_addr = smem_u32(sDS + db_i * L::DS_BYTES);
@@ -259,6 +285,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         tcgen05_commit(&k_empty[ks]);       // the K block is free once the third product has read it
         tcgen05_commit(&ds_empty[db_i]);    // and the dS buffer
         if (j == n_kv - 1) tcgen05_commit(dq_done);
+        XL_ATTN_BWD_STAMP(0, j, 3);
       }
     }
   } else {
@@ -272,31 +299,18 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const bool is_fp16 = p.is_fp16 != 0;
     // per-row constants: log-sum-exp (base 2) and delta = dO . O
     float lse2 = 0.f, delta = 0.f;
-    if (row_ok) {
-      lse2 = p.lse[((long long)b * p.H + h) * p.S + qrow] * 1.4426950408889634f;
-      const uint16_t* orow = (const uint16_t*)p.out + (long long)(row0 + qrow) * p.ldo + h * D;
-      const uint16_t* grow = (const uint16_t*)p.dout + (long long)(row0 + qrow) * p.ld_do + h * D;
-#pragma unroll 4
-      for (int i = 0; i < D / 8; ++i) {
-        const uint4 ov = *(const uint4*)(orow + i * 8), gv = *(const uint4*)(grow + i * 8);
-        const uint16_t* oe = (const uint16_t*)&ov;
-        const uint16_t* ge = (const uint16_t*)&gv;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          const float of = p.is_fp16 ? __half2float(__ushort_as_half(oe[e])) : __bfloat162float(__ushort_as_bfloat16(oe[e]));
-          const float gf = p.is_fp16 ? __half2float(__ushort_as_half(ge[e])) : __bfloat162float(__ushort_as_bfloat16(ge[e]));
-          delta = fmaf(of, gf, delta);
-        }
-      }
-    }
+    if (row_ok) lse2 = p.lse[((long long)b * p.H + h) * p.S + qrow] * 1.4426950408889634f;
+    if (row_ok) delta = p.delta[((long long)b * p.H + h) * p.S + qrow];
     const long long mat = ((long long)b * p.H + h) * p.S * (long long)p.S;  // start of this (batch, head)'s S x S matrices
     uint16_t* prow = (uint16_t*)p.P + mat + (long long)qrow * p.S;
     uint16_t* dsrow = (uint16_t*)p.dS + mat + (long long)qrow * p.S;
     bool ok = true;
     for (int j = 0; j < n_kv && ok; ++j) {
       const int sb = j & 1;
+      if (warp == 2 && lane == 0) XL_ATTN_BWD_STAMP(1, j, 0);
       ok = __all_sync(0xffffffffu, mbar_wait(&sdp_full[sb], (uint32_t)(j / 2) & 1u, abort_flag, p.err, ERR_SDP_FULL_WAIT));
       if (!ok) break;
+      if (warp == 2 && lane == 0) XL_ATTN_BWD_STAMP(1, j, 1);
       tcgen05_fence_after();
       float s[BKV], dp[BKV];
 #pragma unroll
@@ -314,7 +328,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sdp_empty[sb]);  // both buffers may be overwritten
-      const int col0 = j * BKV;
+      if (warp == 2 && lane == 0) XL_ATTN_BWD_STAMP(1, j, 2);
+      const int col0 = (j0 + j) * BKV;
       const int limit = p.causal ? min(qrow, p.S - 1) : p.S - 1;  // last key this row may attend
 #pragma unroll
       for (int i = 0; i < BKV; ++i) {
@@ -322,24 +337,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         s[i] = pr;
         dp[i] = pr * (dp[i] - delta) * p.scale;
       }
-      // P and dS rows to global memory (16-bit): 2 * BKV bytes each, contiguous per thread
-      if (row_ok) {
-#pragma unroll
-        for (int ch = 0; ch < BKV / 8; ++ch) {
-          const uint4 po = pack8_16bit(s + ch * 8, is_fp16), dso = pack8_16bit(dp + ch * 8, is_fp16);
-          const uint16_t* pe = (const uint16_t*)&po;
-          const uint16_t* de = (const uint16_t*)&dso;
-          if (col0 + ch * 8 + 8 <= p.S) {
-            *(uint4*)(prow + col0 + ch * 8) = po;
-            *(uint4*)(dsrow + col0 + ch * 8) = dso;
-          } else {
-            for (int e = 0; e < 8 && col0 + ch * 8 + e < p.S; ++e) {
-              prow[col0 + ch * 8 + e] = pe[e];
-              dsrow[col0 + ch * 8 + e] = de[e];
-            }
-          }
-        }
-      }
+      if (warp == 2 && lane == 0) XL_ATTN_BWD_STAMP(1, j, 3);
       // dS_j -> shared memory for the third product: 16-bit, no swizzle, [chunk column][row group][8 rows x 16 B]
       const int db_i = j & 1;
       if (j >= 2) {
@@ -347,6 +345,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                                                 ERR_DS_EMPTY_WAIT));
         if (!ok) break;
       }
+      if (warp == 2 && lane == 0) XL_ATTN_BWD_STAMP(1, j, 5);
       uint8_t* ds_tile = sDS + db_i * L::DS_BYTES;
 #pragma unroll
       for (int ch = 0; ch < BKV / 8; ++ch) {
@@ -357,18 +356,58 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ds_full[db_i]);
+      if (warp == 2 && lane == 0) XL_ATTN_BWD_STAMP(1, j, 6);
+      // P and dS rows to global memory (16-bit): 2 * BKV bytes each, contiguous per thread, 32 bytes per store where the
+      // rows are 32-byte aligned
+      if (row_ok) {
+        const bool wide = (p.S % 16) == 0 && ((((uintptr_t)p.P) | ((uintptr_t)p.dS)) & 31) == 0;
+#pragma unroll
+        for (int ch = 0; ch < BKV / 8; ch += 2) {
+          const uint4 p0 = pack8_16bit(s + ch * 8, is_fp16), p1 = pack8_16bit(s + ch * 8 + 8, is_fp16);
+          const uint4 d0 = pack8_16bit(dp + ch * 8, is_fp16), d1 = pack8_16bit(dp + ch * 8 + 8, is_fp16);
+          if (wide && col0 + ch * 8 + 16 <= p.S) {
+            st_global_v8(prow + col0 + ch * 8, p0, p1);
+            st_global_v8(dsrow + col0 + ch * 8, d0, d1);
+          } else {
+            const uint4 pv[2] = {p0, p1}, dv[2] = {d0, d1};
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              const int cc = col0 + (ch + half) * 8;
+              const uint16_t* pe = (const uint16_t*)&pv[half];
+              const uint16_t* de = (const uint16_t*)&dv[half];
+              if (cc + 8 <= p.S) {
+                *(uint4*)(prow + cc) = pv[half];
+                *(uint4*)(dsrow + cc) = dv[half];
+              } else {
+                for (int e = 0; e < 8 && cc + e < p.S; ++e) {
+                  prow[cc + e] = pe[e];
+                  dsrow[cc + e] = de[e];
+                }
+              }
+            }
+          }
+        }
+      }
+      if (warp == 2 && lane == 0) XL_ATTN_BWD_STAMP(1, j, 4);
     }
-    // ---- epilogue: dQ -> global memory -------------------------------------------------------------------------------
+    // ---- epilogue: dQ -> global memory (or this CTA's partial sum -> workspace, merged by the last warp to finish) --------
     if (ok && n_kv > 0) ok = __all_sync(0xffffffffu, mbar_wait(dq_done, 0, abort_flag, p.err, ERR_DQ_DONE_WAIT));
     if (ok && n_kv > 0) {
       tcgen05_fence_after();
+      const bool split = n_parts > 1;
+      const long long slot0 = (long long)(b * p.H + h) * p.items + first_slot;  // first partial of this query block
       uint16_t* qrow_out = (uint16_t*)p.dq + (long long)(row0 + qrow) * p.ld_dq + p.dq_col + h * D;
+      float* prow_out = split ? p.part_dq + ((slot0 + part) * BLOCK_Q + r) * D : nullptr;
 #pragma unroll 1
       for (int ch = 0; ch < D / 32; ++ch) {
         uint32_t raw[32];
         tmem_ld_32x32b_x32(tmem_dq + lane_base + ch * 32, raw);
         tmem_ld_wait();
-        if (row_ok) {
+        if (split) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            *(uint4*)(prow_out + ch * 32 + g * 4) = make_uint4(raw[g * 4], raw[g * 4 + 1], raw[g * 4 + 2], raw[g * 4 + 3]);
+        } else if (row_ok) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             float v[8];
@@ -387,6 +426,94 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   if (warp == 1) {
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// delta = dO . O of every (batch, head, position): one warp per row, the lanes across the features.
+template <int D>
+__global__ void __launch_bounds__(256) attn_bwd_delta_kernel(const AttnBwdParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)p.B * p.H * p.S) return;
+  const int s_pos = (int)(w % p.S);
+  const int bh = (int)(w / p.S), b = bh / p.H, h = bh % p.H;
+  constexpr int LANES = D / 8;  // lanes that hold 8 features each
+  const bool is_fp16 = p.is_fp16 != 0;
+  float part = 0.f;
+  if (lane < LANES) {
+    const uint16_t* orow = (const uint16_t*)p.out + (long long)(b * p.S + s_pos) * p.ldo + h * D + lane * 8;
+    const uint16_t* grow = (const uint16_t*)p.dout + (long long)(b * p.S + s_pos) * p.ld_do + h * D + lane * 8;
+    const uint4 ov = *(const uint4*)orow, gv = *(const uint4*)grow;
+    const uint32_t* ow = (const uint32_t*)&ov;
+    const uint32_t* gw = (const uint32_t*)&gv;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float o_lo, o_hi, g_lo, g_hi;
+      if (is_fp16) {
+        o_lo = __half2float(__ushort_as_half((uint16_t)(ow[e] & 0xffffu)));
+        o_hi = __half2float(__ushort_as_half((uint16_t)(ow[e] >> 16)));
+        g_lo = __half2float(__ushort_as_half((uint16_t)(gw[e] & 0xffffu)));
+        g_hi = __half2float(__ushort_as_half((uint16_t)(gw[e] >> 16)));
+      } else {
+        o_lo = __uint_as_float(ow[e] << 16);
+        o_hi = __uint_as_float(ow[e] & 0xffff0000u);
+        g_lo = __uint_as_float(gw[e] << 16);
+        g_hi = __uint_as_float(gw[e] & 0xffff0000u);
+      }
+      part = fmaf(o_lo, g_lo, part);
+      part = fmaf(o_hi, g_hi, part);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+  if (lane == 0) p.delta[w] = part;
+}
+
+// Sum of the partial dQ of split query blocks: one warp per query row. Rows of query blocks that were not split were
+// written by the main kernel already.
+template <int D>
+__global__ void __launch_bounds__(256) attn_bwd_dq_merge_kernel(const AttnBwdParams p, int bkv) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)p.B * p.H * p.S) return;
+  const int s_pos = (int)(w % p.S);
+  const int bh = (int)(w / p.S), b = bh / p.H, h = bh % p.H;
+  const int n_qblocks = (p.S + BLOCK_Q - 1) / BLOCK_Q, qb = s_pos / BLOCK_Q, row = s_pos % BLOCK_Q;
+  const int n_parts = attn_chunks(attn_kv_blocks(qb, p.S, p.causal, bkv), p.chunk);
+  if (n_parts == 1) return;
+  int first_slot = 0;
+  for (int q = n_qblocks - 1; q > qb; --q) first_slot += attn_chunks(attn_kv_blocks(q, p.S, p.causal, bkv), p.chunk);
+  const long long slot0 = (long long)bh * p.items + first_slot;
+  constexpr int EL = D / 32;  // features per lane
+  float acc[EL];
+#pragma unroll
+  for (int e = 0; e < EL; ++e) acc[e] = 0.f;
+  constexpr int UNROLL = 4;  // parts whose loads are in flight together
+  for (int c0 = 0; c0 < n_parts; c0 += UNROLL) {
+    float2 raw[UNROLL][EL / 2];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const bool on = c0 + u < n_parts;
+      const float* src = p.part_dq + ((slot0 + (on ? c0 + u : 0)) * BLOCK_Q + row) * D + lane * EL;
+#pragma unroll
+      for (int e = 0; e < EL / 2; ++e) raw[u][e] = on ? *(const float2*)(src + 2 * e) : make_float2(0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+      for (int e = 0; e < EL / 2; ++e) {
+        acc[2 * e] += raw[u][e].x;
+        acc[2 * e + 1] += raw[u][e].y;
+      }
+  }
+  const bool is_fp16 = p.is_fp16 != 0;
+  uint16_t* dst = (uint16_t*)p.dq + (long long)(b * p.S + s_pos) * p.ld_dq + p.dq_col + h * D + lane * EL;
+#pragma unroll
+  for (int e = 0; e < EL; e += 2) {
+    uint32_t two;
+    if (is_fp16) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(two) : "f"(acc[e + 1]), "f"(acc[e]));
+    else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(two) : "f"(acc[e + 1]), "f"(acc[e]));
+    *(uint32_t*)(dst + e) = two;
   }
 }
 
@@ -421,8 +548,17 @@ int launch(const void* qkv, long long rows, long long cols, long long ld, const 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((p.S + BLOCK_Q - 1) / BLOCK_Q, p.H, p.B);
-  attn_bwd_dq_tcgen05_kernel<D, BKV><<<grid, NUM_THREADS, L::TOTAL, s>>>(mq, mdo, mkv, p);
+  AttnBwdParams q = p;
+  q.items = attn_items(p.S, p.causal, BKV, p.chunk);
+  if (q.items > 65535) return -1;
+  dim3 grid(p.H, q.items, p.B);
+  const long long row_warps = (long long)p.B * p.H * p.S;
+  attn_bwd_delta_kernel<D><<<(unsigned int)((row_warps + 7) / 8), 256, 0, s>>>(q);
+  attn_bwd_dq_tcgen05_kernel<D, BKV><<<grid, NUM_THREADS, L::TOTAL, s>>>(mq, mdo, mkv, q);
+  if (p.chunk > 0) {
+    const long long warps = (long long)p.B * p.H * p.S;
+    attn_bwd_dq_merge_kernel<D><<<(unsigned int)((warps + 7) / 8), 256, 0, s>>>(q, BKV);
+  }
   return (int)cudaGetLastError();
 }
 
@@ -436,11 +572,16 @@ int launch(const void* qkv, long long rows, long long cols, long long ld, const 
 //          (zeros above the diagonal); columns beyond are left untouched (the causal GEMMs never read them).
 //   dq:   (B*S x ld_dq) 16-bit output, head h in columns [dq_col + h*D, ...)
 //   All column offsets and leading dimensions must be multiples of 8, pointers 16-byte aligned, S a multiple of 8.
+//   chunk, part_dq: key-range splitting as planned by xl_attn_bwd_plan (chunk 0: none, the pointer may then be null).
+//         part_dq holds B*H*items*128*D floats; a second kernel on the same stream adds them up into dq.
+//   delta: B*H*S floats of scratch (dO . O of every row, computed by a first kernel of the launch)
+//   trace: null, or 2 * 64 * 8 64-bit words that receive clock stamps of the first CTA's roles (tuning aid).
 // Returns 0, a CUDA error code, or a negative value when the arguments are not supported by this kernel.
 XL_API int xl_attn_bwd_dq_tcgen05(const void* qkv, long long ld, long long cols, const void* out, long long ldo,
                                   const void* dout, long long ld_do, const float* lse, void* P, void* dS, void* dq,
                                   long long ld_dq, int dq_col, int B, int S, int H, int D, int q_col, int k_col, int v_col,
-                                  float scale, int causal, int is_fp16, int* err, cudaStream_t s) {
+                                  float scale, int causal, int is_fp16, int* err, int chunk, float* part_dq,
+                                  float* delta, long long* trace, cudaStream_t s) {
   if (B <= 0 || S <= 0 || H <= 0 || B > 65535 || H > 65535 || (S % 8)) return -1;
   if ((((uintptr_t)qkv) & 15) || (((uintptr_t)out) & 15) || (((uintptr_t)dout) & 15) || (((uintptr_t)P) & 15) ||
       (((uintptr_t)dS) & 15) || (((uintptr_t)dq) & 15))
@@ -457,9 +598,22 @@ XL_API int xl_attn_bwd_dq_tcgen05(const void* qkv, long long ld, long long cols,
   p.q_col = q_col; p.k_col = k_col; p.v_col = v_col;
   p.out = out; p.ldo = ldo; p.dout = dout; p.ld_do = ld_do; p.lse = lse; p.P = P; p.dS = dS; p.dq = dq; p.ld_dq = ld_dq;
   p.dq_col = dq_col; p.scale = scale; p.causal = causal ? 1 : 0; p.is_fp16 = is_fp16 ? 1 : 0; p.err = err;
+  if (chunk < 0 || (chunk > 0 && !part_dq)) return -1;
+  if (!delta) return -1;
+  p.chunk = chunk; p.items = 0; p.part_dq = part_dq; p.delta = delta; p.trace = trace;
   const long long rows = (long long)B * S;
   if (D == 256) return launch<256, 32>(qkv, rows, cols, ld, p, s);
   if (D == 128) return launch<128, 64>(qkv, rows, cols, ld, p, s);
   if (D == 64) return launch<64, 64>(qkv, rows, cols, ld, p, s);
   return -1;
+}
+
+// Plans the key-range splitting of xl_attn_bwd_dq_tcgen05 for a shape on a device with `num_sms` SMs: returns the chunk
+// (key blocks per CTA, 0 = no splitting) and stores the CTAs per head and batch entry in *items.
+XL_API int xl_attn_bwd_plan(int B, int S, int H, int D, int causal, int num_sms, int* items) {
+  if (D != 64 && D != 128 && D != 256) return -1;
+  const int bkv = D == 256 ? 32 : 64;
+  const int chunk = attn_plan_chunk(S, B * H, causal ? 1 : 0, bkv, num_sms > 0 ? num_sms : 148, 2.0, 4.0);
+  if (items) *items = attn_items(S, causal ? 1 : 0, bkv, chunk);
+  return chunk;
 }

@@ -19,6 +19,7 @@
 // Every wait on an mbarrier is bounded: when a wait gives up the kernel records a code in `*err`, raises a CTA-wide abort
 // flag, all roles leave their loops, TMEM is released and the kernel returns normally.
 #include "tcgen05.cuh"
+#include "attention_split.cuh"
 
 namespace {
 
@@ -44,9 +45,17 @@ struct AttnParams {
   int is_fp16;
   int* err;
   long long* trace;  // optional (tuning): clock64 stamps of CTA (0, 0, 0): [role 0 MMA thread | role 1 softmax warp][block][8]
+  // Key-range splitting (chunk > 0): a query block's key blocks are divided evenly over ceil(n / chunk) CTAs. Each writes
+  // its normalised partial output and log-sum-exp to the workspace; a second kernel merges the partials of every row.
+  int chunk;
+  int items;               // CTAs per head and batch entry (grid y)
+  uint16_t* part_o;        // [B*H*items][128][D] 16-bit
+  float* part_lse;         // [B*H*items][128]
 };
 
+
 using namespace xl_tc;
+using namespace xl_attn_split;
 
 #define XL_ATTN_STAMP(role, j, point)                                                                  \
   do {                                                                                                 \
@@ -94,11 +103,19 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_qblocks = (p.S + BLOCK_Q - 1) / BLOCK_Q;
-  const int qb = n_qblocks - 1 - (int)blockIdx.x;  // the blocks with the most keys start first
-  const int h = blockIdx.y, b = blockIdx.z;
+  // grid: x = head, y = work item (query block and part of its keys; the blocks with the most keys come first), z = batch
+  const int h = blockIdx.x, b = blockIdx.z;
+  int qb = n_qblocks - 1, part = (int)blockIdx.y, first_slot = 0, n_kv_all = 0, n_parts = 1;
+  for (;; --qb) {
+    n_kv_all = attn_kv_blocks(qb, p.S, p.causal, BKV);
+    n_parts = attn_chunks(n_kv_all, p.chunk);
+    if (part < n_parts || qb == 0) break;
+    part -= n_parts;
+    first_slot += n_parts;
+  }
   const int q0 = qb * BLOCK_Q;
-  const int kv_end = p.causal ? min(p.S, q0 + BLOCK_Q) : p.S;  // keys [0, kv_end) can be attended by this block
-  const int n_kv = (kv_end + BKV - 1) / BKV;
+  const int j0 = (int)(((long long)part * n_kv_all) / n_parts);           // this CTA's key blocks: [j0, j0 + n_kv)
+  const int n_kv = (int)(((long long)(part + 1) * n_kv_all) / n_parts) - j0;
   const int row0 = b * p.S;  // first token row of this batch entry in the packed matrix
 
   if (threadIdx.x == 0) {
@@ -152,7 +169,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         uint8_t* sK = sKV + stage * L::STAGE_BYTES;
         uint8_t* sV = sK + L::K_BYTES;
-        const int k0 = row0 + j * BKV;
+        const int k0 = row0 + (j0 + j) * BKV;
         if (for_k) {
           mbar_expect_tx(&full[stage], L::K_BYTES);
 #pragma unroll
@@ -268,7 +285,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);  // the score buffer may be overwritten
       if (warp == 2 && lane == 0) XL_ATTN_STAMP(1, j, 2);
-      const int col0 = j * BKV;
+      const int col0 = (j0 + j) * BKV;
       const int limit = p.causal ? min(qrow, p.S - 1) : p.S - 1;  // last key this row may attend
       float m_blk = -INFINITY;
       if (col0 + BKV - 1 > limit) {
@@ -334,8 +351,11 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     if (ok && n_kv > 0) {
       tcgen05_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      const bool row_ok = qrow < p.S;
-      uint16_t* orow = (uint16_t*)p.out + (long long)(row0 + qrow) * p.ldo + h * D;
+      const bool split = n_parts > 1;
+      const long long slot0 = (long long)(b * p.H + h) * p.items + first_slot;  // first partial of this query block
+      const bool row_ok = split || qrow < p.S;  // partial rows past the end are written too (the workspace has room)
+      uint16_t* orow = split ? p.part_o + ((slot0 + part) * BLOCK_Q + r) * D
+                             : (uint16_t*)p.out + (long long)(row0 + qrow) * p.ldo + h * D;
 #pragma unroll 1
       for (int ch = 0; ch < D / 32; ++ch) {
         uint32_t raw[32];
@@ -351,8 +371,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
           }
         }
       }
-      if (row_ok && p.lse)
-        p.lse[((long long)b * p.H + h) * p.S + qrow] = l > 0.f ? m * p.scale + logf(l) : -INFINITY;
+      const float lse_row = l > 0.f ? m * p.scale + logf(l) : -INFINITY;
+      if (!split) {
+        if (row_ok && p.lse) p.lse[((long long)b * p.H + h) * p.S + qrow] = lse_row;
+      } else {
+        p.part_lse[(slot0 + part) * BLOCK_Q + r] = lse_row;
+      }
     }
   }
 
@@ -363,6 +387,79 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     tcgen05_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+// Merge of the partial results of split query blocks: one warp per query row. Rows of query blocks that were not split
+// were written by the main kernel already.
+template <int D>
+__global__ void __launch_bounds__(256) attn_fwd_merge_kernel(const AttnParams p, int bkv) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)p.B * p.H * p.S) return;
+  const int s_pos = (int)(w % p.S);
+  const int bh = (int)(w / p.S), b = bh / p.H, h = bh % p.H;
+  const int n_qblocks = (p.S + BLOCK_Q - 1) / BLOCK_Q, qb = s_pos / BLOCK_Q, row = s_pos % BLOCK_Q;
+  const int n_parts = attn_chunks(attn_kv_blocks(qb, p.S, p.causal, bkv), p.chunk);
+  if (n_parts == 1) return;
+  int first_slot = 0;
+  for (int q = n_qblocks - 1; q > qb; --q) first_slot += attn_chunks(attn_kv_blocks(q, p.S, p.causal, bkv), p.chunk);
+  const long long slot0 = (long long)bh * p.items + first_slot;
+  const bool is_fp16 = p.is_fp16 != 0;
+  // log-sum-exp over the parts (lane c holds part c; more than 32 parts are folded in by the loops)
+  float lse_c = -INFINITY, mx = -INFINITY;
+  for (int c0 = 0; c0 < n_parts; c0 += 32) {
+    const float v = c0 + lane < n_parts ? p.part_lse[(slot0 + c0 + lane) * BLOCK_Q + row] : -INFINITY;
+    mx = fmaxf(mx, v);
+    if (c0 == 0) lse_c = v;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float den = 0.f;
+  for (int c0 = 0; c0 < n_parts; c0 += 32) {
+    const float v = c0 + lane < n_parts ? p.part_lse[(slot0 + c0 + lane) * BLOCK_Q + row] : -INFINITY;
+    den += v > -INFINITY ? __expf(v - mx) : 0.f;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+  const float lse_all = den > 0.f ? mx + logf(den) : -INFINITY;
+  constexpr int EL = D / 32;  // output features per lane
+  float acc[EL];
+#pragma unroll
+  for (int e = 0; e < EL; ++e) acc[e] = 0.f;
+  constexpr int UNROLL = 4;  // parts whose loads are in flight together
+  for (int c0 = 0; c0 < n_parts; c0 += UNROLL) {
+    uint32_t raw[UNROLL][EL / 2];
+    float wgt[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int c = c0 + u;
+      const bool on = c < n_parts;
+      const uint16_t* src = p.part_o + ((slot0 + (on ? c : 0)) * BLOCK_Q + row) * D + lane * EL;
+#pragma unroll
+      for (int e = 0; e < EL / 2; ++e) raw[u][e] = on ? *(const uint32_t*)(src + 2 * e) : 0u;
+      const float lc = c < 32 ? __shfl_sync(0xffffffffu, lse_c, c & 31) : (on ? p.part_lse[(slot0 + c) * BLOCK_Q + row] : -INFINITY);
+      wgt[u] = (on && lc > -INFINITY) ? __expf(lc - lse_all) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+      for (int e = 0; e < EL / 2; ++e) {
+        const uint32_t two = raw[u][e];
+        const float lo = is_fp16 ? __half2float(__ushort_as_half((uint16_t)(two & 0xffffu))) : __uint_as_float(two << 16);
+        const float hi = is_fp16 ? __half2float(__ushort_as_half((uint16_t)(two >> 16))) : __uint_as_float(two & 0xffff0000u);
+        acc[2 * e] = fmaf(wgt[u], lo, acc[2 * e]);
+        acc[2 * e + 1] = fmaf(wgt[u], hi, acc[2 * e + 1]);
+      }
+  }
+  uint16_t* dst = (uint16_t*)p.out + (long long)(b * p.S + s_pos) * p.ldo + h * D + lane * EL;
+#pragma unroll
+  for (int e = 0; e < EL; e += 2) {
+    uint32_t two;
+    if (is_fp16) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(two) : "f"(acc[e + 1]), "f"(acc[e]));
+    else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(two) : "f"(acc[e + 1]), "f"(acc[e]));
+    *(uint32_t*)(dst + e) = two;
+  }
+  if (lane == 0 && p.lse) p.lse[((long long)b * p.H + h) * p.S + s_pos] = lse_all;
 }
 
 // ---- host side -------------------------------------------------------------------------------------------------------
@@ -397,10 +494,19 @@ int launch(const void* qkv, long long rows, long long cols, long long ld, const 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((p.S + BLOCK_Q - 1) / BLOCK_Q, p.H, p.B);
-  attn_fwd_tcgen05_kernel<D, BKV><<<grid, NUM_THREADS, L::TOTAL, s>>>(mq, mk, mv, p);
+  AttnParams q = p;
+  q.items = attn_items(p.S, p.causal, BKV, p.chunk);
+  if (q.items > 65535) return -1;
+  dim3 grid(p.H, q.items, p.B);
+  attn_fwd_tcgen05_kernel<D, BKV><<<grid, NUM_THREADS, L::TOTAL, s>>>(mq, mk, mv, q);
+  if (p.chunk > 0) {
+    const long long warps = (long long)p.B * p.H * p.S;
+    attn_fwd_merge_kernel<D><<<(unsigned int)((warps + 7) / 8), 256, 0, s>>>(q, BKV);
+  }
   return (int)cudaGetLastError();
 }
+
+int bkv_of(int D) { return D == 256 ? 64 : 128; }
 
 }  // namespace
 
@@ -412,9 +518,13 @@ int launch(const void* qkv, long long rows, long long cols, long long ld, const 
 //   err: device int that receives a non-zero code if a bounded wait inside the kernel gave up (may be null).
 //   trace: null, or 2 * 64 * 8 64-bit words that receive clock stamps of the first CTA's roles (tuning aid).
 // Returns 0, a CUDA error code, or a negative value when the arguments are not supported by this kernel.
+//   chunk, part_o, part_lse: key-range splitting as planned by xl_attn_fwd_plan (chunk 0: none, the pointers may then
+//        be null). part_o holds B*H*items*128*D 16-bit values, part_lse B*H*items*128 floats; a second kernel on the
+//        same stream merges them into `out` and `lse`.
 XL_API int xl_attn_fwd_tcgen05(const void* qkv, long long ld, long long cols, void* out, long long ldo, float* lse, int B,
                                int S, int H, int D, int q_col, int k_col, int v_col, float scale, int causal,
-                               int is_fp16, int* err, long long* trace, cudaStream_t s) {
+                               int is_fp16, int* err, long long* trace, int chunk, void* part_o, float* part_lse,
+                               cudaStream_t s) {
   if (B <= 0 || S <= 0 || H <= 0 || B > 65535 || H > 65535) return -1;
   if ((((uintptr_t)qkv) & 15) || (((uintptr_t)out) & 15) || (ld % 8) || (ldo % 8)) return -1;
   if ((q_col % 8) || (k_col % 8) || (v_col % 8) || q_col < 0 || k_col < 0 || v_col < 0) return -1;
@@ -427,9 +537,21 @@ XL_API int xl_attn_fwd_tcgen05(const void* qkv, long long ld, long long cols, vo
   p.out = out; p.ldo = ldo; p.lse = lse; p.scale = scale; p.causal = causal ? 1 : 0; p.is_fp16 = is_fp16 ? 1 : 0;
   p.err = err;
   p.trace = trace;
+  if (chunk < 0 || (chunk > 0 && (!part_o || !part_lse))) return -1;
+  p.chunk = chunk; p.items = 0; p.part_o = (uint16_t*)part_o; p.part_lse = part_lse;
   const long long rows = (long long)B * S;
   if (D == 256) return launch<256, 64>(qkv, rows, cols, ld, p, s);
   if (D == 128) return launch<128, 128>(qkv, rows, cols, ld, p, s);
   if (D == 64) return launch<64, 128>(qkv, rows, cols, ld, p, s);
   return -1;
+}
+
+// Plans the key-range splitting of xl_attn_fwd_tcgen05 for a shape on a device with `num_sms` SMs: returns the chunk
+// (key blocks per CTA, 0 = no splitting) and stores the CTAs per head and batch entry in *items.
+XL_API int xl_attn_fwd_plan(int B, int S, int H, int D, int causal, int num_sms, int* items) {
+  if (D != 64 && D != 128 && D != 256) return -1;
+  const int bkv = bkv_of(D);
+  const int chunk = attn_plan_chunk(S, B * H, causal ? 1 : 0, bkv, num_sms > 0 ? num_sms : 148, 1.5, 2.5);
+  if (items) *items = attn_items(S, causal ? 1 : 0, bkv, chunk);
+  return chunk;
 }

@@ -144,6 +144,13 @@ __device__ __forceinline__ uint4 pack8_16bit(const float* v, bool is_fp16) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// one 32-byte store to global memory (the address must be 32-byte aligned)
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint4& a, const uint4& b) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+               "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+               : "memory");
+}
+
 // writes to shared memory by ordinary stores become visible to the tensor core's (async proxy) reads
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 

@@ -67,9 +67,12 @@ _rotary = _sig("xl_rotary", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_in
 _gq = _sig("xl_gq_decompress", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p)
 _sm_fwd = _sig("xl_attn_softmax_fwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p)
 _attn_flash = _sig("xl_attn_fwd_tcgen05", _c_p, _c_ll, _c_ll, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
-                   _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p, _c_p)
+                   _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p)
+_attn_plan = _sig("xl_attn_fwd_plan", _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p)
 _attn_bwd_dq = _sig("xl_attn_bwd_dq_tcgen05", _c_p, _c_ll, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int,
-                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p)
+                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_int, _c_p, _c_p, _c_p,
+                    _c_p)
+_attn_bwd_plan = _sig("xl_attn_bwd_plan", _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p)
 _sm_bwd = _sig("xl_attn_softmax_bwd", _c_p, _c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p)
 _ce = _sig("xl_ce_fwd_bwd", _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p, _c_f, _c_int, _c_p)
 _gemm = _sig("xl_gemm_tcgen05", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll,
@@ -781,6 +784,23 @@ def _use_flash(B, S, H):
     return B * H * ((S + 127) // 128) >= _FLASH_MIN_CTAS
 
 
+_ATTN_SPLIT = os.environ.get("XL_ATTENTION_SPLIT_KEYS", "1") != "0"
+_ATTN_PLANS: dict = {}
+
+
+def _attention_split(kind, plan_fn, B, S, H, D, causal, device):
+    """Key-range splitting of an attention kernel for this shape: `(chunk, items)` as planned by the library for the
+    device's SM count (chunk 0: every query block keeps all its keys)."""
+    key = (kind, B, S, H, D, bool(causal), device.index or 0)
+    plan = _ATTN_PLANS.get(key)
+    if plan is None:
+        items = ctypes.c_int(0)
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        chunk = plan_fn(B, S, H, D, int(bool(causal)), sms, ctypes.byref(items)) if _ATTN_SPLIT else 0
+        plan = _ATTN_PLANS[key] = (max(int(chunk), 0), int(items.value))
+    return plan
+
+
 def flash_attention_fwd(packed, q_col, k_col, v_col, B, S, H, D, scale, causal, out=None, trace=None):
     """softmax(scale * Q K^T [+ causal mask]) V for the heads stored as column windows of `packed (B*S, cols)`; one
     tcgen05 kernel, scores never leave the chip. Returns `(out (B*S, H*D), lse (B, H, S))` or NotImplemented."""
@@ -790,10 +810,16 @@ def flash_attention_fwd(packed, q_col, k_col, v_col, B, S, H, D, scale, causal, 
     if out is None:
         out = torch.empty((B * S, H * D), dtype=packed.dtype, device=packed.device)
     lse = torch.empty((B, H, S), dtype=torch.float32, device=packed.device)
+    chunk, items = _attention_split("fwd", _attn_plan, B, S, H, D, causal, packed.device)
+    part_o = part_lse = None
+    if chunk > 0:
+        slots = B * H * items * 128
+        ws = workspace(slots * (D * 2 + 4), packed.device, "attn_split")
+        part_o, part_lse = ws.data_ptr(), ws.data_ptr() + slots * D * 2
     rc = _attn_flash(packed.data_ptr(), packed.stride(0), packed.shape[1], out.data_ptr(), out.stride(0), lse.data_ptr(),
                      B, S, H, D, q_col, k_col, v_col, float(scale), int(bool(causal)),
                      int(packed.dtype == torch.float16), gemm_error_flag(packed.device).data_ptr(),
-                     trace.data_ptr() if trace is not None else None, _stream())
+                     trace.data_ptr() if trace is not None else None, chunk, part_o, part_lse, _stream())
     if rc < 0:
         return NotImplemented
     _check(rc, "attn_fwd_tcgen05")
@@ -843,7 +869,7 @@ def attention_qkv_cuda(qkv, sin, cos, seq_len, n_heads, head_dim, rotary_dim, ca
 _FLASH_ATTENTION_BWD = os.environ.get("XL_FLASH_ATTENTION_BWD", "1") != "0"
 
 
-def flash_attention_bwd_dq(qkv_rot, out, dout, lse, dqkv, B, S, H, D, scale, causal):
+def flash_attention_bwd_dq(qkv_rot, out, dout, lse, dqkv, B, S, H, D, scale, causal, trace=None):
     """First pass of the attention backward as one tcgen05 kernel: recomputes P from q, k and `lse`, forms dP = dO V^T and
     dS = P o (dP - dO . O) * scale on chip, accumulates dQ = dS K into the q window of `dqkv`, and writes P and dS once
     as `(B*H, S, S)` 16-bit matrices for the two remaining products. Returns `(P, dS)` or NotImplemented."""
@@ -854,10 +880,16 @@ def flash_attention_bwd_dq(qkv_rot, out, dout, lse, dqkv, B, S, H, D, scale, cau
         return NotImplemented
     P = torch.empty((B * H, S, S), dtype=qkv_rot.dtype, device=qkv_rot.device)
     dS = torch.empty_like(P)
+    chunk, items = _attention_split("bwd", _attn_bwd_plan, B, S, H, D, causal, qkv_rot.device)
+    part_dq = None
+    if chunk > 0:
+        part_dq = workspace(B * H * items * 128 * D * 4, qkv_rot.device, "attn_split").data_ptr()
     rc = _attn_bwd_dq(qkv_rot.data_ptr(), qkv_rot.stride(0), qkv_rot.shape[1], out.data_ptr(), out.stride(0),
                       dout.data_ptr(), dout.stride(0), lse.data_ptr(), P.data_ptr(), dS.data_ptr(), dqkv.data_ptr(),
                       dqkv.stride(0), 0, B, S, H, D, 0, hd, 2 * hd, float(scale), int(bool(causal)),
-                      int(qkv_rot.dtype == torch.float16), gemm_error_flag(qkv_rot.device).data_ptr(), _stream())
+                      int(qkv_rot.dtype == torch.float16), gemm_error_flag(qkv_rot.device).data_ptr(), chunk, part_dq,
+                      workspace(B * H * S * 4, qkv_rot.device, "attn_delta").data_ptr(),
+                      trace.data_ptr() if trace is not None else None, _stream())
     if rc < 0:
         return NotImplemented
     _check(rc, "attn_bwd_dq_tcgen05")

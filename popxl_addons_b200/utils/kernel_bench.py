@@ -163,6 +163,20 @@ def main():
         rows.append(dict(kernel=name + " (single kernel)", shape=f"{H}x{S}x{S}x{D}", ms=one, tflops=fl / one / 1e9,
                          frac_of_peak=fl / one / 1e9 / peaks["bf16_tflops"], lib_ms=default,
                          lib_tflops=fl / default / 1e9, vs_lib=default / one, lib_name="GEMM path"))
+        if nat._attention_split("fwd", nat._attn_plan, 1, S, H, D, True, qkv.device)[0] > 0:
+            # few heads: the row above divided the keys of a query block over several CTAs; the same kernel without
+            saved_split, saved_plans = nat._ATTN_SPLIT, dict(nat._ATTN_PLANS)
+            nat._ATTN_SPLIT = False
+            nat._ATTN_PLANS.clear()
+            try:
+                whole = graph_time_ms(lambda: nat.flash_attention_fwd(qkv, 0, hd, 2 * hd, 1, S, H, D, scale, True), reps=8)
+            finally:
+                nat._ATTN_SPLIT = saved_split
+                nat._ATTN_PLANS.clear()
+                nat._ATTN_PLANS.update(saved_plans)
+            rows.append(dict(kernel=name + " (single kernel, one CTA per query block)", shape=f"{H}x{S}x{S}x{D}", ms=whole,
+                             tflops=fl / whole / 1e9, frac_of_peak=fl / whole / 1e9 / peaks["bf16_tflops"], lib_ms=default,
+                             lib_tflops=fl / default / 1e9, vs_lib=default / whole, lib_name="GEMM path"))
         # fwd + bwd of the op as the training step runs it (forward as dispatched by default, backward GEMM-based)
         do = torch.randn(S, hd, device="cuda", dtype=bf)
 
