@@ -31,19 +31,25 @@ using namespace xl_tc;
 
 constexpr int CTA_M = 128;              // rows of C per CTA
 constexpr int PAIR_M = 2 * CTA_M;       // rows of C per tile
-constexpr int PAIR_N = 256;             // columns of C per tile
-constexpr int HALF_N = PAIR_N / 2;      // rows of the B tile staged by each CTA
 constexpr int BLOCK_K = 64;             // 64 x 2 bytes = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 6;
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
 constexpr int A_BYTES = CTA_M * BLOCK_K * 2;
-constexpr int B_BYTES = HALF_N * BLOCK_K * 2;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-constexpr int SMEM_TOTAL = TILE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr uint32_t TMEM_COLS = 2 * PAIR_N;  // two accumulator buffers: the whole TMEM of the SM
+
+// Tile width PN (columns of C per tile, 256 or 128): each CTA stages PN / 2 rows of the B tile. The narrow tile is for
+// shapes whose 256 x 256 tiles would fill the last wave of CTA pairs badly.
+template <int PN>
+struct PairCfg {
+  static constexpr int PAIR_N = PN;
+  static constexpr int HALF_N = PN / 2;
+  static constexpr int B_BYTES = HALF_N * BLOCK_K * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = PN == 256 ? 6 : 8;
+  static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int SMEM_TOTAL = TILE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr uint32_t TMEM_COLS = 2 * PN;  // two accumulator buffers
+};
 
 enum { ERR2_FULL_WAIT = 21, ERR2_EMPTY_WAIT = 22, ERR2_TMEM_FULL_WAIT = 23, ERR2_TMEM_EMPTY_WAIT = 24 };
 
@@ -155,9 +161,14 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   nb = in_group / rows;
 }
 
+template <int PN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm2cta_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                             const Gemm2Params p) {
+  using Cfg = PairCfg<PN>;
+  constexpr int PAIR_N = Cfg::PAIR_N, HALF_N = Cfg::HALF_N, STAGE_BYTES = Cfg::STAGE_BYTES, STAGES = Cfg::STAGES,
+                TILE_BYTES = Cfg::TILE_BYTES;
+  constexpr uint32_t TMEM_COLS = Cfg::TMEM_COLS;
   extern __shared__ uint8_t smem_raw[];
   // the dynamic shared-memory window starts at the same offset in both CTAs, so the aligned base does too: the MMA
   // applies one descriptor (one offset) to the shared memory of both
@@ -356,10 +367,12 @@ int make_map(CUtensorMap* map, const void* ptr, int is_fp16, long long rows, lon
 }
 
 // number of CTA pairs that can be resident at once on this device (0 if the query fails); looked up once
+template <int PN>
 int max_resident_pairs() {
+  constexpr int SMEM_TOTAL = PairCfg<PN>::SMEM_TOTAL;
   static int cached = -1;
   if (cached >= 0) return cached;
-  if (cudaFuncSetAttribute(gemm2cta_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL) != cudaSuccess) {
+  if (cudaFuncSetAttribute(gemm2cta_tcgen05_kernel<PN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL) != cudaSuccess) {
     cached = 0;
     return 0;
   }
@@ -375,7 +388,7 @@ int max_resident_pairs() {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, gemm2cta_tcgen05_kernel, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&n, gemm2cta_tcgen05_kernel<PN>, &cfg) != cudaSuccess) {
     cudaGetLastError();
     n = 0;
   }
@@ -383,27 +396,65 @@ int max_resident_pairs() {
   return n;
 }
 
+template <int PN>
+int launch_pairs(const CUtensorMap& ma, const CUtensorMap& mb, const Gemm2Params& p, int max_pairs, cudaStream_t s) {
+  int pairs = max_resident_pairs<PN>();
+  if (pairs <= 0) return -4;
+  if (max_pairs > 0 && max_pairs < pairs) pairs = max_pairs;
+  const long long tiles = (long long)((p.M + PAIR_M - 1) / PAIR_M) * ((p.N + PN - 1) / PN) * p.batch;
+  if (tiles < pairs) pairs = (int)tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = PairCfg<PN>::SMEM_TOTAL;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm2cta_tcgen05_kernel<PN>, ma, mb, p);
+  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
+// Tile width for a shape: the one whose tiles take less time in waves over `pairs` CTA pairs (a 256 x 128 tile takes
+// about two thirds of the time of a 256 x 256 one: its MMAs are less efficient and it re-reads A twice as often).
+int choose_pair_n(int M, int N, int batch, int pairs) {
+  if (N <= 128 || pairs <= 0) return N <= 128 ? 128 : 256;
+  const long long tm = (M + PAIR_M - 1) / PAIR_M;
+  const long long t256 = tm * ((N + 255) / 256) * batch, t128 = tm * ((N + 127) / 128) * batch;
+  const double cost256 = (double)((t256 + pairs - 1) / pairs) * 1.0;
+  const double cost128 = (double)((t128 + pairs - 1) / pairs) * 0.66;
+  return cost128 < cost256 ? 128 : 256;
+}
+
 }  // namespace
 
 // C = epilogue(A * B) on CTA pairs; same operand conventions as xl_gemm_tcgen05 (16-bit operands, fp32 accumulation).
 //   accumulate: 0 overwrite, 1 C += alpha*acc, 2 running mean with the step counter `step`.
 //   max_pairs: upper limit of CTA pairs to launch (<= 0: as many as can be resident).
+//   tile_n: columns of C per tile, 256 or 128 (0: whichever takes fewer waves of CTA pairs for this shape).
 // Returns 0, a CUDA error code, -1 for arguments this kernel does not take (the caller then uses the single-CTA
 // kernel), -4 if no CTA pair can be resident on this device.
 XL_API int xl_gemm2cta_tcgen05(const void* a, const void* b, void* c, int M, int N, int K, int batch, int a_mn, int b_mn,
                                long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
                                long long stride_c, int ab_is_fp16, int c_dtype, const void* bias, int bias_dtype, int act,
-                               int accumulate, const float* step, float alpha, int* err, int max_pairs, cudaStream_t s) {
-  if (M <= 0 || N <= HALF_N || K <= 0 || batch <= 0) return -1;
+                               int accumulate, const float* step, float alpha, int* err, int max_pairs, int tile_n,
+                               cudaStream_t s) {
+  if (M <= 0 || N <= 64 || K <= 0 || batch <= 0) return -1;
   if ((((uintptr_t)a) & 15) || (((uintptr_t)b) & 15) || (lda % 8) || (ldb % 8)) return -1;
   if (batch > 1 && ((stride_a % 8) || (stride_b % 8))) return -1;
   if (accumulate < 0 || accumulate > 2 || (accumulate == 2 && step == nullptr)) return -1;
+  if (tile_n != 0 && tile_n != 128 && tile_n != 256) return -1;
+  const int pair_n = tile_n ? tile_n : choose_pair_n(M, N, batch, max_pairs > 0 ? max_pairs : max_resident_pairs<256>());
   CUtensorMap ma, mb;
   int r;
   if (!a_mn) r = make_map(&ma, a, ab_is_fp16, M, K, lda, batch, stride_a, BLOCK_K, CTA_M);
   else r = make_map(&ma, a, ab_is_fp16, K, M, lda, batch, stride_a, 64, BLOCK_K);
   if (r) return r;
-  if (!b_mn) r = make_map(&mb, b, ab_is_fp16, N, K, ldb, batch, stride_b, BLOCK_K, HALF_N);
+  if (!b_mn) r = make_map(&mb, b, ab_is_fp16, N, K, ldb, batch, stride_b, BLOCK_K, pair_n / 2);
   else r = make_map(&mb, b, ab_is_fp16, K, N, ldb, batch, stride_b, 64, BLOCK_K);
   if (r) return r;
   Gemm2Params p;
@@ -413,23 +464,6 @@ XL_API int xl_gemm2cta_tcgen05(const void* a, const void* b, void* c, int M, int
   p.epi.N = N; p.epi.c_dtype = c_dtype; p.epi.bias = bias; p.epi.bias_dtype = bias_dtype; p.epi.act = act;
   p.epi.accumulate = accumulate;
   p.step = step; p.alpha = alpha; p.is_fp16 = ab_is_fp16; p.err = err;
-  int pairs = max_resident_pairs();
-  if (pairs <= 0) return -4;
-  if (max_pairs > 0 && max_pairs < pairs) pairs = max_pairs;
-  const long long tiles = (long long)((M + PAIR_M - 1) / PAIR_M) * ((N + PAIR_N - 1) / PAIR_N) * batch;
-  if (tiles < pairs) pairs = (int)tiles;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * pairs, 1, 1);
-  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = SMEM_TOTAL;
-  cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm2cta_tcgen05_kernel, ma, mb, p);
-  return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+  if (pair_n == 128) return launch_pairs<128>(ma, mb, p, max_pairs, s);
+  return launch_pairs<256>(ma, mb, p, max_pairs, s);
 }

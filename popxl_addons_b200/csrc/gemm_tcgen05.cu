@@ -895,7 +895,12 @@ XL_API int xl_gemm_tcgen05_fused(const void* a, const void* b, void* c, int M, i
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -1;
   if ((((uintptr_t)a) & 15) || (((uintptr_t)b) & 15) || (lda % 8) || (ldb % 8)) return -1;
   if (batch > 1 && ((stride_a % 8) || (stride_b % 8))) return -1;
-  const int block_n = (N <= 128) ? 128 : 256;
+  if (sm_count <= 0) sm_count = 148;
+  int block_n = (N <= 128) ? 128 : 256;
+  // too few 128 x 256 tiles to occupy half of the SMs: narrower tiles double the CTAs that work
+  if (block_n == 256 && !gather_mode && accumulate < 3 &&
+      2LL * ((M + BLOCK_M - 1) / BLOCK_M) * ((N + 255) / 256) * batch <= sm_count)
+    block_n = 128;
   CUtensorMap ma, mb;
   int r;
   if (!a_mn) r = make_map(&ma, a, ab_is_fp16, M, K, lda, batch, stride_a, BLOCK_K, BLOCK_M);

@@ -82,7 +82,8 @@ _gemm_fused = _sig("xl_gemm_tcgen05_fused", _c_p, _c_p, _c_p, _c_int, _c_int, _c
                    _c_ll, _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_p,
                    _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p)
 _gemm_pair = _sig("xl_gemm2cta_tcgen05", _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll,
-                  _c_ll, _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_p)
+                  _c_ll, _c_ll, _c_ll, _c_ll, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_p, _c_f, _c_p, _c_int, _c_int,
+                  _c_p)
 _rts_multi_grid = _sig("xl_rts_adam_multi_grid", _c_int)
 _rts_adam_multi = _sig("xl_rts_adam_multi", _c_p, _c_int, _c_int, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p,
                        _c_p, _c_p, _c_f, _c_f, _c_f, _c_f, _c_f, _c_int, _c_p)
@@ -498,6 +499,8 @@ def _major(t: torch.Tensor, contraction_last: bool):
 # kernel on the transformer shapes); collective epilogues, the all-gather prologue and causal products keep the
 # single-CTA kernel. XL_GEMM_CTA_PAIRS=0 switches the pairs off.
 _GEMM_CTA_PAIRS = os.environ.get("XL_GEMM_CTA_PAIRS", "1") != "0"
+# columns of C per tile of the CTA-pair kernel: 0 lets the library pick 256 or 128 per shape (fewer waves of CTA pairs)
+_GEMM_PAIR_TILE_N = [int(os.environ.get("XL_GEMM_PAIR_TILE_N", "0"))]
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = None, act: int = 0,
@@ -577,7 +580,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, bias: Optional[torch.Tensor] = Non
         rc = _gemm_pair(a.data_ptr(), b.data_ptr(), out_ptr, M, N, K, batch, a_mn, b_mn, lda, ldb, ldc, sa, sb, stride_c,
                         int(a.dtype == torch.float16), _CODE[out.dtype], bias.data_ptr() if bias is not None else None,
                         _CODE[bias.dtype] if bias is not None else 0, act, accumulate,
-                        step.data_ptr() if step is not None else None, float(alpha), err.data_ptr(), 0, _stream())
+                        step.data_ptr() if step is not None else None, float(alpha), err.data_ptr(), 0, _GEMM_PAIR_TILE_N[0],
+                        _stream())
         if rc >= 0:
             _check(rc, "gemm2cta_tcgen05")
             _count("gemm2cta_tcgen05")

@@ -108,19 +108,21 @@ def main():
 
         fl = 2.0 * M * N * K * batch
         lib = graph_time_ms(rotating(lambda av, bv, out: torch.matmul(av, bv, out=out)), reps=reps)
-        saved = nat._GEMM_CTA_PAIRS
+        saved, saved_tile = nat._GEMM_CTA_PAIRS, nat._GEMM_PAIR_TILE_N[0]
         try:
-            for pairs in (True, False):
-                nat._GEMM_CTA_PAIRS = pairs
+            # CTA pairs with the tile width picked per shape (the default), with each width forced, and the single-CTA kernel
+            for pairs, tile_n, tag in ((True, 0, " [CTA pairs]"), (True, 256, " [CTA pairs, 256-wide tiles]"),
+                                       (True, 128, " [CTA pairs, 128-wide tiles]"), (False, 0, " [single CTA]")):
+                nat._GEMM_CTA_PAIRS, nat._GEMM_PAIR_TILE_N[0] = pairs, tile_n
                 if pairs and N <= 128:
                     continue
                 ours = graph_time_ms(rotating(lambda av, bv, out: nat.gemm(av, bv, out=out)), reps=reps)
-                rows.append(dict(kernel=name + (" [CTA pairs]" if pairs else " [single CTA]"),
+                rows.append(dict(kernel=name + tag,
                                  shape=f"{batch}x{M}x{N}x{K}", ms=ours, tflops=fl / ours / 1e9,
                                  frac_of_peak=fl / ours / 1e9 / peaks["bf16_tflops"], lib_ms=lib,
                                  lib_tflops=fl / lib / 1e9, vs_lib=lib / ours))
         finally:
-            nat._GEMM_CTA_PAIRS = saved
+            nat._GEMM_CTA_PAIRS, nat._GEMM_PAIR_TILE_N[0] = saved, saved_tile
 
     gemm_row("gemm fwd qkv", 2048, 12288, 4096)
     gemm_row("gemm fwd fc_in", 2048, 16384, 4096)
@@ -138,6 +140,9 @@ def main():
     gemm_row("gemm tp4 wgrad fc_in (A,B MN-major)", 4096, 4096, 2048, a_t=True)
     gemm_row("gemm tp4 dgrad out (B K-major)", 2048, 1024, 4096, b_t=True)
     gemm_row("gemm tp4 wgrad out (A,B MN-major)", 1024, 4096, 2048, a_t=True)
+    gemm_row("gemm tp4 fwd qkv|fc_in", 2048, 7168, 4096)
+    gemm_row("gemm tp4 dgrad qkv (B K-major)", 2048, 4096, 3072, b_t=True)
+    gemm_row("gemm tp4 wgrad qkv (A,B MN-major)", 4096, 3072, 2048, a_t=True)
 
     def attention_row(name, S, H, D):
         """Causal attention forward of one GPT-J micro-batch: the default path (scores GEMM with causal tile skipping,

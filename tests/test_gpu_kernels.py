@@ -389,8 +389,10 @@ def test_attention_on_packed_qkv_forward_and_fused_backward(nat, B, S, H, D, rot
     (300, 264, 128, 3, False, False, torch.bfloat16),     # batched
     (4096, 4096, 1024, 1, False, True, torch.bfloat16),   # more tiles than CTA pairs: both accumulator buffers cycle
 ])
-def test_cta_pair_gemm(nat, M, N, K, batch, ta, tb, dtype):
-    """256 x 256 tiles on CTA pairs against an fp32 product; every epilogue form on one shape."""
+@pytest.mark.parametrize("tile_n", [256, 128])
+def test_cta_pair_gemm(nat, M, N, K, batch, ta, tb, dtype, tile_n, monkeypatch):
+    """256 x 256 and 256 x 128 tiles on CTA pairs against an fp32 product; every epilogue form on one shape."""
+    monkeypatch.setattr(nat, "_GEMM_PAIR_TILE_N", [tile_n])
     torch.manual_seed(5)
     lead = (batch,) if batch > 1 else ()
     a = torch.randn(*lead, K, M, device="cuda").to(dtype).transpose(-1, -2) if ta else torch.randn(*lead, M, K, device="cuda").to(dtype)
