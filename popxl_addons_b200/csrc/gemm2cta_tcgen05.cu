@@ -47,7 +47,8 @@ struct PairCfg {
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = PN == 256 ? 6 : 8;
   static constexpr int TILE_BYTES = STAGES * STAGE_BYTES;
-  static constexpr int SMEM_TOTAL = TILE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int STAGING_BYTES = NUM_EPI_WARPS * 32 * 32 * 4;  // one 32 x 32 fp32 chunk per epilogue warp
+  static constexpr int SMEM_TOTAL = TILE_BYTES + STAGING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
   static constexpr uint32_t TMEM_COLS = 2 * PN;  // two accumulator buffers
 };
 
@@ -173,7 +174,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
   // the dynamic shared-memory window starts at the same offset in both CTAs, so the aligned base does too: the MMA
   // applies one descriptor (one offset) to the shared memory of both
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = (uint64_t*)(smem + TILE_BYTES);
+  uint8_t* staging = smem + TILE_BYTES;               // fp32 C: chunks are transposed here so that rows are stored whole
+  uint64_t* bars = (uint64_t*)(smem + TILE_BYTES + Cfg::STAGING_BYTES);
   uint64_t* full_bar = bars;                          // [STAGES]  used in the leader only
   uint64_t* empty_bar = bars + STAGES;                // [STAGES]  one per CTA, both signalled by the leader's commits
   uint64_t* tmem_full_bar = bars + 2 * STAGES;        // [2]       one per CTA, both signalled by the leader's commits
@@ -312,21 +314,71 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     for (int tile = pair; tile < num_tiles && ok; tile += npairs) {
       int b, mb, nb;
       tile_coords(tile, tiles_m, tiles_n, b, mb, nb);
+      const int row = mb * PAIR_M + (int)rank * CTA_M + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      uint8_t* crow = (uint8_t*)p.C + ((long long)b * p.batch_stride_c + (long long)row * p.ldc) * esz;
       ok = mbar_wait_pair(&tmem_full_bar[acc], acc_phase, abort_flag, peer_abort_addr, p.err, ERR2_TMEM_FULL_WAIT);
       if (!ok) break;
       tcgen05_fence_after();
-      const int row = mb * PAIR_M + (int)rank * CTA_M + q * 32 + lane;
-      const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * PAIR_N;
-      uint8_t* crow = (uint8_t*)p.C + ((long long)b * p.batch_stride_c + (long long)row * p.ldc) * esz;
+      // fp32 C whose rows are 16-byte aligned: a thread holds 32 columns of ONE row, so storing from the registers would
+      // touch 32 lines per instruction (and so would reading the old contents when accumulating). The chunk goes through
+      // shared memory instead and leaves as whole 128-byte row pieces, four rows per instruction.
+      const bool staged = p.epi.c_dtype == XL_F32 && (p.ldc % 4) == 0 && ((((uintptr_t)p.C) | ((uintptr_t)(p.batch_stride_c * 4))) & 15) == 0;
+      float4* stage = (float4*)(staging + (warp - 2) * (32 * 32 * 4));
+      const int row_base = mb * PAIR_M + (int)rank * CTA_M + q * 32;
 #pragma unroll 1
       for (int c = col_half * COLS_PER_WARP; c < (col_half + 1) * COLS_PER_WARP; c += 32) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(taddr + c, r);
         tmem_ld_wait();
         const int col0 = nb * PAIR_N + c;
-        if (!row_ok || col0 >= p.N) continue;
-        epilogue_store_32cols(p.epi, r, crow, col0, p.alpha, mean_a, mean_b);
+        if (col0 >= p.N) continue;  // uniform over the warp
+        if (!(staged && col0 + 32 <= p.N)) {
+          if (row_ok) epilogue_store_32cols(p.epi, r, crow, col0, p.alpha, mean_a, mean_b);
+          continue;
+        }
+        // old contents first (their latency overlaps the staging): lane -> row (lane / 8) of each group of four, 16 bytes
+        const int sub_row = lane >> 3, sub_col = (lane & 7) * 4;
+        float* cbase = (float*)p.C + (long long)b * p.batch_stride_c + col0 + sub_col;
+        float4 old[8];
+        if (p.epi.accumulate) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = row_base + i * 4 + sub_row;
+            old[i] = rr < p.M ? *(const float4*)(cbase + (long long)rr * p.ldc) : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
+        // this thread's row -> shared memory, 16-byte pieces swizzled by the row so that both phases are conflict-free
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float v[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float x = __uint_as_float(r[j * 4 + e]) * p.alpha;
+            if (p.epi.bias) {
+              const int col = col0 + j * 4 + e;
+              x += p.epi.bias_dtype == XL_F32 ? ((const float*)p.epi.bias)[col]
+                   : p.epi.bias_dtype == XL_BF16 ? __bfloat162float(((const __nv_bfloat16*)p.epi.bias)[col])
+                                                 : __half2float(((const __half*)p.epi.bias)[col]);
+            }
+            v[e] = apply_act(x, p.epi.act);
+          }
+          stage[lane * 8 + (j ^ (lane & 7))] = make_float4(v[0], v[1], v[2], v[3]);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int lr = i * 4 + sub_row, rr = row_base + lr;
+          float4 o = stage[lr * 8 + ((lane & 7) ^ (lr & 7))];
+          if (p.epi.accumulate == 1) { o.x += old[i].x; o.y += old[i].y; o.z += old[i].z; o.w += old[i].w; }
+          else if (p.epi.accumulate == 2) {
+            o.x = old[i].x * mean_a + o.x * mean_b; o.y = old[i].y * mean_a + o.y * mean_b;
+            o.z = old[i].z * mean_a + o.z * mean_b; o.w = old[i].w * mean_a + o.w * mean_b;
+          }
+          if (rr < p.M) *(float4*)(cbase + (long long)rr * p.ldc) = o;
+        }
+        __syncwarp();  // the buffer is rewritten by the next chunk
       }
       // all TMEM reads of this warp are complete (wait::ld above): hand the accumulator back to the leader's MMA thread
       tcgen05_fence_before();

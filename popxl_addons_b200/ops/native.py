@@ -773,11 +773,11 @@ def _heads_view(mat, col0, B, S, H, D):
 
 # the masked half of causal attention products is not computed (XL_CAUSAL_SKIP=0 computes the full products)
 _CAUSAL_SKIP = os.environ.get("XL_CAUSAL_SKIP", "1") != "0"
-# The forward pass of `attention_qkv` runs as one kernel that keeps the scores on chip (measured 1.65x the GEMM + softmax
-# + GEMM path at 16 heads x 2048 x 256) when it has enough (batch, head, query block) work items to fill the SMs; with
-# fewer the batched GEMM path, which also spreads one head's keys over CTAs, is used. XL_FLASH_ATTENTION=0 / 1 forces it.
+# The forward pass of `attention_qkv` runs as one kernel that keeps the scores on chip (measured 2.7x the GEMM + softmax +
+# GEMM path at 16 heads x 2048 x 256 and 1.8x at 4 heads, where the keys of a query block are divided over CTAs). Only
+# with very little work (short sequences of few heads) the batched GEMM path is used. XL_FLASH_ATTENTION=0 / 1 forces it.
 _FLASH_ATTENTION = os.environ.get("XL_FLASH_ATTENTION", "auto")
-_FLASH_MIN_CTAS = 120
+_FLASH_MIN_CTAS = 16
 
 
 def _use_flash(B, S, H):

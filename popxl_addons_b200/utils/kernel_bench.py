@@ -77,7 +77,7 @@ def main():
     rows = []
     bf = torch.bfloat16
 
-    def gemm_row(name, M, N, K, a_t=False, b_t=False, batch=1):
+    def gemm_row(name, M, N, K, a_t=False, b_t=False, batch=1, mean_into_fp32=False):
         """Device time of one launch, from a replayed graph of back-to-back launches that walk round-robin through
         enough operand sets to exceed L2 (so every launch streams its operands from HBM, as inside a training step, and
         the host launch path of a short kernel is not in the number). Both tcgen05 kernels and cuBLAS on every shape."""
@@ -93,7 +93,8 @@ def main():
             bv = b.transpose(-1, -2) if b_t else b
             if batch == 1:
                 av, bv = av[0], bv[0]
-            sets.append((av, bv, torch.empty((batch, M, N) if batch > 1 else (M, N), device="cuda", dtype=bf)))
+            sets.append((av, bv, torch.zeros((batch, M, N) if batch > 1 else (M, N), device="cuda",
+                                             dtype=torch.float32 if mean_into_fp32 else bf)))
         reps = max(n_sets, 24 // n_sets * n_sets)
 
         def rotating(fn):
@@ -107,7 +108,21 @@ def main():
             return call
 
         fl = 2.0 * M * N * K * batch
-        lib = graph_time_ms(rotating(lambda av, bv, out: torch.matmul(av, bv, out=out)), reps=reps)
+        if mean_into_fp32:
+            # weight gradient folded into an fp32 accumulator (running mean over micro-batches) by the GEMM's epilogue;
+            # the library form is a product in 16 bits followed by an in-place update of the accumulator
+            step = torch.full((1,), 3.0, device="cuda")
+            tmp = torch.empty((M, N), device="cuda", dtype=bf)
+
+            def lib_fn(av, bv, out):
+                torch.matmul(av, bv, out=tmp)
+                return out.mul_(0.75).add_(tmp, alpha=0.25)
+
+            lib = graph_time_ms(rotating(lib_fn), reps=reps)
+            ours_fn = lambda av, bv, out: nat.gemm(av, bv, out=out, accumulate=2, step=step)  # noqa: E731
+        else:
+            lib = graph_time_ms(rotating(lambda av, bv, out: torch.matmul(av, bv, out=out)), reps=reps)
+            ours_fn = lambda av, bv, out: nat.gemm(av, bv, out=out)  # noqa: E731
         saved, saved_tile = nat._GEMM_CTA_PAIRS, nat._GEMM_PAIR_TILE_N[0]
         try:
             # CTA pairs with the tile width picked per shape (the default), with each width forced, and the single-CTA kernel
@@ -116,7 +131,7 @@ def main():
                 nat._GEMM_CTA_PAIRS, nat._GEMM_PAIR_TILE_N[0] = pairs, tile_n
                 if pairs and N <= 128:
                     continue
-                ours = graph_time_ms(rotating(lambda av, bv, out: nat.gemm(av, bv, out=out)), reps=reps)
+                ours = graph_time_ms(rotating(ours_fn), reps=reps)
                 rows.append(dict(kernel=name + tag,
                                  shape=f"{batch}x{M}x{N}x{K}", ms=ours, tflops=fl / ours / 1e9,
                                  frac_of_peak=fl / ours / 1e9 / peaks["bf16_tflops"], lib_ms=lib,
@@ -129,7 +144,9 @@ def main():
     gemm_row("gemm fwd fc_out", 2048, 4096, 16384)
     gemm_row("gemm dgrad fc_in (B K-major)", 2048, 4096, 16384, b_t=True)
     gemm_row("gemm wgrad fc_in (A,B MN-major)", 4096, 16384, 2048, a_t=True)
+    gemm_row("gemm wgrad fc_in into fp32 mean (A,B MN-major)", 4096, 16384, 2048, a_t=True, mean_into_fp32=True)
     gemm_row("gemm lm_head", 2048, 50400, 4096)
+    gemm_row("gemm wgrad lm_head into fp32 mean (A,B MN-major)", 4096, 50400, 2048, a_t=True, mean_into_fp32=True)
     gemm_row("gemm attn scores", 2048, 2048, 256, b_t=True, batch=16)
     gemm_row("gemm attn pv", 2048, 256, 2048, batch=16)
     gemm_row("gemm square 8192", 8192, 8192, 8192)

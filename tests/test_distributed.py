@@ -138,7 +138,8 @@ def test_gpu_ranks_fused_collectives(tp, dp):
     kernels = got["kernels"]
     assert "gemm_tcgen05" in kernels or "gemm2cta_tcgen05" in kernels
     if dp > 1:
-        assert kernels.get("rts_adam", 0) > 0 and kernels.get("symm_barrier", 0) > 0
+        # the sharded optimizer step ran as the one-launch-per-bucket kernel (or the per-tensor one) over peer memory
+        assert kernels.get("rts_adam_bucket", 0) + kernels.get("rts_adam", 0) > 0, kernels
     if tp > 1:
         assert got["fused_pairs"] > 0
         assert kernels.get("gemm_ar_pull_tcgen05", 0) > 0, kernels  # the TP all-reduce ran inside the GEMM kernel
