@@ -318,26 +318,50 @@ __global__ void __launch_bounds__(NORM_THREADS)
     for (int k = 0; k < N; ++k) { dw[it][k] = 0.f; db[it][k] = 0.f; ww[it][k] = 0.f; }
     if (i < nvec) xl_load16(w + i * N, ww[it]);
   }
+  // The next row's loads are issued before the current row's two block reductions: with two CTAs of 8 warps per SM the
+  // row-by-row chain load -> reduce -> store would otherwise leave the memory system idle most of the time.
+  // (only while the extra registers keep two CTAs per SM: up to 16 values per array and thread)
+  constexpr bool AHEAD = ITERS * N <= 16;
+  uint4 nx[ITERS], ng[ITERS];
+  float n_mu = 0.f, n_rs = 0.f;
+  auto request = [&](long long row) {
+    if (row >= rows) return;
+    n_mu = RMS ? 0.f : mean[row];
+    n_rs = rstd[row];
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int i = threadIdx.x + it * NORM_THREADS;
+      if (i < nvec) {
+        nx[it] = *reinterpret_cast<const uint4*>(x + row * cols + i * N);
+        ng[it] = *reinterpret_cast<const uint4*>(g + row * cols + i * N);
+      }
+    }
+  };
+  request(blockIdx.x);
   for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float mu = RMS ? 0.f : mean[row];
-    const float rs = rstd[row];
+    if (!AHEAD && row != (long long)blockIdx.x) request(row);
+    const float mu = n_mu, rs = n_rs;
+    uint4 cx[ITERS], cg[ITERS];
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) { cx[it] = nx[it]; cg[it] = ng[it]; }
+    if (AHEAD) request(row + gridDim.x);
     float xh[ITERS][N], gw[ITERS][N];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
       const int i = threadIdx.x + it * NORM_THREADS;
       if (i < nvec) {
-        float xv[N], gv[N];
-        xl_load16(x + row * cols + i * N, xv);
-        xl_load16(g + row * cols + i * N, gv);
+        const T* xe = reinterpret_cast<const T*>(&cx[it]);
+        const T* ge = reinterpret_cast<const T*>(&cg[it]);
 #pragma unroll
         for (int k = 0; k < N; ++k) {
-          xh[it][k] = (xv[k] - mu) * rs;
-          gw[it][k] = gv[k] * ww[it][k];
+          const float xv = xl_to_float(xe[k]), gv = xl_to_float(ge[k]);
+          xh[it][k] = (xv - mu) * rs;
+          gw[it][k] = gv * ww[it][k];
           s1 += gw[it][k];
           s2 += gw[it][k] * xh[it][k];
-          dw[it][k] += gv[k] * xh[it][k];
-          db[it][k] += gv[k];
+          dw[it][k] += gv * xh[it][k];
+          db[it][k] += gv;
         }
       }
     }
@@ -421,6 +445,91 @@ XL_API int xl_layer_norm_bwd(const void* x, const void* w, const float* mean, co
 XL_API int xl_rms_norm_bwd(const void* x, const void* w, const float* rstd, const void* g, void* dx, void* dw,
                            float* scratch, long long rows, int cols, int dtype, cudaStream_t s) {
   return norm_bwd_launch<true>(x, w, nullptr, rstd, g, dx, dw, nullptr, scratch, rows, cols, dtype, s);
+}
+
+// ------------------------------------------------------------------------------------------------------------------
+// Column sums of a row-major matrix (bias gradients: sum over the token rows)
+// ------------------------------------------------------------------------------------------------------------------
+constexpr int COLSUM_THREADS = 256;
+
+// grid (column tiles of 32 lanes x N columns, row parts): the 8 warps of a CTA take every 8th row of the part, four
+// rows in flight per warp; the warps' sums are added through shared memory in a fixed order and written to
+// `partial[part][cols]`; the finish kernel adds the parts in a fixed order (deterministic).
+template <typename T>
+__global__ void __launch_bounds__(COLSUM_THREADS)
+    col_sum_kernel(const T* __restrict__ x, float* __restrict__ partial, long long rows, int cols, long long rows_per_part) {
+  constexpr int N = XlVec<T>::N;
+  __shared__ float red[COLSUM_THREADS / 32][32 * N + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int c0 = (blockIdx.x * 32 + lane) * N;
+  const long long r_begin = blockIdx.y * rows_per_part;
+  const long long r_end = r_begin + rows_per_part < rows ? r_begin + rows_per_part : rows;
+  float acc[N];
+#pragma unroll
+  for (int k = 0; k < N; ++k) acc[k] = 0.f;
+  if (c0 < cols) {
+    constexpr int WARPS = COLSUM_THREADS / 32;
+    long long r = r_begin + warp;
+    for (; r + 3 * WARPS < r_end; r += 4 * WARPS) {
+      float v[4][N];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) xl_load16(x + (r + u * WARPS) * cols + c0, v[u]);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int k = 0; k < N; ++k) acc[k] += v[u][k];
+    }
+    for (; r < r_end; r += WARPS) {
+      float v[N];
+      xl_load16(x + r * cols + c0, v);
+#pragma unroll
+      for (int k = 0; k < N; ++k) acc[k] += v[k];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < N; ++k) red[warp][lane * N + k] = acc[k];
+  __syncthreads();
+  for (int i = threadIdx.x; i < 32 * N; i += COLSUM_THREADS) {
+    const int c = blockIdx.x * 32 * N + i;
+    if (c < cols) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < COLSUM_THREADS / 32; ++w) t += red[w][i];
+      partial[(long long)blockIdx.y * cols + c] = t;
+    }
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(256) col_sum_finish_kernel(const float* __restrict__ partial, T* __restrict__ out, int parts, int cols) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= cols) return;
+  float t = 0.f;
+  for (int p = 0; p < parts; ++p) t += partial[(long long)p * cols + c];
+  out[c] = xl_from_float<T>(t);
+}
+
+// Row parts (= rows of the fp32 scratch `partial`, parts x cols) that xl_col_sum uses for this shape.
+XL_API int xl_col_sum_parts(long long rows, int cols, int dtype) {
+  const int n = dtype == XL_F32 ? 4 : 8;
+  const long long tiles = (cols + 32 * n - 1) / (32 * n);
+  long long parts = (4 * 148 + tiles - 1) / tiles;  // about four CTAs per SM in total
+  const long long max_parts = (rows + 31) / 32;     // at least 32 rows per part
+  if (parts > max_parts) parts = max_parts;
+  if (parts > 256) parts = 256;
+  return (int)(parts < 1 ? 1 : parts);
+}
+// out[c] = sum over rows of x[r][c]; x row-major (rows x cols) with cols a multiple of 16 bytes, 16-byte aligned.
+XL_API int xl_col_sum(const void* x, void* out, float* partial, long long rows, int cols, int dtype, cudaStream_t s) {
+  const int n = dtype == XL_F32 ? 4 : 8;
+  if (rows <= 0 || cols <= 0 || (cols % n) || (((uintptr_t)x) & 15)) return -1;
+  const int parts = xl_col_sum_parts(rows, cols, dtype);
+  const long long rows_per_part = (rows + parts - 1) / parts;
+  dim3 grid((cols + 32 * n - 1) / (32 * n), parts);
+  XL_DISPATCH_DTYPE(dtype, T, {
+    col_sum_kernel<T><<<grid, COLSUM_THREADS, 0, s>>>((const T*)x, partial, rows, cols, rows_per_part);
+    col_sum_finish_kernel<T><<<(cols + 255) / 256, 256, 0, s>>>(partial, (T*)out, parts, cols);
+  });
+  return (int)cudaGetLastError();
 }
 
 // ------------------------------------------------------------------------------------------------------------------

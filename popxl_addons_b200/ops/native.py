@@ -59,6 +59,8 @@ _norm_parts = _sig("xl_norm_bwd_parts", _c_ll)
 _adam = _sig("xl_adam_step", _c_p, _c_int, _c_p, _c_int, _c_p, _c_int, _c_p, _c_p, _c_p, _c_f, _c_f, _c_f, _c_f, _c_f,
              _c_f, _c_int, _c_ll, _c_p)
 _sgd = _sig("xl_sgd_step", _c_p, _c_int, _c_p, _c_int, _c_p, _c_f, _c_f, _c_f, _c_f, _c_ll, _c_p)
+_col_sum = _sig("xl_col_sum", _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_p)
+_col_sum_parts = _sig("xl_col_sum_parts", _c_ll, _c_int, _c_int)
 _acc_mean = _sig("xl_accumulate_mean", _c_p, _c_int, _c_p, _c_int, _c_p, _c_ll, _c_p)
 _sumsq_parts = _sig("xl_sumsq_parts", _c_ll)
 _sumsq = _sig("xl_grad_sumsq", _c_p, _c_int, _c_p, _c_p, _c_p, _c_ll, _c_p)
@@ -399,6 +401,32 @@ def sgd_cuda(w, g, *rest, has_momentum, **attrs):
     _check(rc, "sgd_step")
     _count("sgd_step")
     return w
+
+
+@native("sum")
+def sum_cuda(a, axis, keepdims):
+    """Sum over the leading axes of a contiguous tensor (bias gradients: over the token rows): column sums in fp32,
+    added in a fixed order."""
+    if axis is None or keepdims or not _ok(a) or a.dim() < 2:
+        return NotImplemented
+    axes = sorted(int(x) % a.dim() for x in axis)
+    if axes != list(range(len(axes))) or len(axes) == a.dim():
+        return NotImplemented
+    cols = 1
+    for d in a.shape[len(axes):]:
+        cols *= d
+    rows = a.numel() // max(cols, 1)
+    n = 4 if a.dtype == torch.float32 else 8
+    if rows < 64 or cols % n or a.dtype not in _CODE:
+        return NotImplemented
+    out = torch.empty(a.shape[len(axes):], dtype=a.dtype, device=a.device)
+    ws = workspace(_col_sum_parts(rows, cols, _CODE[a.dtype]) * cols * 4, a.device, "col_sum")
+    rc = _col_sum(a.data_ptr(), out.data_ptr(), ws.data_ptr(), rows, cols, _CODE[a.dtype], _stream())
+    if rc == -1:
+        return NotImplemented
+    _check(rc, "col_sum")
+    _count("col_sum")
+    return out
 
 
 @native("accumulate_mean_")

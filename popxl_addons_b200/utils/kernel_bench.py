@@ -59,12 +59,56 @@ def graph_time_ms(fn, reps=40, iters=5):
     return times[len(times) // 2]
 
 
+def attention_trace(nat, H, S=2048, D=256):
+    """Where an iteration (one key block) of the attention kernels goes: SM clock stamps taken by the MMA-issuing thread
+    and by the first softmax / element-wise warp of CTA (0, 0, 0), which owns the last query block."""
+    import math
+
+    hd = H * D
+    torch.manual_seed(0)
+    qkv = (torch.randn(S, 3 * hd, device="cuda") * 0.5).bfloat16()
+    do = (torch.randn(S, hd, device="cuda") * 0.5).bfloat16()
+    scale = 1 / math.sqrt(D)
+
+    def stamps(run):
+        trace = torch.zeros(2 * 64 * 8, dtype=torch.int64, device="cuda")
+        for _ in range(3):
+            run(None)
+        run(trace)
+        torch.cuda.synchronize()
+        t = trace.view(2, 64, 8).cpu()
+        return t, int(t[t > 0].min()), int((t[0, :, 0] > 0).sum())
+
+    def show(t, t0, n, role, cols, label):
+        print(label)
+        for j in list(range(min(n, 4))) + list(range(max(4, n - 2), n)):
+            print("   block %2d" % j, [int(t[role, j, k]) - t0 if t[role, j, k] > 0 else -1 for k in cols])
+
+    t, t0, n = stamps(lambda tr: nat.flash_attention_fwd(qkv, 0, hd, 2 * hd, 1, S, H, D, scale, True, trace=tr))
+    print(f"forward, {H} heads: {n} key blocks of 64 in CTA 0")
+    show(t, t0, n, 0, (0, 1, 2, 3, 4), "  MMA thread: iteration start | scores of block j+1 issued | V_j there | P_j there | P_j V_j issued")
+    show(t, t0, n, 1, (0, 1, 2, 3, 4, 5), "  softmax warp: enter | S_j there | loaded | exponentials done | previous PV done | P_j written")
+    m = t[0, :, 0].double()
+    print("  clocks per iteration:", round(float((m[n - 1] - m[1]) / max(1, n - 2))))
+    out, lse = nat.flash_attention_fwd(qkv, 0, hd, 2 * hd, 1, S, H, D, scale, True)
+    dqkv = torch.empty_like(qkv)
+    t, t0, n = stamps(lambda tr: nat.flash_attention_bwd_dq(qkv, out, do, lse, dqkv, 1, S, H, D, scale, True, trace=tr))
+    print(f"backward (dQ pass), {H} heads: {n} key blocks of 32 in CTA 0")
+    show(t, t0, n, 0, (0, 1, 2, 3), "  MMA thread: iteration start | S and dP of block j+1 issued | dS_j there | dQ += dS_j K_j issued")
+    show(t, t0, n, 1, (0, 1, 2, 3, 5, 6, 4), "  element-wise warp: enter | S, dP there | loaded | P, dS computed | dS buffer free | dS in shared memory | P, dS in global memory")
+    m = t[0, :, 0].double()
+    print("  clocks per iteration:", round(float((m[n - 1] - m[1]) / max(1, n - 2))))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--peaks", default=os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json"))
     ap.add_argument("--out", default=None)
     ap.add_argument("--only", default=None, help="run only the rows whose name contains this text (profiler captures)")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--attention-trace", type=int, default=0, metavar="HEADS",
+                    help="print the clock stamps that the first CTA of the attention kernels records (forward and "
+                         "backward, sequence 2048, head dimension 256, this many heads) and exit")
     args = ap.parse_args()
     want = (lambda name: args.only is None or args.only in name)
     peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -74,6 +118,9 @@ def main():
         src = "measured"
     from popxl_addons_b200.ops import native as nat
 
+    if args.attention_trace:
+        attention_trace(nat, args.attention_trace)
+        return
     rows = []
     bf = torch.bfloat16
 

@@ -790,7 +790,10 @@ class Session:
         count = op.attrs["count"]
         want = op.attrs.get("cuda_graph") or (self.ir.options.capture_loops and count >= 3
                                               and self._capture_safe(graph))
-        if (want and self.device.type == "cuda" and self.num_local == 1 and self.ir.options.cuda_graphs
+        # values that live on another process (a pipeline stage of a replica spanning processes) are None here: such a
+        # loop exchanges them by send / recv and runs eagerly
+        local = all(v is not None and all(x is not None for x in v) for v in vals)
+        if (want and local and self.device.type == "cuda" and self.num_local == 1 and self.ir.options.cuda_graphs
                 and self.profile is None and op.uid not in self._uncapturable and not self._capturing):
             outs = self._run_repeat_captured(op, graph, vals, count)
             if outs is not None:

@@ -184,7 +184,7 @@ def test_gpu_rank_collectives():
 
 @pytest.mark.gpu
 @pytest.mark.multigpu
-@pytest.mark.parametrize("nproc,m,n,k", [(2, 1024, 1024, 1024), (2, 512, 2304, 320), (4, 1024, 1024, 1024),
+@pytest.mark.parametrize("nproc,m,n,k", [(2, 1024, 1024, 1024), (2, 512, 2304, 384), (4, 1024, 1024, 1024),
                                          (4, 2048, 4096, 1024)])
 def test_gpu_gemm_reduce_scatter_and_all_gather_gemm(nproc, m, n, k):
     """The tcgen05 GEMM fused with its collective, against NCCL + fp32 matmul on the same data, on 2 and 4 ranks and

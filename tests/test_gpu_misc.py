@@ -130,3 +130,21 @@ def test_row_statistics_kernels(nat):
         torch.testing.assert_close(nls.float(), want_nls, rtol=2e-2, atol=5e-2)
         back = nat.ce_nls_grad(nls, labels, off, scale.to(nls.dtype))
         torch.testing.assert_close(back.float(), xf.grad[:, off:off + sh.shape[1]], rtol=5e-2, atol=5e-3)
+
+
+@pytest.mark.parametrize("shape,axes,dtype", [((2048, 4096), [0], torch.bfloat16), ((300, 1024), [0], torch.float32),
+                                              ((2, 128, 264), [0, 1], torch.float16), ((2048, 16384), [0], torch.bfloat16)])
+def test_column_sums(nat, shape, axes, dtype):
+    """`sum` over the leading axes (bias gradients) against an fp32 sum of the same values; two launches give the
+    same bits (fixed order of additions)."""
+    torch.manual_seed(3)
+    a = torch.randn(*shape, device="cuda").to(dtype)
+    before = nat.LAUNCHES["by_kernel"].get("col_sum", 0)
+    got = nat.sum_cuda(a, axes, False)
+    assert got is not NotImplemented and nat.LAUNCHES["by_kernel"].get("col_sum", 0) == before + 1
+    want = a.float().sum(dim=axes)
+    rows = a.numel() // want.numel()
+    tol = {torch.float32: 1e-5, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[dtype] * (rows ** 0.5)
+    torch.testing.assert_close(got.float(), want, rtol=1e-2 if dtype != torch.float32 else 1e-5, atol=tol)
+    assert torch.equal(got, nat.sum_cuda(a, axes, False))
+    assert nat.sum_cuda(a, [len(shape) - 1], False) is NotImplemented  # trailing axes stay on the library path

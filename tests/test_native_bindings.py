@@ -95,9 +95,10 @@ def test_gemm_entry_points_reject_unsupported_arguments_on_the_host():
         v = {**ok, **kw}
         return native._gemm_pair(v["a"], v["b"], v["c"], v["M"], v["N"], v["K"], v["batch"], v["a_mn"], v["b_mn"],
                                  v["lda"], v["ldb"], v["ldc"], v["sa"], v["sb"], v["sc"], v["fp16"], v["cdt"], None, 0, 0,
-                                 v.get("accumulate", 0), None, 1.0, None, 0, None)
+                                 v.get("accumulate", 0), None, 1.0, None, 0, v.get("tile_n", 0), None)
 
-    assert pair(N=128) == -1              # narrow outputs stay on the single-CTA kernel
+    assert pair(N=64) == -1               # narrow outputs stay on the single-CTA kernel
+    assert pair(tile_n=192) == -1         # tiles are 256 or 128 columns wide
     assert pair(M=0) == -1
     assert pair(a=260) == -1              # operand not 16-byte aligned
     assert pair(lda=60) == -1             # leading dimension not a multiple of 8 elements
