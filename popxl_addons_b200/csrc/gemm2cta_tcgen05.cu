@@ -325,6 +325,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
       // touch 32 lines per instruction (and so would reading the old contents when accumulating). The chunk goes through
       // shared memory instead and leaves as whole 128-byte row pieces, four rows per instruction.
       const bool staged = p.epi.c_dtype == XL_F32 && (p.ldc % 4) == 0 && ((((uintptr_t)p.C) | ((uintptr_t)(p.batch_stride_c * 4))) & 15) == 0;
+      const bool staged16 = p.epi.c_dtype != XL_F32 && !p.epi.accumulate && (p.ldc % 8) == 0 &&
+                            ((((uintptr_t)p.C) | ((uintptr_t)(p.batch_stride_c * 2))) & 15) == 0;
       float4* stage = (float4*)(staging + (warp - 2) * (32 * 32 * 4));
       const int row_base = mb * PAIR_M + (int)rank * CTA_M + q * 32;
 #pragma unroll 1
@@ -334,6 +336,38 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         tmem_ld_wait();
         const int col0 = nb * PAIR_N + c;
         if (col0 >= p.N) continue;  // uniform over the warp
+        if (staged16 && col0 + 32 <= p.N) {
+          // 16-bit C, no accumulation: the thread's 32 columns (64 bytes) go to shared memory, 16-byte pieces rotated by
+          // the row pair so that neither phase has bank conflicts; then 4 lanes store one row's 64 bytes, 8 rows per
+          // instruction
+          uint4* stage16 = (uint4*)stage;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              float x = __uint_as_float(r[j * 8 + e]) * p.alpha;
+              if (p.epi.bias) {
+                const int col = col0 + j * 8 + e;
+                x += p.epi.bias_dtype == XL_F32 ? ((const float*)p.epi.bias)[col]
+                     : p.epi.bias_dtype == XL_BF16 ? __bfloat162float(((const __nv_bfloat16*)p.epi.bias)[col])
+                                                   : __half2float(((const __half*)p.epi.bias)[col]);
+              }
+              v[e] = apply_act(x, p.epi.act);
+            }
+            stage16[lane * 4 + ((j + (lane >> 1)) & 3)] = pack8_16bit(v, p.epi.c_dtype == XL_F16);
+          }
+          __syncwarp();
+          uint16_t* cbase16 = (uint16_t*)p.C + (long long)b * p.batch_stride_c + col0 + (lane & 3) * 8;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int lr = i * 8 + (lane >> 2), rr = row_base + lr;
+            const uint4 o = stage16[lr * 4 + (((lane & 3) + (lr >> 1)) & 3)];
+            if (rr < p.M) *(uint4*)(cbase16 + (long long)rr * p.ldc) = o;
+          }
+          __syncwarp();
+          continue;
+        }
         if (!(staged && col0 + 32 <= p.N)) {
           if (row_ok) epilogue_store_32cols(p.epi, r, crow, col0, p.alpha, mean_a, mean_b);
           continue;

@@ -116,3 +116,27 @@ def test_gemm_entry_points_reject_unsupported_arguments_on_the_host():
     assert single(b=516) == -1
     assert single(accumulate=4) == -1     # reduce-scatter needs the full entry point
     assert single(accumulate=3) < 0       # all-reduce without signal pads (or no driver to encode tensor maps)
+
+
+def test_attention_key_split_planner_on_the_host():
+    """The planner that divides a query block's keys over CTAs is host code: many heads keep one CTA per query block,
+    few heads are split so that the launch fills the SMs, and the split never produces an empty part."""
+    import ctypes
+
+    from popxl_addons_b200.ops import native
+
+    def plan(fn, B, S, H, D, sms=148):
+        items = ctypes.c_int(0)
+        chunk = fn(B, S, H, D, 1, sms, ctypes.byref(items))
+        return chunk, items.value
+
+    for fn, bkv in ((native._attn_plan, 64), (native._attn_bwd_plan, 32)):
+        chunk, items = plan(fn, 1, 2048, 16, 256)
+        assert chunk == 0 and items == 16                      # 256 CTAs already: no splitting
+        chunk, items = plan(fn, 1, 2048, 4, 256)
+        assert chunk >= 2 and 16 < items and 4 * items <= 2 * 148   # about one wave of CTAs
+        n_last = 2048 // bkv
+        assert -(-n_last // chunk) <= n_last                   # every part of the longest block has at least one key block
+        chunk, items = plan(fn, 1, 128, 1, 64)
+        assert chunk == 0 and items == 1                       # a single query block with two key blocks stays whole
+        assert fn(1, 2048, 4, 96, 1, 148, None) == -1          # unsupported head dimension
