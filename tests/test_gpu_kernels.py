@@ -59,10 +59,12 @@ def test_swiglu_and_silu(nat, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("cols", [768, 4096])
-def test_layer_norm_fwd_bwd(nat, dtype, cols):
+@pytest.mark.parametrize("rows,cols", [(300, 768), (300, 4096), (40, 4096), (2051, 2048)])
+def test_layer_norm_fwd_bwd(nat, dtype, rows, cols):
+    """Forward and backward against the fp32 reference: rows shorter and longer than one register tiling, fewer rows
+    than CTAs, a row count that is no multiple of the grid."""
     torch.manual_seed(2)
-    x = torch.randn(300, cols, device="cuda", dtype=dtype) * 2 + 0.5
+    x = torch.randn(rows, cols, device="cuda", dtype=dtype) * 2 + 0.5
     w = torch.randn(cols, device="cuda", dtype=dtype)
     b = torch.randn(cols, device="cuda", dtype=dtype)
     g = torch.randn_like(x)
@@ -74,7 +76,7 @@ def test_layer_norm_fwd_bwd(nat, dtype, cols):
     dx, dw, db = nat.layer_norm_grad_cuda(x, w, mean, rstd, g)
     rdx, rdw, rdb = _ref("layer_norm_grad")(x.float(), w.float(), rmean, rrstd, g.float())
     torch.testing.assert_close(dx.float(), rdx, **_tol(dtype))
-    big = dict(rtol=3e-2, atol=0.3) if dtype != torch.float32 else dict(rtol=1e-3, atol=1e-3)
+    big = dict(rtol=3e-2, atol=0.3 * max(1.0, (rows / 300) ** 0.5)) if dtype != torch.float32 else dict(rtol=1e-3, atol=2e-3)
     torch.testing.assert_close(dw.float(), rdw, **big)
     torch.testing.assert_close(db.float(), rdb, **big)
 
