@@ -559,7 +559,21 @@ def expand(t: Tensor, shape: Iterable[int]) -> Tensor:
     return emit1("expand", [t], {"shape": tuple(shape)})
 
 
-OpDef("tile", impl=lambda a, repeats: a.repeat(repeats))
+def _vjp_tile(ctx, op, gs):
+    """Gradient of `tile`: every element of the operand appears `prod(repeats)` times in the result, so its gradient is
+    the sum over the copies. The result is viewed as (r0, s0, r1, s1, ...) and the repeat axes are summed."""
+    x = op.inputs[0]
+    reps = tuple(op.attrs["repeats"])
+    shape = (1,) * (len(reps) - x.rank) + tuple(x.shape)
+    split = []
+    for r, n in zip(reps, shape):
+        split += [r, n]
+    g = reshape(gs[0], tuple(split))
+    g = sum(g, axis=list(range(0, 2 * len(reps), 2)), keepdims=False)
+    return [reshape(g, tuple(x.shape))]
+
+
+OpDef("tile", impl=lambda a, repeats: a.repeat(repeats), vjp=_vjp_tile)
 
 
 def tile(t: Tensor, repeats: Iterable[int]) -> Tensor:

