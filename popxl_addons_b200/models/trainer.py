@@ -20,7 +20,6 @@ import numpy as np
 import torch
 
 from .. import xl
-from ..graph import GraphWithNamedArgs
 from ..named_tensors import NamedTensors
 from ..ops.cross_entropy_sharded_loss import cross_entropy_sharded_with_grad
 from ..optimizers.adam import AdamOptimizerStep
@@ -30,7 +29,7 @@ from ..task_session import TaskSession
 from ..transforms.autodiff import autodiff_with_accumulation
 from ..transforms.recomputation import recompute_graph
 from ..streams import InputStreams, OutputStreams
-from ..layers.embedding import Embedding, model_vocab_offsets, model_vocab_shard_size
+from ..layers.embedding import model_vocab_offsets
 from ..xl import ops
 from .decoder import DecoderBlock, DecoderConfig, DecoderEmbedding, DecoderHead, _Parallel, rotary_tables
 
@@ -55,7 +54,6 @@ def build_optimizer(ir, cfg, par, groups, hp, state_dtype, shard_optimizer, fuse
     masters: Dict[str, xl.Variable] = {}
     opt_state = {}
     opt_graphs: Dict[tuple, tuple] = {}
-    from ..optimizers.rts_adam import RTSAdamStep
 
     fused_jobs = []  # (weight, accumulator, master shard, decay, name): emitted together below
     for group_name, wtree, atree in groups:

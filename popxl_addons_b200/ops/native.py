@@ -11,7 +11,6 @@ from typing import Dict, Optional, Tuple
 
 import torch
 
-from ..xl import dtypes as _dt
 from ..xl.opdef import FALLBACKS, OPS, STRICT, NativeFallback, native, note_fallback  # noqa: F401  (re-exported)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))

@@ -19,7 +19,6 @@ import torch
 from .. import xl
 from ..module import Module
 from ..xl.opdef import OPS, OpDef, emit1
-from ..xl.ops.var_updates import _adam_fused_ref
 
 __all__ = ["RTSAdamStep", "RTSAdamBucketStep", "rts_adam_", "rts_adam_bucket_", "rts_reduce_bucket_"]
 

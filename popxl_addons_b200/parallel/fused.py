@@ -9,7 +9,7 @@ import torch
 
 from ..xl.comm import DistComm
 from ..xl.core import ReplicaGrouping
-from .symm import LOCAL_SYNC_OFFSET, SymmArena
+from .symm import SymmArena
 
 _SMALL_ALL_REDUCE_ELEMS = 16384  # fp32 elements served by the one-shot kernel (64 KiB)
 _SMALL_ALL_REDUCE_16BIT_BYTES = 128 << 10  # 16-bit activations served by the one-shot multimem kernel
